@@ -1,0 +1,92 @@
+// Shared helpers of the sm_100a kernels: element types, conversions, reductions and
+// the C calling convention.
+//
+// Every exported function is `extern "C"`, takes raw device pointers, sizes and the
+// CUDA stream to launch on, allocates nothing and returns 0 or a cudaError_t value
+// (the launch error); the Python side turns a non-zero code into an exception.
+// Activations and weights are either float (the 32-bit path) or __nv_bfloat16; the
+// `dtype` argument says which: 0 = float32, 1 = bfloat16.  All arithmetic is fp32.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define PYRE_API extern "C" __attribute__((visibility("default")))
+
+enum PyreDType : int { PYRE_F32 = 0, PYRE_BF16 = 1 };
+
+// Error codes of argument checks (outside the cudaError_t range that launches return).
+#define PYRE_ERR_BAD_ARG 100001
+#define PYRE_ERR_UNSUPPORTED 100002
+
+#define PYRE_LAUNCH_CHECK()                      \
+    do {                                         \
+        cudaError_t e__ = cudaGetLastError();    \
+        if (e__ != cudaSuccess) return (int)e__; \
+    } while (0)
+
+template <typename T> struct ElemOps;
+
+template <> struct ElemOps<float> {
+    static __device__ __forceinline__ float load(const float* p) { return *p; }
+    static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+};
+
+template <> struct ElemOps<__nv_bfloat16> {
+    static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// A vector of N elements of T that is loaded and stored in one transaction.
+template <typename T, int N> struct alignas(sizeof(T) * N) Vec {
+    T v[N];
+};
+
+template <typename T, int N> __device__ __forceinline__ Vec<T, N> load_vec(const T* p) {
+    return *reinterpret_cast<const Vec<T, N>*>(p);
+}
+template <typename T, int N> __device__ __forceinline__ void store_vec(T* p, const Vec<T, N>& x) {
+    *reinterpret_cast<Vec<T, N>*>(p) = x;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The order of
+// the additions is fixed by the thread layout, so a row's result does not depend on
+// what else the launch holds.  `scratch` is 33 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < n_warps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+static inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }

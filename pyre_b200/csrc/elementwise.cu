@@ -1,0 +1,295 @@
+// Memory-bound kernels of the decoder step: embedding lookup, fused residual-add +
+// RMSNorm (with optional row gather), rotary tables, bias + rotary + paged K/V write,
+// and SiLU(gate) * up.  All arithmetic is fp32; `dtype` is the type of the
+// activations and of the cache (0 = float32, 1 = bfloat16).  The residual stream is
+// always float32.
+//
+// Formulas follow the reference's model code (Lalitaditya-tickoo/pyre):
+//   RMSNorm   pyre/model.py:33-38     rotary  pyre/model.py:41-63
+//   SwiGLU    pyre/model.py:128-139   embed   pyre/model.py:196
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// Embedding: x[t, :] = float(table[ids[t], :]).  An id outside [0, V) gives a zero row
+// and raises the error flag (the host checks ids first; this only guards memory).
+// ---------------------------------------------------------------------------
+template <typename T, int VEC>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
+                                 int H, int V, int* __restrict__ err) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* dst = x + (size_t)t * H;
+    if (id < 0 || id >= V) {
+        if (threadIdx.x == 0 && err) atomicExch(err, 1);
+        for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = 0.f;
+        return;
+    }
+    const T* src = table + (size_t)id * H;
+    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+        Vec<T, VEC> a = load_vec<T, VEC>(src + i);
+        Vec<float, VEC> o;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) o.v[k] = to_f32<T>(a.v[k]);
+        store_vec<float, VEC>(dst + i, o);
+    }
+}
+
+PYRE_API int pyre_embedding(const void* table, int dtype, const int* ids, float* x, int n_tokens, int H, int V,
+                            int* err_flag, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const bool vec = (H % 4 == 0);
+    const int threads = vec ? min(256, max(32, ((H / 4 + 31) / 32) * 32)) : 256;
+    if (dtype == PYRE_F32) {
+        if (vec) embedding_kernel<float, 4><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, x, H, V, err_flag);
+        else embedding_kernel<float, 1><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, x, H, V, err_flag);
+    } else if (dtype == PYRE_BF16) {
+        if (vec) embedding_kernel<__nv_bfloat16, 4><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, x, H, V, err_flag);
+        else embedding_kernel<__nv_bfloat16, 1><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, x, H, V, err_flag);
+    } else {
+        return PYRE_ERR_BAD_ARG;
+    }
+    PYRE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Fused residual add + RMSNorm.
+//   src = rows ? rows[r] : r
+//   v   = x[src] + (delta ? delta[src] : 0)          (fp32 sum)
+//   if update_x: x[src] = v                           (only without a row gather)
+//   out[r] = (v * (1 / sqrt(mean(v^2) + eps))) * w    (the reference's order of products)
+// One block per output row; the block size depends on H only, so a row's sum of
+// squares is added in the same order whatever the batch holds.
+// ---------------------------------------------------------------------------
+template <typename T, int VEC>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ w,
+                                   T* __restrict__ out, const int* __restrict__ rows, int H, float eps, int update_x) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    float* xr = x + (size_t)src * H;
+    const T* dr = delta ? delta + (size_t)src * H : nullptr;
+    T* orow = out + (size_t)r * H;
+
+    float ss = 0.f;
+    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+        Vec<float, VEC> a = load_vec<float, VEC>(xr + i);
+        if (dr) {
+            Vec<T, VEC> d = load_vec<T, VEC>(dr + i);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) a.v[k] = a.v[k] + to_f32<T>(d.v[k]);
+            if (update_x) store_vec<float, VEC>(xr + i, a);
+        }
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) ss = fmaf(a.v[k], a.v[k], ss);
+    }
+    const float total = block_sum(ss, scratch);
+    const float rstd = 1.0f / sqrtf(total / (float)H + eps);
+
+    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+        Vec<float, VEC> a = load_vec<float, VEC>(xr + i);
+        if (dr && !update_x) {
+            Vec<T, VEC> d = load_vec<T, VEC>(dr + i);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) a.v[k] = a.v[k] + to_f32<T>(d.v[k]);
+        }
+        Vec<float, VEC> g = load_vec<float, VEC>(w + i);
+        Vec<T, VEC> o;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) o.v[k] = from_f32<T>(__fmul_rn(__fmul_rn(a.v[k], rstd), g.v[k]));
+        store_vec<T, VEC>(orow + i, o);
+    }
+}
+
+PYRE_API int pyre_add_rmsnorm(float* x, const void* delta, const float* weight, void* out, const int* rows,
+                              int n_rows, int H, float eps, int update_x, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (rows && update_x) return PYRE_ERR_BAD_ARG;  // two output rows could name one source row
+    const bool vec = (H % 4 == 0);
+    const int per = vec ? H / 4 : H;
+    const int threads = min(512, max(32, ((per + 31) / 32) * 32));
+#define LAUNCH(TT, V) add_rmsnorm_kernel<TT, V><<<n_rows, threads, 0, stream>>>(x, (const TT*)delta, weight, (TT*)out, rows, H, eps, update_x)
+    if (dtype == PYRE_F32) { if (vec) LAUNCH(float, 4); else LAUNCH(float, 1); }
+    else if (dtype == PYRE_BF16) { if (vec) LAUNCH(__nv_bfloat16, 4); else LAUNCH(__nv_bfloat16, 1); }
+    else return PYRE_ERR_BAD_ARG;
+#undef LAUNCH
+    PYRE_LAUNCH_CHECK();
+    return 0;
+}
+
+// x[t, :] += delta[t, :] (fp32 sum), for a residual that no norm follows.
+template <typename T>
+__global__ void add_residual_kernel(float* __restrict__ x, const T* __restrict__ delta, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        x[i] = x[i] + to_f32<T>(delta[i]);
+}
+
+PYRE_API int pyre_add_residual(float* x, const void* delta, long long n, int dtype, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int threads = 256;
+    const int blocks = (int)min((long long)148 * 8, ceil_div_ll(n, threads));
+    if (dtype == PYRE_F32) add_residual_kernel<float><<<blocks, threads, 0, stream>>>(x, (const float*)delta, (size_t)n);
+    else if (dtype == PYRE_BF16) add_residual_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(x, (const __nv_bfloat16*)delta, (size_t)n);
+    else return PYRE_ERR_BAD_ARG;
+    PYRE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Rotary tables of one step: cos/sin[t, j] of angle = float(position[t]) * inv_freq[j],
+// all in fp32 (accurate sincosf; this file is never built with fast-math).  Computed
+// once per step and shared by every layer with the same rotary settings.
+// ---------------------------------------------------------------------------
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float* __restrict__ cos_out, float* __restrict__ sin_out, int n_tokens, int half) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_tokens * half) return;
+    const int t = i / half, j = i - t * half;
+    const float ang = __fmul_rn((float)positions[t], inv_freq[j]);
+    float s, c;
+    sincosf(ang, &s, &c);
+    cos_out[i] = c;
+    sin_out[i] = s;
+}
+
+PYRE_API int pyre_rope_table(const int* positions, const float* inv_freq, float* cos_out, float* sin_out,
+                             int n_tokens, int half, cudaStream_t stream) {
+    const long long n = (long long)n_tokens * half;
+    if (n <= 0) return 0;
+    rope_table_kernel<<<(int)ceil_div_ll(n, 256), 256, 0, stream>>>(positions, inv_freq, cos_out, sin_out, n_tokens, half);
+    PYRE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Bias + rotary + paged K/V write.
+//   qkv  [T, (nh + 2 nkv) * hd]   product of the fused q/k/v projection, no bias yet
+//   bias [(nh + 2 nkv) * hd] fp32 or null
+//   q_out[T, nh * hd]             rotated queries
+//   cache: one layer of a paged pool, [page][2 (K,V)][nkv][page_size][hd]
+//   slot_mapping[t] = page * page_size + offset of token t, or < 0: do not store
+// Rotation (half-split pairs over the first `rot` dims of a head, pyre/model.py:54-63):
+//   out[j]        = x[j] * cos[j]        - x[j + rot/2] * sin[j]
+//   out[j + rot/2] = x[j + rot/2] * cos[j] + x[j]        * sin[j]
+// computed in fp32 with separately rounded products, as the reference's fp32 path does.
+// Dims at and beyond `rot`, and the whole of v, pass through (plus bias).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void qkv_rope_write_kernel(const T* __restrict__ qkv, const float* __restrict__ bias,
+                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                      T* __restrict__ q_out, T* __restrict__ cache,
+                                      const int* __restrict__ slot_mapping, int nh, int nkv, int hd, int rot,
+                                      int page_size) {
+    const int t = blockIdx.x;
+    const int half = rot / 2;
+    const int chunks = hd / 4;
+    const int n_heads_all = nh + 2 * nkv;
+    const T* in = qkv + (size_t)t * n_heads_all * hd;
+    const float* ct = cos_t + (size_t)t * half;
+    const float* st = sin_t + (size_t)t * half;
+    const int slot = (cache && slot_mapping) ? slot_mapping[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0;
+    const int off = slot >= 0 ? slot - page * page_size : 0;
+
+    for (int item = threadIdx.x; item < n_heads_all * chunks; item += blockDim.x) {
+        const int h = item / chunks;
+        const int d0 = (item - h * chunks) * 4;
+        const bool is_v = h >= nh + nkv;
+        const bool is_k = !is_v && h >= nh;
+        // destination row of this head
+        T* dst;
+        if (!is_k && !is_v) {
+            dst = q_out + ((size_t)t * nh + h) * hd;
+        } else {
+            if (slot < 0) continue;
+            const int kvh = is_k ? h - nh : h - nh - nkv;
+            const size_t row = ((size_t)(page * 2 + (is_v ? 1 : 0)) * nkv + kvh) * page_size + off;
+            dst = cache + row * hd;
+        }
+        const T* src = in + (size_t)h * hd;
+        const float* b = bias ? bias + (size_t)h * hd : nullptr;
+        if (is_v || d0 >= rot) {
+            Vec<T, 4> a = load_vec<T, 4>(src + d0);
+            Vec<T, 4> o;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float v = to_f32<T>(a.v[k]);
+                if (b) v = v + b[d0 + k];
+                o.v[k] = from_f32<T>(v);
+            }
+            store_vec<T, 4>(dst + d0, o);
+        } else if (d0 < half) {
+            Vec<T, 4> a1 = load_vec<T, 4>(src + d0);
+            Vec<T, 4> a2 = load_vec<T, 4>(src + d0 + half);
+            Vec<T, 4> o1, o2;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float x1 = to_f32<T>(a1.v[k]);
+                float x2 = to_f32<T>(a2.v[k]);
+                if (b) { x1 = x1 + b[d0 + k]; x2 = x2 + b[d0 + half + k]; }
+                const float c = ct[d0 + k], s = st[d0 + k];
+                o1.v[k] = from_f32<T>(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(-x2, s)));
+                o2.v[k] = from_f32<T>(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s)));
+            }
+            store_vec<T, 4>(dst + d0, o1);
+            store_vec<T, 4>(dst + d0 + half, o2);
+        }  // chunks in [half, rot) are written by their partner
+    }
+}
+
+PYRE_API int pyre_qkv_rope_write(const void* qkv, const float* bias, const float* cos_t, const float* sin_t,
+                                 void* q_out, void* cache, const int* slot_mapping, int n_tokens, int nh, int nkv,
+                                 int hd, int rot, int page_size, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (hd % 8 || rot % 8 || rot > hd || rot < 0 || page_size <= 0) return PYRE_ERR_BAD_ARG;
+    const int items = (nh + 2 * nkv) * (hd / 4);
+    const int threads = min(256, max(32, ((items + 31) / 32) * 32));
+    if (dtype == PYRE_F32)
+        qkv_rope_write_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)qkv, bias, cos_t, sin_t, (float*)q_out, (float*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
+    else if (dtype == PYRE_BF16)
+        qkv_rope_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)qkv, bias, cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
+    else return PYRE_ERR_BAD_ARG;
+    PYRE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i],  silu(z) = z / (1 + exp(-z))  in fp32.
+// ---------------------------------------------------------------------------
+template <typename T, int VEC>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tokens, int I) {
+    const size_t per_row = (size_t)(I / VEC);
+    const size_t total = per_row * n_tokens;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / per_row;
+        const int i = (int)(idx - t * per_row) * VEC;
+        const T* row = gu + t * (size_t)(2 * I);
+        Vec<T, VEC> g = load_vec<T, VEC>(row + i);
+        Vec<T, VEC> u = load_vec<T, VEC>(row + I + i);
+        Vec<T, VEC> o;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            const float z = to_f32<T>(g.v[k]);
+            const float s = z / (1.0f + expf(-z));
+            o.v[k] = from_f32<T>(__fmul_rn(s, to_f32<T>(u.v[k])));
+        }
+        store_vec<T, VEC>(out + t * (size_t)I + i, o);
+    }
+}
+
+PYRE_API int pyre_silu_mul(const void* gu, void* out, int n_tokens, int I, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0 || I <= 0) return 0;
+    const int threads = 256;
+#define LAUNCH(TT, V)                                                                                      \
+    do {                                                                                                   \
+        long long total = (long long)n_tokens * (I / V);                                                   \
+        int blocks = (int)min((long long)148 * 16, ceil_div_ll(total, threads));                           \
+        silu_mul_kernel<TT, V><<<blocks, threads, 0, stream>>>((const TT*)gu, (TT*)out, n_tokens, I);      \
+    } while (0)
+    if (dtype == PYRE_F32) { if (I % 4 == 0) LAUNCH(float, 4); else LAUNCH(float, 1); }
+    else if (dtype == PYRE_BF16) { if (I % 8 == 0) LAUNCH(__nv_bfloat16, 8); else if (I % 4 == 0) LAUNCH(__nv_bfloat16, 4); else LAUNCH(__nv_bfloat16, 1); }
+    else return PYRE_ERR_BAD_ARG;
+#undef LAUNCH
+    PYRE_LAUNCH_CHECK();
+    return 0;
+}

@@ -1,0 +1,104 @@
+"""Trace replay: feed given token ids through a model step by step and write logits.
+
+It samples nothing and has no model code of its own: it opens the model folder through
+the registry, builds the same ``Model``, ``CacheManager`` and ``Stepper`` that generation
+uses, and calls ``Stepper.step`` once per line of its input.
+
+Input, one JSON object per line on standard input:
+
+    {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": ["b"]}
+
+``entries``: per request its next tokens and the places among them whose logits are
+wanted; all entries of a line are one batch.  An id seen for the first time begins a
+request.  ``end``: requests that are finished after this step; their pages and state slot
+go back to the pools.  For a step with wanted places the fp32 logits ``[wanted, vocab]``
+are written little-endian to ``<out>/<step>.f32``, in the order of the entries and of
+``want``.  After every step a line ``done <step>`` goes to standard output.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+from ..cache import CacheManager
+from ..config import load_config, architecture_of, parse_dtype
+from ..kernels import build
+from ..models.model import Model
+from .step import StepEntry, Stepper
+
+DEFAULT_PAGE_SIZE = 16
+MAX_LIVE_REQUESTS = 64
+
+
+def build_runtime(model_dir, dtype, max_tokens: int, page_size: int = DEFAULT_PAGE_SIZE,
+                  device: str = "cuda:0", max_requests: int = MAX_LIVE_REQUESTS, poison: bool = False):
+    """Model, cache manager and stepper for a model folder: the pieces every entry point shares."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("pyre_b200 needs a CUDA device (sm_100a); there is no CPU path")
+    dtype = parse_dtype(dtype)
+    config = load_config(model_dir)
+    spec = architecture_of(config).build(config)
+    model = Model(spec, dtype, device)
+    build.ensure_built(model.kernel_libraries())
+    model.load_weights(model_dir)
+    num_pages = max(1, -(-int(max_tokens) // page_size))
+    cache = CacheManager(model.kv_groups, model.state_groups, page_size, num_pages, max_requests, dtype, device)
+    cache.set_poison(poison)
+    stepper = Stepper(model, cache, max_positions=spec.max_positions or None)
+    return model, cache, stepper
+
+
+def replay(stepper: Stepper, lines, out_dir: Path, done=print) -> None:
+    cache = stepper.cache
+    out_dir.mkdir(parents=True, exist_ok=True)
+    for line in lines:
+        line = line.strip()
+        if not line:
+            continue
+        rec = json.loads(line)
+        step = rec["step"]
+        entries = []
+        for e in rec.get("entries", []):
+            rid = e["id"]
+            if rid not in cache.lengths:
+                cache.begin(rid)
+            entries.append(StepEntry(rid, e["tokens"], e.get("want", [])))
+        if entries:
+            logits = stepper.step(entries)
+            if logits.shape[0]:
+                logits.to("cpu").numpy().astype("<f4", copy=False).tofile(out_dir / f"{step}.f32")
+        for rid in rec.get("end", []):
+            cache.end(rid)
+        done(f"done {step}")
+    torch.cuda.synchronize()
+    stepper.check_device_errors()
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
+    ap.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
+    ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
+    ap.add_argument("--out", required=True, help="folder for the <step>.f32 files")
+    ap.add_argument("--max-tokens", type=int, required=True,
+                    help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
+    ap.add_argument("--page-size", type=int, default=DEFAULT_PAGE_SIZE, help="tokens per cache page (divides 64)")
+    ap.add_argument("--device", default="cuda:0")
+    ap.add_argument("--poison-freed-pages", action="store_true",
+                    help="debug: fill pages with NaN when they go back to the pool")
+    args = ap.parse_args(argv)
+    if 64 % args.page_size:
+        ap.error("--page-size must divide 64")
+    _, _, stepper = build_runtime(args.model, args.dtype, args.max_tokens, args.page_size, args.device,
+                                  poison=args.poison_freed_pages)
+
+    def done(msg):
+        sys.stdout.write(msg + "\n")
+        sys.stdout.flush()
+
+    replay(stepper, sys.stdin, Path(args.out), done)
+    return 0

@@ -1,0 +1,177 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A batch may hold portions of prompts beside single decoded tokens, cut anywhere.  The
+step runs only the tokens it is given, as one ragged batch, against the cache that
+earlier steps left, and returns fp32 logits at the wanted places.  The reference has
+two disjoint functions instead: one sequence with any number of tokens
+(``forward_paged``, pyre/model.py:250-294) or many sequences with one token each
+(``forward_paged_batch``, pyre/model.py:296-342).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Hashable, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, OutOfPages
+from ..kernels import lib
+from ..models.model import Model
+from .context import KVView, StateView, StepContext
+
+
+@dataclass
+class StepEntry:
+    """The next tokens of one live request and the places among them whose logits are wanted."""
+
+    request: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=tuple)
+
+
+class _Staging:
+    """Pinned host buffers for the step's integer arrays: one copy to the device per step.
+    Two buffers alternate; a buffer is rewritten only after its last copy has finished."""
+
+    def __init__(self, device):
+        self.device = device
+        self.bufs = [None, None]
+        self.events = [None, None]
+        self.turn = 0
+
+    def upload(self, flat: np.ndarray) -> torch.Tensor:
+        i = self.turn
+        self.turn ^= 1
+        n = flat.shape[0]
+        if self.bufs[i] is None or self.bufs[i].shape[0] < n:
+            self.bufs[i] = torch.empty(max(n, 4096) * 2, dtype=torch.int32, pin_memory=True)
+            self.events[i] = None
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        host = self.bufs[i][:n]
+        host.numpy()[:] = flat
+        dev = torch.empty(n, dtype=torch.int32, device=self.device)
+        dev.copy_(host, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+        return dev
+
+
+class Stepper:
+    """Binds a model to a cache manager and runs steps."""
+
+    def __init__(self, model: Model, cache: CacheManager, max_positions: "int | None" = None):
+        self.model, self.cache = model, cache
+        self.device = model.device
+        self.max_positions = max_positions
+        self._staging = _Staging(self.device)
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.steps_run = 0
+
+    def build_context(self, entries: Sequence[StepEntry], reserve: bool = True) -> StepContext:
+        """Check the entries, make room in the cache (unless the caller has) and lay the
+        batch out flat.  Raises OutOfPages if a pool is too small; nothing is taken then."""
+        cache = self.cache
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        seen = set()
+        vocab = self.model.vocab_size
+        starts, counts = [], []
+        for e in entries:
+            if e.request in seen:
+                raise ValueError(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.request!r}: an entry needs at least one token")
+            toks = np.asarray(e.tokens)
+            if toks.min() < 0 or toks.max() >= vocab:
+                raise ValueError(f"request {e.request!r}: token id outside [0, {vocab})")
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {e.request!r}: wanted place {w} outside its {n} tokens")
+            start = cache.length(e.request)
+            if self.max_positions is not None and start + n > self.max_positions:
+                raise ValueError(f"request {e.request!r}: {start + n} tokens exceed the model's "
+                                 f"{self.max_positions} positions")
+            starts.append(start)
+            counts.append(n)
+        if reserve:
+            taken = []
+            for e, s, n in zip(entries, starts, counts):
+                if not cache.reserve(e.request, s + n):
+                    # nothing of this step stays half-reserved in a way that matters: pages
+                    # taken for earlier entries remain theirs and are used by a later step
+                    raise OutOfPages(f"request {e.request!r}: no pages left to grow from {s} to {s + n} tokens "
+                                     f"(free pages per group: {cache.stats().pages_free})")
+                taken.append(e.request)
+
+        B = len(entries)
+        T = int(sum(counts))
+        cu = np.zeros(B + 1, dtype=np.int32)
+        cu[1:] = np.cumsum(counts)
+        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        positions = np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(starts, counts)])
+        seq_of_token = np.repeat(np.arange(B, dtype=np.int32), counts)
+        rows = [cu[b] + w for b, e in enumerate(entries) for w in e.want]
+        logit_rows = np.asarray(rows, dtype=np.int32)
+        reqs = [e.request for e in entries]
+
+        pieces = [token_ids, positions, seq_of_token, cu, logit_rows]
+        tables = []
+        for g in range(len(cache.groups)):
+            slots = np.concatenate([cache.slots_for(g, e.request, s, n) for e, s, n in zip(entries, starts, counts)])
+            table = cache.block_table_rows(g, reqs)
+            tables.append(table.shape)
+            pieces += [slots, table.reshape(-1)]
+        state_slots = np.asarray([cache.state.slot_of[r] for r in reqs], dtype=np.int32)
+        pieces.append(state_slots)
+
+        # every piece starts on a 16-byte boundary of the flat buffer
+        offsets, total = [], 0
+        for p in pieces:
+            offsets.append(total)
+            total += -(-p.shape[0] // 4) * 4
+        flat = np.zeros(max(total, 4), dtype=np.int32)
+        for o, p in zip(offsets, pieces):
+            flat[o:o + p.shape[0]] = p
+        dev = self._staging.upload(flat)
+
+        def view(i):
+            return dev[offsets[i]:offsets[i] + pieces[i].shape[0]]
+
+        ctx = StepContext(
+            dtype=self.model.dtype, device=self.device, num_tokens=T, num_seqs=B, num_logit_rows=len(rows),
+            token_ids=view(0), positions=view(1), seq_of_token=view(2), cu_seqlens=view(3), logit_rows=view(4),
+            cu_seqlens_host=cu, start_pos_host=np.asarray(starts, dtype=np.int64), error_flag=self.error_flag)
+        k = 5
+        for g, group in enumerate(cache.groups):
+            ctx.kv_groups.append(KVView(group.pool, view(k + 1).view(tables[g]), view(k), group.page_size,
+                                        group.spec.window))
+            k += 2
+        slots_dev = view(k)
+        for buf in cache.state.buffers:
+            ctx.state_groups.append(StateView(buf, slots_dev, state_slots))
+        ctx._entries = entries  # type: ignore[attr-defined]
+        ctx._new_lens = [s + n for s, n in zip(starts, counts)]  # type: ignore[attr-defined]
+        return ctx
+
+    def run_context(self, ctx: StepContext) -> torch.Tensor:
+        logits = self.model.forward(ctx)
+        for e, new_len in zip(ctx._entries, ctx._new_lens):  # type: ignore[attr-defined]
+            self.cache.commit(e.request, new_len)
+        self.steps_run += 1
+        return logits
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """fp32 logits [R, vocab] on the device, R = total number of wanted places, in the
+        order of the entries and of each entry's ``want``."""
+        return self.run_context(self.build_context(entries))
+
+    def check_device_errors(self) -> None:
+        if int(self.error_flag.item()) != 0:
+            self.error_flag.zero_()
+            raise lib.KernelError("a kernel met an index outside its range (token id outside the vocabulary)")

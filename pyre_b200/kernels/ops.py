@@ -1,0 +1,264 @@
+"""The kernels as Python functions over torch tensors.
+
+Each function checks shapes, dtypes, contiguity and device, then launches the CUDA
+kernel on torch's current stream.  A size the kernels do not take is refused with a
+clear error; nothing here computes on the CPU or falls back to a library.
+
+The matrix products of the bfloat16 path are the one place where a library stands in
+(cuBLAS through ``torch``), as the reference's engine uses one for every projection
+(``nn.Linear``, pyre/model.py:84-87,133-135,172); see ``linear``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import lib
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class UnsupportedSize(ValueError):
+    """A configuration whose sizes the kernels refuse."""
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: "torch.Tensor | None") -> "int | None":
+    return None if t is None else t.data_ptr()
+
+
+def _check(t: torch.Tensor, name: str, dtype=None, dim: "int | None" = None) -> None:
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (pyre_b200 has no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous, got strides {t.stride()} for shape {tuple(t.shape)}")
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+    if dim is not None and t.dim() != dim:
+        raise ValueError(f"{name} must have {dim} dimensions, got shape {tuple(t.shape)}")
+
+
+def _dt(dtype: torch.dtype) -> int:
+    try:
+        return _DT[dtype]
+    except KeyError:
+        raise ValueError(f"activations must be float32 or bfloat16, got {dtype}") from None
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: "torch.Tensor | None" = None,
+              err_flag: "torch.Tensor | None" = None) -> torch.Tensor:
+    """x[t] = float32(table[ids[t]]); ids int32 [T]; returns the fp32 residual stream [T, H]."""
+    _check(table, "table", dim=2)
+    _check(ids, "ids", torch.int32, 1)
+    V, H = table.shape
+    T = ids.shape[0]
+    if out is None:
+        out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    else:
+        _check(out, "out", torch.float32, 2)
+    lib.call("pyre_embedding", table.data_ptr(), _dt(table.dtype), ids.data_ptr(), out.data_ptr(), T, H, V,
+             _ptr(err_flag), _stream())
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, delta: "torch.Tensor | None", weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: "torch.Tensor | None" = None, update_x: bool = True,
+                out: "torch.Tensor | None" = None) -> torch.Tensor:
+    """out[r] = rmsnorm(x[src] + delta[src]) * weight with src = rows[r] (or r).
+
+    ``x`` is the fp32 residual stream [T, H]; with ``update_x`` (and no ``rows``) the sum is
+    written back to it.  ``delta`` has the activation dtype.  ``weight`` is fp32 [H]."""
+    _check(x, "x", torch.float32, 2)
+    _check(weight, "weight", torch.float32, 1)
+    T, H = x.shape
+    if weight.shape[0] != H:
+        raise ValueError(f"norm weight has {weight.shape[0]} entries, rows have {H}")
+    if delta is not None:
+        _check(delta, "delta", out_dtype, 2)
+        if tuple(delta.shape) != (T, H):
+            raise ValueError(f"delta shape {tuple(delta.shape)} != x shape {(T, H)}")
+    n_rows = T
+    if rows is not None:
+        _check(rows, "rows", torch.int32, 1)
+        n_rows = rows.shape[0]
+        update_x = False
+    if out is None:
+        out = torch.empty((n_rows, H), dtype=out_dtype, device=x.device)
+    else:
+        _check(out, "out", out_dtype, 2)
+    lib.call("pyre_add_rmsnorm", x.data_ptr(), _ptr(delta), weight.data_ptr(), out.data_ptr(), _ptr(rows),
+             n_rows, H, float(eps), int(bool(update_x and delta is not None)), _dt(out_dtype), _stream())
+    return out
+
+
+def add_residual(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    _check(x, "x", torch.float32)
+    _check(delta, "delta")
+    if x.shape != delta.shape:
+        raise ValueError("x and delta differ in shape")
+    lib.call("pyre_add_residual", x.data_ptr(), delta.data_ptr(), x.numel(), _dt(delta.dtype), _stream())
+    return x
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor):
+    """cos, sin fp32 [T, rot/2] of float(position) * inv_freq."""
+    _check(positions, "positions", torch.int32, 1)
+    _check(inv_freq, "inv_freq", torch.float32, 1)
+    T, half = positions.shape[0], inv_freq.shape[0]
+    cos = torch.empty((T, half), dtype=torch.float32, device=positions.device)
+    sin = torch.empty_like(cos)
+    lib.call("pyre_rope_table", positions.data_ptr(), inv_freq.data_ptr(), cos.data_ptr(), sin.data_ptr(), T, half,
+             _stream())
+    return cos, sin
+
+
+def qkv_rope_write(qkv: torch.Tensor, bias: "torch.Tensor | None", cos: torch.Tensor, sin: torch.Tensor,
+                   cache_layer: "torch.Tensor | None", slot_mapping: "torch.Tensor | None",
+                   n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int, page_size: int,
+                   q_out: "torch.Tensor | None" = None) -> torch.Tensor:
+    """Bias, rotary and the paged K/V write in one pass; returns rotated q [T, nh*hd].
+
+    ``cache_layer``: [pages, 2, nkv, page_size, hd] of the activation dtype, or None to
+    store nothing (a layer that reads another layer's cache)."""
+    _check(qkv, "qkv", dim=2)
+    T = qkv.shape[0]
+    width = (n_heads + 2 * n_kv_heads) * head_dim
+    if qkv.shape[1] != width:
+        raise ValueError(f"qkv has {qkv.shape[1]} columns, expected (nh + 2 nkv) * hd = {width}")
+    if head_dim % 8 or rotary_dim % 8 or not 0 <= rotary_dim <= head_dim:
+        raise UnsupportedSize(f"head_dim ({head_dim}) and rotary_dim ({rotary_dim}) must be multiples of 8, "
+                              f"rotary_dim <= head_dim")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != width:
+            raise ValueError(f"qkv bias has {bias.shape[0]} entries, expected {width}")
+    half = rotary_dim // 2
+    if rotary_dim:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if tuple(cos.shape) != (T, half) or tuple(sin.shape) != (T, half):
+            raise ValueError(f"cos/sin must be [{T}, {half}], got {tuple(cos.shape)}")
+    if cache_layer is not None:
+        _check(cache_layer, "cache_layer", qkv.dtype, 5)
+        if tuple(cache_layer.shape[1:]) != (2, n_kv_heads, page_size, head_dim):
+            raise ValueError(f"cache layer shape {tuple(cache_layer.shape)} does not match "
+                             f"[pages, 2, {n_kv_heads}, {page_size}, {head_dim}]")
+        if slot_mapping is None:
+            raise ValueError("slot_mapping is required with a cache")
+        _check(slot_mapping, "slot_mapping", torch.int32, 1)
+        if slot_mapping.shape[0] != T:
+            raise ValueError("slot_mapping must have one entry per token")
+    if q_out is None:
+        q_out = torch.empty((T, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    lib.call("pyre_qkv_rope_write", qkv.data_ptr(), _ptr(bias), _ptr(cos) if rotary_dim else None,
+             _ptr(sin) if rotary_dim else None, q_out.data_ptr(), _ptr(cache_layer),
+             _ptr(slot_mapping) if cache_layer is not None else None, T, n_heads, n_kv_heads, head_dim,
+             rotary_dim, page_size, _dt(qkv.dtype), _stream())
+    return q_out
+
+
+def silu_mul(gate_up: torch.Tensor, out: "torch.Tensor | None" = None) -> torch.Tensor:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _check(gate_up, "gate_up", dim=2)
+    T, two_i = gate_up.shape
+    if two_i % 2:
+        raise ValueError("gate_up must have an even number of columns")
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty((T, inter), dtype=gate_up.dtype, device=gate_up.device)
+    lib.call("pyre_silu_mul", gate_up.data_ptr(), out.data_ptr(), T, inter, _dt(gate_up.dtype), _stream())
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: "torch.Tensor | None" = None, seeds: "torch.Tensor | None" = None,
+           token_index: "torch.Tensor | None" = None, out: "torch.Tensor | None" = None) -> torch.Tensor:
+    """One token id per row of fp32 logits [R, V]: argmax where temperature is 0, else Gumbel-max."""
+    if logits.dim() != 2 or logits.dtype != torch.float32 or not logits.is_cuda or logits.stride(1) != 1:
+        raise ValueError("logits must be a CUDA float32 matrix with contiguous rows")
+    R, V = logits.shape
+    if temperature is not None:
+        _check(temperature, "temperature", torch.float32, 1)
+        if seeds is None or token_index is None:
+            raise ValueError("temperature sampling needs seeds and token_index")
+        _check(seeds, "seeds", torch.int64, 1)
+        _check(token_index, "token_index", torch.int32, 1)
+        if not (temperature.shape[0] == seeds.shape[0] == token_index.shape[0] == R):
+            raise ValueError("temperature, seeds and token_index need one entry per row")
+    if out is None:
+        out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    lib.call("pyre_sample", logits.data_ptr(), logits.stride(0), _ptr(temperature), _ptr(seeds), _ptr(token_index),
+             out.data_ptr(), R, V, _stream())
+    return out
+
+
+def paged_attention_generic(q: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor,
+                            seq_of_token: torch.Tensor, positions: torch.Tensor, n_heads: int, n_kv_heads: int,
+                            head_dim: int, scale: float, window: "int | None" = None,
+                            out: "torch.Tensor | None" = None) -> torch.Tensor:
+    """Exact fp32-arithmetic attention of every query token over its sequence's pages."""
+    _check(q, "q", dim=2)
+    _check(cache_layer, "cache_layer", q.dtype, 5)
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    _check(positions, "positions", torch.int32, 1)
+    T = q.shape[0]
+    if q.shape[1] != n_heads * head_dim:
+        raise ValueError(f"q has {q.shape[1]} columns, expected nh * hd = {n_heads * head_dim}")
+    if head_dim % 16 or head_dim > 256:
+        raise UnsupportedSize(f"head_dim {head_dim}: the attention kernels take multiples of 16 up to 256")
+    if n_heads % n_kv_heads:
+        raise UnsupportedSize(f"{n_heads} query heads cannot be shared among {n_kv_heads} key/value heads")
+    page_size = cache_layer.shape[3]
+    if tuple(cache_layer.shape[1:]) != (2, n_kv_heads, page_size, head_dim):
+        raise ValueError(f"cache layer shape {tuple(cache_layer.shape)} does not match the head sizes")
+    if out is None:
+        out = torch.empty_like(q)
+    lib.call("pyre_paged_attention_generic", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(),
+             block_table.data_ptr(), block_table.stride(0), seq_of_token.data_ptr(), positions.data_ptr(), T,
+             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), _dt(q.dtype), _stream())
+    return out
+
+
+def sgemm_nt(a: torch.Tensor, w: torch.Tensor, bias: "torch.Tensor | None" = None,
+             out: "torch.Tensor | None" = None) -> torch.Tensor:
+    """C = A W^T (+ bias) in IEEE fp32 on the CUDA cores; a [M, K], w [N, K]."""
+    for t, n in ((a, "a"), (w, "w")):
+        if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+            raise ValueError(f"{n} must be a CUDA float32 matrix with contiguous rows")
+    M, K = a.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise ValueError(f"inner sizes differ: a is [{M}, {K}], w is [{N}, {K2}]")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    lib.call("pyre_sgemm_nt", a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0),
+             _ptr(bias), M, N, K, _stream())
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: "torch.dtype | None" = None) -> torch.Tensor:
+    """y = x W^T for a weight in the linear-layer layout [out, in].
+
+    float32: the package's own fp32 kernel (no reduced-precision matrix mode).
+    bfloat16: a library product with fp32 accumulation; ``out_dtype=torch.float32`` keeps
+    the accumulator's precision (used for the logits)."""
+    if x.dtype == torch.float32:
+        return sgemm_nt(x, w)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise ValueError(f"linear: unsupported dtypes {x.dtype} x {w.dtype}")
+    if out_dtype is None or out_dtype == torch.bfloat16:
+        return torch.mm(x, w.t())
+    return torch.mm(x, w.t(), out_dtype=out_dtype)
+
+
+def required_libraries(dtype: torch.dtype) -> list[str]:
+    """Kernel libraries that a decoder step in ``dtype`` calls (built before the first step)."""
+    libs = ["elementwise", "sampling", "attention_generic"]
+    if dtype == torch.float32:
+        libs.append("gemm_f32")
+    return libs

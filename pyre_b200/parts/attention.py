@@ -1,0 +1,95 @@
+"""Grouped-query attention over the paged cache (pyre/model.py:75-125 for the math,
+pyre/model.py:296-342 and pyre/kernels/paged_attn.py for reading pages in place)."""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights.specs import TensorSpec
+from .base import PagedKVSpec, Part, PartSpec, make_part, register_part
+
+
+class Attention(Part):
+    """q, k, v projections (stacked into one product), position encoding on q and k,
+    keys and values written to the pages of this call's cache layer, attention of every
+    token of the step over its sequence's cached keys, output projection.
+
+    Parameters: ``width`` (model width), ``n_heads``, ``n_kv_heads``, ``head_dim``
+    (``n_heads * head_dim`` need not equal ``width``), ``qkv_bias`` / ``o_bias``,
+    ``scale`` (default head_dim^-0.5, pyre/model.py:82), ``window`` (None = all keys)
+    and ``position``, the PartSpec of the position encoding applied to q and k.
+    A query at position p sees keys max(0, p - window + 1)..p.
+    """
+
+    def __init__(self, dtype, device, width: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                 position: "PartSpec | None" = None, qkv_bias: bool = True, o_bias: bool = False,
+                 scale: "float | None" = None, window: "int | None" = None):
+        super().__init__(dtype, device)
+        self.width, self.n_heads, self.n_kv_heads, self.head_dim = int(width), int(n_heads), int(n_kv_heads), int(head_dim)
+        if self.n_heads % self.n_kv_heads:
+            raise ops.UnsupportedSize(f"{n_heads} query heads cannot be shared among {n_kv_heads} key/value heads")
+        if self.head_dim % 16 or not 16 <= self.head_dim <= 256:
+            raise ops.UnsupportedSize(f"head_dim {head_dim}: the attention kernels take multiples of 16 from 16 to 256")
+        if o_bias:
+            raise ops.UnsupportedSize("an output-projection bias is not implemented")
+        if window is not None and window <= 0:
+            raise ValueError("window must be positive or None")
+        self.qkv_bias = bool(qkv_bias)
+        self.scale = float(scale) if scale is not None else self.head_dim ** -0.5
+        self.window = window
+        self.position = make_part("position", position or PartSpec("none"), dtype, device)
+        self.w_qkv = self.b_qkv = self.w_o = None
+
+    def children(self):
+        return {}  # the position encodings built so far own no tensors
+
+    def tensors(self):
+        q, kv = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        t = {
+            "q_proj.weight": TensorSpec((q, self.width)),
+            "k_proj.weight": TensorSpec((kv, self.width)),
+            "v_proj.weight": TensorSpec((kv, self.width)),
+            "o_proj.weight": TensorSpec((self.width, q)),
+        }
+        if self.qkv_bias:
+            t["q_proj.bias"] = TensorSpec((q,), role="vector")
+            t["k_proj.bias"] = TensorSpec((kv,), role="vector")
+            t["v_proj.bias"] = TensorSpec((kv,), role="vector")
+        # checkpoint order: weight then bias per projection, o last
+        order = ["q_proj.weight", "q_proj.bias", "k_proj.weight", "k_proj.bias", "v_proj.weight", "v_proj.bias",
+                 "o_proj.weight"]
+        return {k: t[k] for k in order if k in t}
+
+    def load(self, tensors):
+        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]],
+                               dim=0).contiguous()
+        if self.qkv_bias:
+            self.b_qkv = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]]).contiguous()
+        self.w_o = tensors["o_proj.weight"]
+
+    def kernel_libraries(self):
+        libs = ["elementwise", "attention_generic"] + self.position.kernel_libraries()
+        if self.dtype == torch.float32:
+            libs.append("gemm_f32")
+        return libs
+
+    def cache_spec(self):
+        return PagedKVSpec(self.n_kv_heads, self.head_dim, self.window)
+
+    def state_spec(self):
+        return None
+
+    def forward(self, ctx, h, call):
+        kv = ctx.kv_group(call.kv_group)
+        layer = kv.pool[call.kv_layer]
+        qkv = ops.linear(h, self.w_qkv)
+        cos, sin = self.position.tables(ctx)
+        q = ops.qkv_rope_write(qkv, self.b_qkv, cos, sin, layer if call.kv_write else None, kv.slot_mapping,
+                               self.n_heads, self.n_kv_heads, self.head_dim, self.position.rotary_dim, kv.page_size)
+        a = ops.paged_attention_generic(q, layer, kv.block_table, ctx.seq_of_token, ctx.positions, self.n_heads,
+                                        self.n_kv_heads, self.head_dim, self.scale, self.window)
+        return ops.linear(a, self.w_o)
+
+
+register_part("mixer", "attention", Attention)

@@ -1,0 +1,151 @@
+"""The vocabulary of model parts.
+
+A model is put together from parts of seven categories: ``embed``, ``norm``,
+``position``, ``mixer``, ``ffn``, ``block`` and ``head``.  A part
+
+* is described by data: ``PartSpec(kind, params)``; ``kind`` is looked up in the
+  registry of its category, ``params`` are the sizes and constants it is built with
+  (a part never reads a model configuration and never knows which model it is in);
+* lists the checkpoint tensors it owns (``tensors()``: local name -> ``TensorSpec``);
+* takes them on the device (``load``), packing them as its kernels want;
+* computes on a ``StepContext`` (``pyre_b200.engine.context``), the flat batch of one step.
+
+Interfaces by category (``ctx`` is the StepContext, T its number of tokens):
+
+    embed     forward(ctx) -> x                     fp32 residual stream [T, width]
+    norm      forward(ctx, x, delta=None, rows=None, update_x=True) -> h
+              h = norm(x + delta) in the activation dtype; writes the sum back to x
+              when update_x; with rows, only those rows (gathered), x untouched
+    position  tables(ctx) -> per-step tensors the mixer hands to its kernels
+    mixer     forward(ctx, h, call) -> [T, width]    ``call`` (BoundCall) names the cache
+              layer or state layer of this use of the mixer; cache_spec()/state_spec()
+              say what it needs from the cache manager
+    ffn       forward(ctx, h) -> [T, width]
+    block     forward(ctx, x, pending, call) -> (x, pending)   ``pending`` is a branch
+              output not yet added to x; the next norm adds it (fused)
+    head      forward(ctx, h_rows) -> fp32 logits [R, vocab]
+
+A new part is a class with these methods and one ``register_part`` call; nothing else
+in the package has to change.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Mapping
+
+import torch
+
+from ..weights.specs import TensorSpec
+
+CATEGORIES = ("embed", "norm", "position", "mixer", "ffn", "block", "head")
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    kind: str
+    params: Mapping[str, Any] = field(default_factory=dict)
+
+    def __hash__(self):
+        return hash((self.kind, repr(sorted(self.params.items(), key=lambda kv: kv[0]))))
+
+
+@dataclass(frozen=True)
+class PagedKVSpec:
+    """What an attention-like mixer needs from the paged cache: per token and layer,
+    keys and values of ``n_kv_heads * head_dim`` elements each.  ``window``: only the
+    last ``window`` positions are ever read (None = all), so older pages may be given back."""
+
+    n_kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """State of fixed size per request and per use of the mixer, kept across steps in a
+    slot of the cache manager; it starts as zeros when a request begins."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class BoundCall:
+    """One entry of the layer schedule, resolved against the cache manager's groups."""
+
+    index: int                 # position in the schedule
+    block: int                 # which block's weights
+    kv_group: int | None = None
+    kv_layer: int = 0          # layer index inside the group's pool
+    kv_write: bool = True      # False: read what another call wrote
+    state_group: int | None = None
+    state_layer: int = 0
+
+
+class Part:
+    category: str = ""
+
+    def __init__(self, dtype: torch.dtype, device: torch.device):
+        self.dtype = dtype
+        self.device = device
+
+    def tensors(self) -> dict[str, TensorSpec]:
+        return {}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        """Take the tensors named by ``tensors()`` (already on the device, already in
+        their roles' dtypes)."""
+
+    def kernel_libraries(self) -> list[str]:
+        return []
+
+    def children(self) -> "dict[str, Part]":
+        """Sub-parts by the name prefix of their tensors."""
+        return {}
+
+
+_REGISTRY: dict[str, dict[str, Callable[..., Part]]] = {c: {} for c in CATEGORIES}
+
+
+def register_part(category: str, kind: str, cls: Callable[..., Part], *, replace: bool = False) -> None:
+    if category not in _REGISTRY:
+        raise ValueError(f"unknown part category {category!r}; categories: {CATEGORIES}")
+    if kind in _REGISTRY[category] and not replace:
+        raise ValueError(f"{category} part {kind!r} is already registered")
+    _REGISTRY[category][kind] = cls
+
+
+def registered_parts(category: str) -> list[str]:
+    return sorted(_REGISTRY[category])
+
+
+def make_part(category: str, spec: PartSpec, dtype: torch.dtype, device) -> Part:
+    try:
+        cls = _REGISTRY[category][spec.kind]
+    except KeyError:
+        raise ValueError(f"unknown {category} part {spec.kind!r}; registered: {registered_parts(category)}") from None
+    part = cls(dtype=dtype, device=torch.device(device), **dict(spec.params))
+    part.category = category
+    return part
+
+
+def collect_tensors(part: Part, prefix: str = "") -> dict[str, TensorSpec]:
+    """Full names of a part's tensors and of its sub-parts', under ``prefix``."""
+    out = {prefix + name: spec for name, spec in part.tensors().items()}
+    for sub_prefix, child in part.children().items():
+        out.update(collect_tensors(child, prefix + sub_prefix))
+    return out
+
+
+def load_part(part: Part, tensors: Mapping[str, torch.Tensor], prefix: str = "") -> None:
+    part.load({name: tensors[prefix + name] for name in part.tensors()})
+    for sub_prefix, child in part.children().items():
+        load_part(child, tensors, prefix + sub_prefix)
+
+
+def collect_libraries(part: Part) -> list[str]:
+    libs = list(part.kernel_libraries())
+    for child in part.children().values():
+        libs += collect_libraries(child)
+    return libs

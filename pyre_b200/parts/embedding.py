@@ -1,0 +1,58 @@
+"""Token embedding (pyre/model.py:162,196) and the output head (pyre/model.py:172,201)."""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights.specs import TensorSpec
+from .base import Part, register_part
+
+
+class TokenEmbedding(Part):
+    """x[t] = table[token[t]], widened to the fp32 residual stream."""
+
+    def __init__(self, dtype, device, vocab: int, width: int):
+        super().__init__(dtype, device)
+        self.vocab, self.width = int(vocab), int(width)
+        self.table = None
+
+    def tensors(self):
+        return {"weight": TensorSpec((self.vocab, self.width))}
+
+    def load(self, tensors):
+        self.table = tensors["weight"]
+
+    def kernel_libraries(self):
+        return ["elementwise"]
+
+    def forward(self, ctx):
+        return ops.embedding(self.table, ctx.token_ids, err_flag=ctx.error_flag)
+
+
+class LinearHead(Part):
+    """fp32 logits = h W^T for the rows that were asked for.  ``tied_to`` names the
+    tensor (full checkpoint name) that stands in when the head's own weight is absent:
+    the embedding table of a model with tied embeddings (pyre/loader.py:58-61); the
+    storage is then shared, not copied."""
+
+    def __init__(self, dtype, device, vocab: int, width: int, tied_to: "str | None" = None):
+        super().__init__(dtype, device)
+        self.vocab, self.width, self.tied_to = int(vocab), int(width), tied_to
+        self.weight = None
+
+    def tensors(self):
+        return {"weight": TensorSpec((self.vocab, self.width), optional_alias=self.tied_to)}
+
+    def load(self, tensors):
+        self.weight = tensors["weight"]
+
+    def kernel_libraries(self):
+        return ["gemm_f32"] if self.dtype == torch.float32 else []
+
+    def forward(self, ctx, h_rows):
+        return ops.linear(h_rows, self.weight, out_dtype=torch.float32)
+
+
+register_part("embed", "token_embedding", TokenEmbedding)
+register_part("head", "linear_head", LinearHead)

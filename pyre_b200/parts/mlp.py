@@ -1,0 +1,43 @@
+"""Dense gated feed-forward (SwiGLU, pyre/model.py:128-139)."""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights.specs import TensorSpec
+from .base import Part, register_part
+
+
+class GatedMLP(Part):
+    """down(act(gate(h)) * up(h)) without biases.  The gate and up weights are stacked
+    into one [2 I, width] matrix at load, so one product feeds the activation kernel."""
+
+    def __init__(self, dtype, device, width: int, intermediate: int, activation: str = "silu"):
+        super().__init__(dtype, device)
+        self.width, self.intermediate = int(width), int(intermediate)
+        if activation != "silu":
+            raise ops.UnsupportedSize(f"activation {activation!r}: only silu is implemented")
+        self.w_gate_up = self.w_down = None
+
+    def tensors(self):
+        return {
+            "gate_proj.weight": TensorSpec((self.intermediate, self.width)),
+            "up_proj.weight": TensorSpec((self.intermediate, self.width)),
+            "down_proj.weight": TensorSpec((self.width, self.intermediate)),
+        }
+
+    def load(self, tensors):
+        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
+        self.w_down = tensors["down_proj.weight"]
+
+    def kernel_libraries(self):
+        return ["elementwise"] + (["gemm_f32"] if self.dtype == torch.float32 else [])
+
+    def forward(self, ctx, h):
+        gate_up = ops.linear(h, self.w_gate_up)
+        act = ops.silu_mul(gate_up)
+        return ops.linear(act, self.w_down)
+
+
+register_part("ffn", "gated_mlp", GatedMLP)

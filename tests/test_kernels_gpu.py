@@ -1,0 +1,226 @@
+"""Each kernel alone against a plain fp32 statement of the same operation, at sizes other
+than the engine's."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=1e-5, atol=1e-6) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1e-3)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from pyre_b200.kernels import ops
+    return ops
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [40, 101, 3584])
+def test_embedding(ops, dtype, H):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    table = torch.randn(300, H, device="cuda", generator=g).to(dtype)
+    ids = torch.tensor([0, 299, 5, 5, 17], dtype=torch.int32, device="cuda")
+    x = ops.embedding(table, ids)
+    assert x.dtype == torch.float32
+    assert torch.equal(x, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,eps", [(40, 1e-5), (101, 1e-6), (3584, 1e-6), (5120, 3e-6)])
+def test_add_rmsnorm(ops, dtype, H, eps):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    T = 7
+    x = torch.randn(T, H, device="cuda", generator=g) * 3
+    delta = torch.randn(T, H, device="cuda", generator=g).to(dtype)
+    w = 1 + 0.1 * torch.randn(H, device="cuda", generator=g)
+    x0 = x.clone()
+    v = x0 + delta.float()
+    want = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)) * w
+    out = ops.add_rmsnorm(x, delta, w, eps, dtype)
+    torch.testing.assert_close(x, v, rtol=0, atol=0)          # the sum went back to the stream
+    torch.testing.assert_close(out.float(), want, **tol(dtype))
+    # without delta, x untouched
+    x1 = x0.clone()
+    out = ops.add_rmsnorm(x1, None, w, eps, dtype)
+    assert torch.equal(x1, x0)
+    want0 = (x0 * torch.rsqrt(x0.pow(2).mean(-1, keepdim=True) + eps)) * w
+    torch.testing.assert_close(out.float(), want0, **tol(dtype))
+    # gathered rows: x untouched, delta still counted
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device="cuda")
+    x2 = x0.clone()
+    out = ops.add_rmsnorm(x2, delta, w, eps, dtype, rows=rows)
+    assert torch.equal(x2, x0)
+    torch.testing.assert_close(out.float(), want[rows.long()], **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("I", [176, 99, 1000])
+def test_silu_mul(ops, dtype, I):
+    g = torch.Generator(device="cuda").manual_seed(2)
+    gu = (torch.randn(5, 2 * I, device="cuda", generator=g) * 4).to(dtype)
+    want = torch.nn.functional.silu(gu[:, :I].float()) * gu[:, I:].float()
+    torch.testing.assert_close(ops.silu_mul(gu).float(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 130, 70), (5, 64, 64), (33, 257, 100), (200, 300, 131), (64, 1000, 96)])
+def test_sgemm_is_true_fp32(ops, M, N, K):
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randn(M, K, device="cuda", generator=g)
+    w = torch.randn(N, K, device="cuda", generator=g)
+    bias = torch.randn(N, device="cuda", generator=g)
+    want = (a.double() @ w.double().t()).float()
+    got = ops.sgemm_nt(a, w)
+    # fp32 products and sums: error of a K-term sum, far below what TF32 (10-bit mantissa) gives
+    assert (got - want).abs().max().item() <= 2e-6 * K * 4
+    torch.testing.assert_close(ops.sgemm_nt(a, w, bias), got + bias, rtol=1e-6, atol=1e-6)
+    # a row's result does not depend on how many rows are in the product
+    if M > 1:
+        assert torch.equal(ops.sgemm_nt(a[:1].contiguous(), w), got[:1])
+
+
+def plain_rope(x, pos, theta, rot):
+    # x [T, n, hd]; half-split pairs over the first rot dims (pyre/model.py:41-63)
+    inv = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32, device=x.device) / rot))
+    ang = pos.float()[:, None] * inv[None, :]
+    cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+    x1, x2 = x[..., :rot // 2], x[..., rot // 2:rot]
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin, x[..., rot:]], dim=-1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,rot,page,theta", [(4, 2, 16, 16, 16, 1e4), (3, 1, 32, 32, 8, 1e6),
+                                                     (5, 5, 48, 32, 4, 5e4), (28, 4, 128, 128, 16, 1e6)])
+def test_qkv_rope_write(ops, dtype, nh, nkv, hd, rot, page, theta):
+    g = torch.Generator(device="cuda").manual_seed(4)
+    T, pages = 13, 9
+    width = (nh + 2 * nkv) * hd
+    qkv = torch.randn(T, width, device="cuda", generator=g).to(dtype)
+    bias = torch.randn(width, device="cuda", generator=g) * 0.5
+    pos = torch.tensor([0, 1, 2, 3, 40, 41, 1000, 7, 8, 9, 30000, 5, 6], dtype=torch.int32, device="cuda")
+    slots = torch.randperm(pages * page, device="cuda", generator=g)[:T].to(torch.int32)
+    slots[3] = -1  # this token stores nothing
+    inv = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    cos, sin = ops.rope_table(pos, inv.cuda())
+    ang = pos.float()[:, None] * inv.cuda()[None, :]
+    torch.testing.assert_close(cos, ang.cos(), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(sin, ang.sin(), rtol=1e-5, atol=1e-6)
+    cache = torch.full((pages, 2, nkv, page, hd), 7.0, device="cuda").to(dtype)
+    q = ops.qkv_rope_write(qkv, bias, cos, sin, cache, slots, nh, nkv, hd, rot, page)
+
+    full = qkv.float() + bias
+    qw = plain_rope(full[:, :nh * hd].view(T, nh, hd), pos, theta, rot)
+    kw = plain_rope(full[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd), pos, theta, rot)
+    vw = full[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    torch.testing.assert_close(q.float().view(T, nh, hd), qw, **tol(dtype))
+    want_cache = torch.full((pages, 2, nkv, page, hd), 7.0, device="cuda")
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        want_cache[s // page, 0, :, s % page] = kw[t]
+        want_cache[s // page, 1, :, s % page] = vw[t]
+    torch.testing.assert_close(cache.float(), want_cache, **tol(dtype))
+
+
+def plain_paged_attention(q, cache, table, seq_of_token, positions, nh, nkv, hd, scale, window):
+    T = q.shape[0]
+    page = cache.shape[3]
+    out = torch.zeros(T, nh, hd, dtype=torch.float64, device=q.device)
+    qf = q.double().view(T, nh, hd)
+    for t in range(T):
+        s, p = int(seq_of_token[t]), int(positions[t])
+        lo = max(0, p - window + 1) if window else 0
+        idx = torch.arange(lo, p + 1, device=q.device)
+        pages = table[s, idx // page].long()
+        k = cache[pages, 0, :, idx % page].double()   # [n, nkv, hd]
+        v = cache[pages, 1, :, idx % page].double()
+        for h in range(nh):
+            kvh = h // (nh // nkv)
+            sc = (k[:, kvh] @ qf[t, h]) * scale
+            pr = torch.softmax(sc, dim=0)
+            out[t, h] = pr @ v[:, kvh]
+    return out.view(T, nh * hd).float()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 4, 37),
+                                                   (8, 2, 64, 32, None), (7, 1, 128, 16, 50), (2, 2, 256, 16, None)])
+def test_paged_attention_generic(ops, dtype, nh, nkv, hd, page, window):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    # three sequences: a decode token far into a long context, a prompt portion that
+    # starts mid-page, and a short whole prompt
+    ctx_lens = [301, 77, 9]
+    new = [1, 20, 9]
+    n_pages = sum(-(-c // page) for c in ctx_lens) + 3
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(6)).tolist()
+    W = max(-(-c // page) for c in ctx_lens)
+    table = torch.full((3, W), -1, dtype=torch.int32)
+    for s, c in enumerate(ctx_lens):
+        for lp in range(-(-c // page)):
+            table[s, lp] = perm.pop()
+    table = table.cuda()
+    cache = torch.randn(n_pages, 2, nkv, page, hd, device="cuda", generator=g)
+    # positions never written hold NaN: a kernel that reads past a sequence's end shows it
+    for s, c in enumerate(ctx_lens):
+        last = int(table[s, (c - 1) // page])
+        if c % page:
+            cache[last, :, :, c % page:] = float("nan")
+    for p in perm:
+        cache[p] = float("nan")
+    seq_of_token = torch.tensor(sum(([s] * n for s, n in enumerate(new)), []), dtype=torch.int32, device="cuda")
+    positions = torch.tensor(sum((list(range(c - n, c)) for c, n in zip(ctx_lens, new)), []), dtype=torch.int32, device="cuda")
+    T = int(seq_of_token.shape[0])
+    q = torch.randn(T, nh * hd, device="cuda", generator=g)
+    # make one far key decide the first (decode) token: a key near the start of the long
+    # context gets a large score for head 0 (if it is inside the window)
+    far = 3 if not window else ctx_lens[0] - window + 1
+    kvh0 = 0
+    pg, off = int(table[0, far // page]), far % page
+    cache[pg, 0, kvh0, off] = q[0, :hd] * 3.0
+    cache = cache.to(dtype)
+    q = q.to(dtype)
+    scale = hd ** -0.5
+    want = plain_paged_attention(q.float(), cache.float(), table, seq_of_token, positions, nh, nkv, hd, scale, window)
+    got = ops.paged_attention_generic(q, cache, table, seq_of_token, positions, nh, nkv, hd, scale, window)
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got.float(), want, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else tol(dtype)))
+    # the far key really decides: head 0 of token 0 is close to that key's value
+    v_far = cache[pg, 1, kvh0, off].float()
+    assert (got[0, :hd].float() - v_far).abs().max() < 0.2 * v_far.abs().max() + 0.1
+
+
+def test_sampling(ops):
+    from plain import qwen2_plain
+    g = torch.Generator(device="cuda").manual_seed(7)
+    V = 1531
+    logits = torch.randn(6, V, device="cuda", generator=g)
+    logits[2, 100] = logits[2, 900] = 50.0      # a tie: the lower index wins
+    got = ops.sample(logits)
+    want = [int(logits[r].argmax()) for r in range(6)]
+    want[2] = 100
+    assert got.tolist() == want
+    temps = torch.tensor([0.0, 0.8, 0.8, 1.5, 0.3, 0.8], device="cuda")
+    seeds = torch.tensor([1, 1, 2, 3, 4, 1], dtype=torch.int64, device="cuda")
+    tix = torch.tensor([0, 0, 0, 5, 9, 1], dtype=torch.int32, device="cuda")
+    got = ops.sample(logits, temps, seeds, tix).tolist()
+    want = [qwen2_plain.sample(logits[r].cpu(), float(temps[r]), int(seeds[r]), int(tix[r])) for r in range(6)]
+    assert got == want
+    # the draw depends on (seed, token index) only, not on the row or the batch
+    alone = ops.sample(logits[1:2].contiguous(), temps[1:2].contiguous(), seeds[1:2].contiguous(), tix[1:2].contiguous())
+    assert alone.tolist() == [got[1]]
+    # large vocabulary, many draws: frequencies follow softmax(logits / T)
+    V2 = 50
+    lg = torch.randn(1, V2, device="cuda", generator=g).repeat(4000, 1)
+    draws = ops.sample(lg, torch.full((4000,), 0.7, device="cuda"), torch.arange(4000, dtype=torch.int64, device="cuda"),
+                       torch.zeros(4000, dtype=torch.int32, device="cuda"))
+    freq = torch.bincount(draws.long(), minlength=V2).float() / 4000
+    p = torch.softmax(lg[0] / 0.7, dim=0)
+    assert (freq - p).abs().max().item() < 0.03
