@@ -1,0 +1,141 @@
+"""The Python entry point: a model folder (or a configuration and a seed) in, token ids out.
+
+The reference has no engine class (pyre/engine.py is a stub); its de-facto entry is
+``Scheduler.add_request(prompt_ids, max_new_tokens, eos_id)`` followed by ``run()``, which
+returns ``{seq_id: generated ids}`` (pyre/scheduler.py:40-44,105-114).  ``Engine`` keeps
+those two calls with the same names and meanings and adds ``generate`` for a list of
+prompts.  Tokens in, tokens out: a tokenizer is not part of the engine (the reference
+borrows one from another package in its server only, pyre/server/app.py:54-68).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Sequence
+
+import torch
+
+from ..cache import CacheManager
+from ..config import EngineConfig, ModelConfig, architecture_of, load_config
+from ..kernels import build, lib
+from ..models.model import Model
+from ..sampling import Sampler, SamplingParams
+from .scheduler import Request, Scheduler
+from .step import StepEntry, Stepper
+
+
+@dataclass
+class RequestOutput:
+    seq_id: int
+    prompt_ids: list[int]
+    token_ids: list[int]
+    finish_reason: str
+    preemptions: int = 0
+
+
+class Engine:
+    def __init__(self, model: "str | Path | None" = None, engine_config: "EngineConfig | None" = None, *,
+                 config: "ModelConfig | None" = None, seed: "int | None" = None, **overrides):
+        """``Engine("path/to/model")`` loads config.json and the safetensors files of the
+        folder; ``Engine(config=cfg, seed=0)`` draws random weights on the device.
+        Keyword ``overrides`` set fields of ``EngineConfig`` (``dtype="float32"``, ...)."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("pyre_b200 needs a CUDA device (sm_100a); there is no CPU path")
+        ec = engine_config or EngineConfig()
+        for k, v in overrides.items():
+            if not hasattr(ec, k):
+                raise TypeError(f"unknown engine option {k!r}")
+            setattr(ec, k, v)
+        ec.__post_init__()
+        self.engine_config = ec
+        if (model is None) == (config is None):
+            raise ValueError("give either a model folder or config= with seed=")
+        self.model_config = load_config(model) if model is not None else config
+        spec = architecture_of(self.model_config).build(self.model_config)
+        self.model = Model(spec, ec.dtype, ec.device)
+        build.ensure_built(self.model.kernel_libraries())
+        with torch.cuda.device(self.model.device):
+            if model is not None:
+                self.model.load_weights(model)
+            else:
+                self.model.init_random(int(seed or 0))
+        max_positions = spec.max_positions or (1 << 30)
+        default_tokens = min(max_positions, 8192) * min(ec.max_num_seqs, 8)
+        num_pages = ec.resolve_num_pages(default_tokens)
+        self.max_model_len = min(ec.max_model_len or max_positions, max_positions, num_pages * ec.page_size)
+        self.cache = CacheManager(self.model.kv_groups, self.model.state_groups, ec.page_size, num_pages,
+                                  ec.max_num_seqs, ec.dtype, ec.device)
+        self.cache.set_poison(ec.debug_poison_freed_pages)
+        self.stepper = Stepper(self.model, self.cache, max_positions=max_positions)
+        self.scheduler = Scheduler(self.cache, ec.max_num_seqs, ec.max_num_batched_tokens, ec.prefill_chunk,
+                                   self.max_model_len)
+        self.sampler = Sampler(ec.device)
+        self._requests: dict[int, Request] = {}
+
+    # ------------------------------------------------------------------ the reference's two calls
+    def add_request(self, prompt_ids: Sequence[int], max_new_tokens: int = 16, eos_id: "int | None" = None,
+                    temperature: float = 0.0, seed: int = 0, params: "SamplingParams | None" = None) -> int:
+        """Queue a request; returns its ``seq_id`` (pyre/scheduler.py:40-44)."""
+        vocab = self.model.vocab_size
+        if any(not 0 <= int(t) < vocab for t in prompt_ids):
+            raise ValueError(f"prompt holds a token id outside [0, {vocab})")
+        p = params or SamplingParams(temperature=temperature, seed=seed, max_new_tokens=max_new_tokens, eos_id=eos_id)
+        r = self.scheduler.add_request(prompt_ids, p)
+        self._requests[r.seq_id] = r
+        return r.seq_id
+
+    def step(self) -> list[RequestOutput]:
+        """One scheduler iteration: plan, run the mixed batch, sample, record.  Returns the
+        requests that finished in it."""
+        before = {r.seq_id for r in self._requests.values() if not r.done}
+        plan = self.scheduler.schedule()
+        outs = []
+        if plan:
+            entries = [StepEntry(s.request.seq_id, s.request.tokens(s.start, s.count),
+                                 [s.count - 1] if s.samples else []) for s in plan]
+            with torch.cuda.device(self.model.device):
+                ctx = self.stepper.build_context(entries, reserve=False)
+                logits = self.stepper.run_context(ctx)
+                sampling = [s for s in plan if s.samples]
+                ids = self.sampler.sample(logits, [s.request.params for s in sampling],
+                                          [len(s.request.generated) for s in sampling])
+            self.scheduler.update(plan, ids)
+        for sid in before:
+            r = self._requests[sid]
+            if r.done:
+                outs.append(RequestOutput(r.seq_id, r.prompt_ids, list(r.generated), r.finish_reason or "", r.preemptions))
+                del self._requests[sid]
+        return outs
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_unfinished()
+
+    def run(self) -> dict[int, list[int]]:
+        """Run every queued request to its end: ``{seq_id: generated ids}`` (pyre/scheduler.py:105-114)."""
+        results = {}
+        while self.has_unfinished():
+            for out in self.step():
+                results[out.seq_id] = out.token_ids
+        return results
+
+    # ------------------------------------------------------------------ convenience
+    def generate(self, prompts: Sequence[Sequence[int]], params: "SamplingParams | Sequence[SamplingParams] | None" = None
+                 ) -> list[RequestOutput]:
+        """Token ids of several prompts in, one ``RequestOutput`` per prompt out (in order)."""
+        if params is None or isinstance(params, SamplingParams):
+            params = [params or SamplingParams()] * len(prompts)
+        if len(params) != len(prompts):
+            raise ValueError("one SamplingParams per prompt, or one for all")
+        order = [self.add_request(p, params=sp) for p, sp in zip(prompts, params)]
+        done: dict[int, RequestOutput] = {}
+        while self.has_unfinished():
+            for out in self.step():
+                done[out.seq_id] = out
+        return [done[sid] for sid in order]
+
+    def stats(self) -> dict:
+        s, c = self.scheduler.stats, self.cache.stats()
+        return {"steps": s.steps, "admitted": s.admitted, "preempted": s.preempted, "finished": s.finished,
+                "scheduled_tokens": s.scheduled_tokens, "pages_free": c.pages_free, "pages_total": c.pages_total,
+                "kernel_launches": lib.launch_count}

@@ -46,11 +46,19 @@ def build_runtime(model_dir, dtype, max_tokens: int, page_size: int = DEFAULT_PA
     model = Model(spec, dtype, device)
     build.ensure_built(model.kernel_libraries())
     model.load_weights(model_dir)
-    num_pages = max(1, -(-int(max_tokens) // page_size))
-    cache = CacheManager(model.kv_groups, model.state_groups, page_size, num_pages, max_requests, dtype, device)
-    cache.set_poison(poison)
-    stepper = Stepper(model, cache, max_positions=spec.max_positions or None)
+    cache, stepper = runtime_for_model(model, max_tokens, page_size, max_requests, poison)
     return model, cache, stepper
+
+
+def runtime_for_model(model: Model, max_tokens: int, page_size: int = DEFAULT_PAGE_SIZE,
+                      max_requests: int = MAX_LIVE_REQUESTS, poison: bool = False):
+    """Cache manager and stepper for a model that already has its weights."""
+    num_pages = max(1, -(-int(max_tokens) // page_size))
+    cache = CacheManager(model.kv_groups, model.state_groups, page_size, num_pages, max_requests, model.dtype,
+                         model.device)
+    cache.set_poison(poison)
+    stepper = Stepper(model, cache, max_positions=model.spec.max_positions or None)
+    return cache, stepper
 
 
 def replay(stepper: Stepper, lines, out_dir: Path, done=print) -> None:

@@ -1,0 +1,217 @@
+"""Continuous batching above the step function: which tokens of which requests run next.
+
+Host logic only; it talks to a ``CacheManager`` and returns a plan, so it is tested on
+the CPU with a fake step.  What the reference does (pyre/scheduler.py:27-114): a FIFO
+``waiting`` list, a ``running`` list bounded by ``max_batch``, each admitted request
+prefilled alone and whole, then one decode step per iteration for all running requests,
+no look at free pages (exhaustion is a MemoryError that ends ``run``).  Here:
+
+* every iteration is ONE mixed step under a token budget: first one token for every
+  request that is decoding, then portions of prompts (at most ``prefill_chunk`` tokens of
+  a request) while budget is left, oldest request first;
+* a request is admitted when a state slot is free and its first portion fits in the pools;
+* when pages run out for a request that is already running, the request admitted LAST
+  is preempted: its pages and slot go back, it returns to the FRONT of the waiting list
+  and later recomputes prompt + tokens generated so far in portions; tokens already
+  produced are kept, and the sampler's noise is keyed by token index, so the final output
+  is what it would have been;
+* a request that cannot grow even when it is alone in the cache ends with reason
+  ``"cache_full"``;
+* the token that completes a request (end-of-sequence id or the last allowed token) is
+  kept (pyre/scheduler.py:82), and a finished request takes part in no further step
+  (the reference lets a request that finishes at admission decode once more).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+from ..cache import CacheManager
+from ..sampling.params import SamplingParams
+
+WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+
+
+@dataclass
+class Request:
+    seq_id: int
+    prompt_ids: list[int]
+    params: SamplingParams
+    generated: list[int] = field(default_factory=list)
+    status: str = WAITING
+    num_computed: int = 0          # tokens whose keys and values are in the cache
+    finish_reason: "str | None" = None
+    preemptions: int = 0
+
+    @property
+    def cur_len(self) -> int:
+        return len(self.prompt_ids) + len(self.generated)
+
+    @property
+    def done(self) -> bool:
+        return self.status == FINISHED
+
+    def token_at(self, i: int) -> int:
+        n = len(self.prompt_ids)
+        return self.prompt_ids[i] if i < n else self.generated[i - n]
+
+    def tokens(self, start: int, count: int) -> list[int]:
+        return [self.token_at(i) for i in range(start, start + count)]
+
+
+@dataclass
+class Scheduled:
+    """One entry of the next step: ``count`` tokens of ``request`` from ``start``; the step's
+    last token completes what is known of the request iff ``samples``."""
+
+    request: Request
+    start: int
+    count: int
+    samples: bool
+
+
+@dataclass
+class SchedulerStats:
+    steps: int = 0
+    admitted: int = 0
+    preempted: int = 0
+    finished: int = 0
+    scheduled_tokens: int = 0
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, max_num_seqs: int, max_num_batched_tokens: int,
+                 prefill_chunk: int, max_model_len: int):
+        self.cache = cache
+        self.max_num_seqs = max_num_seqs
+        self.max_num_batched_tokens = max_num_batched_tokens
+        self.prefill_chunk = prefill_chunk
+        self.max_model_len = max_model_len
+        self.waiting: list[Request] = []
+        self.running: list[Request] = []     # in order of admission
+        self._next_seq = 0
+        self._finished_now: list[Request] = []
+        self.stats = SchedulerStats()
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt_ids: Sequence[int], params: SamplingParams) -> Request:
+        prompt = [int(t) for t in prompt_ids]
+        if not prompt:
+            raise ValueError("a request needs at least one prompt token")
+        if len(prompt) >= self.max_model_len:
+            raise ValueError(f"prompt of {len(prompt)} tokens leaves no room under max_model_len {self.max_model_len}")
+        r = Request(self._next_seq, prompt, params)
+        self._next_seq += 1
+        self.waiting.append(r)
+        return r
+
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------ planning
+    def _preempt(self, victim: Request) -> None:
+        self.cache.end(victim.seq_id)
+        self.running.remove(victim)
+        victim.status = WAITING
+        victim.num_computed = 0
+        victim.preemptions += 1
+        self.waiting.insert(0, victim)
+        self.stats.preempted += 1
+
+    def _finish(self, r: Request, reason: str) -> None:
+        if r.status == RUNNING:
+            self.cache.end(r.seq_id)
+            self.running.remove(r)
+        r.status = FINISHED
+        r.finish_reason = reason
+        self.stats.finished += 1
+        self._finished_now.append(r)
+
+    def schedule(self) -> list[Scheduled]:
+        """Plan the next step and reserve its pages.  May preempt or finish requests
+        (see the module text); returns [] only if nothing is left to run."""
+        budget = self.max_num_batched_tokens
+        plan: list[Scheduled] = []
+        planned: set[int] = set()
+        aborted: list[Request] = []
+
+        def try_schedule(r: Request) -> bool:
+            nonlocal budget
+            remaining = r.cur_len - r.num_computed
+            count = min(remaining, self.prefill_chunk, budget)
+            if count <= 0:
+                return False
+            while not self.cache.reserve(r.seq_id, r.num_computed + count):
+                # the most recently admitted request that is not yet in this step's plan gives way
+                victims = [v for v in reversed(self.running) if v.seq_id not in planned]
+                victim = victims[0] if victims else None
+                if victim is None or victim is r:
+                    if len(self.running) == 1 and victim is r:
+                        aborted.append(r)   # alone and still too large for the pools
+                    elif victim is r:
+                        self._preempt(r)
+                    return False
+                self._preempt(victim)
+            plan.append(Scheduled(r, r.num_computed, count, r.num_computed + count == r.cur_len))
+            planned.add(r.seq_id)
+            budget -= count
+            return True
+
+        # 1. requests that are decoding (one token each), oldest first
+        for r in [r for r in self.running if r.cur_len - r.num_computed == 1]:
+            if r.status == RUNNING and budget > 0:
+                try_schedule(r)
+        # 2. requests in the middle of their prompt (or of a recompute)
+        for r in [r for r in self.running if r.cur_len - r.num_computed > 1]:
+            if r.status == RUNNING and budget > 0 and r.seq_id not in planned:
+                try_schedule(r)
+        for r in aborted:
+            self._finish(r, "cache_full")
+        # 3. admit waiting requests while there is budget, a slot and room for a first portion
+        while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs and self.cache.has_free_slot():
+            r = self.waiting[0]
+            count = min(r.cur_len, self.prefill_chunk, budget)
+            self.cache.begin(r.seq_id)
+            if not self.cache.reserve(r.seq_id, count):
+                self.cache.end(r.seq_id)
+                if not self.running:
+                    # the pools are empty and the first portion still does not fit
+                    self.waiting.pop(0)
+                    self._finish(r, "cache_full")
+                    continue
+                break
+            self.waiting.pop(0)
+            r.status = RUNNING
+            self.running.append(r)
+            self.stats.admitted += 1
+            plan.append(Scheduled(r, 0, count, count == r.cur_len))
+            planned.add(r.seq_id)
+            budget -= count
+        if plan:
+            self.stats.steps += 1
+            self.stats.scheduled_tokens += sum(s.count for s in plan)
+        return plan
+
+    # ------------------------------------------------------------------ results
+    def update(self, plan: Sequence[Scheduled], sampled: Sequence[int]) -> list[Request]:
+        """Record a finished step: ``sampled`` holds one token per plan entry with
+        ``samples`` set, in plan order.  Returns the requests that finished since the last
+        call, those that ``schedule`` ended with "cache_full" included."""
+        it = iter(sampled)
+        for s in plan:
+            r = s.request
+            r.num_computed = s.start + s.count
+            if not s.samples:
+                continue
+            tok = int(next(it))
+            r.generated.append(tok)
+            p = r.params
+            if p.eos_id is not None and tok == p.eos_id and not p.ignore_eos:
+                self._finish(r, "eos")
+            elif len(r.generated) >= p.max_new_tokens:
+                self._finish(r, "length")
+            elif r.cur_len >= self.max_model_len:
+                self._finish(r, "max_model_len")
+        finished, self._finished_now = self._finished_now, []
+        return finished

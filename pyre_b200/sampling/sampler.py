@@ -1,0 +1,40 @@
+"""Device-side sampling of one token per row of logits."""
+
+from __future__ import annotations
+
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from .params import SamplingParams
+
+
+class Sampler:
+    """Greedy and temperature sampling in one kernel launch; one device-to-host copy of
+    the chosen ids per step (the reference copies once per request, pyre/scheduler.py:94)."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], token_index: Sequence[int]) -> list[int]:
+        """``logits`` [R, V] fp32; ``params[r]`` and ``token_index[r]`` (how many tokens row r's
+        request has generated so far) select the rule and the noise of row r."""
+        R = logits.shape[0]
+        if R == 0:
+            return []
+        if all(p.temperature == 0.0 for p in params):
+            ids = ops.sample(logits)
+        else:
+            host = np.empty((R, 4), dtype=np.int32)
+            host[:, 0] = np.asarray([p.temperature for p in params], dtype=np.float32).view(np.int32)
+            seeds = np.asarray([p.seed & 0x7FFFFFFFFFFFFFFF for p in params], dtype=np.int64)
+            host[:, 1:3] = seeds.view(np.int32).reshape(R, 2)
+            host[:, 3] = np.asarray(token_index, dtype=np.int32)
+            dev = torch.from_numpy(host).to(self.device, non_blocking=False)
+            temperature = dev[:, 0].contiguous().view(torch.float32)
+            seeds_dev = dev[:, 1:3].contiguous().view(torch.int64).reshape(R)
+            tix = dev[:, 3].contiguous()
+            ids = ops.sample(logits, temperature, seeds_dev, tix)
+        return ids.tolist()

@@ -62,6 +62,15 @@ def plain_logits(path: Path, ids, bf16_weights: bool = False) -> np.ndarray:
         return qwen2_plain.forward(list(ids), w, raw).numpy()
 
 
+def plain_logits_in_bf16(path: Path, ids) -> np.ndarray:
+    """The plain implementation with every tensor in bfloat16, as the reference runs a
+    model in a 16-bit dtype (pyre/loader.py:74)."""
+    raw = json.loads((Path(path) / "config.json").read_text())
+    w = {k: v.to(torch.bfloat16) for k, v in load_plain_weights(path).items()}
+    with torch.inference_mode():
+        return qwen2_plain.forward(list(ids), w, raw).float().numpy()
+
+
 def random_ids(vocab: int, n: int, seed: int) -> list[int]:
     g = np.random.default_rng(seed)
     return [int(x) for x in g.integers(0, vocab, n)]

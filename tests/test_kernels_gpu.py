@@ -86,9 +86,10 @@ def test_sgemm_is_true_fp32(ops, M, N, K):
         assert torch.equal(ops.sgemm_nt(a[:1].contiguous(), w), got[:1])
 
 
-def plain_rope(x, pos, theta, rot):
-    # x [T, n, hd]; half-split pairs over the first rot dims (pyre/model.py:41-63)
-    inv = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32, device=x.device) / rot))
+def plain_rope(x, pos, inv, rot):
+    # x [T, n, hd]; half-split pairs over the first rot dims (pyre/model.py:41-63);
+    # inv = theta^(-2j/rot) is computed once on the CPU and shared with the kernel under
+    # test: at position 30000 one ulp of inv_freq already moves the angle by 3e-3
     ang = pos.float()[:, None] * inv[None, :]
     cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
     x1, x2 = x[..., :rot // 2], x[..., rot // 2:rot]
@@ -107,17 +108,17 @@ def test_qkv_rope_write(ops, dtype, nh, nkv, hd, rot, page, theta):
     pos = torch.tensor([0, 1, 2, 3, 40, 41, 1000, 7, 8, 9, 30000, 5, 6], dtype=torch.int32, device="cuda")
     slots = torch.randperm(pages * page, device="cuda", generator=g)[:T].to(torch.int32)
     slots[3] = -1  # this token stores nothing
-    inv = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
-    cos, sin = ops.rope_table(pos, inv.cuda())
-    ang = pos.float()[:, None] * inv.cuda()[None, :]
+    inv = (1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).cuda()
+    cos, sin = ops.rope_table(pos, inv)
+    ang = pos.float()[:, None] * inv[None, :]
     torch.testing.assert_close(cos, ang.cos(), rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(sin, ang.sin(), rtol=1e-5, atol=1e-6)
     cache = torch.full((pages, 2, nkv, page, hd), 7.0, device="cuda").to(dtype)
     q = ops.qkv_rope_write(qkv, bias, cos, sin, cache, slots, nh, nkv, hd, rot, page)
 
     full = qkv.float() + bias
-    qw = plain_rope(full[:, :nh * hd].view(T, nh, hd), pos, theta, rot)
-    kw = plain_rope(full[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd), pos, theta, rot)
+    qw = plain_rope(full[:, :nh * hd].view(T, nh, hd), pos, inv, rot)
+    kw = plain_rope(full[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd), pos, inv, rot)
     vw = full[:, (nh + nkv) * hd:].view(T, nkv, hd)
     torch.testing.assert_close(q.float().view(T, nh, hd), qw, **tol(dtype))
     want_cache = torch.full((pages, 2, nkv, page, hd), 7.0, device="cuda")

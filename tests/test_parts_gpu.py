@@ -1,0 +1,334 @@
+"""Each part of a layer alone against the plain implementation's function for it; the
+schedule as data (a layer run twice, a layer that reads another layer's cache); layers
+with a window beside layers without (two cache groups); and a toy mixer with state of
+its own, defined here, registered, built and stepped without any change to the package."""
+
+import json
+from dataclasses import dataclass
+from typing import ClassVar
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+from plain import qwen2_plain
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, scale=1.0):
+    return dict(rtol=2e-5, atol=2e-6 * scale) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-3 * scale)
+
+
+def mini_context(dtype, token_ids=None, positions=None):
+    from pyre_b200.engine.context import StepContext
+    n = len(positions if positions is not None else token_ids)
+    z = torch.zeros(n, dtype=torch.int32, device="cuda")
+    return StepContext(dtype=dtype, device=torch.device("cuda"), num_tokens=n, num_seqs=1, num_logit_rows=0,
+                       token_ids=torch.tensor(token_ids or [0] * n, dtype=torch.int32, device="cuda"),
+                       positions=torch.tensor(positions or list(range(n)), dtype=torch.int32, device="cuda"),
+                       seq_of_token=z, cu_seqlens=torch.tensor([0, n], dtype=torch.int32, device="cuda"),
+                       logit_rows=z[:0], cu_seqlens_host=np.array([0, n]), start_pos_host=np.array([0]),
+                       error_flag=torch.zeros(1, dtype=torch.int32, device="cuda"))
+
+
+def make(category, kind, dtype, **params):
+    from pyre_b200.parts import PartSpec, make_part
+    return make_part(category, PartSpec(kind, params), dtype, "cuda")
+
+
+def load_random(part, seed, scale=0.3):
+    g = torch.Generator().manual_seed(seed)
+    tensors = {}
+    for name, spec in part.tensors().items():
+        t = torch.randn(spec.shape, generator=g) * scale
+        if spec.role == "vector":
+            tensors[name] = (t + (1.0 if name == "weight" else 0.0)).cuda()
+        else:
+            tensors[name] = t.to(part.dtype).cuda()
+    part.load(dict(tensors))
+    return {k: v.float().cpu() for k, v in tensors.items()}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_norm_part(dtype):
+    norm = make("norm", "rms_norm", dtype, width=120, eps=3e-6)
+    w = load_random(norm, 0)
+    x = torch.randn(9, 120, device="cuda") * 2
+    delta = torch.randn(9, 120, device="cuda").to(dtype)
+    want = qwen2_plain.rms_norm((x + delta.float()).cpu(), w["weight"], 3e-6)
+    got = norm.forward(mini_context(dtype, positions=list(range(9))), x, delta=delta)
+    torch.testing.assert_close(got.float().cpu(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("head_dim,theta", [(16, 1e4), (48, 5e4), (128, 1e6)])
+def test_rotary_part(head_dim, theta):
+    rot = make("position", "rotary", torch.float32, head_dim=head_dim, theta=theta)
+    pos = [0, 1, 2, 77, 4095, 32767]
+    ctx = mini_context(torch.float32, positions=pos)
+    cos, sin = rot.tables(ctx)
+    want_cos, want_sin = qwen2_plain.rope_tables(torch.tensor(pos), head_dim, theta, torch.float32)
+    torch.testing.assert_close(cos.cpu(), want_cos[:, :head_dim // 2], rtol=1e-5, atol=2e-6)
+    torch.testing.assert_close(sin.cpu(), want_sin[:, :head_dim // 2], rtol=1e-5, atol=2e-6)
+    assert rot.tables(ctx)[0] is cos          # computed once per step, shared by the layers
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_feed_forward_part(dtype):
+    ffn = make("ffn", "gated_mlp", dtype, width=72, intermediate=200)
+    w = load_random(ffn, 1)
+    h = torch.randn(11, 72, device="cuda").to(dtype)
+    want = qwen2_plain.swiglu_mlp(h.float().cpu(), w, "")
+    got = ffn.forward(mini_context(dtype, positions=list(range(11))), h)
+    torch.testing.assert_close(got.float().cpu(), want, **tol(dtype, 3.0))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_head_parts(dtype):
+    emb = make("embed", "token_embedding", dtype, vocab=333, width=40)
+    w = load_random(emb, 2)
+    ids = [0, 332, 7, 7]
+    x = emb.forward(mini_context(dtype, token_ids=ids))
+    assert x.dtype == torch.float32 and torch.equal(x.cpu(), w["weight"][ids])
+    head = make("head", "linear_head", dtype, vocab=333, width=40)
+    wh = load_random(head, 3)
+    h = torch.randn(3, 40, device="cuda").to(dtype)
+    logits = head.forward(None, h)
+    assert logits.dtype == torch.float32
+    torch.testing.assert_close(logits.cpu(), h.float().cpu() @ wh["weight"].t(), **tol(dtype, 2.0))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,window", [(4, 2, 16, None), (6, 3, 48, 7), (3, 1, 32, None)])
+def test_attention_part(dtype, nh, nkv, hd, window):
+    """The mixer alone, fed in two portions through its paged cache, against the plain
+    projections + rotary + attention + output projection on the whole sequence."""
+    from pyre_b200.cache import CacheManager
+    from pyre_b200.engine.context import KVView
+    from pyre_b200.parts import BoundCall, PartSpec
+    width, S, page = 56, 29, 8
+    att = make("mixer", "attention", dtype, width=width, n_heads=nh, n_kv_heads=nkv, head_dim=hd, window=window,
+               position=PartSpec("rotary", {"head_dim": hd, "theta": 1e4}))
+    w = load_random(att, 4, scale=0.4)
+    h = torch.randn(S, width, device="cuda").to(dtype)
+
+    hf = h.float().cpu()
+    q, k, v = qwen2_plain.project_qkv(hf, w, "", nh, nkv, hd)
+    cos, sin = qwen2_plain.rope_tables(torch.arange(S), hd, 1e4, torch.float32)
+    a = qwen2_plain.attention(qwen2_plain.apply_rope(q, cos, sin), qwen2_plain.apply_rope(k, cos, sin), v, window)
+    want = a @ w["o_proj.weight"].t()
+
+    @dataclass(frozen=True)
+    class G:
+        spec: object
+        n_layers: int
+    cache = CacheManager([G(att.cache_spec(), 1)], [], page, 16, 2, dtype, "cuda")
+    cache.begin("r")
+    outs = []
+    for start, n in ((0, 18), (18, 11)):
+        assert cache.reserve("r", start + n)
+        ctx = mini_context(dtype, positions=list(range(start, start + n)))
+        table = torch.from_numpy(cache.block_table_rows(0, ["r"])).cuda()
+        slots = torch.from_numpy(cache.slots_for(0, "r", start, n)).cuda()
+        ctx.kv_groups.append(KVView(cache.groups[0].pool, table, slots, page, window))
+        outs.append(att.forward(ctx, h[start:start + n].contiguous(), BoundCall(0, 0, 0, 0, True)))
+        cache.commit("r", start + n)
+    got = torch.cat(outs).float().cpu()
+    torch.testing.assert_close(got, want, **tol(dtype, 3.0))
+
+
+# --------------------------------------------------------------------------- whole models from specs
+def run_spec(spec, model_dir, dtype, ids, portions, page_size=8, max_tokens=256):
+    from pyre_b200.engine.replay import runtime_for_model
+    from pyre_b200.engine.step import StepEntry
+    from pyre_b200.kernels import build
+    from pyre_b200.models import Model
+    model = Model(spec, dtype, "cuda")
+    build.ensure_built(model.kernel_libraries())
+    model.load_weights(model_dir)
+    cache, stepper = runtime_for_model(model, max_tokens, page_size, poison=True)
+    cache.begin("r")
+    out, pos = [], 0
+    for n in portions:
+        out.append(stepper.step([StepEntry("r", ids[pos:pos + n], list(range(n)))]).cpu())
+        pos += n
+    assert pos == len(ids)
+    cache.end("r")
+    cache.check()
+    return torch.cat(out).numpy(), cache
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_schedule_is_data(tmp_path, dtype):
+    """Layer 0 runs twice (each run with a cache layer of its own) and the last entry runs
+    layer 1's weights again on the keys and values that layer 1's first run stored."""
+    from pyre_b200.config import architecture, config_from_dict
+    from pyre_b200.models import LayerCall
+    from pyre_b200.config import parse_dtype
+    raw = H.TINY_A
+    H.make_model_dir(tmp_path, raw, seed=21)
+    cfg = config_from_dict(raw)
+    spec = architecture("Qwen2ForCausalLM").build(cfg)
+    spec.schedule = [LayerCall(0), LayerCall(1, cache="shared"), LayerCall(0), LayerCall(1, cache="shared", write=False)]
+    ids = H.random_ids(raw["vocab_size"], 45, seed=4)
+    got, cache = run_spec(spec, tmp_path, parse_dtype(dtype), ids, [20, 2, 23])
+    assert cache.groups[0].n_layers == 3                     # three cache layers for four entries
+    w = H.load_plain_weights(tmp_path, round_matrices_to_bf16=(dtype == "bfloat16"))
+    with torch.inference_mode():
+        want = qwen2_plain.forward(ids, w, raw, schedule=[(0, None), (1, None), (0, None), (1, 1)]).numpy()
+    assert np.abs(got - want).max() <= (2e-4 if dtype == "float32" else 0.08)
+    with pytest.raises(ValueError, match="before any entry wrote"):
+        spec.schedule = [LayerCall(0, cache="x", write=False), LayerCall(1)]
+        from pyre_b200.models import Model
+        Model(spec, torch.float32, "cuda")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_window_layers_beside_full_layers(tmp_path, dtype):
+    """Layer 1 of three attends over a window of 11 keys: it gets a cache group of its own
+    whose pages are given back as the window passes them; logits equal the plain
+    implementation's with the same window, whole and in portions that straddle its edge."""
+    from pyre_b200.config import architecture, config_from_dict, parse_dtype
+    from pyre_b200.parts import PartSpec
+    raw = H.TINY_B
+    H.make_model_dir(tmp_path, raw, seed=22)
+    spec = architecture("Qwen2ForCausalLM").build(config_from_dict(raw))
+    b = spec.blocks[1]
+    mixer = PartSpec("attention", dict(b.params["mixer"].params, window=11))
+    spec.blocks[1] = PartSpec(b.kind, dict(b.params, mixer=mixer))
+    ids = H.random_ids(raw["vocab_size"], 90, seed=5)
+    w = H.load_plain_weights(tmp_path, round_matrices_to_bf16=(dtype == "bfloat16"))
+    with torch.inference_mode():
+        want = qwen2_plain.forward(ids, w, raw, windows=[None, 11, None]).numpy()
+    bound = 2e-4 if dtype == "float32" else 0.08
+    for portions in ([90], [40] + [1] * 50, [3, 9, 2, 30, 11, 12, 23]):
+        got, cache = run_spec(spec, tmp_path, parse_dtype(dtype), ids, portions, page_size=4, max_tokens=128)
+        err = np.abs(got - want).max(axis=1)
+        assert err.max() <= bound, f"portions {portions[:4]}...: first wrong position {int(np.where(err > bound)[0][0])}"
+        assert len(cache.groups) == 2 and cache.groups[1].spec.window == 11
+    # while decoding, the windowed group holds only the pages its window touches
+    from pyre_b200.engine.replay import runtime_for_model
+    from pyre_b200.engine.step import StepEntry
+    from pyre_b200.models import Model
+    model = Model(spec, parse_dtype(dtype), "cuda")
+    model.load_weights(tmp_path)
+    cache, stepper = runtime_for_model(model, 128, 4)
+    cache.begin("r")
+    stepper.step([StepEntry("r", ids[:60], [])])
+    assert cache.groups[0].pages_held("r") == 15 and cache.groups[1].pages_held("r") <= 4
+
+
+# --------------------------------------------------------------------------- a toy mixer with state
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    """A mixer that is no attention at all: a per-request running state
+    s_t = decay * s_{t-1} + h_t W_in, output s_t W_out.  It is defined, registered and given an
+    architecture of its own right here; the package's files are untouched.  Its state
+    lives in the cache manager's slots, so a sequence cut into portions (and mixed with
+    another request) gives what the whole sequence gives."""
+    from pyre_b200.config import ModelConfig, config_from_dict, register_architecture
+    from pyre_b200.engine.replay import runtime_for_model
+    from pyre_b200.engine.step import StepEntry
+    from pyre_b200.models import Model, ModelSpec
+    from pyre_b200.parts import Part, PartSpec, StateSpec, register_part
+    from pyre_b200.weights import TensorSpec, write_random_model
+
+    class ToyDecayMixer(Part):
+        def __init__(self, dtype, device, width, state_width, decay):
+            super().__init__(dtype, device)
+            self.width, self.state_width, self.decay = width, state_width, decay
+
+        def tensors(self):
+            return {"in_proj.weight": TensorSpec((self.state_width, self.width), init=("normal", 0.0, 0.2)),
+                    "out_proj.weight": TensorSpec((self.width, self.state_width), init=("normal", 0.0, 0.2))}
+
+        def load(self, tensors):
+            self.w_in, self.w_out = tensors["in_proj.weight"].float(), tensors["out_proj.weight"].float()
+
+        def cache_spec(self):
+            return None
+
+        def state_spec(self):
+            return StateSpec((self.state_width,), torch.float32)
+
+        def forward(self, ctx, h, call):
+            view = ctx.state_group(call.state_group)
+            u = h.float() @ self.w_in.t()
+            out = torch.empty_like(u)
+            cu = ctx.cu_seqlens_host
+            for b in range(ctx.num_seqs):                       # rows of one request in order
+                s = view.buffer[call.state_layer, int(view.slots_host[b])]
+                for t in range(cu[b], cu[b + 1]):
+                    s.mul_(self.decay).add_(u[t])
+                    out[t] = s
+            return (out @ self.w_out.t()).to(self.dtype)
+
+    register_part("mixer", "toy_decay", ToyDecayMixer, replace=True)
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        architecture: ClassVar[str] = "ToyDecayForCausalLM"
+        width: int = 24
+        layers: int = 2
+        vocab: int = 50
+        state_width: int = 10
+        decays: tuple = (0.5, 0.9)
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["width"], raw["layers"], raw["vocab"], raw["state_width"], tuple(raw["decays"]))
+
+    def build_toy(cfg):
+        norm = PartSpec("rms_norm", {"width": cfg.width, "eps": 1e-5})
+        blocks = [PartSpec("prenorm", {
+            "norm1": norm, "norm2": norm,
+            "mixer": PartSpec("toy_decay", {"width": cfg.width, "state_width": cfg.state_width, "decay": cfg.decays[i]}),
+            "ffn": PartSpec("gated_mlp", {"width": cfg.width, "intermediate": 40}),
+            "names": {"mixer": "mixer."}}) for i in range(cfg.layers)]
+        return ModelSpec(embed=PartSpec("token_embedding", {"vocab": cfg.vocab, "width": cfg.width}), blocks=blocks,
+                         final_norm=norm, head=PartSpec("linear_head", {"vocab": cfg.vocab, "width": cfg.width}),
+                         vocab_size=cfg.vocab, max_positions=4096)
+
+    register_architecture("ToyDecayForCausalLM", ToyConfig, build_toy, replace=True)
+
+    cfg = ToyConfig()
+    write_random_model(tmp_path, cfg, seed=1)                    # the random-weights mode knows the new parts
+    assert config_from_dict(json.loads((tmp_path / "config.json").read_text())) == cfg
+    from safetensors.torch import load_file
+    w = load_file(str(tmp_path / "model.safetensors"))
+    assert "model.layers.1.mixer.in_proj.weight" in w and len(w) == 2 * 7 + 3
+
+    def plain(ids):
+        x = w["model.embed_tokens.weight"][ids]
+        for i in range(cfg.layers):
+            p = f"model.layers.{i}."
+            h = qwen2_plain.rms_norm(x, w[p + "input_layernorm.weight"], 1e-5)
+            u = h @ w[p + "mixer.in_proj.weight"].t()
+            s, rows = torch.zeros(cfg.state_width), []
+            for t in range(len(ids)):
+                s = cfg.decays[i] * s + u[t]
+                rows.append(s)
+            x = x + torch.stack(rows) @ w[p + "mixer.out_proj.weight"].t()
+            h = qwen2_plain.rms_norm(x, w[p + "post_attention_layernorm.weight"], 1e-5)
+            x = x + qwen2_plain.swiglu_mlp(h, w, p + "mlp.")
+        return qwen2_plain.rms_norm(x, w["model.norm.weight"], 1e-5) @ w["lm_head.weight"].t()
+
+    from pyre_b200.config import architecture_of
+    model = Model(architecture_of(cfg).build(cfg), torch.float32, "cuda")
+    assert model.kv_groups == [] and len(model.state_groups) == 1 and model.state_groups[0].n_layers == 2
+    model.load_weights(tmp_path)
+    cache, stepper = runtime_for_model(model, 64, 16, max_requests=3)
+    a, b = H.random_ids(50, 23, seed=1), H.random_ids(50, 9, seed=2)
+    cache.begin("a"); cache.begin("b")
+    got_a = [stepper.step([StepEntry("a", a[:7], list(range(7)))])]
+    both = stepper.step([StepEntry("b", b[:4], list(range(4))), StepEntry("a", a[7:9], [0, 1])])
+    got_b, got_a = [both[:4]], got_a + [both[4:]]
+    both = stepper.step([StepEntry("a", a[9:], list(range(14))), StepEntry("b", b[4:], list(range(5)))])
+    got_a.append(both[:14]); got_b.append(both[14:])
+    torch.testing.assert_close(torch.cat(got_a).cpu(), plain(a), rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(torch.cat(got_b).cpu(), plain(b), rtol=1e-4, atol=1e-5)
+    # a slot is zeroed for its next owner
+    cache.end("a"); cache.begin("c")
+    got_c = stepper.step([StepEntry("c", b, list(range(9)))])
+    torch.testing.assert_close(got_c.cpu(), plain(b), rtol=1e-4, atol=1e-5)
