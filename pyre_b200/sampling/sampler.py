@@ -27,14 +27,13 @@ class Sampler:
         if all(p.temperature == 0.0 for p in params):
             ids = ops.sample(logits)
         else:
-            host = np.empty((R, 4), dtype=np.int32)
-            host[:, 0] = np.asarray([p.temperature for p in params], dtype=np.float32).view(np.int32)
             seeds = np.asarray([p.seed & 0x7FFFFFFFFFFFFFFF for p in params], dtype=np.int64)
-            host[:, 1:3] = seeds.view(np.int32).reshape(R, 2)
-            host[:, 3] = np.asarray(token_index, dtype=np.int32)
-            dev = torch.from_numpy(host).to(self.device, non_blocking=False)
-            temperature = dev[:, 0].contiguous().view(torch.float32)
-            seeds_dev = dev[:, 1:3].contiguous().view(torch.int64).reshape(R)
-            tix = dev[:, 3].contiguous()
+            small = np.empty((2, R), dtype=np.int32)
+            small[0] = np.asarray([p.temperature for p in params], dtype=np.float32).view(np.int32)
+            small[1] = np.asarray(token_index, dtype=np.int32)
+            seeds_dev = torch.from_numpy(seeds).to(self.device)
+            small_dev = torch.from_numpy(small).to(self.device)
+            temperature = small_dev[0].view(torch.float32)
+            tix = small_dev[1]
             ids = ops.sample(logits, temperature, seeds_dev, tix)
         return ids.tolist()

@@ -18,8 +18,14 @@ pytestmark = pytest.mark.gpu
 DTYPES = [torch.float32, torch.bfloat16]
 
 
-def tol(dtype, scale=1.0):
-    return dict(rtol=2e-5, atol=2e-6 * scale) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-3 * scale)
+def close(got, want, dtype, roundings=1):
+    """Largest error against the size of the part's output.  float32: sums in another order,
+    1e-5 of the largest output.  bfloat16: every tensor the part rounds to bf16 on the way
+    (``roundings`` of them) may be off by 2^-8 relative, so the bound is that many times
+    0.4 % of the largest output."""
+    bound = (1e-5 if dtype == torch.float32 else roundings * 2.0 ** -8) * float(want.abs().max())
+    err = (got.float().cpu() - want).abs()
+    assert float(err.max()) <= bound, f"max error {float(err.max()):.3e} > {bound:.3e} (output max {float(want.abs().max()):.3f})"
 
 
 def mini_context(dtype, token_ids=None, positions=None):
@@ -60,7 +66,7 @@ def test_norm_part(dtype):
     delta = torch.randn(9, 120, device="cuda").to(dtype)
     want = qwen2_plain.rms_norm((x + delta.float()).cpu(), w["weight"], 3e-6)
     got = norm.forward(mini_context(dtype, positions=list(range(9))), x, delta=delta)
-    torch.testing.assert_close(got.float().cpu(), want, **tol(dtype))
+    close(got, want, dtype)
 
 
 @pytest.mark.parametrize("head_dim,theta", [(16, 1e4), (48, 5e4), (128, 1e6)])
@@ -82,7 +88,7 @@ def test_feed_forward_part(dtype):
     h = torch.randn(11, 72, device="cuda").to(dtype)
     want = qwen2_plain.swiglu_mlp(h.float().cpu(), w, "")
     got = ffn.forward(mini_context(dtype, positions=list(range(11))), h)
-    torch.testing.assert_close(got.float().cpu(), want, **tol(dtype, 3.0))
+    close(got, want, dtype, roundings=4)      # input, gate/up, activation, output
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -97,7 +103,7 @@ def test_embedding_and_head_parts(dtype):
     h = torch.randn(3, 40, device="cuda").to(dtype)
     logits = head.forward(None, h)
     assert logits.dtype == torch.float32
-    torch.testing.assert_close(logits.cpu(), h.float().cpu() @ wh["weight"].t(), **tol(dtype, 2.0))
+    close(logits, h.float().cpu() @ wh["weight"].t(), torch.float32)      # fp32 logits from the accumulator in both modes
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -111,7 +117,7 @@ def test_attention_part(dtype, nh, nkv, hd, window):
     width, S, page = 56, 29, 8
     att = make("mixer", "attention", dtype, width=width, n_heads=nh, n_kv_heads=nkv, head_dim=hd, window=window,
                position=PartSpec("rotary", {"head_dim": hd, "theta": 1e4}))
-    w = load_random(att, 4, scale=0.4)
+    w = load_random(att, 4, scale=0.15)
     h = torch.randn(S, width, device="cuda").to(dtype)
 
     hf = h.float().cpu()
@@ -136,7 +142,7 @@ def test_attention_part(dtype, nh, nkv, hd, window):
         outs.append(att.forward(ctx, h[start:start + n].contiguous(), BoundCall(0, 0, 0, 0, True)))
         cache.commit("r", start + n)
     got = torch.cat(outs).float().cpu()
-    torch.testing.assert_close(got, want, **tol(dtype, 3.0))
+    close(got, want, dtype, roundings=5)      # qkv, rotated q and k, v, attention output, result
 
 
 # --------------------------------------------------------------------------- whole models from specs
