@@ -1,0 +1,290 @@
+"""Benchmark of the serving step: decode tokens/s and prefill tokens/s of a
+Qwen2.5-7B-shaped model with random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of a batch of 8 requests whose prompts of 2,048 tokens are
+already cached (context 2,048 + tokens decoded so far, inside the benchmark context of
+4,096).  It prints ONE JSON line:
+
+  value            decoded tokens/s of the timed K steps, timed on the device with CUDA
+                   events (host tokens chosen beforehand, sampling kernel included)
+  e2e              the same through the Python entry point (Engine.step): every step
+                   uploads its integer arrays from pinned host memory and reads the sampled
+                   ids back to the host
+  prefill          one prompt of 2,048 tokens in one step: tokens/s, ms, fraction of the
+                   bf16 peak that its flops reach
+  roofline         bytes the decode step must read (every weight once + the cache of the
+                   live requests) / its time, against the HBM peak
+  points           decode tokens/s at batch 1 and 64
+
+Peaks come from MEASURED_PEAKS.json beside this file if it is there, else from the
+fallback figures (6.65 TB/s copy bandwidth, 1.59 PFLOP/s bf16).  Every step streams
+15 GB of weights, far more than the 126 MB of L2, so no separate L2 flush is needed.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# BASELINE.json configs[2]: the Qwen2.5-7B shape
+CONFIG_7B = dict(architectures=["Qwen2ForCausalLM"], hidden_size=3584, intermediate_size=18944,
+                 num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, head_dim=128,
+                 vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                 max_position_embeddings=32768)
+PROMPT_LEN = 2048
+CONTEXT = 4096
+PAGE_SIZE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        try:
+            raw = json.loads(p.read_text())
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(raw.get("bf16_tflops_sustained", raw["bf16_tflops"])),
+                    "source": "measured"}
+        except (KeyError, ValueError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0):
+        self.index, self.rows, self.proc, self.thread = index, [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def mark(self) -> int:
+        return len(self.rows)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, lo: int = 0, hi: "int | None" = None) -> dict:
+        rows = [r for r in self.rows[lo:hi] if len(r) == 6] or [r for r in self.rows if len(r) == 6]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        mhz = sorted(int(r[0]) for r in rows if r[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None,
+                "sm_max_mhz": int(rows[0][1]) if rows[0][1].isdigit() else None, "reasons": reasons,
+                "samples": len(rows)}
+
+
+def model_numbers(cfg: dict, layers: int):
+    """Weight bytes a decode step reads, cache bytes per token, and flops of a step of T tokens."""
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = H * (nh + 2 * nkv) * hd + nh * hd * H + 3 * H * I
+    small = layers * (2 * H + (nh + 2 * nkv) * hd) * 4 + H * 4
+    weight_bytes = (layers * per_layer + V * H) * 2 + small
+    kv_bytes_per_token = layers * 2 * nkv * hd * 2
+
+    def flops(T: int, context_start: int, logit_rows: int) -> float:
+        linear = 2.0 * T * layers * per_layer
+        # causal attention of T new tokens over context_start cached ones: QK^T and PV
+        keys = T * context_start + T * (T + 1) / 2
+        attn = 4.0 * layers * nh * hd * keys
+        return linear + attn + 2.0 * logit_rows * H * V
+    return weight_bytes, kv_bytes_per_token, flops
+
+
+def run_ours(args) -> dict:
+    import numpy as np
+    import torch
+
+    from pyre_b200 import Engine, SamplingParams
+    from pyre_b200.config import config_from_dict
+    from pyre_b200.engine.step import StepEntry
+    from pyre_b200.kernels import lib, ops
+
+    peaks = load_peaks()
+    cfg_raw = dict(CONFIG_7B)
+    layers_full = cfg_raw["num_hidden_layers"]
+    layers = args.layers or layers_full
+    cfg_raw["num_hidden_layers"] = layers
+    cfg = config_from_dict(cfg_raw)
+    B = args.batch
+    steps, warmup = args.steps, max(args.warmup, 3)
+    biggest = max(B, 64 if not args.skip_points else B)
+    tokens_needed = biggest * (PROMPT_LEN + 64 + warmup + steps + PAGE_SIZE) + 2 * CONTEXT
+    torch.cuda.set_device(0)
+    engine = Engine(config=cfg, seed=0, dtype="bfloat16", device="cuda:0", page_size=PAGE_SIZE,
+                    max_cache_tokens=tokens_needed, max_num_seqs=biggest, max_num_batched_tokens=PROMPT_LEN,
+                    prefill_chunk=PROMPT_LEN, max_model_len=CONTEXT)
+    stepper, cache = engine.stepper, engine.cache
+    vocab = cfg.vocab_size
+    rng = np.random.default_rng(0)
+    weight_bytes, kv_per_token, flops = model_numbers(cfg_raw, layers)
+    clocks = ClockSampler(0)
+    clocks.start()
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    # ---------------------------------------------------------------- prefill, 2,048 tokens in one step
+    def prefill_once(rid):
+        cache.begin(rid)
+        ids = rng.integers(0, vocab, PROMPT_LEN).tolist()
+        logits = stepper.step([StepEntry(rid, ids, [PROMPT_LEN - 1])])
+        return ops.sample(logits)
+
+    for i in range(2):
+        prefill_once(("warm", i))
+        cache.end(("warm", i))
+    torch.cuda.synchronize()
+    times = []
+    for i in range(args.prefill_reps):
+        a, b = ev(), ev()
+        a.record()
+        prefill_once(("pf", i))
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+        cache.end(("pf", i))
+    pf_ms = sorted(times)[len(times) // 2]
+    pf_flops = flops(PROMPT_LEN, 0, 1)
+    prefill = {"value": round(PROMPT_LEN / pf_ms * 1e3, 1), "tokens": PROMPT_LEN, "ms": round(pf_ms, 3),
+               "frac": round(pf_flops / (pf_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+
+    # ---------------------------------------------------------------- decode, device-timed
+    def decode_run(batch: int, n_warm: int, n_steps: int, tag: str):
+        reqs = [(tag, i) for i in range(batch)]
+        for r in reqs:
+            cache.begin(r)
+            stepper.step([StepEntry(r, rng.integers(0, vocab, PROMPT_LEN).tolist(), [])])
+        toks = rng.integers(0, vocab, (n_warm + n_steps, batch))
+
+        def one(k):
+            logits = stepper.step([StepEntry(r, [int(toks[k, i])], [0]) for i, r in enumerate(reqs)])
+            return ops.sample(logits)
+
+        for k in range(n_warm):
+            one(k)
+        torch.cuda.synchronize()
+        launches0, mark0 = lib.launch_count, clocks.mark()
+        a, b = ev(), ev()
+        a.record()
+        for k in range(n_warm, n_warm + n_steps):
+            one(k)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / n_steps
+        info = {"ms": ms, "launches": lib.launch_count - launches0, "clock_rows": (mark0, clocks.mark()),
+                "mean_context": PROMPT_LEN + n_warm + (n_steps + 1) / 2}
+        for r in reqs:
+            cache.end(r)
+        return batch / ms * 1e3, info
+
+    value, info = decode_run(B, warmup, steps, "dec")
+    ms_per_step = info["ms"]
+    step_bytes = weight_bytes + kv_per_token * info["mean_context"] * B
+    achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": peaks["source"]}
+    clock_summary = clocks.summary(*info["clock_rows"])
+
+    points = {}
+    if not args.skip_points:
+        for b_ in (1, 64):
+            v, _ = decode_run(b_, 3, max(8, steps // 2), f"p{b_}")
+            points[f"decode_b{b_}"] = round(v, 1)
+
+    # ---------------------------------------------------------------- end to end through Engine.step
+    sp = SamplingParams(max_new_tokens=warmup + steps + 2, ignore_eos=True)
+    sids = [engine.add_request(rng.integers(0, vocab, PROMPT_LEN).tolist(), params=sp) for _ in range(B)]
+    live = [engine._requests[sid] for sid in sids]
+    while any(not r.generated for r in live):
+        engine.step()                      # the prompts, one per step under the token budget
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    up0 = stepper._staging.bytes_uploaded + engine.sampler.bytes_uploaded
+    down0 = engine.sampler.bytes_downloaded
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    e2e = {"value": round(B * steps / dt, 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": (stepper._staging.bytes_uploaded + engine.sampler.bytes_uploaded - up0) // steps,
+           "d2h_bytes_per_step": (engine.sampler.bytes_downloaded - down0) // steps}
+    while engine.has_unfinished():
+        engine.step()
+    clocks.stop()
+
+    return {
+        "metric": "decode tok/s (Qwen2.5-7B shape, batch 8, 2,048-token prompts)", "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "Qwen2.5-7B-shaped, random weights", "layers": layers, "layers_full": layers_full,
+                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                   "global_batch": B, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": PAGE_SIZE,
+                   "parallelism": "single GPU", "l2": "inputs larger than L2 (15 GB of weights per step)"},
+        "clocks": clock_summary, "e2e": e2e, "gpu_launches": info["launches"], "prefill": prefill,
+        "roofline": roofline, "points": points, "impl": "ours",
+    }
+
+
+def run_reference(args) -> dict:
+    from baseline import reference_arm
+    return reference_arm.run(args, CONFIG_7B, PROMPT_LEN)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")
+    ap.add_argument("--prefill-reps", type=int, default=5)
+    ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
+    args = ap.parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
+        return 2
+    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

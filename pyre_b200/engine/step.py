@@ -40,6 +40,7 @@ class _Staging:
         self.bufs = [None, None]
         self.events = [None, None]
         self.turn = 0
+        self.bytes_uploaded = 0
 
     def upload(self, flat: np.ndarray) -> torch.Tensor:
         i = self.turn
@@ -54,6 +55,7 @@ class _Staging:
         host.numpy()[:] = flat
         dev = torch.empty(n, dtype=torch.int32, device=self.device)
         dev.copy_(host, non_blocking=True)
+        self.bytes_uploaded += n * 4
         ev = torch.cuda.Event()
         ev.record()
         self.events[i] = ev

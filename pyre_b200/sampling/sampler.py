@@ -17,6 +17,8 @@ class Sampler:
 
     def __init__(self, device):
         self.device = torch.device(device)
+        self.bytes_uploaded = 0      # sampling parameters sent to the device
+        self.bytes_downloaded = 0    # chosen ids read back
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], token_index: Sequence[int]) -> list[int]:
         """``logits`` [R, V] fp32; ``params[r]`` and ``token_index[r]`` (how many tokens row r's
@@ -34,6 +36,8 @@ class Sampler:
             seeds_dev = torch.from_numpy(seeds).to(self.device)
             small_dev = torch.from_numpy(small).to(self.device)
             temperature = small_dev[0].view(torch.float32)
+            self.bytes_uploaded += seeds.nbytes + small.nbytes
             tix = small_dev[1]
             ids = ops.sample(logits, temperature, seeds_dev, tix)
+        self.bytes_downloaded += R * 4
         return ids.tolist()
