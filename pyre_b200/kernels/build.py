@@ -30,6 +30,7 @@ LIBRARIES = {
     "sampling": "sampling.cu",
     "attention_generic": "attention_generic.cu",
     "gemm_f32": "gemm_f32.cu",
+    "attention_mma": "attention_mma.cu",
 }
 
 HEADERS = ["common.cuh"]

@@ -25,6 +25,7 @@ SIGNATURES: dict[str, tuple[str, list]] = {
     "pyre_sample": ("sampling", [P, LL, P, P, P, P, I, I, P]),
     "pyre_paged_attention_generic": ("attention_generic", [P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, P]),
     "pyre_sgemm_nt": ("gemm_f32", [P, LL, P, LL, P, LL, P, I, I, I, P]),
+    "pyre_paged_attention_mma": ("attention_mma", [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P]),
 }
 
 _ERRORS = {100001: "bad argument", 100002: "unsupported size"}

@@ -222,6 +222,63 @@ def paged_attention_generic(q: torch.Tensor, cache_layer: torch.Tensor, block_ta
     return out
 
 
+MMA_MAX_HEAD_DIM = 128
+_SM_COUNT = 148
+
+
+def attention_splits(n_tokens: int, n_seqs: int, n_heads: int, n_kv_heads: int, max_context: int,
+                     window: "int | None") -> int:
+    """How many ways the tensor-core kernel splits each sequence's keys: enough CTAs for
+    two per SM, but at least four 16-key tiles per split."""
+    n_rep = n_heads // n_kv_heads
+    hpg = min(n_rep, 16)
+    tpg = 16 // hpg
+    ctas = (n_tokens // tpg + n_seqs) * n_kv_heads * (-(-n_rep // hpg))
+    span = max_context if not window else min(max_context, window + tpg)
+    tiles = -(-span // 16) + 1
+    return int(max(1, min(-(-2 * _SM_COUNT // max(ctas, 1)), -(-tiles // 4), 64)))
+
+
+def paged_attention_mma(q: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor,
+                        cu_seqlens: torch.Tensor, positions: torch.Tensor, n_seqs: int, n_heads: int,
+                        n_kv_heads: int, head_dim: int, scale: float, window: "int | None" = None,
+                        n_splits: int = 1, out: "torch.Tensor | None" = None,
+                        scratch: "torch.Tensor | None" = None) -> torch.Tensor:
+    """bfloat16 attention on the tensor cores over the block table (decode tokens and
+    prompt portions alike); ``n_splits`` > 1 splits each sequence's keys over CTAs and needs
+    ``T * nh * n_splits * (hd + 2)`` floats of scratch (allocated here if not given)."""
+    _check(q, "q", torch.bfloat16, 2)
+    _check(cache_layer, "cache_layer", torch.bfloat16, 5)
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    _check(positions, "positions", torch.int32, 1)
+    T = q.shape[0]
+    if q.shape[1] != n_heads * head_dim:
+        raise ValueError(f"q has {q.shape[1]} columns, expected nh * hd = {n_heads * head_dim}")
+    if head_dim % 16 or not 16 <= head_dim <= MMA_MAX_HEAD_DIM:
+        raise UnsupportedSize(f"head_dim {head_dim}: the tensor-core attention takes multiples of 16 up to {MMA_MAX_HEAD_DIM}")
+    if n_heads % n_kv_heads:
+        raise UnsupportedSize(f"{n_heads} query heads cannot be shared among {n_kv_heads} key/value heads")
+    page_size = cache_layer.shape[3]
+    if tuple(cache_layer.shape[1:]) != (2, n_kv_heads, page_size, head_dim):
+        raise ValueError(f"cache layer shape {tuple(cache_layer.shape)} does not match the head sizes")
+    if cu_seqlens.shape[0] != n_seqs + 1 or positions.shape[0] != T or block_table.shape[0] < n_seqs:
+        raise ValueError("cu_seqlens, positions and block_table do not match the batch")
+    if out is None:
+        out = torch.empty_like(q)
+    n_splits = int(n_splits)
+    if n_splits > 1:
+        need = T * n_heads * n_splits * (head_dim + 2)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+        elif scratch.dtype != torch.float32 or scratch.numel() < need or not scratch.is_contiguous():
+            raise ValueError(f"scratch must be {need} contiguous floats")
+    lib.call("pyre_paged_attention_mma", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(), _ptr(scratch),
+             block_table.data_ptr(), block_table.stride(0), cu_seqlens.data_ptr(), positions.data_ptr(), T, n_seqs,
+             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), n_splits, _stream())
+    return out
+
+
 def sgemm_nt(a: torch.Tensor, w: torch.Tensor, bias: "torch.Tensor | None" = None,
              out: "torch.Tensor | None" = None) -> torch.Tensor:
     """C = A W^T (+ bias) in IEEE fp32 on the CUDA cores; a [M, K], w [N, K]."""

@@ -69,7 +69,11 @@ class Attention(Part):
         self.w_o = tensors["o_proj.weight"]
 
     def kernel_libraries(self):
-        libs = ["elementwise", "attention_generic"] + self.position.kernel_libraries()
+        libs = ["elementwise"] + self.position.kernel_libraries()
+        if self.dtype == torch.bfloat16 and self.head_dim <= ops.MMA_MAX_HEAD_DIM:
+            libs.append("attention_mma")
+        else:
+            libs.append("attention_generic")
         if self.dtype == torch.float32:
             libs.append("gemm_f32")
         return libs
@@ -87,8 +91,15 @@ class Attention(Part):
         cos, sin = self.position.tables(ctx)
         q = ops.qkv_rope_write(qkv, self.b_qkv, cos, sin, layer if call.kv_write else None, kv.slot_mapping,
                                self.n_heads, self.n_kv_heads, self.head_dim, self.position.rotary_dim, kv.page_size)
-        a = ops.paged_attention_generic(q, layer, kv.block_table, ctx.seq_of_token, ctx.positions, self.n_heads,
-                                        self.n_kv_heads, self.head_dim, self.scale, self.window)
+        if self.dtype == torch.bfloat16 and self.head_dim <= ops.MMA_MAX_HEAD_DIM:
+            splits = ops.attention_splits(ctx.num_tokens, ctx.num_seqs, self.n_heads, self.n_kv_heads,
+                                          ctx.max_context, self.window)
+            a = ops.paged_attention_mma(q, layer, kv.block_table, ctx.cu_seqlens, ctx.positions, ctx.num_seqs,
+                                        self.n_heads, self.n_kv_heads, self.head_dim, self.scale, self.window, splits)
+        else:
+            # float32 and head sizes above 128: the exact fp32-arithmetic kernel
+            a = ops.paged_attention_generic(q, layer, kv.block_table, ctx.seq_of_token, ctx.positions, self.n_heads,
+                                            self.n_kv_heads, self.head_dim, self.scale, self.window)
         return ops.linear(a, self.w_o)
 
 

@@ -198,6 +198,51 @@ def test_paged_attention_generic(ops, dtype, nh, nkv, hd, page, window):
     assert (got[0, :hd].float() - v_far).abs().max() < 0.2 * v_far.abs().max() + 0.1
 
 
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 4, 37),
+                                                   (8, 2, 64, 32, None), (28, 4, 128, 16, None), (7, 1, 128, 16, 50),
+                                                   (40, 2, 80, 16, None), (5, 5, 112, 8, 19), (16, 16, 96, 16, None)])
+@pytest.mark.parametrize("n_splits", [1, 3])
+def test_paged_attention_mma(ops, nh, nkv, hd, page, window, n_splits):
+    """The tensor-core kernel on a mixed batch (a decode token deep in a long context, a
+    prompt portion that starts in the middle of a page, a short whole prompt, a second decode
+    token) with scrambled pages, unowned slots full of NaN and one far key that decides."""
+    g = torch.Generator(device="cuda").manual_seed(15)
+    ctx_lens = [301, 77, 9, 160]
+    new = [1, 20, 9, 1]
+    n_pages = sum(-(-c // page) for c in ctx_lens) + 3
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(16)).tolist()
+    W = max(-(-c // page) for c in ctx_lens)
+    table = torch.full((4, W), -1, dtype=torch.int32)
+    for s_, c in enumerate(ctx_lens):
+        for lp in range(-(-c // page)):
+            table[s_, lp] = perm.pop()
+    table = table.cuda()
+    cache = torch.randn(n_pages, 2, nkv, page, hd, device="cuda", generator=g)
+    for s_, c in enumerate(ctx_lens):
+        if c % page:
+            cache[int(table[s_, (c - 1) // page]), :, :, c % page:] = float("nan")
+    for pg in perm:
+        cache[pg] = float("nan")
+    seq_of_token = torch.tensor(sum(([s_] * n for s_, n in enumerate(new)), []), dtype=torch.int32, device="cuda")
+    positions = torch.tensor(sum((list(range(c - n, c)) for c, n in zip(ctx_lens, new)), []), dtype=torch.int32, device="cuda")
+    cu = torch.tensor([0, 1, 21, 30, 31], dtype=torch.int32, device="cuda")
+    T = int(seq_of_token.shape[0])
+    q = torch.randn(T, nh * hd, device="cuda", generator=g)
+    far = 3 if not window else ctx_lens[0] - window + 1
+    pg, off = int(table[0, far // page]), far % page
+    cache[pg, 0, 0, off] = q[0, :hd] * 3.0
+    cache, q = cache.to(torch.bfloat16), q.to(torch.bfloat16)
+    scale = hd ** -0.5
+    want = plain_paged_attention(q.float(), cache.float(), table, seq_of_token, positions, nh, nkv, hd, scale, window)
+    got = ops.paged_attention_mma(q, cache, table, cu, positions, 4, nh, nkv, hd, scale, window, n_splits)
+    assert torch.isfinite(got).all()
+    torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=1.2e-2)
+    exact = ops.paged_attention_generic(q, cache, table, seq_of_token, positions, nh, nkv, hd, scale, window)
+    assert (got.float() - exact.float()).abs().max().item() < 0.03
+    v_far = cache[pg, 1, 0, off].float()
+    assert (got[0, :hd].float() - v_far).abs().max() < 0.2 * v_far.abs().max() + 0.1
+
+
 def test_sampling(ops):
     from plain import qwen2_plain
     g = torch.Generator(device="cuda").manual_seed(7)

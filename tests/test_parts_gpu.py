@@ -36,7 +36,8 @@ def mini_context(dtype, token_ids=None, positions=None):
                        token_ids=torch.tensor(token_ids or [0] * n, dtype=torch.int32, device="cuda"),
                        positions=torch.tensor(positions or list(range(n)), dtype=torch.int32, device="cuda"),
                        seq_of_token=z, cu_seqlens=torch.tensor([0, n], dtype=torch.int32, device="cuda"),
-                       logit_rows=z[:0], cu_seqlens_host=np.array([0, n]), start_pos_host=np.array([0]),
+                       logit_rows=z[:0], cu_seqlens_host=np.array([0, n]),
+                       start_pos_host=np.array([positions[0] if positions is not None else 0]),
                        error_flag=torch.zeros(1, dtype=torch.int32, device="cuda"))
 
 
