@@ -31,9 +31,12 @@ LIBRARIES = {
     "attention_generic": "attention_generic.cu",
     "gemm_f32": "gemm_f32.cu",
     "attention_mma": "attention_mma.cu",
+    "attention_mma_noalloc": "attention_mma_noalloc.cu",
 }
 
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "attention_mma_noalloc.h"]
+# sources that a library's source includes (they count towards its fingerprint)
+INCLUDED_SOURCES = {"attention_mma_noalloc": ["attention_mma.cu"]}
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -97,7 +100,7 @@ def build_dir() -> Path:
 def _fingerprint(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    for rel in [LIBRARIES[name]] + sorted(HEADERS):
+    for rel in [LIBRARIES[name]] + INCLUDED_SOURCES.get(name, []) + sorted(HEADERS):
         p = CSRC / rel
         h.update(rel.encode())
         h.update(p.read_bytes())
