@@ -7,12 +7,11 @@
  * Who that is.  pyre_paged_attention_mma() splits long contexts over several CTAs and
  * needs a few megabytes of scratch for the partial results; its caller passes a scratch
  * pointer, which in practice comes from cudaMalloc or from a framework's allocator.  Some
- * callers cannot do that at the point where they call attention: code running between
- * cudaStreamBeginCapture and cudaStreamEndCapture (allocation is illegal there), a
- * latency-critical serving loop whose memory budget was fixed at start-up and must never
- * grow or fragment, a plug-in hosted by a runtime that owns all device memory and hands
- * none out, or a thin C or Rust host that links this library without a device allocator
- * of its own.  For them the scratch lives inside the library, in a file-scope
+ * callers cannot do that at the point where they call attention: a latency-critical
+ * serving loop whose memory budget was fixed at start-up and must never grow or
+ * fragment, a plug-in hosted by a runtime that owns all device memory and hands none
+ * out, or a thin C or Rust host that links this library without a device allocator of
+ * its own.  For them the scratch lives inside the library, in a file-scope
  * `static __device__` array, and the entry point below uses it.
  *
  * What it costs.  The array is PYRE_NOALLOC_SCRATCH_FLOATS floats (16 MiB).  Every GPU on

@@ -1,8 +1,8 @@
 """The allocation-free attention entry point, called through its exported C symbol.
 
 Some callers of the kernel library cannot allocate device memory where they call
-attention (inside a stream capture, in a serving loop with a fixed memory budget, under a
-host runtime that owns all device memory); ``pyre_paged_attention_mma_noalloc`` keeps the
+attention (in a serving loop with a fixed memory budget, under a host runtime that owns
+all device memory, from a C host without an allocator); ``pyre_paged_attention_mma_noalloc`` keeps the
 split-KV scratch in a device array inside its own library for them.  This test loads
 that library with ctypes, calls the symbol twice in a row on different inputs (the
 array keeps the first call's contents) and checks each result against the ordinary entry
