@@ -226,7 +226,7 @@ def run_ours(args) -> dict:
             points[f"decode_b{b_}"] = round(v, 1)
 
     # ---------------------------------------------------------------- end to end through Engine.step
-    sp = SamplingParams(max_new_tokens=warmup + steps + 2, ignore_eos=True)
+    sp = SamplingParams(max_new_tokens=warmup + steps + B + 8, ignore_eos=True)
     sids = [engine.add_request(rng.integers(0, vocab, PROMPT_LEN).tolist(), params=sp) for _ in range(B)]
     live = [engine._requests[sid] for sid in sids]
     while any(not r.generated for r in live):

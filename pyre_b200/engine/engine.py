@@ -67,7 +67,7 @@ class Engine:
         self.cache = CacheManager(self.model.kv_groups, self.model.state_groups, ec.page_size, num_pages,
                                   ec.max_num_seqs, ec.dtype, ec.device)
         self.cache.set_poison(ec.debug_poison_freed_pages)
-        self.stepper = Stepper(self.model, self.cache, max_positions=max_positions)
+        self.stepper = Stepper(self.model, self.cache, max_positions=max_positions, cuda_graphs=ec.cuda_graphs)
         self.scheduler = Scheduler(self.cache, ec.max_num_seqs, ec.max_num_batched_tokens, ec.prefill_chunk,
                                    self.max_model_len)
         self.sampler = Sampler(ec.device)
@@ -95,8 +95,7 @@ class Engine:
             entries = [StepEntry(s.request.seq_id, s.request.tokens(s.start, s.count),
                                  [s.count - 1] if s.samples else []) for s in plan]
             with torch.cuda.device(self.model.device):
-                ctx = self.stepper.build_context(entries, reserve=False)
-                logits = self.stepper.run_context(ctx)
+                logits = self.stepper.step(entries, reserve=False)
                 sampling = [s for s in plan if s.samples]
                 ids = self.sampler.sample(logits, [s.request.params for s in sampling],
                                           [len(s.request.generated) for s in sampling])

@@ -51,13 +51,13 @@ def build_runtime(model_dir, dtype, max_tokens: int, page_size: int = DEFAULT_PA
 
 
 def runtime_for_model(model: Model, max_tokens: int, page_size: int = DEFAULT_PAGE_SIZE,
-                      max_requests: int = MAX_LIVE_REQUESTS, poison: bool = False):
+                      max_requests: int = MAX_LIVE_REQUESTS, poison: bool = False, cuda_graphs: bool = True):
     """Cache manager and stepper for a model that already has its weights."""
     num_pages = max(1, -(-int(max_tokens) // page_size))
     cache = CacheManager(model.kv_groups, model.state_groups, page_size, num_pages, max_requests, model.dtype,
                          model.device)
     cache.set_poison(poison)
-    stepper = Stepper(model, cache, max_positions=model.spec.max_positions or None)
+    stepper = Stepper(model, cache, max_positions=model.spec.max_positions or None, cuda_graphs=cuda_graphs)
     return cache, stepper
 
 

@@ -42,9 +42,9 @@ class _Staging:
         self.turn = 0
         self.bytes_uploaded = 0
 
-    def upload(self, flat: np.ndarray) -> torch.Tensor:
+    def stage(self, flat: np.ndarray) -> torch.Tensor:
+        """Copy ``flat`` into the pinned buffer whose turn it is; returns that host tensor."""
         i = self.turn
-        self.turn ^= 1
         n = flat.shape[0]
         if self.bufs[i] is None or self.bufs[i].shape[0] < n:
             self.bufs[i] = torch.empty(max(n, 4096) * 2, dtype=torch.int32, pin_memory=True)
@@ -53,29 +53,69 @@ class _Staging:
             self.events[i].synchronize()
         host = self.bufs[i][:n]
         host.numpy()[:] = flat
-        dev = torch.empty(n, dtype=torch.int32, device=self.device)
-        dev.copy_(host, non_blocking=True)
         self.bytes_uploaded += n * 4
+        return host
+
+    def mark_copied(self) -> None:
+        """The copy out of the current pinned buffer has been issued on the current stream."""
         ev = torch.cuda.Event()
         ev.record()
-        self.events[i] = ev
+        self.events[self.turn] = ev
+        self.turn ^= 1
+
+    def upload(self, flat: np.ndarray) -> torch.Tensor:
+        host = self.stage(flat)
+        dev = torch.empty(flat.shape[0], dtype=torch.int32, device=self.device)
+        dev.copy_(host, non_blocking=True)
+        self.mark_copied()
         return dev
 
 
-class Stepper:
-    """Binds a model to a cache manager and runs steps."""
+@dataclass
+class _DecodeGraph:
+    """A captured decode step: the static integer buffer its kernels read, the context whose
+    tensors are views of it, the captured launch sequence and the logits it leaves."""
 
-    def __init__(self, model: Model, cache: CacheManager, max_positions: "int | None" = None):
+    flat_dev: torch.Tensor
+    ctx: StepContext
+    graph: "torch.cuda.CUDAGraph"
+    logits: torch.Tensor
+    replays: int = 0
+
+
+class Stepper:
+    """Binds a model to a cache manager and runs steps.
+
+    Steps that hold only single decoded tokens (one per entry, each wanting its logits) are
+    launch-bound: a few hundred small kernels.  With ``cuda_graphs`` such a step is
+    captured once per shape (number of entries, width of the block tables, split count of
+    the attention) into a CUDA graph whose kernels read a static integer buffer; later
+    steps of that shape copy their integers into the buffer and replay the graph.  The
+    arithmetic is the same launch sequence either way."""
+
+    MAX_GRAPHS = 32
+
+    def __init__(self, model: Model, cache: CacheManager, max_positions: "int | None" = None,
+                 cuda_graphs: bool = False):
         self.model, self.cache = model, cache
         self.device = model.device
         self.max_positions = max_positions
         self._staging = _Staging(self.device)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.steps_run = 0
+        self.cuda_graphs = bool(cuda_graphs) and model.graph_safe
+        self._graphs: dict[tuple, _DecodeGraph] = {}
+        self._graph_pool = None
+        self.graph_replays = 0
+        self.launches_per_graph: dict[tuple, int] = {}
 
-    def build_context(self, entries: Sequence[StepEntry], reserve: bool = True) -> StepContext:
+    def build_context(self, entries: Sequence[StepEntry], reserve: bool = True, table_width: "int | None" = None,
+                      upload: bool = True):
         """Check the entries, make room in the cache (unless the caller has) and lay the
-        batch out flat.  Raises OutOfPages if a pool is too small; nothing is taken then."""
+        batch out flat.  Raises OutOfPages if a pool is too small; nothing is taken then.
+        ``table_width`` pads the block tables to a fixed width (the layout of a captured
+        step must not change); ``upload=False`` returns (context factory, flat host array)
+        for a caller that owns the device buffer."""
         cache = self.cache
         if not entries:
             raise ValueError("a step needs at least one entry")
@@ -126,7 +166,7 @@ class Stepper:
         tables = []
         for g in range(len(cache.groups)):
             slots = np.concatenate([cache.slots_for(g, e.request, s, n) for e, s, n in zip(entries, starts, counts)])
-            table = cache.block_table_rows(g, reqs)
+            table = cache.block_table_rows(g, reqs, table_width)
             tables.append(table.shape)
             pieces += [slots, table.reshape(-1)]
         state_slots = np.asarray([cache.state.slot_of[r] for r in reqs], dtype=np.int32)
@@ -140,13 +180,24 @@ class Stepper:
         flat = np.zeros(max(total, 4), dtype=np.int32)
         for o, p in zip(offsets, pieces):
             flat[o:o + p.shape[0]] = p
-        dev = self._staging.upload(flat)
+        new_lens = [s + n for s, n in zip(starts, counts)]
+
+        def make(dev: torch.Tensor) -> StepContext:
+            return self._make_context(dev, offsets, pieces, tables, entries, new_lens, cu, starts, state_slots,
+                                      T, B, len(rows))
+
+        if not upload:
+            return make, flat
+        return make(self._staging.upload(flat))
+
+    def _make_context(self, dev, offsets, pieces, tables, entries, new_lens, cu, starts, state_slots, T, B, R):
+        cache = self.cache
 
         def view(i):
             return dev[offsets[i]:offsets[i] + pieces[i].shape[0]]
 
         ctx = StepContext(
-            dtype=self.model.dtype, device=self.device, num_tokens=T, num_seqs=B, num_logit_rows=len(rows),
+            dtype=self.model.dtype, device=self.device, num_tokens=T, num_seqs=B, num_logit_rows=R,
             token_ids=view(0), positions=view(1), seq_of_token=view(2), cu_seqlens=view(3), logit_rows=view(4),
             cu_seqlens_host=cu, start_pos_host=np.asarray(starts, dtype=np.int64), error_flag=self.error_flag)
         k = 5
@@ -158,7 +209,7 @@ class Stepper:
         for buf in cache.state.buffers:
             ctx.state_groups.append(StateView(buf, slots_dev, state_slots))
         ctx._entries = entries  # type: ignore[attr-defined]
-        ctx._new_lens = [s + n for s, n in zip(starts, counts)]  # type: ignore[attr-defined]
+        ctx._new_lens = new_lens  # type: ignore[attr-defined]
         return ctx
 
     def run_context(self, ctx: StepContext) -> torch.Tensor:
@@ -168,10 +219,73 @@ class Stepper:
         self.steps_run += 1
         return logits
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], reserve: bool = True) -> torch.Tensor:
         """fp32 logits [R, vocab] on the device, R = total number of wanted places, in the
-        order of the entries and of each entry's ``want``."""
-        return self.run_context(self.build_context(entries))
+        order of the entries and of each entry's ``want``.  The tensor is valid until the
+        next step (a replayed graph writes its logits to the same memory every time)."""
+        if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            return self._graph_step(entries, reserve)
+        return self.run_context(self.build_context(entries, reserve))
+
+    # ------------------------------------------------------------------ captured decode steps
+    def _graph_step(self, entries: Sequence[StepEntry], reserve: bool) -> torch.Tensor:
+        cache = self.cache
+        need = 1
+        for e in entries:
+            need = max(need, -(-(cache.length(e.request) + 1) // cache.page_size))
+        width = 1 << (need - 1).bit_length()            # power-of-two buckets keep the layout stable
+        make, flat = self.build_context(entries, reserve, table_width=width, upload=False)
+        new_lens = [cache.length(e.request) + 1 for e in entries]
+        key = (len(entries), width, self._splits_key(len(entries), max(new_lens)), flat.shape[0])
+        g = self._graphs.get(key)
+        if g is None:
+            if len(self._graphs) >= self.MAX_GRAPHS:
+                self._graphs.pop(next(iter(self._graphs)))
+            # first step of this shape: run it eagerly (its result is this step's result), then
+            # capture the same launch sequence on a static buffer for the steps to come
+            flat_dev = torch.empty(flat.shape[0], dtype=torch.int32, device=self.device)
+            self._copy_flat(flat_dev, flat)
+            ctx = make(flat_dev)
+            eager_logits = self.model.forward(ctx).clone()
+            ctx.scratch.clear()
+            before = lib.launch_count
+            graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                logits = self.model.forward(ctx)
+            self.launches_per_graph[key] = lib.launch_count - before
+            self._graphs[key] = _DecodeGraph(flat_dev, ctx, graph, logits)
+            result = eager_logits
+        else:
+            self._copy_flat(g.flat_dev, flat)
+            g.graph.replay()
+            g.replays += 1
+            self.graph_replays += 1
+            lib.launch_count += self.launches_per_graph[key]
+            result = g.logits
+        for e, new_len in zip(entries, new_lens):
+            cache.commit(e.request, new_len)
+        self.steps_run += 1
+        return result
+
+    def _splits_key(self, n_entries: int, max_context: int) -> tuple:
+        """What the attention kernels derive from host-side facts of a decode step; a
+        captured graph is reused only while these stay the same."""
+        from ..kernels import ops
+        out = set()
+        for blk in self.model.blocks:
+            m = getattr(blk, "mixer", None)
+            if hasattr(m, "n_kv_heads"):
+                out.add(ops.attention_splits(n_entries, n_entries, m.n_heads, m.n_kv_heads, max_context,
+                                             getattr(m, "window", None)))
+        return tuple(sorted(out))
+
+    def _copy_flat(self, flat_dev: torch.Tensor, flat: np.ndarray) -> None:
+        host = self._staging.stage(flat)
+        flat_dev.copy_(host, non_blocking=True)
+        self._staging.mark_copied()
 
     def check_device_errors(self) -> None:
         if int(self.error_flag.item()) != 0:

@@ -9,8 +9,8 @@ from pathlib import Path
 import torch
 
 from .. import parts as _parts  # noqa: F401  (registers the built-in parts)
-from ..parts.base import (BoundCall, PagedKVSpec, StateSpec, collect_libraries, collect_tensors, load_part,
-                          make_part)
+from ..parts.base import (BoundCall, PagedKVSpec, StateSpec, all_graph_safe, collect_libraries, collect_tensors,
+                          load_part, make_part)
 from ..weights import loader, random_init
 from ..weights.specs import TensorSpec
 from .spec import ModelSpec
@@ -59,6 +59,10 @@ class Model:
         self.vocab_size = spec.vocab_size
         self.calls, self.kv_groups, self.state_groups = self._bind_schedule()
         self.loaded = False
+        self.graph_safe = all(all_graph_safe(p) for p in [self.embed, self.final_norm, self.head, *self.blocks])
+        # the mixer's position encoding is built by the mixer itself
+        self.graph_safe = self.graph_safe and all(getattr(getattr(b, 'mixer', None), 'position', None) is None
+                                                  or b.mixer.position.graph_safe for b in self.blocks)
 
     # ------------------------------------------------------------------ schedule
     def _bind_schedule(self):

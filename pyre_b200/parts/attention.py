@@ -22,6 +22,8 @@ class Attention(Part):
     A query at position p sees keys max(0, p - window + 1)..p.
     """
 
+    graph_safe = True
+
     def __init__(self, dtype, device, width: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: "PartSpec | None" = None, qkv_bias: bool = True, o_bias: bool = False,
                  scale: "float | None" = None, window: "int | None" = None):

@@ -85,6 +85,10 @@ class BoundCall:
 
 class Part:
     category: str = ""
+    # True if forward() only launches work on the current stream from device-side inputs
+    # (no host reads of the step's arrays, no host synchronisation): such a part may be
+    # captured in a CUDA graph and replayed for later steps of the same shape.
+    graph_safe: bool = False
 
     def __init__(self, dtype: torch.dtype, device: torch.device):
         self.dtype = dtype
@@ -142,6 +146,10 @@ def load_part(part: Part, tensors: Mapping[str, torch.Tensor], prefix: str = "")
     part.load({name: tensors[prefix + name] for name in part.tensors()})
     for sub_prefix, child in part.children().items():
         load_part(child, tensors, prefix + sub_prefix)
+
+
+def all_graph_safe(part: Part) -> bool:
+    return bool(part.graph_safe) and all(all_graph_safe(c) for c in part.children().values())
 
 
 def collect_libraries(part: Part) -> list[str]:

@@ -15,6 +15,8 @@ class PreNormBlock(Part):
 
     ``names`` gives the prefix of each sub-part's tensors inside the layer."""
 
+    graph_safe = True
+
     DEFAULT_NAMES = {"norm1": "input_layernorm.", "mixer": "self_attn.",
                      "norm2": "post_attention_layernorm.", "ffn": "mlp."}
 

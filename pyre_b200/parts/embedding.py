@@ -12,6 +12,8 @@ from .base import Part, register_part
 class TokenEmbedding(Part):
     """x[t] = table[token[t]], widened to the fp32 residual stream."""
 
+    graph_safe = True
+
     def __init__(self, dtype, device, vocab: int, width: int):
         super().__init__(dtype, device)
         self.vocab, self.width = int(vocab), int(width)
@@ -35,6 +37,8 @@ class LinearHead(Part):
     tensor (full checkpoint name) that stands in when the head's own weight is absent:
     the embedding table of a model with tied embeddings (pyre/loader.py:58-61); the
     storage is then shared, not copied."""
+
+    graph_safe = True
 
     def __init__(self, dtype, device, vocab: int, width: int, tied_to: "str | None" = None):
         super().__init__(dtype, device)

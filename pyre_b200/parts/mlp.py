@@ -13,6 +13,8 @@ class GatedMLP(Part):
     """down(act(gate(h)) * up(h)) without biases.  The gate and up weights are stacked
     into one [2 I, width] matrix at load, so one product feeds the activation kernel."""
 
+    graph_safe = True
+
     def __init__(self, dtype, device, width: int, intermediate: int, activation: str = "silu"):
         super().__init__(dtype, device)
         self.width, self.intermediate = int(width), int(intermediate)

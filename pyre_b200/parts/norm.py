@@ -11,6 +11,8 @@ class RMSNorm(Part):
     """h = (v / sqrt(mean(v^2) + eps)) * weight with v = x + delta, all in fp32; ``x`` is
     the fp32 residual stream and receives the sum."""
 
+    graph_safe = True
+
     def __init__(self, dtype, device, width: int, eps: float):
         super().__init__(dtype, device)
         self.width, self.eps = int(width), float(eps)

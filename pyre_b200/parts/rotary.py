@@ -15,6 +15,8 @@ class Rotary(Part):
     float(position) * inv_freq for the step's tokens, shared by all layers that have
     the same settings.  ``rotary_dim`` < head_dim rotates only the first dims of a head."""
 
+    graph_safe = True
+
     def __init__(self, dtype, device, head_dim: int, theta: float, rotary_dim: "int | None" = None,
                  pairing: str = "half"):
         super().__init__(dtype, device)
@@ -42,6 +44,8 @@ class Rotary(Part):
 
 class NoPosition(Part):
     """No position encoding: queries and keys are used as projected."""
+
+    graph_safe = True
 
     rotary_dim = 0
 
