@@ -293,3 +293,30 @@ PYRE_API int pyre_silu_mul(const void* gu, void* out, int n_tokens, int I, int d
     PYRE_LAUNCH_CHECK();
     return 0;
 }
+
+// ---------------------------------------------------------------------------
+// out[i] = sum_s partials[s * split_stride + i]: adds up the fp32 partial sums of a
+// product whose K was split over CTAs, in a fixed order, and converts.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void sum_partials_kernel(const float* __restrict__ partials, int n_splits, long long split_stride,
+                                    T* __restrict__ out, long long n) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float acc = partials[i];
+        for (int s = 1; s < n_splits; ++s) acc += partials[(long long)s * split_stride + i];
+        out[i] = from_f32<T>(acc);
+    }
+}
+
+PYRE_API int pyre_sum_partials(const float* partials, int n_splits, long long split_stride, void* out, long long n,
+                               int dtype, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (n_splits < 1) return PYRE_ERR_BAD_ARG;
+    const int threads = 256;
+    const int blocks = (int)min((long long)148 * 8, ceil_div_ll(n, threads));
+    if (dtype == PYRE_F32) sum_partials_kernel<float><<<blocks, threads, 0, stream>>>(partials, n_splits, split_stride, (float*)out, n);
+    else if (dtype == PYRE_BF16) sum_partials_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(partials, n_splits, split_stride, (__nv_bfloat16*)out, n);
+    else return PYRE_ERR_BAD_ARG;
+    PYRE_LAUNCH_CHECK();
+    return 0;
+}

@@ -1,0 +1,358 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:  D[x, y] = sum_k X[x, k] * Y[y, k]
+// with X [x_rows, K] and Y [y_rows, K] both row-major (K contiguous), fp32 accumulation in
+// tensor memory, output in fp32 or bfloat16 with arbitrary strides.
+//
+// One kernel serves both orientations of a linear layer y = a W^T (pyre/model.py:84-87):
+//   few tokens (decode)  : X = W (the out-features fill the 128 rows of the MMA), Y = a
+//                          (8..128 tokens are the narrow N side), output stored transposed;
+//                          K may be split over CTAs (blockIdx.z) into fp32 partial sums
+//                          that the consumer kernel adds up, so that shapes with few
+//                          128-row tiles still put a CTA on every SM;
+//   many tokens (prefill): X = a (128 tokens per tile), Y = W (up to 256 features per tile).
+//
+// Structure of a CTA (192 threads), one 128 x BN output tile, K in blocks of 64:
+//   warp 0, one thread : TMA producer.  cp.async.bulk.tensor.2d loads an X box (128 x 64)
+//                        and a Y box (BN x 64) per K block into a ring of shared-memory
+//                        stages, 128-byte swizzled, completion counted on a "full" mbarrier.
+//   warp 1, one thread : issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = BN,
+//                        K = 16, four per K block) from shared-memory descriptors into a
+//                        TMEM accumulator; tcgen05.commit frees each stage ("empty"
+//                        mbarrier) and finally signals the accumulator.  Warp 1 also
+//                        allocates and frees the TMEM columns.
+//   warps 2..5         : epilogue.  tcgen05.ld (32 lanes x 32 bit, 16 columns at a time)
+//                        reads the warp's quarter of the 128 accumulator rows and stores
+//                        it, converted if asked.
+// Rows or K beyond the matrices are zero-filled by TMA, so any x_rows, y_rows and K work
+// (K and the leading dimensions must be multiples of 8 elements: TMA strides are 16-byte
+// multiples).  No load uses cluster multicast.
+//
+// Every wait on an mbarrier is bounded.  If one runs out, the kernel raises the error
+// flag, stops waiting everywhere, skips its stores, frees its tensor memory and returns;
+// the host reads the flag.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;           // rows of X per tile = TMEM lanes
+constexpr int BK = 64;            // K per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 400000;
+constexpr int ERR_TIMEOUT = 2;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false if the limit ran out or another thread already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err_flag) {
+    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 63) == 63 && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    if (err_flag) atomicExch(err_flag, ERR_TIMEOUT);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128B swizzle:
+// start address >> 4, leading byte offset 1 (unused with swizzle), stride byte offset
+// 1024 >> 4 (eight rows), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+
+struct GemmParams {
+    int x_rows, y_rows, K;
+    int k_blocks_per_split;       // K blocks (of 64) per blockIdx.z
+    long long stride_x, stride_y, split_stride;  // output element strides
+    void* out;
+    int out_f32;
+    int* err_flag;
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+    static constexpr int X_BYTES = BM * BK * 2;
+    static constexpr int Y_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = X_BYTES + Y_BYTES;
+    static constexpr int TILES = STAGES * STAGE_BYTES;
+    static constexpr int TOTAL = TILES + (2 * STAGES + 1) * 8 + 16 + 1024;  // + barriers, tmem slot, alignment slack
+};
+
+template <int BN, int STAGES, bool X_CONTIGUOUS_OUT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const GemmParams p) {
+    using L = SmemLayout<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles want 1024-byte alignment
+    uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bar_full = base + L::TILES;
+    const uint32_t bar_empty = bar_full + STAGES * 8;
+    const uint32_t bar_accum = bar_empty + STAGES * 8;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::TILES + (2 * STAGES + 1) * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::TILES + (2 * STAGES + 1) * 8 + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int x0 = blockIdx.x * BM, y0 = blockIdx.y * BN;
+    const int total_kb = (p.K + BK - 1) / BK;
+    const int kb_begin = blockIdx.z * p.k_blocks_per_split;
+    const int kb_end = min(kb_begin + p.k_blocks_per_split, total_kb);
+    const int n_kb = max(kb_end - kb_begin, 0);
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;   // power of two >= 32
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- producer
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_x)) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_y)) : "memory");
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % STAGES;
+                const uint32_t phase = (i / STAGES) & 1;
+                if (!mbar_wait(bar_empty + 8 * s, phase ^ 1, abort_flag, p.err_flag)) break;
+                mbar_expect_tx(bar_full + 8 * s, L::STAGE_BYTES);
+                const uint32_t xs = base + s * L::STAGE_BYTES, ys = xs + L::X_BYTES;
+                const int k = (kb_begin + i) * BK;
+                tma_load_2d(xs, &map_x, bar_full + 8 * s, k, x0);
+                tma_load_2d(ys, &map_y, bar_full + 8 * s, k, y0);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---------------- MMA issuer
+            // instruction descriptor: D fp32 (bit 4), A and B bf16 (bits 7, 10), both K-major,
+            // N >> 3 at bit 17, M >> 4 at bit 24
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % STAGES;
+                const uint32_t phase = (i / STAGES) & 1;
+                ok = mbar_wait(bar_full + 8 * s, phase, abort_flag, p.err_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t xs = base + s * L::STAGE_BYTES, ys = xs + L::X_BYTES;
+                const uint64_t da = umma_desc(xs), db = umma_desc(ys);
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k)   // 16 bf16 = 32 bytes = 2 descriptor units along K
+                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(bar_empty + 8 * s);     // the stage is free once these MMAs have read it
+            }
+            umma_commit(bar_accum);                 // the accumulator is complete
+        }
+    } else {
+        // ---------------- epilogue: warp w reads TMEM lanes 32 (w % 4) .. + 31
+        const int quarter = warp & 3;
+        const int xr = x0 + quarter * 32 + lane;
+        bool ok = true;
+        if (n_kb > 0) ok = mbar_wait(bar_accum, 0, abort_flag, p.err_flag);
+        ok = ok && !*abort_flag;   // the issuer signals the accumulator even when it gave up
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const long long out_base = (long long)blockIdx.z * p.split_stride + (long long)xr * p.stride_x;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+            uint32_t r[16];
+            __syncwarp();   // tcgen05.ld is warp-wide: converge after the per-thread stores
+            if (n_kb > 0) {
+                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = 0u;
+            }
+            if (!ok || xr >= p.x_rows) {
+                // nothing to store for this thread
+            } else if constexpr (!X_CONTIGUOUS_OUT) {
+                // a thread owns a row of the output: 16 consecutive elements (stride_y == 1)
+                const int yc = y0 + c;
+                if (yc + 16 <= p.y_rows) {
+                    if (p.out_f32) {
+                        float4* dst = reinterpret_cast<float4*>((float*)p.out + out_base + yc);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                    } else {
+                        uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)p.out + out_base + yc);
+                        uint32_t w[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                            w[j] = *reinterpret_cast<uint32_t*>(&v);
+                        }
+                        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    }
+                } else {
+                    for (int j = 0; j < 16 && yc + j < p.y_rows; ++j) {
+                        const float v = __uint_as_float(r[j]);
+                        if (p.out_f32) ((float*)p.out)[out_base + yc + j] = v;
+                        else ((__nv_bfloat16*)p.out)[out_base + yc + j] = __float2bfloat16_rn(v);
+                    }
+                }
+            } else {
+                // transposed store: for each y the 32 lanes write 32 consecutive x (stride_x == 1)
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int y = y0 + c + j;
+                    if (y < p.y_rows) {
+                        const float v = __uint_as_float(r[j]);
+                        if (p.out_f32) ((float*)p.out)[out_base + (long long)y * p.stride_y] = v;
+                        else ((__nv_bfloat16*)p.out)[out_base + (long long)y * p.stride_y] = __float2bfloat16_rn(v);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------- teardown: all tensor-memory reads are done before the columns are freed
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// [rows, K] bf16 row-major with leading dimension ld (elements); boxes of box_rows x 64, 128B swizzle.
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return PYRE_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : PYRE_ERR_BAD_ARG;
+}
+
+template <int BN, int STAGES, bool XC>
+int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+    using L = SmemLayout<BN, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, XC>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    gemm_tc_kernel<BN, STAGES, XC><<<grid, THREADS, L::TOTAL, stream>>>(mx, my, p);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// D[x, y] = sum_k X[x, k] Y[y, k] for bf16 X [x_rows, K] (leading dimension ldx) and Y [y_rows, K] (ldy).
+// out[z * split_stride + x * stride_x + y * stride_y] receives split z's partial sum (fp32 if
+// out_f32 else bf16).  One of stride_x, stride_y must be 1: stride_x == 1 selects the transposed
+// store (X = weights), stride_y == 1 the row store (X = tokens).  bn: tile width along y, one of
+// 16, 32, 64, 128, 256.  splits >= 1 divides the K blocks among blockIdx.z.
+PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* Y, int y_rows, long long ldy, int K,
+                          void* out, int out_f32, long long stride_x, long long stride_y, long long split_stride,
+                          int splits, int bn, int* err_flag, cudaStream_t stream) {
+    if (x_rows <= 0 || y_rows <= 0) return 0;
+    if (K <= 0 || K % 8 || ldx % 8 || ldy % 8 || splits < 1) return PYRE_ERR_UNSUPPORTED;
+    if (((uintptr_t)X & 15) || ((uintptr_t)Y & 15)) return PYRE_ERR_UNSUPPORTED;
+    if (stride_x != 1 && stride_y != 1) return PYRE_ERR_BAD_ARG;
+    const bool xc = (stride_x == 1);
+    if (!xc && ((stride_x % 8) || ((uintptr_t)out & 15))) return PYRE_ERR_UNSUPPORTED;  // vector stores of a row
+    CUtensorMap mx, my;
+    int rc = make_map(&mx, X, x_rows, K, ldx, BM);
+    if (rc) return rc;
+    rc = make_map(&my, Y, y_rows, K, ldy, bn);
+    if (rc) return rc;
+    const int total_kb = (K + BK - 1) / BK;
+    if (splits > total_kb) splits = total_kb;
+    GemmParams p;
+    p.x_rows = x_rows; p.y_rows = y_rows; p.K = K;
+    p.k_blocks_per_split = (total_kb + splits - 1) / splits;
+    p.stride_x = stride_x; p.stride_y = stride_y; p.split_stride = split_stride;
+    p.out = out; p.out_f32 = out_f32; p.err_flag = err_flag;
+    dim3 grid(ceil_div(x_rows, BM), ceil_div(y_rows, bn), splits);
+#define GO(BN_, ST_)                                                              \
+    rc = xc ? launch<BN_, ST_, true>(mx, my, p, grid, stream) : launch<BN_, ST_, false>(mx, my, p, grid, stream)
+    switch (bn) {
+        case 16: GO(16, 10); break;
+        case 32: GO(32, 10); break;
+        case 64: GO(64, 8); break;
+        case 128: GO(128, 6); break;
+        case 256: GO(256, 4); break;
+        default: return PYRE_ERR_BAD_ARG;
+    }
+#undef GO
+    return rc;
+}

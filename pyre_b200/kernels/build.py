@@ -31,6 +31,7 @@ LIBRARIES = {
     "attention_generic": "attention_generic.cu",
     "gemm_f32": "gemm_f32.cu",
     "attention_mma": "attention_mma.cu",
+    "gemm_tc": "gemm_tc.cu",
     "attention_mma_noalloc": "attention_mma_noalloc.cu",
 }
 

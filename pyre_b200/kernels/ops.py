@@ -298,16 +298,109 @@ def sgemm_nt(a: torch.Tensor, w: torch.Tensor, bias: "torch.Tensor | None" = Non
     return out
 
 
+_error_flags: dict = {}
+
+
+def device_error_flag(device) -> torch.Tensor:
+    """One int32 per device that kernels raise when a bounded wait runs out or an index is out of range."""
+    key = torch.device(device).index or 0
+    flag = _error_flags.get(key)
+    if flag is None:
+        flag = torch.zeros(1, dtype=torch.int32, device=device)
+        _error_flags[key] = flag
+    return flag
+
+
+def check_device_errors(device="cuda") -> None:
+    flag = device_error_flag(device)
+    code = int(flag.item())
+    if code:
+        flag.zero_()
+        raise lib.KernelError({2: "a tensor-core GEMM gave up waiting on its pipeline (bounded wait ran out)"}.get(
+            code, f"a kernel raised error code {code}"))
+
+
+def tc_gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """The TMA-fed tcgen05 kernel takes bf16 operands whose rows are 16-byte multiples and 16-byte aligned."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2
+            and x.stride(1) == 1 and w.stride(1) == 1 and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def tc_gemm_plan(M: int, N: int, K: int) -> tuple[bool, int, int]:
+    """(weights_as_rows, bn, splits) for y[M, N] = a[M, K] w[N, K]^T.
+
+    Up to 128 tokens the weights take the 128-row side of the MMA and the tokens the
+    narrow side (bn = tokens rounded up to 16/32/64/128); K is split so that about one
+    CTA lands on every SM, each split keeping at least four 64-wide K blocks.  Beyond
+    that the tokens take the rows and 256 output features form a tile."""
+    kb = -(-K // 64)
+    if M <= 128 or N % 8:
+        bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+        tiles = -(-N // 128) * -(-M // bn)
+        splits = max(1, min(_SM_COUNT // tiles if tiles < _SM_COUNT else 1, kb // 4, 16))
+        return True, bn, splits
+    bn = 256 if N >= 256 else 128
+    tiles = -(-M // 128) * -(-N // bn)
+    splits = max(1, min(_SM_COUNT // tiles if tiles * 2 <= _SM_COUNT else 1, kb // 8, 8))
+    return False, bn, splits
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+            plan: "tuple[bool, int, int] | None" = None, reduce: bool = True) -> torch.Tensor:
+    """y = x w^T on the tensor cores (tcgen05, TMEM accumulators, TMA-fed), bf16 in, fp32 accumulate.
+
+    With a split K the kernel leaves fp32 partial sums [splits, M, N]; ``reduce`` adds
+    them up here (fixed order) and converts to ``out_dtype``.  ``reduce=False`` returns the
+    partials for a consumer kernel that adds them itself."""
+    if not tc_gemm_supported(x, w):
+        raise UnsupportedSize("gemm_tc needs bf16 operands with K and leading dimensions that are multiples of 8")
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise ValueError(f"inner sizes differ: x is [{M}, {K}], w is [{N}, {K2}]")
+    weights_as_rows, bn, splits = plan or tc_gemm_plan(M, N, K)
+    splits = max(1, min(splits, -(-K // 64)))
+    err = device_error_flag(x.device)
+    if splits == 1 and reduce:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        target, split_stride = out, 0
+    else:
+        target = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+        split_stride = M * N
+    f32 = int(target.dtype == torch.float32)
+    if weights_as_rows:
+        lib.call("pyre_gemm_tc", w.data_ptr(), N, w.stride(0), x.data_ptr(), M, x.stride(0), K, target.data_ptr(), f32,
+                 1, N, split_stride, splits, bn, err.data_ptr(), _stream())
+    else:
+        lib.call("pyre_gemm_tc", x.data_ptr(), M, x.stride(0), w.data_ptr(), N, w.stride(0), K, target.data_ptr(), f32,
+                 N, 1, split_stride, splits, bn, err.data_ptr(), _stream())
+    if target.dim() == 2:
+        return target
+    if not reduce:
+        return target
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    lib.call("pyre_sum_partials", target.data_ptr(), splits, split_stride, out.data_ptr(), M * N, _dt(out_dtype), _stream())
+    return out
+
+
+USE_TC_GEMM = True
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: "torch.dtype | None" = None) -> torch.Tensor:
     """y = x W^T for a weight in the linear-layer layout [out, in].
 
     float32: the package's own fp32 kernel (no reduced-precision matrix mode).
-    bfloat16: a library product with fp32 accumulation; ``out_dtype=torch.float32`` keeps
-    the accumulator's precision (used for the logits)."""
+    bfloat16: the package's tcgen05 kernel (``gemm_tc``); rows that are no 16-byte multiple
+    (K not a multiple of 8) go to a library product instead, as the reference uses a library
+    for every projection.  ``out_dtype=torch.float32`` keeps the accumulator's precision
+    (used for the logits)."""
     if x.dtype == torch.float32:
         return sgemm_nt(x, w)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise ValueError(f"linear: unsupported dtypes {x.dtype} x {w.dtype}")
+    if USE_TC_GEMM and tc_gemm_supported(x, w):
+        return gemm_tc(x, w, out_dtype or torch.bfloat16)
     if out_dtype is None or out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)
@@ -316,6 +409,5 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: "torch.dtype | None" = N
 def required_libraries(dtype: torch.dtype) -> list[str]:
     """Kernel libraries that a decoder step in ``dtype`` calls (built before the first step)."""
     libs = ["elementwise", "sampling", "attention_generic"]
-    if dtype == torch.float32:
-        libs.append("gemm_f32")
+    libs.append("gemm_f32" if dtype == torch.float32 else "gemm_tc")
     return libs

@@ -76,8 +76,7 @@ class Attention(Part):
             libs.append("attention_mma")
         else:
             libs.append("attention_generic")
-        if self.dtype == torch.float32:
-            libs.append("gemm_f32")
+        libs.append("gemm_f32" if self.dtype == torch.float32 else "gemm_tc")
         return libs
 
     def cache_spec(self):

@@ -52,7 +52,7 @@ class LinearHead(Part):
         self.weight = tensors["weight"]
 
     def kernel_libraries(self):
-        return ["gemm_f32"] if self.dtype == torch.float32 else []
+        return ["gemm_f32"] if self.dtype == torch.float32 else ["gemm_tc"]
 
     def forward(self, ctx, h_rows):
         return ops.linear(h_rows, self.weight, out_dtype=torch.float32)

@@ -34,7 +34,7 @@ class GatedMLP(Part):
         self.w_down = tensors["down_proj.weight"]
 
     def kernel_libraries(self):
-        return ["elementwise"] + (["gemm_f32"] if self.dtype == torch.float32 else [])
+        return ["elementwise"] + (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_tc"])
 
     def forward(self, ctx, h):
         gate_up = ops.linear(h, self.w_gate_up)

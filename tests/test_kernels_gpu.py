@@ -86,6 +86,39 @@ def test_sgemm_is_true_fp32(ops, M, N, K):
         assert torch.equal(ops.sgemm_nt(a[:1].contiguous(), w), got[:1])
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 4608, 3584), (8, 3584, 3584), (8, 3584, 18944), (8, 37888, 3584), (5, 130, 72),
+                                   (16, 256, 64), (17, 1000, 96), (64, 777, 200), (100, 640, 1024), (128, 152064 // 8, 512),
+                                   (129, 512, 256), (300, 1000, 96), (300, 777, 200), (2048, 4608, 3584), (1000, 3584, 1888)])
+def test_gemm_tc_matches_fp32_product(ops, M, N, K):
+    """The tcgen05 kernel against an fp32 product of the same bf16 operands: fp32
+    accumulation, so only the order of the sum and the final rounding differ."""
+    g = torch.Generator(device="cuda").manual_seed(M * 7 + N)
+    a = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    want = a.float() @ w.float().t()
+    got32 = ops.gemm_tc(a, w, torch.float32)
+    ops.check_device_errors()
+    scale = float(want.abs().max())
+    assert float((got32 - want).abs().max()) <= 2e-5 * scale * max(1.0, (K / 64) ** 0.5)
+    got16 = ops.gemm_tc(a, w, torch.bfloat16)
+    assert float((got16.float() - want).abs().max()) <= 2.0 ** -8 * scale
+    # every plan gives the same product: both orientations, every tile width, split K
+    for plan in [(True, 16, 1), (True, 32, 3), (True, 64, 2), (True, 128, 1), (True, 256, 4), (False, 128, 1), (False, 256, 2)]:
+        if not plan[0] and N % 8:
+            continue
+        if plan[0] and M > 4 * plan[1]:
+            continue
+        other = ops.gemm_tc(a, w, torch.float32, plan=plan)
+        assert float((other - want).abs().max()) <= 2e-5 * scale * max(1.0, (K / 64) ** 0.5), f"plan {plan}"
+    ops.check_device_errors()
+    # strided activations (a slice of a wider buffer)
+    if K % 16 == 0:
+        wide = torch.randn(M, 2 * K, device="cuda", generator=g).to(torch.bfloat16)
+        part = wide[:, K:]
+        got = ops.gemm_tc(part, w, torch.float32)
+        assert float((got - part.float() @ w.float().t()).abs().max()) <= 2e-5 * scale * max(1.0, (K / 64) ** 0.5) * 2
+
+
 def plain_rope(x, pos, inv, rot):
     # x [T, n, hd]; half-split pairs over the first rot dims (pyre/model.py:41-63);
     # inv = theta^(-2j/rot) is computed once on the CPU and shared with the kernel under
