@@ -61,23 +61,45 @@ PYRE_API int pyre_embedding(const void* table, int dtype, const int* ids, float*
 // One block per output row; the block size depends on H only, so a row's sum of
 // squares is added in the same order whatever the batch holds.
 // ---------------------------------------------------------------------------
+// delta may come as `n_partials` fp32 partial sums [n_partials][T][H] (a product whose K
+// was split over CTAs): they are added in index order, then to x.
 template <typename T, int VEC>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ w,
+__device__ __forceinline__ void load_delta(Vec<float, VEC>& a, const T* dr, const float* pr, int n_partials,
+                                           long long partial_stride, int i) {
+    if (pr) {
+        Vec<float, VEC> acc = load_vec<float, VEC>(pr + i);
+        for (int s = 1; s < n_partials; ++s) {
+            Vec<float, VEC> q = load_vec<float, VEC>(pr + (size_t)s * partial_stride + i);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) acc.v[k] += q.v[k];
+        }
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) a.v[k] = a.v[k] + acc.v[k];
+    } else {
+        Vec<T, VEC> d = load_vec<T, VEC>(dr + i);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) a.v[k] = a.v[k] + to_f32<T>(d.v[k]);
+    }
+}
+
+template <typename T, int VEC>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ partials,
+                                   int n_partials, long long partial_stride, const float* __restrict__ w,
                                    T* __restrict__ out, const int* __restrict__ rows, int H, float eps, int update_x) {
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     float* xr = x + (size_t)src * H;
     const T* dr = delta ? delta + (size_t)src * H : nullptr;
+    const float* pr = partials ? partials + (size_t)src * H : nullptr;
+    const bool has_delta = dr || pr;
     T* orow = out + (size_t)r * H;
 
     float ss = 0.f;
     for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
         Vec<float, VEC> a = load_vec<float, VEC>(xr + i);
-        if (dr) {
-            Vec<T, VEC> d = load_vec<T, VEC>(dr + i);
-#pragma unroll
-            for (int k = 0; k < VEC; ++k) a.v[k] = a.v[k] + to_f32<T>(d.v[k]);
+        if (has_delta) {
+            load_delta<T, VEC>(a, dr, pr, n_partials, partial_stride, i);
             if (update_x) store_vec<float, VEC>(xr + i, a);
         }
 #pragma unroll
@@ -88,11 +110,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
 
     for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
         Vec<float, VEC> a = load_vec<float, VEC>(xr + i);
-        if (dr && !update_x) {
-            Vec<T, VEC> d = load_vec<T, VEC>(dr + i);
-#pragma unroll
-            for (int k = 0; k < VEC; ++k) a.v[k] = a.v[k] + to_f32<T>(d.v[k]);
-        }
+        if (has_delta && !update_x) load_delta<T, VEC>(a, dr, pr, n_partials, partial_stride, i);
         Vec<float, VEC> g = load_vec<float, VEC>(w + i);
         Vec<T, VEC> o;
 #pragma unroll
@@ -101,14 +119,19 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
     }
 }
 
-PYRE_API int pyre_add_rmsnorm(float* x, const void* delta, const float* weight, void* out, const int* rows,
+// delta: activation dtype [T, H] or null; partials: fp32 [n_partials][T][H] (stride between
+// partials in elements) or null; at most one of the two.
+PYRE_API int pyre_add_rmsnorm(float* x, const void* delta, const float* partials, int n_partials,
+                              long long partial_stride, const float* weight, void* out, const int* rows,
                               int n_rows, int H, float eps, int update_x, int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (rows && update_x) return PYRE_ERR_BAD_ARG;  // two output rows could name one source row
+    if (delta && partials) return PYRE_ERR_BAD_ARG;
+    if (partials && n_partials < 1) return PYRE_ERR_BAD_ARG;
     const bool vec = (H % 4 == 0);
     const int per = vec ? H / 4 : H;
     const int threads = min(512, max(32, ((per + 31) / 32) * 32));
-#define LAUNCH(TT, V) add_rmsnorm_kernel<TT, V><<<n_rows, threads, 0, stream>>>(x, (const TT*)delta, weight, (TT*)out, rows, H, eps, update_x)
+#define LAUNCH(TT, V) add_rmsnorm_kernel<TT, V><<<n_rows, threads, 0, stream>>>(x, (const TT*)delta, partials, n_partials, partial_stride, weight, (TT*)out, rows, H, eps, update_x)
     if (dtype == PYRE_F32) { if (vec) LAUNCH(float, 4); else LAUNCH(float, 1); }
     else if (dtype == PYRE_BF16) { if (vec) LAUNCH(__nv_bfloat16, 4); else LAUNCH(__nv_bfloat16, 1); }
     else return PYRE_ERR_BAD_ARG;
@@ -175,7 +198,27 @@ PYRE_API int pyre_rope_table(const int* positions, const float* inv_freq, float*
 // Dims at and beyond `rot`, and the whole of v, pass through (plus bias).
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void qkv_rope_write_kernel(const T* __restrict__ qkv, const float* __restrict__ bias,
+__device__ __forceinline__ void load_qkv4(float (&v)[4], const T* in, const float* pin, int n_partials,
+                                          long long partial_stride, int idx) {
+    if (pin) {
+        Vec<float, 4> acc = load_vec<float, 4>(pin + idx);
+        for (int s = 1; s < n_partials; ++s) {
+            Vec<float, 4> q = load_vec<float, 4>(pin + (size_t)s * partial_stride + idx);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) acc.v[k] += q.v[k];
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = acc.v[k];
+    } else {
+        Vec<T, 4> a = load_vec<T, 4>(in + idx);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = to_f32<T>(a.v[k]);
+    }
+}
+
+template <typename T>
+__global__ void qkv_rope_write_kernel(const T* __restrict__ qkv, const float* __restrict__ partials, int n_partials,
+                                      long long partial_stride, const float* __restrict__ bias,
                                       const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                       T* __restrict__ q_out, T* __restrict__ cache,
                                       const int* __restrict__ slot_mapping, int nh, int nkv, int hd, int rot,
@@ -184,7 +227,8 @@ __global__ void qkv_rope_write_kernel(const T* __restrict__ qkv, const float* __
     const int half = rot / 2;
     const int chunks = hd / 4;
     const int n_heads_all = nh + 2 * nkv;
-    const T* in = qkv + (size_t)t * n_heads_all * hd;
+    const T* in = qkv ? qkv + (size_t)t * n_heads_all * hd : nullptr;
+    const float* pin = partials ? partials + (size_t)t * n_heads_all * hd : nullptr;
     const float* ct = cos_t + (size_t)t * half;
     const float* st = sin_t + (size_t)t * half;
     const int slot = (cache && slot_mapping) ? slot_mapping[t] : -1;
@@ -206,26 +250,28 @@ __global__ void qkv_rope_write_kernel(const T* __restrict__ qkv, const float* __
             const size_t row = ((size_t)(page * 2 + (is_v ? 1 : 0)) * nkv + kvh) * page_size + off;
             dst = cache + row * hd;
         }
-        const T* src = in + (size_t)h * hd;
+        const int hoff = h * hd;
         const float* b = bias ? bias + (size_t)h * hd : nullptr;
         if (is_v || d0 >= rot) {
-            Vec<T, 4> a = load_vec<T, 4>(src + d0);
+            float a[4];
+            load_qkv4<T>(a, in, pin, n_partials, partial_stride, hoff + d0);
             Vec<T, 4> o;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                float v = to_f32<T>(a.v[k]);
+                float v = a[k];
                 if (b) v = v + b[d0 + k];
                 o.v[k] = from_f32<T>(v);
             }
             store_vec<T, 4>(dst + d0, o);
         } else if (d0 < half) {
-            Vec<T, 4> a1 = load_vec<T, 4>(src + d0);
-            Vec<T, 4> a2 = load_vec<T, 4>(src + d0 + half);
+            float a1[4], a2[4];
+            load_qkv4<T>(a1, in, pin, n_partials, partial_stride, hoff + d0);
+            load_qkv4<T>(a2, in, pin, n_partials, partial_stride, hoff + d0 + half);
             Vec<T, 4> o1, o2;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                float x1 = to_f32<T>(a1.v[k]);
-                float x2 = to_f32<T>(a2.v[k]);
+                float x1 = a1[k];
+                float x2 = a2[k];
                 if (b) { x1 = x1 + b[d0 + k]; x2 = x2 + b[d0 + half + k]; }
                 const float c = ct[d0 + k], s = st[d0 + k];
                 o1.v[k] = from_f32<T>(__fadd_rn(__fmul_rn(x1, c), __fmul_rn(-x2, s)));
@@ -237,17 +283,21 @@ __global__ void qkv_rope_write_kernel(const T* __restrict__ qkv, const float* __
     }
 }
 
-PYRE_API int pyre_qkv_rope_write(const void* qkv, const float* bias, const float* cos_t, const float* sin_t,
+// qkv: activation dtype [T, width] or null; partials: fp32 [n_partials][T][width] or null (one of the two).
+PYRE_API int pyre_qkv_rope_write(const void* qkv, const float* partials, int n_partials, long long partial_stride,
+                                 const float* bias, const float* cos_t, const float* sin_t,
                                  void* q_out, void* cache, const int* slot_mapping, int n_tokens, int nh, int nkv,
                                  int hd, int rot, int page_size, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd % 8 || rot % 8 || rot > hd || rot < 0 || page_size <= 0) return PYRE_ERR_BAD_ARG;
+    if ((qkv == nullptr) == (partials == nullptr)) return PYRE_ERR_BAD_ARG;
+    if (partials && n_partials < 1) return PYRE_ERR_BAD_ARG;
     const int items = (nh + 2 * nkv) * (hd / 4);
     const int threads = min(256, max(32, ((items + 31) / 32) * 32));
     if (dtype == PYRE_F32)
-        qkv_rope_write_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)qkv, bias, cos_t, sin_t, (float*)q_out, (float*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
+        qkv_rope_write_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (float*)q_out, (float*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
     else if (dtype == PYRE_BF16)
-        qkv_rope_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)qkv, bias, cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
+        qkv_rope_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;

@@ -73,14 +73,86 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long ld, co
     }
 }
 
+// Large vocabularies: stage 1 scans a slice of the row per block and leaves its best
+// (score, index) in scratch; stage 2 picks the best slice.  The winner is the same as
+// in the one-block kernel: largest score, lowest index on a tie.
+__global__ void sample_slices_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ temperature,
+                                     const unsigned long long* __restrict__ seeds, const int* __restrict__ token_index,
+                                     float* __restrict__ slice_score, int* __restrict__ slice_index, int V, int slice) {
+    __shared__ Best warp_best[32];
+    const int r = blockIdx.y, sl = blockIdx.x;
+    const float* row = logits + (size_t)r * ld;
+    const float temp = temperature ? temperature[r] : 0.f;
+    const bool greedy = !(temp > 0.f);
+    const float inv_t = greedy ? 1.f : 1.0f / temp;
+    const unsigned long long seed = seeds ? seeds[r] : 0ull;
+    const unsigned int tix = token_index ? (unsigned int)token_index[r] : 0u;
+    const int begin = sl * slice, end = min(begin + slice, V);
+    Best best{-INFINITY, 0x7fffffff};
+    for (int v = begin + threadIdx.x; v < end; v += blockDim.x) {
+        float s = row[v];
+        if (!greedy) s = __fadd_rn(__fmul_rn(s, inv_t), gumbel(seed, tix, (unsigned int)v));
+        if (s > best.score || best.index == 0x7fffffff) best = Best{s, v};
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other{__shfl_xor_sync(0xffffffffu, best.score, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
+        best = better(best, other);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) warp_best[warp] = best;
+    __syncthreads();
+    if (warp == 0) {
+        const int n_warps = (blockDim.x + 31) >> 5;
+        best = lane < n_warps ? warp_best[lane] : Best{-INFINITY, 0x7fffffff};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            Best other{__shfl_xor_sync(0xffffffffu, best.score, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
+            best = better(best, other);
+        }
+        if (lane == 0) {
+            slice_score[(size_t)r * gridDim.x + sl] = best.score;
+            slice_index[(size_t)r * gridDim.x + sl] = best.index;
+        }
+    }
+}
+
+__global__ void sample_pick_kernel(const float* __restrict__ slice_score, const int* __restrict__ slice_index,
+                                   int* __restrict__ out, int n_slices) {
+    const int r = blockIdx.x;
+    Best best{-INFINITY, 0x7fffffff};
+    for (int i = threadIdx.x; i < n_slices; i += 32)
+        best = better(best, Best{slice_score[(size_t)r * n_slices + i], slice_index[(size_t)r * n_slices + i]});
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best other{__shfl_xor_sync(0xffffffffu, best.score, o), __shfl_xor_sync(0xffffffffu, best.index, o)};
+        best = better(best, other);
+    }
+    if (threadIdx.x == 0) out[r] = best.index == 0x7fffffff ? 0 : best.index;
+}
+
+// Slices the two-stage path cuts a row of V entries into (0: use the one-block kernel).
+PYRE_API int pyre_sample_slices(int V) { return V >= 16384 ? (V + 4095) / 4096 : 0; }
+
 // logits [R, V] fp32 with row stride ld; temperature [R] fp32 (null = all greedy);
 // seeds [R] uint64 and token_index [R] int32 (may be null when all rows are greedy);
-// out [R] int32.
+// out [R] int32.  scratch: R * pyre_sample_slices(V) * 2 words, needed when that is not 0.
 PYRE_API int pyre_sample(const float* logits, long long ld, const float* temperature,
                          const unsigned long long* seeds, const int* token_index, int* out, int n_rows, int V,
-                         cudaStream_t stream) {
+                         void* scratch, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (V <= 0) return PYRE_ERR_BAD_ARG;
+    const int n_slices = pyre_sample_slices(V);
+    if (n_slices > 0) {
+        if (!scratch) return PYRE_ERR_BAD_ARG;
+        float* sc = (float*)scratch;
+        int* ix = (int*)scratch + (size_t)n_rows * n_slices;
+        sample_slices_kernel<<<dim3(n_slices, n_rows), 256, 0, stream>>>(logits, ld, temperature, seeds, token_index, sc, ix, V, 4096);
+        PYRE_LAUNCH_CHECK();
+        sample_pick_kernel<<<n_rows, 32, 0, stream>>>(sc, ix, out, n_slices);
+        PYRE_LAUNCH_CHECK();
+        return 0;
+    }
     const int threads = V >= 8192 ? 1024 : (V >= 1024 ? 256 : 64);
     sample_kernel<<<n_rows, threads, 0, stream>>>(logits, ld, temperature, seeds, token_index, out, V);
     PYRE_LAUNCH_CHECK();

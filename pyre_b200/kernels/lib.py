@@ -17,14 +17,15 @@ P, I, LL, F = c_void_p, c_int, c_longlong, c_float
 # function name -> (library, argument types).  Every function returns int: 0 or an error code.
 SIGNATURES: dict[str, tuple[str, list]] = {
     "pyre_embedding": ("elementwise", [P, I, P, P, I, I, I, P, P]),
-    "pyre_add_rmsnorm": ("elementwise", [P, P, P, P, P, I, I, F, I, I, P]),
+    "pyre_add_rmsnorm": ("elementwise", [P, P, P, I, LL, P, P, P, I, I, F, I, I, P]),
     "pyre_add_residual": ("elementwise", [P, P, LL, I, P]),
     "pyre_rope_table": ("elementwise", [P, P, P, P, I, I, P]),
-    "pyre_qkv_rope_write": ("elementwise", [P, P, P, P, P, P, P, I, I, I, I, I, I, I, P]),
+    "pyre_qkv_rope_write": ("elementwise", [P, P, I, LL, P, P, P, P, P, P, I, I, I, I, I, I, I, P]),
     "pyre_silu_mul": ("elementwise", [P, P, I, I, I, P]),
     "pyre_sum_partials": ("elementwise", [P, I, LL, P, LL, I, P]),
     "pyre_gemm_tc": ("gemm_tc", [P, I, LL, P, I, LL, I, P, I, LL, LL, LL, I, I, P, P]),
-    "pyre_sample": ("sampling", [P, LL, P, P, P, P, I, I, P]),
+    "pyre_sample": ("sampling", [P, LL, P, P, P, P, I, I, P, P]),
+    "pyre_sample_slices": ("sampling", [I]),
     "pyre_paged_attention_generic": ("attention_generic", [P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, P]),
     "pyre_sgemm_nt": ("gemm_f32", [P, LL, P, LL, P, LL, P, I, I, I, P]),
     "pyre_paged_attention_mma": ("attention_mma", [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, P]),
@@ -72,6 +73,11 @@ def function(name: str):
         fn.restype = c_int
         _funcs[name] = fn
     return fn
+
+
+def call_value(name: str, *args) -> int:
+    """Call a function that returns a plain number (no launch, no error code)."""
+    return int(function(name)(*args))
 
 
 def call(name: str, *args) -> None:

@@ -22,6 +22,35 @@ class UnsupportedSize(ValueError):
     """A configuration whose sizes the kernels refuse."""
 
 
+class PartialSums:
+    """fp32 partial sums [n, T, N] of a matrix product whose inner dimension was split over
+    CTAs.  The kernels that consume a product (``add_rmsnorm``, ``qkv_rope_write``) add the n
+    parts themselves, in index order, so no separate reduction runs; anything else calls
+    ``materialize``."""
+
+    def __init__(self, parts: torch.Tensor, dtype: torch.dtype):
+        self.parts = parts          # contiguous [n, T, N] float32
+        self.dtype = dtype          # what materialize() rounds to
+
+    @property
+    def shape(self):
+        return self.parts.shape[1:]
+
+    @property
+    def n(self) -> int:
+        return self.parts.shape[0]
+
+
+def materialize(t: "torch.Tensor | PartialSums") -> torch.Tensor:
+    """A plain tensor in the activation dtype from either a tensor or partial sums."""
+    if not isinstance(t, PartialSums):
+        return t
+    out = torch.empty(tuple(t.shape), dtype=t.dtype, device=t.parts.device)
+    n = t.parts[0].numel()
+    lib.call("pyre_sum_partials", t.parts.data_ptr(), t.n, n, out.data_ptr(), n, _dt(t.dtype), _stream())
+    return out
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -70,13 +99,19 @@ def add_rmsnorm(x: torch.Tensor, delta: "torch.Tensor | None", weight: torch.Ten
     """out[r] = rmsnorm(x[src] + delta[src]) * weight with src = rows[r] (or r).
 
     ``x`` is the fp32 residual stream [T, H]; with ``update_x`` (and no ``rows``) the sum is
-    written back to it.  ``delta`` has the activation dtype.  ``weight`` is fp32 [H]."""
+    written back to it.  ``delta`` has the activation dtype, or is a ``PartialSums`` whose
+    parts the kernel adds.  ``weight`` is fp32 [H]."""
     _check(x, "x", torch.float32, 2)
     _check(weight, "weight", torch.float32, 1)
     T, H = x.shape
     if weight.shape[0] != H:
         raise ValueError(f"norm weight has {weight.shape[0]} entries, rows have {H}")
-    if delta is not None:
+    parts, n_parts, part_stride = None, 0, 0
+    if isinstance(delta, PartialSums):
+        if tuple(delta.shape) != (T, H):
+            raise ValueError(f"delta shape {tuple(delta.shape)} != x shape {(T, H)}")
+        parts, n_parts, part_stride, delta = delta.parts, delta.n, T * H, None
+    elif delta is not None:
         _check(delta, "delta", out_dtype, 2)
         if tuple(delta.shape) != (T, H):
             raise ValueError(f"delta shape {tuple(delta.shape)} != x shape {(T, H)}")
@@ -89,8 +124,9 @@ def add_rmsnorm(x: torch.Tensor, delta: "torch.Tensor | None", weight: torch.Ten
         out = torch.empty((n_rows, H), dtype=out_dtype, device=x.device)
     else:
         _check(out, "out", out_dtype, 2)
-    lib.call("pyre_add_rmsnorm", x.data_ptr(), _ptr(delta), weight.data_ptr(), out.data_ptr(), _ptr(rows),
-             n_rows, H, float(eps), int(bool(update_x and delta is not None)), _dt(out_dtype), _stream())
+    lib.call("pyre_add_rmsnorm", x.data_ptr(), _ptr(delta), _ptr(parts), n_parts, part_stride, weight.data_ptr(),
+             out.data_ptr(), _ptr(rows), n_rows, H, float(eps),
+             int(bool(update_x and (delta is not None or parts is not None))), _dt(out_dtype), _stream())
     return out
 
 
@@ -123,7 +159,12 @@ def qkv_rope_write(qkv: torch.Tensor, bias: "torch.Tensor | None", cos: torch.Te
 
     ``cache_layer``: [pages, 2, nkv, page_size, hd] of the activation dtype, or None to
     store nothing (a layer that reads another layer's cache)."""
-    _check(qkv, "qkv", dim=2)
+    parts, n_parts = None, 0
+    if isinstance(qkv, PartialSums):
+        parts, n_parts, act_dtype, device = qkv.parts, qkv.n, qkv.dtype, qkv.parts.device
+    else:
+        _check(qkv, "qkv", dim=2)
+        act_dtype, device = qkv.dtype, qkv.device
     T = qkv.shape[0]
     width = (n_heads + 2 * n_kv_heads) * head_dim
     if qkv.shape[1] != width:
@@ -142,7 +183,7 @@ def qkv_rope_write(qkv: torch.Tensor, bias: "torch.Tensor | None", cos: torch.Te
         if tuple(cos.shape) != (T, half) or tuple(sin.shape) != (T, half):
             raise ValueError(f"cos/sin must be [{T}, {half}], got {tuple(cos.shape)}")
     if cache_layer is not None:
-        _check(cache_layer, "cache_layer", qkv.dtype, 5)
+        _check(cache_layer, "cache_layer", act_dtype, 5)
         if tuple(cache_layer.shape[1:]) != (2, n_kv_heads, page_size, head_dim):
             raise ValueError(f"cache layer shape {tuple(cache_layer.shape)} does not match "
                              f"[pages, 2, {n_kv_heads}, {page_size}, {head_dim}]")
@@ -152,11 +193,12 @@ def qkv_rope_write(qkv: torch.Tensor, bias: "torch.Tensor | None", cos: torch.Te
         if slot_mapping.shape[0] != T:
             raise ValueError("slot_mapping must have one entry per token")
     if q_out is None:
-        q_out = torch.empty((T, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
-    lib.call("pyre_qkv_rope_write", qkv.data_ptr(), _ptr(bias), _ptr(cos) if rotary_dim else None,
+        q_out = torch.empty((T, n_heads * head_dim), dtype=act_dtype, device=device)
+    lib.call("pyre_qkv_rope_write", None if parts is not None else qkv.data_ptr(), _ptr(parts), n_parts, T * width,
+             _ptr(bias), _ptr(cos) if rotary_dim else None,
              _ptr(sin) if rotary_dim else None, q_out.data_ptr(), _ptr(cache_layer),
              _ptr(slot_mapping) if cache_layer is not None else None, T, n_heads, n_kv_heads, head_dim,
-             rotary_dim, page_size, _dt(qkv.dtype), _stream())
+             rotary_dim, page_size, _dt(act_dtype), _stream())
     return q_out
 
 
@@ -189,8 +231,10 @@ def sample(logits: torch.Tensor, temperature: "torch.Tensor | None" = None, seed
             raise ValueError("temperature, seeds and token_index need one entry per row")
     if out is None:
         out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    slices = lib.call_value("pyre_sample_slices", V)
+    scratch = torch.empty(R * slices * 2, dtype=torch.int32, device=logits.device) if slices else None
     lib.call("pyre_sample", logits.data_ptr(), logits.stride(0), _ptr(temperature), _ptr(seeds), _ptr(token_index),
-             out.data_ptr(), R, V, _stream())
+             out.data_ptr(), R, V, _ptr(scratch), _stream())
     return out
 
 
@@ -351,8 +395,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     """y = x w^T on the tensor cores (tcgen05, TMEM accumulators, TMA-fed), bf16 in, fp32 accumulate.
 
     With a split K the kernel leaves fp32 partial sums [splits, M, N]; ``reduce`` adds
-    them up here (fixed order) and converts to ``out_dtype``.  ``reduce=False`` returns the
-    partials for a consumer kernel that adds them itself."""
+    them up here (fixed order) and converts to ``out_dtype``.  ``reduce=False`` returns them
+    as ``PartialSums`` for a consumer kernel that adds them itself."""
     if not tc_gemm_supported(x, w):
         raise UnsupportedSize("gemm_tc needs bf16 operands with K and leading dimensions that are multiples of 8")
     M, K = x.shape
@@ -378,29 +422,28 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     if target.dim() == 2:
         return target
     if not reduce:
-        return target
-    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    lib.call("pyre_sum_partials", target.data_ptr(), splits, split_stride, out.data_ptr(), M * N, _dt(out_dtype), _stream())
-    return out
+        return PartialSums(target, out_dtype)
+    return materialize(PartialSums(target, out_dtype))
 
 
 USE_TC_GEMM = True
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: "torch.dtype | None" = None) -> torch.Tensor:
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: "torch.dtype | None" = None, partials_ok: bool = False):
     """y = x W^T for a weight in the linear-layer layout [out, in].
 
     float32: the package's own fp32 kernel (no reduced-precision matrix mode).
     bfloat16: the package's tcgen05 kernel (``gemm_tc``); rows that are no 16-byte multiple
     (K not a multiple of 8) go to a library product instead, as the reference uses a library
     for every projection.  ``out_dtype=torch.float32`` keeps the accumulator's precision
-    (used for the logits)."""
+    (used for the logits).  ``partials_ok``: the caller's consumer adds split-K partial
+    sums itself, so a ``PartialSums`` may come back instead of a tensor."""
     if x.dtype == torch.float32:
         return sgemm_nt(x, w)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise ValueError(f"linear: unsupported dtypes {x.dtype} x {w.dtype}")
     if USE_TC_GEMM and tc_gemm_supported(x, w):
-        return gemm_tc(x, w, out_dtype or torch.bfloat16)
+        return gemm_tc(x, w, out_dtype or torch.bfloat16, reduce=not partials_ok)
     if out_dtype is None or out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)

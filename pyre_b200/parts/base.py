@@ -22,7 +22,11 @@ Interfaces by category (``ctx`` is the StepContext, T its number of tokens):
               say what it needs from the cache manager
     ffn       forward(ctx, h) -> [T, width]
     block     forward(ctx, x, pending, call) -> (x, pending)   ``pending`` is a branch
-              output not yet added to x; the next norm adds it (fused)
+              output not yet added to x; the next norm adds it (fused).  A branch output
+              (what a mixer or a feed-forward returns, hence ``delta`` and ``pending``) is a
+              tensor [T, width] in the activation dtype or ``kernels.ops.PartialSums``,
+              fp32 partial sums that the built-in norm adds up; a part that needs a plain
+              tensor calls ``kernels.ops.materialize`` on it
     head      forward(ctx, h_rows) -> fp32 logits [R, vocab]
 
 A new part is a class with these methods and one ``register_part`` call; nothing else

@@ -39,7 +39,7 @@ class GatedMLP(Part):
     def forward(self, ctx, h):
         gate_up = ops.linear(h, self.w_gate_up)
         act = ops.silu_mul(gate_up)
-        return ops.linear(act, self.w_down)
+        return ops.linear(act, self.w_down, partials_ok=True)
 
 
 register_part("ffn", "gated_mlp", GatedMLP)

@@ -276,6 +276,59 @@ def test_paged_attention_mma(ops, nh, nkv, hd, page, window, n_splits):
     assert (got[0, :hd].float() - v_far).abs().max() < 0.2 * v_far.abs().max() + 0.1
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_consumers_add_partial_sums(ops, dtype):
+    """A product whose K was split arrives as fp32 partial sums; the norm and the rotary
+    kernel add them themselves and give what they give on the summed tensor."""
+    g = torch.Generator(device="cuda").manual_seed(21)
+    T, H, n = 6, 136, 3
+    parts = torch.randn(n, T, H, device="cuda", generator=g)
+    x = torch.randn(T, H, device="cuda", generator=g)
+    w = 1 + 0.1 * torch.randn(H, device="cuda", generator=g)
+    total = parts[0] + parts[1] + parts[2]
+    x1, x2 = x.clone(), x.clone()
+    a = ops.add_rmsnorm(x1, ops.PartialSums(parts, dtype), w, 1e-6, dtype)
+    v = x + total
+    want = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6)) * w
+    torch.testing.assert_close(x1, v, rtol=0, atol=0)
+    torch.testing.assert_close(a.float(), want, **tol(dtype))
+    rows = torch.tensor([4, 1], dtype=torch.int32, device="cuda")
+    b = ops.add_rmsnorm(x2, ops.PartialSums(parts, dtype), w, 1e-6, dtype, rows=rows)
+    assert torch.equal(x2, x)
+    torch.testing.assert_close(b.float(), want[rows.long()], **tol(dtype))
+    torch.testing.assert_close(ops.materialize(ops.PartialSums(parts, dtype)).float(), total, **tol(dtype))
+    # rotary: partial sums in, same result as the summed tensor in the activation dtype (fp32: exactly)
+    nh, nkv, hd, page = 3, 1, 32, 8
+    width = (nh + 2 * nkv) * hd
+    parts = torch.randn(n, T, width, device="cuda", generator=g)
+    bias = torch.randn(width, device="cuda", generator=g)
+    pos = torch.arange(10, 10 + T, dtype=torch.int32, device="cuda")
+    inv = (1.0 / (1e4 ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))).cuda()
+    cos, sin = ops.rope_table(pos, inv)
+    slots = torch.arange(T, dtype=torch.int32, device="cuda")
+    c1 = torch.zeros(2, 2, nkv, page, hd, device="cuda", dtype=dtype)
+    c2 = torch.zeros(2, 2, nkv, page, hd, device="cuda")
+    q1 = ops.qkv_rope_write(ops.PartialSums(parts, dtype), bias, cos, sin, c1, slots, nh, nkv, hd, hd, page)
+    q2 = ops.qkv_rope_write(parts[0] + parts[1] + parts[2], bias, cos, sin, c2, slots, nh, nkv, hd, hd, page)
+    torch.testing.assert_close(c1.float(), c2, **tol(dtype))
+    torch.testing.assert_close(q1.float(), q2, **tol(dtype))
+
+
+def test_sampling_large_vocabulary_two_stages(ops):
+    from plain import qwen2_plain
+    g = torch.Generator(device="cuda").manual_seed(8)
+    V = 40001                                  # above the one-block limit, not a multiple of the slice
+    logits = torch.randn(3, V, device="cuda", generator=g)
+    logits[1, 4095] = logits[1, 4096] = logits[1, 39999] = 30.0     # ties across slices: the lowest index wins
+    assert ops.sample(logits).tolist() == [int(logits[0].argmax()), 4095, int(logits[2].argmax())]
+    temps = torch.tensor([0.9, 0.0, 1.3], device="cuda")
+    seeds = torch.tensor([5, 6, 7], dtype=torch.int64, device="cuda")
+    tix = torch.tensor([2, 0, 11], dtype=torch.int32, device="cuda")
+    got = ops.sample(logits, temps, seeds, tix).tolist()
+    want = [qwen2_plain.sample(logits[r].cpu(), float(temps[r]), int(seeds[r]), int(tix[r])) for r in range(3)]
+    assert got == want
+
+
 def test_sampling(ops):
     from plain import qwen2_plain
     g = torch.Generator(device="cuda").manual_seed(7)
