@@ -31,6 +31,8 @@ __global__ void paged_attention_generic_kernel(
     const int* __restrict__ positions,     // [n_tokens]
     int n_tokens, int nh, int nkv, int hd, int page_size, int window, float scale) {
     extern __shared__ float q_smem[];  // [warps][hd]
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int warps = blockDim.x >> 5;
     const long long item = (long long)blockIdx.x * warps + warp;
@@ -112,11 +114,11 @@ PYRE_API int pyre_paged_attention_generic(const void* q, const void* cache, void
     const int blocks = (int)ceil_div_ll(items, warps);
     const size_t smem = (size_t)warps * hd * sizeof(float);
     if (dtype == PYRE_F32)
-        paged_attention_generic_kernel<float><<<blocks, warps * 32, smem, stream>>>(
+        pyre_launch(paged_attention_generic_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream, 
             (const float*)q, (const float*)cache, (float*)out, block_table, bt_stride, seq_of_token, positions,
             n_tokens, nh, nkv, hd, page_size, window, scale);
     else if (dtype == PYRE_BF16)
-        paged_attention_generic_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
+        pyre_launch(paged_attention_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, stream, 
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, block_table, bt_stride,
             seq_of_token, positions, n_tokens, nh, nkv, hd, page_size, window, scale);
     else return PYRE_ERR_BAD_ARG;

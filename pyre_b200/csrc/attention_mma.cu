@@ -100,6 +100,8 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
+    pdl_trigger();
+    pdl_wait();   // queries, the pages of this step and the step's index arrays come from earlier kernels
 
     // ---- which group is this CTA's?  groups are counted entry by entry
     int grp = blockIdx.x, seq = -1, tok0 = 0, n_tok = 0;
@@ -294,6 +296,8 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
 // out[t, h, :] = sum_s acc_s exp(m_s - M) / sum_s l_s exp(m_s - M)
 __global__ void combine_splits_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                       __nv_bfloat16* __restrict__ out, int n_splits, int hd) {
+    pdl_trigger();
+    pdl_wait();
     const size_t th = blockIdx.x;
     const float* ml = part_ml + th * n_splits * 2;
     float M = -INFINITY;
@@ -311,7 +315,7 @@ __global__ void combine_splits_kernel(const float* __restrict__ part_acc, const 
 template <int HD>
 int launch(const AttnParams& p, int n_groups_bound, cudaStream_t stream) {
     dim3 grid(n_groups_bound, p.nkv * p.head_blocks, p.n_splits);
-    paged_attention_mma_kernel<HD><<<grid, WARPS * 32, 0, stream>>>(p);
+    pyre_launch(paged_attention_mma_kernel<HD>, dim3(grid), dim3(WARPS * 32), 0, stream, p);
     return (int)cudaGetLastError();
 }
 
@@ -360,7 +364,7 @@ PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* ou
     }
     if (rc) return rc;
     if (n_splits > 1) {
-        combine_splits_kernel<<<n_tokens * nh, hd >= 64 ? 64 : 32, 0, stream>>>(p.part_acc, p.part_ml, p.out, n_splits, hd);
+        pyre_launch(combine_splits_kernel, dim3(n_tokens * nh), dim3(hd >= 64 ? 64 : 32), 0, stream, p.part_acc, p.part_ml, p.out, n_splits, hd);
         PYRE_LAUNCH_CHECK();
     }
     return 0;

@@ -88,5 +88,45 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return scratch[32];
 }
 
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel of the decoder step is launched with the
+// "programmatic stream serialization" attribute: it may be scheduled while the kernel
+// before it in the stream is still running, as soon as that kernel's CTAs have called
+// pdl_trigger().  Whatever a kernel does before pdl_wait() must not touch memory that an
+// earlier kernel of the step writes or still reads (only its own set-up and constant
+// weights); pdl_wait() returns when the kernel before it has completed and its writes
+// are visible, which, by induction along the stream, holds for all earlier kernels too.
+// Without the attribute both calls do nothing.  PYRE_PDL=0 in the environment turns the
+// attribute off.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <cstdlib>
+static inline bool pyre_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("PYRE_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on != 0;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t pyre_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                      Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pyre_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 static inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }

@@ -16,6 +16,8 @@
 template <typename T, int VEC>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
                                  int H, int V, int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* dst = x + (size_t)t * H;
@@ -40,11 +42,11 @@ PYRE_API int pyre_embedding(const void* table, int dtype, const int* ids, float*
     const bool vec = (H % 4 == 0);
     const int threads = vec ? min(256, max(32, ((H / 4 + 31) / 32) * 32)) : 256;
     if (dtype == PYRE_F32) {
-        if (vec) embedding_kernel<float, 4><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, x, H, V, err_flag);
-        else embedding_kernel<float, 1><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, x, H, V, err_flag);
+        if (vec) pyre_launch(embedding_kernel<float, 4>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, ids, x, H, V, err_flag);
+        else pyre_launch(embedding_kernel<float, 1>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, ids, x, H, V, err_flag);
     } else if (dtype == PYRE_BF16) {
-        if (vec) embedding_kernel<__nv_bfloat16, 4><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, x, H, V, err_flag);
-        else embedding_kernel<__nv_bfloat16, 1><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, x, H, V, err_flag);
+        if (vec) pyre_launch(embedding_kernel<__nv_bfloat16, 4>, dim3(n_tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, x, H, V, err_flag);
+        else pyre_launch(embedding_kernel<__nv_bfloat16, 1>, dim3(n_tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)table, ids, x, H, V, err_flag);
     } else {
         return PYRE_ERR_BAD_ARG;
     }
@@ -86,6 +88,8 @@ template <typename T, int VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ partials,
                                    int n_partials, long long partial_stride, const float* __restrict__ w,
                                    T* __restrict__ out, const int* __restrict__ rows, int H, float eps, int update_x) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -131,7 +135,7 @@ PYRE_API int pyre_add_rmsnorm(float* x, const void* delta, const float* partials
     const bool vec = (H % 4 == 0);
     const int per = vec ? H / 4 : H;
     const int threads = min(512, max(32, ((per + 31) / 32) * 32));
-#define LAUNCH(TT, V) add_rmsnorm_kernel<TT, V><<<n_rows, threads, 0, stream>>>(x, (const TT*)delta, partials, n_partials, partial_stride, weight, (TT*)out, rows, H, eps, update_x)
+#define LAUNCH(TT, V) pyre_launch(add_rmsnorm_kernel<TT, V>, dim3(n_rows), dim3(threads), 0, stream, x, (const TT*)delta, partials, n_partials, partial_stride, weight, (TT*)out, rows, H, eps, update_x)
     if (dtype == PYRE_F32) { if (vec) LAUNCH(float, 4); else LAUNCH(float, 1); }
     else if (dtype == PYRE_BF16) { if (vec) LAUNCH(__nv_bfloat16, 4); else LAUNCH(__nv_bfloat16, 1); }
     else return PYRE_ERR_BAD_ARG;
@@ -143,6 +147,8 @@ PYRE_API int pyre_add_rmsnorm(float* x, const void* delta, const float* partials
 // x[t, :] += delta[t, :] (fp32 sum), for a residual that no norm follows.
 template <typename T>
 __global__ void add_residual_kernel(float* __restrict__ x, const T* __restrict__ delta, size_t n) {
+    pdl_trigger();
+    pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         x[i] = x[i] + to_f32<T>(delta[i]);
 }
@@ -151,8 +157,8 @@ PYRE_API int pyre_add_residual(float* x, const void* delta, long long n, int dty
     if (n <= 0) return 0;
     const int threads = 256;
     const int blocks = (int)min((long long)148 * 8, ceil_div_ll(n, threads));
-    if (dtype == PYRE_F32) add_residual_kernel<float><<<blocks, threads, 0, stream>>>(x, (const float*)delta, (size_t)n);
-    else if (dtype == PYRE_BF16) add_residual_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(x, (const __nv_bfloat16*)delta, (size_t)n);
+    if (dtype == PYRE_F32) pyre_launch(add_residual_kernel<float>, dim3(blocks), dim3(threads), 0, stream, x, (const float*)delta, (size_t)n);
+    else if (dtype == PYRE_BF16) pyre_launch(add_residual_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, x, (const __nv_bfloat16*)delta, (size_t)n);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;
@@ -165,6 +171,8 @@ PYRE_API int pyre_add_residual(float* x, const void* delta, long long n, int dty
 // ---------------------------------------------------------------------------
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                   float* __restrict__ cos_out, float* __restrict__ sin_out, int n_tokens, int half) {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_tokens * half) return;
     const int t = i / half, j = i - t * half;
@@ -179,7 +187,7 @@ PYRE_API int pyre_rope_table(const int* positions, const float* inv_freq, float*
                              int n_tokens, int half, cudaStream_t stream) {
     const long long n = (long long)n_tokens * half;
     if (n <= 0) return 0;
-    rope_table_kernel<<<(int)ceil_div_ll(n, 256), 256, 0, stream>>>(positions, inv_freq, cos_out, sin_out, n_tokens, half);
+    pyre_launch(rope_table_kernel, dim3((int)ceil_div_ll(n, 256)), dim3(256), 0, stream, positions, inv_freq, cos_out, sin_out, n_tokens, half);
     PYRE_LAUNCH_CHECK();
     return 0;
 }
@@ -223,6 +231,8 @@ __global__ void qkv_rope_write_kernel(const T* __restrict__ qkv, const float* __
                                       T* __restrict__ q_out, T* __restrict__ cache,
                                       const int* __restrict__ slot_mapping, int nh, int nkv, int hd, int rot,
                                       int page_size) {
+    pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int half = rot / 2;
     const int chunks = hd / 4;
@@ -295,9 +305,9 @@ PYRE_API int pyre_qkv_rope_write(const void* qkv, const float* partials, int n_p
     const int items = (nh + 2 * nkv) * (hd / 4);
     const int threads = min(256, max(32, ((items + 31) / 32) * 32));
     if (dtype == PYRE_F32)
-        qkv_rope_write_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (float*)q_out, (float*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
+        pyre_launch(qkv_rope_write_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (float*)q_out, (float*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
     else if (dtype == PYRE_BF16)
-        qkv_rope_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>((const __nv_bfloat16*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
+        pyre_launch(qkv_rope_write_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;
@@ -308,6 +318,8 @@ PYRE_API int pyre_qkv_rope_write(const void* qkv, const float* partials, int n_p
 // ---------------------------------------------------------------------------
 template <typename T, int VEC>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tokens, int I) {
+    pdl_trigger();
+    pdl_wait();
     const size_t per_row = (size_t)(I / VEC);
     const size_t total = per_row * n_tokens;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -334,7 +346,7 @@ PYRE_API int pyre_silu_mul(const void* gu, void* out, int n_tokens, int I, int d
     do {                                                                                                   \
         long long total = (long long)n_tokens * (I / V);                                                   \
         int blocks = (int)min((long long)148 * 16, ceil_div_ll(total, threads));                           \
-        silu_mul_kernel<TT, V><<<blocks, threads, 0, stream>>>((const TT*)gu, (TT*)out, n_tokens, I);      \
+        pyre_launch(silu_mul_kernel<TT, V>, dim3(blocks), dim3(threads), 0, stream, (const TT*)gu, (TT*)out, n_tokens, I);      \
     } while (0)
     if (dtype == PYRE_F32) { if (I % 4 == 0) LAUNCH(float, 4); else LAUNCH(float, 1); }
     else if (dtype == PYRE_BF16) { if (I % 8 == 0) LAUNCH(__nv_bfloat16, 8); else if (I % 4 == 0) LAUNCH(__nv_bfloat16, 4); else LAUNCH(__nv_bfloat16, 1); }
@@ -351,6 +363,8 @@ PYRE_API int pyre_silu_mul(const void* gu, void* out, int n_tokens, int I, int d
 template <typename T>
 __global__ void sum_partials_kernel(const float* __restrict__ partials, int n_splits, long long split_stride,
                                     T* __restrict__ out, long long n) {
+    pdl_trigger();
+    pdl_wait();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         float acc = partials[i];
         for (int s = 1; s < n_splits; ++s) acc += partials[(long long)s * split_stride + i];
@@ -364,8 +378,8 @@ PYRE_API int pyre_sum_partials(const float* partials, int n_splits, long long sp
     if (n_splits < 1) return PYRE_ERR_BAD_ARG;
     const int threads = 256;
     const int blocks = (int)min((long long)148 * 8, ceil_div_ll(n, threads));
-    if (dtype == PYRE_F32) sum_partials_kernel<float><<<blocks, threads, 0, stream>>>(partials, n_splits, split_stride, (float*)out, n);
-    else if (dtype == PYRE_BF16) sum_partials_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(partials, n_splits, split_stride, (__nv_bfloat16*)out, n);
+    if (dtype == PYRE_F32) pyre_launch(sum_partials_kernel<float>, dim3(blocks), dim3(threads), 0, stream, partials, n_splits, split_stride, (float*)out, n);
+    else if (dtype == PYRE_BF16) pyre_launch(sum_partials_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, partials, n_splits, split_stride, (__nv_bfloat16*)out, n);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;

@@ -17,6 +17,8 @@ sgemm_nt_kernel(const float* __restrict__ A, long long lda, const float* __restr
     constexpr int THREADS = (BM / TM) * (BN / TN);
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    pdl_trigger();
+    pdl_wait();
     const int tid = threadIdx.x;
     const int tx = tid % (BN / TN);  // column group
     const int ty = tid / (BN / TN);  // row group
@@ -73,10 +75,10 @@ PYRE_API int pyre_sgemm_nt(const float* A, long long lda, const float* W, long l
     if (K < 0) return PYRE_ERR_BAD_ARG;
     if (M > 32) {
         dim3 grid(ceil_div(N, 128), ceil_div(M, 128));
-        sgemm_nt_kernel<128, 128, 8, 8, 8><<<grid, 256, 0, stream>>>(A, lda, W, ldw, C, ldc, bias, M, N, K);
+        pyre_launch(sgemm_nt_kernel<128, 128, 8, 8, 8>, dim3(grid), dim3(256), 0, stream, A, lda, W, ldw, C, ldc, bias, M, N, K);
     } else {
         dim3 grid(ceil_div(N, 128), ceil_div(M, 32));
-        sgemm_nt_kernel<32, 128, 16, 2, 8><<<grid, 256, 0, stream>>>(A, lda, W, ldw, C, ldc, bias, M, N, K);
+        pyre_launch(sgemm_nt_kernel<32, 128, 16, 2, 8>, dim3(grid), dim3(256), 0, stream, A, lda, W, ldw, C, ldc, bias, M, N, K);
     }
     PYRE_LAUNCH_CHECK();
     return 0;

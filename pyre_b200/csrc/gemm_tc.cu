@@ -107,6 +107,7 @@ struct GemmParams {
     long long stride_x, stride_y, split_stride;  // output element strides
     void* out;
     int out_f32;
+    int x_is_constant;            // 1: X holds weights (may be loaded before the kernels before this one finish); 0: Y does
     int* err_flag;
 };
 
@@ -140,6 +141,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const int n_kb = max(kb_end - kb_begin, 0);
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;   // power of two >= 32
 
+    pdl_trigger();
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
@@ -163,7 +165,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             // ---------------- producer
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_x)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_y)) : "memory");
-            for (int i = 0; i < n_kb; ++i) {
+            // The weights do not depend on the kernels before this one: fill the ring with
+            // their tiles first, then wait for those kernels, then fetch the activations.
+            const int pre = n_kb < STAGES ? n_kb : STAGES;
+            for (int i = 0; i < pre; ++i) {
+                mbar_expect_tx(bar_full + 8 * i, L::STAGE_BYTES);
+                const uint32_t xs = base + i * L::STAGE_BYTES, ys = xs + L::X_BYTES;
+                const int k = (kb_begin + i) * BK;
+                if (p.x_is_constant) tma_load_2d(xs, &map_x, bar_full + 8 * i, k, x0);
+                else tma_load_2d(ys, &map_y, bar_full + 8 * i, k, y0);
+            }
+            pdl_wait();
+            for (int i = 0; i < pre; ++i) {
+                const uint32_t xs = base + i * L::STAGE_BYTES, ys = xs + L::X_BYTES;
+                const int k = (kb_begin + i) * BK;
+                if (p.x_is_constant) tma_load_2d(ys, &map_y, bar_full + 8 * i, k, y0);
+                else tma_load_2d(xs, &map_x, bar_full + 8 * i, k, x0);
+            }
+            for (int i = pre; i < n_kb; ++i) {
                 const int s = i % STAGES;
                 const uint32_t phase = (i / STAGES) & 1;
                 if (!mbar_wait(bar_empty + 8 * s, phase ^ 1, abort_flag, p.err_flag)) break;
@@ -202,6 +221,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const int xr = x0 + quarter * 32 + lane;
         bool ok = true;
         if (n_kb > 0) ok = mbar_wait(bar_accum, 0, abort_flag, p.err_flag);
+        else pdl_wait();   // nothing orders this store after the earlier kernels otherwise
         ok = ok && !*abort_flag;   // the issuer signals the accumulator even when it gave up
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const long long out_base = (long long)blockIdx.z * p.split_stride + (long long)xr * p.stride_x;
@@ -310,7 +330,8 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, di
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    gemm_tc_kernel<BN, STAGES, XC><<<grid, THREADS, L::TOTAL, stream>>>(mx, my, p);
+    cudaError_t e = pyre_launch(gemm_tc_kernel<BN, STAGES, XC>, grid, dim3(THREADS), (size_t)L::TOTAL, stream, mx, my, p);
+    if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();
 }
 
@@ -320,10 +341,12 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, di
 // out[z * split_stride + x * stride_x + y * stride_y] receives split z's partial sum (fp32 if
 // out_f32 else bf16).  One of stride_x, stride_y must be 1: stride_x == 1 selects the transposed
 // store (X = weights), stride_y == 1 the row store (X = tokens).  bn: tile width along y, one of
-// 16, 32, 64, 128, 256.  splits >= 1 divides the K blocks among blockIdx.z.
+// 16, 32, 64, 128, 256.  splits >= 1 divides the K blocks among blockIdx.z.  x_is_constant says
+// which operand holds weights: its first tiles are fetched before the kernel waits for the
+// kernels before it in the stream (programmatic dependent launch).
 PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* Y, int y_rows, long long ldy, int K,
                           void* out, int out_f32, long long stride_x, long long stride_y, long long split_stride,
-                          int splits, int bn, int* err_flag, cudaStream_t stream) {
+                          int splits, int bn, int x_is_constant, int* err_flag, cudaStream_t stream) {
     if (x_rows <= 0 || y_rows <= 0) return 0;
     if (K <= 0 || K % 8 || ldx % 8 || ldy % 8 || splits < 1) return PYRE_ERR_UNSUPPORTED;
     if (((uintptr_t)X & 15) || ((uintptr_t)Y & 15)) return PYRE_ERR_UNSUPPORTED;
@@ -341,7 +364,7 @@ PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* 
     p.x_rows = x_rows; p.y_rows = y_rows; p.K = K;
     p.k_blocks_per_split = (total_kb + splits - 1) / splits;
     p.stride_x = stride_x; p.stride_y = stride_y; p.split_stride = split_stride;
-    p.out = out; p.out_f32 = out_f32; p.err_flag = err_flag;
+    p.out = out; p.out_f32 = out_f32; p.x_is_constant = x_is_constant; p.err_flag = err_flag;
     dim3 grid(ceil_div(x_rows, BM), ceil_div(y_rows, bn), splits);
 #define GO(BN_, ST_)                                                              \
     rc = xc ? launch<BN_, ST_, true>(mx, my, p, grid, stream) : launch<BN_, ST_, false>(mx, my, p, grid, stream)

@@ -39,6 +39,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long ld, co
                               const unsigned long long* __restrict__ seeds, const int* __restrict__ token_index,
                               int* __restrict__ out, int V) {
     __shared__ Best warp_best[32];
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * ld;
     const float temp = temperature ? temperature[r] : 0.f;
@@ -80,6 +82,8 @@ __global__ void sample_slices_kernel(const float* __restrict__ logits, long long
                                      const unsigned long long* __restrict__ seeds, const int* __restrict__ token_index,
                                      float* __restrict__ slice_score, int* __restrict__ slice_index, int V, int slice) {
     __shared__ Best warp_best[32];
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.y, sl = blockIdx.x;
     const float* row = logits + (size_t)r * ld;
     const float temp = temperature ? temperature[r] : 0.f;
@@ -119,6 +123,8 @@ __global__ void sample_slices_kernel(const float* __restrict__ logits, long long
 
 __global__ void sample_pick_kernel(const float* __restrict__ slice_score, const int* __restrict__ slice_index,
                                    int* __restrict__ out, int n_slices) {
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     Best best{-INFINITY, 0x7fffffff};
     for (int i = threadIdx.x; i < n_slices; i += 32)
@@ -147,14 +153,14 @@ PYRE_API int pyre_sample(const float* logits, long long ld, const float* tempera
         if (!scratch) return PYRE_ERR_BAD_ARG;
         float* sc = (float*)scratch;
         int* ix = (int*)scratch + (size_t)n_rows * n_slices;
-        sample_slices_kernel<<<dim3(n_slices, n_rows), 256, 0, stream>>>(logits, ld, temperature, seeds, token_index, sc, ix, V, 4096);
+        pyre_launch(sample_slices_kernel, dim3(dim3(n_slices, n_rows)), dim3(256), 0, stream, logits, ld, temperature, seeds, token_index, sc, ix, V, 4096);
         PYRE_LAUNCH_CHECK();
-        sample_pick_kernel<<<n_rows, 32, 0, stream>>>(sc, ix, out, n_slices);
+        pyre_launch(sample_pick_kernel, dim3(n_rows), dim3(32), 0, stream, sc, ix, out, n_slices);
         PYRE_LAUNCH_CHECK();
         return 0;
     }
     const int threads = V >= 8192 ? 1024 : (V >= 1024 ? 256 : 64);
-    sample_kernel<<<n_rows, threads, 0, stream>>>(logits, ld, temperature, seeds, token_index, out, V);
+    pyre_launch(sample_kernel, dim3(n_rows), dim3(threads), 0, stream, logits, ld, temperature, seeds, token_index, out, V);
     PYRE_LAUNCH_CHECK();
     return 0;
 }

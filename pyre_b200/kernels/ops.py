@@ -415,10 +415,10 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     f32 = int(target.dtype == torch.float32)
     if weights_as_rows:
         lib.call("pyre_gemm_tc", w.data_ptr(), N, w.stride(0), x.data_ptr(), M, x.stride(0), K, target.data_ptr(), f32,
-                 1, N, split_stride, splits, bn, err.data_ptr(), _stream())
+                 1, N, split_stride, splits, bn, 1, err.data_ptr(), _stream())
     else:
         lib.call("pyre_gemm_tc", x.data_ptr(), M, x.stride(0), w.data_ptr(), N, w.stride(0), K, target.data_ptr(), f32,
-                 N, 1, split_stride, splits, bn, err.data_ptr(), _stream())
+                 N, 1, split_stride, splits, bn, 0, err.data_ptr(), _stream())
     if target.dim() == 2:
         return target
     if not reduce:

@@ -88,7 +88,8 @@ def test_feed_forward_part(dtype):
     w = load_random(ffn, 1)
     h = torch.randn(11, 72, device="cuda").to(dtype)
     want = qwen2_plain.swiglu_mlp(h.float().cpu(), w, "")
-    got = ffn.forward(mini_context(dtype, positions=list(range(11))), h)
+    from pyre_b200.kernels import ops
+    got = ops.materialize(ffn.forward(mini_context(dtype, positions=list(range(11))), h))
     close(got, want, dtype, roundings=4)      # input, gate/up, activation, output
 
 
@@ -114,6 +115,7 @@ def test_attention_part(dtype, nh, nkv, hd, window):
     projections + rotary + attention + output projection on the whole sequence."""
     from pyre_b200.cache import CacheManager
     from pyre_b200.engine.context import KVView
+    from pyre_b200.kernels import ops
     from pyre_b200.parts import BoundCall, PartSpec
     width, S, page = 56, 29, 8
     att = make("mixer", "attention", dtype, width=width, n_heads=nh, n_kv_heads=nkv, head_dim=hd, window=window,
@@ -140,7 +142,7 @@ def test_attention_part(dtype, nh, nkv, hd, window):
         table = torch.from_numpy(cache.block_table_rows(0, ["r"])).cuda()
         slots = torch.from_numpy(cache.slots_for(0, "r", start, n)).cuda()
         ctx.kv_groups.append(KVView(cache.groups[0].pool, table, slots, page, window))
-        outs.append(att.forward(ctx, h[start:start + n].contiguous(), BoundCall(0, 0, 0, 0, True)))
+        outs.append(ops.materialize(att.forward(ctx, h[start:start + n].contiguous(), BoundCall(0, 0, 0, 0, True))))
         cache.commit("r", start + n)
     got = torch.cat(outs).float().cpu()
     close(got, want, dtype, roundings=5)      # qkv, rotated q and k, v, attention output, result
