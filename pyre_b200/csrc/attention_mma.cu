@@ -85,6 +85,7 @@ struct AttnParams {
     const int* cu_seqlens;       // [B + 1]
     const int* positions;        // [T]
     int bt_stride, n_seqs, nh, nkv, page_size, window, n_splits, tpg, hpg, head_blocks;
+    int max_len;                 // > 0: only entries with at most this many tokens (longer ones go to the prefill kernel)
     float scale;
 };
 
@@ -107,6 +108,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
     int grp = blockIdx.x, seq = -1, tok0 = 0, n_tok = 0;
     for (int b = 0; b < p.n_seqs; ++b) {
         const int begin = p.cu_seqlens[b], len = p.cu_seqlens[b + 1] - begin;
+        if (p.max_len > 0 && len > p.max_len) continue;
         const int ng = (len + p.tpg - 1) / p.tpg;
         if (grp < ng) {
             seq = b;
@@ -295,10 +297,20 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
 
 // out[t, h, :] = sum_s acc_s exp(m_s - M) / sum_s l_s exp(m_s - M)
 __global__ void combine_splits_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                      __nv_bfloat16* __restrict__ out, int n_splits, int hd) {
+                                      __nv_bfloat16* __restrict__ out, int n_splits, int hd, int nh,
+                                      const int* __restrict__ cu_seqlens, int n_seqs, int max_len) {
     pdl_trigger();
     pdl_wait();
     const size_t th = blockIdx.x;
+    if (max_len > 0) {
+        // rows of entries longer than max_len belong to the prefill kernel: no partials, nothing to do
+        const int tok = (int)(th / nh);
+        for (int b = 0; b < n_seqs; ++b)
+            if (tok < cu_seqlens[b + 1]) {
+                if (cu_seqlens[b + 1] - cu_seqlens[b] > max_len) return;
+                break;
+            }
+    }
     const float* ml = part_ml + th * n_splits * 2;
     float M = -INFINITY;
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
@@ -330,7 +342,8 @@ PYRE_API long long pyre_attention_mma_scratch_floats(int n_tokens, int nh, int h
 PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* out, float* scratch,
                                       const int* block_table, int bt_stride, const int* cu_seqlens,
                                       const int* positions, int n_tokens, int n_seqs, int nh, int nkv, int hd,
-                                      int page_size, int window, float scale, int n_splits, cudaStream_t stream) {
+                                      int page_size, int window, float scale, int n_splits, int max_len,
+                                      cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd % 16 || hd < 16 || hd > 128 || nkv <= 0 || nh % nkv || page_size <= 0 || n_splits < 1) return PYRE_ERR_UNSUPPORTED;
     if (n_splits > 1 && !scratch) return PYRE_ERR_BAD_ARG;
@@ -344,7 +357,7 @@ PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* ou
     p.cu_seqlens = cu_seqlens;
     p.positions = positions;
     p.bt_stride = bt_stride; p.n_seqs = n_seqs; p.nh = nh; p.nkv = nkv; p.page_size = page_size;
-    p.window = window; p.n_splits = n_splits; p.scale = scale;
+    p.window = window; p.n_splits = n_splits; p.scale = scale; p.max_len = max_len;
     const int n_rep = nh / nkv;
     p.hpg = n_rep < 16 ? n_rep : 16;
     p.tpg = 16 / p.hpg;
@@ -364,7 +377,7 @@ PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* ou
     }
     if (rc) return rc;
     if (n_splits > 1) {
-        pyre_launch(combine_splits_kernel, dim3(n_tokens * nh), dim3(hd >= 64 ? 64 : 32), 0, stream, p.part_acc, p.part_ml, p.out, n_splits, hd);
+        pyre_launch(combine_splits_kernel, dim3(n_tokens * nh), dim3(hd >= 64 ? 64 : 32), 0, stream, p.part_acc, p.part_ml, p.out, n_splits, hd, nh, cu_seqlens, n_seqs, max_len);
         PYRE_LAUNCH_CHECK();
     }
     return 0;

@@ -32,6 +32,7 @@ LIBRARIES = {
     "gemm_f32": "gemm_f32.cu",
     "attention_mma": "attention_mma.cu",
     "gemm_tc": "gemm_tc.cu",
+    "attention_prefill": "attention_prefill.cu",
     "attention_mma_noalloc": "attention_mma_noalloc.cu",
 }
 

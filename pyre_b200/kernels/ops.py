@@ -287,7 +287,7 @@ def paged_attention_mma(q: torch.Tensor, cache_layer: torch.Tensor, block_table:
                         cu_seqlens: torch.Tensor, positions: torch.Tensor, n_seqs: int, n_heads: int,
                         n_kv_heads: int, head_dim: int, scale: float, window: "int | None" = None,
                         n_splits: int = 1, out: "torch.Tensor | None" = None,
-                        scratch: "torch.Tensor | None" = None) -> torch.Tensor:
+                        scratch: "torch.Tensor | None" = None, max_len: int = 0) -> torch.Tensor:
     """bfloat16 attention on the tensor cores over the block table (decode tokens and
     prompt portions alike); ``n_splits`` > 1 splits each sequence's keys over CTAs and needs
     ``T * nh * n_splits * (hd + 2)`` floats of scratch (allocated here if not given)."""
@@ -319,7 +319,60 @@ def paged_attention_mma(q: torch.Tensor, cache_layer: torch.Tensor, block_table:
             raise ValueError(f"scratch must be {need} contiguous floats")
     lib.call("pyre_paged_attention_mma", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(), _ptr(scratch),
              block_table.data_ptr(), block_table.stride(0), cu_seqlens.data_ptr(), positions.data_ptr(), T, n_seqs,
-             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), n_splits, _stream())
+             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), n_splits, int(max_len), _stream())
+    return out
+
+
+PREFILL_HEAD_DIMS = (64, 128)
+PREFILL_MIN_LEN = 32     # entries with at least this many tokens go to the prompt-portion kernel
+
+
+def attention_prefill(q: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor, cu_seqlens: torch.Tensor,
+                      positions: torch.Tensor, n_seqs: int, n_long_tokens: int, n_heads: int, n_kv_heads: int,
+                      head_dim: int, scale: float, window: "int | None", out: torch.Tensor,
+                      min_len: int = PREFILL_MIN_LEN) -> torch.Tensor:
+    """bfloat16 attention of the entries with at least ``min_len`` tokens (64 queries of a head
+    per CTA, keys and values tiled through shared memory); writes only those entries' rows of ``out``."""
+    _check(q, "q", torch.bfloat16, 2)
+    _check(cache_layer, "cache_layer", torch.bfloat16, 5)
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    _check(positions, "positions", torch.int32, 1)
+    _check(out, "out", torch.bfloat16, 2)
+    if head_dim not in PREFILL_HEAD_DIMS:
+        raise UnsupportedSize(f"head_dim {head_dim}: the prompt-portion attention kernel takes {PREFILL_HEAD_DIMS}")
+    if n_heads % n_kv_heads:
+        raise UnsupportedSize(f"{n_heads} query heads cannot be shared among {n_kv_heads} key/value heads")
+    page_size = cache_layer.shape[3]
+    if tuple(cache_layer.shape[1:]) != (2, n_kv_heads, page_size, head_dim) or q.shape[1] != n_heads * head_dim:
+        raise ValueError("q or the cache layer do not match the head sizes")
+    if out.shape != q.shape or cu_seqlens.shape[0] != n_seqs + 1 or positions.shape[0] != q.shape[0]:
+        raise ValueError("out, cu_seqlens and positions do not match the batch")
+    lib.call("pyre_attention_prefill", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(), block_table.data_ptr(),
+             block_table.stride(0), cu_seqlens.data_ptr(), positions.data_ptr(), int(n_long_tokens), n_seqs, n_heads,
+             n_kv_heads, head_dim, page_size, int(window or 0), float(scale), int(min_len), _stream())
+    return out
+
+
+def paged_attention_bf16(ctx, q: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor, n_heads: int,
+                         n_kv_heads: int, head_dim: int, scale: float, window: "int | None") -> torch.Tensor:
+    """Attention of a whole step in bfloat16: entries with many tokens go to the
+    prompt-portion kernel, the others (decoded tokens, short portions) to the split-KV kernel."""
+    lens = ctx.cu_seqlens_host[1:] - ctx.cu_seqlens_host[:-1]
+    long_mask = lens >= PREFILL_MIN_LEN if head_dim in PREFILL_HEAD_DIMS else lens < 0
+    n_long = int(lens[long_mask].sum())
+    n_short_seqs = int((~long_mask).sum())
+    out = torch.empty_like(q)
+    if n_long:
+        attention_prefill(q, cache_layer, block_table, ctx.cu_seqlens, ctx.positions, ctx.num_seqs, n_long, n_heads,
+                          n_kv_heads, head_dim, scale, window, out)
+    if n_short_seqs:
+        n_short = ctx.num_tokens - n_long
+        short_ctx = int((ctx.start_pos_host + lens)[~long_mask].max())
+        splits = attention_splits(n_short, n_short_seqs, n_heads, n_kv_heads, short_ctx, window)
+        paged_attention_mma(q, cache_layer, block_table, ctx.cu_seqlens, ctx.positions, ctx.num_seqs, n_heads,
+                            n_kv_heads, head_dim, scale, window, splits, out=out,
+                            max_len=PREFILL_MIN_LEN - 1 if n_long else 0)
     return out
 
 

@@ -74,6 +74,8 @@ class Attention(Part):
         libs = ["elementwise"] + self.position.kernel_libraries()
         if self.dtype == torch.bfloat16 and self.head_dim <= ops.MMA_MAX_HEAD_DIM:
             libs.append("attention_mma")
+            if self.head_dim in ops.PREFILL_HEAD_DIMS:
+                libs.append("attention_prefill")
         else:
             libs.append("attention_generic")
         libs.append("gemm_f32" if self.dtype == torch.float32 else "gemm_tc")
@@ -93,10 +95,8 @@ class Attention(Part):
         q = ops.qkv_rope_write(qkv, self.b_qkv, cos, sin, layer if call.kv_write else None, kv.slot_mapping,
                                self.n_heads, self.n_kv_heads, self.head_dim, self.position.rotary_dim, kv.page_size)
         if self.dtype == torch.bfloat16 and self.head_dim <= ops.MMA_MAX_HEAD_DIM:
-            splits = ops.attention_splits(ctx.num_tokens, ctx.num_seqs, self.n_heads, self.n_kv_heads,
-                                          ctx.max_context, self.window)
-            a = ops.paged_attention_mma(q, layer, kv.block_table, ctx.cu_seqlens, ctx.positions, ctx.num_seqs,
-                                        self.n_heads, self.n_kv_heads, self.head_dim, self.scale, self.window, splits)
+            a = ops.paged_attention_bf16(ctx, q, layer, kv.block_table, self.n_heads, self.n_kv_heads, self.head_dim,
+                                         self.scale, self.window)
         else:
             # float32 and head sizes above 128: the exact fp32-arithmetic kernel
             a = ops.paged_attention_generic(q, layer, kv.block_table, ctx.seq_of_token, ctx.positions, self.n_heads,

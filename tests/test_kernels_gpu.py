@@ -314,6 +314,64 @@ def test_consumers_add_partial_sums(ops, dtype):
     torch.testing.assert_close(q1.float(), q2, **tol(dtype))
 
 
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [(4, 2, 64, 16, None), (7, 1, 128, 16, None), (6, 3, 128, 8, 70),
+                                                   (8, 8, 64, 32, 33), (28, 4, 128, 16, None)])
+def test_attention_prefill_and_mixed_dispatch(ops, nh, nkv, hd, page, window):
+    """Prompt portions (one that starts mid-page deep in a context, one whole prompt, one of
+    exactly 64 tokens) beside decode tokens in ONE step: the long entries go to the tiled
+    kernel, the short ones to the split-KV kernel, both write the same output tensor."""
+    import numpy as np
+    from pyre_b200.engine.context import StepContext
+    g = torch.Generator(device="cuda").manual_seed(31)
+    ctx_lens = [450, 100, 64, 333, 77, 40]
+    new = [150, 100, 64, 1, 1, 20]
+    B = len(new)
+    n_pages = sum(-(-c // page) for c in ctx_lens) + 3
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(32)).tolist()
+    W = max(-(-c // page) for c in ctx_lens)
+    table = torch.full((B, W), -1, dtype=torch.int32)
+    for s_, c in enumerate(ctx_lens):
+        for lp in range(-(-c // page)):
+            table[s_, lp] = perm.pop()
+    table = table.cuda()
+    cache = torch.randn(n_pages, 2, nkv, page, hd, device="cuda", generator=g)
+    for s_, c in enumerate(ctx_lens):
+        if c % page:
+            cache[int(table[s_, (c - 1) // page]), :, :, c % page:] = float("nan")
+    for pg in perm:
+        cache[pg] = float("nan")
+    seq_of_token = torch.tensor(sum(([s_] * n for s_, n in enumerate(new)), []), dtype=torch.int32, device="cuda")
+    positions = torch.tensor(sum((list(range(c - n, c)) for c, n in zip(ctx_lens, new)), []), dtype=torch.int32, device="cuda")
+    cu_host = np.concatenate([[0], np.cumsum(new)]).astype(np.int32)
+    cu = torch.from_numpy(cu_host).cuda()
+    T = int(seq_of_token.shape[0])
+    q = torch.randn(T, nh * hd, device="cuda", generator=g) * 1.5
+    # one far key decides a row in the middle of the first portion (if its window reaches it)
+    row = 77
+    far = 5 if not window else int(positions[row]) - window + 1
+    pg, off = int(table[0, far // page]), far % page
+    cache[pg, 0, 0, off] = q[row, :hd] * 2.0
+    cache, q = cache.to(torch.bfloat16), q.to(torch.bfloat16)
+    scale = hd ** -0.5
+    want = plain_paged_attention(q.float(), cache.float(), table, seq_of_token, positions, nh, nkv, hd, scale, window)
+    z = torch.zeros(T, dtype=torch.int32, device="cuda")
+    ctx = StepContext(dtype=torch.bfloat16, device=torch.device("cuda"), num_tokens=T, num_seqs=B, num_logit_rows=0,
+                      token_ids=z, positions=positions, seq_of_token=seq_of_token, cu_seqlens=cu, logit_rows=z[:0],
+                      cu_seqlens_host=cu_host, start_pos_host=np.asarray([c - n for c, n in zip(ctx_lens, new)]))
+    got = ops.paged_attention_bf16(ctx, q, cache, table, nh, nkv, hd, scale, window)
+    assert torch.isfinite(got).all()
+    err = (got.float() - want).abs()
+    bad = (err > 1.2e-2 + 1.6e-2 * want.abs()).any(dim=1)
+    assert not bad.any(), f"first wrong token row {int(torch.where(bad)[0][0])} of {T}, max error {float(err.max()):.3e}"
+    v_far = cache[pg, 1, 0, off].float()
+    assert (got[row, :hd].float() - v_far).abs().max() < 0.25 * v_far.abs().max() + 0.1
+    # the tiled kernel alone leaves the short entries' rows untouched
+    out = torch.full_like(q, 7.0)
+    ops.attention_prefill(q, cache, table, cu, positions, B, 150 + 100 + 64, nh, nkv, hd, scale, window, out)
+    assert float((out[314:316].float() - 7.0).abs().max()) == 0.0 and float((out[316:].float() - 7.0).abs().max()) == 0.0
+    assert (out[:314].float() - want[:314]).abs().max() < 0.05
+
+
 def test_sampling_large_vocabulary_two_stages(ops):
     from plain import qwen2_plain
     g = torch.Generator(device="cuda").manual_seed(8)
