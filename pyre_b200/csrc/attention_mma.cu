@@ -8,7 +8,9 @@
 // share of the group's keys in tiles of 16; its 4 warps take tiles round-robin, each
 // with its own online softmax, and merge through shared memory.  With more than one
 // split the CTA writes an unnormalised partial (max, sum, accumulator) to scratch and
-// `combine` merges the splits; with one split it writes the output directly.
+// `combine` merges the splits; with one split it writes the output directly.  When the
+// caller gives no scratch, the splits of a group form a thread-block cluster (up to 16 CTAs)
+// and merge through distributed shared memory instead: no scratch, no second kernel.
 //
 // Keys and values go from global memory straight into MMA fragments, no shared memory:
 //  * S = Q K^T contracts over head dims.  A permutation of the contraction index applied
@@ -26,7 +28,11 @@
 // Formula: pyre/model.py:104-124, pyre/kernels/paged_attn.py:43-71 (online softmax, fp32
 // scores; probabilities rounded to the activation dtype before the product with V, as
 // pyre/model.py:122 does).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -89,7 +95,9 @@ struct AttnParams {
     float scale;
 };
 
-template <int HD>
+// CLUSTER: the n_splits CTAs of a (group, kv head) form one thread-block cluster and merge their
+// partial results through distributed shared memory; no scratch, no second kernel.
+template <int HD, bool CLUSTER>
 __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const AttnParams p) {
     constexpr int KW = HD / 8;    // 32-bit words of K per lane per key   (HD/4 dims)
     constexpr int VW = HD / 16;   // 32-bit words of V per lane per key   (HD/8 dims)
@@ -98,6 +106,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
     __shared__ float sm_o[WARPS][16][HD + 1];
     __shared__ float sm_m[WARPS][16];
     __shared__ float sm_l[WARPS][16];
+    __shared__ float sm_cm[16], sm_cl[16];   // this CTA's merged (max, sum) per row, read by its cluster peers
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -160,16 +169,38 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
     const int* table = p.block_table + (size_t)seq * p.bt_stride;
     const size_t kv_stride = (size_t)p.nkv * p.page_size * HD;  // K block -> V block of a page
 
+    // Page numbers of a tile's six rows (two for K, four for V) are read one tile ahead, so
+    // that the dependent loads of keys and values never wait for the block table.
+    auto tile_pages = [&](int kt, int (&pk)[2], int (&pv)[4]) {
+        const int key0 = kt * TILE;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int key = key0 + 8 * i + g;
+            pk[i] = (kt < tile_end && key >= lo_g && key <= pos_last) ? table[key / p.page_size] : -1;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int key = key0 + 2 * t + (i & 1) + 8 * (i >> 1);
+            pv[i] = (kt < tile_end && key >= lo_g && key <= pos_last) ? table[key / p.page_size] : -1;
+        }
+    };
+    int pk_next[2], pv_next[4];
+    tile_pages(tile_begin + warp, pk_next, pv_next);
+
     for (int kt = tile_begin + warp; kt < tile_end; kt += WARPS) {
         const int key0 = kt * TILE;
+        int pk[2], pv[4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) pk[i] = pk_next[i];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pv[i] = pv_next[i];
         // ---- K: keys key0 + 8 i + g, i = 0, 1
         uint32_t kw[2][KW];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int key = key0 + 8 * i + g;
-            if (key >= lo_g && key <= pos_last) {
-                const int page = table[key / p.page_size];
-                const size_t row = ((size_t)(page * 2) * p.nkv + kvh) * p.page_size + key % p.page_size;
+            if (pk[i] >= 0) {
+                const size_t row = ((size_t)(pk[i] * 2) * p.nkv + kvh) * p.page_size + key % p.page_size;
                 load_words<KW>(kw[i], p.cache + row * HD + t * (HD / 4));
             } else {
                 zero_words<KW>(kw[i]);
@@ -180,14 +211,14 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int key = key0 + 2 * t + (i & 1) + 8 * (i >> 1);
-            if (key >= lo_g && key <= pos_last) {
-                const int page = table[key / p.page_size];
-                const size_t row = ((size_t)(page * 2) * p.nkv + kvh) * p.page_size + key % p.page_size;
+            if (pv[i] >= 0) {
+                const size_t row = ((size_t)(pv[i] * 2) * p.nkv + kvh) * p.page_size + key % p.page_size;
                 load_words<VW>(vw[i], p.cache + kv_stride + row * HD + g * (HD / 8));
             } else {
                 zero_words<VW>(vw[i]);
             }
         }
+        tile_pages(kt + WARPS, pk_next, pv_next);
         // ---- S = Q K^T
         float s[2][4];
 #pragma unroll
@@ -285,12 +316,43 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
         const size_t th = (size_t)(tok0 + ti) * p.nh + (kvh * n_rep + h_in_kv);
         if (p.n_splits == 1) {
             p.out[th * HD + d] = __float2bfloat16_rn(O / L);
+        } else if constexpr (CLUSTER) {
+            // keep this CTA's merged partial in its own shared memory: element (row, d) of warp
+            // slot 1 is read by this thread only, so it can be overwritten now; the row's max
+            // and sum are read by many threads and get arrays of their own
+            sm_o[1][row][d] = O;
+            if (d == 0) { sm_cm[row] = M; sm_cl[row] = L; }
         } else {
             p.part_acc[(th * p.n_splits + split) * HD + d] = O;
             if (d == 0) {
                 p.part_ml[(th * p.n_splits + split) * 2] = M;
                 p.part_ml[(th * p.n_splits + split) * 2 + 1] = L;
             }
+        }
+    }
+    if constexpr (CLUSTER) {
+        if (p.n_splits > 1) {
+            cg::cluster_group cluster = cg::this_cluster();
+            cluster.sync();
+            const int n = p.n_splits, rank = (int)cluster.block_rank();
+            for (int e = threadIdx.x * n + rank; e < 16 * HD; e += WARPS * 32 * n) {
+                const int row = e / HD, d = e % HD;
+                const int ti = row / p.hpg, hi = row % p.hpg;
+                const int h_in_kv = hb * p.hpg + hi;
+                if (!(ti < n_tok && ti < p.tpg && h_in_kv < n_rep)) continue;
+                float M = -INFINITY;
+                for (int c = 0; c < n; ++c) M = fmaxf(M, *cluster.map_shared_rank(&sm_cm[row], c));
+                const float m_use = (M == -INFINITY) ? 0.f : M;
+                float L = 0.f, O = 0.f;
+                for (int c = 0; c < n; ++c) {
+                    const float f = expf(*cluster.map_shared_rank(&sm_cm[row], c) - m_use);
+                    L += *cluster.map_shared_rank(&sm_cl[row], c) * f;
+                    O += *cluster.map_shared_rank(&sm_o[1][row][d], c) * f;
+                }
+                const size_t th = (size_t)(tok0 + ti) * p.nh + (kvh * n_rep + h_in_kv);
+                p.out[th * HD + d] = __float2bfloat16_rn(O / L);
+            }
+            cluster.sync();   // nobody leaves while a peer may still read its shared memory
         }
     }
 }
@@ -325,9 +387,34 @@ __global__ void combine_splits_kernel(const float* __restrict__ part_acc, const 
 }
 
 template <int HD>
-int launch(const AttnParams& p, int n_groups_bound, cudaStream_t stream) {
+int launch(const AttnParams& p, int n_groups_bound, bool use_cluster, cudaStream_t stream) {
     dim3 grid(n_groups_bound, p.nkv * p.head_blocks, p.n_splits);
-    pyre_launch(paged_attention_mma_kernel<HD>, dim3(grid), dim3(WARPS * 32), 0, stream, p);
+    if (!use_cluster) {
+        pyre_launch(paged_attention_mma_kernel<HD, false>, dim3(grid), dim3(WARPS * 32), 0, stream, p);
+        return (int)cudaGetLastError();
+    }
+    static bool configured = false;
+    if (!configured) {   // clusters of more than 8 CTAs are an opt-in
+        cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel<HD, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(WARPS * 32);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = p.n_splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pyre_pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, paged_attention_mma_kernel<HD, true>, p);
+    if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();
 }
 
@@ -346,7 +433,9 @@ PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* ou
                                       cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd % 16 || hd < 16 || hd > 128 || nkv <= 0 || nh % nkv || page_size <= 0 || n_splits < 1) return PYRE_ERR_UNSUPPORTED;
-    if (n_splits > 1 && !scratch) return PYRE_ERR_BAD_ARG;
+    // without scratch the splits merge through a thread-block cluster (at most 16 CTAs)
+    const bool use_cluster = n_splits > 1 && !scratch;
+    if (use_cluster && n_splits > 16) return PYRE_ERR_BAD_ARG;
     AttnParams p;
     p.q = (const __nv_bfloat16*)q;
     p.cache = (const __nv_bfloat16*)cache;
@@ -365,18 +454,18 @@ PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* ou
     const int groups_bound = n_tokens / p.tpg + n_seqs;  // sum over entries of ceil(len / tpg) is at most this
     int rc;
     switch (hd) {
-        case 16: rc = launch<16>(p, groups_bound, stream); break;
-        case 32: rc = launch<32>(p, groups_bound, stream); break;
-        case 48: rc = launch<48>(p, groups_bound, stream); break;
-        case 64: rc = launch<64>(p, groups_bound, stream); break;
-        case 80: rc = launch<80>(p, groups_bound, stream); break;
-        case 96: rc = launch<96>(p, groups_bound, stream); break;
-        case 112: rc = launch<112>(p, groups_bound, stream); break;
-        case 128: rc = launch<128>(p, groups_bound, stream); break;
+        case 16: rc = launch<16>(p, groups_bound, use_cluster, stream); break;
+        case 32: rc = launch<32>(p, groups_bound, use_cluster, stream); break;
+        case 48: rc = launch<48>(p, groups_bound, use_cluster, stream); break;
+        case 64: rc = launch<64>(p, groups_bound, use_cluster, stream); break;
+        case 80: rc = launch<80>(p, groups_bound, use_cluster, stream); break;
+        case 96: rc = launch<96>(p, groups_bound, use_cluster, stream); break;
+        case 112: rc = launch<112>(p, groups_bound, use_cluster, stream); break;
+        case 128: rc = launch<128>(p, groups_bound, use_cluster, stream); break;
         default: return PYRE_ERR_UNSUPPORTED;
     }
     if (rc) return rc;
-    if (n_splits > 1) {
+    if (n_splits > 1 && !use_cluster) {
         pyre_launch(combine_splits_kernel, dim3(n_tokens * nh), dim3(hd >= 64 ? 64 : 32), 0, stream, p.part_acc, p.part_ml, p.out, n_splits, hd, nh, cu_seqlens, n_seqs, max_len);
         PYRE_LAUNCH_CHECK();
     }

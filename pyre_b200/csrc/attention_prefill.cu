@@ -61,7 +61,7 @@ struct PrefillParams {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(WARPS * 32) attention_prefill_kernel(const PrefillParams p) {
+__global__ void __launch_bounds__(WARPS * 32, 3) attention_prefill_kernel(const PrefillParams p) {
     constexpr int CH = HD / 8;                 // 16-byte chunks per row
     constexpr int TILE_BYTES = BN * HD * 2;
     extern __shared__ __align__(128) uint8_t smem[];   // [2 stages][K tile, V tile]
@@ -73,15 +73,18 @@ __global__ void __launch_bounds__(WARPS * 32) attention_prefill_kernel(const Pre
     pdl_wait();   // queries, pages and index arrays come from earlier kernels of the step
 
     // ---- which 64-token tile of which entry is this CTA's?  (entries shorter than min_len are skipped)
+    // CTAs start in the order of blockIdx.x; the last tile of a portion sees the most keys, so
+    // tiles are numbered from the end of each portion (longest work first, short tail last).
     int tile = blockIdx.x, seq = -1, tok0 = 0, n_tok = 0;
     for (int b = 0; b < p.n_seqs; ++b) {
         const int begin = p.cu_seqlens[b], len = p.cu_seqlens[b + 1] - begin;
         if (len < p.min_len) continue;
         const int nt = (len + BM - 1) / BM;
         if (tile < nt) {
+            const int qt = nt - 1 - tile;
             seq = b;
-            tok0 = begin + tile * BM;
-            n_tok = min(BM, len - tile * BM);
+            tok0 = begin + qt * BM;
+            n_tok = min(BM, len - qt * BM);
             break;
         }
         tile -= nt;
@@ -163,16 +166,20 @@ __global__ void __launch_bounds__(WARPS * 32) attention_prefill_kernel(const Pre
             for (int i = 0; i < BN / 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
 #pragma unroll
             for (int k = 0; k < HD / 16; ++k) {
+                // the four fragment loads of a k-step go out together, then its eight products
+                uint32_t b[BN / 16][4];
 #pragma unroll
                 for (int n = 0; n < BN / 16; ++n) {
                     // matrices: (keys n*16 + 0..7 | 8..15) x (dims 16k + 0..7 | 8..15)
                     const int mi = lane >> 3;
                     const int row = n * 16 + (mi >> 1) * 8 + (lane & 7);
                     const int ch = 2 * k + (mi & 1);
-                    uint32_t b[4];
-                    ldmatrix_x4(b, k_tile + row * (HD * 2) + ((ch ^ (row & 7)) * 16));
-                    mma_bf16_16816(s[2 * n], qa[k], b[0], b[1]);
-                    mma_bf16_16816(s[2 * n + 1], qa[k], b[2], b[3]);
+                    ldmatrix_x4(b[n], k_tile + row * (HD * 2) + ((ch ^ (row & 7)) * 16));
+                }
+#pragma unroll
+                for (int n = 0; n < BN / 16; ++n) {
+                    mma_bf16_16816(s[2 * n], qa[k], b[n][0], b[n][1]);
+                    mma_bf16_16816(s[2 * n + 1], qa[k], b[n][2], b[n][3]);
                 }
             }
             // ---- scale, mask (only tiles that touch a row's limits), online softmax
@@ -220,15 +227,22 @@ __global__ void __launch_bounds__(WARPS * 32) attention_prefill_kernel(const Pre
                 const uint32_t pa[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
                                         pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
 #pragma unroll
-                for (int d = 0; d < HD / 16; ++d) {
-                    // matrices (stored [key][dim], read transposed): (keys 16kk + 0..7 | 8..15) x (dims 16d + 0..7 | 8..15)
-                    const int mi = lane >> 3;
-                    const int row = kk * 16 + (mi & 1) * 8 + (lane & 7);
-                    const int ch = 2 * d + (mi >> 1);
-                    uint32_t b[4];
-                    ldmatrix_x4_trans(b, v_tile + row * (HD * 2) + ((ch ^ (row & 7)) * 16));
-                    mma_bf16_16816(o[2 * d], pa, b[0], b[1]);
-                    mma_bf16_16816(o[2 * d + 1], pa, b[2], b[3]);
+                for (int d0 = 0; d0 < HD / 16; d0 += 4) {
+                    uint32_t b[4][4];
+#pragma unroll
+                    for (int dd = 0; dd < 4; ++dd) {
+                        // matrices (stored [key][dim], read transposed): (keys 16kk + 0..7 | 8..15) x (dims 16d + 0..7 | 8..15)
+                        const int d = d0 + dd;
+                        const int mi = lane >> 3;
+                        const int row = kk * 16 + (mi & 1) * 8 + (lane & 7);
+                        const int ch = 2 * d + (mi >> 1);
+                        ldmatrix_x4_trans(b[dd], v_tile + row * (HD * 2) + ((ch ^ (row & 7)) * 16));
+                    }
+#pragma unroll
+                    for (int dd = 0; dd < 4; ++dd) {
+                        mma_bf16_16816(o[2 * (d0 + dd)], pa, b[dd][0], b[dd][1]);
+                        mma_bf16_16816(o[2 * (d0 + dd) + 1], pa, b[dd][2], b[dd][3]);
+                    }
                 }
             }
         }

@@ -233,7 +233,7 @@ __global__ void qkv_rope_write_kernel(const T* __restrict__ qkv, const float* __
                                       int page_size) {
     pdl_trigger();
     pdl_wait();
-    const int t = blockIdx.x;
+    const int t = blockIdx.x;   // one token per blockIdx.x; blockIdx.y strides over its items
     const int half = rot / 2;
     const int chunks = hd / 4;
     const int n_heads_all = nh + 2 * nkv;
@@ -245,7 +245,7 @@ __global__ void qkv_rope_write_kernel(const T* __restrict__ qkv, const float* __
     const int page = slot >= 0 ? slot / page_size : 0;
     const int off = slot >= 0 ? slot - page * page_size : 0;
 
-    for (int item = threadIdx.x; item < n_heads_all * chunks; item += blockDim.x) {
+    for (int item = blockIdx.y * blockDim.x + threadIdx.x; item < n_heads_all * chunks; item += gridDim.y * blockDim.x) {
         const int h = item / chunks;
         const int d0 = (item - h * chunks) * 4;
         const bool is_v = h >= nh + nkv;
@@ -303,11 +303,14 @@ PYRE_API int pyre_qkv_rope_write(const void* qkv, const float* partials, int n_p
     if ((qkv == nullptr) == (partials == nullptr)) return PYRE_ERR_BAD_ARG;
     if (partials && n_partials < 1) return PYRE_ERR_BAD_ARG;
     const int items = (nh + 2 * nkv) * (hd / 4);
-    const int threads = min(256, max(32, ((items + 31) / 32) * 32));
+    const int threads = min(128, max(32, ((items + 31) / 32) * 32));
+    // few tokens: spread a token's items over several blocks (one item per thread); many tokens:
+    // one block per token is plenty of parallelism
+    const int by = n_tokens >= 256 ? 1 : min(ceil_div(items, threads), 64);
     if (dtype == PYRE_F32)
-        pyre_launch(qkv_rope_write_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (float*)q_out, (float*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
+        pyre_launch(qkv_rope_write_kernel<float>, dim3(n_tokens, by), dim3(threads), 0, stream, (const float*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (float*)q_out, (float*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
     else if (dtype == PYRE_BF16)
-        pyre_launch(qkv_rope_write_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
+        pyre_launch(qkv_rope_write_kernel<__nv_bfloat16>, dim3(n_tokens, by), dim3(threads), 0, stream, (const __nv_bfloat16*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;

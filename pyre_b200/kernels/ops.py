@@ -267,20 +267,25 @@ def paged_attention_generic(q: torch.Tensor, cache_layer: torch.Tensor, block_ta
 
 
 MMA_MAX_HEAD_DIM = 128
+CLUSTER_MAX_SPLITS = 16      # splits of one group merge through a thread-block cluster up to this many
 _SM_COUNT = 148
 
 
 def attention_splits(n_tokens: int, n_seqs: int, n_heads: int, n_kv_heads: int, max_context: int,
                      window: "int | None") -> int:
     """How many ways the tensor-core kernel splits each sequence's keys: enough CTAs for
-    two per SM, but at least four 16-key tiles per split."""
+    two per SM, at least two 16-key tiles per split, at most 16 (the splits of a group
+    form one thread-block cluster)."""
     n_rep = n_heads // n_kv_heads
     hpg = min(n_rep, 16)
     tpg = 16 // hpg
     ctas = (n_tokens // tpg + n_seqs) * n_kv_heads * (-(-n_rep // hpg))
     span = max_context if not window else min(max_context, window + tpg)
     tiles = -(-span // 16) + 1
-    return int(max(1, min(-(-2 * _SM_COUNT // max(ctas, 1)), -(-tiles // 4), 64)))
+    want = max(1, min(-(-2 * _SM_COUNT // max(ctas, 1)), -(-tiles // 2), CLUSTER_MAX_SPLITS))
+    if want > 8:
+        return 16 if want >= 12 else 8
+    return int(want)
 
 
 def paged_attention_mma(q: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor,
@@ -311,7 +316,7 @@ def paged_attention_mma(q: torch.Tensor, cache_layer: torch.Tensor, block_table:
     if out is None:
         out = torch.empty_like(q)
     n_splits = int(n_splits)
-    if n_splits > 1:
+    if n_splits > 1 and not (scratch is None and n_splits <= CLUSTER_MAX_SPLITS):
         need = T * n_heads * n_splits * (head_dim + 2)
         if scratch is None:
             scratch = torch.empty(need, dtype=torch.float32, device=q.device)

@@ -234,7 +234,7 @@ def test_paged_attention_generic(ops, dtype, nh, nkv, hd, page, window):
 @pytest.mark.parametrize("nh,nkv,hd,page,window", [(4, 2, 16, 16, None), (3, 1, 32, 8, None), (6, 3, 48, 4, 37),
                                                    (8, 2, 64, 32, None), (28, 4, 128, 16, None), (7, 1, 128, 16, 50),
                                                    (40, 2, 80, 16, None), (5, 5, 112, 8, 19), (16, 16, 96, 16, None)])
-@pytest.mark.parametrize("n_splits", [1, 3])
+@pytest.mark.parametrize("n_splits", [1, 3, 16, -5])
 def test_paged_attention_mma(ops, nh, nkv, hd, page, window, n_splits):
     """The tensor-core kernel on a mixed batch (a decode token deep in a long context, a
     prompt portion that starts in the middle of a page, a short whole prompt, a second decode
@@ -267,7 +267,13 @@ def test_paged_attention_mma(ops, nh, nkv, hd, page, window, n_splits):
     cache, q = cache.to(torch.bfloat16), q.to(torch.bfloat16)
     scale = hd ** -0.5
     want = plain_paged_attention(q.float(), cache.float(), table, seq_of_token, positions, nh, nkv, hd, scale, window)
-    got = ops.paged_attention_mma(q, cache, table, cu, positions, 4, nh, nkv, hd, scale, window, n_splits)
+    # splits merge through a thread-block cluster (up to 16 CTAs); a negative count here asks
+    # for the other way: partial results in scratch memory and a combining kernel
+    if n_splits > 0:
+        got = ops.paged_attention_mma(q, cache, table, cu, positions, 4, nh, nkv, hd, scale, window, n_splits)
+    else:
+        scratch = torch.empty(T * nh * -n_splits * (hd + 2), dtype=torch.float32, device="cuda")
+        got = ops.paged_attention_mma(q, cache, table, cu, positions, 4, nh, nkv, hd, scale, window, -n_splits, scratch=scratch)
     assert torch.isfinite(got).all()
     torch.testing.assert_close(got.float(), want, rtol=1.6e-2, atol=1.2e-2)
     exact = ops.paged_attention_generic(q, cache, table, seq_of_token, positions, nh, nkv, hd, scale, window)

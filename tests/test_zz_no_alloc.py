@@ -64,7 +64,10 @@ def test_noalloc_entry_matches_the_ordinary_one_twice_in_a_row():
         q, cache, table, cu, positions, n_seqs = _case(40 + n, **shape)
         nh, nkv, hd = shape["nh"], shape["nkv"], shape["hd"]
         scale = hd ** -0.5
-        want = ops.paged_attention_mma(q, cache, table, cu, positions, n_seqs, nh, nkv, hd, scale, None, n_splits)
+        # the ordinary entry point with scratch from the caller (torch's allocator here)
+        scratch = torch.empty(max(1, q.shape[0] * nh * n_splits * (hd + 2)), dtype=torch.float32, device="cuda")
+        want = ops.paged_attention_mma(q, cache, table, cu, positions, n_seqs, nh, nkv, hd, scale, None, n_splits,
+                                       scratch=scratch)
         got = torch.full_like(q, float("nan"))
         rc = fn(q.data_ptr(), cache.data_ptr(), got.data_ptr(), table.data_ptr(), table.stride(0), cu.data_ptr(),
                 positions.data_ptr(), q.shape[0], n_seqs, nh, nkv, hd, shape["page"], 0, scale, n_splits, stream)
