@@ -12,18 +12,13 @@
 // caller gives no scratch, the splits of a group form a thread-block cluster (up to 16 CTAs)
 // and merge through distributed shared memory instead: no scratch, no second kernel.
 //
-// Keys and values go from global memory straight into MMA fragments, no shared memory:
-//  * S = Q K^T contracts over head dims.  A permutation of the contraction index applied
-//    to both operands changes nothing, so lane (g, t) of the m16n8k16 fragment owns the
-//    CONTIGUOUS dims [t*HD/4, (t+1)*HD/4) of key g: one or more 16-byte loads, and four
-//    lanes cover a whole row.
-//  * O = P V contracts over keys, and a B fragment register holds two adjacent KEYS of
-//    one dim, while memory is contiguous along dims.  Lane (g, t) loads the contiguous
-//    dims [g*HD/8, (g+1)*HD/8) of keys 2t, 2t+1, 2t+8, 2t+9 and pairs the keys with
-//    byte permutes; the permutation of the output dims this implies is undone at the store.
-// Masked keys (beyond a row's position, before its window, outside the sequence) are
-// never loaded: their fragments are zero and their scores -inf, so stale or non-finite
-// memory in unowned slots cannot reach the result.
+// Each warp owns a two-stage ring in shared memory: while it computes on tile i, the
+// cp.async copies of tile i + 1 (16 keys and 16 values, fetched row by row through the
+// block table in 16-byte chunks) are in flight, so the memory system always has work from
+// every warp.  Rows are XOR-swizzled by chunk so that the copies and the ldmatrix reads
+// (plain for K, transposed for V) do not collide on banks.  Masked keys (beyond a row's
+// position, before its window, outside the sequence) are zero-filled by the copy and get
+// a score of -inf, so stale or non-finite memory in unowned slots cannot reach the result.
 //
 // Formula: pyre/model.py:104-124, pyre/kernels/paged_attn.py:43-71 (online softmax, fp32
 // scores; probabilities rounded to the activation dtype before the product with V, as
@@ -51,35 +46,19 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Load N 32-bit words from p (aligned to the widest vector that divides N words).
-template <int N>
-__device__ __forceinline__ void load_words(uint32_t (&dst)[N], const void* p) {
-    if constexpr (N % 4 == 0) {
-        const uint4* s = reinterpret_cast<const uint4*>(p);
-#pragma unroll
-        for (int i = 0; i < N / 4; ++i) {
-            uint4 v = __ldg(s + i);
-            dst[4 * i] = v.x; dst[4 * i + 1] = v.y; dst[4 * i + 2] = v.z; dst[4 * i + 3] = v.w;
-        }
-    } else if constexpr (N % 2 == 0) {
-        const uint2* s = reinterpret_cast<const uint2*>(p);
-#pragma unroll
-        for (int i = 0; i < N / 2; ++i) {
-            uint2 v = __ldg(s + i);
-            dst[2 * i] = v.x; dst[2 * i + 1] = v.y;
-        }
-    } else {
-        const uint32_t* s = reinterpret_cast<const uint32_t*>(p);
-#pragma unroll
-        for (int i = 0; i < N; ++i) dst[i] = __ldg(s + i);
-    }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
-
-template <int N>
-__device__ __forceinline__ void zero_words(uint32_t (&dst)[N]) {
-#pragma unroll
-    for (int i = 0; i < N; ++i) dst[i] = 0u;
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
 struct AttnParams {
     const __nv_bfloat16* q;      // [T, nh, HD]
@@ -99,14 +78,21 @@ struct AttnParams {
 // partial results through distributed shared memory; no scratch, no second kernel.
 template <int HD, bool CLUSTER>
 __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const AttnParams p) {
-    constexpr int KW = HD / 8;    // 32-bit words of K per lane per key   (HD/4 dims)
-    constexpr int VW = HD / 16;   // 32-bit words of V per lane per key   (HD/8 dims)
     constexpr int KSTEPS = HD / 16;
     constexpr int NT_O = HD / 8;  // output n-tiles
-    __shared__ float sm_o[WARPS][16][HD + 1];
+    constexpr int CH = HD / 8;    // 16-byte chunks per row
+    constexpr int SWZ = (CH % 8 == 0) ? 7 : (CH % 4 == 0) ? 3 : (CH % 2 == 0) ? 1 : 0;   // XOR mask that stays inside a row
+    constexpr int TILE_BYTES = TILE * HD * 2;          // one K (or V) tile
+    constexpr int WARP_BYTES = 2 * 2 * TILE_BYTES;     // two stages of K + V
+    static_assert(16 * (HD + 1) * 4 <= WARP_BYTES, "the merge buffer of a warp must fit into its ring");
+    // a warp's ring is dead once its key loop is over; its merge buffer sm_o[warp] reuses the space
+    extern __shared__ __align__(128) uint8_t smem_dyn[];
     __shared__ float sm_m[WARPS][16];
     __shared__ float sm_l[WARPS][16];
     __shared__ float sm_cm[16], sm_cl[16];   // this CTA's merged (max, sum) per row, read by its cluster peers
+    auto sm_o = [&](int w, int row, int d) -> float& {
+        return reinterpret_cast<float*>(smem_dyn + (size_t)w * WARP_BYTES)[row * (HD + 1) + d];
+    };
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -154,12 +140,18 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
     const int tile_begin = tile_lo + split * tps;
     const int tile_end = min(tile_begin + tps, tile_hi + 1);
 
-    // ---- Q fragments: lane (g, t) holds dims [t*HD/4, (t+1)*HD/4) of rows g and g + 8
-    uint32_t qw[2][KW];
+    // ---- Q fragments (A operand, natural layout) straight from global memory
+    uint32_t qa[KSTEPS][4];
+    {
+        const __nv_bfloat16* q0 = p.q + ((size_t)row_tok[0] * p.nh + row_head[0]) * HD;
+        const __nv_bfloat16* q1 = p.q + ((size_t)row_tok[1] * p.nh + row_head[1]) * HD;
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        if (row_ok[r]) load_words<KW>(qw[r], p.q + ((size_t)row_tok[r] * p.nh + row_head[r]) * HD + t * (HD / 4));
-        else zero_words<KW>(qw[r]);
+        for (int k = 0; k < KSTEPS; ++k) {
+            qa[k][0] = row_ok[0] ? *reinterpret_cast<const uint32_t*>(q0 + 16 * k + 2 * t) : 0u;
+            qa[k][1] = row_ok[1] ? *reinterpret_cast<const uint32_t*>(q1 + 16 * k + 2 * t) : 0u;
+            qa[k][2] = row_ok[0] ? *reinterpret_cast<const uint32_t*>(q0 + 16 * k + 8 + 2 * t) : 0u;
+            qa[k][3] = row_ok[1] ? *reinterpret_cast<const uint32_t*>(q1 + 16 * k + 8 + 2 * t) : 0u;
+        }
     }
 
     float o[NT_O][4];
@@ -168,67 +160,50 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const int* table = p.block_table + (size_t)seq * p.bt_stride;
     const size_t kv_stride = (size_t)p.nkv * p.page_size * HD;  // K block -> V block of a page
+    const uint32_t ring = (uint32_t)__cvta_generic_to_shared(smem_dyn) + warp * WARP_BYTES;
 
-    // Page numbers of a tile's six rows (two for K, four for V) are read one tile ahead, so
-    // that the dependent loads of keys and values never wait for the block table.
-    auto tile_pages = [&](int kt, int (&pk)[2], int (&pv)[4]) {
-        const int key0 = kt * TILE;
+    // copy tile kt (16 keys, 16 values) into a stage of this warp's ring; chunk i of the
+    // 16 * CH chunks of a tile belongs to row i / CH
+    auto load_tile = [&](int kt, int stage) {
+        const uint32_t k_dst = ring + stage * 2 * TILE_BYTES, v_dst = k_dst + TILE_BYTES;
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int key = key0 + 8 * i + g;
-            pk[i] = (kt < tile_end && key >= lo_g && key <= pos_last) ? table[key / p.page_size] : -1;
-        }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int key = key0 + 2 * t + (i & 1) + 8 * (i >> 1);
-            pv[i] = (kt < tile_end && key >= lo_g && key <= pos_last) ? table[key / p.page_size] : -1;
+        for (int i = lane; i < TILE * CH; i += 32) {
+            const int row = i / CH, c = i % CH;
+            const int key = kt * TILE + row;
+            const bool live = key >= lo_g && key <= pos_last;
+            const int page = live ? table[key / p.page_size] : 0;
+            const size_t krow = ((size_t)(page * 2) * p.nkv + kvh) * p.page_size + (live ? key % p.page_size : 0);
+            const __nv_bfloat16* ksrc = p.cache + krow * HD + c * 8;
+            const uint32_t off = row * (HD * 2) + ((c ^ (row & SWZ)) * 16);
+            cp_async_16(k_dst + off, ksrc, live ? 16 : 0);
+            cp_async_16(v_dst + off, ksrc + kv_stride, live ? 16 : 0);
         }
     };
-    int pk_next[2], pv_next[4];
-    tile_pages(tile_begin + warp, pk_next, pv_next);
 
-    for (int kt = tile_begin + warp; kt < tile_end; kt += WARPS) {
+    int kt = tile_begin + warp;
+    if (kt < tile_end) load_tile(kt, 0);
+    cp_async_commit();
+    for (int it = 0; kt < tile_end; kt += WARPS, ++it) {
+        const int stage = it & 1;
+        if (kt + WARPS < tile_end) load_tile(kt + WARPS, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();       // every lane's copies of this tile have landed
         const int key0 = kt * TILE;
-        int pk[2], pv[4];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) pk[i] = pk_next[i];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) pv[i] = pv_next[i];
-        // ---- K: keys key0 + 8 i + g, i = 0, 1
-        uint32_t kw[2][KW];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int key = key0 + 8 * i + g;
-            if (pk[i] >= 0) {
-                const size_t row = ((size_t)(pk[i] * 2) * p.nkv + kvh) * p.page_size + key % p.page_size;
-                load_words<KW>(kw[i], p.cache + row * HD + t * (HD / 4));
-            } else {
-                zero_words<KW>(kw[i]);
-            }
-        }
-        // ---- V: keys key0 + 2t + {0, 1, 8, 9}, dims [g*HD/8, (g+1)*HD/8)
-        uint32_t vw[4][VW];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int key = key0 + 2 * t + (i & 1) + 8 * (i >> 1);
-            if (pv[i] >= 0) {
-                const size_t row = ((size_t)(pv[i] * 2) * p.nkv + kvh) * p.page_size + key % p.page_size;
-                load_words<VW>(vw[i], p.cache + kv_stride + row * HD + g * (HD / 8));
-            } else {
-                zero_words<VW>(vw[i]);
-            }
-        }
-        tile_pages(kt + WARPS, pk_next, pv_next);
-        // ---- S = Q K^T
+        const uint32_t k_tile = ring + stage * 2 * TILE_BYTES, v_tile = k_tile + TILE_BYTES;
+        const int mi = lane >> 3, lr = lane & 7;
+        // ---- S = Q K^T: matrices (keys 0..7 | 8..15) x (dims 16k + 0..7 | 8..15)
         float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
+        s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-#pragma unroll
-            for (int j = 0; j < KSTEPS; ++j) {
-                const uint32_t a[4] = {qw[0][2 * j], qw[1][2 * j], qw[0][2 * j + 1], qw[1][2 * j + 1]};
-                mma_bf16_16816(s[i], a, kw[i][2 * j], kw[i][2 * j + 1]);
-            }
+        for (int k = 0; k < KSTEPS; ++k) {
+            const int row = (mi >> 1) * 8 + lr;
+            const int ch = 2 * k + (mi & 1);
+            uint32_t b[4];
+            ldmatrix_x4(b, k_tile + row * (HD * 2) + ((ch ^ (row & SWZ)) * 16));
+            mma_bf16_16816(s[0], qa[k], b[0], b[1]);
+            mma_bf16_16816(s[1], qa[k], b[2], b[3]);
         }
         // ---- mask, scale, online softmax (rows g: c = 0, 1; rows g + 8: c = 2, 3)
         float tile_max[2] = {-INFINITY, -INFINITY};
@@ -265,18 +240,22 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
             o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
             o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
         }
-        // ---- O += P V
+        // ---- O += P V: matrices read transposed, (keys 0..7 | 8..15) x (dims 16d + 0..7 | 8..15)
         const uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
                                 pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
 #pragma unroll
-        for (int i = 0; i < NT_O; ++i) {
-            const int c = i >> 1;
-            const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;  // high or low halves of two words
-            const uint32_t b0 = __byte_perm(vw[0][c], vw[1][c], sel);
-            const uint32_t b1 = __byte_perm(vw[2][c], vw[3][c], sel);
-            mma_bf16_16816(o[i], pa, b0, b1);
+        for (int d = 0; d < HD / 16; ++d) {
+            const int row = (mi & 1) * 8 + lr;
+            const int ch = 2 * d + (mi >> 1);
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, v_tile + row * (HD * 2) + ((ch ^ (row & SWZ)) * 16));
+            mma_bf16_16816(o[2 * d], pa, b[0], b[1]);
+            mma_bf16_16816(o[2 * d + 1], pa, b[2], b[3]);
         }
+        __syncwarp();       // the stage is refilled by the copies issued in the next iteration
     }
+    cp_async_wait<0>();
+    __syncwarp();
 
     // ---- merge the warps of the CTA
 #pragma unroll
@@ -292,8 +271,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
     for (int i = 0; i < NT_O; ++i)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const int dim = (2 * t + (c & 1)) * (HD / 8) + i;  // undo the dim permutation of the V fragments
-            sm_o[warp][g + 8 * (c >> 1)][dim] = o[i][c];
+            sm_o(warp, g + 8 * (c >> 1), 8 * i + 2 * t + (c & 1)) = o[i][c];
         }
     __syncthreads();
 
@@ -311,7 +289,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
         for (int w = 0; w < WARPS; ++w) {
             const float f = expf(sm_m[w][row] - m_use);
             L += sm_l[w][row] * f;
-            O += sm_o[w][row][d] * f;
+            O += sm_o(w, row, d) * f;
         }
         const size_t th = (size_t)(tok0 + ti) * p.nh + (kvh * n_rep + h_in_kv);
         if (p.n_splits == 1) {
@@ -320,7 +298,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
             // keep this CTA's merged partial in its own shared memory: element (row, d) of warp
             // slot 1 is read by this thread only, so it can be overwritten now; the row's max
             // and sum are read by many threads and get arrays of their own
-            sm_o[1][row][d] = O;
+            sm_o(1, row, d) = O;
             if (d == 0) { sm_cm[row] = M; sm_cl[row] = L; }
         } else {
             p.part_acc[(th * p.n_splits + split) * HD + d] = O;
@@ -347,7 +325,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
                 for (int c = 0; c < n; ++c) {
                     const float f = expf(*cluster.map_shared_rank(&sm_cm[row], c) - m_use);
                     L += *cluster.map_shared_rank(&sm_cl[row], c) * f;
-                    O += *cluster.map_shared_rank(&sm_o[1][row][d], c) * f;
+                    O += *cluster.map_shared_rank(&sm_o(1, row, d), c) * f;
                 }
                 const size_t th = (size_t)(tok0 + ti) * p.nh + (kvh * n_rep + h_in_kv);
                 p.out[th * HD + d] = __float2bfloat16_rn(O / L);
@@ -389,20 +367,24 @@ __global__ void combine_splits_kernel(const float* __restrict__ part_acc, const 
 template <int HD>
 int launch(const AttnParams& p, int n_groups_bound, bool use_cluster, cudaStream_t stream) {
     dim3 grid(n_groups_bound, p.nkv * p.head_blocks, p.n_splits);
-    if (!use_cluster) {
-        pyre_launch(paged_attention_mma_kernel<HD, false>, dim3(grid), dim3(WARPS * 32), 0, stream, p);
-        return (int)cudaGetLastError();
-    }
+    constexpr int SMEM = WARPS * 2 * 2 * TILE * HD * 2;   // per warp: two stages of a K and a V tile
     static bool configured = false;
-    if (!configured) {   // clusters of more than 8 CTAs are an opt-in
-        cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel<HD, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (!configured) {   // more than 48 KB of dynamic shared memory and clusters of more than 8 CTAs are opt-ins
+        cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(paged_attention_mma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(paged_attention_mma_kernel<HD, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
         if (e != cudaSuccess) return (int)e;
         configured = true;
+    }
+    if (!use_cluster) {
+        cudaError_t e = pyre_launch(paged_attention_mma_kernel<HD, false>, dim3(grid), dim3(WARPS * 32), (size_t)SMEM, stream, p);
+        if (e != cudaSuccess) return (int)e;
+        return (int)cudaGetLastError();
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(WARPS * 32);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = SMEM;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
