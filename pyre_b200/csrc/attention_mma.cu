@@ -24,6 +24,9 @@
 // scores; probabilities rounded to the activation dtype before the product with V, as
 // pyre/model.py:122 does).
 #include <cooperative_groups.h>
+#include <cuda.h>
+
+#include <cstring>
 
 #include "common.cuh"
 
@@ -60,6 +63,30 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int s
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
+// ---- TMA pieces (tiles of power-of-two pages, head sizes that are multiples of 64)
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+constexpr uint32_t TMA_WAIT_LIMIT = 2000000;
+constexpr int ERR_ATTN_TIMEOUT = 3;
+
 struct AttnParams {
     const __nv_bfloat16* q;      // [T, nh, HD]
     const __nv_bfloat16* cache;  // layer: [page][2][nkv][page_size][HD]
@@ -70,6 +97,11 @@ struct AttnParams {
     const int* cu_seqlens;       // [B + 1]
     const int* positions;        // [T]
     int bt_stride, n_seqs, nh, nkv, page_size, window, n_splits, tpg, hpg, head_blocks;
+    int page_shift;              // log2(page_size) if it is a power of two, else -1
+    int use_tma;                 // tiles come by TMA through `map` (power-of-two pages, HD % 64 == 0)
+    int box_rows;                // rows per TMA box: min(16, page_size)
+    int* err_flag;
+    int uniform_len;             // > 0: every entry has exactly this many tokens (a decode step): no scan for the group
     int max_len;                 // > 0: only entries with at most this many tokens (longer ones go to the prefill kernel)
     float scale;
 };
@@ -77,7 +109,7 @@ struct AttnParams {
 // CLUSTER: the n_splits CTAs of a (group, kv head) form one thread-block cluster and merge their
 // partial results through distributed shared memory; no scratch, no second kernel.
 template <int HD, bool CLUSTER>
-__global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const __grid_constant__ CUtensorMap map, const AttnParams p) {
     constexpr int KSTEPS = HD / 16;
     constexpr int NT_O = HD / 8;  // output n-tiles
     constexpr int CH = HD / 8;    // 16-byte chunks per row
@@ -86,10 +118,13 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
     constexpr int WARP_BYTES = 2 * 2 * TILE_BYTES;     // two stages of K + V
     static_assert(16 * (HD + 1) * 4 <= WARP_BYTES, "the merge buffer of a warp must fit into its ring");
     // a warp's ring is dead once its key loop is over; its merge buffer sm_o[warp] reuses the space
-    extern __shared__ __align__(128) uint8_t smem_dyn[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // 128B-swizzled boxes must start on 1024-byte boundaries
+    uint8_t* smem_dyn = smem_raw + ((1024u - ((uint32_t)__cvta_generic_to_shared(smem_raw) & 1023u)) & 1023u);
     __shared__ float sm_m[WARPS][16];
     __shared__ float sm_l[WARPS][16];
     __shared__ float sm_cm[16], sm_cl[16];   // this CTA's merged (max, sum) per row, read by its cluster peers
+    __shared__ __align__(8) uint64_t tma_bar[WARPS][2];   // per warp and stage: "the tile has landed"
     auto sm_o = [&](int w, int row, int d) -> float& {
         return reinterpret_cast<float*>(smem_dyn + (size_t)w * WARP_BYTES)[row * (HD + 1) + d];
     };
@@ -101,6 +136,15 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
 
     // ---- which group is this CTA's?  groups are counted entry by entry
     int grp = blockIdx.x, seq = -1, tok0 = 0, n_tok = 0;
+    if (p.uniform_len > 0) {
+        const int ng = (p.uniform_len + p.tpg - 1) / p.tpg;
+        const int b = grp / ng, gi = grp % ng;
+        if (b < p.n_seqs) {
+            seq = b;
+            tok0 = b * p.uniform_len + gi * p.tpg;
+            n_tok = min(p.tpg, p.uniform_len - gi * p.tpg);
+        }
+    } else
     for (int b = 0; b < p.n_seqs; ++b) {
         const int begin = p.cu_seqlens[b], len = p.cu_seqlens[b + 1] - begin;
         if (p.max_len > 0 && len > p.max_len) continue;
@@ -171,8 +215,10 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
             const int row = i / CH, c = i % CH;
             const int key = kt * TILE + row;
             const bool live = key >= lo_g && key <= pos_last;
-            const int page = live ? table[key / p.page_size] : 0;
-            const size_t krow = ((size_t)(page * 2) * p.nkv + kvh) * p.page_size + (live ? key % p.page_size : 0);
+            const int lp = p.page_shift >= 0 ? key >> p.page_shift : key / p.page_size;
+            const int slot = p.page_shift >= 0 ? key & (p.page_size - 1) : key % p.page_size;
+            const int page = live ? table[lp] : 0;
+            const size_t krow = ((size_t)(page * 2) * p.nkv + kvh) * p.page_size + (live ? slot : 0);
             const __nv_bfloat16* ksrc = p.cache + krow * HD + c * 8;
             const uint32_t off = row * (HD * 2) + ((c ^ (row & SWZ)) * 16);
             cp_async_16(k_dst + off, ksrc, live ? 16 : 0);
@@ -180,31 +226,105 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
         }
     };
 
+    // TMA variant: one lane brings a tile with a few bulk tensor copies.  A tile is HD / 64
+    // column boxes of 128 bytes (the swizzle span) for K and for V, each 16 / box_rows row
+    // pieces (one piece per page the tile touches).  Stage layout: [K col 0][K col 1]..[V col 0]..,
+    // every box 16 rows x 128 B = 2 KB, 128B-swizzled by the copy engine.
+    const bool tma = p.use_tma != 0;
+    const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(&tma_bar[warp][0]);
+    if (tma && lane == 0) {
+        mbar_init(bar0, 1);
+        mbar_init(bar0 + 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    auto tma_tile = [&](int kt, int stage) {   // lane 0 only
+        const uint32_t dst = ring + stage * 2 * TILE_BYTES;
+        const uint32_t bar = bar0 + 8 * stage;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier generic accesses to the stage come first
+        mbar_expect_tx(bar, 2 * TILE_BYTES);
+        const int pieces = TILE / p.box_rows;
+        for (int pc = 0; pc < pieces; ++pc) {
+            const int key = kt * TILE + pc * p.box_rows;
+            // a piece wholly outside [lo_g, pos_last] still has to be filled: read page 0 (its scores are masked)
+            const int lp = key >> p.page_shift;
+            const bool live = key + p.box_rows - 1 >= lo_g && key <= pos_last;
+            const int page = live ? table[lp] : 0;
+            const int krow = ((page * 2) * p.nkv + kvh) * p.page_size + (key & (p.page_size - 1));
+            const int vrow = krow + p.nkv * p.page_size;
+#pragma unroll
+            for (int cb = 0; cb < HD / 64; ++cb) {
+                tma_load_2d(dst + cb * 2048 + pc * p.box_rows * 128, &map, bar, cb * 64, krow);
+                tma_load_2d(dst + TILE_BYTES + cb * 2048 + pc * p.box_rows * 128, &map, bar, cb * 64, vrow);
+            }
+        }
+    };
+    // shared-memory address of 16-byte chunk `ch` of row `row` of a tile
+    auto chunk_addr = [&](uint32_t tile, int row, int ch) -> uint32_t {
+        if (tma) return tile + (ch >> 3) * 2048 + row * 128 + (((ch & 7) ^ (row & 7)) * 16);
+        return tile + row * (HD * 2) + ((ch ^ (row & SWZ)) * 16);
+    };
+    bool timed_out = false;
+
     int kt = tile_begin + warp;
-    if (kt < tile_end) load_tile(kt, 0);
+    if (kt < tile_end) {
+        if (!tma) load_tile(kt, 0);
+        else if (lane == 0) tma_tile(kt, 0);
+    }
     cp_async_commit();
     for (int it = 0; kt < tile_end; kt += WARPS, ++it) {
         const int stage = it & 1;
-        if (kt + WARPS < tile_end) load_tile(kt + WARPS, stage ^ 1);
+        if (kt + WARPS < tile_end) {
+            if (!tma) load_tile(kt + WARPS, stage ^ 1);
+            else if (lane == 0) tma_tile(kt + WARPS, stage ^ 1);
+        }
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncwarp();       // every lane's copies of this tile have landed
         const int key0 = kt * TILE;
         const uint32_t k_tile = ring + stage * 2 * TILE_BYTES, v_tile = k_tile + TILE_BYTES;
+        if (!tma) {
+            cp_async_wait<1>();
+        } else {
+            const uint32_t parity = (it >> 1) & 1;
+            uint32_t spins = 0;
+            while (!mbar_try_wait(bar0 + 8 * stage, parity)) {
+                if (++spins > TMA_WAIT_LIMIT) { timed_out = true; break; }
+            }
+            timed_out = __any_sync(0xffffffffu, timed_out);   // the whole warp gives up together
+            if (timed_out) break;
+            // the copy engine brought whole rows of the page: rows outside [lo_g, pos_last] may hold
+            // anything, so their values are zeroed here (their scores are masked below)
+            if (key0 + TILE - 1 > pos_last || key0 < lo_g) {
+                for (int i = lane; i < TILE * CH; i += 32) {
+                    const int row = i / CH, c = i % CH;
+                    const int key = key0 + row;
+                    if (key > pos_last || key < lo_g)
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(chunk_addr(v_tile, row, c)), "r"(0u) : "memory");
+                }
+            }
+        }
+        __syncwarp();       // every lane sees the whole tile
         const int mi = lane >> 3, lr = lane & 7;
         // ---- S = Q K^T: matrices (keys 0..7 | 8..15) x (dims 16k + 0..7 | 8..15)
-        float s[2][4];
-        s[0][0] = s[0][1] = s[0][2] = s[0][3] = 0.f;
-        s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+        // two sets of accumulators (even and odd k-steps) halve the chain of dependent products
+        float s[2][4], s2[2][4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) { s[0][c] = s[1][c] = s2[0][c] = s2[1][c] = 0.f; }
 #pragma unroll
         for (int k = 0; k < KSTEPS; ++k) {
             const int row = (mi >> 1) * 8 + lr;
             const int ch = 2 * k + (mi & 1);
             uint32_t b[4];
-            ldmatrix_x4(b, k_tile + row * (HD * 2) + ((ch ^ (row & SWZ)) * 16));
-            mma_bf16_16816(s[0], qa[k], b[0], b[1]);
-            mma_bf16_16816(s[1], qa[k], b[2], b[3]);
+            ldmatrix_x4(b, chunk_addr(k_tile, row, ch));
+            if (k & 1) {
+                mma_bf16_16816(s2[0], qa[k], b[0], b[1]);
+                mma_bf16_16816(s2[1], qa[k], b[2], b[3]);
+            } else {
+                mma_bf16_16816(s[0], qa[k], b[0], b[1]);
+                mma_bf16_16816(s[1], qa[k], b[2], b[3]);
+            }
         }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) { s[0][c] += s2[0][c]; s[1][c] += s2[1][c]; }
         // ---- mask, scale, online softmax (rows g: c = 0, 1; rows g + 8: c = 2, 3)
         float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -248,13 +368,14 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
             const int row = (mi & 1) * 8 + lr;
             const int ch = 2 * d + (mi >> 1);
             uint32_t b[4];
-            ldmatrix_x4_trans(b, v_tile + row * (HD * 2) + ((ch ^ (row & SWZ)) * 16));
+            ldmatrix_x4_trans(b, chunk_addr(v_tile, row, ch));
             mma_bf16_16816(o[2 * d], pa, b[0], b[1]);
             mma_bf16_16816(o[2 * d + 1], pa, b[2], b[3]);
         }
         __syncwarp();       // the stage is refilled by the copies issued in the next iteration
     }
     cp_async_wait<0>();
+    if (timed_out && p.err_flag) atomicExch(p.err_flag, ERR_ATTN_TIMEOUT);   // the result of this group is wrong; the host reads the flag
     __syncwarp();
 
     // ---- merge the warps of the CTA
@@ -318,14 +439,28 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const A
                 const int ti = row / p.hpg, hi = row % p.hpg;
                 const int h_in_kv = hb * p.hpg + hi;
                 if (!(ti < n_tok && ti < p.tpg && h_in_kv < n_rep)) continue;
+                // all remote loads first (they are independent), then the arithmetic
+                float pm[16], pl[16], po[16];
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    if (c < n) {
+                        pm[c] = *cluster.map_shared_rank(&sm_cm[row], c);
+                        pl[c] = *cluster.map_shared_rank(&sm_cl[row], c);
+                        po[c] = *cluster.map_shared_rank(&sm_o(1, row, d), c);
+                    } else {
+                        pm[c] = -INFINITY; pl[c] = 0.f; po[c] = 0.f;
+                    }
+                }
                 float M = -INFINITY;
-                for (int c = 0; c < n; ++c) M = fmaxf(M, *cluster.map_shared_rank(&sm_cm[row], c));
+#pragma unroll
+                for (int c = 0; c < 16; ++c) M = fmaxf(M, pm[c]);
                 const float m_use = (M == -INFINITY) ? 0.f : M;
                 float L = 0.f, O = 0.f;
-                for (int c = 0; c < n; ++c) {
-                    const float f = expf(*cluster.map_shared_rank(&sm_cm[row], c) - m_use);
-                    L += *cluster.map_shared_rank(&sm_cl[row], c) * f;
-                    O += *cluster.map_shared_rank(&sm_o(1, row, d), c) * f;
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const float f = expf(pm[c] - m_use);
+                    L += pl[c] * f;
+                    O += po[c] * f;
                 }
                 const size_t th = (size_t)(tok0 + ti) * p.nh + (kvh * n_rep + h_in_kv);
                 p.out[th * HD + d] = __float2bfloat16_rn(O / L);
@@ -364,10 +499,39 @@ __global__ void combine_splits_kernel(const float* __restrict__ part_acc, const 
     }
 }
 
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// The cache layer seen as a matrix [rows = pages * 2 * nkv * page_size, hd]; boxes of box_rows x 64.
+bool make_cache_map(CUtensorMap* map, const void* cache, long long rows, int hd, int box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int HD>
-int launch(const AttnParams& p, int n_groups_bound, bool use_cluster, cudaStream_t stream) {
+int launch(const CUtensorMap& map, const AttnParams& p, int n_groups_bound, bool use_cluster, cudaStream_t stream) {
     dim3 grid(n_groups_bound, p.nkv * p.head_blocks, p.n_splits);
-    constexpr int SMEM = WARPS * 2 * 2 * TILE * HD * 2;   // per warp: two stages of a K and a V tile
+    constexpr int SMEM = WARPS * 2 * 2 * TILE * HD * 2 + 1024;   // per warp: two stages of a K and a V tile; alignment slack
     static bool configured = false;
     if (!configured) {   // more than 48 KB of dynamic shared memory and clusters of more than 8 CTAs are opt-ins
         cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -377,7 +541,7 @@ int launch(const AttnParams& p, int n_groups_bound, bool use_cluster, cudaStream
         configured = true;
     }
     if (!use_cluster) {
-        cudaError_t e = pyre_launch(paged_attention_mma_kernel<HD, false>, dim3(grid), dim3(WARPS * 32), (size_t)SMEM, stream, p);
+        cudaError_t e = pyre_launch(paged_attention_mma_kernel<HD, false>, dim3(grid), dim3(WARPS * 32), (size_t)SMEM, stream, map, p);
         if (e != cudaSuccess) return (int)e;
         return (int)cudaGetLastError();
     }
@@ -395,7 +559,7 @@ int launch(const AttnParams& p, int n_groups_bound, bool use_cluster, cudaStream
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pyre_pdl_enabled() ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, paged_attention_mma_kernel<HD, true>, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, paged_attention_mma_kernel<HD, true>, map, p);
     if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();
 }
@@ -412,7 +576,7 @@ PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* ou
                                       const int* block_table, int bt_stride, const int* cu_seqlens,
                                       const int* positions, int n_tokens, int n_seqs, int nh, int nkv, int hd,
                                       int page_size, int window, float scale, int n_splits, int max_len,
-                                      cudaStream_t stream) {
+                                      long long n_pages, int uniform_len, int* err_flag, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd % 16 || hd < 16 || hd > 128 || nkv <= 0 || nh % nkv || page_size <= 0 || n_splits < 1) return PYRE_ERR_UNSUPPORTED;
     // without scratch the splits merge through a thread-block cluster (at most 16 CTAs)
@@ -429,6 +593,18 @@ PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* ou
     p.positions = positions;
     p.bt_stride = bt_stride; p.n_seqs = n_seqs; p.nh = nh; p.nkv = nkv; p.page_size = page_size;
     p.window = window; p.n_splits = n_splits; p.scale = scale; p.max_len = max_len;
+    p.page_shift = -1;
+    if ((page_size & (page_size - 1)) == 0) { p.page_shift = 0; while ((1 << p.page_shift) < page_size) ++p.page_shift; }
+    // TMA tiles: power-of-two pages, head size a multiple of 64 (the 128-byte swizzle span), aligned base
+    CUtensorMap map;
+    memset(&map, 0, sizeof(map));
+    p.err_flag = err_flag;
+    p.uniform_len = (uniform_len > 0 && (long long)uniform_len * n_seqs == n_tokens) ? uniform_len : 0;
+    p.box_rows = page_size < TILE ? page_size : TILE;
+    p.use_tma = 0;
+    if (p.page_shift >= 0 && hd % 64 == 0 && n_pages > 0 && ((uintptr_t)cache & 127) == 0 &&
+        n_pages * 2 * nkv * page_size < (1ll << 31))
+        p.use_tma = make_cache_map(&map, cache, n_pages * 2 * nkv * page_size, hd, p.box_rows) ? 1 : 0;
     const int n_rep = nh / nkv;
     p.hpg = n_rep < 16 ? n_rep : 16;
     p.tpg = 16 / p.hpg;
@@ -436,14 +612,14 @@ PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* ou
     const int groups_bound = n_tokens / p.tpg + n_seqs;  // sum over entries of ceil(len / tpg) is at most this
     int rc;
     switch (hd) {
-        case 16: rc = launch<16>(p, groups_bound, use_cluster, stream); break;
-        case 32: rc = launch<32>(p, groups_bound, use_cluster, stream); break;
-        case 48: rc = launch<48>(p, groups_bound, use_cluster, stream); break;
-        case 64: rc = launch<64>(p, groups_bound, use_cluster, stream); break;
-        case 80: rc = launch<80>(p, groups_bound, use_cluster, stream); break;
-        case 96: rc = launch<96>(p, groups_bound, use_cluster, stream); break;
-        case 112: rc = launch<112>(p, groups_bound, use_cluster, stream); break;
-        case 128: rc = launch<128>(p, groups_bound, use_cluster, stream); break;
+        case 16: rc = launch<16>(map, p, groups_bound, use_cluster, stream); break;
+        case 32: rc = launch<32>(map, p, groups_bound, use_cluster, stream); break;
+        case 48: rc = launch<48>(map, p, groups_bound, use_cluster, stream); break;
+        case 64: rc = launch<64>(map, p, groups_bound, use_cluster, stream); break;
+        case 80: rc = launch<80>(map, p, groups_bound, use_cluster, stream); break;
+        case 96: rc = launch<96>(map, p, groups_bound, use_cluster, stream); break;
+        case 112: rc = launch<112>(map, p, groups_bound, use_cluster, stream); break;
+        case 128: rc = launch<128>(map, p, groups_bound, use_cluster, stream); break;
         default: return PYRE_ERR_UNSUPPORTED;
     }
     if (rc) return rc;

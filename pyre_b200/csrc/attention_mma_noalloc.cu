@@ -44,5 +44,5 @@ PYRE_API int pyre_paged_attention_mma_noalloc(const void* q, const void* cache, 
         scratch = g_scratch_addr[dev];
     }
     return pyre_paged_attention_mma(q, cache, out, scratch, block_table, bt_stride, cu_seqlens, positions, n_tokens,
-                                    n_seqs, nh, nkv, hd, page_size, window, scale, n_splits, 0, stream);
+                                    n_seqs, nh, nkv, hd, page_size, window, scale, n_splits, 0, 0, 0, nullptr, stream);
 }

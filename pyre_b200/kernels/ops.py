@@ -272,17 +272,19 @@ _SM_COUNT = 148
 
 
 def attention_splits(n_tokens: int, n_seqs: int, n_heads: int, n_kv_heads: int, max_context: int,
-                     window: "int | None") -> int:
+                     window: "int | None", n_groups: "int | None" = None) -> int:
     """How many ways the tensor-core kernel splits each sequence's keys: enough CTAs for
     two per SM, at least two 16-key tiles per split, at most 16 (the splits of a group
     form one thread-block cluster)."""
     n_rep = n_heads // n_kv_heads
     hpg = min(n_rep, 16)
     tpg = 16 // hpg
-    ctas = (n_tokens // tpg + n_seqs) * n_kv_heads * (-(-n_rep // hpg))
+    if n_groups is None:     # one token per entry (decode) when the counts agree, else an upper bound
+        n_groups = n_seqs if n_tokens == n_seqs else n_tokens // tpg + n_seqs
+    ctas = n_groups * n_kv_heads * (-(-n_rep // hpg))
     span = max_context if not window else min(max_context, window + tpg)
     tiles = -(-span // 16) + 1
-    want = max(1, min(-(-2 * _SM_COUNT // max(ctas, 1)), -(-tiles // 2), CLUSTER_MAX_SPLITS))
+    want = max(1, min(2 * _SM_COUNT // max(ctas, 1), -(-tiles // 2), CLUSTER_MAX_SPLITS))
     if want > 8:
         return 16 if want >= 12 else 8
     return int(want)
@@ -292,7 +294,7 @@ def paged_attention_mma(q: torch.Tensor, cache_layer: torch.Tensor, block_table:
                         cu_seqlens: torch.Tensor, positions: torch.Tensor, n_seqs: int, n_heads: int,
                         n_kv_heads: int, head_dim: int, scale: float, window: "int | None" = None,
                         n_splits: int = 1, out: "torch.Tensor | None" = None,
-                        scratch: "torch.Tensor | None" = None, max_len: int = 0) -> torch.Tensor:
+                        scratch: "torch.Tensor | None" = None, max_len: int = 0, uniform_len: int = 0) -> torch.Tensor:
     """bfloat16 attention on the tensor cores over the block table (decode tokens and
     prompt portions alike); ``n_splits`` > 1 splits each sequence's keys over CTAs and needs
     ``T * nh * n_splits * (hd + 2)`` floats of scratch (allocated here if not given)."""
@@ -324,7 +326,8 @@ def paged_attention_mma(q: torch.Tensor, cache_layer: torch.Tensor, block_table:
             raise ValueError(f"scratch must be {need} contiguous floats")
     lib.call("pyre_paged_attention_mma", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(), _ptr(scratch),
              block_table.data_ptr(), block_table.stride(0), cu_seqlens.data_ptr(), positions.data_ptr(), T, n_seqs,
-             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), n_splits, int(max_len), _stream())
+             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), n_splits, int(max_len),
+             cache_layer.shape[0], int(uniform_len), device_error_flag(q.device).data_ptr(), _stream())
     return out
 
 
@@ -374,10 +377,13 @@ def paged_attention_bf16(ctx, q: torch.Tensor, cache_layer: torch.Tensor, block_
     if n_short_seqs:
         n_short = ctx.num_tokens - n_long
         short_ctx = int((ctx.start_pos_host + lens)[~long_mask].max())
-        splits = attention_splits(n_short, n_short_seqs, n_heads, n_kv_heads, short_ctx, window)
+        tpg = max(1, 16 // min(n_heads // n_kv_heads, 16))
+        groups = int((-(-lens[~long_mask] // tpg)).sum())
+        splits = attention_splits(n_short, n_short_seqs, n_heads, n_kv_heads, short_ctx, window, groups)
+        uniform = int(lens[0]) if not n_long and bool((lens == lens[0]).all()) else 0
         paged_attention_mma(q, cache_layer, block_table, ctx.cu_seqlens, ctx.positions, ctx.num_seqs, n_heads,
                             n_kv_heads, head_dim, scale, window, splits, out=out,
-                            max_len=PREFILL_MIN_LEN - 1 if n_long else 0)
+                            max_len=PREFILL_MIN_LEN - 1 if n_long else 0, uniform_len=uniform)
     return out
 
 
@@ -418,7 +424,8 @@ def check_device_errors(device="cuda") -> None:
     code = int(flag.item())
     if code:
         flag.zero_()
-        raise lib.KernelError({2: "a tensor-core GEMM gave up waiting on its pipeline (bounded wait ran out)"}.get(
+        raise lib.KernelError({2: "a tensor-core GEMM gave up waiting on its pipeline (bounded wait ran out)",
+                               3: "the attention kernel gave up waiting for a tile copy (bounded wait ran out)"}.get(
             code, f"a kernel raised error code {code}"))
 
 
