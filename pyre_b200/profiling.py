@@ -44,13 +44,19 @@ def main(argv=None) -> int:
                  cuda_graphs=False)
     rng = np.random.default_rng(0)
     st, cache = eng.stepper, eng.cache
+    # the measured region is bracketed by cudaProfilerStart/Stop: with `ncu --profile-from-start off`
+    # only its kernels are captured
     if args.mode == "prefill":
         for i in range(2):
             cache.begin(i)
+            if i == 1:
+                torch.cuda.synchronize()
+                torch.cuda.profiler.start()
             logits = st.step([StepEntry(i, rng.integers(0, cfg.vocab_size, args.tokens).tolist(), [args.tokens - 1])])
             ops.sample(logits)
             torch.cuda.synchronize()
             print(f"prefill {i}: launches so far {lib.launch_count}", file=sys.stderr)
+        torch.cuda.profiler.stop()
     else:
         reqs = list(range(args.batch))
         for r in reqs:
@@ -59,9 +65,13 @@ def main(argv=None) -> int:
         torch.cuda.synchronize()
         print(f"prompts cached: launches so far {lib.launch_count}", file=sys.stderr)
         for k in range(args.steps):
+            if k == args.steps - 1:
+                torch.cuda.synchronize()
+                torch.cuda.profiler.start()
             logits = st.step([StepEntry(r, [int(rng.integers(0, cfg.vocab_size))], [0]) for r in reqs])
             ops.sample(logits)
         torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
         print(f"decoded {args.steps} steps: launches so far {lib.launch_count}", file=sys.stderr)
     return 0
 
