@@ -22,6 +22,9 @@
 //   warps 2..5         : epilogue.  tcgen05.ld (32 lanes x 32 bit, 16 columns at a time)
 //                        reads the warp's quarter of the 128 accumulator rows and stores
 //                        it, converted if asked.
+// The CTA is persistent (one per SM, walking tiles c, c + gridDim.x, ...) and holds TWO
+// accumulators in tensor memory: while the epilogue warps drain tile i, the MMA thread is
+// already multiplying tile i + 1 into the other one, and the TMA ring never stops.
 // Rows or K beyond the matrices are zero-filled by TMA, so any x_rows, y_rows and K work
 // (K and the leading dimensions must be multiples of 8 elements: TMA strides are 16-byte
 // multiples).  No load uses cluster multicast.
@@ -104,6 +107,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 struct GemmParams {
     int x_rows, y_rows, K;
     int k_blocks_per_split;       // K blocks (of 64) per blockIdx.z
+    int tiles_x, tiles_y;         // output tiles; CTA c works on tiles c, c + gridDim.x, ... (x fastest)
     long long stride_x, stride_y, split_stride;  // output element strides
     void* out;
     int out_f32;
@@ -117,9 +121,13 @@ struct SmemLayout {
     static constexpr int Y_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = X_BYTES + Y_BYTES;
     static constexpr int TILES = STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = TILES + (2 * STAGES + 1) * 8 + 16 + 1024;  // + barriers, tmem slot, alignment slack
+    static constexpr int N_BARS = 2 * STAGES + 4;     // full, empty per stage; accumulator full, empty per TMEM buffer
+    static constexpr int TOTAL = TILES + N_BARS * 8 + 16 + 1024;  // + tmem slot and abort flag, alignment slack
 };
 
+// A CTA is persistent: it walks output tiles c, c + gridDim.x, ...  Two TMEM accumulators
+// alternate, so the epilogue warps drain tile i while the MMA thread already works on tile
+// i + 1; the shared-memory ring runs on across tiles.
 template <int BN, int STAGES, bool X_CONTIGUOUS_OUT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const GemmParams p) {
@@ -129,17 +137,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t bar_full = base + L::TILES;
     const uint32_t bar_empty = bar_full + STAGES * 8;
-    const uint32_t bar_accum = bar_empty + STAGES * 8;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::TILES + (2 * STAGES + 1) * 8);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::TILES + (2 * STAGES + 1) * 8 + 8);
+    const uint32_t bar_acc_full = bar_empty + STAGES * 8;     // [2]
+    const uint32_t bar_acc_empty = bar_acc_full + 16;         // [2]
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::TILES + L::N_BARS * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::TILES + L::N_BARS * 8 + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int x0 = blockIdx.x * BM, y0 = blockIdx.y * BN;
     const int total_kb = (p.K + BK - 1) / BK;
     const int kb_begin = blockIdx.z * p.k_blocks_per_split;
     const int kb_end = min(kb_begin + p.k_blocks_per_split, total_kb);
     const int n_kb = max(kb_end - kb_begin, 0);
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;   // power of two >= 32
+    const int n_tiles = p.tiles_x * p.tiles_y;
+    constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;    // columns of one accumulator
+    constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;        // power of two >= 32, at most 512
 
     pdl_trigger();
     if (threadIdx.x == 0) {
@@ -148,7 +158,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
-        mbar_init(bar_accum, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_acc_full + 8 * b, 1);
+            mbar_init(bar_acc_empty + 8 * b, 4);      // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -165,33 +178,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             // ---------------- producer
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_x)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_y)) : "memory");
-            // The weights do not depend on the kernels before this one: fill the ring with
-            // their tiles first, then wait for those kernels, then fetch the activations.
-            const int pre = n_kb < STAGES ? n_kb : STAGES;
-            for (int i = 0; i < pre; ++i) {
-                mbar_expect_tx(bar_full + 8 * i, L::STAGE_BYTES);
-                const uint32_t xs = base + i * L::STAGE_BYTES, ys = xs + L::X_BYTES;
-                const int k = (kb_begin + i) * BK;
-                if (p.x_is_constant) tma_load_2d(xs, &map_x, bar_full + 8 * i, k, x0);
-                else tma_load_2d(ys, &map_y, bar_full + 8 * i, k, y0);
+            int it = 0;   // K blocks issued so far, over all tiles of this CTA
+            bool waited = false;
+            for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
+                const int x0 = (tile % p.tiles_x) * BM, y0 = (tile / p.tiles_x) * BN;
+                int i = 0;
+                if (!waited) {
+                    // The weights do not depend on the kernels before this one: fill the ring with
+                    // their tiles first, then wait for those kernels, then fetch the activations.
+                    const int pre = n_kb < STAGES ? n_kb : STAGES;
+                    for (int j = 0; j < pre; ++j) {
+                        mbar_expect_tx(bar_full + 8 * j, L::STAGE_BYTES);
+                        const uint32_t xs = base + j * L::STAGE_BYTES, ys = xs + L::X_BYTES;
+                        const int k = (kb_begin + j) * BK;
+                        if (p.x_is_constant) tma_load_2d(xs, &map_x, bar_full + 8 * j, k, x0);
+                        else tma_load_2d(ys, &map_y, bar_full + 8 * j, k, y0);
+                    }
+                    pdl_wait();
+                    waited = true;
+                    for (int j = 0; j < pre; ++j) {
+                        const uint32_t xs = base + j * L::STAGE_BYTES, ys = xs + L::X_BYTES;
+                        const int k = (kb_begin + j) * BK;
+                        if (p.x_is_constant) tma_load_2d(ys, &map_y, bar_full + 8 * j, k, y0);
+                        else tma_load_2d(xs, &map_x, bar_full + 8 * j, k, x0);
+                    }
+                    i = pre;
+                    it = pre;
+                }
+                bool ok = true;
+                for (; i < n_kb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t phase = (it / STAGES) & 1;
+                    ok = mbar_wait(bar_empty + 8 * s, phase ^ 1, abort_flag, p.err_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(bar_full + 8 * s, L::STAGE_BYTES);
+                    const uint32_t xs = base + s * L::STAGE_BYTES, ys = xs + L::X_BYTES;
+                    const int k = (kb_begin + i) * BK;
+                    tma_load_2d(xs, &map_x, bar_full + 8 * s, k, x0);
+                    tma_load_2d(ys, &map_y, bar_full + 8 * s, k, y0);
+                }
+                if (!ok) break;
             }
-            pdl_wait();
-            for (int i = 0; i < pre; ++i) {
-                const uint32_t xs = base + i * L::STAGE_BYTES, ys = xs + L::X_BYTES;
-                const int k = (kb_begin + i) * BK;
-                if (p.x_is_constant) tma_load_2d(ys, &map_y, bar_full + 8 * i, k, y0);
-                else tma_load_2d(xs, &map_x, bar_full + 8 * i, k, x0);
-            }
-            for (int i = pre; i < n_kb; ++i) {
-                const int s = i % STAGES;
-                const uint32_t phase = (i / STAGES) & 1;
-                if (!mbar_wait(bar_empty + 8 * s, phase ^ 1, abort_flag, p.err_flag)) break;
-                mbar_expect_tx(bar_full + 8 * s, L::STAGE_BYTES);
-                const uint32_t xs = base + s * L::STAGE_BYTES, ys = xs + L::X_BYTES;
-                const int k = (kb_begin + i) * BK;
-                tma_load_2d(xs, &map_x, bar_full + 8 * s, k, x0);
-                tma_load_2d(ys, &map_y, bar_full + 8 * s, k, y0);
-            }
+            if (!waited) pdl_wait();
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -199,85 +227,106 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             // instruction descriptor: D fp32 (bit 4), A and B bf16 (bits 7, 10), both K-major,
             // N >> 3 at bit 17, M >> 4 at bit 24
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            int it = 0, j = 0;
             bool ok = true;
-            for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % STAGES;
-                const uint32_t phase = (i / STAGES) & 1;
-                ok = mbar_wait(bar_full + 8 * s, phase, abort_flag, p.err_flag);
+            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++j) {
+                const int buf = j & 1;
+                // the epilogue must have drained this accumulator (two tiles ago)
+                ok = mbar_wait(bar_acc_empty + 8 * buf, ((j >> 1) & 1) ^ 1, abort_flag, p.err_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t xs = base + s * L::STAGE_BYTES, ys = xs + L::X_BYTES;
-                const uint64_t da = umma_desc(xs), db = umma_desc(ys);
+                const uint32_t acc = tmem_base + buf * ACC_COLS;
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t phase = (it / STAGES) & 1;
+                    ok = mbar_wait(bar_full + 8 * s, phase, abort_flag, p.err_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t xs = base + s * L::STAGE_BYTES, ys = xs + L::X_BYTES;
+                    const uint64_t da = umma_desc(xs), db = umma_desc(ys);
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k)   // 16 bf16 = 32 bytes = 2 descriptor units along K
-                    umma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-                umma_commit(bar_empty + 8 * s);     // the stage is free once these MMAs have read it
+                    for (int k = 0; k < BK / 16; ++k)   // 16 bf16 = 32 bytes = 2 descriptor units along K
+                        umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(bar_empty + 8 * s);     // the stage is free once these MMAs have read it
+                }
+                umma_commit(bar_acc_full + 8 * buf);    // this tile's accumulator is complete (also signalled on abort)
             }
-            umma_commit(bar_accum);                 // the accumulator is complete
         }
     } else {
         // ---------------- epilogue: warp w reads TMEM lanes 32 (w % 4) .. + 31
         const int quarter = warp & 3;
-        const int xr = x0 + quarter * 32 + lane;
-        bool ok = true;
-        if (n_kb > 0) ok = mbar_wait(bar_accum, 0, abort_flag, p.err_flag);
-        else pdl_wait();   // nothing orders this store after the earlier kernels otherwise
-        ok = ok && !*abort_flag;   // the issuer signals the accumulator even when it gave up
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const long long out_base = (long long)blockIdx.z * p.split_stride + (long long)xr * p.stride_x;
+        int j = 0;
+        bool alive = true;
+        if (n_kb == 0) pdl_wait();   // nothing orders the zero stores after the earlier kernels otherwise
+        for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++j) {
+            const int buf = j & 1;
+            const int x0 = (tile % p.tiles_x) * BM, y0 = (tile / p.tiles_x) * BN;
+            const int xr = x0 + quarter * 32 + lane;
+            bool ok = true;
+            if (n_kb > 0) ok = mbar_wait(bar_acc_full + 8 * buf, (j >> 1) & 1, abort_flag, p.err_flag);
+            ok = ok && !*abort_flag;   // the issuer signals the accumulator even when it gave up
+            alive = __all_sync(0xffffffffu, ok);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const long long out_base = (long long)blockIdx.z * p.split_stride + (long long)xr * p.stride_x;
+            const uint32_t acc = tmem_base + buf * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 16) {
-            uint32_t r[16];
-            __syncwarp();   // tcgen05.ld is warp-wide: converge after the per-thread stores
-            if (n_kb > 0) {
-                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + c, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            } else {
+            for (int c = 0; c < BN; c += 16) {
+                uint32_t r[16];
+                __syncwarp();   // tcgen05.ld is warp-wide: converge after the per-thread stores
+                if (n_kb > 0) {
+                    tmem_ld16(acc + c, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) r[j] = 0u;
-            }
-            if (!ok || xr >= p.x_rows) {
-                // nothing to store for this thread
-            } else if constexpr (!X_CONTIGUOUS_OUT) {
-                // a thread owns a row of the output: 16 consecutive elements (stride_y == 1)
-                const int yc = y0 + c;
-                if (yc + 16 <= p.y_rows) {
-                    if (p.out_f32) {
-                        float4* dst = reinterpret_cast<float4*>((float*)p.out + out_base + yc);
+                    for (int q = 0; q < 16; ++q) r[q] = 0u;
+                }
+                if (!alive || xr >= p.x_rows) {
+                    // nothing to store for this thread
+                } else if constexpr (!X_CONTIGUOUS_OUT) {
+                    // a thread owns a row of the output: 16 consecutive elements (stride_y == 1)
+                    const int yc = y0 + c;
+                    if (yc + 16 <= p.y_rows) {
+                        if (p.out_f32) {
+                            float4* dst = reinterpret_cast<float4*>((float*)p.out + out_base + yc);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            dst[j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                    } else {
-                        uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)p.out + out_base + yc);
-                        uint32_t w[8];
+                            for (int q = 0; q < 4; ++q)
+                                dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                     __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                        } else {
+                            uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)p.out + out_base + yc);
+                            uint32_t w[8];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-                            w[j] = *reinterpret_cast<uint32_t*>(&v);
+                            for (int q = 0; q < 8; ++q) {
+                                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * q]), __uint_as_float(r[2 * q + 1]));
+                                w[q] = *reinterpret_cast<uint32_t*>(&v);
+                            }
+                            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
                         }
-                        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    } else {
+                        for (int q = 0; q < 16 && yc + q < p.y_rows; ++q) {
+                            const float v = __uint_as_float(r[q]);
+                            if (p.out_f32) ((float*)p.out)[out_base + yc + q] = v;
+                            else ((__nv_bfloat16*)p.out)[out_base + yc + q] = __float2bfloat16_rn(v);
+                        }
                     }
                 } else {
-                    for (int j = 0; j < 16 && yc + j < p.y_rows; ++j) {
-                        const float v = __uint_as_float(r[j]);
-                        if (p.out_f32) ((float*)p.out)[out_base + yc + j] = v;
-                        else ((__nv_bfloat16*)p.out)[out_base + yc + j] = __float2bfloat16_rn(v);
-                    }
-                }
-            } else {
-                // transposed store: for each y the 32 lanes write 32 consecutive x (stride_x == 1)
+                    // transposed store: for each y the 32 lanes write 32 consecutive x (stride_x == 1)
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int y = y0 + c + j;
-                    if (y < p.y_rows) {
-                        const float v = __uint_as_float(r[j]);
-                        if (p.out_f32) ((float*)p.out)[out_base + (long long)y * p.stride_y] = v;
-                        else ((__nv_bfloat16*)p.out)[out_base + (long long)y * p.stride_y] = __float2bfloat16_rn(v);
+                    for (int q = 0; q < 16; ++q) {
+                        const int y = y0 + c + q;
+                        if (y < p.y_rows) {
+                            const float v = __uint_as_float(r[q]);
+                            if (p.out_f32) ((float*)p.out)[out_base + (long long)y * p.stride_y] = v;
+                            else ((__nv_bfloat16*)p.out)[out_base + (long long)y * p.stride_y] = __float2bfloat16_rn(v);
+                        }
                     }
                 }
             }
+            // this warp has read its quarter of the accumulator: hand the buffer back to the MMA thread
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
         }
     }
 
@@ -365,7 +414,12 @@ PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* 
     p.k_blocks_per_split = (total_kb + splits - 1) / splits;
     p.stride_x = stride_x; p.stride_y = stride_y; p.split_stride = split_stride;
     p.out = out; p.out_f32 = out_f32; p.x_is_constant = x_is_constant; p.err_flag = err_flag;
-    dim3 grid(ceil_div(x_rows, BM), ceil_div(y_rows, bn), splits);
+    p.tiles_x = ceil_div(x_rows, BM); p.tiles_y = ceil_div(y_rows, bn);
+    const long long n_tiles = (long long)p.tiles_x * p.tiles_y;
+    // one CTA per SM stays resident and walks the tiles (a split K keeps one CTA per tile and split)
+    static int sm_count = 0;
+    if (!sm_count) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev); if (sm_count <= 0) sm_count = 148; }
+    dim3 grid((unsigned)(splits > 1 ? n_tiles : (n_tiles < sm_count ? n_tiles : sm_count)), 1, splits);
 #define GO(BN_, ST_)                                                              \
     rc = xc ? launch<BN_, ST_, true>(mx, my, p, grid, stream) : launch<BN_, ST_, false>(mx, my, p, grid, stream)
     switch (bn) {
