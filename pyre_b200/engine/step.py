@@ -122,6 +122,7 @@ class Stepper:
         seen = set()
         vocab = self.model.vocab_size
         starts, counts = [], []
+        tok_list: list[int] = []
         for e in entries:
             if e.request in seen:
                 raise ValueError(f"request {e.request!r} appears twice in one step")
@@ -129,9 +130,14 @@ class Stepper:
             n = len(e.tokens)
             if n == 0:
                 raise ValueError(f"request {e.request!r}: an entry needs at least one token")
-            toks = np.asarray(e.tokens)
-            if toks.min() < 0 or toks.max() >= vocab:
-                raise ValueError(f"request {e.request!r}: token id outside [0, {vocab})")
+            if n <= 8:      # a decoded token or a tiny portion: plain integers are cheaper than an array
+                if min(e.tokens) < 0 or max(e.tokens) >= vocab:
+                    raise ValueError(f"request {e.request!r}: token id outside [0, {vocab})")
+            else:
+                toks = np.asarray(e.tokens)
+                if toks.min() < 0 or toks.max() >= vocab:
+                    raise ValueError(f"request {e.request!r}: token id outside [0, {vocab})")
+            tok_list.extend(e.tokens)
             for w in e.want:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.request!r}: wanted place {w} outside its {n} tokens")
@@ -142,30 +148,42 @@ class Stepper:
             starts.append(start)
             counts.append(n)
         if reserve:
-            taken = []
             for e, s, n in zip(entries, starts, counts):
                 if not cache.reserve(e.request, s + n):
                     # nothing of this step stays half-reserved in a way that matters: pages
                     # taken for earlier entries remain theirs and are used by a later step
                     raise OutOfPages(f"request {e.request!r}: no pages left to grow from {s} to {s + n} tokens "
                                      f"(free pages per group: {cache.stats().pages_free})")
-                taken.append(e.request)
 
         B = len(entries)
-        T = int(sum(counts))
+        T = len(tok_list)
         cu = np.zeros(B + 1, dtype=np.int32)
-        cu[1:] = np.cumsum(counts)
-        token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
-        positions = np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(starts, counts)])
-        seq_of_token = np.repeat(np.arange(B, dtype=np.int32), counts)
-        rows = [cu[b] + w for b, e in enumerate(entries) for w in e.want]
+        np.cumsum(counts, out=cu[1:])
+        token_ids = np.asarray(tok_list, dtype=np.int32)
+        if T == B:      # one token per entry
+            positions = np.asarray(starts, dtype=np.int32)
+            seq_of_token = np.arange(B, dtype=np.int32)
+        else:
+            positions = np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(starts, counts)])
+            seq_of_token = np.repeat(np.arange(B, dtype=np.int32), counts)
+        rows = [int(cu[b]) + w for b, e in enumerate(entries) for w in e.want]
         logit_rows = np.asarray(rows, dtype=np.int32)
         reqs = [e.request for e in entries]
 
         pieces = [token_ids, positions, seq_of_token, cu, logit_rows]
         tables = []
-        for g in range(len(cache.groups)):
-            slots = np.concatenate([cache.slots_for(g, e.request, s, n) for e, s, n in zip(entries, starts, counts)])
+        ps = cache.page_size
+        for g, group in enumerate(cache.groups):
+            if T == B:
+                slot_list = []
+                for r, s_ in zip(reqs, starts):
+                    page = group.tables[r][s_ // ps]
+                    if page < 0:
+                        raise RuntimeError(f"request {r!r}: a token would be written to a page already given back")
+                    slot_list.append(page * ps + s_ % ps)
+                slots = np.asarray(slot_list, dtype=np.int32)
+            else:
+                slots = np.concatenate([cache.slots_for(g, e.request, s_, n) for e, s_, n in zip(entries, starts, counts)])
             table = cache.block_table_rows(g, reqs, table_width)
             tables.append(table.shape)
             pieces += [slots, table.reshape(-1)]
