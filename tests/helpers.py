@@ -27,7 +27,7 @@ TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
 PAGE_SIZE = {"A": 16, "B": 8, "C": 32}
 
 
-def make_model_dir(path: Path, raw_cfg: dict, seed: int, sharpen: float = 6.0) -> dict[str, torch.Tensor]:
+def make_model_dir(path: Path, raw_cfg: dict, seed: int, sharpen: float = 6.0, matrix_scale: float = 2.5) -> dict[str, torch.Tensor]:
     """Write config.json + model.safetensors (fp32) with the package's random mode, then
     scale the query and key projections so that attention is peaked: with N(0, 0.02)
     weights every score is near zero and a wrong key would change nothing.  Returns the
@@ -42,7 +42,7 @@ def make_model_dir(path: Path, raw_cfg: dict, seed: int, sharpen: float = 6.0) -
         if name.endswith(("q_proj.weight", "k_proj.weight", "q_proj.bias", "k_proj.bias")):
             state[name] = state[name] * sharpen
         elif state[name].dim() == 2:
-            state[name] = state[name] * 2.5
+            state[name] = state[name] * matrix_scale
     (path / "config.json").write_text(json.dumps(raw_cfg))
     save_file({k: v.contiguous() for k, v in state.items()}, str(path / "model.safetensors"))
     return state
