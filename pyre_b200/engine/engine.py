@@ -60,10 +60,12 @@ class Engine:
                 self.model.load_weights(model)
             else:
                 self.model.init_random(int(seed or 0))
-        max_positions = spec.max_positions or (1 << 30)
+        # max_position_embeddings is a default for the longest sequence, not a hard limit (the
+        # reference never enforces it); ``max_model_len`` in the engine configuration overrides it
+        max_positions = spec.max_positions or (1 << 20)
         default_tokens = min(max_positions, 8192) * min(ec.max_num_seqs, 8)
         num_pages = ec.resolve_num_pages(default_tokens)
-        self.max_model_len = min(ec.max_model_len or max_positions, max_positions, num_pages * ec.page_size)
+        self.max_model_len = min(ec.max_model_len or max_positions, num_pages * ec.page_size)
         self.cache = CacheManager(self.model.kv_groups, self.model.state_groups, ec.page_size, num_pages,
                                   ec.max_num_seqs, ec.dtype, ec.device)
         self.cache.set_poison(ec.debug_poison_freed_pages)

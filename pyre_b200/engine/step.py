@@ -22,6 +22,11 @@ from ..models.model import Model
 from .context import KVView, StateView, StepContext
 
 
+# The model's ``max_position_embeddings`` is not enforced here: the reference parses it and never
+# uses it (pyre/config.py:60), and rotary angles are computed from the position itself.
+MAX_EXACT_POSITION = 1 << 24
+
+
 @dataclass
 class StepEntry:
     """The next tokens of one live request and the places among them whose logits are wanted."""
@@ -142,9 +147,9 @@ class Stepper:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.request!r}: wanted place {w} outside its {n} tokens")
             start = cache.length(e.request)
-            if self.max_positions is not None and start + n > self.max_positions:
-                raise ValueError(f"request {e.request!r}: {start + n} tokens exceed the model's "
-                                 f"{self.max_positions} positions")
+            if start + n > MAX_EXACT_POSITION:
+                raise ValueError(f"request {e.request!r}: position {start + n} is beyond {MAX_EXACT_POSITION}, the "
+                                 f"largest that converts to fp32 exactly for the rotary angles")
             starts.append(start)
             counts.append(n)
         if reserve:

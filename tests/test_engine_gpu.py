@@ -161,6 +161,15 @@ def test_first_tokens_of_a_sequence(model_dirs, dtype):
         assert np.abs(got - want).max() <= tol
 
 
+def test_positions_beyond_the_nominal_maximum(model_dirs):
+    """max_position_embeddings (256 for configuration A) is advisory, as in the reference: a
+    longer sequence replays and matches the plain implementation."""
+    d, raw = model_dirs["A"], H.TINY["A"]
+    ids = H.random_ids(raw["vocab_size"], 300, seed=12)
+    got = H.run_trace_in_process(d, "float32", H.trace_portions("x", ids, [128, 1, 60]), 320, 16)["x"]
+    assert np.abs(got - H.plain_logits(d, ids)).max() <= 2e-4
+
+
 def test_command_line_and_trace_run_program(model_dirs, tmp_path):
     """The two programs as a user runs them: bin/pyre_generate and bin/trace_run."""
     d, raw = model_dirs["A"], H.TINY["A"]
