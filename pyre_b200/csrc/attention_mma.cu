@@ -266,6 +266,9 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
     };
     bool timed_out = false;
 
+    const bool upper = __any_sync(0xffffffffu, row_ok[1]);   // does any lane own a valid row among rows 8..15?
+    const float sl2 = p.scale * 1.44269504088896341f;        // log2(e): maxima and scores live in base 2
+
     int kt = tile_begin + warp;
     if (kt < tile_end) {
         if (!tma) load_tile(kt, 0);
@@ -325,40 +328,51 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) { s[0][c] += s2[0][c]; s[1][c] += s2[1][c]; }
-        // ---- mask, scale, online softmax (rows g: c = 0, 1; rows g + 8: c = 2, 3)
+        // ---- mask, scale, online softmax (rows g: c = 0, 1; rows g + 8: c = 2, 3).  Scores are kept
+        // in units of log2(e) so that exp2f serves; when no lane has a valid row among the upper
+        // eight (a decode token of a model with at most 8 query heads per key/value head) that
+        // half is skipped, and the accumulator is rescaled only when some row's maximum moved.
         float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
         for (int i = 0; i < 2; ++i)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const int r = c >> 1;
+                if (r == 1 && !upper) { s[i][c] = 0.f; continue; }
                 const int key = key0 + 8 * i + 2 * t + (c & 1);
                 const bool ok = row_ok[r] && key <= row_pos[r] && key >= row_lo[r];
-                s[i][c] = ok ? s[i][c] * p.scale : -INFINITY;
+                s[i][c] = ok ? s[i][c] * sl2 : -INFINITY;
                 tile_max[r] = fmaxf(tile_max[r], s[i][c]);
             }
-        float alpha[2];
+        float alpha[2] = {1.f, 1.f};
+        bool moved = false;
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
+            if (r == 1 && !upper) continue;
             tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 1));
             tile_max[r] = fmaxf(tile_max[r], __shfl_xor_sync(0xffffffffu, tile_max[r], 2));
             const float m_new = fmaxf(m_run[r], tile_max[r]);
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            alpha[r] = expf(m_run[r] - m_use);
+            if (m_new != m_run[r]) {
+                alpha[r] = exp2f(m_run[r] - m_use);
+                moved = true;
+            }
             m_run[r] = m_new;
             float sum = 0.f;
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                s[i][2 * r] = expf(s[i][2 * r] - m_use);
-                s[i][2 * r + 1] = expf(s[i][2 * r + 1] - m_use);
+                s[i][2 * r] = exp2f(s[i][2 * r] - m_use);
+                s[i][2 * r + 1] = exp2f(s[i][2 * r + 1] - m_use);
                 sum += s[i][2 * r] + s[i][2 * r + 1];
             }
             l_run[r] = l_run[r] * alpha[r] + sum;  // this lane's share; the quad is summed at the end
         }
+        if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
-        for (int i = 0; i < NT_O; ++i) {
-            o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-            o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+            for (int i = 0; i < NT_O; ++i) {
+                o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+                o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+            }
         }
         // ---- O += P V: matrices read transposed, (keys 0..7 | 8..15) x (dims 16d + 0..7 | 8..15)
         const uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
@@ -408,7 +422,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
         float L = 0.f, O = 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
-            const float f = expf(sm_m[w][row] - m_use);
+            const float f = exp2f(sm_m[w][row] - m_use);
             L += sm_l[w][row] * f;
             O += sm_o(w, row, d) * f;
         }
@@ -458,7 +472,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
                 float L = 0.f, O = 0.f;
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
-                    const float f = expf(pm[c] - m_use);
+                    const float f = exp2f(pm[c] - m_use);
                     L += pl[c] * f;
                     O += po[c] * f;
                 }
@@ -470,7 +484,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
     }
 }
 
-// out[t, h, :] = sum_s acc_s exp(m_s - M) / sum_s l_s exp(m_s - M)
+// out[t, h, :] = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)   (maxima are kept in base 2)
 __global__ void combine_splits_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                       __nv_bfloat16* __restrict__ out, int n_splits, int hd, int nh,
                                       const int* __restrict__ cu_seqlens, int n_seqs, int max_len) {
@@ -491,10 +505,10 @@ __global__ void combine_splits_kernel(const float* __restrict__ part_acc, const 
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
     const float m_use = (M == -INFINITY) ? 0.f : M;
     float L = 0.f;
-    for (int s = 0; s < n_splits; ++s) L += ml[2 * s + 1] * expf(ml[2 * s] - m_use);
+    for (int s = 0; s < n_splits; ++s) L += ml[2 * s + 1] * exp2f(ml[2 * s] - m_use);
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float O = 0.f;
-        for (int s = 0; s < n_splits; ++s) O += part_acc[(th * n_splits + s) * hd + d] * expf(ml[2 * s] - m_use);
+        for (int s = 0; s < n_splits; ++s) O += part_acc[(th * n_splits + s) * hd + d] * exp2f(ml[2 * s] - m_use);
         out[th * hd + d] = __float2bfloat16_rn(O / L);
     }
 }
