@@ -72,7 +72,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
@@ -262,6 +262,90 @@ def run_ours(args) -> dict:
     }
 
 
+SHAPES = {
+    # BASELINE.json configs[3] and configs[4]
+    "14b": dict(architectures=["Qwen2ForCausalLM"], hidden_size=5120, intermediate_size=13824, num_hidden_layers=48,
+                num_attention_heads=40, num_key_value_heads=8, head_dim=128, vocab_size=152064, rope_theta=1e6,
+                rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=32768),
+    "32b": dict(architectures=["Qwen2ForCausalLM"], hidden_size=5120, intermediate_size=27648, num_hidden_layers=64,
+                num_attention_heads=40, num_key_value_heads=8, head_dim=128, vocab_size=152064, rope_theta=1e6,
+                rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=32768),
+}
+
+
+def run_workload(args) -> dict:
+    """The two other workloads of the baseline description, outside the one-line contract:
+    ``serve14b``: continuous batching of 64 requests (prompts uniform in 128-4096 tokens, outputs
+    uniform in 64-512) on the 14B shape through Engine.generate;
+    ``mixed32b``: steps of 16 decoded tokens plus a 1,024-token prompt portion at contexts up
+    to 8,192 on the 32B shape."""
+    import numpy as np
+    import torch
+
+    from pyre_b200 import Engine, SamplingParams
+    from pyre_b200.config import config_from_dict
+    from pyre_b200.engine.step import StepEntry
+    from pyre_b200.kernels import ops
+
+    rng = np.random.default_rng(1)
+    if args.workload == "serve14b":
+        raw = dict(SHAPES["14b"])
+        if args.layers:
+            raw["num_hidden_layers"] = args.layers
+        cfg = config_from_dict(raw)
+        n_req = 64
+        prompts = [rng.integers(0, cfg.vocab_size, int(rng.integers(128, 4097))).tolist() for _ in range(n_req)]
+        outs_len = [int(rng.integers(64, 513)) for _ in range(n_req)]
+        need = sum(len(p) + o for p, o in zip(prompts, outs_len))
+        eng = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=int(need * args.cache_fraction),
+                     max_num_seqs=64, max_num_batched_tokens=4096, prefill_chunk=2048, max_model_len=8192)
+        params = [SamplingParams(max_new_tokens=o, ignore_eos=True) for o in outs_len]
+        eng.generate(prompts[:2], params[:2])       # warm-up: builds, graphs of small shapes
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        res = eng.generate(prompts, params)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        st = eng.stats()
+        eng.cache.check()
+        n_out = sum(len(r.token_ids) for r in res)
+        n_in = sum(len(p) for p in prompts)
+        return {"workload": "serve14b", "layers": cfg.num_hidden_layers, "requests": n_req, "prompt_tokens": n_in,
+                "output_tokens": n_out, "seconds": round(dt, 3), "output_tok_s": round(n_out / dt, 1),
+                "total_tok_s": round((n_in + n_out) / dt, 1), "steps": st["steps"], "preempted": st["preempted"],
+                "cache_tokens": int(need * args.cache_fraction), "finished": sum(r.finish_reason == "length" for r in res)}
+    raw = dict(SHAPES["32b"])
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    cfg = config_from_dict(raw)
+    n_dec, chunk, ctx = 16, 1024, 8192
+    eng = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=(n_dec + 1) * (ctx + 64),
+                 max_num_seqs=n_dec + 1, max_num_batched_tokens=4096, prefill_chunk=4096, max_model_len=ctx + 64)
+    st, cache = eng.stepper, eng.cache
+    reqs = list(range(n_dec))
+    for r in reqs:                              # decoding requests at contexts between 2,048 and 8,000
+        cache.begin(r)
+        n = int(rng.integers(2048, ctx - 200))
+        for lo in range(0, n, 4096):
+            st.step([StepEntry(r, rng.integers(0, cfg.vocab_size, min(4096, n - lo)).tolist(), [])])
+    cache.begin("p")
+    times = []
+    for k in range(ctx // chunk - 1):           # the prompt grows by 1,024 tokens per step beside 16 decoded tokens
+        entries = [StepEntry(r, [int(rng.integers(0, cfg.vocab_size))], [0]) for r in reqs]
+        entries.append(StepEntry("p", rng.integers(0, cfg.vocab_size, chunk).tolist(), [chunk - 1]))
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        ops.sample(st.step(entries))
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    cache.check()
+    ms = sorted(times[1:])[len(times[1:]) // 2]
+    return {"workload": "mixed32b", "layers": cfg.num_hidden_layers, "tokens_per_step": n_dec + chunk,
+            "ms_per_step_median": round(ms, 2), "tok_s": round((n_dec + chunk) / ms * 1e3, 1),
+            "ms_first_last": [round(times[1], 2), round(times[-1], 2)]}
+
+
 def run_reference(args) -> dict:
     from baseline import reference_arm
     return reference_arm.run(args, CONFIG_7B, PROMPT_LEN)
@@ -277,10 +361,17 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")
     ap.add_argument("--prefill-reps", type=int, default=5)
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
+    ap.add_argument("--workload", choices=["serve14b", "mixed32b"], default=None,
+                    help="run one of the two other baseline workloads instead (prints its own JSON line)")
+    ap.add_argument("--cache-fraction", type=float, default=1.0,
+                    help="serve14b: cache capacity as a fraction of what all requests need at once (< 1 forces preemption)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
         return 2
+    if args.workload:
+        print(json.dumps(run_workload(args)))
+        return 0
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
     return 0
