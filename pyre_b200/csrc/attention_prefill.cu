@@ -182,44 +182,59 @@ __global__ void __launch_bounds__(WARPS * 32, 3) attention_prefill_kernel(const 
                     mma_bf16_16816(s[2 * n + 1], qa[k], b[n][2], b[n][3]);
                 }
             }
-            // ---- scale, mask (only tiles that touch a row's limits), online softmax
+            // ---- mask (only tiles that touch a row's limits), online softmax.  The maximum is taken
+            // on the raw scores (the scale is positive) in four independent chains; the scale and
+            // the maximum enter the exponent through one fused multiply-add; the accumulator is
+            // rescaled only when some row's maximum moved.
             const bool need_mask = key0 + BN - 1 > warp_pos_lo || (p.window > 0 && key0 < warp_key_lo + 15) || !ok0 || !ok1;
-            float tmax[2] = {-INFINITY, -INFINITY};
+            if (need_mask) {
 #pragma unroll
-            for (int i = 0; i < BN / 8; ++i)
+                for (int i = 0; i < BN / 8; ++i)
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    float v = s[i][c] * sl2;
-                    if (need_mask) {
+                    for (int c = 0; c < 4; ++c) {
                         const int key = key0 + 8 * i + 2 * t + (c & 1);
                         const bool okk = (c < 2) ? (ok0 && key <= pos0 && key >= lo0) : (ok1 && key <= pos1 && key >= lo1);
-                        v = okk ? v : -INFINITY;
+                        s[i][c] = okk ? s[i][c] : -INFINITY;
                     }
-                    s[i][c] = v;
-                    tmax[c >> 1] = fmaxf(tmax[c >> 1], v);
-                }
-            float alpha[2];
+            }
+            float tm[2][4];
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) tm[r][q] = fmaxf(s[q][2 * r], s[q][2 * r + 1]);
+#pragma unroll
+            for (int i = 4; i < BN / 8; ++i)
+#pragma unroll
+                for (int r = 0; r < 2; ++r) tm[r][i & 3] = fmaxf(tm[r][i & 3], fmaxf(s[i][2 * r], s[i][2 * r + 1]));
+            float alpha[2] = {1.f, 1.f};
+            bool moved = false;
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 1));
-                tmax[r] = fmaxf(tmax[r], __shfl_xor_sync(0xffffffffu, tmax[r], 2));
-                const float m_new = fmaxf(m_run[r], tmax[r]);
+                float tmax = fmaxf(fmaxf(tm[r][0], tm[r][1]), fmaxf(tm[r][2], tm[r][3])) * sl2;   // base-2 units
+                tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+                tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+                const float m_new = fmaxf(m_run[r], tmax);
                 const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-                alpha[r] = exp2f(m_run[r] - m_use);
+                if (m_new != m_run[r]) {
+                    alpha[r] = exp2f(m_run[r] - m_use);
+                    moved = true;
+                }
                 m_run[r] = m_new;
-                float sum = 0.f;
+                float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                 for (int i = 0; i < BN / 8; ++i) {
-                    s[i][2 * r] = exp2f(s[i][2 * r] - m_use);
-                    s[i][2 * r + 1] = exp2f(s[i][2 * r + 1] - m_use);
-                    sum += s[i][2 * r] + s[i][2 * r + 1];
+                    s[i][2 * r] = exp2f(fmaf(s[i][2 * r], sl2, -m_use));
+                    s[i][2 * r + 1] = exp2f(fmaf(s[i][2 * r + 1], sl2, -m_use));
+                    sum[i & 3] += s[i][2 * r] + s[i][2 * r + 1];
                 }
-                l_run[r] = l_run[r] * alpha[r] + sum;
+                l_run[r] = l_run[r] * alpha[r] + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
             }
+            if (__any_sync(0xffffffffu, moved)) {
 #pragma unroll
-            for (int i = 0; i < HD / 8; ++i) {
-                o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-                o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+                for (int i = 0; i < HD / 8; ++i) {
+                    o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+                    o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+                }
             }
             // ---- O += P V : 4 key k-steps x HD/8 dim n-tiles
 #pragma unroll
