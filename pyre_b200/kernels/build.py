@@ -33,6 +33,7 @@ LIBRARIES = {
     "attention_mma": "attention_mma.cu",
     "gemm_tc": "gemm_tc.cu",
     "attention_prefill": "attention_prefill.cu",
+    "attention_tc": "attention_tc.cu",
     "attention_mma_noalloc": "attention_mma_noalloc.cu",
 }
 

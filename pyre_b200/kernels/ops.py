@@ -362,16 +362,51 @@ def attention_prefill(q: torch.Tensor, cache_layer: torch.Tensor, block_table: t
     return out
 
 
+USE_TC_ATTENTION = True
+TC_ATTENTION_MIN_LEN = 64    # entries with at least this many tokens go to the tcgen05 kernel (128-query tiles)
+
+
+def attention_prefill_tc(q: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor, cu_seqlens: torch.Tensor,
+                         positions: torch.Tensor, n_seqs: int, n_long_tokens: int, n_heads: int, n_kv_heads: int,
+                         head_dim: int, scale: float, window: "int | None", out: torch.Tensor, min_len: int) -> torch.Tensor:
+    """bfloat16 attention of the entries with at least ``min_len`` tokens on the tcgen05 tensor
+    cores (scores and output in tensor memory, Q/K/V tiles by TMA); writes only those entries' rows."""
+    _check(q, "q", torch.bfloat16, 2)
+    _check(cache_layer, "cache_layer", torch.bfloat16, 5)
+    _check(block_table, "block_table", torch.int32, 2)
+    _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    _check(positions, "positions", torch.int32, 1)
+    _check(out, "out", torch.bfloat16, 2)
+    page_size = cache_layer.shape[3]
+    if head_dim not in PREFILL_HEAD_DIMS or page_size & (page_size - 1):
+        raise UnsupportedSize(f"the tcgen05 attention takes head sizes {PREFILL_HEAD_DIMS} and power-of-two pages")
+    if tuple(cache_layer.shape[1:]) != (2, n_kv_heads, page_size, head_dim) or q.shape[1] != n_heads * head_dim:
+        raise ValueError("q or the cache layer do not match the head sizes")
+    if out.shape != q.shape or cu_seqlens.shape[0] != n_seqs + 1 or positions.shape[0] != q.shape[0]:
+        raise ValueError("out, cu_seqlens and positions do not match the batch")
+    lib.call("pyre_attention_prefill_tc", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(), block_table.data_ptr(),
+             block_table.stride(0), cu_seqlens.data_ptr(), positions.data_ptr(), q.shape[0], int(n_long_tokens), n_seqs,
+             n_heads, n_kv_heads, head_dim, page_size, cache_layer.shape[0], int(window or 0), float(scale), int(min_len),
+             device_error_flag(q.device).data_ptr(), _stream())
+    return out
+
+
 def paged_attention_bf16(ctx, q: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor, n_heads: int,
                          n_kv_heads: int, head_dim: int, scale: float, window: "int | None") -> torch.Tensor:
     """Attention of a whole step in bfloat16: entries with many tokens go to the
     prompt-portion kernel, the others (decoded tokens, short portions) to the split-KV kernel."""
     lens = ctx.cu_seqlens_host[1:] - ctx.cu_seqlens_host[:-1]
-    long_mask = lens >= PREFILL_MIN_LEN if head_dim in PREFILL_HEAD_DIMS else lens < 0
+    page_size = cache_layer.shape[3]
+    use_tc = USE_TC_ATTENTION and head_dim in PREFILL_HEAD_DIMS and page_size & (page_size - 1) == 0
+    min_len = TC_ATTENTION_MIN_LEN if use_tc else PREFILL_MIN_LEN
+    long_mask = lens >= min_len if head_dim in PREFILL_HEAD_DIMS else lens < 0
     n_long = int(lens[long_mask].sum())
     n_short_seqs = int((~long_mask).sum())
     out = torch.empty_like(q)
-    if n_long:
+    if n_long and use_tc:
+        attention_prefill_tc(q, cache_layer, block_table, ctx.cu_seqlens, ctx.positions, ctx.num_seqs, n_long, n_heads,
+                             n_kv_heads, head_dim, scale, window, out, min_len)
+    elif n_long:
         attention_prefill(q, cache_layer, block_table, ctx.cu_seqlens, ctx.positions, ctx.num_seqs, n_long, n_heads,
                           n_kv_heads, head_dim, scale, window, out)
     if n_short_seqs:
@@ -383,7 +418,7 @@ def paged_attention_bf16(ctx, q: torch.Tensor, cache_layer: torch.Tensor, block_
         uniform = int(lens[0]) if not n_long and bool((lens == lens[0]).all()) else 0
         paged_attention_mma(q, cache_layer, block_table, ctx.cu_seqlens, ctx.positions, ctx.num_seqs, n_heads,
                             n_kv_heads, head_dim, scale, window, splits, out=out,
-                            max_len=PREFILL_MIN_LEN - 1 if n_long else 0, uniform_len=uniform)
+                            max_len=min_len - 1 if n_long else 0, uniform_len=uniform)
     return out
 
 
@@ -425,7 +460,9 @@ def check_device_errors(device="cuda") -> None:
     if code:
         flag.zero_()
         raise lib.KernelError({2: "a tensor-core GEMM gave up waiting on its pipeline (bounded wait ran out)",
-                               3: "the attention kernel gave up waiting for a tile copy (bounded wait ran out)"}.get(
+                               3: "the attention kernel gave up waiting for a tile copy (bounded wait ran out)",
+                               4: "the tcgen05 attention kernel gave up waiting on its pipeline (bounded wait ran out)",
+                               5: "the tcgen05 attention kernel found its shared memory misaligned"}.get(
             code, f"a kernel raised error code {code}"))
 
 

@@ -75,7 +75,7 @@ class Attention(Part):
         if self.dtype == torch.bfloat16 and self.head_dim <= ops.MMA_MAX_HEAD_DIM:
             libs.append("attention_mma")
             if self.head_dim in ops.PREFILL_HEAD_DIMS:
-                libs.append("attention_prefill")
+                libs += ["attention_prefill", "attention_tc"]
         else:
             libs.append("attention_generic")
         libs.append("gemm_f32" if self.dtype == torch.float32 else "gemm_tc")

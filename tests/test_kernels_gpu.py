@@ -371,6 +371,22 @@ def test_attention_prefill_and_mixed_dispatch(ops, nh, nkv, hd, page, window):
     assert not bad.any(), f"first wrong token row {int(torch.where(bad)[0][0])} of {T}, max error {float(err.max()):.3e}"
     v_far = cache[pg, 1, 0, off].float()
     assert (got[row, :hd].float() - v_far).abs().max() < 0.25 * v_far.abs().max() + 0.1
+    ops.check_device_errors()
+    # both prompt-portion kernels alone (the tcgen05 one and the mma.sync one) agree with the plain statement
+    for kernel, min_len in ((ops.attention_prefill_tc, 64), (ops.attention_prefill, 32)):
+        if kernel is ops.attention_prefill_tc and page & (page - 1):
+            continue
+        alone = torch.full_like(q, 7.0)
+        n_long = sum(n for n in new if n >= min_len)
+        if kernel is ops.attention_prefill_tc:
+            kernel(q, cache, table, cu, positions, B, n_long, nh, nkv, hd, scale, window, alone, min_len)
+        else:
+            kernel(q, cache, table, cu, positions, B, n_long, nh, nkv, hd, scale, window, alone)
+        ops.check_device_errors()
+        e2 = (alone[:314].float() - want[:314]).abs()
+        bad2 = (e2 > 1.2e-2 + 1.6e-2 * want[:314].abs()).any(dim=1)
+        assert not bad2.any(), f"{kernel.__name__}: first wrong row {int(torch.where(bad2)[0][0])}, max error {float(e2.max()):.3e}"
+        assert float((alone[314:316].float() - 7.0).abs().max()) == 0.0
     # the tiled kernel alone leaves the short entries' rows untouched
     out = torch.full_like(q, 7.0)
     ops.attention_prefill(q, cache, table, cu, positions, B, 150 + 100 + 64, nh, nkv, hd, scale, window, out)
