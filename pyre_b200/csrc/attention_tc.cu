@@ -9,18 +9,19 @@
 //                        [T, nh * hd] activation matrix), then per key tile the K and the V
 //                        rows of 64 / box_rows pages through a tensor map over the cache
 //                        layer viewed as [rows, hd] (128-byte swizzle, two stages).
-//   warp 1, one thread : issues the MMAs.  S (128 x 64, fp32, TMEM columns 0..63) = Q K^T with
+//   warp 1, one thread : issues the MMAs.  S (128 x 64, fp32, one of two TMEM buffers) = Q K^T with
 //                        both operands K-major; then, once the softmax threads have put P
 //                        (bf16, 128 x 64) into shared memory, O (128 x hd, TMEM columns
-//                        64..) += P V with V as an MN-major operand straight from the page rows.
+//                        128..) += P V with V as an MN-major operand straight from the page rows.
 //   warps 2..5         : one thread per query row.  Reads its row of S with tcgen05.ld, masks
 //                        by position (causal limit, window), keeps the running maximum and sum
 //                        in fp32, writes P.  No shuffles: a row lives in one thread.
 // The accumulator O is rescaled only when a row's maximum grows by more than 2^8 beyond the
 // value it was scaled with (probabilities then stay below 256, exact in the final O / l);
 // the rescale is a tcgen05.ld / multiply / tcgen05.st pass over the row.
-// Two CTAs fit on an SM (112 KB of shared memory, 256 TMEM columns each), so while one CTA's
-// row threads work on a tile, the tensor core multiplies for the other.
+// S is double-buffered in tensor memory: the scores of tile i + 1 are computed while the row
+// threads work on tile i.  Two CTAs fit on an SM (112 KB of shared memory, 256 TMEM columns
+// each), so the tensor core also alternates between two CTAs.
 //
 // Whole page rows arrive, so rows of a V tile outside [first row's window start, last row's
 // position] may hold anything; the row threads zero them in shared memory before the P V
@@ -113,6 +114,38 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
+// Two fp32 lanes in one 64-bit register for the packed fma/add of sm_100 (each lane is the same
+// IEEE operation as its scalar form).
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// 2^x on the special-function unit; results below 2^-126 are flushed to zero (a weight that
+// small adds nothing to a sum whose largest term is at least 2^-8).
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -138,8 +171,8 @@ struct Smem {
     static constexpr int OFF_K = Q_BYTES;                  // [2 stages]
     static constexpr int OFF_V = OFF_K + 2 * KV_TILE;      // [2 stages]
     static constexpr int OFF_P = OFF_V + 2 * KV_TILE;
-    static constexpr int OFF_BAR = OFF_P + P_BYTES;        // q_full, kv_full[2], kv_empty[2], s_full, p_full, o_ready
-    static constexpr int N_BARS = 8;
+    static constexpr int OFF_BAR = OFF_P + P_BYTES;        // q_full, kv_full[2], kv_empty[2], s_full[2], p_full, o_ready
+    static constexpr int N_BARS = 9;
     static constexpr int TOTAL = OFF_BAR + N_BARS * 8 + 16;   // the dynamic window must start 1024-byte aligned (checked)
 };
 
@@ -148,8 +181,8 @@ __global__ void __launch_bounds__(THREADS, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, const TcParams p) {
     using L = Smem<HD>;
     constexpr int HALVES = L::HALVES;
-    constexpr uint32_t TMEM_COLS = HD == 128 ? 256 : 128;   // S: 64 columns, O: HD columns; a power of two
-    constexpr uint32_t S_COL = 0, O_COL = 64;
+    constexpr uint32_t TMEM_COLS = 256;                     // two S buffers of 64 columns, O: HD columns
+    constexpr uint32_t S_COL = 0, O_COL = 128;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
     uint8_t* gen = smem_raw;
@@ -158,7 +191,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         return;
     }
     const uint32_t bar_q = base + L::OFF_BAR, bar_kv_full = bar_q + 8, bar_kv_empty = bar_q + 24;
-    const uint32_t bar_s = bar_q + 40, bar_p = bar_q + 48, bar_o = bar_q + 56;
+    const uint32_t bar_s = bar_q + 40 /* [2] */, bar_p = bar_q + 56, bar_o = bar_q + 64;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::OFF_BAR + L::N_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::OFF_BAR + L::N_BARS * 8 + 8);
 
@@ -167,7 +200,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     // ---- which 128-token tile of which entry?  tiles are numbered from the end of each portion
     // (the last tile sees the most keys and starts first)
-    int tile = blockIdx.x, seq = -1, tok0 = 0, n_tok = 0;
+    int tile = blockIdx.y, seq = -1, tok0 = 0, n_tok = 0;
     for (int b = 0; b < p.n_seqs; ++b) {
         const int begin = p.cu_seqlens[b], len = p.cu_seqlens[b + 1] - begin;
         if (len < p.min_len) continue;
@@ -182,7 +215,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         tile -= nt;
     }
     if (seq < 0) return;   // the grid is an upper bound (whole CTA leaves: nothing was set up yet)
-    const int head = blockIdx.y;
+    const int head = blockIdx.x;   // heads are the fast grid dimension: the longest tiles of all heads start first
     const int kvh = head / (p.nh / p.nkv);
     const int* table = p.block_table + (size_t)seq * p.bt_stride;
     const int pos_first = p.positions[tok0], pos_last = pos_first + n_tok - 1;   // consecutive positions
@@ -195,6 +228,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         mbar_init(bar_q, 1);
         for (int s = 0; s < 2; ++s) { mbar_init(bar_kv_full + 8 * s, 1); mbar_init(bar_kv_empty + 8 * s, 1); }
         mbar_init(bar_s, 1);
+        mbar_init(bar_s + 8, 1);
         mbar_init(bar_p, 4);      // one arrival per row warp
         mbar_init(bar_o, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -218,6 +252,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
             for (int h = 0; h < HALVES; ++h) tma_load_2d(base + L::OFF_Q + h * (BM * 128), &map_q, bar_q, head * HD + h * 64, tok0);
             const int pieces = BN / p.box_rows;
+            // The page numbers of a tile's pieces are read together (independent loads) and one
+            // tile ahead, while the producer waits for a free stage anyway.
+            constexpr int MAX_PIECES = 16;   // pages of at least 4 tokens; smaller pages look up inline
+            int pages[MAX_PIECES];
+            auto read_pages = [&](int i) {
+#pragma unroll
+                for (int pc = 0; pc < MAX_PIECES; ++pc) {
+                    const int key = (tile_lo + i) * BN + pc * p.box_rows;
+                    const bool live = pc < pieces && i < n_tiles && key + p.box_rows - 1 >= lo_cta && key <= pos_last;
+                    pages[pc] = live ? table[key >> p.page_shift] : 0;   // pieces outside the range read page 0 (masked)
+                }
+            };
+            read_pages(0);
             for (int i = 0; i < n_tiles; ++i) {
                 const int s = i & 1;
                 if (!mbar_wait(bar_kv_empty + 8 * s, ((i >> 1) & 1) ^ 1, abort_flag, p.err_flag)) break;
@@ -225,8 +272,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 const uint32_t kd = base + L::OFF_K + s * L::KV_TILE, vd = base + L::OFF_V + s * L::KV_TILE;
                 for (int pc = 0; pc < pieces; ++pc) {
                     const int key = (tile_lo + i) * BN + pc * p.box_rows;
-                    const bool live = key + p.box_rows - 1 >= lo_cta && key <= pos_last;
-                    const int page = live ? table[key >> p.page_shift] : 0;   // pieces outside the range read page 0 (masked)
+                    int page;
+                    if (pc < MAX_PIECES) {
+                        page = pages[pc];
+                    } else {
+                        const bool live = key + p.box_rows - 1 >= lo_cta && key <= pos_last;
+                        page = live ? table[key >> p.page_shift] : 0;
+                    }
                     const int krow = ((page * 2) * p.nkv + kvh) * p.page_size + (key & (p.page_size - 1));
                     const int vrow = krow + p.nkv * p.page_size;
 #pragma unroll
@@ -235,6 +287,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                         tma_load_2d(vd + h * (BN * 128) + pc * p.box_rows * 128, &map_kv, bar_kv_full + 8 * s, h * 64, vrow);
                     }
                 }
+                read_pages(i + 1);
             }
         }
     } else if (warp == 1) {
@@ -244,31 +297,41 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             // bit 16: B is MN-major (V: the head dims are contiguous, the keys are the K index)
             constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-            bool ok = mbar_wait(bar_q, 0, abort_flag, p.err_flag);
-            for (int i = 0; i < n_tiles && ok; ++i) {
-                const int s = i & 1;
-                ok = mbar_wait(bar_kv_full + 8 * s, (i >> 1) & 1, abort_flag, p.err_flag);
-                if (!ok) break;
+            // S of tile i goes to S buffer i & 1; it is issued one tile ahead, so the tensor core
+            // works on the next scores while the row threads are busy with this tile's softmax
+            auto issue_s = [&](int i) -> bool {
+                const int st = i & 1;
+                if (!mbar_wait(bar_kv_full + 8 * st, (i >> 1) & 1, abort_flag, p.err_flag)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t kd = base + L::OFF_K + s * L::KV_TILE, vd = base + L::OFF_V + s * L::KV_TILE;
-                // S = Q K^T: HD / 16 steps of 16 dims; 4 steps per 128-byte column box
+                const uint32_t kd = base + L::OFF_K + st * L::KV_TILE;
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h)
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        umma_bf16(tmem_base + S_COL, desc_k_major(base + L::OFF_Q + h * (BM * 128)) + 2 * j,
+                    for (int j = 0; j < 4; ++j)   // HD / 16 steps of 16 dims; 4 steps per 128-byte column box
+                        umma_bf16(tmem_base + S_COL + st * BN, desc_k_major(base + L::OFF_Q + h * (BM * 128)) + 2 * j,
                                   desc_k_major(kd + h * (BN * 128)) + 2 * j, idesc_s, (h > 0 || j > 0) ? 1u : 0u);
-                umma_commit(bar_s);
+                umma_commit(bar_s + 8 * st);
+                return true;
+            };
+            bool ok = mbar_wait(bar_q, 0, abort_flag, p.err_flag);
+            if (ok) ok = issue_s(0);
+            for (int i = 0; i < n_tiles && ok; ++i) {
+                const int st = i & 1;
+                if (i + 1 < n_tiles) {
+                    ok = issue_s(i + 1);
+                    if (!ok) break;
+                }
                 ok = mbar_wait(bar_p, i & 1, abort_flag, p.err_flag);   // P is in shared memory, O has been rescaled
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t vd = base + L::OFF_V + st * L::KV_TILE;
                 // O += P V: 4 steps of 16 keys; V rows are 128 B per column box, the second box lies BN * 128 B further
 #pragma unroll
                 for (int j = 0; j < BN / 16; ++j)
                     umma_bf16(tmem_base + O_COL, desc_k_major(base + L::OFF_P) + 2 * j,
                               desc_mn_major(vd + j * (16 * 128), BN * 128), idesc_pv, (i > 0 || j > 0) ? 1u : 0u);
-                umma_commit(bar_kv_empty + 8 * s);   // the stage may be refilled
-                umma_commit(bar_o);                  // O holds this tile; P may be overwritten
+                umma_commit(bar_kv_empty + 8 * st);   // the stage may be refilled
+                umma_commit(bar_o);                   // O holds this tile; P may be overwritten
             }
         }
     } else {
@@ -285,41 +348,64 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int i = 0; i < n_tiles && alive; ++i) {
             const int s = i & 1;
             const int key0 = (tile_lo + i) * BN;
-            bool ok = mbar_wait(bar_s, i & 1, abort_flag, p.err_flag);
+            bool ok = mbar_wait(bar_s + 8 * s, (i >> 1) & 1, abort_flag, p.err_flag);
             alive = __all_sync(0xffffffffu, ok);
             if (!alive) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float sc[BN];
-#pragma unroll
-            for (int c = 0; c < BN; c += 16) {
-                uint32_t r[16];
-                tmem_ld16(lane_addr + S_COL + c, r);
+            {
+                uint32_t r0[16], r1[16], r2[16], r3[16];   // all four loads go out before the one wait
+                tmem_ld16(lane_addr + S_COL + s * BN, r0);
+                tmem_ld16(lane_addr + S_COL + s * BN + 16, r1);
+                tmem_ld16(lane_addr + S_COL + s * BN + 32, r2);
+                tmem_ld16(lane_addr + S_COL + s * BN + 48, r3);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int q = 0; q < 16; ++q) sc[c + q] = __uint_as_float(r[q]);
+                for (int q = 0; q < 16; ++q) {
+                    sc[q] = __uint_as_float(r0[q]); sc[16 + q] = __uint_as_float(r1[q]);
+                    sc[32 + q] = __uint_as_float(r2[q]); sc[48 + q] = __uint_as_float(r3[q]);
+                }
             }
-            // mask by position; the raw maximum in four chains
+            // mask by position (only tiles that some row's causal limit or window edge cuts; rows
+            // beyond the portion's end are never stored, so they need no mask); the raw maximum in four chains
+            const bool need_mask = key0 + BN - 1 > pos_first || (p.window > 0 && key0 < pos_last - p.window + 1);
+            if (need_mask) {
+#pragma unroll
+                for (int c = 0; c < BN; ++c) {
+                    const int key = key0 + c;
+                    const bool okk = row_ok && key <= pos && key >= lo;
+                    sc[c] = okk ? sc[c] : -INFINITY;
+                }
+            }
             float tm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < BN; ++c) {
-                const int key = key0 + c;
-                const bool okk = row_ok && key <= pos && key >= lo;
-                sc[c] = okk ? sc[c] : -INFINITY;
-                tm[c & 3] = fmaxf(tm[c & 3], sc[c]);
+            for (int c = 0; c < BN; c += 8) {
+                tm[0] = max3(tm[0], sc[c], sc[c + 1]);
+                tm[1] = max3(tm[1], sc[c + 2], sc[c + 3]);
+                tm[2] = max3(tm[2], sc[c + 4], sc[c + 5]);
+                tm[3] = max3(tm[3], sc[c + 6], sc[c + 7]);
             }
             const float tmax = fmaxf(fmaxf(tm[0], tm[1]), fmaxf(tm[2], tm[3])) * sl2;
             // the accumulator keeps its scaling unless the maximum grew by more than 2^8
             const bool grow = tmax > m_ref + RESCALE_THRESHOLD;   // also the first finite maximum (m_ref = -inf)
             const float m_new = grow ? tmax : m_ref;
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            const float alpha = grow ? exp2f(m_ref - m_use) : 1.f;   // exp2(-inf) = 0 the first time
+            const float alpha = grow ? ex2(m_ref - m_use) : 1.f;   // 2^(-inf) = 0 the first time
             m_ref = m_new;
-            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            // p = 2^(s * scale * log2 e - m): packed fma, one special-function op per element, packed sums
+            const uint64_t sl2_2 = pack2(sl2, sl2), neg_m2 = pack2(-m_use, -m_use);
+            uint64_t sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
-            for (int c = 0; c < BN; ++c) {
-                sc[c] = exp2f(fmaf(sc[c], sl2, -m_use));
-                sum[c & 3] += sc[c];
+            for (int c = 0; c < BN; c += 2) {
+                float a, b;
+                unpack2(fma2(pack2(sc[c], sc[c + 1]), sl2_2, neg_m2), a, b);
+                sc[c] = ex2(a);
+                sc[c + 1] = ex2(b);
+                sum2[(c >> 1) & 1] = add2(sum2[(c >> 1) & 1], pack2(sc[c], sc[c + 1]));
             }
+            float sum[4];
+            unpack2(sum2[0], sum[0], sum[1]);
+            unpack2(sum2[1], sum[2], sum[3]);
             l_sum = l_sum * alpha + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
 
             // the previous tile's P V must be complete before P is overwritten or O is touched
@@ -443,7 +529,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const TcParams& p, int
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    cudaError_t e = pyre_launch(attention_tc_kernel<HD>, dim3(tiles_bound, p.nh), dim3(THREADS), (size_t)L::TOTAL, stream, mq, mkv, p);
+    cudaError_t e = pyre_launch(attention_tc_kernel<HD>, dim3(p.nh, tiles_bound), dim3(THREADS), (size_t)L::TOTAL, stream, mq, mkv, p);
     if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();
 }
@@ -478,5 +564,6 @@ PYRE_API int pyre_attention_prefill_tc(const void* q, const void* cache, void* o
     if (!make_map(&mq, q, n_tokens, (long long)nh * hd, (long long)nh * hd, BM)) return PYRE_ERR_UNSUPPORTED;
     if (!make_map(&mkv, cache, kv_rows, hd, hd, p.box_rows)) return PYRE_ERR_UNSUPPORTED;
     const int tiles_bound = n_long_tokens / BM + n_seqs;
+    if (tiles_bound > 65535) return PYRE_ERR_BAD_ARG;   // grid.y
     return hd == 128 ? launch<128>(mq, mkv, p, tiles_bound, stream) : launch<64>(mq, mkv, p, tiles_bound, stream);
 }
