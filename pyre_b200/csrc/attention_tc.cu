@@ -2,13 +2,16 @@
 // sizes 64 and 128): both products, S = Q K^T and O = P V, are tcgen05.mma instructions with
 // their accumulators in tensor memory; queries, keys and values arrive by TMA.
 //
-// A CTA (192 threads) owns 128 consecutive tokens of one portion and one query head and walks
+// A CTA (224 threads) owns 128 consecutive tokens of one portion and one query head and walks
 // the keys in tiles of 64, from the tile holding the start of the first row's window to the
 // tile holding the last row's position:
-//   warp 0, one thread : TMA producer.  The Q tile once (128 rows of this head out of the
-//                        [T, nh * hd] activation matrix), then per key tile the K and the V
-//                        rows of 64 / box_rows pages through a tensor map over the cache
-//                        layer viewed as [rows, hd] (128-byte swizzle, two stages).
+//   warps 0 and 6      : TMA producers (lane 0 issues).  Warp 0 copies the Q tile once (128 rows
+//                        of this head out of the [T, nh * hd] activation matrix) and then the K
+//                        tiles, warp 6 the V tiles: per key tile the rows of 64 / box_rows pages
+//                        through a tensor map over the cache layer viewed as [rows, hd]
+//                        (128-byte swizzle).  K and V have two-stage rings of their own: a K stage
+//                        is free as soon as its scores exist, a V stage after its P V.  Issuing a
+//                        copy costs about a hundred cycles, so the two rings have a warp each.
 //   warp 1, one thread : issues the MMAs.  S (128 x 64, fp32, one of two TMEM buffers) = Q K^T with
 //                        both operands K-major; then, once the softmax threads have put P
 //                        (bf16, 128 x 64) into shared memory, O (128 x hd, TMEM columns
@@ -21,7 +24,10 @@
 // the rescale is a tcgen05.ld / multiply / tcgen05.st pass over the row.
 // S is double-buffered in tensor memory: the scores of tile i + 1 are computed while the row
 // threads work on tile i.  Two CTAs fit on an SM (112 KB of shared memory, 256 TMEM columns
-// each), so the tensor core also alternates between two CTAs.
+// each), so the tensor core also alternates between two CTAs.  The grid runs the heads fastest
+// and the tiles of a portion from its end, so the tiles with the most keys start first.
+// The softmax arithmetic uses the packed fp32 pairs of sm_100 (fma.rn.f32x2, add.rn.f32x2), the
+// three-input max and ex2.approx: about four instructions per score.
 //
 // Whole page rows arrive, so rows of a V tile outside [first row's window start, last row's
 // position] may hold anything; the row threads zero them in shared memory before the P V
@@ -42,7 +48,7 @@ namespace {
 
 constexpr int BM = 128;       // queries per CTA = TMEM lanes
 constexpr int BN = 64;        // keys per tile
-constexpr int THREADS = 192;
+constexpr int THREADS = 224;   // warp 0: K producer, 1: MMA issuer, 2-5: one thread per query row, 6: V producer
 constexpr uint32_t WAIT_LIMIT = 400000;
 constexpr int ERR_TIMEOUT = 4;
 constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
@@ -171,8 +177,8 @@ struct Smem {
     static constexpr int OFF_K = Q_BYTES;                  // [2 stages]
     static constexpr int OFF_V = OFF_K + 2 * KV_TILE;      // [2 stages]
     static constexpr int OFF_P = OFF_V + 2 * KV_TILE;
-    static constexpr int OFF_BAR = OFF_P + P_BYTES;        // q_full, kv_full[2], kv_empty[2], s_full[2], p_full, o_ready
-    static constexpr int N_BARS = 9;
+    static constexpr int OFF_BAR = OFF_P + P_BYTES;        // q_full, k_full[2], v_full[2], s_full[2], o_ready[2], p_full
+    static constexpr int N_BARS = 10;
     static constexpr int TOTAL = OFF_BAR + N_BARS * 8 + 16;   // the dynamic window must start 1024-byte aligned (checked)
 };
 
@@ -190,8 +196,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (threadIdx.x == 0 && p.err_flag) atomicExch(p.err_flag, ERR_TIMEOUT + 1);
         return;
     }
-    const uint32_t bar_q = base + L::OFF_BAR, bar_kv_full = bar_q + 8, bar_kv_empty = bar_q + 24;
-    const uint32_t bar_s = bar_q + 40 /* [2] */, bar_p = bar_q + 56, bar_o = bar_q + 64;
+    // s_full[t & 1] also tells the producer that the K stage of tile t is free, o_ready[t & 1] that its V stage is
+    const uint32_t bar_q = base + L::OFF_BAR, bar_k_full = bar_q + 8, bar_v_full = bar_q + 24;
+    const uint32_t bar_s = bar_q + 40 /* [2] */, bar_o = bar_q + 56 /* [2] */, bar_p = bar_q + 72;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::OFF_BAR + L::N_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::OFF_BAR + L::N_BARS * 8 + 8);
 
@@ -226,11 +233,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         mbar_init(bar_q, 1);
-        for (int s = 0; s < 2; ++s) { mbar_init(bar_kv_full + 8 * s, 1); mbar_init(bar_kv_empty + 8 * s, 1); }
-        mbar_init(bar_s, 1);
-        mbar_init(bar_s + 8, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar_k_full + 8 * s, 1); mbar_init(bar_v_full + 8 * s, 1);
+            mbar_init(bar_s + 8 * s, 1); mbar_init(bar_o + 8 * s, 1);
+        }
         mbar_init(bar_p, 4);      // one arrival per row warp
-        mbar_init(bar_o, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -242,53 +249,54 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0) {
+    if (warp == 0 || warp == 6) {
+        // ---------------- producers: warp 0 copies Q and the K tiles, warp 6 the V tiles.  The whole
+        // warp runs the loop (no divergent region) and lane 0 issues the copies.
+        const int which = warp == 0 ? 0 : 1;
         if (lane == 0) {
-            // ---------------- producer
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_q)) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_kv)) : "memory");
-            pdl_wait();   // queries and pages of this step come from earlier kernels
+        }
+        pdl_wait();   // queries and pages of this step come from earlier kernels
+        if (which == 0 && lane == 0) {
             mbar_expect_tx(bar_q, L::Q_BYTES);
 #pragma unroll
             for (int h = 0; h < HALVES; ++h) tma_load_2d(base + L::OFF_Q + h * (BM * 128), &map_q, bar_q, head * HD + h * 64, tok0);
-            const int pieces = BN / p.box_rows;
-            // The page numbers of a tile's pieces are read together (independent loads) and one
-            // tile ahead, while the producer waits for a free stage anyway.
-            constexpr int MAX_PIECES = 16;   // pages of at least 4 tokens; smaller pages look up inline
-            int pages[MAX_PIECES];
-            auto read_pages = [&](int i) {
+        }
+        // K and V have rings of their own (two stages each).  A K stage is free again as soon
+        // as its scores are computed (s_full), a V stage after its P V (o_ready).
+        // A tile is copied in pieces of one page (or of the whole tile, for pages of 64 tokens and
+        // more); lane pc holds the page number of piece pc, read two tiles ahead of its use.
+        const int pieces = BN / p.box_rows;   // at most 16 (pages of 4 tokens or more)
+        auto read_pages = [&](int i) -> int {
+            const int key = (tile_lo + i) * BN + lane * p.box_rows;
+            const bool live = lane < pieces && i < n_tiles && key + p.box_rows - 1 >= lo_cta && key <= pos_last;
+            return live ? table[key >> p.page_shift] : 0;   // pieces outside the range read page 0 (masked)
+        };
+        const uint32_t bar_empty = which ? bar_o : bar_s, bar_full = which ? bar_v_full : bar_k_full;
+        const uint32_t ring = base + (which ? L::OFF_V : L::OFF_K);
+        const int row_base = (which * p.nkv + kvh) * p.page_size, page_rows = 2 * p.nkv * p.page_size;
+        int pg0 = read_pages(0), pg1 = read_pages(1), pg2 = read_pages(2);   // tiles i, i + 1, i + 2
+        for (int i = 0; i < n_tiles; ++i) {
+            const int s = i & 1;
+            const bool ok = mbar_wait(bar_empty + 8 * s, ((i >> 1) & 1) ^ 1, abort_flag, p.err_flag);
+            if (!__all_sync(0xffffffffu, ok)) break;
+            const uint32_t full = bar_full + 8 * s, dst = ring + s * L::KV_TILE;
+            if (lane == 0) mbar_expect_tx(full, L::KV_TILE);
+            for (int pc = 0; pc < pieces; ++pc) {
+                const int page = __shfl_sync(0xffffffffu, pg0, pc);
+                const int key = (tile_lo + i) * BN + pc * p.box_rows;
+                const int row = page * page_rows + row_base + (key & (p.page_size - 1));
+                if (lane == 0) {
 #pragma unroll
-                for (int pc = 0; pc < MAX_PIECES; ++pc) {
-                    const int key = (tile_lo + i) * BN + pc * p.box_rows;
-                    const bool live = pc < pieces && i < n_tiles && key + p.box_rows - 1 >= lo_cta && key <= pos_last;
-                    pages[pc] = live ? table[key >> p.page_shift] : 0;   // pieces outside the range read page 0 (masked)
+                    for (int h = 0; h < HALVES; ++h)
+                        tma_load_2d(dst + h * (BN * 128) + pc * p.box_rows * 128, &map_kv, full, h * 64, row);
                 }
-            };
-            read_pages(0);
-            for (int i = 0; i < n_tiles; ++i) {
-                const int s = i & 1;
-                if (!mbar_wait(bar_kv_empty + 8 * s, ((i >> 1) & 1) ^ 1, abort_flag, p.err_flag)) break;
-                mbar_expect_tx(bar_kv_full + 8 * s, 2 * L::KV_TILE);
-                const uint32_t kd = base + L::OFF_K + s * L::KV_TILE, vd = base + L::OFF_V + s * L::KV_TILE;
-                for (int pc = 0; pc < pieces; ++pc) {
-                    const int key = (tile_lo + i) * BN + pc * p.box_rows;
-                    int page;
-                    if (pc < MAX_PIECES) {
-                        page = pages[pc];
-                    } else {
-                        const bool live = key + p.box_rows - 1 >= lo_cta && key <= pos_last;
-                        page = live ? table[key >> p.page_shift] : 0;
-                    }
-                    const int krow = ((page * 2) * p.nkv + kvh) * p.page_size + (key & (p.page_size - 1));
-                    const int vrow = krow + p.nkv * p.page_size;
-#pragma unroll
-                    for (int h = 0; h < HALVES; ++h) {
-                        tma_load_2d(kd + h * (BN * 128) + pc * p.box_rows * 128, &map_kv, bar_kv_full + 8 * s, h * 64, krow);
-                        tma_load_2d(vd + h * (BN * 128) + pc * p.box_rows * 128, &map_kv, bar_kv_full + 8 * s, h * 64, vrow);
-                    }
-                }
-                read_pages(i + 1);
             }
+            __syncwarp();
+            pg0 = pg1;
+            pg1 = pg2;
+            pg2 = read_pages(i + 3);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -301,7 +309,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             // works on the next scores while the row threads are busy with this tile's softmax
             auto issue_s = [&](int i) -> bool {
                 const int st = i & 1;
-                if (!mbar_wait(bar_kv_full + 8 * st, (i >> 1) & 1, abort_flag, p.err_flag)) return false;
+                if (!mbar_wait(bar_k_full + 8 * st, (i >> 1) & 1, abort_flag, p.err_flag)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t kd = base + L::OFF_K + st * L::KV_TILE;
 #pragma unroll
@@ -322,6 +330,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     if (!ok) break;
                 }
                 ok = mbar_wait(bar_p, i & 1, abort_flag, p.err_flag);   // P is in shared memory, O has been rescaled
+                if (ok) ok = mbar_wait(bar_v_full + 8 * st, (i >> 1) & 1, abort_flag, p.err_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t vd = base + L::OFF_V + st * L::KV_TILE;
@@ -330,8 +339,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 for (int j = 0; j < BN / 16; ++j)
                     umma_bf16(tmem_base + O_COL, desc_k_major(base + L::OFF_P) + 2 * j,
                               desc_mn_major(vd + j * (16 * 128), BN * 128), idesc_pv, (i > 0 || j > 0) ? 1u : 0u);
-                umma_commit(bar_kv_empty + 8 * st);   // the stage may be refilled
-                umma_commit(bar_o);                   // O holds this tile; P may be overwritten
+                umma_commit(bar_o + 8 * st);   // O holds this tile; P may be overwritten, the V stage refilled
             }
         }
     } else {
@@ -410,7 +418,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
             // the previous tile's P V must be complete before P is overwritten or O is touched
             if (i > 0) {
-                ok = mbar_wait(bar_o, (i - 1) & 1, abort_flag, p.err_flag);
+                ok = mbar_wait(bar_o + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, abort_flag, p.err_flag);
                 alive = __all_sync(0xffffffffu, ok);
                 if (!alive) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -429,7 +437,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             }
             // rows of the V tile outside [lo_cta, pos_last] hold whatever the page holds: zero them
             if (key0 + BN - 1 > pos_last || key0 < lo_cta) {
-                ok = mbar_wait(bar_kv_full + 8 * s, (i >> 1) & 1, abort_flag, p.err_flag);   // the tile has landed
+                ok = mbar_wait(bar_v_full + 8 * s, (i >> 1) & 1, abort_flag, p.err_flag);   // the tile has landed
                 alive = __all_sync(0xffffffffu, ok);
                 if (!alive) break;
                 const uint32_t vd = base + L::OFF_V + s * L::KV_TILE;
@@ -457,7 +465,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         // ---- the last P V, then out = O / l
         if (alive) {
-            bool ok = mbar_wait(bar_o, (n_tiles - 1) & 1, abort_flag, p.err_flag);
+            bool ok = mbar_wait(bar_o + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag, p.err_flag);
             alive = __all_sync(0xffffffffu, ok);
         }
         if (alive) {
@@ -537,7 +545,7 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const TcParams& p, int
 }  // namespace
 
 // Attention of every entry with at least min_len tokens (other entries' rows are left untouched).
-// bfloat16, head sizes 64 and 128, pages of a power-of-two number of tokens.  n_long_tokens: total
+// bfloat16, head sizes 64 and 128, pages of a power-of-two number of tokens (4 or more).  n_long_tokens: total
 // tokens of those entries (bounds the grid); n_tokens: rows of q; n_pages: pages of the cache layer.
 PYRE_API int pyre_attention_prefill_tc(const void* q, const void* cache, void* out, const int* block_table,
                                        int bt_stride, const int* cu_seqlens, const int* positions, int n_tokens,
@@ -545,7 +553,7 @@ PYRE_API int pyre_attention_prefill_tc(const void* q, const void* cache, void* o
                                        long long n_pages, int window, float scale, int min_len, int* err_flag,
                                        cudaStream_t stream) {
     if (n_long_tokens <= 0) return 0;
-    if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || (page_size & (page_size - 1)) || min_len < 1)
+    if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || page_size < 4 || (page_size & (page_size - 1)) || min_len < 1)
         return PYRE_ERR_UNSUPPORTED;
     const long long kv_rows = n_pages * 2 * nkv * page_size;
     if (((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)out & 15) || kv_rows >= (1ll << 31) || n_pages <= 0)

@@ -378,7 +378,7 @@ def attention_prefill_tc(q: torch.Tensor, cache_layer: torch.Tensor, block_table
     _check(positions, "positions", torch.int32, 1)
     _check(out, "out", torch.bfloat16, 2)
     page_size = cache_layer.shape[3]
-    if head_dim not in PREFILL_HEAD_DIMS or page_size & (page_size - 1):
+    if head_dim not in PREFILL_HEAD_DIMS or page_size & (page_size - 1) or page_size < 4:
         raise UnsupportedSize(f"the tcgen05 attention takes head sizes {PREFILL_HEAD_DIMS} and power-of-two pages")
     if tuple(cache_layer.shape[1:]) != (2, n_kv_heads, page_size, head_dim) or q.shape[1] != n_heads * head_dim:
         raise ValueError("q or the cache layer do not match the head sizes")
@@ -397,7 +397,7 @@ def paged_attention_bf16(ctx, q: torch.Tensor, cache_layer: torch.Tensor, block_
     prompt-portion kernel, the others (decoded tokens, short portions) to the split-KV kernel."""
     lens = ctx.cu_seqlens_host[1:] - ctx.cu_seqlens_host[:-1]
     page_size = cache_layer.shape[3]
-    use_tc = USE_TC_ATTENTION and head_dim in PREFILL_HEAD_DIMS and page_size & (page_size - 1) == 0
+    use_tc = USE_TC_ATTENTION and head_dim in PREFILL_HEAD_DIMS and page_size & (page_size - 1) == 0 and page_size >= 4
     min_len = TC_ATTENTION_MIN_LEN if use_tc else PREFILL_MIN_LEN
     long_mask = lens >= min_len if head_dim in PREFILL_HEAD_DIMS else lens < 0
     n_long = int(lens[long_mask].sum())
