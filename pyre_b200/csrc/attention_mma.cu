@@ -10,15 +10,22 @@
 // split the CTA writes an unnormalised partial (max, sum, accumulator) to scratch and
 // `combine` merges the splits; with one split it writes the output directly.  When the
 // caller gives no scratch, the splits of a group form a thread-block cluster (up to 16 CTAs)
-// and merge through distributed shared memory instead: no scratch, no second kernel.
+// and merge through distributed shared memory instead: every CTA pushes its partial to the
+// CTA that owns the output dims (remote stores, nobody waits for a remote load), one cluster
+// barrier makes them visible, and each CTA reduces and writes its dims.  No scratch, no
+// second kernel.
 //
-// Each warp owns a two-stage ring in shared memory: while it computes on tile i, the
-// cp.async copies of tile i + 1 (16 keys and 16 values, fetched row by row through the
-// block table in 16-byte chunks) are in flight, so the memory system always has work from
-// every warp.  Rows are XOR-swizzled by chunk so that the copies and the ldmatrix reads
-// (plain for K, transposed for V) do not collide on banks.  Masked keys (beyond a row's
-// position, before its window, outside the sequence) are zero-filled by the copy and get
-// a score of -inf, so stale or non-finite memory in unowned slots cannot reach the result.
+// Each warp owns a three-stage ring in shared memory, so two tiles are in flight while it
+// computes on a third.  With power-of-two pages and head sizes that are multiples of 64 the
+// tiles come by TMA; with pages of 16 tokens or more one 5-d tensor copy brings a whole tile
+// ([K, V] x [column boxes] x [16 rows] x [64 columns], 128-byte swizzle), and the page numbers
+// of a warp's tiles are read 32 at a time, one per lane.  Other sizes use cp.async copies
+// (16 keys and 16 values, row by row through the block table in 16-byte chunks) with rows
+// XOR-swizzled by chunk, so that the copies and the ldmatrix reads (plain for K, transposed
+// for V) do not collide on banks.  Masked keys (beyond a row's position, before its window,
+// outside the sequence) get a score of -inf and their value rows are zero (zero-filled by
+// cp.async, zeroed in shared memory after a TMA copy), so stale or non-finite memory in
+// unowned slots cannot reach the result.
 //
 // Formula: pyre/model.py:104-124, pyre/kernels/paged_attn.py:43-71 (online softmax, fp32
 // scores; probabilities rounded to the activation dtype before the product with V, as
@@ -36,6 +43,7 @@ namespace {
 
 constexpr int WARPS = 4;
 constexpr int TILE = 16;  // keys per tile
+constexpr int STAGES = 3; // tiles in flight per warp
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -84,6 +92,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
+// 2^x on the special-function unit (results below 2^-126 become 0; 2^-inf = 0)
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 constexpr uint32_t TMA_WAIT_LIMIT = 2000000;
 constexpr int ERR_ATTN_TIMEOUT = 3;
 
@@ -98,7 +117,8 @@ struct AttnParams {
     const int* positions;        // [T]
     int bt_stride, n_seqs, nh, nkv, page_size, window, n_splits, tpg, hpg, head_blocks;
     int page_shift;              // log2(page_size) if it is a power of two, else -1
-    int use_tma;                 // tiles come by TMA through `map` (power-of-two pages, HD % 64 == 0)
+    int use_tma;                 // tiles come by TMA through `map` (power-of-two pages, HD % 64 == 0): 1 = one copy per
+                                 // 128-byte column box, page piece and K/V (pages under 16 tokens), 2 = one 5-d copy per tile
     int box_rows;                // rows per TMA box: min(16, page_size)
     int* err_flag;
     int uniform_len;             // > 0: every entry has exactly this many tokens (a decode step): no scan for the group
@@ -115,7 +135,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
     constexpr int CH = HD / 8;    // 16-byte chunks per row
     constexpr int SWZ = (CH % 8 == 0) ? 7 : (CH % 4 == 0) ? 3 : (CH % 2 == 0) ? 1 : 0;   // XOR mask that stays inside a row
     constexpr int TILE_BYTES = TILE * HD * 2;          // one K (or V) tile
-    constexpr int WARP_BYTES = 2 * 2 * TILE_BYTES;     // two stages of K + V
+    constexpr int WARP_BYTES = STAGES * 2 * TILE_BYTES;   // the stages of K + V
     static_assert(16 * (HD + 1) * 4 <= WARP_BYTES, "the merge buffer of a warp must fit into its ring");
     // a warp's ring is dead once its key loop is over; its merge buffer sm_o[warp] reuses the space
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -123,14 +143,19 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
     uint8_t* smem_dyn = smem_raw + ((1024u - ((uint32_t)__cvta_generic_to_shared(smem_raw) & 1023u)) & 1023u);
     __shared__ float sm_m[WARPS][16];
     __shared__ float sm_l[WARPS][16];
-    __shared__ float sm_cm[16], sm_cl[16];   // this CTA's merged (max, sum) per row, read by its cluster peers
-    __shared__ __align__(8) uint64_t tma_bar[WARPS][2];   // per warp and stage: "the tile has landed"
+    // cluster merge: partials pushed by the peers, [rank][row][dims owned by this CTA] and [rank][row][max, sum];
+    // n * ceil(HD / n) <= HD + 15 dims in all
+    __shared__ __align__(16) float rx_o[CLUSTER ? 16 * (HD + 16) : 4];
+    __shared__ __align__(16) float rx_ml[CLUSTER ? 16 * 16 * 2 : 4];
+    __shared__ int sm_th[16];                // per row: token * nh + head of its output row, or -1
+    __shared__ __align__(8) uint64_t tma_bar[WARPS][STAGES];   // per warp and stage: "the tile has landed"
     auto sm_o = [&](int w, int row, int d) -> float& {
         return reinterpret_cast<float*>(smem_dyn + (size_t)w * WARP_BYTES)[row * (HD + 1) + d];
     };
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
+    if constexpr (CLUSTER) (void)cg::this_cluster().barrier_arrive();   // phase 1 ("this CTA runs"), awaited before the merge
     pdl_trigger();
     pdl_wait();   // queries, the pages of this step and the step's index arrays come from earlier kernels
 
@@ -184,20 +209,6 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
     const int tile_begin = tile_lo + split * tps;
     const int tile_end = min(tile_begin + tps, tile_hi + 1);
 
-    // ---- Q fragments (A operand, natural layout) straight from global memory
-    uint32_t qa[KSTEPS][4];
-    {
-        const __nv_bfloat16* q0 = p.q + ((size_t)row_tok[0] * p.nh + row_head[0]) * HD;
-        const __nv_bfloat16* q1 = p.q + ((size_t)row_tok[1] * p.nh + row_head[1]) * HD;
-#pragma unroll
-        for (int k = 0; k < KSTEPS; ++k) {
-            qa[k][0] = row_ok[0] ? *reinterpret_cast<const uint32_t*>(q0 + 16 * k + 2 * t) : 0u;
-            qa[k][1] = row_ok[1] ? *reinterpret_cast<const uint32_t*>(q1 + 16 * k + 2 * t) : 0u;
-            qa[k][2] = row_ok[0] ? *reinterpret_cast<const uint32_t*>(q0 + 16 * k + 8 + 2 * t) : 0u;
-            qa[k][3] = row_ok[1] ? *reinterpret_cast<const uint32_t*>(q1 + 16 * k + 8 + 2 * t) : 0u;
-        }
-    }
-
     float o[NT_O][4];
 #pragma unroll
     for (int i = 0; i < NT_O; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
@@ -233,19 +244,48 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
     const bool tma = p.use_tma != 0;
     const uint32_t bar0 = (uint32_t)__cvta_generic_to_shared(&tma_bar[warp][0]);
     if (tma && lane == 0) {
-        mbar_init(bar0, 1);
-        mbar_init(bar0 + 8, 1);
+#pragma unroll
+        for (int st = 0; st < STAGES; ++st) mbar_init(bar0 + 8 * st, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
-    auto tma_tile = [&](int kt, int stage) {   // lane 0 only
+    // This warp's tiles are tile_begin + warp + WARPS * j, j = 0, 1, ...  With pages of 16 tokens or
+    // more a tile lies in one page; lane l then holds the page number of tile j_base + l, read 32
+    // tiles at a time (one coalesced look-up instead of one dependent load per tile).
+    int pg = 0, j_base = 0;
+    auto read_pages = [&](int jb) {
+        j_base = jb;
+        const int kt2 = tile_begin + warp + WARPS * (jb + lane);
+        const int key = kt2 * TILE;
+        const bool live = kt2 < tile_end && key + TILE - 1 >= lo_g && key <= pos_last;
+        pg = live ? table[key >> p.page_shift] : 0;   // a tile wholly outside [lo_g, pos_last] reads page 0 (masked)
+    };
+    if (p.use_tma == 2) read_pages(0);
+    // bring tile number j of this warp into `stage` (the whole warp calls; lane 0 issues)
+    auto tma_tile = [&](int j, int stage) {
+        const int kt2 = tile_begin + warp + WARPS * j;
         const uint32_t dst = ring + stage * 2 * TILE_BYTES;
         const uint32_t bar = bar0 + 8 * stage;
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier generic accesses to the stage come first
+        if (p.use_tma == 2) {
+            // one 5-d copy: [K, V] x [column boxes] x [16 rows] x [64 columns], the layout of a stage
+            if (j - j_base >= 32) read_pages(j_base + 32);
+            const int page = __shfl_sync(0xffffffffu, pg, j - j_base);
+            if (lane == 0) {
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier generic accesses to the stage come first
+                mbar_expect_tx(bar, 2 * TILE_BYTES);
+                tma_load_5d(dst, &map, bar, 0, kvh * p.page_size + ((kt2 * TILE) & (p.page_size - 1)), 0, 0, page);
+            }
+            return;
+        }
+        if (lane != 0) return;
+        // pages under 16 tokens: a tile is HD / 64 column boxes of 128 bytes (the swizzle span) for K
+        // and for V, each 16 / box_rows row pieces (one piece per page the tile touches).  Stage layout:
+        // [K col 0][K col 1]..[V col 0].., every box 16 rows x 128 B = 2 KB, 128B-swizzled by the copy engine.
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         mbar_expect_tx(bar, 2 * TILE_BYTES);
         const int pieces = TILE / p.box_rows;
         for (int pc = 0; pc < pieces; ++pc) {
-            const int key = kt * TILE + pc * p.box_rows;
+            const int key = kt2 * TILE + pc * p.box_rows;
             // a piece wholly outside [lo_g, pos_last] still has to be filled: read page 0 (its scores are masked)
             const int lp = key >> p.page_shift;
             const bool live = key + p.box_rows - 1 >= lo_g && key <= pos_last;
@@ -269,25 +309,50 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
     const bool upper = __any_sync(0xffffffffu, row_ok[1]);   // does any lane own a valid row among rows 8..15?
     const float sl2 = p.scale * 1.44269504088896341f;        // log2(e): maxima and scores live in base 2
 
-    int kt = tile_begin + warp;
-    if (kt < tile_end) {
-        if (!tma) load_tile(kt, 0);
-        else if (lane == 0) tma_tile(kt, 0);
+    // ---- the first STAGES - 1 tiles go out before anything else is read
+    const int n_mine = tile_begin + warp < tile_end ? (tile_end - tile_begin - warp + WARPS - 1) / WARPS : 0;
+#pragma unroll
+    for (int j = 0; j < STAGES - 1; ++j) {
+        if (j < n_mine) {
+            if (!tma) load_tile(tile_begin + warp + WARPS * j, j);
+            else tma_tile(j, j);
+        }
+        cp_async_commit();
     }
-    cp_async_commit();
-    for (int it = 0; kt < tile_end; kt += WARPS, ++it) {
-        const int stage = it & 1;
-        if (kt + WARPS < tile_end) {
-            if (!tma) load_tile(kt + WARPS, stage ^ 1);
-            else if (lane == 0) tma_tile(kt + WARPS, stage ^ 1);
+
+    // ---- Q fragments (A operand, natural layout) straight from global memory
+    uint32_t qa[KSTEPS][4];
+    {
+        const __nv_bfloat16* q0 = p.q + ((size_t)row_tok[0] * p.nh + row_head[0]) * HD;
+        const __nv_bfloat16* q1 = p.q + ((size_t)row_tok[1] * p.nh + row_head[1]) * HD;
+#pragma unroll
+        for (int k = 0; k < KSTEPS; ++k) {
+            qa[k][0] = row_ok[0] ? *reinterpret_cast<const uint32_t*>(q0 + 16 * k + 2 * t) : 0u;
+            qa[k][1] = row_ok[1] ? *reinterpret_cast<const uint32_t*>(q1 + 16 * k + 2 * t) : 0u;
+            qa[k][2] = row_ok[0] ? *reinterpret_cast<const uint32_t*>(q0 + 16 * k + 8 + 2 * t) : 0u;
+            qa[k][3] = row_ok[1] ? *reinterpret_cast<const uint32_t*>(q1 + 16 * k + 8 + 2 * t) : 0u;
+        }
+    }
+
+    if constexpr (CLUSTER) {
+        // phase 1 of the cluster barrier (every CTA of the cluster runs, so its shared memory may be written
+        // by the merge below); waited for here, where the first tiles are still on their way
+        if (p.n_splits > 1) cg::this_cluster().barrier_wait();
+    }
+    for (int it = 0; it < n_mine; ++it) {
+        const int kt = tile_begin + warp + WARPS * it;
+        const int stage = it % STAGES;
+        if (it + STAGES - 1 < n_mine) {   // the stage that was read in the last iteration
+            if (!tma) load_tile(kt + WARPS * (STAGES - 1), (it + STAGES - 1) % STAGES);
+            else tma_tile(it + STAGES - 1, (it + STAGES - 1) % STAGES);
         }
         cp_async_commit();
         const int key0 = kt * TILE;
         const uint32_t k_tile = ring + stage * 2 * TILE_BYTES, v_tile = k_tile + TILE_BYTES;
         if (!tma) {
-            cp_async_wait<1>();
+            cp_async_wait<STAGES - 1>();
         } else {
-            const uint32_t parity = (it >> 1) & 1;
+            const uint32_t parity = (it / STAGES) & 1;
             uint32_t spins = 0;
             while (!mbar_try_wait(bar0 + 8 * stage, parity)) {
                 if (++spins > TMA_WAIT_LIMIT) { timed_out = true; break; }
@@ -329,7 +394,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
 #pragma unroll
         for (int c = 0; c < 4; ++c) { s[0][c] += s2[0][c]; s[1][c] += s2[1][c]; }
         // ---- mask, scale, online softmax (rows g: c = 0, 1; rows g + 8: c = 2, 3).  Scores are kept
-        // in units of log2(e) so that exp2f serves; when no lane has a valid row among the upper
+        // in units of log2(e) so that ex2 serves; when no lane has a valid row among the upper
         // eight (a decode token of a model with at most 8 query heads per key/value head) that
         // half is skipped, and the accumulator is rescaled only when some row's maximum moved.
         float tile_max[2] = {-INFINITY, -INFINITY};
@@ -354,15 +419,15 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
             const float m_new = fmaxf(m_run[r], tile_max[r]);
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
             if (m_new != m_run[r]) {
-                alpha[r] = exp2f(m_run[r] - m_use);
+                alpha[r] = ex2(m_run[r] - m_use);
                 moved = true;
             }
             m_run[r] = m_new;
             float sum = 0.f;
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                s[i][2 * r] = exp2f(s[i][2 * r] - m_use);
-                s[i][2 * r + 1] = exp2f(s[i][2 * r + 1] - m_use);
+                s[i][2 * r] = ex2(s[i][2 * r] - m_use);
+                s[i][2 * r + 1] = ex2(s[i][2 * r + 1] - m_use);
                 sum += s[i][2 * r] + s[i][2 * r + 1];
             }
             l_run[r] = l_run[r] * alpha[r] + sum;  // this lane's share; the quad is summed at the end
@@ -392,7 +457,8 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
     if (timed_out && p.err_flag) atomicExch(p.err_flag, ERR_ATTN_TIMEOUT);   // the result of this group is wrong; the host reads the flag
     __syncwarp();
 
-    // ---- merge the warps of the CTA
+    // ---- merge the warps of the CTA: (max, sum) per warp and row, the accumulators of the valid
+    // row halves, then one pass over the valid (row, dim) elements
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
@@ -406,37 +472,65 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
     for (int i = 0; i < NT_O; ++i)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
+            if (c >= 2 && !upper) continue;   // rows 8..15 are all invalid
             sm_o(warp, g + 8 * (c >> 1), 8 * i + 2 * t + (c & 1)) = o[i][c];
         }
+    // which of the 16 rows are real (token, head) pairs, and where their output rows start
+    if (threadIdx.x < 16) {
+        const int row = threadIdx.x, ti = row / p.hpg, hi = row % p.hpg;
+        const bool v = ti < n_tok && ti < p.tpg && hb * p.hpg + hi < n_rep;
+        sm_th[row] = v ? (tok0 + ti) * p.nh + (kvh * n_rep + hb * p.hpg + hi) : -1;
+    }
     __syncthreads();
 
-    for (int e = threadIdx.x; e < 16 * HD; e += WARPS * 32) {
-        const int row = e / HD, d = e % HD;
-        const int ti = row / p.hpg, hi = row % p.hpg;
-        const int h_in_kv = hb * p.hpg + hi;
-        if (!(ti < n_tok && ti < p.tpg && h_in_kv < n_rep)) continue;
+    int n_cl = 1, rank = 0, cp = HD;   // cluster size, this CTA's rank, output dims owned per rank
+    if constexpr (CLUSTER) {
+        if (p.n_splits > 1) {
+            n_cl = p.n_splits;
+            rank = (int)cg::this_cluster().block_rank();
+            cp = (HD + n_cl - 1) / n_cl;
+        }
+    }
+    // four consecutive output dims of a row per thread
+    for (int e = threadIdx.x; e < 16 * (HD / 4); e += WARPS * 32) {
+        const int row = e / (HD / 4), d4 = e % (HD / 4), d = 4 * d4;
+        const int th_row = sm_th[row];
+        if (th_row < 0) continue;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) M = fmaxf(M, sm_m[w][row]);
         const float m_use = (M == -INFINITY) ? 0.f : M;
-        float L = 0.f, O = 0.f;
+        float L = 0.f, O[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
-            const float f = exp2f(sm_m[w][row] - m_use);
+            const float f = ex2(sm_m[w][row] - m_use);
             L += sm_l[w][row] * f;
-            O += sm_o(w, row, d) * f;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) O[k] += sm_o(w, row, d + k) * f;
         }
-        const size_t th = (size_t)(tok0 + ti) * p.nh + (kvh * n_rep + h_in_kv);
+        const size_t th = (size_t)th_row;
         if (p.n_splits == 1) {
-            p.out[th * HD + d] = __float2bfloat16_rn(O / L);
+            const float inv = 1.0f / L;
+            *reinterpret_cast<uint2*>(p.out + th * HD + d) = make_uint2(pack_bf16(O[0] * inv, O[1] * inv), pack_bf16(O[2] * inv, O[3] * inv));
         } else if constexpr (CLUSTER) {
-            // keep this CTA's merged partial in its own shared memory: element (row, d) of warp
-            // slot 1 is read by this thread only, so it can be overwritten now; the row's max
-            // and sum are read by many threads and get arrays of their own
-            sm_o(1, row, d) = O;
-            if (d == 0) { sm_cm[row] = M; sm_cl[row] = L; }
+            // push this CTA's partial to the CTA that owns the output dims: slot [this rank][row][d - owner * cp]
+            // of its receive buffer; the row's (max, sum) go to every CTA
+            cg::cluster_group cluster = cg::this_cluster();
+            if ((cp & 3) == 0) {
+                const int owner = d / cp;
+                *reinterpret_cast<float4*>(cluster.map_shared_rank(&rx_o[(rank * 16 + row) * cp + (d - owner * cp)], owner)) =
+                    make_float4(O[0], O[1], O[2], O[3]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int owner = (d + k) / cp;
+                    *cluster.map_shared_rank(&rx_o[(rank * 16 + row) * cp + (d + k - owner * cp)], owner) = O[k];
+                }
+            }
+            for (int c = d4; c < n_cl; c += HD / 4)
+                *reinterpret_cast<float2*>(cluster.map_shared_rank(&rx_ml[(rank * 16 + row) * 2], c)) = make_float2(M, L);
         } else {
-            p.part_acc[(th * p.n_splits + split) * HD + d] = O;
+            *reinterpret_cast<float4*>(p.part_acc + (th * p.n_splits + split) * HD + d) = make_float4(O[0], O[1], O[2], O[3]);
             if (d == 0) {
                 p.part_ml[(th * p.n_splits + split) * 2] = M;
                 p.part_ml[(th * p.n_splits + split) * 2 + 1] = L;
@@ -445,41 +539,28 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
     }
     if constexpr (CLUSTER) {
         if (p.n_splits > 1) {
+            // phase 2: all partials have arrived (release / acquire); nobody touches remote memory afterwards,
+            // so a CTA may leave as soon as it has written its share of the output
             cg::cluster_group cluster = cg::this_cluster();
-            cluster.sync();
-            const int n = p.n_splits, rank = (int)cluster.block_rank();
-            for (int e = threadIdx.x * n + rank; e < 16 * HD; e += WARPS * 32 * n) {
-                const int row = e / HD, d = e % HD;
-                const int ti = row / p.hpg, hi = row % p.hpg;
-                const int h_in_kv = hb * p.hpg + hi;
-                if (!(ti < n_tok && ti < p.tpg && h_in_kv < n_rep)) continue;
-                // all remote loads first (they are independent), then the arithmetic
-                float pm[16], pl[16], po[16];
-#pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    if (c < n) {
-                        pm[c] = *cluster.map_shared_rank(&sm_cm[row], c);
-                        pl[c] = *cluster.map_shared_rank(&sm_cl[row], c);
-                        po[c] = *cluster.map_shared_rank(&sm_o(1, row, d), c);
-                    } else {
-                        pm[c] = -INFINITY; pl[c] = 0.f; po[c] = 0.f;
-                    }
-                }
+            (void)cluster.barrier_arrive();
+            cluster.barrier_wait();
+            const int d0 = rank * cp, n_own = min(cp, HD - d0);   // may be <= 0 for the last ranks
+            for (int e = threadIdx.x; e < 16 * n_own; e += WARPS * 32) {
+                const int row = e / n_own, dl = e - row * n_own;
+                const int th_row = sm_th[row];
+                if (th_row < 0) continue;
                 float M = -INFINITY;
-#pragma unroll
-                for (int c = 0; c < 16; ++c) M = fmaxf(M, pm[c]);
+                for (int c = 0; c < n_cl; ++c) M = fmaxf(M, rx_ml[(c * 16 + row) * 2]);
                 const float m_use = (M == -INFINITY) ? 0.f : M;
                 float L = 0.f, O = 0.f;
-#pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    const float f = exp2f(pm[c] - m_use);
-                    L += pl[c] * f;
-                    O += po[c] * f;
+                for (int c = 0; c < n_cl; ++c) {
+                    const float2 ml = *reinterpret_cast<const float2*>(&rx_ml[(c * 16 + row) * 2]);
+                    const float f = ex2(ml.x - m_use);
+                    L += ml.y * f;
+                    O += rx_o[(c * 16 + row) * cp + dl] * f;
                 }
-                const size_t th = (size_t)(tok0 + ti) * p.nh + (kvh * n_rep + h_in_kv);
-                p.out[th * HD + d] = __float2bfloat16_rn(O / L);
+                p.out[(size_t)th_row * HD + d0 + dl] = __float2bfloat16_rn(O / L);
             }
-            cluster.sync();   // nobody leaves while a peer may still read its shared memory
         }
     }
 }
@@ -542,10 +623,26 @@ bool make_cache_map(CUtensorMap* map, const void* cache, long long rows, int hd,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The cache layer as a 5-d tensor for whole-tile copies (pages of 16 tokens or more):
+// [page][K, V][column box of 64][row = kv head * page_size + slot][64 columns]; a box is one tile:
+// 1 page x 2 x (hd / 64) x 16 rows x 64 columns, which lands as [K col 0][K col 1]..[V col 0].. .
+bool make_cache_map_5d(CUtensorMap* map, const void* cache, long long n_pages, int nkv, int page_size, int hd) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) return false;
+    const cuuint64_t row_bytes = (cuuint64_t)hd * 2, kv_bytes = (cuuint64_t)nkv * page_size * row_bytes;
+    cuuint64_t dims[5] = {64, (cuuint64_t)nkv * page_size, (cuuint64_t)(hd / 64), 2, (cuuint64_t)n_pages};
+    cuuint64_t strides[4] = {row_bytes, 128, kv_bytes, 2 * kv_bytes};
+    cuuint32_t box[5] = {64, (cuuint32_t)TILE, (cuuint32_t)(hd / 64), 2, 1};
+    cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(cache), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int HD>
 int launch(const CUtensorMap& map, const AttnParams& p, int n_groups_bound, bool use_cluster, cudaStream_t stream) {
     dim3 grid(n_groups_bound, p.nkv * p.head_blocks, p.n_splits);
-    constexpr int SMEM = WARPS * 2 * 2 * TILE * HD * 2 + 1024;   // per warp: two stages of a K and a V tile; alignment slack
+    constexpr int SMEM = WARPS * STAGES * 2 * TILE * HD * 2 + 1024;   // per warp: the stages of a K and a V tile; alignment slack
     static bool configured = false;
     if (!configured) {   // more than 48 KB of dynamic shared memory and clusters of more than 8 CTAs are opt-ins
         cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -618,7 +715,11 @@ PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* ou
     p.use_tma = 0;
     if (p.page_shift >= 0 && hd % 64 == 0 && n_pages > 0 && ((uintptr_t)cache & 127) == 0 &&
         n_pages * 2 * nkv * page_size < (1ll << 31))
-        p.use_tma = make_cache_map(&map, cache, n_pages * 2 * nkv * page_size, hd, p.box_rows) ? 1 : 0;
+    {
+        // whole-tile copies when a tile lies in one page; if the driver refuses the 5-d map, the 2-d one serves
+        if (page_size >= TILE && make_cache_map_5d(&map, cache, n_pages, nkv, page_size, hd)) p.use_tma = 2;
+        else p.use_tma = make_cache_map(&map, cache, n_pages * 2 * nkv * page_size, hd, p.box_rows) ? 1 : 0;
+    }
     const int n_rep = nh / nkv;
     p.hpg = n_rep < 16 ? n_rep : 16;
     p.tpg = 16 / p.hpg;

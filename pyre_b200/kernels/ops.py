@@ -286,7 +286,8 @@ def attention_splits(n_tokens: int, n_seqs: int, n_heads: int, n_kv_heads: int, 
     tiles = -(-span // 16) + 1
     want = max(1, min(2 * _SM_COUNT // max(ctas, 1), -(-tiles // 2), CLUSTER_MAX_SPLITS))
     if want > 8:
-        return 16 if want >= 12 else 8
+        # a cluster of 16 CTAs must sit in one GPC: it pays only while all of them fit on the chip at once
+        return 16 if ctas * 16 <= _SM_COUNT else 8
     return int(want)
 
 
