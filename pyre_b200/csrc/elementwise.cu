@@ -320,7 +320,7 @@ PYRE_API int pyre_qkv_rope_write(const void* qkv, const float* partials, int n_p
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i],  silu(z) = z / (1 + exp(-z))  in fp32.
 // ---------------------------------------------------------------------------
 template <typename T, int VEC>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tokens, int I) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tokens, int I, int block) {
     pdl_trigger();
     pdl_wait();
     const size_t per_row = (size_t)(I / VEC);
@@ -329,8 +329,11 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
         const size_t t = idx / per_row;
         const int i = (int)(idx - t * per_row) * VEC;
         const T* row = gu + t * (size_t)(2 * I);
-        Vec<T, VEC> g = load_vec<T, VEC>(row + i);
-        Vec<T, VEC> u = load_vec<T, VEC>(row + I + i);
+        // block == 0: [all gates | all ups]; else gates and ups alternate in blocks of `block` features
+        const int gi = block ? (i / block) * 2 * block + i % block : i;
+        const int ui = block ? gi + block : I + i;
+        Vec<T, VEC> g = load_vec<T, VEC>(row + gi);
+        Vec<T, VEC> u = load_vec<T, VEC>(row + ui);
         Vec<T, VEC> o;
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
@@ -342,14 +345,17 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
     }
 }
 
-PYRE_API int pyre_silu_mul(const void* gu, void* out, int n_tokens, int I, int dtype, cudaStream_t stream) {
+// block: 0 for gate_up = [gates | ups]; n > 0 for gates and ups interleaved in blocks of n features
+// (n a multiple of 8 that divides I).
+PYRE_API int pyre_silu_mul(const void* gu, void* out, int n_tokens, int I, int block, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0 || I <= 0) return 0;
+    if (block < 0 || (block > 0 && (block % 8 || I % block))) return PYRE_ERR_BAD_ARG;
     const int threads = 256;
 #define LAUNCH(TT, V)                                                                                      \
     do {                                                                                                   \
         long long total = (long long)n_tokens * (I / V);                                                   \
         int blocks = (int)min((long long)148 * 16, ceil_div_ll(total, threads));                           \
-        pyre_launch(silu_mul_kernel<TT, V>, dim3(blocks), dim3(threads), 0, stream, (const TT*)gu, (TT*)out, n_tokens, I);      \
+        pyre_launch(silu_mul_kernel<TT, V>, dim3(blocks), dim3(threads), 0, stream, (const TT*)gu, (TT*)out, n_tokens, I, block);      \
     } while (0)
     if (dtype == PYRE_F32) { if (I % 4 == 0) LAUNCH(float, 4); else LAUNCH(float, 1); }
     else if (dtype == PYRE_BF16) { if (I % 8 == 0) LAUNCH(__nv_bfloat16, 8); else if (I % 4 == 0) LAUNCH(__nv_bfloat16, 4); else LAUNCH(__nv_bfloat16, 1); }

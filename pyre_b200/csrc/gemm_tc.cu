@@ -112,6 +112,8 @@ struct GemmParams {
     void* out;
     int out_f32;
     int x_is_constant;            // 1: X holds weights (may be loaded before the kernels before this one finish); 0: Y does
+    int gated;                    // 1: the y rows are gate/up weights interleaved in blocks of 128 (gate rows, then the up
+                                  // rows of the same features); the epilogue writes silu(gate) * up, half as many columns
     int* err_flag;
 };
 
@@ -269,6 +271,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const long long out_base = (long long)blockIdx.z * p.split_stride + (long long)xr * p.stride_x;
             const uint32_t acc = tmem_base + buf * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+            if constexpr (!X_CONTIGUOUS_OUT && BN == 256) {
+                if (p.gated) {
+                    // columns 0..127 of the tile are gate features, 128..255 the up features of the same
+                    // indices: out[x, y0 / 2 + c] = silu(gate) * up, with the products rounded to bfloat16
+                    // first (as a separate activation kernel would read them) and the rest in fp32
+#pragma unroll 1
+                    for (int c = 0; c < 128; c += 16) {
+                        uint32_t g[16], u[16];
+                        __syncwarp();
+                        tmem_ld16(acc + c, g);
+                        tmem_ld16(acc + 128 + c, u);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (alive && xr < p.x_rows) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                float o[2];
+#pragma unroll
+                                for (int e = 0; e < 2; ++e) {
+                                    const float z = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[2 * q + e])));
+                                    const float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[2 * q + e])));
+                                    o[e] = __fmul_rn(z / (1.0f + expf(-z)), v);
+                                }
+                                __nv_bfloat162 pr = __floats2bfloat162_rn(o[0], o[1]);
+                                w[q] = *reinterpret_cast<uint32_t*>(&pr);
+                            }
+                            uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)p.out + out_base + (y0 >> 1) + c);
+                            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        }
+                    }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
+                    continue;
+                }
+            }
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 uint32_t r[16];
@@ -392,11 +431,15 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, di
 // store (X = weights), stride_y == 1 the row store (X = tokens).  bn: tile width along y, one of
 // 16, 32, 64, 128, 256.  splits >= 1 divides the K blocks among blockIdx.z.  x_is_constant says
 // which operand holds weights: its first tiles are fetched before the kernel waits for the
-// kernels before it in the stream (programmatic dependent launch).
+// kernels before it in the stream (programmatic dependent launch).  gated: Y holds gate and up
+// weights interleaved in blocks of 128 rows; out[x, j] = silu(D[x, gate row of j]) * D[x, up row of j]
+// for j < y_rows / 2 (row store, bn 256, one split, bf16 out).
 PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* Y, int y_rows, long long ldy, int K,
                           void* out, int out_f32, long long stride_x, long long stride_y, long long split_stride,
-                          int splits, int bn, int x_is_constant, int* err_flag, cudaStream_t stream) {
+                          int splits, int bn, int x_is_constant, int gated, int* err_flag, cudaStream_t stream) {
     if (x_rows <= 0 || y_rows <= 0) return 0;
+    // the gated epilogue: tokens on the row side, whole 256-wide tiles of interleaved gate/up rows, bf16 rows out
+    if (gated && (stride_y != 1 || bn != 256 || splits != 1 || out_f32 || y_rows % 256)) return PYRE_ERR_BAD_ARG;
     if (K <= 0 || K % 8 || ldx % 8 || ldy % 8 || splits < 1) return PYRE_ERR_UNSUPPORTED;
     if (((uintptr_t)X & 15) || ((uintptr_t)Y & 15)) return PYRE_ERR_UNSUPPORTED;
     if (stride_x != 1 && stride_y != 1) return PYRE_ERR_BAD_ARG;
@@ -413,7 +456,7 @@ PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* 
     p.x_rows = x_rows; p.y_rows = y_rows; p.K = K;
     p.k_blocks_per_split = (total_kb + splits - 1) / splits;
     p.stride_x = stride_x; p.stride_y = stride_y; p.split_stride = split_stride;
-    p.out = out; p.out_f32 = out_f32; p.x_is_constant = x_is_constant; p.err_flag = err_flag;
+    p.out = out; p.out_f32 = out_f32; p.x_is_constant = x_is_constant; p.err_flag = err_flag; p.gated = gated ? 1 : 0;
     p.tiles_x = ceil_div(x_rows, BM); p.tiles_y = ceil_div(y_rows, bn);
     const long long n_tiles = (long long)p.tiles_x * p.tiles_y;
     // one CTA per SM stays resident and walks the tiles (a split K keeps one CTA per tile and split)

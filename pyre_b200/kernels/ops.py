@@ -202,16 +202,19 @@ def qkv_rope_write(qkv: torch.Tensor, bias: "torch.Tensor | None", cos: torch.Te
     return q_out
 
 
-def silu_mul(gate_up: torch.Tensor, out: "torch.Tensor | None" = None) -> torch.Tensor:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+def silu_mul(gate_up: torch.Tensor, out: "torch.Tensor | None" = None, block: int = 0) -> torch.Tensor:
+    """out[t, i] = silu(gate[t, i]) * up[t, i].  ``block == 0``: gate_up = [all gates | all ups];
+    ``block == n``: gates and ups alternate in blocks of n features (n gates, their n ups, ...)."""
     _check(gate_up, "gate_up", dim=2)
     T, two_i = gate_up.shape
     if two_i % 2:
         raise ValueError("gate_up must have an even number of columns")
     inter = two_i // 2
+    if block and (block % 8 or inter % block):
+        raise UnsupportedSize(f"silu_mul: blocks of {block} features do not tile {inter} features in steps of 8")
     if out is None:
         out = torch.empty((T, inter), dtype=gate_up.dtype, device=gate_up.device)
-    lib.call("pyre_silu_mul", gate_up.data_ptr(), out.data_ptr(), T, inter, _dt(gate_up.dtype), _stream())
+    lib.call("pyre_silu_mul", gate_up.data_ptr(), out.data_ptr(), T, inter, int(block), _dt(gate_up.dtype), _stream())
     return out
 
 
@@ -493,13 +496,20 @@ def tc_gemm_plan(M: int, N: int, K: int) -> tuple[bool, int, int]:
     return False, bn, splits
 
 
+GATED_BLOCK = 128    # gate and up rows of a fused feed-forward weight alternate in blocks of this many features
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-            plan: "tuple[bool, int, int] | None" = None, reduce: bool = True) -> torch.Tensor:
+            plan: "tuple[bool, int, int] | None" = None, reduce: bool = True, gated: bool = False) -> torch.Tensor:
     """y = x w^T on the tensor cores (tcgen05, TMEM accumulators, TMA-fed), bf16 in, fp32 accumulate.
 
     With a split K the kernel leaves fp32 partial sums [splits, M, N]; ``reduce`` adds
     them up here (fixed order) and converts to ``out_dtype``.  ``reduce=False`` returns them
-    as ``PartialSums`` for a consumer kernel that adds them itself."""
+    as ``PartialSums`` for a consumer kernel that adds them itself.
+
+    ``gated``: w holds gate and up rows alternating in blocks of ``GATED_BLOCK`` features; the
+    result is silu(x gate^T) * (x up^T), [M, N / 2] bf16.  With the tokens on the row side and
+    whole 256-wide tiles the activation runs in the product's epilogue; otherwise after it."""
     if not tc_gemm_supported(x, w):
         raise UnsupportedSize("gemm_tc needs bf16 operands with K and leading dimensions that are multiples of 8")
     M, K = x.shape
@@ -509,6 +519,15 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     weights_as_rows, bn, splits = plan or tc_gemm_plan(M, N, K)
     splits = max(1, min(splits, -(-K // 64)))
     err = device_error_flag(x.device)
+    if gated:
+        if N % (2 * GATED_BLOCK) or out_dtype != torch.bfloat16:
+            raise UnsupportedSize("a gated product needs whole blocks of gate and up rows and a bfloat16 result")
+        if not weights_as_rows and bn == 256 and splits == 1:
+            out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+            lib.call("pyre_gemm_tc", x.data_ptr(), M, x.stride(0), w.data_ptr(), N, w.stride(0), K, out.data_ptr(), 0,
+                     N // 2, 1, 0, 1, bn, 0, 1, err.data_ptr(), _stream())
+            return out
+        return silu_mul(gemm_tc(x, w, torch.bfloat16, (weights_as_rows, bn, splits)), block=GATED_BLOCK)
     if splits == 1 and reduce:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         target, split_stride = out, 0
@@ -518,10 +537,10 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     f32 = int(target.dtype == torch.float32)
     if weights_as_rows:
         lib.call("pyre_gemm_tc", w.data_ptr(), N, w.stride(0), x.data_ptr(), M, x.stride(0), K, target.data_ptr(), f32,
-                 1, N, split_stride, splits, bn, 1, err.data_ptr(), _stream())
+                 1, N, split_stride, splits, bn, 1, 0, err.data_ptr(), _stream())
     else:
         lib.call("pyre_gemm_tc", x.data_ptr(), M, x.stride(0), w.data_ptr(), N, w.stride(0), K, target.data_ptr(), f32,
-                 N, 1, split_stride, splits, bn, 0, err.data_ptr(), _stream())
+                 N, 1, split_stride, splits, bn, 0, 0, err.data_ptr(), _stream())
     if target.dim() == 2:
         return target
     if not reduce:
@@ -550,6 +569,23 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: "torch.dtype | None" = N
     if out_dtype is None or out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int = GATED_BLOCK) -> torch.Tensor:
+    """[2 I, K]: ``block`` gate rows, the up rows of the same features, the next gate rows, ... (I % block == 0)."""
+    inter, K = gate.shape
+    if up.shape != gate.shape or inter % block:
+        raise UnsupportedSize(f"cannot interleave {tuple(gate.shape)} and {tuple(up.shape)} in blocks of {block}")
+    return torch.stack([gate.view(inter // block, block, K), up.view(inter // block, block, K)], dim=1).reshape(2 * inter, K).contiguous()
+
+
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool) -> torch.Tensor:
+    """silu(x gate^T) * (x up^T) for the stacked weight of a gated feed-forward: [gates | ups] rows, or
+    (``interleaved``) blocks of ``GATED_BLOCK`` gate rows and up rows in turn, which lets the bfloat16
+    tensor-core product apply the activation in its epilogue."""
+    if interleaved and x.dtype == torch.bfloat16 and USE_TC_GEMM and tc_gemm_supported(x, w_gate_up):
+        return gemm_tc(x, w_gate_up, torch.bfloat16, gated=True)
+    return silu_mul(linear(x, w_gate_up), block=GATED_BLOCK if interleaved else 0)
 
 
 def required_libraries(dtype: torch.dtype) -> list[str]:

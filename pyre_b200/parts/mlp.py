@@ -11,7 +11,9 @@ from .base import Part, register_part
 
 class GatedMLP(Part):
     """down(act(gate(h)) * up(h)) without biases.  The gate and up weights are stacked
-    into one [2 I, width] matrix at load, so one product feeds the activation kernel."""
+    into one [2 I, width] matrix at load, so one product feeds the activation; in bfloat16,
+    when I is a multiple of 128, their rows alternate in blocks of 128 features so that one
+    output tile of the product holds both halves and the activation runs in its epilogue."""
 
     graph_safe = True
 
@@ -21,6 +23,7 @@ class GatedMLP(Part):
         if activation != "silu":
             raise ops.UnsupportedSize(f"activation {activation!r}: only silu is implemented")
         self.w_gate_up = self.w_down = None
+        self.interleaved = dtype == torch.bfloat16 and self.intermediate % ops.GATED_BLOCK == 0
 
     def tensors(self):
         return {
@@ -30,15 +33,17 @@ class GatedMLP(Part):
         }
 
     def load(self, tensors):
-        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
+        if self.interleaved:
+            self.w_gate_up = ops.interleave_gate_up(tensors["gate_proj.weight"], tensors["up_proj.weight"])
+        else:
+            self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"]
 
     def kernel_libraries(self):
         return ["elementwise"] + (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_tc"])
 
     def forward(self, ctx, h):
-        gate_up = ops.linear(h, self.w_gate_up)
-        act = ops.silu_mul(gate_up)
+        act = ops.gated_linear(h, self.w_gate_up, self.interleaved)
         return ops.linear(act, self.w_down, partials_ok=True)
 
 
