@@ -150,7 +150,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     const int kb_end = min(kb_begin + p.k_blocks_per_split, total_kb);
     const int n_kb = max(kb_end - kb_begin, 0);
     const int n_tiles = p.tiles_x * p.tiles_y;
-    constexpr uint32_t ACC_COLS = BN < 32 ? 32 : BN;    // columns of one accumulator
+    constexpr uint32_t ACC_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;   // columns of one accumulator (a power of two)
     constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;        // power of two >= 32, at most 512
 
     pdl_trigger();
@@ -429,7 +429,7 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, di
 // out[z * split_stride + x * stride_x + y * stride_y] receives split z's partial sum (fp32 if
 // out_f32 else bf16).  One of stride_x, stride_y must be 1: stride_x == 1 selects the transposed
 // store (X = weights), stride_y == 1 the row store (X = tokens).  bn: tile width along y, one of
-// 16, 32, 64, 128, 256.  splits >= 1 divides the K blocks among blockIdx.z.  x_is_constant says
+// 16, 32, 64, 128, 256, and for the row store also 160, 192, 208, 224.  splits >= 1 divides the K blocks among blockIdx.z.  x_is_constant says
 // which operand holds weights: its first tiles are fetched before the kernel waits for the
 // kernels before it in the stream (programmatic dependent launch).  gated: Y holds gate and up
 // weights interleaved in blocks of 128 rows; out[x, j] = silu(D[x, gate row of j]) * D[x, up row of j]
@@ -471,6 +471,12 @@ PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* 
         case 64: GO(64, 8); break;
         case 128: GO(128, 6); break;
         case 256: GO(256, 4); break;
+        // widths between 128 and 256 exist for the row-store orientation only: they let the planner pick the
+        // tile count that fills the rounds of the persistent CTAs best
+        case 160: if (xc) return PYRE_ERR_BAD_ARG; rc = launch<160, 6, false>(mx, my, p, grid, stream); break;
+        case 192: if (xc) return PYRE_ERR_BAD_ARG; rc = launch<192, 5, false>(mx, my, p, grid, stream); break;
+        case 208: if (xc) return PYRE_ERR_BAD_ARG; rc = launch<208, 5, false>(mx, my, p, grid, stream); break;
+        case 224: if (xc) return PYRE_ERR_BAD_ARG; rc = launch<224, 5, false>(mx, my, p, grid, stream); break;
         default: return PYRE_ERR_BAD_ARG;
     }
 #undef GO

@@ -483,15 +483,26 @@ def tc_gemm_plan(M: int, N: int, K: int) -> tuple[bool, int, int]:
     Up to 128 tokens the weights take the 128-row side of the MMA and the tokens the
     narrow side (bn = tokens rounded up to 16/32/64/128); K is split so that about one
     CTA lands on every SM, each split keeping at least four 64-wide K blocks.  Beyond
-    that the tokens take the rows and 256 output features form a tile."""
+    that the tokens take the rows and 128 to 256 output features form a tile, whichever
+    width fills the rounds of the persistent CTAs best."""
     kb = -(-K // 64)
     if M <= 128 or N % 8:
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
         tiles = -(-N // 128) * -(-M // bn)
         splits = max(1, min(_SM_COUNT // tiles if tiles < _SM_COUNT else 1, kb // 4, 16))
         return True, bn, splits
-    bn = 256 if N >= 256 else 128
-    tiles = -(-M // 128) * -(-N // bn)
+    # the tile width that needs the least time on the persistent CTAs: rounds of tiles x width of a tile
+    # (3584 features of 2048 tokens: 224 tiles of 256 features take two rounds; so do 288 tiles of 208)
+    rows = -(-M // 128)
+    best = None
+    for cand in (256, 224, 208, 192, 160, 128):
+        if cand > 128 and N < cand:
+            continue
+        t = rows * -(-N // cand)
+        cost = -(-t // _SM_COUNT) * cand
+        if best is None or cost < best[0]:
+            best = (cost, cand, t)
+    _, bn, tiles = best
     splits = max(1, min(_SM_COUNT // tiles if tiles * 2 <= _SM_COUNT else 1, kb // 8, 8))
     return False, bn, splits
 
@@ -522,6 +533,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     if gated:
         if N % (2 * GATED_BLOCK) or out_dtype != torch.bfloat16:
             raise UnsupportedSize("a gated product needs whole blocks of gate and up rows and a bfloat16 result")
+        if not weights_as_rows and plan is None:
+            bn, splits = 256, 1      # the fused activation needs whole 256-wide tiles and saves more than a better fit
         if not weights_as_rows and bn == 256 and splits == 1:
             out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
             lib.call("pyre_gemm_tc", x.data_ptr(), M, x.stride(0), w.data_ptr(), N, w.stride(0), K, out.data_ptr(), 0,

@@ -142,7 +142,8 @@ def test_gemm_tc_matches_fp32_product(ops, M, N, K):
     got16 = ops.gemm_tc(a, w, torch.bfloat16)
     assert float((got16.float() - want).abs().max()) <= 2.0 ** -8 * scale
     # every plan gives the same product: both orientations, every tile width, split K
-    for plan in [(True, 16, 1), (True, 32, 3), (True, 64, 2), (True, 128, 1), (True, 256, 4), (False, 128, 1), (False, 256, 2)]:
+    for plan in [(True, 16, 1), (True, 32, 3), (True, 64, 2), (True, 128, 1), (True, 256, 4), (False, 128, 1), (False, 256, 2),
+                 (False, 160, 1), (False, 192, 2), (False, 208, 1), (False, 224, 1)]:
         if not plan[0] and N % 8:
             continue
         if plan[0] and M > 4 * plan[1]:
