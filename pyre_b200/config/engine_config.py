@@ -42,6 +42,8 @@ class EngineConfig:
     ``prefill_chunk``: most prompt tokens of one request in one step.
     ``max_model_len``: longest sequence (prompt + output); defaults to the model's
     ``max_position_embeddings`` capped by the cache capacity.
+    ``lookahead``: start a step before the ids sampled by the step before have reached the
+    host (they are fed on the device); the host work of a step then hides behind the GPU's.
     """
 
     dtype: "str | torch.dtype" = "bfloat16"
@@ -54,6 +56,7 @@ class EngineConfig:
     prefill_chunk: int = 2048
     max_model_len: int | None = None
     cuda_graphs: bool = True
+    lookahead: bool = True
     debug_poison_freed_pages: bool = False
 
     def __post_init__(self):

@@ -393,3 +393,24 @@ PYRE_API int pyre_sum_partials(const float* partials, int n_splits, long long sp
     PYRE_LAUNCH_CHECK();
     return 0;
 }
+
+// ---------------------------------------------------------------------------
+// ids[dst[i]] = prev[src[i]] for every i with dst[i] >= 0: the tokens that the last step
+// sampled become inputs of the next step without a trip through the host.
+// ---------------------------------------------------------------------------
+__global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ dst, const int* __restrict__ src,
+                                   const int* __restrict__ prev, int n) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int d = dst[i];
+    if (d >= 0) ids[d] = prev[src[i]];
+}
+
+PYRE_API int pyre_feed_tokens(int* ids, const int* dst, const int* src, const int* prev, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    pyre_launch(feed_tokens_kernel, dim3(ceil_div(n, 128)), dim3(128), 0, stream, ids, dst, src, prev, n);
+    PYRE_LAUNCH_CHECK();
+    return 0;
+}

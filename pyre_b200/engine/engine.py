@@ -21,7 +21,7 @@ from ..config import EngineConfig, ModelConfig, architecture_of, load_config
 from ..kernels import build, lib
 from ..models.model import Model
 from ..sampling import Sampler, SamplingParams
-from .scheduler import Request, Scheduler
+from .scheduler import PENDING, Request, Scheduler
 from .step import StepEntry, Stepper
 
 
@@ -74,6 +74,7 @@ class Engine:
                                    self.max_model_len)
         self.sampler = Sampler(ec.device)
         self._requests: dict[int, Request] = {}
+        self._flight = None      # (plan, sampling ticket) of the step whose ids have not been read yet
 
     # ------------------------------------------------------------------ the reference's two calls
     def add_request(self, prompt_ids: Sequence[int], max_new_tokens: int = 16, eos_id: "int | None" = None,
@@ -89,28 +90,51 @@ class Engine:
 
     def step(self) -> list[RequestOutput]:
         """One scheduler iteration: plan, run the mixed batch, sample, record.  Returns the
-        requests that finished in it."""
-        before = {r.seq_id for r in self._requests.values() if not r.done}
-        plan = self.scheduler.schedule()
-        outs = []
+        requests that finished in it.
+
+        With ``lookahead`` (the default) the step is started before the ids of the step before
+        have been read: the tokens it needs from that step are taken on the device, and the host
+        reads the older ids while the GPU is busy with the new step.  A request's result is then
+        returned one call later, and a request that hits its end-of-sequence token has computed
+        one token too many (dropped).  The ids are the same either way."""
+        sched = self.scheduler
+        plan = sched.schedule()
+        flight = None
         if plan:
-            entries = [StepEntry(s.request.seq_id, s.request.tokens(s.start, s.count),
-                                 [s.count - 1] if s.samples else []) for s in plan]
+            prev = self._flight
+            entries = []
+            for s in plan:
+                toks = s.request.tokens(s.start, s.count)
+                feed = None
+                if toks[-1] == PENDING:
+                    toks[-1], feed = 0, s.request.feed_row
+                entries.append(StepEntry(s.request.seq_id, toks, [s.count - 1] if s.samples else [], feed))
             with torch.cuda.device(self.model.device):
-                logits = self.stepper.step(entries, reserve=False)
+                logits = self.stepper.step(entries, reserve=False, fed_from=prev[1].ids if prev and prev[1] is not None else None)
                 sampling = [s for s in plan if s.samples]
-                ids = self.sampler.sample(logits, [s.request.params for s in sampling],
-                                          [len(s.request.generated) for s in sampling])
-            self.scheduler.update(plan, ids)
-        for sid in before:
-            r = self._requests[sid]
-            if r.done:
-                outs.append(RequestOutput(r.seq_id, r.prompt_ids, list(r.generated), r.finish_reason or "", r.preemptions))
-                del self._requests[sid]
+                ticket = self.sampler.sample_async(logits, [s.request.params for s in sampling],
+                                                   [len(s.request.generated) for s in sampling]) if sampling else None
+            sched.launched(plan)
+            flight = (plan, ticket)
+        if self._flight is not None:
+            self._land(self._flight)
+        self._flight = flight
+        if flight is not None and not self.engine_config.lookahead:
+            self._land(flight)
+            self._flight = None
+        outs = []
+        for sid in [sid for sid, r in self._requests.items() if r.done and not r.pending]:
+            r = self._requests.pop(sid)
+            outs.append(RequestOutput(r.seq_id, r.prompt_ids, list(r.generated), r.finish_reason or "", r.preemptions))
         return outs
 
+    def _land(self, flight) -> None:
+        """Read the ids of a started step and let the scheduler record them."""
+        plan, ticket = flight
+        self.scheduler.resolve(plan, self.sampler.read(ticket) if ticket is not None else [])
+
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
+        return self.scheduler.has_unfinished() or self._flight is not None or any(r.done for r in self._requests.values())
 
     def run(self) -> dict[int, list[int]]:
         """Run every queued request to its end: ``{seq_id: generated ids}`` (pyre/scheduler.py:105-114)."""

@@ -20,6 +20,12 @@ no look at free pages (exhaustion is a MemoryError that ends ``run``).  Here:
 * the token that completes a request (end-of-sequence id or the last allowed token) is
   kept (pyre/scheduler.py:82), and a finished request takes part in no further step
   (the reference lets a request that finishes at admission decode once more).
+
+A step may be planned while the tokens of the step before are still on the device:
+``launched`` records a step that has been started (its sampled tokens stand in the requests
+as ``PENDING``), ``resolve`` fills in the values when they have arrived.  ``update`` is the
+two in a row.  With one step in flight a request may run one token past its end-of-sequence
+token; that token is dropped when it arrives.
 """
 
 from __future__ import annotations
@@ -31,6 +37,7 @@ from ..cache import CacheManager
 from ..sampling.params import SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+PENDING = -1     # a token that has been sampled on the device and not yet been read back
 
 
 @dataclass
@@ -43,6 +50,9 @@ class Request:
     num_computed: int = 0          # tokens whose keys and values are in the cache
     finish_reason: "str | None" = None
     preemptions: int = 0
+    pending: int = 0               # steps in flight that will deliver a token of this request
+    closed: bool = False           # the tokens in flight complete it by length: nothing more is asked for
+    feed_row: int = -1             # row of its newest pending token among the ids of the step in flight
 
     @property
     def cur_len(self) -> int:
@@ -69,6 +79,7 @@ class Scheduled:
     start: int
     count: int
     samples: bool
+    slot: int = -1                 # index in ``request.generated`` of the token this entry samples (set by ``launched``)
 
 
 @dataclass
@@ -123,6 +134,8 @@ class Scheduler:
         if r.status == RUNNING:
             self.cache.end(r.seq_id)
             self.running.remove(r)
+        elif r in self.waiting:
+            self.waiting.remove(r)    # preempted, and the token that was in flight meanwhile ends it
         r.status = FINISHED
         r.finish_reason = reason
         self.stats.finished += 1
@@ -159,11 +172,11 @@ class Scheduler:
             return True
 
         # 1. requests that are decoding (one token each), oldest first
-        for r in [r for r in self.running if r.cur_len - r.num_computed == 1]:
+        for r in [r for r in self.running if r.cur_len - r.num_computed == 1 and not r.closed]:
             if r.status == RUNNING and budget > 0:
                 try_schedule(r)
         # 2. requests in the middle of their prompt (or of a recompute)
-        for r in [r for r in self.running if r.cur_len - r.num_computed > 1]:
+        for r in [r for r in self.running if r.cur_len - r.num_computed > 1 and not r.closed]:
             if r.status == RUNNING and budget > 0 and r.seq_id not in planned:
                 try_schedule(r)
         for r in aborted:
@@ -171,6 +184,8 @@ class Scheduler:
         # 3. admit waiting requests while there is budget, a slot and room for a first portion
         while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs and self.cache.has_free_slot():
             r = self.waiting[0]
+            if r.pending:
+                break    # preempted with a token still in flight: its recompute needs the value
             count = min(r.cur_len, self.prefill_chunk, budget)
             self.cache.begin(r.seq_id)
             if not self.cache.reserve(r.seq_id, count):
@@ -194,24 +209,53 @@ class Scheduler:
         return plan
 
     # ------------------------------------------------------------------ results
-    def update(self, plan: Sequence[Scheduled], sampled: Sequence[int]) -> list[Request]:
-        """Record a finished step: ``sampled`` holds one token per plan entry with
-        ``samples`` set, in plan order.  Returns the requests that finished since the last
-        call, those that ``schedule`` ended with "cache_full" included."""
-        it = iter(sampled)
+    def launched(self, plan: Sequence[Scheduled]) -> None:
+        """Record that the step of ``plan`` has been started: its tokens count as computed and
+        every token it samples stands in its request as ``PENDING`` until ``resolve``."""
+        row = 0
         for s in plan:
             r = s.request
             r.num_computed = s.start + s.count
             if not s.samples:
                 continue
+            s.slot = len(r.generated)
+            r.generated.append(PENDING)
+            r.pending += 1
+            r.feed_row = row
+            row += 1
+            if len(r.generated) >= r.params.max_new_tokens or r.cur_len >= self.max_model_len:
+                r.closed = True
+
+    def resolve(self, plan: Sequence[Scheduled], sampled: Sequence[int]) -> list[Request]:
+        """The ids sampled by the step of ``plan`` (one per entry with ``samples`` set, in plan
+        order) have arrived.  Returns the requests that finished since the last call, those
+        that ``schedule`` ended with "cache_full" included."""
+        it = iter(sampled)
+        for s in plan:
+            if not s.samples:
+                continue
             tok = int(next(it))
-            r.generated.append(tok)
+            r = s.request
+            r.pending -= 1
+            if s.slot >= len(r.generated):
+                continue                      # the request ended before this token (end of sequence one step earlier)
+            r.generated[s.slot] = tok
+            if r.status == FINISHED:
+                continue                      # ended by the scheduler while the step was in flight; the token is kept
             p = r.params
             if p.eos_id is not None and tok == p.eos_id and not p.ignore_eos:
+                del r.generated[s.slot + 1:]  # a token asked for beyond the end is dropped when it arrives
                 self._finish(r, "eos")
-            elif len(r.generated) >= p.max_new_tokens:
+            elif s.slot + 1 >= p.max_new_tokens:
                 self._finish(r, "length")
-            elif r.cur_len >= self.max_model_len:
+            elif len(r.prompt_ids) + s.slot + 1 >= self.max_model_len:
                 self._finish(r, "max_model_len")
         finished, self._finished_now = self._finished_now, []
         return finished
+
+    def update(self, plan: Sequence[Scheduled], sampled: Sequence[int]) -> list[Request]:
+        """Record a finished step: ``sampled`` holds one token per plan entry with
+        ``samples`` set, in plan order.  Returns the requests that finished since the last
+        call, those that ``schedule`` ended with "cache_full" included."""
+        self.launched(plan)
+        return self.resolve(plan, sampled)

@@ -34,6 +34,8 @@ class StepEntry:
     request: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=tuple)
+    feed: "int | None" = None     # the entry's last token is row ``feed`` of the ids that the step before sampled
+                                  # (still on the device); ``tokens[-1]`` is then a stand-in
 
 
 class _Staging:
@@ -174,8 +176,11 @@ class Stepper:
         rows = [int(cu[b]) + w for b, e in enumerate(entries) for w in e.want]
         logit_rows = np.asarray(rows, dtype=np.int32)
         reqs = [e.request for e in entries]
+        # one slot per entry (so the layout depends on the batch's shape only): where a fed token goes, or -1
+        feed_dst = np.asarray([int(cu[b + 1]) - 1 if e.feed is not None else -1 for b, e in enumerate(entries)], dtype=np.int32)
+        feed_src = np.asarray([e.feed if e.feed is not None else 0 for e in entries], dtype=np.int32)
 
-        pieces = [token_ids, positions, seq_of_token, cu, logit_rows]
+        pieces = [token_ids, positions, seq_of_token, cu, logit_rows, feed_dst, feed_src]
         tables = []
         ps = cache.page_size
         for g, group in enumerate(cache.groups):
@@ -223,7 +228,8 @@ class Stepper:
             dtype=self.model.dtype, device=self.device, num_tokens=T, num_seqs=B, num_logit_rows=R,
             token_ids=view(0), positions=view(1), seq_of_token=view(2), cu_seqlens=view(3), logit_rows=view(4),
             cu_seqlens_host=cu, start_pos_host=np.asarray(starts, dtype=np.int64), error_flag=self.error_flag)
-        k = 5
+        ctx._feed = (view(5), view(6))  # type: ignore[attr-defined]
+        k = 7
         for g, group in enumerate(cache.groups):
             ctx.kv_groups.append(KVView(group.pool, view(k + 1).view(tables[g]), view(k), group.page_size,
                                         group.spec.window))
@@ -235,23 +241,34 @@ class Stepper:
         ctx._new_lens = new_lens  # type: ignore[attr-defined]
         return ctx
 
-    def run_context(self, ctx: StepContext) -> torch.Tensor:
+    def _feed(self, ctx: StepContext, entries: Sequence[StepEntry], fed_from: "torch.Tensor | None") -> None:
+        """Put the ids that the step before sampled (``fed_from``, on the device) into this step's token array."""
+        if any(e.feed is not None for e in entries):
+            if fed_from is None:
+                raise ValueError("an entry asks for a token of the step before, but its sampled ids were not given")
+            from ..kernels import ops
+            dst, src = ctx._feed  # type: ignore[attr-defined]
+            ops.feed_tokens(ctx.token_ids, dst, src, fed_from)
+
+    def run_context(self, ctx: StepContext, fed_from: "torch.Tensor | None" = None) -> torch.Tensor:
+        self._feed(ctx, ctx._entries, fed_from)  # type: ignore[attr-defined]
         logits = self.model.forward(ctx)
         for e, new_len in zip(ctx._entries, ctx._new_lens):  # type: ignore[attr-defined]
             self.cache.commit(e.request, new_len)
         self.steps_run += 1
         return logits
 
-    def step(self, entries: Sequence[StepEntry], reserve: bool = True) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], reserve: bool = True, fed_from: "torch.Tensor | None" = None) -> torch.Tensor:
         """fp32 logits [R, vocab] on the device, R = total number of wanted places, in the
         order of the entries and of each entry's ``want``.  The tensor is valid until the
-        next step (a replayed graph writes its logits to the same memory every time)."""
+        next step (a replayed graph writes its logits to the same memory every time).
+        ``fed_from``: the int32 ids that the step before sampled, for entries with ``feed``."""
         if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            return self._graph_step(entries, reserve)
-        return self.run_context(self.build_context(entries, reserve))
+            return self._graph_step(entries, reserve, fed_from)
+        return self.run_context(self.build_context(entries, reserve), fed_from)
 
     # ------------------------------------------------------------------ captured decode steps
-    def _graph_step(self, entries: Sequence[StepEntry], reserve: bool) -> torch.Tensor:
+    def _graph_step(self, entries: Sequence[StepEntry], reserve: bool, fed_from: "torch.Tensor | None" = None) -> torch.Tensor:
         cache = self.cache
         need = 1
         for e in entries:
@@ -269,6 +286,7 @@ class Stepper:
             flat_dev = torch.empty(flat.shape[0], dtype=torch.int32, device=self.device)
             self._copy_flat(flat_dev, flat)
             ctx = make(flat_dev)
+            self._feed(ctx, entries, fed_from)
             eager_logits = self.model.forward(ctx).clone()
             ctx.scratch.clear()
             before = lib.launch_count
@@ -283,6 +301,7 @@ class Stepper:
             result = eager_logits
         else:
             self._copy_flat(g.flat_dev, flat)
+            self._feed(g.ctx, entries, fed_from)     # outside the graph: writes the static token array before the replay
             g.graph.replay()
             g.replays += 1
             self.graph_replays += 1

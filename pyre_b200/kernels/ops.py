@@ -218,6 +218,16 @@ def silu_mul(gate_up: torch.Tensor, out: "torch.Tensor | None" = None, block: in
     return out
 
 
+def feed_tokens(token_ids: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, prev: torch.Tensor) -> None:
+    """token_ids[dst[i]] = prev[src[i]] where dst[i] >= 0 (all int32, on the device): tokens sampled by
+    the last step enter the next one without a trip through the host."""
+    for t, name in ((token_ids, "token_ids"), (dst, "dst"), (src, "src"), (prev, "prev")):
+        _check(t, name, torch.int32, 1)
+    if dst.shape[0] != src.shape[0]:
+        raise ValueError("dst and src must have one entry each per fed token")
+    lib.call("pyre_feed_tokens", token_ids.data_ptr(), dst.data_ptr(), src.data_ptr(), prev.data_ptr(), dst.shape[0], _stream())
+
+
 def sample(logits: torch.Tensor, temperature: "torch.Tensor | None" = None, seeds: "torch.Tensor | None" = None,
            token_index: "torch.Tensor | None" = None, out: "torch.Tensor | None" = None) -> torch.Tensor:
     """One token id per row of fp32 logits [R, V]: argmax where temperature is 0, else Gumbel-max."""

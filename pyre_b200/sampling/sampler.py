@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Sequence
 
 import numpy as np
@@ -9,6 +10,13 @@ import torch
 
 from ..kernels import ops
 from .params import SamplingParams
+
+
+@dataclass
+class SampleTicket:
+    ids: torch.Tensor      # [R] int32 on the device
+    host: torch.Tensor     # the same in pinned host memory, valid once ``done`` has passed
+    done: "torch.cuda.Event"
 
 
 class Sampler:
@@ -19,13 +27,20 @@ class Sampler:
         self.device = torch.device(device)
         self.bytes_uploaded = 0      # sampling parameters sent to the device
         self.bytes_downloaded = 0    # chosen ids read back
+        self._host = [None, None]    # pinned buffers for the ids; two tickets may be open at a time
+        self._turn = 0
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], token_index: Sequence[int]) -> list[int]:
         """``logits`` [R, V] fp32; ``params[r]`` and ``token_index[r]`` (how many tokens row r's
         request has generated so far) select the rule and the noise of row r."""
-        R = logits.shape[0]
-        if R == 0:
+        if logits.shape[0] == 0:
             return []
+        return self.read(self.sample_async(logits, params, token_index))
+
+    def sample_async(self, logits: torch.Tensor, params: Sequence[SamplingParams], token_index: Sequence[int]):
+        """Launch the sampling of ``sample`` and the copy of its ids to pinned host memory without
+        waiting for them: returns a ticket for ``read``; ``ticket.ids`` are the int32 ids on the device."""
+        R = logits.shape[0]
         if all(p.temperature == 0.0 for p in params):
             ids = ops.sample(logits)
         else:
@@ -40,4 +55,17 @@ class Sampler:
             tix = small_dev[1]
             ids = ops.sample(logits, temperature, seeds_dev, tix)
         self.bytes_downloaded += R * 4
-        return ids.tolist()
+        i = self._turn
+        self._turn ^= 1
+        if self._host[i] is None or self._host[i].shape[0] < R:
+            self._host[i] = torch.empty(max(R, 256), dtype=torch.int32, pin_memory=True)
+        host = self._host[i][:R]
+        host.copy_(ids, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return SampleTicket(ids, host, done)
+
+    def read(self, ticket: "SampleTicket") -> list[int]:
+        """Wait for a ticket's ids and return them."""
+        ticket.done.synchronize()
+        return ticket.host.tolist()

@@ -129,6 +129,43 @@ def test_preemption_recomputes_and_keeps_tokens(model_dirs, dtype):
     assert tight.stats()["pages_free"] == tight.stats()["pages_total"]
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_lookahead_gives_the_same_tokens(model_dirs, name):
+    """Starting a step before the ids of the step before have reached the host (they are fed on
+    the device) changes no token: greedy and temperature requests, ends of sequence (where one token
+    too many is computed and dropped), length limits, and preemption in a tight cache, in 32-bit."""
+    from pyre_b200 import Engine, SamplingParams
+    d, raw = model_dirs[name], H.TINY[name]
+    prompts = [H.random_ids(raw["vocab_size"], L, seed=40 + L) for L in (30, 3, 17, 26, 9)]
+    kw = dict(dtype="float32", page_size=H.PAGE_SIZE[name], max_num_seqs=4, max_num_batched_tokens=24, prefill_chunk=16)
+    probe = Engine(d, max_cache_tokens=2048, lookahead=False, **kw)
+    free = probe.generate(prompts, SamplingParams(max_new_tokens=24))
+    params = [SamplingParams(max_new_tokens=24, eos_id=free[0].token_ids[6]),        # ends early
+              SamplingParams(max_new_tokens=1),                                     # one token only
+              SamplingParams(max_new_tokens=24, temperature=0.8, seed=11),
+              SamplingParams(max_new_tokens=13, eos_id=free[3].token_ids[12]),       # end of sequence on the last allowed token
+              SamplingParams(max_new_tokens=24, temperature=1.3, seed=5, eos_id=free[4].token_ids[2])]
+    long_prompts = [H.random_ids(raw["vocab_size"], L, seed=70 + L) for L in (30, 28, 26)]
+    long_params = [SamplingParams(max_new_tokens=40, temperature=0.7, seed=5)] * 3
+    scenarios = [(prompts, params, dict(max_cache_tokens=2048)),
+                 # 3 x 70 tokens wanted, about 60 % of the pages there: requests are preempted and recomputed
+                 (long_prompts, long_params, dict(num_pages={16: 9, 8: 18}[H.PAGE_SIZE[name]], debug_poison_freed_pages=True))]
+    for ps, sps, cache_kw in scenarios:
+        plain = Engine(d, lookahead=False, **cache_kw, **kw)
+        ahead = Engine(d, lookahead=True, **cache_kw, **kw)
+        a, b = plain.generate(ps, sps), ahead.generate(ps, sps)
+        assert [o.token_ids for o in a] == [o.token_ids for o in b]
+        assert [o.finish_reason for o in a] == [o.finish_reason for o in b]
+        if "num_pages" in cache_kw:
+            assert ahead.stats()["preempted"] >= 1
+        else:
+            assert a[0].finish_reason == "eos" and len(a[1].token_ids) == 1
+        for eng in (plain, ahead):
+            eng.cache.check()
+            assert eng.stats()["pages_free"] == eng.stats()["pages_total"] and not eng.has_unfinished()
+        ahead.stepper.check_device_errors()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding(model_dirs, dtype):
     """300 decoded tokens across many pages, checked teacher-forced against the plain

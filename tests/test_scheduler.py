@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from pyre_b200.cache import CacheManager
-from pyre_b200.engine.scheduler import Scheduler
+from pyre_b200.engine.scheduler import PENDING, Scheduler
 from pyre_b200.parts import PagedKVSpec
 from pyre_b200.sampling import SamplingParams
 
@@ -177,4 +177,72 @@ def test_random_workloads_match_running_alone(seed):
             assert len(prompt) + n > cap - cache.page_size and got.generated == want[:len(got.generated)]
         else:
             assert got.generated == want
+    assert cache.stats().pages_free == [cache.num_pages]
+
+
+def drive_lookahead(sched, cache, max_steps=10_000):
+    """As ``drive``, but every step is planned and started before the tokens of the step before are
+    known to the scheduler (they stand as PENDING); the fake device knows them, as the real one does."""
+    done = {}
+    fed = {}
+    flight = None        # (plan, sampled) of the step whose tokens the scheduler has not seen yet
+    for _ in range(max_steps):
+        if not sched.has_unfinished() and flight is None:
+            break
+        plan = sched.schedule()
+        started = None
+        if plan:
+            assert sum(s.count for s in plan) <= sched.max_num_batched_tokens
+            sampled = []
+            for s in plan:
+                r = s.request
+                assert cache.length(r.seq_id) == s.start and cache.reserved[r.seq_id] >= s.start + s.count
+                toks = r.tokens(s.start, s.count)
+                assert PENDING not in toks[:-1]                 # only the newest token may still be on the device
+                if toks[-1] == PENDING:
+                    assert flight is not None and r.pending == 1
+                    toks[-1] = flight[1][r.feed_row]
+                if s.start == 0:
+                    fed[r.seq_id] = []
+                assert len(fed[r.seq_id]) == s.start
+                fed[r.seq_id] += toks
+                cache.commit(r.seq_id, s.start + s.count)
+                if s.samples:
+                    sampled.append(fake_token(fed[r.seq_id]))
+            sched.launched(plan)
+            started = (plan, sampled)
+        if flight is not None:
+            for r in sched.resolve(*flight):
+                done[r.seq_id] = r
+        flight = started
+        cache.check()
+    assert not sched.has_unfinished() and flight is None, "scheduler did not finish"
+    for r in done.values():
+        assert r.pending == 0 and PENDING not in r.generated
+    return done
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_lookahead_gives_the_same_tokens(seed):
+    """One step in flight while the next is planned: same tokens as running alone, with ends of
+    sequence (a token too many is computed and dropped), length limits, preemption and recompute."""
+    import random
+    rnd = random.Random(100 + seed)
+    sched, cache = make(num_pages=rnd.randint(8, 20), page_size=rnd.choice([2, 4, 8]), max_num_seqs=rnd.randint(2, 4),
+                        budget=rnd.randint(4, 24), chunk=rnd.randint(2, 12), max_model_len=rnd.choice([20, 256]))
+    cap = cache.num_pages * cache.page_size
+    reqs = []
+    for _ in range(12):
+        prompt = [rnd.randint(0, 96) for _ in range(rnd.randint(1, 14))]
+        n = rnd.randint(1, 12)
+        eos = rnd.choice([None, None] + alone(prompt, n)[:3])     # often a token that really comes up
+        reqs.append((sched.add_request(prompt, SamplingParams(max_new_tokens=n, eos_id=eos)), prompt, n, eos))
+    done = drive_lookahead(sched, cache)
+    for r, prompt, n, eos in reqs:
+        want = alone(prompt, n, eos)[:max(0, sched.max_model_len - len(prompt))]
+        got = done[r.seq_id]
+        if got.finish_reason == "cache_full":
+            assert got.generated == want[:len(got.generated)]
+        else:
+            assert got.generated == want, (got.finish_reason, got.generated, want)
     assert cache.stats().pages_free == [cache.num_pages]
