@@ -476,3 +476,100 @@ def test_sampling(ops):
     freq = torch.bincount(draws.long(), minlength=V2).float() / 4000
     p = torch.softmax(lg[0] / 0.7, dim=0)
     assert (freq - p).abs().max().item() < 0.03
+
+
+def plain_attention_one_sequence(q, cache, table_row, positions, nh, nkv, hd, scale, window):
+    """The queries of ONE sequence at ``positions`` over its cached keys 0..max position, all at once (fp64)."""
+    page = cache.shape[3]
+    n_ctx = int(positions.max()) + 1
+    idx = torch.arange(n_ctx, device=q.device)
+    pages = table_row[idx // page].long()
+    k = cache[pages, 0, :, idx % page].double()            # [n_ctx, nkv, hd]
+    v = cache[pages, 1, :, idx % page].double()
+    T = q.shape[0]
+    qf = q.double().view(T, nh, hd)
+    pos = positions.long()[:, None]
+    seen = idx[None, :] <= pos
+    if window:
+        seen &= idx[None, :] > pos - window
+    out = torch.empty(T, nh, hd, dtype=torch.float64, device=q.device)
+    for h in range(nh):
+        kvh = h // (nh // nkv)
+        sc = (qf[:, h] @ k[:, kvh].t()) * scale
+        sc = sc.masked_fill(~seen, float("-inf"))
+        out[:, h] = torch.softmax(sc, dim=-1) @ v[:, kvh]
+    return out.view(T, nh * hd).float()
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [(8, 2, 128, 16, None), (4, 1, 64, 64, 3000), (7, 1, 128, 32, None),
+                                                   (6, 2, 128, 8, 5000)])
+def test_attention_long_context(ops, nh, nkv, hd, page, window):
+    """Thousands of keys: a 700-token portion at the end of a 9,000-token context (the tcgen05 kernel walks
+    140 key tiles: its rings, its barrier phases and its lazy rescale wrap many times) and a decode token
+    over 7,000 keys with 1, 4 and 16 splits (with one split a warp walks over a hundred tiles and re-reads
+    its page numbers every 32), on scrambled pages, with one far key that decides a row."""
+    import numpy as np
+    from pyre_b200.engine.context import StepContext
+    g = torch.Generator(device="cuda").manual_seed(41)
+    ctx_lens, new = [9000, 7000], [700, 1]
+    n_pages = sum(-(-c // page) for c in ctx_lens) + 5
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(42)).tolist()
+    W = max(-(-c // page) for c in ctx_lens)
+    table = torch.full((2, W), -1, dtype=torch.int32)
+    for s_, c in enumerate(ctx_lens):
+        for lp in range(-(-c // page)):
+            table[s_, lp] = perm.pop()
+    table = table.cuda()
+    cache = torch.randn(n_pages, 2, nkv, page, hd, device="cuda", generator=g)
+    for pg in perm:
+        cache[pg] = float("nan")                                   # pages nobody owns
+    for s_, c in enumerate(ctx_lens):
+        if c % page:
+            cache[int(table[s_, (c - 1) // page]), :, :, c % page:] = float("nan")
+    positions = torch.tensor(list(range(8300, 9000)) + [6999], dtype=torch.int32, device="cuda")
+    seq_of_token = torch.tensor([0] * 700 + [1], dtype=torch.int32, device="cuda")
+    cu_host = np.asarray([0, 700, 701], dtype=np.int32)
+    cu = torch.from_numpy(cu_host).cuda()
+    T = 701
+    q = torch.randn(T, nh * hd, device="cuda", generator=g) * 1.5
+    # a far key decides row 300 of the portion and the decode token: position 3, or the first inside the window
+    marks = []
+    for row, s_ in ((300, 0), (700, 1)):
+        far = 3 if not window else int(positions[row]) - window + 1
+        pg, off = int(table[s_, far // page]), far % page
+        cache[pg, 0, 0, off] = q[row, :hd] * 2.5
+        marks.append((row, pg, off))
+    cache, q = cache.to(torch.bfloat16), q.to(torch.bfloat16)
+    scale = hd ** -0.5
+    want = torch.cat([plain_attention_one_sequence(q[:700].float(), cache.float(), table[0], positions[:700], nh, nkv, hd, scale, window),
+                      plain_attention_one_sequence(q[700:].float(), cache.float(), table[1], positions[700:], nh, nkv, hd, scale, window)])
+    z = torch.zeros(T, dtype=torch.int32, device="cuda")
+    ctx = StepContext(dtype=torch.bfloat16, device=torch.device("cuda"), num_tokens=T, num_seqs=2, num_logit_rows=0,
+                      token_ids=z, positions=positions, seq_of_token=seq_of_token, cu_seqlens=cu, logit_rows=z[:0],
+                      cu_seqlens_host=cu_host, start_pos_host=np.asarray([8300, 6999]))
+
+    def check(got, rows, what):
+        assert torch.isfinite(got[rows]).all(), what
+        err = (got[rows].float() - want[rows]).abs()
+        bad = (err > 1.2e-2 + 1.6e-2 * want[rows].abs()).any(dim=1)
+        assert not bad.any(), f"{what}: first wrong row {int(torch.where(bad)[0][0])}, max error {float(err.max()):.3e}"
+
+    got = ops.paged_attention_bf16(ctx, q, cache, table, nh, nkv, hd, scale, window)
+    ops.check_device_errors()
+    check(got, slice(0, T), "dispatch")
+    for row, pg, off in marks:
+        v_far = cache[pg, 1, 0, off].float()
+        assert (got[row, :hd].float() - v_far).abs().max() < 0.25 * v_far.abs().max() + 0.1
+    # the decode token alone through the split-KV kernel: one split (long walks per warp), clusters of 4 and 16
+    dec_cu = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    for n_splits in (1, 4, 16):
+        alone = ops.paged_attention_mma(q[700:].contiguous(), cache, table[1:2].contiguous(), dec_cu, positions[700:].contiguous(),
+                                        1, nh, nkv, hd, scale, window, n_splits, uniform_len=1)
+        ops.check_device_errors()
+        err = (alone.float() - want[700:]).abs()
+        assert float((err - 1.2e-2 - 1.6e-2 * want[700:].abs()).max()) <= 0, f"{n_splits} splits: max error {float(err.max()):.3e}"
+    # the portion through the mma.sync prompt kernel as well
+    other = torch.full_like(q, 7.0)
+    ops.attention_prefill(q, cache, table, cu, positions, 2, 700, nh, nkv, hd, scale, window, other)
+    ops.check_device_errors()
+    check(other, slice(0, 700), "mma.sync prompt kernel")
