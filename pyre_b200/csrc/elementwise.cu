@@ -293,6 +293,85 @@ __global__ void qkv_rope_write_kernel(const T* __restrict__ qkv, const float* __
     }
 }
 
+// The common case, rotary over the whole head (rot == hd): one item is a pair of VEC-wide chunks (d0, d0 + hd / 2)
+// of one head, the two halves that a rotation mixes (for v: two plain chunks), so no thread idles and every access
+// is VEC elements wide.  Same arithmetic as the general kernel above.
+template <typename T, int VEC>
+__device__ __forceinline__ void load_qkv_vec(float (&v)[VEC], const T* in, const float* pin, int n_partials,
+                                             long long partial_stride, int idx) {
+    if (pin) {
+        Vec<float, VEC> acc = load_vec<float, VEC>(pin + idx);
+        for (int s = 1; s < n_partials; ++s) {
+            Vec<float, VEC> q = load_vec<float, VEC>(pin + (size_t)s * partial_stride + idx);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) acc.v[k] += q.v[k];
+        }
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v[k] = acc.v[k];
+    } else {
+        Vec<T, VEC> a = load_vec<T, VEC>(in + idx);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v[k] = to_f32<T>(a.v[k]);
+    }
+}
+
+template <typename T, int VEC>
+__global__ void qkv_rope_write_full_kernel(const T* __restrict__ qkv, const float* __restrict__ partials, int n_partials,
+                                           long long partial_stride, const float* __restrict__ bias,
+                                           const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                           T* __restrict__ q_out, T* __restrict__ cache,
+                                           const int* __restrict__ slot_mapping, int nh, int nkv, int hd, int page_size) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int half = hd / 2;
+    const int per_head = half / VEC;
+    const int n_heads_all = nh + 2 * nkv;
+    const T* in = qkv ? qkv + (size_t)t * n_heads_all * hd : nullptr;
+    const float* pin = partials ? partials + (size_t)t * n_heads_all * hd : nullptr;
+    const float* ct = cos_t + (size_t)t * half;
+    const float* st = sin_t + (size_t)t * half;
+    const int slot = (cache && slot_mapping) ? slot_mapping[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0;
+    const int off = slot >= 0 ? slot - page * page_size : 0;
+    for (int item = blockIdx.y * blockDim.x + threadIdx.x; item < n_heads_all * per_head; item += gridDim.y * blockDim.x) {
+        const int h = item / per_head;
+        const int d0 = (item - h * per_head) * VEC;
+        const bool is_v = h >= nh + nkv;
+        const bool is_k = !is_v && h >= nh;
+        T* dst;
+        if (!is_k && !is_v) {
+            dst = q_out + ((size_t)t * nh + h) * hd;
+        } else {
+            if (slot < 0) continue;
+            const int kvh = is_k ? h - nh : h - nh - nkv;
+            dst = cache + (((size_t)(page * 2 + (is_v ? 1 : 0)) * nkv + kvh) * page_size + off) * hd;
+        }
+        float a1[VEC], a2[VEC];
+        load_qkv_vec<T, VEC>(a1, in, pin, n_partials, partial_stride, h * hd + d0);
+        load_qkv_vec<T, VEC>(a2, in, pin, n_partials, partial_stride, h * hd + d0 + half);
+        if (bias) {
+            const float* b = bias + (size_t)h * hd;
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) { a1[k] = a1[k] + b[d0 + k]; a2[k] = a2[k] + b[d0 + half + k]; }
+        }
+        Vec<T, VEC> o1, o2;
+        if (is_v) {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) { o1.v[k] = from_f32<T>(a1[k]); o2.v[k] = from_f32<T>(a2[k]); }
+        } else {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                const float c = ct[d0 + k], s_ = st[d0 + k];
+                o1.v[k] = from_f32<T>(__fadd_rn(__fmul_rn(a1[k], c), __fmul_rn(-a2[k], s_)));
+                o2.v[k] = from_f32<T>(__fadd_rn(__fmul_rn(a2[k], c), __fmul_rn(a1[k], s_)));
+            }
+        }
+        store_vec<T, VEC>(dst + d0, o1);
+        store_vec<T, VEC>(dst + d0 + half, o2);
+    }
+}
+
 // qkv: activation dtype [T, width] or null; partials: fp32 [n_partials][T][width] or null (one of the two).
 PYRE_API int pyre_qkv_rope_write(const void* qkv, const float* partials, int n_partials, long long partial_stride,
                                  const float* bias, const float* cos_t, const float* sin_t,
@@ -302,12 +381,19 @@ PYRE_API int pyre_qkv_rope_write(const void* qkv, const float* partials, int n_p
     if (hd % 8 || rot % 8 || rot > hd || rot < 0 || page_size <= 0) return PYRE_ERR_BAD_ARG;
     if ((qkv == nullptr) == (partials == nullptr)) return PYRE_ERR_BAD_ARG;
     if (partials && n_partials < 1) return PYRE_ERR_BAD_ARG;
-    const int items = (nh + 2 * nkv) * (hd / 4);
+    // rotary over the whole head: the pair kernel, 8 bf16 (4 fp32) per access
+    const int vec = dtype == PYRE_BF16 ? 8 : 4;
+    const bool full = rot == hd && hd % (2 * vec) == 0;
+    const int items = full ? (nh + 2 * nkv) * (hd / (2 * vec)) : (nh + 2 * nkv) * (hd / 4);
     const int threads = min(128, max(32, ((items + 31) / 32) * 32));
     // few tokens: spread a token's items over several blocks (one item per thread); many tokens:
     // one block per token is plenty of parallelism
     const int by = n_tokens >= 256 ? 1 : min(ceil_div(items, threads), 64);
-    if (dtype == PYRE_F32)
+    if (full && dtype == PYRE_F32)
+        pyre_launch(qkv_rope_write_full_kernel<float, 4>, dim3(n_tokens, by), dim3(threads), 0, stream, (const float*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (float*)q_out, (float*)cache, slot_mapping, nh, nkv, hd, page_size);
+    else if (full && dtype == PYRE_BF16)
+        pyre_launch(qkv_rope_write_full_kernel<__nv_bfloat16, 8>, dim3(n_tokens, by), dim3(threads), 0, stream, (const __nv_bfloat16*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, slot_mapping, nh, nkv, hd, page_size);
+    else if (dtype == PYRE_F32)
         pyre_launch(qkv_rope_write_kernel<float>, dim3(n_tokens, by), dim3(threads), 0, stream, (const float*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (float*)q_out, (float*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
     else if (dtype == PYRE_BF16)
         pyre_launch(qkv_rope_write_kernel<__nv_bfloat16>, dim3(n_tokens, by), dim3(threads), 0, stream, (const __nv_bfloat16*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, slot_mapping, nh, nkv, hd, rot, page_size);

@@ -34,7 +34,7 @@ def test_embedding(ops, dtype, H):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,eps", [(40, 1e-5), (101, 1e-6), (3584, 1e-6), (5120, 3e-6)])
+@pytest.mark.parametrize("H,eps", [(40, 1e-5), (101, 1e-6), (3584, 1e-6), (5120, 3e-6), (9000, 1e-6), (2051, 1e-5)])
 def test_add_rmsnorm(ops, dtype, H, eps):
     g = torch.Generator(device="cuda").manual_seed(1)
     T = 7
