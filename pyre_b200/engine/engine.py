@@ -74,7 +74,9 @@ class Engine:
                                    self.max_model_len)
         self.sampler = Sampler(ec.device)
         self._requests: dict[int, Request] = {}
-        self._flight = None      # (plan, sampling ticket) of the step whose ids have not been read yet
+        self._flight = None      # (plan, sampling ticket, error word) of the step whose ids have not been read yet
+        self._err_host = [torch.zeros(1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._err_turn = 0
 
     # ------------------------------------------------------------------ the reference's two calls
     def add_request(self, prompt_ids: Sequence[int], max_new_tokens: int = 16, eos_id: "int | None" = None,
@@ -111,11 +113,16 @@ class Engine:
                 entries.append(StepEntry(s.request.seq_id, toks, [s.count - 1] if s.samples else [], feed))
             with torch.cuda.device(self.model.device):
                 logits = self.stepper.step(entries, reserve=False, fed_from=prev[1].ids if prev and prev[1] is not None else None)
+                # the device's error flag travels with the ids: a kernel that gave up (bounded wait, bad index) is
+                # reported when this step is read, without a synchronisation of its own
+                err = self._err_host[self._err_turn]
+                self._err_turn ^= 1
+                err.copy_(self.stepper.error_flag, non_blocking=True)
                 sampling = [s for s in plan if s.samples]
                 ticket = self.sampler.sample_async(logits, [s.request.params for s in sampling],
                                                    [len(s.request.generated) for s in sampling]) if sampling else None
             sched.launched(plan)
-            flight = (plan, ticket)
+            flight = (plan, ticket, err)
         if self._flight is not None:
             self._land(self._flight)
         self._flight = flight
@@ -130,8 +137,11 @@ class Engine:
 
     def _land(self, flight) -> None:
         """Read the ids of a started step and let the scheduler record them."""
-        plan, ticket = flight
-        self.scheduler.resolve(plan, self.sampler.read(ticket) if ticket is not None else [])
+        plan, ticket, err = flight
+        ids = self.sampler.read(ticket) if ticket is not None else []
+        if ticket is not None and int(err[0]) != 0:
+            self.stepper.check_device_errors()      # raises with the kernel's reason
+        self.scheduler.resolve(plan, ids)
 
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished() or self._flight is not None or any(r.done for r in self._requests.values())

@@ -108,7 +108,8 @@ class Stepper:
         self.device = model.device
         self.max_positions = max_positions
         self._staging = _Staging(self.device)
-        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        from ..kernels import ops
+        self.error_flag = ops.device_error_flag(self.device)   # one flag per device, raised by any kernel
         self.steps_run = 0
         self.cuda_graphs = bool(cuda_graphs) and model.graph_safe
         self._graphs: dict[tuple, _DecodeGraph] = {}
@@ -330,6 +331,6 @@ class Stepper:
         self._staging.mark_copied()
 
     def check_device_errors(self) -> None:
-        if int(self.error_flag.item()) != 0:
-            self.error_flag.zero_()
-            raise lib.KernelError("a kernel met an index outside its range (token id outside the vocabulary)")
+        """Raise if a kernel of an earlier step raised the device's error flag (synchronises)."""
+        from ..kernels import ops
+        ops.check_device_errors(self.device)

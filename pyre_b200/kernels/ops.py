@@ -473,7 +473,8 @@ def check_device_errors(device="cuda") -> None:
     code = int(flag.item())
     if code:
         flag.zero_()
-        raise lib.KernelError({2: "a tensor-core GEMM gave up waiting on its pipeline (bounded wait ran out)",
+        raise lib.KernelError({1: "a kernel met an index outside its range (token id outside the vocabulary)",
+                               2: "a tensor-core GEMM gave up waiting on its pipeline (bounded wait ran out)",
                                3: "the attention kernel gave up waiting for a tile copy (bounded wait ran out)",
                                4: "the tcgen05 attention kernel gave up waiting on its pipeline (bounded wait ran out)",
                                5: "the tcgen05 attention kernel found its shared memory misaligned"}.get(

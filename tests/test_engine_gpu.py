@@ -232,3 +232,19 @@ def test_command_line_and_trace_run_program(model_dirs, tmp_path):
     got = H.collect_trace_logits(steps, lambda n: np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, raw["vocab_size"]))["a"]
     want = H.plain_logits(d, ids)[7:]
     assert np.abs(got - want).max() <= 2e-4
+
+
+def test_a_raised_error_flag_stops_generation(model_dirs):
+    """Kernels report a bounded wait that ran out (or an index out of range) through one flag per
+    device; the engine reads it with every step's ids.  Here the flag is set by hand (nothing on the
+    GPU goes wrong): the next step that is read raises, and the flag is clear afterwards."""
+    from pyre_b200 import Engine, SamplingParams
+    from pyre_b200.kernels import lib, ops
+    d, raw = model_dirs["A"], H.TINY["A"]
+    eng = Engine(d, dtype="bfloat16", max_cache_tokens=512)
+    prompt = H.random_ids(raw["vocab_size"], 9, seed=8)
+    assert len(eng.generate([prompt], SamplingParams(max_new_tokens=4))[0].token_ids) == 4
+    ops.device_error_flag(eng.model.device).fill_(2)
+    with pytest.raises(lib.KernelError, match="bounded wait"):
+        eng.generate([prompt], SamplingParams(max_new_tokens=4))
+    assert int(ops.device_error_flag(eng.model.device).item()) == 0
