@@ -346,6 +346,85 @@ def run_workload(args) -> dict:
             "ms_first_last": [round(times[1], 2), round(times[-1], 2)]}
 
 
+def run_sweep(args) -> dict:
+    """Decode throughput over a grid of batch sizes and context lengths and prefill throughput over
+    several portion lengths on the 7B shape, each with its fraction of the roofline (device-timed,
+    the same way as the headline numbers).  One JSON object; not part of the one-line contract."""
+    import numpy as np
+    import torch
+
+    from pyre_b200 import Engine
+    from pyre_b200.config import config_from_dict
+    from pyre_b200.engine.step import StepEntry
+    from pyre_b200.kernels import ops
+
+    peaks = load_peaks()
+    cfg_raw = dict(CONFIG_7B)
+    layers = args.layers or cfg_raw["num_hidden_layers"]
+    cfg_raw["num_hidden_layers"] = layers
+    cfg_raw["max_position_embeddings"] = 40960
+    cfg = config_from_dict(cfg_raw)
+    weight_bytes, kv_per_token, flops = model_numbers(cfg_raw, layers)
+    grid = [(1, 512), (1, 8192), (1, 32768), (8, 512), (8, 2048), (8, 8192), (8, 32768), (32, 2048), (64, 512), (64, 2048),
+            (64, 8192), (128, 2048)]
+    biggest = max(b * (c + 64) for b, c in grid)
+    eng = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=biggest + 8192,
+                 max_num_seqs=128, max_num_batched_tokens=8192, prefill_chunk=8192, max_model_len=40960)
+    st, cache = eng.stepper, eng.cache
+    rng = np.random.default_rng(0)
+    vocab = cfg.vocab_size
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    decode = []
+    for batch, ctx in grid:
+        reqs = [("d", batch, ctx, i) for i in range(batch)]
+        for r in reqs:
+            cache.begin(r)
+            for lo in range(0, ctx, 8192):
+                st.step([StepEntry(r, rng.integers(0, vocab, min(8192, ctx - lo)).tolist(), [])])
+        n_warm, n_steps = 3, 12
+        toks = rng.integers(0, vocab, (n_warm + n_steps, batch))
+        for k in range(n_warm):
+            ops.sample(st.step([StepEntry(r, [int(toks[k, i])], [0]) for i, r in enumerate(reqs)]))
+        torch.cuda.synchronize()
+        a, b = ev(), ev()
+        a.record()
+        for k in range(n_warm, n_warm + n_steps):
+            ops.sample(st.step([StepEntry(r, [int(toks[k, i])], [0]) for i, r in enumerate(reqs)]))
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / n_steps
+        step_bytes = weight_bytes + kv_per_token * (ctx + n_warm + n_steps / 2) * batch
+        decode.append({"batch": batch, "context": ctx, "ms_per_step": round(ms, 3), "tok_s": round(batch / ms * 1e3, 1),
+                       "hbm_frac": round(step_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 3)})
+        for r in reqs:
+            cache.end(r)
+    prefill = []
+    for T, start in ((512, 0), (2048, 0), (4096, 0), (8192, 0), (2048, 8192), (2048, 30720)):
+        times = []
+        for rep in range(4):
+            r = ("p", T, start, rep)
+            cache.begin(r)
+            for lo in range(0, start, 8192):
+                st.step([StepEntry(r, rng.integers(0, vocab, min(8192, start - lo)).tolist(), [])])
+            ids = rng.integers(0, vocab, T).tolist()
+            torch.cuda.synchronize()
+            a, b = ev(), ev()
+            a.record()
+            ops.sample(st.step([StepEntry(r, ids, [T - 1])]))
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+            cache.end(r)
+        ms = sorted(times[1:])[len(times[1:]) // 2]
+        prefill.append({"tokens": T, "context_before": start, "ms": round(ms, 3), "tok_s": round(T / ms * 1e3, 1),
+                        "flops_frac": round(flops(T, start, 1) / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 3)})
+    cache.check()
+    return {"workload": "sweep", "layers": layers, "peaks": peaks, "decode": decode, "prefill": prefill}
+
+
 def run_reference(args) -> dict:
     from baseline import reference_arm
     return reference_arm.run(args, CONFIG_7B, PROMPT_LEN)
@@ -361,8 +440,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")
     ap.add_argument("--prefill-reps", type=int, default=5)
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
-    ap.add_argument("--workload", choices=["serve14b", "mixed32b"], default=None,
-                    help="run one of the two other baseline workloads instead (prints its own JSON line)")
+    ap.add_argument("--workload", choices=["serve14b", "mixed32b", "sweep"], default=None,
+                    help="run one of the two other baseline workloads, or a sweep over batch sizes, context lengths and "
+                         "portion lengths on the 7B shape, instead (prints its own JSON line)")
     ap.add_argument("--cache-fraction", type=float, default=1.0,
                     help="serve14b: cache capacity as a fraction of what all requests need at once (< 1 forces preemption)")
     args = ap.parse_args()
@@ -370,7 +450,7 @@ def main() -> int:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
         return 2
     if args.workload:
-        print(json.dumps(run_workload(args)))
+        print(json.dumps(run_sweep(args) if args.workload == "sweep" else run_workload(args)))
         return 0
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
     print(json.dumps(result))
