@@ -384,7 +384,7 @@ def run_sweep(args) -> dict:
             cache.begin(r)
             for lo in range(0, ctx, 8192):
                 st.step([StepEntry(r, rng.integers(0, vocab, min(8192, ctx - lo)).tolist(), [])])
-        n_warm, n_steps = 3, 12
+        n_warm, n_steps = 8, 32
         toks = rng.integers(0, vocab, (n_warm + n_steps, batch))
         for k in range(n_warm):
             ops.sample(st.step([StepEntry(r, [int(toks[k, i])], [0]) for i, r in enumerate(reqs)]))
