@@ -247,6 +247,7 @@ def run_ours(args) -> dict:
     while engine.has_unfinished():
         engine.step()
     clocks.stop()
+    stepper.check_device_errors()      # a kernel that gave up waiting would have raised the device's error word
 
     return {
         "metric": "decode tok/s (Qwen2.5-7B shape, batch 8, 2,048-token prompts)", "value": round(value, 1),
@@ -422,6 +423,7 @@ def run_sweep(args) -> dict:
         prefill.append({"tokens": T, "context_before": start, "ms": round(ms, 3), "tok_s": round(T / ms * 1e3, 1),
                         "flops_frac": round(flops(T, start, 1) / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 3)})
     cache.check()
+    st.check_device_errors()
     return {"workload": "sweep", "layers": layers, "peaks": peaks, "decode": decode, "prefill": prefill}
 
 

@@ -462,7 +462,19 @@ PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* 
     // one CTA per SM stays resident and walks the tiles (a split K keeps one CTA per tile and split)
     static int sm_count = 0;
     if (!sm_count) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev); if (sm_count <= 0) sm_count = 148; }
-    dim3 grid((unsigned)(splits > 1 ? n_tiles : (n_tiles < sm_count ? n_tiles : sm_count)), 1, splits);
+    long long ctas = splits > 1 ? n_tiles : (n_tiles < sm_count ? n_tiles : sm_count);
+    if (xc && splits == 1 && n_tiles > sm_count) {
+        // A weight stream (few tokens) is bound by memory: what counts is that no round of the persistent CTAs
+        // runs nearly empty at the end while the memory system idles.  Take the CTA count, at least 7/8 of the
+        // SMs, that fills the rounds best (1188 tiles: 132 CTAs x 9 rounds instead of 148 x 8 + 4).
+        long long best = sm_count, best_waste = ((n_tiles + sm_count - 1) / sm_count) * sm_count - n_tiles;
+        for (long long g = sm_count - 1; g >= sm_count - sm_count / 8 && best_waste > 0; --g) {
+            const long long waste = ((n_tiles + g - 1) / g) * g - n_tiles;
+            if (waste * sm_count < best_waste * g) { best = g; best_waste = waste; }
+        }
+        ctas = best;
+    }
+    dim3 grid((unsigned)ctas, 1, splits);
 #define GO(BN_, ST_)                                                              \
     rc = xc ? launch<BN_, ST_, true>(mx, my, p, grid, stream) : launch<BN_, ST_, false>(mx, my, p, grid, stream)
     switch (bn) {
