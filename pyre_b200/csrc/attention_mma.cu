@@ -103,7 +103,6 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-constexpr uint32_t TMA_WAIT_LIMIT = 2000000;
 constexpr int ERR_ATTN_TIMEOUT = 3;
 
 struct AttnParams {
@@ -353,9 +352,12 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
             cp_async_wait<STAGES - 1>();
         } else {
             const uint32_t parity = (it / STAGES) & 1;
-            uint32_t spins = 0;
-            while (!mbar_try_wait(bar0 + 8 * stage, parity)) {
-                if (++spins > TMA_WAIT_LIMIT) { timed_out = true; break; }
+            if (!mbar_try_wait(bar0 + 8 * stage, parity)) {
+                const unsigned long long t0 = pyre_now_ns();
+                uint32_t spins = 0;
+                while (!mbar_try_wait(bar0 + 8 * stage, parity)) {
+                    if ((++spins & 255) == 0 && pyre_now_ns() - t0 > PYRE_WAIT_NS) { timed_out = true; break; }
+                }
             }
             timed_out = __any_sync(0xffffffffu, timed_out);   // the whole warp gives up together
             if (timed_out) break;

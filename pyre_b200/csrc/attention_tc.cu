@@ -49,7 +49,6 @@ namespace {
 constexpr int BM = 128;       // queries per CTA = TMEM lanes
 constexpr int BN = 64;        // keys per tile
 constexpr int THREADS = 224;   // warp 0: K producer, 1: MMA issuer, 2-5: one thread per query row, 6: V producer
-constexpr uint32_t WAIT_LIMIT = 400000;
 constexpr int ERR_TIMEOUT = 4;
 constexpr float RESCALE_THRESHOLD = 8.0f;   // log2 units
 
@@ -73,9 +72,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err_flag) {
-    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = pyre_now_ns();
+    for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 63) == 63 && *abort_flag) return false;
+        if ((it & 63) == 0) {
+            if (*abort_flag) return false;
+            if (pyre_now_ns() - t0 > PYRE_WAIT_NS) break;
+        }
     }
     *abort_flag = 1;
     if (err_flag) atomicExch(err_flag, ERR_TIMEOUT);

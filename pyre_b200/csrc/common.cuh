@@ -100,6 +100,17 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // attribute off.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Spin-waits in the kernels (mbarriers of the TMA / tcgen05 pipelines) are bounded by time, not by a
+// count of polls: a wait may legitimately last as long as the kernels before it in the stream run (a CTA
+// can be resident and polling while its predecessor drains), but never seconds.  After PYRE_WAIT_NS the
+// waiter gives up, raises the error word and the kernel winds down.
+constexpr unsigned long long PYRE_WAIT_NS = 4000000000ull;
+__device__ __forceinline__ unsigned long long pyre_now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 #include <cstdlib>

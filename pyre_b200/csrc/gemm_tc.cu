@@ -41,7 +41,6 @@ namespace {
 constexpr int BM = 128;           // rows of X per tile = TMEM lanes
 constexpr int BK = 64;            // K per stage: 64 bf16 = one 128-byte swizzle row
 constexpr int THREADS = 192;
-constexpr uint32_t WAIT_LIMIT = 400000;
 constexpr int ERR_TIMEOUT = 2;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -63,9 +62,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false if the limit ran out or another thread already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err_flag) {
-    for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = pyre_now_ns();
+    for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 63) == 63 && *abort_flag) return false;
+        if ((it & 63) == 0) {
+            if (*abort_flag) return false;
+            if (pyre_now_ns() - t0 > PYRE_WAIT_NS) break;
+        }
     }
     *abort_flag = 1;
     if (err_flag) atomicExch(err_flag, ERR_TIMEOUT);
