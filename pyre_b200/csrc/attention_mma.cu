@@ -156,16 +156,19 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
     const int g = lane >> 2, t = lane & 3;
     if constexpr (CLUSTER) (void)cg::this_cluster().barrier_arrive();   // phase 1 ("this CTA runs"), awaited before the merge
     pdl_trigger();
-    pdl_wait();   // queries, the pages of this step and the step's index arrays come from earlier kernels
+    // What follows until pdl_wait() reads only what no kernel of this step writes: the step's index arrays
+    // (copied from the host before the step's first kernel) and keys and values of EARLIER steps.  The
+    // queries, and the keys and values of this step's own tokens, are touched after the wait.
 
     // ---- which group is this CTA's?  groups are counted entry by entry
-    int grp = blockIdx.x, seq = -1, tok0 = 0, n_tok = 0;
+    int grp = blockIdx.x, seq = -1, tok0 = 0, n_tok = 0, seq_begin = 0;
     if (p.uniform_len > 0) {
         const int ng = (p.uniform_len + p.tpg - 1) / p.tpg;
         const int b = grp / ng, gi = grp % ng;
         if (b < p.n_seqs) {
             seq = b;
-            tok0 = b * p.uniform_len + gi * p.tpg;
+            seq_begin = b * p.uniform_len;
+            tok0 = seq_begin + gi * p.tpg;
             n_tok = min(p.tpg, p.uniform_len - gi * p.tpg);
         }
     } else
@@ -175,6 +178,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
         const int ng = (len + p.tpg - 1) / p.tpg;
         if (grp < ng) {
             seq = b;
+            seq_begin = begin;
             tok0 = begin + grp * p.tpg;
             n_tok = min(p.tpg, len - grp * p.tpg);
             break;
@@ -201,6 +205,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
         row_lo[r] = (p.window > 0 && row_pos[r] - p.window + 1 > 0) ? row_pos[r] - p.window + 1 : 0;
     }
     const int pos_first = p.positions[tok0], pos_last = p.positions[tok0 + n_tok - 1];
+    const int new_from = p.positions[seq_begin];   // the sequence's keys from here on are written by this step
     const int lo_g = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
     const int tile_lo = lo_g / TILE, tile_hi = pos_last / TILE;
     const int tiles_total = tile_hi - tile_lo + 1;
@@ -308,11 +313,22 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
     const bool upper = __any_sync(0xffffffffu, row_ok[1]);   // does any lane own a valid row among rows 8..15?
     const float sl2 = p.scale * 1.44269504088896341f;        // log2(e): maxima and scores live in base 2
 
-    // ---- the first STAGES - 1 tiles go out before anything else is read
+    // ---- the first STAGES - 1 tiles go out before anything else is read: those that hold only keys of
+    // earlier steps even before this kernel waits for the kernels before it (their latency, and all of the
+    // set-up above, then hide behind the kernel that writes this step's keys)
     const int n_mine = tile_begin + warp < tile_end ? (tile_end - tile_begin - warp + WARPS - 1) / WARPS : 0;
+    auto is_old = [&](int j) { return (tile_begin + warp + WARPS * j) * TILE + TILE - 1 < new_from; };
 #pragma unroll
     for (int j = 0; j < STAGES - 1; ++j) {
-        if (j < n_mine) {
+        if (j < n_mine && is_old(j)) {
+            if (!tma) load_tile(tile_begin + warp + WARPS * j, j);
+            else tma_tile(j, j);
+        }
+    }
+    pdl_wait();
+#pragma unroll
+    for (int j = 0; j < STAGES - 1; ++j) {
+        if (j < n_mine && !is_old(j)) {
             if (!tma) load_tile(tile_begin + warp + WARPS * j, j);
             else tma_tile(j, j);
         }
