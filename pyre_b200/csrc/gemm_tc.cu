@@ -116,8 +116,8 @@ struct GemmParams {
     void* out;
     int out_f32;
     int x_is_constant;            // 1: X holds weights (may be loaded before the kernels before this one finish); 0: Y does
-    int gated;                    // 1: the y rows are gate/up weights interleaved in blocks of 128 (gate rows, then the up
-                                  // rows of the same features); the epilogue writes silu(gate) * up, half as many columns
+    int gated;                    // 1: the weight rows are gate/up rows interleaved in blocks of 64 (gate rows, then the up
+                                  // rows of the same features); the epilogue writes silu(gate) * up, half as many features
     int* err_flag;
 };
 
@@ -128,7 +128,8 @@ struct SmemLayout {
     static constexpr int STAGE_BYTES = X_BYTES + Y_BYTES;
     static constexpr int TILES = STAGES * STAGE_BYTES;
     static constexpr int N_BARS = 2 * STAGES + 4;     // full, empty per stage; accumulator full, empty per TMEM buffer
-    static constexpr int TOTAL = TILES + N_BARS * 8 + 16 + 1024;  // + tmem slot and abort flag, alignment slack
+    static constexpr int EXCH_BYTES = BN <= 128 ? 64 * BN * 4 : 0;  // gated transposed epilogue: 64 up rows x BN tokens, fp32
+    static constexpr int TOTAL = TILES + N_BARS * 8 + 16 + EXCH_BYTES + 1024;  // + tmem slot and abort flag, alignment slack
 };
 
 // A CTA is persistent: it walks output tiles c, c + gridDim.x, ...  Two TMEM accumulators
@@ -277,15 +278,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const uint32_t acc = tmem_base + buf * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
             if constexpr (!X_CONTIGUOUS_OUT && BN == 256) {
                 if (p.gated) {
-                    // columns 0..127 of the tile are gate features, 128..255 the up features of the same
-                    // indices: out[x, y0 / 2 + c] = silu(gate) * up, with the products rounded to bfloat16
+                    // the tile's columns are two blocks of 64 gate features followed by the 64 up features of the
+                    // same indices: out[x, y0 / 2 + c] = silu(gate) * up, with the products rounded to bfloat16
                     // first (as a separate activation kernel would read them) and the rest in fp32
 #pragma unroll 1
                     for (int c = 0; c < 128; c += 16) {
                         uint32_t g[16], u[16];
+                        const int gc = (c >> 6) * 128 + (c & 63);   // column of gate feature c of this tile
                         __syncwarp();
-                        tmem_ld16(acc + c, g);
-                        tmem_ld16(acc + 128 + c, u);
+                        tmem_ld16(acc + gc, g);
+                        tmem_ld16(acc + gc + 64, u);
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                         if (alive && xr < p.x_rows) {
                             uint32_t w[8];
@@ -305,6 +307,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                             dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
                             dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
                         }
+                    }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
+                    continue;
+                }
+            }
+            if constexpr (X_CONTIGUOUS_OUT && BN <= 128) {
+                if (p.gated) {
+                    // weights on the rows: this tile's 128 rows are 64 gate features (warps of rows 0..63) and the
+                    // up features of the same indices (rows 64..127), its columns are tokens.  The up warps hand
+                    // their values over through shared memory; the gate warps compute silu(gate) * up as above and
+                    // store out[token, x0 / 2 + row] (for a token 32 consecutive features per warp).
+                    float* exch = reinterpret_cast<float*>(gen + L::TILES + L::N_BARS * 8 + 16);
+                    const bool up_warp = quarter >= 2;
+                    const int frow = (quarter & 1) * 32 + lane;        // feature within the block of 64
+#pragma unroll 1
+                    for (int c = 0; c < BN; c += 16) {
+                        uint32_t r[16];
+                        __syncwarp();
+                        tmem_ld16(acc + c, r);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (up_warp) {
+                            float4* dst = reinterpret_cast<float4*>(exch + frow * 16);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+                                dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                     __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                        }
+                        asm volatile("bar.sync 1, 128;" ::: "memory");     // the four epilogue warps
+                        if (!up_warp && alive) {
+                            const float4* src = reinterpret_cast<const float4*>(exch + frow * 16);
+                            const int feature = (x0 >> 1) + frow;
+#pragma unroll
+                            for (int q4 = 0; q4 < 4; ++q4) {
+                                const float4 u4 = src[q4];
+                                const float uu[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const int y = y0 + c + 4 * q4 + e;
+                                    if (y < p.y_rows && x0 + (quarter & 1) * 32 + lane < p.x_rows) {
+                                        const float z = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[4 * q4 + e])));
+                                        const float v = __bfloat162float(__float2bfloat16_rn(uu[e]));
+                                        ((__nv_bfloat16*)p.out)[(long long)y * p.stride_y + feature] =
+                                            __float2bfloat16_rn(__fmul_rn(z / (1.0f + expf(-z)), v));
+                                    }
+                                }
+                            }
+                        }
+                        asm volatile("bar.sync 1, 128;" ::: "memory");     // the buffer is free for the next chunk
                     }
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
@@ -435,15 +487,19 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, di
 // store (X = weights), stride_y == 1 the row store (X = tokens).  bn: tile width along y, one of
 // 16, 32, 64, 128, 256, and for the row store also 160, 192, 208, 224.  splits >= 1 divides the K blocks among blockIdx.z.  x_is_constant says
 // which operand holds weights: its first tiles are fetched before the kernel waits for the
-// kernels before it in the stream (programmatic dependent launch).  gated: Y holds gate and up
-// weights interleaved in blocks of 128 rows; out[x, j] = silu(D[x, gate row of j]) * D[x, up row of j]
-// for j < y_rows / 2 (row store, bn 256, one split, bf16 out).
+// kernels before it in the stream (programmatic dependent launch).  gated: the weight operand holds gate
+// and up rows interleaved in blocks of 64 (64 gate rows, the up rows of the same features, ...); the output is
+// silu(gate product) * (up product), half as many features: row store (weights = Y, bn 256, out[x, j]) or
+// transposed store (weights = X, bn <= 128, out[y * stride_y + j]); one split, bf16 out.
 PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* Y, int y_rows, long long ldy, int K,
                           void* out, int out_f32, long long stride_x, long long stride_y, long long split_stride,
                           int splits, int bn, int x_is_constant, int gated, int* err_flag, cudaStream_t stream) {
     if (x_rows <= 0 || y_rows <= 0) return 0;
-    // the gated epilogue: tokens on the row side, whole 256-wide tiles of interleaved gate/up rows, bf16 rows out
-    if (gated && (stride_y != 1 || bn != 256 || splits != 1 || out_f32 || y_rows % 256)) return PYRE_ERR_BAD_ARG;
+    // the gated epilogue: whole tiles of gate/up rows interleaved in blocks of 64, one split, bf16 out; with the
+    // tokens on the row side 256-wide tiles, with the weights on the row side at most 128 tokens per tile
+    if (gated && (splits != 1 || out_f32)) return PYRE_ERR_BAD_ARG;
+    if (gated && stride_y == 1 && stride_x != 1 && (bn != 256 || y_rows % 256)) return PYRE_ERR_BAD_ARG;
+    if (gated && stride_x == 1 && (bn > 128 || x_rows % 128)) return PYRE_ERR_BAD_ARG;
     if (K <= 0 || K % 8 || ldx % 8 || ldy % 8 || splits < 1) return PYRE_ERR_UNSUPPORTED;
     if (((uintptr_t)X & 15) || ((uintptr_t)Y & 15)) return PYRE_ERR_UNSUPPORTED;
     if (stride_x != 1 && stride_y != 1) return PYRE_ERR_BAD_ARG;

@@ -518,7 +518,7 @@ def tc_gemm_plan(M: int, N: int, K: int) -> tuple[bool, int, int]:
     return False, bn, splits
 
 
-GATED_BLOCK = 128    # gate and up rows of a fused feed-forward weight alternate in blocks of this many features
+GATED_BLOCK = 64     # gate and up rows of a fused feed-forward weight alternate in blocks of this many features
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
@@ -530,8 +530,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     as ``PartialSums`` for a consumer kernel that adds them itself.
 
     ``gated``: w holds gate and up rows alternating in blocks of ``GATED_BLOCK`` features; the
-    result is silu(x gate^T) * (x up^T), [M, N / 2] bf16.  With the tokens on the row side and
-    whole 256-wide tiles the activation runs in the product's epilogue; otherwise after it."""
+    result is silu(x gate^T) * (x up^T), [M, N / 2] bf16.  The activation runs in the product's
+    epilogue (whole tiles, one split: the usual case in both orientations), otherwise after it."""
     if not tc_gemm_supported(x, w):
         raise UnsupportedSize("gemm_tc needs bf16 operands with K and leading dimensions that are multiples of 8")
     M, K = x.shape
@@ -544,12 +544,17 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     if gated:
         if N % (2 * GATED_BLOCK) or out_dtype != torch.bfloat16:
             raise UnsupportedSize("a gated product needs whole blocks of gate and up rows and a bfloat16 result")
-        if not weights_as_rows and plan is None:
+        if not weights_as_rows and plan is None and N % 256 == 0:
             bn, splits = 256, 1      # the fused activation needs whole 256-wide tiles and saves more than a better fit
-        if not weights_as_rows and bn == 256 and splits == 1:
+        if not weights_as_rows and bn == 256 and splits == 1 and N % 256 == 0:
             out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
             lib.call("pyre_gemm_tc", x.data_ptr(), M, x.stride(0), w.data_ptr(), N, w.stride(0), K, out.data_ptr(), 0,
                      N // 2, 1, 0, 1, bn, 0, 1, err.data_ptr(), _stream())
+            return out
+        if weights_as_rows and bn <= 128 and splits == 1 and N % 128 == 0:
+            out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+            lib.call("pyre_gemm_tc", w.data_ptr(), N, w.stride(0), x.data_ptr(), M, x.stride(0), K, out.data_ptr(), 0,
+                     1, N // 2, 0, 1, bn, 1, 1, err.data_ptr(), _stream())
             return out
         return silu_mul(gemm_tc(x, w, torch.bfloat16, (weights_as_rows, bn, splits)), block=GATED_BLOCK)
     if splits == 1 and reduce:

@@ -12,7 +12,7 @@ from .base import Part, register_part
 class GatedMLP(Part):
     """down(act(gate(h)) * up(h)) without biases.  The gate and up weights are stacked
     into one [2 I, width] matrix at load, so one product feeds the activation; in bfloat16,
-    when I is a multiple of 128, their rows alternate in blocks of 128 features so that one
+    when I is a multiple of 128, their rows alternate in blocks of 64 features so that one
     output tile of the product holds both halves and the activation runs in its epilogue."""
 
     graph_safe = True
@@ -23,7 +23,7 @@ class GatedMLP(Part):
         if activation != "silu":
             raise ops.UnsupportedSize(f"activation {activation!r}: only silu is implemented")
         self.w_gate_up = self.w_down = None
-        self.interleaved = dtype == torch.bfloat16 and self.intermediate % ops.GATED_BLOCK == 0
+        self.interleaved = dtype == torch.bfloat16 and self.intermediate % (2 * ops.GATED_BLOCK) == 0
 
     def tensors(self):
         return {
