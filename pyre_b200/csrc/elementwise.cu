@@ -381,9 +381,10 @@ PYRE_API int pyre_qkv_rope_write(const void* qkv, const float* partials, int n_p
     if (hd % 8 || rot % 8 || rot > hd || rot < 0 || page_size <= 0) return PYRE_ERR_BAD_ARG;
     if ((qkv == nullptr) == (partials == nullptr)) return PYRE_ERR_BAD_ARG;
     if (partials && n_partials < 1) return PYRE_ERR_BAD_ARG;
-    // rotary over the whole head: the pair kernel, 8 bf16 (4 fp32) per access
+    // rotary over the whole head and many tokens (a bandwidth-bound pass): the pair kernel, 8 bf16 (4 fp32) per
+    // access; few tokens (a latency-bound pass) keep the narrower items of the general kernel: more threads, shorter chains
     const int vec = dtype == PYRE_BF16 ? 8 : 4;
-    const bool full = rot == hd && hd % (2 * vec) == 0;
+    const bool full = rot == hd && hd % (2 * vec) == 0 && n_tokens >= 256;
     const int items = full ? (nh + 2 * nkv) * (hd / (2 * vec)) : (nh + 2 * nkv) * (hd / 4);
     const int threads = min(128, max(32, ((items + 31) / 32) * 32));
     // few tokens: spread a token's items over several blocks (one item per thread); many tokens:

@@ -287,8 +287,8 @@ _SM_COUNT = 148
 def attention_splits(n_tokens: int, n_seqs: int, n_heads: int, n_kv_heads: int, max_context: int,
                      window: "int | None", n_groups: "int | None" = None) -> int:
     """How many ways the tensor-core kernel splits each sequence's keys: enough CTAs for
-    two per SM, at least two 16-key tiles per split, at most 16 (the splits of a group
-    form one thread-block cluster)."""
+    about one and a half per SM, at least two 16-key tiles per split, at most 16 (the
+    splits of a group form one thread-block cluster)."""
     n_rep = n_heads // n_kv_heads
     hpg = min(n_rep, 16)
     tpg = 16 // hpg
@@ -297,10 +297,13 @@ def attention_splits(n_tokens: int, n_seqs: int, n_heads: int, n_kv_heads: int, 
     ctas = n_groups * n_kv_heads * (-(-n_rep // hpg))
     span = max_context if not window else min(max_context, window + tpg)
     tiles = -(-span // 16) + 1
-    want = max(1, min(2 * _SM_COUNT // max(ctas, 1), -(-tiles // 2), CLUSTER_MAX_SPLITS))
+    # Measured inside whole decode steps (7B shape, contexts of 2-3 thousand tokens): about one and a half CTAs per
+    # SM in all is best (batch 8: 7 splits, 16: 4, 32: 2, 64: 1); with two per SM the product that follows
+    # finds no SM on which to prefetch its weights while the attention runs.
+    want = max(1, min(int(1.57 * _SM_COUNT / max(ctas, 1) + 0.5), -(-tiles // 2), CLUSTER_MAX_SPLITS))
     if want > 8:
         # a cluster of 16 CTAs must sit in one GPC: it pays only while all of them fit on the chip at once
-        return 16 if ctas * 16 <= _SM_COUNT else 8
+        return 16 if ctas * 16 <= _SM_COUNT else min(want, 10)
     return int(want)
 
 

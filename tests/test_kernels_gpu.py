@@ -173,13 +173,15 @@ def plain_rope(x, pos, inv, rot):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd,rot,page,theta", [(4, 2, 16, 16, 16, 1e4), (3, 1, 32, 32, 8, 1e6),
                                                      (5, 5, 48, 32, 4, 5e4), (28, 4, 128, 128, 16, 1e6)])
-def test_qkv_rope_write(ops, dtype, nh, nkv, hd, rot, page, theta):
+@pytest.mark.parametrize("T", [13, 300])      # few tokens and many tokens take different kernels when the rotary covers the head
+def test_qkv_rope_write(ops, dtype, nh, nkv, hd, rot, page, theta, T):
     g = torch.Generator(device="cuda").manual_seed(4)
-    T, pages = 13, 9
+    pages = -(-T // page) + 8
     width = (nh + 2 * nkv) * hd
     qkv = torch.randn(T, width, device="cuda", generator=g).to(dtype)
     bias = torch.randn(width, device="cuda", generator=g) * 0.5
-    pos = torch.tensor([0, 1, 2, 3, 40, 41, 1000, 7, 8, 9, 30000, 5, 6], dtype=torch.int32, device="cuda")
+    base = [0, 1, 2, 3, 40, 41, 1000, 7, 8, 9, 30000, 5, 6]
+    pos = torch.tensor([base[t] if t < 13 else (t * 37) % 9001 for t in range(T)], dtype=torch.int32, device="cuda")
     slots = torch.randperm(pages * page, device="cuda", generator=g)[:T].to(torch.int32)
     slots[3] = -1  # this token stores nothing
     inv = (1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))).cuda()
