@@ -121,15 +121,22 @@ struct GemmParams {
     int* err_flag;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool XC>
 struct SmemLayout {
     static constexpr int X_BYTES = BM * BK * 2;
     static constexpr int Y_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = X_BYTES + Y_BYTES;
     static constexpr int TILES = STAGES * STAGE_BYTES;
     static constexpr int N_BARS = 2 * STAGES + 4;     // full, empty per stage; accumulator full, empty per TMEM buffer
-    static constexpr int EXCH_BYTES = BN <= 128 ? 64 * BN * 4 : 0;  // gated transposed epilogue: 64 up rows x BN tokens, fp32
-    static constexpr int TOTAL = TILES + N_BARS * 8 + 16 + EXCH_BYTES + 1024;  // + tmem slot and abort flag, alignment slack
+    static constexpr int EPI_OFF = TILES + N_BARS * 8 + 16;
+    // transposed store: the gated epilogue's exchange of 64 up rows x BN tokens (fp32) between epilogue warps;
+    // row store: per epilogue warp 32 rows x GW bf16 (pitch 2 GW + 16 bytes) for stores of whole lines, GW = 64
+    // (128-byte lines) if the ring leaves room, else 32, else 0 (every thread stores its own 32 bytes)
+    static constexpr int ROOM = 232448 - 1024 - EPI_OFF;
+    static constexpr int GW = XC ? 0 : (ROOM >= 4 * 32 * 144 ? 64 : ROOM >= 4 * 32 * 80 ? 32 : 0);
+    static constexpr int OUT_PITCH = 2 * GW + 16;
+    static constexpr int EPI_BYTES = XC ? (BN <= 128 ? 64 * BN * 4 : 0) : 4 * 32 * OUT_PITCH * (GW > 0 ? 1 : 0);
+    static constexpr int TOTAL = EPI_OFF + EPI_BYTES + 1024;  // bars, tmem slot and abort flag, epilogue buffer, alignment slack
 };
 
 // A CTA is persistent: it walks output tiles c, c + gridDim.x, ...  Two TMEM accumulators
@@ -138,7 +145,7 @@ struct SmemLayout {
 template <int BN, int STAGES, bool X_CONTIGUOUS_OUT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const GemmParams p) {
-    using L = SmemLayout<BN, STAGES>;
+    using L = SmemLayout<BN, STAGES, X_CONTIGUOUS_OUT>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles want 1024-byte alignment
     uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
@@ -276,21 +283,50 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const long long out_base = (long long)blockIdx.z * p.split_stride + (long long)xr * p.stride_x;
             const uint32_t acc = tmem_base + buf * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+            // Row store of bf16: a thread owns a row, but 32 threads writing 32 bytes each of 32 different rows waste
+            // the memory system's lines.  64 columns of the warp's 32 rows go through shared memory instead and leave
+            // as whole 128-byte lines (eight lanes per row, four rows per instruction).
+            constexpr int GW = L::GW;     // columns per staged group (0: no staging)
+            [[maybe_unused]] const uint32_t out_stage = base + L::EPI_OFF + (X_CONTIGUOUS_OUT ? 0 : quarter * 32 * L::OUT_PITCH);
+            [[maybe_unused]] auto store_lines = [&](const uint32_t (&w)[GW > 0 ? GW / 2 : 1], long long col0, long long row_stride) {
+                // w: GW bf16 of this thread's row, columns col0 .. col0 + GW - 1 of the output
+                if constexpr (GW > 0) {
+                    constexpr int LPR = GW / 8;            // lanes (16-byte pieces) per row
+                    __syncwarp();
+#pragma unroll
+                    for (int q = 0; q < LPR; ++q)
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(out_stage + lane * L::OUT_PITCH + q * 16),
+                                     "r"(w[4 * q]), "r"(w[4 * q + 1]), "r"(w[4 * q + 2]), "r"(w[4 * q + 3]) : "memory");
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < LPR; ++i) {
+                        const int rr = i * (32 / LPR) + lane / LPR, piece = lane % LPR;
+                        uint32_t v0, v1, v2, v3;
+                        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
+                                     : "r"(out_stage + rr * L::OUT_PITCH + piece * 16) : "memory");
+                        const int grow = x0 + quarter * 32 + rr;
+                        if (alive && grow < p.x_rows)
+                            *reinterpret_cast<uint4*>((__nv_bfloat16*)p.out + (long long)blockIdx.z * p.split_stride + grow * row_stride + col0 + piece * 8) =
+                                make_uint4(v0, v1, v2, v3);
+                    }
+                }
+            };
             if constexpr (!X_CONTIGUOUS_OUT && BN == 256) {
                 if (p.gated) {
                     // the tile's columns are two blocks of 64 gate features followed by the 64 up features of the
                     // same indices: out[x, y0 / 2 + c] = silu(gate) * up, with the products rounded to bfloat16
                     // first (as a separate activation kernel would read them) and the rest in fp32
 #pragma unroll 1
-                    for (int c = 0; c < 128; c += 16) {
-                        uint32_t g[16], u[16];
-                        const int gc = (c >> 6) * 128 + (c & 63);   // column of gate feature c of this tile
-                        __syncwarp();
-                        tmem_ld16(acc + gc, g);
-                        tmem_ld16(acc + gc + 64, u);
-                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        if (alive && xr < p.x_rows) {
-                            uint32_t w[8];
+                    for (int blk = 0; blk < 2; ++blk) {      // 64 output features per block of 64 gates + 64 ups
+                        static_assert(BN != 256 || L::GW == 64, "the gated epilogue stages 64 columns");
+                        uint32_t w[32];
+#pragma unroll
+                        for (int cc = 0; cc < 64; cc += 16) {
+                            uint32_t g[16], u[16];
+                            __syncwarp();
+                            tmem_ld16(acc + blk * 128 + cc, g);
+                            tmem_ld16(acc + blk * 128 + 64 + cc, u);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                             for (int q = 0; q < 8; ++q) {
                                 float o[2];
@@ -301,12 +337,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                                     o[e] = __fmul_rn(z / (1.0f + expf(-z)), v);
                                 }
                                 __nv_bfloat162 pr = __floats2bfloat162_rn(o[0], o[1]);
-                                w[q] = *reinterpret_cast<uint32_t*>(&pr);
+                                w[cc / 2 + q] = *reinterpret_cast<uint32_t*>(&pr);
                             }
-                            uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)p.out + out_base + (y0 >> 1) + c);
-                            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
                         }
+                        store_lines(w, (y0 >> 1) + blk * 64, p.stride_x);
                     }
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
@@ -320,7 +354,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     // up features of the same indices (rows 64..127), its columns are tokens.  The up warps hand
                     // their values over through shared memory; the gate warps compute silu(gate) * up as above and
                     // store out[token, x0 / 2 + row] (for a token 32 consecutive features per warp).
-                    float* exch = reinterpret_cast<float*>(gen + L::TILES + L::N_BARS * 8 + 16);
+                    float* exch = reinterpret_cast<float*>(gen + L::EPI_OFF);
                     const bool up_warp = quarter >= 2;
                     const int frow = (quarter & 1) * 32 + lane;        // feature within the block of 64
 #pragma unroll 1
@@ -364,8 +398,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     continue;
                 }
             }
+            int c_begin = 0;
+            if constexpr (!X_CONTIGUOUS_OUT && GW > 0) {
+                if (!p.out_f32 && n_kb > 0) {
+                    const int whole = min(BN, p.y_rows - y0) / GW;      // groups of GW columns inside the matrix
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
+                    for (int gq = 0; gq < whole; ++gq) {
+                        uint32_t w[GW / 2];
+#pragma unroll
+                        for (int cc = 0; cc < GW; cc += 16) {
+                            uint32_t r[16];
+                            __syncwarp();
+                            tmem_ld16(acc + gq * GW + cc, r);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * q]), __uint_as_float(r[2 * q + 1]));
+                                w[cc / 2 + q] = *reinterpret_cast<uint32_t*>(&v);
+                            }
+                        }
+                        store_lines(w, y0 + gq * GW, p.stride_x);
+                    }
+                    c_begin = whole * GW;
+                }
+            }
+#pragma unroll 1
+            for (int c = c_begin; c < BN; c += 16) {
                 uint32_t r[16];
                 __syncwarp();   // tcgen05.ld is warp-wide: converge after the per-thread stores
                 if (n_kb > 0) {
@@ -467,7 +525,7 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, long long ld, i
 
 template <int BN, int STAGES, bool XC>
 int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, dim3 grid, cudaStream_t stream) {
-    using L = SmemLayout<BN, STAGES>;
+    using L = SmemLayout<BN, STAGES, XC>;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, XC>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
@@ -545,7 +603,7 @@ PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* 
         case 256: GO(256, 4); break;
         // widths between 128 and 256 exist for the row-store orientation only: they let the planner pick the
         // tile count that fills the rounds of the persistent CTAs best
-        case 160: if (xc) return PYRE_ERR_BAD_ARG; rc = launch<160, 6, false>(mx, my, p, grid, stream); break;
+        case 160: if (xc) return PYRE_ERR_BAD_ARG; rc = launch<160, 5, false>(mx, my, p, grid, stream); break;
         case 192: if (xc) return PYRE_ERR_BAD_ARG; rc = launch<192, 5, false>(mx, my, p, grid, stream); break;
         case 208: if (xc) return PYRE_ERR_BAD_ARG; rc = launch<208, 5, false>(mx, my, p, grid, stream); break;
         case 224: if (xc) return PYRE_ERR_BAD_ARG; rc = launch<224, 5, false>(mx, my, p, grid, stream); break;
