@@ -599,17 +599,43 @@ __global__ void combine_splits_kernel(const float* __restrict__ part_acc, const 
                 break;
             }
     }
+    // blockDim.x (32 or 64) splits at a time: one split's (max, sum) per thread, the factors 2^(m_s - M) shared,
+    // then every thread adds up its output dims with independent loads
+    __shared__ float sm_f[64];
+    __shared__ float sm_red[2];
+    __shared__ float sm_out[128];
     const float* ml = part_ml + th * n_splits * 2;
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, ml[2 * s]);
-    const float m_use = (M == -INFINITY) ? 0.f : M;
-    float L = 0.f;
-    for (int s = 0; s < n_splits; ++s) L += ml[2 * s + 1] * exp2f(ml[2 * s] - m_use);
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-        float O = 0.f;
-        for (int s = 0; s < n_splits; ++s) O += part_acc[(th * n_splits + s) * hd + d] * exp2f(ml[2 * s] - m_use);
-        out[th * hd + d] = __float2bfloat16_rn(O / L);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, chunk = blockDim.x;
+    float M = -INFINITY, L = 0.f;
+    for (int s0 = 0; s0 < n_splits; s0 += chunk) {
+        const int s = s0 + tid;
+        const float m_s = s < n_splits ? ml[2 * s] : -INFINITY;
+        const float l_s = s < n_splits ? ml[2 * s + 1] : 0.f;
+        float cm = warp_max(m_s);
+        if (lane == 0) sm_red[warp] = cm;
+        __syncthreads();
+        cm = chunk > 32 ? fmaxf(sm_red[0], sm_red[1]) : sm_red[0];
+        const float M_new = fmaxf(M, cm);
+        const float m_use = (M_new == -INFINITY) ? 0.f : M_new;
+        const float f = exp2f(m_s - m_use);                // 0 for the padding
+        float cl = warp_sum(l_s * f);
+        __syncthreads();
+        if (lane == 0) sm_red[warp] = cl;
+        sm_f[tid] = f;
+        __syncthreads();
+        cl = chunk > 32 ? sm_red[0] + sm_red[1] : sm_red[0];
+        const float rescale = exp2f(M - m_use);            // 0 the first time (M = -inf)
+        L = L * rescale + cl;
+        const int n = min(chunk, n_splits - s0);
+        for (int d = tid; d < hd; d += chunk) {
+            float O = s0 == 0 ? 0.f : sm_out[d] * rescale;
+            for (int k = 0; k < n; ++k) O += part_acc[(th * n_splits + s0 + k) * hd + d] * sm_f[k];
+            sm_out[d] = O;
+        }
+        M = M_new;
+        __syncthreads();
     }
+    for (int d = tid; d < hd; d += chunk) out[th * hd + d] = __float2bfloat16_rn(sm_out[d] / L);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

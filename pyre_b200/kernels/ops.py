@@ -288,7 +288,8 @@ def attention_splits(n_tokens: int, n_seqs: int, n_heads: int, n_kv_heads: int, 
                      window: "int | None", n_groups: "int | None" = None) -> int:
     """How many ways the tensor-core kernel splits each sequence's keys: enough CTAs for
     about one and a half per SM, at least two 16-key tiles per split, at most 16 (the
-    splits of a group form one thread-block cluster)."""
+    splits of a group form one thread-block cluster), or 32 through scratch memory for a
+    single very long sequence."""
     n_rep = n_heads // n_kv_heads
     hpg = min(n_rep, 16)
     tpg = 16 // hpg
@@ -303,7 +304,13 @@ def attention_splits(n_tokens: int, n_seqs: int, n_heads: int, n_kv_heads: int, 
     want = max(1, min(int(1.57 * _SM_COUNT / max(ctas, 1) + 0.5), -(-tiles // 2), CLUSTER_MAX_SPLITS))
     if want > 8:
         # a cluster of 16 CTAs must sit in one GPC: it pays only while all of them fit on the chip at once
-        return 16 if ctas * 16 <= _SM_COUNT else min(want, 10)
+        if ctas * 16 > _SM_COUNT:
+            return min(want, 10)
+        # one or two sequences with tens of thousands of keys: 16 CTAs per group leave most SMs idle; 32 splits
+        # through scratch memory and the combining kernel win from about 24 thousand keys on
+        if ctas * 32 <= _SM_COUNT and tiles >= 1536:
+            return 32
+        return 16
     return int(want)
 
 

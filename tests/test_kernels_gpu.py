@@ -563,9 +563,10 @@ def test_attention_long_context(ops, nh, nkv, hd, page, window):
     for row, pg, off in marks:
         v_far = cache[pg, 1, 0, off].float()
         assert (got[row, :hd].float() - v_far).abs().max() < 0.25 * v_far.abs().max() + 0.1
-    # the decode token alone through the split-KV kernel: one split (long walks per warp), clusters of 4 and 16
+    # the decode token alone through the split-KV kernel: one split (long walks per warp), clusters of 4 and 16,
+    # and 32 splits, which go through scratch memory and the combining kernel
     dec_cu = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
-    for n_splits in (1, 4, 16):
+    for n_splits in (1, 4, 16, 32):
         alone = ops.paged_attention_mma(q[700:].contiguous(), cache, table[1:2].contiguous(), dec_cu, positions[700:].contiguous(),
                                         1, nh, nkv, hd, scale, window, n_splits, uniform_len=1)
         ops.check_device_errors()
