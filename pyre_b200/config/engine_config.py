@@ -37,6 +37,9 @@ class EngineConfig:
     IEEE fp32, no reduced-precision matrix mode).
     ``page_size``: tokens per cache page (the reference's BLOCK_SIZE).
     ``max_cache_tokens``: capacity of the paged pools in tokens; ``num_pages`` wins if set.
+    ``cache_memory_fraction``: with neither of the two, size the pools to this fraction of the
+    device memory that is free once the weights are loaded (less a reserve for the activations
+    of the largest step); None keeps a small default (8 requests of 8,192 tokens).
     ``max_num_seqs``: most requests live at once (also the number of state slots).
     ``max_num_batched_tokens``: token budget of one step.
     ``prefill_chunk``: most prompt tokens of one request in one step.
@@ -51,6 +54,7 @@ class EngineConfig:
     page_size: int = 16
     num_pages: int | None = None
     max_cache_tokens: int | None = None
+    cache_memory_fraction: float | None = None
     max_num_seqs: int = 64
     max_num_batched_tokens: int = 2048
     prefill_chunk: int = 2048
@@ -63,6 +67,8 @@ class EngineConfig:
         self.dtype = parse_dtype(self.dtype)
         if self.page_size <= 0:
             raise ValueError("page_size must be positive")
+        if self.cache_memory_fraction is not None and not 0.0 < self.cache_memory_fraction <= 1.0:
+            raise ValueError("cache_memory_fraction must lie in (0, 1]")
         if self.max_num_seqs <= 0 or self.max_num_batched_tokens <= 0 or self.prefill_chunk <= 0:
             raise ValueError("max_num_seqs, max_num_batched_tokens and prefill_chunk must be positive")
 

@@ -65,6 +65,8 @@ class Engine:
         max_positions = spec.max_positions or (1 << 20)
         default_tokens = min(max_positions, 8192) * min(ec.max_num_seqs, 8)
         num_pages = ec.resolve_num_pages(default_tokens)
+        if ec.num_pages is None and ec.max_cache_tokens is None and ec.cache_memory_fraction:
+            num_pages = self._pages_for_memory(ec, spec)
         self.max_model_len = min(ec.max_model_len or max_positions, num_pages * ec.page_size)
         self.cache = CacheManager(self.model.kv_groups, self.model.state_groups, ec.page_size, num_pages,
                                   ec.max_num_seqs, ec.dtype, ec.device)
@@ -77,6 +79,25 @@ class Engine:
         self._flight = None      # (plan, sampling ticket, error word) of the step whose ids have not been read yet
         self._err_host = [torch.zeros(1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._err_turn = 0
+
+    def _pages_for_memory(self, ec: EngineConfig, spec) -> int:
+        """Pages per group so that all pools together take ``cache_memory_fraction`` of the memory that is free
+        now (the weights are on the device), less a reserve for the activations of the largest step."""
+        free, _total = torch.cuda.mem_get_info(self.model.device)
+        elem = torch.empty((), dtype=ec.dtype).element_size()
+        per_page = sum(g.n_layers * 2 * g.spec.n_kv_heads * g.spec.head_dim * ec.page_size * elem for g in self.model.kv_groups)
+        if per_page == 0:
+            return 1
+        # activations of a step: a few buffers as wide as the widest matrix output per token (the vocabulary aside),
+        # fp32 logits of the wanted rows (one per request in generation), and a gigabyte for everything small
+        widest = max([t.shape[0] for t in self.model.tensor_table().values()
+                      if len(t.shape) == 2 and t.shape[0] != self.model.vocab_size] or [4096])
+        reserve = ec.max_num_batched_tokens * widest * 8 + ec.max_num_seqs * self.model.vocab_size * 8 + (1 << 30)
+        budget = int(free * ec.cache_memory_fraction) - reserve
+        if budget < per_page:
+            raise RuntimeError(f"cache_memory_fraction {ec.cache_memory_fraction} of {free / 2**30:.1f} GiB free leaves no room "
+                               f"for a page of {per_page / 2**20:.1f} MiB after a reserve of {reserve / 2**30:.1f} GiB")
+        return budget // per_page
 
     # ------------------------------------------------------------------ the reference's two calls
     def add_request(self, prompt_ids: Sequence[int], max_new_tokens: int = 16, eos_id: "int | None" = None,

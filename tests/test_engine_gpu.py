@@ -248,3 +248,18 @@ def test_a_raised_error_flag_stops_generation(model_dirs):
     with pytest.raises(lib.KernelError, match="bounded wait"):
         eng.generate([prompt], SamplingParams(max_new_tokens=4))
     assert int(ops.device_error_flag(eng.model.device).item()) == 0
+
+
+def test_cache_sized_by_a_fraction_of_free_memory(model_dirs):
+    """Without a page count the pools can take a fraction of what the device has free after loading."""
+    from pyre_b200 import Engine, SamplingParams
+    d, raw = model_dirs["A"], H.TINY["A"]
+    free_before, _ = torch.cuda.mem_get_info()
+    eng = Engine(d, dtype="bfloat16", cache_memory_fraction=0.02, max_num_seqs=4)
+    pool_bytes = sum(g.pool.numel() * g.pool.element_size() for g in eng.cache.groups)
+    assert 0 < pool_bytes <= 0.02 * free_before
+    assert pool_bytes >= 0.02 * free_before - (3 << 30)          # what is not reserved for activations is used
+    out = eng.generate([H.random_ids(raw["vocab_size"], 20, seed=1)], SamplingParams(max_new_tokens=5))[0]
+    assert len(out.token_ids) == 5
+    with pytest.raises(ValueError):
+        Engine(d, cache_memory_fraction=1.5)
