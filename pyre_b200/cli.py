@@ -36,7 +36,7 @@ def cmd_generate(args) -> int:
         print("no prompts: give --prompt-ids or --prompt-ids-file", file=sys.stderr)
         return 2
     ec = EngineConfig(dtype=args.dtype, device=args.device, page_size=args.page_size, num_pages=args.num_pages,
-                      cache_memory_fraction=args.cache_memory_fraction,
+                      cache_memory_fraction=args.cache_memory_fraction, lookahead=not args.no_lookahead,
                       max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_batched_tokens,
                       prefill_chunk=args.prefill_chunk)
     print(f"loading {args.model} on {args.device} ...", file=sys.stderr)
@@ -92,6 +92,8 @@ def main(argv=None) -> int:
     g.add_argument("--eos-id", type=int, default=None)
     g.add_argument("--page-size", type=int, default=16, help="tokens per cache page")
     g.add_argument("--num-pages", type=int, default=None, help="pages of the cache pool")
+    g.add_argument("--no-lookahead", action="store_true",
+                   help="read every step's ids before the next step is started (the strictly sequential loop)")
     g.add_argument("--cache-memory-fraction", type=float, default=None,
                    help="without --num-pages: size the cache to this fraction of the device memory left after loading")
     g.add_argument("--max-num-seqs", type=int, default=64, help="most requests live at once")
