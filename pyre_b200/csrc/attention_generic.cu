@@ -66,20 +66,22 @@ __global__ void paged_attention_generic_kernel(
             const size_t krow = ((size_t)(page * 2) * nkv + kvh) * page_size + off;
             vrow = (int)(((size_t)(page * 2 + 1) * nkv + kvh) * page_size + off);
             const T* kp = cache + krow * hd;
-            float dot = 0.f;
+            // four interleaved chains (dims e, e + 4 of every 8), added as a tree: shorter sums round less
+            float dot[4] = {0.f, 0.f, 0.f, 0.f};
             for (int d = 0; d < hd; d += 8) {
                 Vec<T, 8> kv = load_vec<T, 8>(kp + d);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + e], to_f32<T>(kv.v[e]), dot);
+                for (int e = 0; e < 8; ++e) dot[e & 3] = fmaf(qs[d + e], to_f32<T>(kv.v[e]), dot[e & 3]);
             }
-            score = dot * scale;
+            score = ((dot[0] + dot[1]) + (dot[2] + dot[3])) * scale;
         }
         const float m_new = fmaxf(m, warp_max(score));
         const float p = valid ? expf(score - m_new) : 0.f;
         const float alpha = expf(m - m_new);  // m = -inf at the start: exp(-inf) = 0
         l = l * alpha + warp_sum(p);
+        float part[8];  // this chunk's share of the output, summed on its own and then added to the older keys'
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] *= alpha;
+        for (int i = 0; i < 8; ++i) part[i] = 0.f;
         const int n_keys = min(32, pos - c + 1);
         for (int jj = 0; jj < n_keys; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
@@ -89,9 +91,11 @@ __global__ void paged_attention_generic_kernel(
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const int d = lane + 32 * i;
-                if (i < n_own && d < hd) acc[i] = fmaf(pj, to_f32<T>(vp[d]), acc[i]);
+                if (i < n_own && d < hd) part[i] = fmaf(pj, to_f32<T>(vp[d]), part[i]);
             }
         }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = fmaf(acc[i], alpha, part[i]);
         m = m_new;
     }
     const float inv_l = 1.0f / l;

@@ -2,9 +2,11 @@
 //
 // IEEE fp32 multiply-add on the CUDA cores, no tensor-core or TF32 mode anywhere.  W has
 // the layout of a linear layer's weight ([out, in], in-dim contiguous, pyre/model.py:84-87
-// via nn.Linear).  Every output element is one chain acc = fma(a[k], w[k], acc) over
-// k = 0..K-1 in ascending order, whatever tile shape computes it: a row's result is
-// bit-identical for any M and any batch composition.
+// via nn.Linear).  Every output element is summed in two levels: a chain
+// part = fma(a[k], w[k], part) over each run of 32 consecutive k (from k = 0, ascending),
+// and the runs' sums added in ascending order.  The rounding error then grows with
+// K / 32 + 32 terms instead of K.  The grouping depends on k alone, whatever tile shape
+// computes it: a row's result is bit-identical for any M and any batch composition.
 //
 // Two tile shapes (same arithmetic): 128x128 with 8x8 per thread for many rows,
 // 32x128 with 2x8 per thread for few (decode).
@@ -24,11 +26,13 @@ sgemm_nt_kernel(const float* __restrict__ A, long long lda, const float* __restr
     const int ty = tid / (BN / TN);  // row group
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
 
-    float acc[TM][TN];
+    constexpr int RUN = 32;  // k per first-level sum; a multiple of both tile depths
+    static_assert(RUN % BK == 0, "a run of the first level must end at a tile's end");
+    float acc[TM][TN], part[TM][TN];
 #pragma unroll
     for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+        for (int j = 0; j < TN; ++j) acc[i][j] = part[i][j] = 0.f;
 
     for (int k0 = 0; k0 < K; k0 += BK) {
         // tile loads: consecutive threads read consecutive k of one row
@@ -53,7 +57,16 @@ sgemm_nt_kernel(const float* __restrict__ A, long long lda, const float* __restr
 #pragma unroll
             for (int i = 0; i < TM; ++i)
 #pragma unroll
-                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+                for (int j = 0; j < TN; ++j) part[i][j] = fmaf(a[i], w[j], part[i][j]);
+        }
+        if ((k0 + BK) % RUN == 0 || k0 + BK >= K) {
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) {
+                    acc[i][j] += part[i][j];
+                    part[i][j] = 0.f;
+                }
         }
         __syncthreads();
     }
