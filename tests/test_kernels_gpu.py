@@ -126,6 +126,17 @@ def test_sgemm_is_true_fp32(ops, M, N, K):
         assert torch.equal(ops.sgemm_nt(a[:1].contiguous(), w), got[:1])
 
 
+def test_sgemm_sums_in_two_levels(ops):
+    """Positive operands and a long K are the worst case of a single chain of additions (its
+    relative error passes 3e-6 at K = 8192); runs of 32 summed on their own stay under 1e-6."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a = torch.rand(40, 8192, device="cuda", generator=g)
+    w = torch.rand(96, 8192, device="cuda", generator=g)
+    want = a.double() @ w.double().t()
+    got = ops.sgemm_nt(a, w).double()
+    assert ((got - want).abs() / want).max().item() <= 2e-6
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 4608, 3584), (8, 3584, 3584), (8, 3584, 18944), (8, 37888, 3584), (5, 130, 72),
                                    (16, 256, 64), (17, 1000, 96), (64, 777, 200), (100, 640, 1024), (128, 152064 // 8, 512),
                                    (129, 512, 256), (300, 1000, 96), (300, 777, 200), (2048, 4608, 3584), (1000, 3584, 1888)])
