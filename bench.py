@@ -314,7 +314,9 @@ def run_workload(args) -> dict:
         return {"workload": "serve14b", "layers": cfg.num_hidden_layers, "requests": n_req, "prompt_tokens": n_in,
                 "output_tokens": n_out, "seconds": round(dt, 3), "output_tok_s": round(n_out / dt, 1),
                 "total_tok_s": round((n_in + n_out) / dt, 1), "steps": st["steps"], "preempted": st["preempted"],
-                "cache_tokens": int(need * args.cache_fraction), "finished": sum(r.finish_reason == "length" for r in res)}
+                "cache_tokens": int(need * args.cache_fraction), "finished": sum(r.finish_reason == "length" for r in res),
+                "graph_captures": eng.stepper.graph_captures, "graph_replays": eng.stepper.graph_replays,
+                "capture_seconds": round(eng.stepper.capture_seconds, 3)}
     raw = dict(SHAPES["32b"])
     if args.layers:
         raw["num_hidden_layers"] = args.layers

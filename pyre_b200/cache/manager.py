@@ -8,10 +8,13 @@ group, as in the reference, pyre/paged_cache.py:107), its own allocator and its 
 block table per request.  A group with a window gives a page back as soon as every
 position in it lies before the window of any token still to come; a group without one
 gives pages back when the request ends.  The reference has one implicit group and frees
-only at the end (pyre/paged_cache.py:163-167).
+only at the end (pyre/paged_cache.py:163-167).  Each pool has one page more than the
+allocator hands out (``scratch_page``), and each state buffer one slot more
+(``scratch_slot``): they belong to the rows with which a captured decode step is padded
+to a common size.
 
 State.  Beside the pages there is a slot per live request for state of fixed size
-(``StateSpec``), in buffers ``[layers, max_requests, *shape]`` per state group, zeroed when
+(``StateSpec``), in buffers ``[layers, max_requests + 1, *shape]`` per state group, zeroed when
 a request begins.  An architecture without such state has no buffers, but requests
 still take and return a slot, so the bookkeeping is exercised.
 
@@ -47,9 +50,12 @@ class PagedGroup:
         self.allocator = PageAllocator(num_pages)
         self.tables: dict[Hashable, list[int]] = {}      # logical page -> physical page, -1 once given back
         self.first_live: dict[Hashable, int] = {}        # first logical page not yet given back
+        # one page beyond the allocator's range belongs to no request: the rows that pad a captured step to a
+        # common size write their token there and read it back
+        self.scratch_page = num_pages
         self.pool = None
         if allocate_pool:
-            self.pool = torch.zeros((n_layers, num_pages, 2, spec.n_kv_heads, page_size, spec.head_dim),
+            self.pool = torch.zeros((n_layers, num_pages + 1, 2, spec.n_kv_heads, page_size, spec.head_dim),
                                     dtype=dtype, device=device)
         self.poison = False
 
@@ -114,9 +120,10 @@ class StateSlots:
         self._free = list(range(max_requests - 1, -1, -1))
         self.slot_of: dict[Hashable, int] = {}
         self.specs = [g for g, _ in groups]
+        self.scratch_slot = max_requests     # a slot beyond the requests' own, for the rows that pad a captured step
         self.buffers: list[torch.Tensor | None] = []
         for spec, n_layers in groups:
-            self.buffers.append(torch.zeros((n_layers, max_requests, *spec.shape), dtype=spec.dtype, device=device)
+            self.buffers.append(torch.zeros((n_layers, max_requests + 1, *spec.shape), dtype=spec.dtype, device=device)
                                 if allocate else None)
 
     @property

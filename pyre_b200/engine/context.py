@@ -23,7 +23,7 @@ class KVView:
 class StateView:
     """A state group during one step: ``buffer[layer, slots[b]]`` is request b's state."""
 
-    buffer: torch.Tensor          # [layers, max_requests, *shape]
+    buffer: torch.Tensor          # [layers, max_requests + 1, *shape]; the last slot is scratch
     slots: torch.Tensor           # int32 [B] on the device
     slots_host: np.ndarray
 

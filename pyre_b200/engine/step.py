@@ -10,6 +10,8 @@ two disjoint functions instead: one sequence with any number of tokens
 
 from __future__ import annotations
 
+import time
+
 from dataclasses import dataclass, field
 from typing import Hashable, Sequence
 
@@ -95,12 +97,25 @@ class Stepper:
 
     Steps that hold only single decoded tokens (one per entry, each wanting its logits) are
     launch-bound: a few hundred small kernels.  With ``cuda_graphs`` such a step is
-    captured once per shape (number of entries, width of the block tables, split count of
+    captured once per shape (number of rows, width of the block tables, split count of
     the attention) into a CUDA graph whose kernels read a static integer buffer; later
     steps of that shape copy their integers into the buffer and replay the graph.  The
-    arithmetic is the same launch sequence either way."""
+    arithmetic is the same launch sequence either way.  Above four entries the step is
+    padded to the next of a few sizes with rows that belong to no request (they write to
+    the cache's scratch page and scratch slot, and their logits are dropped)."""
 
-    MAX_GRAPHS = 32
+    MAX_GRAPHS = 48
+    MIN_TABLE_WIDTH = 16      # pages; narrower block tables are padded to this
+
+    @staticmethod
+    def padded_size(n: int) -> int:
+        """Rows of the captured step that serves ``n`` decoded tokens.  A batch that shrinks by one request at a
+        time would otherwise capture a graph per size; the rows added cost next to nothing (a step of few tokens
+        is bound by reading the weights)."""
+        if n <= 4:
+            return n
+        q = 4 if n <= 16 else 8 if n <= 64 else 16
+        return -(-n // q) * q
 
     def __init__(self, model: Model, cache: CacheManager, max_positions: "int | None" = None,
                  cuda_graphs: bool = False):
@@ -115,15 +130,20 @@ class Stepper:
         self._graphs: dict[tuple, _DecodeGraph] = {}
         self._graph_pool = None
         self.graph_replays = 0
+        self.graph_captures = 0
+        self.capture_seconds = 0.0      # host time spent on first steps of a shape (eager run + capture)
         self.launches_per_graph: dict[tuple, int] = {}
 
     def build_context(self, entries: Sequence[StepEntry], reserve: bool = True, table_width: "int | None" = None,
-                      upload: bool = True):
+                      upload: bool = True, pad_to: int = 0):
         """Check the entries, make room in the cache (unless the caller has) and lay the
         batch out flat.  Raises OutOfPages if a pool is too small; nothing is taken then.
         ``table_width`` pads the block tables to a fixed width (the layout of a captured
         step must not change); ``upload=False`` returns (context factory, flat host array)
-        for a caller that owns the device buffer."""
+        for a caller that owns the device buffer.  ``pad_to`` (steps of single tokens only)
+        appends rows that belong to no request until the step has that many: token 0 at
+        position 0 of a sequence whose only page is the scratch page, wanting its logits
+        (the rows after the entries' own)."""
         cache = self.cache
         if not entries:
             raise ValueError("a step needs at least one entry")
@@ -181,6 +201,20 @@ class Stepper:
         feed_dst = np.asarray([int(cu[b + 1]) - 1 if e.feed is not None else -1 for b, e in enumerate(entries)], dtype=np.int32)
         feed_src = np.asarray([e.feed if e.feed is not None else 0 for e in entries], dtype=np.int32)
 
+        P = max(0, pad_to - B)
+        if P:
+            if T != B or len(rows) != B:
+                raise ValueError("only a step of single tokens that all want their logits can be padded")
+            zeros = np.zeros(P, dtype=np.int32)
+            token_ids = np.concatenate([token_ids, zeros])
+            positions = np.concatenate([positions, zeros])
+            seq_of_token = np.arange(B + P, dtype=np.int32)
+            cu = np.arange(B + P + 1, dtype=np.int32)
+            logit_rows = np.arange(B + P, dtype=np.int32)
+            feed_dst = np.concatenate([feed_dst, zeros - 1])
+            feed_src = np.concatenate([feed_src, zeros])
+            starts = starts + [0] * P
+
         pieces = [token_ids, positions, seq_of_token, cu, logit_rows, feed_dst, feed_src]
         tables = []
         ps = cache.page_size
@@ -196,9 +230,12 @@ class Stepper:
             else:
                 slots = np.concatenate([cache.slots_for(g, e.request, s_, n) for e, s_, n in zip(entries, starts, counts)])
             table = cache.block_table_rows(g, reqs, table_width)
+            if P:
+                slots = np.concatenate([slots, np.full(P, group.scratch_page * ps, dtype=np.int32)])
+                table = np.concatenate([table, np.full((P, table.shape[1]), group.scratch_page, dtype=np.int32)])
             tables.append(table.shape)
             pieces += [slots, table.reshape(-1)]
-        state_slots = np.asarray([cache.state.slot_of[r] for r in reqs], dtype=np.int32)
+        state_slots = np.asarray([cache.state.slot_of[r] for r in reqs] + [cache.state.scratch_slot] * P, dtype=np.int32)
         pieces.append(state_slots)
 
         # every piece starts on a 16-byte boundary of the flat buffer
@@ -209,11 +246,11 @@ class Stepper:
         flat = np.zeros(max(total, 4), dtype=np.int32)
         for o, p in zip(offsets, pieces):
             flat[o:o + p.shape[0]] = p
-        new_lens = [s + n for s, n in zip(starts, counts)]
+        new_lens = [s + n for s, n in zip(starts, counts)]      # of the entries; the padding rows commit nothing
 
         def make(dev: torch.Tensor) -> StepContext:
             return self._make_context(dev, offsets, pieces, tables, entries, new_lens, cu, starts, state_slots,
-                                      T, B, len(rows))
+                                      T + P, B + P, len(rows) + P)
 
         if not upload:
             return make, flat
@@ -274,16 +311,18 @@ class Stepper:
         need = 1
         for e in entries:
             need = max(need, -(-(cache.length(e.request) + 1) // cache.page_size))
-        width = 1 << (need - 1).bit_length()            # power-of-two buckets keep the layout stable
-        make, flat = self.build_context(entries, reserve, table_width=width, upload=False)
+        width = max(self.MIN_TABLE_WIDTH, 1 << (need - 1).bit_length())      # power-of-two buckets keep the layout stable
+        n, rows = len(entries), self.padded_size(len(entries))
+        make, flat = self.build_context(entries, reserve, table_width=width, upload=False, pad_to=rows)
         new_lens = [cache.length(e.request) + 1 for e in entries]
-        key = (len(entries), width, self._splits_key(len(entries), max(new_lens)), flat.shape[0])
+        key = (rows, width, self._splits_key(rows, max(new_lens)), flat.shape[0])
         g = self._graphs.get(key)
         if g is None:
             if len(self._graphs) >= self.MAX_GRAPHS:
                 self._graphs.pop(next(iter(self._graphs)))
             # first step of this shape: run it eagerly (its result is this step's result), then
             # capture the same launch sequence on a static buffer for the steps to come
+            t_capture = time.perf_counter()
             flat_dev = torch.empty(flat.shape[0], dtype=torch.int32, device=self.device)
             self._copy_flat(flat_dev, flat)
             ctx = make(flat_dev)
@@ -299,7 +338,9 @@ class Stepper:
                 logits = self.model.forward(ctx)
             self.launches_per_graph[key] = lib.launch_count - before
             self._graphs[key] = _DecodeGraph(flat_dev, ctx, graph, logits)
-            result = eager_logits
+            result = eager_logits[:n]
+            self.graph_captures += 1
+            self.capture_seconds += time.perf_counter() - t_capture
         else:
             self._copy_flat(g.flat_dev, flat)
             self._feed(g.ctx, entries, fed_from)     # outside the graph: writes the static token array before the replay
@@ -307,7 +348,7 @@ class Stepper:
             g.replays += 1
             self.graph_replays += 1
             lib.launch_count += self.launches_per_graph[key]
-            result = g.logits
+            result = g.logits[:n]
         for e, new_len in zip(entries, new_lens):
             cache.commit(e.request, new_len)
         self.steps_run += 1

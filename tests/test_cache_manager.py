@@ -129,7 +129,7 @@ def test_state_slots_are_zeroed_and_bounded():
     m.end("a")
     m.begin("c")
     assert m.state.slot_of["c"] == sa and float(m.state.buffers[0][:, sa].abs().max()) == 0.0
-    assert m.state.buffers[0].shape == (2, 2, 3, 5)
+    assert m.state.buffers[0].shape == (2, 2 + 1, 3, 5)      # the requests' slots and the scratch slot
 
 
 @settings(max_examples=150, deadline=None)

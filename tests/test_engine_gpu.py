@@ -263,3 +263,43 @@ def test_cache_sized_by_a_fraction_of_free_memory(model_dirs):
     assert len(out.token_ids) == 5
     with pytest.raises(ValueError):
         Engine(d, cache_memory_fraction=1.5)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_padded_captured_steps_give_the_same_logits(model_dirs, dtype):
+    """A captured decode step of 5 to 13 tokens is padded to the next of a few sizes with rows that belong to no
+    request.  The entries' logits are those of the same step launched kernel by kernel without padding (bit for
+    bit in 32-bit, where a row's arithmetic does not depend on the batch), the pages of the requests stay intact,
+    and few graphs serve all the sizes."""
+    from pyre_b200.engine import replay as rp
+    from pyre_b200.engine.step import StepEntry, Stepper
+    d, raw = model_dirs["B"], H.TINY["B"]
+    n_req = 13
+    prompts = [H.random_ids(raw["vocab_size"], 3 + 5 * i, seed=50 + i) for i in range(n_req)]
+    runs = []
+    for graphs in (True, False):
+        model, cache, _ = rp.build_runtime(d, dtype, 2048, 8, max_requests=n_req, poison=True)
+        stepper = Stepper(model, cache, max_positions=None, cuda_graphs=graphs)
+        for i, p in enumerate(prompts):
+            cache.begin(i)
+            stepper.step([StepEntry(i, p, [])])
+        live, out = list(range(n_req)), []
+        for k in range(3 * n_req):
+            entries = [StepEntry(i, [(7 * i + k) % raw["vocab_size"]], [0]) for i in live]
+            out.append(stepper.step(entries).float().cpu().numpy().copy())
+            if k % 3 == 2:                                   # a request ends every third step: 13, 12, ... 1 rows
+                cache.end(live.pop(k % len(live)))
+        cache.check()
+        assert all(f == t for f, t in zip(cache.stats().pages_free, cache.stats().pages_total))
+        runs.append(out)
+        if graphs:
+            assert stepper.graph_replays > 0
+            sizes = {Stepper.padded_size(n) for n in range(1, n_req + 1)}
+            assert sizes == {1, 2, 3, 4, 8, 12, 16}
+            assert stepper.graph_captures <= 2 * len(sizes)   # the width of the tables changes once on the way
+    for a, b in zip(*runs):
+        assert a.shape == b.shape
+        if dtype == "float32":
+            assert np.array_equal(a, b)
+        else:
+            assert np.abs(a - b).max() <= 2e-2 * max(1.0, np.abs(b).max())
