@@ -512,20 +512,37 @@ def tc_gemm_plan(M: int, N: int, K: int) -> tuple[bool, int, int]:
         tiles = -(-N // 128) * -(-M // bn)
         splits = max(1, min(_SM_COUNT // tiles if tiles < _SM_COUNT else 1, kb // 4, 16))
         return True, bn, splits
-    # the tile width that needs the least time on the persistent CTAs: rounds of tiles x width of a tile
-    # (3584 features of 2048 tokens: 224 tiles of 256 features take two rounds; so do 288 tiles of 208)
+    # The tile width and the split of K with the least estimated time on the persistent CTAs (microseconds).
+    # Measured on products of 256-2,048 tokens: the main loop is bound by loads, not by the MMAs.  One SM pulls
+    # what its ring holds in flight (all stages but the one being multiplied) per memory latency, 1.1 us when
+    # many row tiles share each weight tile in L2 and 1.6 us when few do; all SMs together pull about 18 TB/s
+    # from L2 into shared memory.  Wide tiles move the fewest bytes, narrow ones fill the CTAs' rounds better,
+    # and a split K fills the SMs when there are few tiles (512 tokens x 3,584 features over K = 18,944:
+    # 224 wide with K in two takes 63 us, 112 tiles of 128 take 88 us).
     rows = -(-M // 128)
-    best = None
-    for cand in (256, 224, 208, 192, 160, 128):
+    latency = 1.7 - 0.035 * min(rows, 16)
+    best = [None, None]      # without and with a split K
+    for cand, stages in ((256, 4), (224, 5), (208, 5), (192, 5), (160, 5), (128, 6)):
         if cand > 128 and N < cand:
             continue
-        t = rows * -(-N // cand)
-        cost = -(-t // _SM_COUNT) * cand
-        if best is None or cost < best[0]:
-            best = (cost, cand, t)
-    _, bn, tiles = best
-    splits = max(1, min(_SM_COUNT // tiles if tiles * 2 <= _SM_COUNT else 1, kb // 8, 8))
-    return False, bn, splits
+        cols = -(-N // cand)
+        nbytes = (128 + cand) * 128                               # one K block of both operands
+        per_block = max(cand * 2 / 1900.0, latency / (stages - 1))
+        for sp in (1, 2, 3, 4):
+            if sp > 1 and kb // sp < 8:
+                break
+            items = rows * cols * sp
+            per_cta = -(-items // _SM_COUNT)
+            blocks = -(-kb // sp)
+            cost = max(per_cta * blocks * per_block, items * blocks * nbytes / 18e6) \
+                + per_cta * (1.5 + cand / 64.0 * (2 if sp > 1 else 1))
+            # near-ties go to the wider tile; a split K (fp32 partials, estimated less surely) has to gain a tenth
+            if best[sp > 1] is None or cost < best[sp > 1][0] * 0.98:
+                best[sp > 1] = (cost, cand, sp)
+    whole, split = best
+    if split is not None and split[0] < 0.9 * whole[0]:
+        return False, split[1], split[2]
+    return False, whole[1], whole[2]
 
 
 GATED_BLOCK = 64     # gate and up rows of a fused feed-forward weight alternate in blocks of this many features
