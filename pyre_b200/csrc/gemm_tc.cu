@@ -81,6 +81,23 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1) : "memory");
 }
+// The same for a CTA of a pair: the destination is this CTA's shared memory, the mbarrier may be the peer's
+// (a shared::cluster address).  No multicast: each CTA fetches its own boxes.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+// shared::cluster address of the same shared-memory offset in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 
 // Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128B swizzle:
 // start address >> 4, leading byte offset 1 (unused with swizzle), stride byte offset
@@ -99,6 +116,21 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// A pair of CTAs on one tile (cta_group::2): M = 256, each CTA holds 128 rows of A, half the rows of B and, in its
+// tensor memory, its 128 rows of D.  Issued by one thread of the pair's first CTA; the descriptors name the same
+// shared-memory offsets in both.  The commit arrives on the barrier of that offset in both CTAs.
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(both) : "memory");
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
@@ -121,10 +153,10 @@ struct GemmParams {
     int* err_flag;
 };
 
-template <int BN, int STAGES, bool XC>
+template <int BN, int STAGES, bool XC, int CTAS = 1>
 struct SmemLayout {
     static constexpr int X_BYTES = BM * BK * 2;
-    static constexpr int Y_BYTES = BN * BK * 2;
+    static constexpr int Y_BYTES = (BN / CTAS) * BK * 2;      // a CTA of a pair holds half of the tile's Y rows
     static constexpr int STAGE_BYTES = X_BYTES + Y_BYTES;
     static constexpr int TILES = STAGES * STAGE_BYTES;
     static constexpr int N_BARS = 2 * STAGES + 4;     // full, empty per stage; accumulator full, empty per TMEM buffer
@@ -142,10 +174,21 @@ struct SmemLayout {
 // A CTA is persistent: it walks output tiles c, c + gridDim.x, ...  Two TMEM accumulators
 // alternate, so the epilogue warps drain tile i while the MMA thread already works on tile
 // i + 1; the shared-memory ring runs on across tiles.
-template <int BN, int STAGES, bool X_CONTIGUOUS_OUT>
+//
+// CTAS == 2 (row store only): two CTAs of a cluster, on the two SMs of a TPC, share a 256 x BN tile.  Each loads its
+// own 128 rows of X and half of the tile's Y rows, so a K block costs an SM 128 (128 + BN / 2) bytes of loads
+// instead of 128 (128 + BN) for the same MMA work; the first CTA's thread issues the MMAs for both, every CTA
+// drains its own 128 accumulator rows.  Barriers: the first CTA's "full" barriers count the bytes of both CTAs'
+// loads; the MMA commits arrive on the "empty" and "accumulator full" barriers of both; the epilogue warps of
+// both arrive on the first CTA's "accumulator empty" barriers.
+template <int BN, int STAGES, bool X_CONTIGUOUS_OUT, int CTAS = 1>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const GemmParams p) {
-    using L = SmemLayout<BN, STAGES, X_CONTIGUOUS_OUT>;
+    static_assert(CTAS == 1 || (CTAS == 2 && !X_CONTIGUOUS_OUT && BN % 32 == 0), "pairs serve the row store");
+    using L = SmemLayout<BN, STAGES, X_CONTIGUOUS_OUT, CTAS>;
+    uint32_t rank = 0;                       // of this CTA in its pair
+    if constexpr (CTAS == 2) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int worker = blockIdx.x / CTAS, n_workers = gridDim.x / CTAS;   // a worker (CTA or pair) walks tiles worker, worker + n_workers, ...
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzled tiles want 1024-byte alignment
     uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
@@ -174,16 +217,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_acc_full + 8 * b, 1);
-            mbar_init(bar_acc_empty + 8 * b, 4);      // one arrival per epilogue warp
+            mbar_init(bar_acc_empty + 8 * b, 4 * CTAS);      // one arrival per epilogue warp (of both CTAs of a pair)
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (CTAS == 2) {      // the same warp of both CTAs allocates the same columns in both
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
+    if constexpr (CTAS == 2) cluster_sync_all();     // the peer's barriers exist before anything arrives on them
+    else __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
@@ -194,27 +243,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_y)) : "memory");
             int it = 0;   // K blocks issued so far, over all tiles of this CTA
             bool waited = false;
-            for (int tile = blockIdx.x; tile < n_tiles && !*abort_flag; tile += gridDim.x) {
-                const int x0 = (tile % p.tiles_x) * BM, y0 = (tile / p.tiles_x) * BN;
+            // loads of a pair's second CTA complete on the first CTA's barriers, which expect the bytes of both
+            const uint32_t full_to = CTAS == 2 ? mapa_u32(bar_full, 0) : bar_full;
+            auto load = [&](uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+                if constexpr (CTAS == 2) tma_load_2d_pair(dst, map, bar, c0, c1);
+                else tma_load_2d(dst, map, bar, c0, c1);
+            };
+            for (int tile = worker; tile < n_tiles && !*abort_flag; tile += n_workers) {
+                const int x0 = (tile % p.tiles_x) * (BM * CTAS) + rank * BM;
+                const int y0 = (tile / p.tiles_x) * BN + rank * (BN / CTAS);
                 int i = 0;
                 if (!waited) {
                     // The weights do not depend on the kernels before this one: fill the ring with
                     // their tiles first, then wait for those kernels, then fetch the activations.
                     const int pre = n_kb < STAGES ? n_kb : STAGES;
                     for (int j = 0; j < pre; ++j) {
-                        mbar_expect_tx(bar_full + 8 * j, L::STAGE_BYTES);
+                        if (rank == 0) mbar_expect_tx(bar_full + 8 * j, CTAS * L::STAGE_BYTES);
                         const uint32_t xs = base + j * L::STAGE_BYTES, ys = xs + L::X_BYTES;
                         const int k = (kb_begin + j) * BK;
-                        if (p.x_is_constant) tma_load_2d(xs, &map_x, bar_full + 8 * j, k, x0);
-                        else tma_load_2d(ys, &map_y, bar_full + 8 * j, k, y0);
+                        if (p.x_is_constant) load(xs, &map_x, full_to + 8 * j, k, x0);
+                        else load(ys, &map_y, full_to + 8 * j, k, y0);
                     }
                     pdl_wait();
                     waited = true;
                     for (int j = 0; j < pre; ++j) {
                         const uint32_t xs = base + j * L::STAGE_BYTES, ys = xs + L::X_BYTES;
                         const int k = (kb_begin + j) * BK;
-                        if (p.x_is_constant) tma_load_2d(ys, &map_y, bar_full + 8 * j, k, y0);
-                        else tma_load_2d(xs, &map_x, bar_full + 8 * j, k, x0);
+                        if (p.x_is_constant) load(ys, &map_y, full_to + 8 * j, k, y0);
+                        else load(xs, &map_x, full_to + 8 * j, k, x0);
                     }
                     i = pre;
                     it = pre;
@@ -225,25 +281,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     const uint32_t phase = (it / STAGES) & 1;
                     ok = mbar_wait(bar_empty + 8 * s, phase ^ 1, abort_flag, p.err_flag);
                     if (!ok) break;
-                    mbar_expect_tx(bar_full + 8 * s, L::STAGE_BYTES);
+                    if (rank == 0) mbar_expect_tx(bar_full + 8 * s, CTAS * L::STAGE_BYTES);
                     const uint32_t xs = base + s * L::STAGE_BYTES, ys = xs + L::X_BYTES;
                     const int k = (kb_begin + i) * BK;
-                    tma_load_2d(xs, &map_x, bar_full + 8 * s, k, x0);
-                    tma_load_2d(ys, &map_y, bar_full + 8 * s, k, y0);
+                    load(xs, &map_x, full_to + 8 * s, k, x0);
+                    load(ys, &map_y, full_to + 8 * s, k, y0);
                 }
                 if (!ok) break;
             }
             if (!waited) pdl_wait();
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            // ---------------- MMA issuer
+        if (lane == 0 && rank == 0) {
+            // ---------------- MMA issuer (of a pair: the first CTA's, for both)
             // instruction descriptor: D fp32 (bit 4), A and B bf16 (bits 7, 10), both K-major,
             // N >> 3 at bit 17, M >> 4 at bit 24
-            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((BM * CTAS) >> 4) << 24);
+            auto mma = [&](uint32_t d, uint64_t a, uint64_t b, uint32_t accumulate) {
+                if constexpr (CTAS == 2) umma_bf16_pair(d, a, b, idesc, accumulate);
+                else umma_bf16(d, a, b, idesc, accumulate);
+            };
+            auto commit = [&](uint32_t bar) {
+                if constexpr (CTAS == 2) umma_commit_pair(bar);
+                else umma_commit(bar);
+            };
             int it = 0, j = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++j) {
+            for (int tile = worker; tile < n_tiles && ok; tile += n_workers, ++j) {
                 const int buf = j & 1;
                 // the epilogue must have drained this accumulator (two tiles ago)
                 ok = mbar_wait(bar_acc_empty + 8 * buf, ((j >> 1) & 1) ^ 1, abort_flag, p.err_flag);
@@ -260,10 +324,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     const uint64_t da = umma_desc(xs), db = umma_desc(ys);
 #pragma unroll
                     for (int k = 0; k < BK / 16; ++k)   // 16 bf16 = 32 bytes = 2 descriptor units along K
-                        umma_bf16(acc, da + 2 * k, db + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(bar_empty + 8 * s);     // the stage is free once these MMAs have read it
+                        mma(acc, da + 2 * k, db + 2 * k, (i > 0 || k > 0) ? 1u : 0u);
+                    commit(bar_empty + 8 * s);     // the stage is free once these MMAs have read it
                 }
-                umma_commit(bar_acc_full + 8 * buf);    // this tile's accumulator is complete (also signalled on abort)
+                commit(bar_acc_full + 8 * buf);    // this tile's accumulator is complete (also signalled on abort)
             }
         }
     } else {
@@ -272,13 +336,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         int j = 0;
         bool alive = true;
         if (n_kb == 0) pdl_wait();   // nothing orders the zero stores after the earlier kernels otherwise
-        for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++j) {
+        // the accumulator goes back to the MMA thread, which for a pair sits in the first CTA
+        const uint32_t acc_empty_to = CTAS == 2 ? mapa_u32(bar_acc_empty, 0) : bar_acc_empty;
+        auto hand_back = [&](int buf) {
+            if constexpr (CTAS == 2) asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(acc_empty_to + 8 * buf) : "memory");
+            else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty_to + 8 * buf) : "memory");
+        };
+        for (int tile = worker; tile < n_tiles && alive; tile += n_workers, ++j) {
             const int buf = j & 1;
-            const int x0 = (tile % p.tiles_x) * BM, y0 = (tile / p.tiles_x) * BN;
+            const int x0 = (tile % p.tiles_x) * (BM * CTAS) + rank * BM, y0 = (tile / p.tiles_x) * BN;
             const int xr = x0 + quarter * 32 + lane;
             bool ok = true;
             if (n_kb > 0) ok = mbar_wait(bar_acc_full + 8 * buf, (j >> 1) & 1, abort_flag, p.err_flag);
             ok = ok && !*abort_flag;   // the issuer signals the accumulator even when it gave up
+            if constexpr (CTAS == 2) ok = ok && (p.err_flag == nullptr || *(volatile int*)p.err_flag == 0);   // ... and it may sit in the peer CTA
             alive = __all_sync(0xffffffffu, ok);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const long long out_base = (long long)blockIdx.z * p.split_stride + (long long)xr * p.stride_x;
@@ -344,7 +415,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     }
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
-                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
+                    if (lane == 0) hand_back(buf);
                     continue;
                 }
             }
@@ -394,7 +465,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     }
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
-                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
+                    if (lane == 0) hand_back(buf);
                     continue;
                 }
             }
@@ -479,16 +550,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             // this warp has read its quarter of the accumulator: hand the buffer back to the MMA thread
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
+            if (lane == 0) hand_back(buf);
         }
     }
 
     // ---------------- teardown: all tensor-memory reads are done before the columns are freed
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
+    if constexpr (CTAS == 2) cluster_sync_all();     // neither CTA leaves while the other may still touch its memory or barriers
+    else __syncthreads();
     if (warp == 1) {
         __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        if constexpr (CTAS == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -523,16 +596,37 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, long long ld, i
     return r == CUDA_SUCCESS ? 0 : PYRE_ERR_BAD_ARG;
 }
 
-template <int BN, int STAGES, bool XC>
+template <int BN, int STAGES, bool XC, int CTAS = 1>
 int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, dim3 grid, cudaStream_t stream) {
-    using L = SmemLayout<BN, STAGES, XC>;
+    using L = SmemLayout<BN, STAGES, XC, CTAS>;
+    static_assert(L::TOTAL <= 232448, "the ring does not fit into shared memory");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, XC>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, XC, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    cudaError_t e = pyre_launch(gemm_tc_kernel<BN, STAGES, XC>, grid, dim3(THREADS), (size_t)L::TOTAL, stream, mx, my, p);
+    cudaError_t e;
+    if constexpr (CTAS == 2) {
+        // pairs of CTAs: a cluster of two along x (the two SMs of a TPC), with the dependent-launch attribute as everywhere
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = (size_t)L::TOTAL;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pyre_pdl_enabled() ? 2 : 1;
+        e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, XC, CTAS>, mx, my, p);
+    } else {
+        e = pyre_launch(gemm_tc_kernel<BN, STAGES, XC, CTAS>, grid, dim3(THREADS), (size_t)L::TOTAL, stream, mx, my, p);
+    }
     if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();
 }
@@ -548,10 +642,11 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, di
 // kernels before it in the stream (programmatic dependent launch).  gated: the weight operand holds gate
 // and up rows interleaved in blocks of 64 (64 gate rows, the up rows of the same features, ...); the output is
 // silu(gate product) * (up product), half as many features: row store (weights = Y, bn 256, out[x, j]) or
-// transposed store (weights = X, bn <= 128, out[y * stride_y + j]); one split, bf16 out.
+// transposed store (weights = X, bn <= 128, out[y * stride_y + j]); one split, bf16 out.  pair: two CTAs of a
+// cluster share each 256 x bn tile (row store, bn 128-256 in steps of 32).
 PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* Y, int y_rows, long long ldy, int K,
                           void* out, int out_f32, long long stride_x, long long stride_y, long long split_stride,
-                          int splits, int bn, int x_is_constant, int gated, int* err_flag, cudaStream_t stream) {
+                          int splits, int bn, int x_is_constant, int gated, int pair, int* err_flag, cudaStream_t stream) {
     if (x_rows <= 0 || y_rows <= 0) return 0;
     // the gated epilogue: whole tiles of gate/up rows interleaved in blocks of 64, one split, bf16 out; with the
     // tokens on the row side 256-wide tiles, with the weights on the row side at most 128 tokens per tile
@@ -563,10 +658,11 @@ PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* 
     if (stride_x != 1 && stride_y != 1) return PYRE_ERR_BAD_ARG;
     const bool xc = (stride_x == 1);
     if (!xc && ((stride_x % 8) || ((uintptr_t)out & 15))) return PYRE_ERR_UNSUPPORTED;  // vector stores of a row
+    if (pair && (xc || bn < 128 || bn % 32)) return PYRE_ERR_BAD_ARG;     // pairs of CTAs serve the row store, widths 128-256 in steps of 32
     CUtensorMap mx, my;
     int rc = make_map(&mx, X, x_rows, K, ldx, BM);
     if (rc) return rc;
-    rc = make_map(&my, Y, y_rows, K, ldy, bn);
+    rc = make_map(&my, Y, y_rows, K, ldy, pair ? bn / 2 : bn);      // a CTA of a pair fetches half of the tile's Y rows
     if (rc) return rc;
     const int total_kb = (K + BK - 1) / BK;
     if (splits > total_kb) splits = total_kb;
@@ -575,7 +671,7 @@ PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* 
     p.k_blocks_per_split = (total_kb + splits - 1) / splits;
     p.stride_x = stride_x; p.stride_y = stride_y; p.split_stride = split_stride;
     p.out = out; p.out_f32 = out_f32; p.x_is_constant = x_is_constant; p.err_flag = err_flag; p.gated = gated ? 1 : 0;
-    p.tiles_x = ceil_div(x_rows, BM); p.tiles_y = ceil_div(y_rows, bn);
+    p.tiles_x = ceil_div(x_rows, pair ? 2 * BM : BM); p.tiles_y = ceil_div(y_rows, bn);
     const long long n_tiles = (long long)p.tiles_x * p.tiles_y;
     // one CTA per SM stays resident and walks the tiles (a split K keeps one CTA per tile and split)
     static int sm_count = 0;
@@ -591,6 +687,19 @@ PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* 
             if (waste * sm_count < best_waste * g) { best = g; best_waste = waste; }
         }
         ctas = best;
+    }
+    if (pair) {
+        // one pair per TPC stays resident (a split K keeps one pair per tile and split)
+        const long long pairs = splits > 1 ? n_tiles : (n_tiles < sm_count / 2 ? n_tiles : sm_count / 2);
+        dim3 grid2((unsigned)(2 * pairs), 1, splits);
+        switch (bn) {
+            case 128: return launch<128, 8, false, 2>(mx, my, p, grid2, stream);
+            case 160: return launch<160, 7, false, 2>(mx, my, p, grid2, stream);
+            case 192: return launch<192, 7, false, 2>(mx, my, p, grid2, stream);
+            case 224: return launch<224, 6, false, 2>(mx, my, p, grid2, stream);
+            case 256: return launch<256, 6, false, 2>(mx, my, p, grid2, stream);
+            default: return PYRE_ERR_BAD_ARG;
+        }
     }
     dim3 grid((unsigned)ctas, 1, splits);
 #define GO(BN_, ST_)                                                              \

@@ -24,7 +24,7 @@ SIGNATURES: dict[str, tuple[str, list]] = {
     "pyre_silu_mul": ("elementwise", [P, P, I, I, I, I, P]),
     "pyre_sum_partials": ("elementwise", [P, I, LL, P, LL, I, P]),
     "pyre_feed_tokens": ("elementwise", [P, P, P, P, I, P]),
-    "pyre_gemm_tc": ("gemm_tc", [P, I, LL, P, I, LL, I, P, I, LL, LL, LL, I, I, I, I, P, P]),
+    "pyre_gemm_tc": ("gemm_tc", [P, I, LL, P, I, LL, I, P, I, LL, LL, LL, I, I, I, I, I, P, P]),
     "pyre_sample": ("sampling", [P, LL, P, P, P, P, I, I, P, P]),
     "pyre_sample_slices": ("sampling", [I]),
     "pyre_paged_attention_generic": ("attention_generic", [P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, P]),

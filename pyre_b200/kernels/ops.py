@@ -498,6 +498,9 @@ def tc_gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
             and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+CTA_PAIRS = True     # prompt portions: two CTAs of a cluster share each 256-row tile (tcgen05 cta_group::2)
+
+
 def tc_gemm_plan(M: int, N: int, K: int) -> tuple[bool, int, int]:
     """(weights_as_rows, bn, splits) for y[M, N] = a[M, K] w[N, K]^T.
 
@@ -519,23 +522,29 @@ def tc_gemm_plan(M: int, N: int, K: int) -> tuple[bool, int, int]:
     # from L2 into shared memory.  Wide tiles move the fewest bytes, narrow ones fill the CTAs' rounds better,
     # and a split K fills the SMs when there are few tiles (512 tokens x 3,584 features over K = 18,944:
     # 224 wide with K in two takes 63 us, 112 tiles of 128 take 88 us).
-    rows = -(-M // 128)
-    latency = 1.7 - 0.035 * min(rows, 16)
+    # With CTA pairs (two CTAs of a cluster on a 256-row tile, each loading half of the tile's weight rows) an SM
+    # loads 128 (128 + bn / 2) bytes per K block, its ring is deeper, and the workers are the 74 pairs.
+    pair = CTA_PAIRS
+    workers = _SM_COUNT // 2 if pair else _SM_COUNT
+    rows = -(-M // (256 if pair else 128))
+    latency = 1.7 - 0.035 * min(-(-M // 128), 16)
+    widths = ((256, 6), (224, 6), (192, 7), (160, 7), (128, 8)) if pair else \
+        ((256, 4), (224, 5), (208, 5), (192, 5), (160, 5), (128, 6))
     best = [None, None]      # without and with a split K
-    for cand, stages in ((256, 4), (224, 5), (208, 5), (192, 5), (160, 5), (128, 6)):
+    for cand, stages in widths:
         if cand > 128 and N < cand:
             continue
         cols = -(-N // cand)
-        nbytes = (128 + cand) * 128                               # one K block of both operands
+        nbytes = ((256 + cand) if pair else (128 + cand)) * 128       # one K block of both operands, per worker
         per_block = max(cand * 2 / 1900.0, latency / (stages - 1))
         for sp in (1, 2, 3, 4):
             if sp > 1 and kb // sp < 8:
                 break
             items = rows * cols * sp
-            per_cta = -(-items // _SM_COUNT)
+            per_worker = -(-items // workers)
             blocks = -(-kb // sp)
-            cost = max(per_cta * blocks * per_block, items * blocks * nbytes / 18e6) \
-                + per_cta * (1.5 + cand / 64.0 * (2 if sp > 1 else 1))
+            cost = max(per_worker * blocks * per_block, items * blocks * nbytes / 18e6) \
+                + per_worker * (1.5 + cand / 64.0 * (2 if sp > 1 else 1))
             # near-ties go to the wider tile; a split K (fp32 partials, estimated less surely) has to gain a tenth
             if best[sp > 1] is None or cost < best[sp > 1][0] * 0.98:
                 best[sp > 1] = (cost, cand, sp)
@@ -549,7 +558,8 @@ GATED_BLOCK = 64     # gate and up rows of a fused feed-forward weight alternate
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
-            plan: "tuple[bool, int, int] | None" = None, reduce: bool = True, gated: bool = False) -> torch.Tensor:
+            plan: "tuple[bool, int, int] | None" = None, reduce: bool = True, gated: bool = False,
+            pair: "bool | None" = None) -> torch.Tensor:
     """y = x w^T on the tensor cores (tcgen05, TMEM accumulators, TMA-fed), bf16 in, fp32 accumulate.
 
     With a split K the kernel leaves fp32 partial sums [splits, M, N]; ``reduce`` adds
@@ -567,6 +577,9 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
         raise ValueError(f"inner sizes differ: x is [{M}, {K}], w is [{N}, {K2}]")
     weights_as_rows, bn, splits = plan or tc_gemm_plan(M, N, K)
     splits = max(1, min(splits, -(-K // 64)))
+    if pair is None:
+        pair = CTA_PAIRS
+    pair = int(bool(pair) and not weights_as_rows and M > 128 and bn >= 128 and bn % 32 == 0)
     err = device_error_flag(x.device)
     if gated:
         if N % (2 * GATED_BLOCK) or out_dtype != torch.bfloat16:
@@ -576,14 +589,14 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
         if not weights_as_rows and bn == 256 and splits == 1 and N % 256 == 0:
             out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
             lib.call("pyre_gemm_tc", x.data_ptr(), M, x.stride(0), w.data_ptr(), N, w.stride(0), K, out.data_ptr(), 0,
-                     N // 2, 1, 0, 1, bn, 0, 1, err.data_ptr(), _stream())
+                     N // 2, 1, 0, 1, bn, 0, 1, pair, err.data_ptr(), _stream())
             return out
         if weights_as_rows and bn <= 128 and splits == 1 and N % 128 == 0:
             out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
             lib.call("pyre_gemm_tc", w.data_ptr(), N, w.stride(0), x.data_ptr(), M, x.stride(0), K, out.data_ptr(), 0,
-                     1, N // 2, 0, 1, bn, 1, 1, err.data_ptr(), _stream())
+                     1, N // 2, 0, 1, bn, 1, 1, 0, err.data_ptr(), _stream())
             return out
-        return silu_mul(gemm_tc(x, w, torch.bfloat16, (weights_as_rows, bn, splits)), block=GATED_BLOCK)
+        return silu_mul(gemm_tc(x, w, torch.bfloat16, (weights_as_rows, bn, splits), pair=bool(pair)), block=GATED_BLOCK)
     if splits == 1 and reduce:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         target, split_stride = out, 0
@@ -593,10 +606,10 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     f32 = int(target.dtype == torch.float32)
     if weights_as_rows:
         lib.call("pyre_gemm_tc", w.data_ptr(), N, w.stride(0), x.data_ptr(), M, x.stride(0), K, target.data_ptr(), f32,
-                 1, N, split_stride, splits, bn, 1, 0, err.data_ptr(), _stream())
+                 1, N, split_stride, splits, bn, 1, 0, 0, err.data_ptr(), _stream())
     else:
         lib.call("pyre_gemm_tc", x.data_ptr(), M, x.stride(0), w.data_ptr(), N, w.stride(0), K, target.data_ptr(), f32,
-                 N, 1, split_stride, splits, bn, 0, 0, err.data_ptr(), _stream())
+                 N, 1, split_stride, splits, bn, 0, 0, pair, err.data_ptr(), _stream())
     if target.dim() == 2:
         return target
     if not reduce:

@@ -101,6 +101,8 @@ def test_gated_product(ops, M, I, K):
     separate = ops.silu_mul(ops.gemm_tc(x, stacked, torch.bfloat16, plan=(plan[0], plan[1], 1)))
     if plan[2] == 1:
         assert torch.equal(got, separate)
+    if M > 128 and (2 * I) % 256 == 0:      # one CTA per tile and a pair of CTAs per 256-row tile: the same bits
+        assert torch.equal(ops.gemm_tc(x, mixed, gated=True, pair=False), ops.gemm_tc(x, mixed, gated=True, pair=True))
     gate = (x.float() @ wg.float().t()).to(torch.bfloat16).float()
     up = (x.float() @ wu.float().t()).to(torch.bfloat16).float()
     want = torch.nn.functional.silu(gate) * up
@@ -160,8 +162,12 @@ def test_gemm_tc_matches_fp32_product(ops, M, N, K):
             continue
         if plan[0] and M > 4 * plan[1]:
             continue
-        other = ops.gemm_tc(a, w, torch.float32, plan=plan)
+        other = ops.gemm_tc(a, w, torch.float32, plan=plan, pair=False)
         assert float((other - want).abs().max()) <= 2e-5 * scale * max(1.0, (K / 64) ** 0.5), f"plan {plan}"
+        # two CTAs of a cluster on each 256-row tile (widths in steps of 32): the same sums in the same order
+        if not plan[0] and plan[1] % 32 == 0 and M > 128:
+            paired = ops.gemm_tc(a, w, torch.float32, plan=plan, pair=True)
+            assert torch.equal(paired, other), f"plan {plan} with CTA pairs"
     ops.check_device_errors()
     # strided activations (a slice of a wider buffer)
     if K % 16 == 0:
