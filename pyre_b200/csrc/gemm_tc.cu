@@ -184,7 +184,7 @@ struct SmemLayout {
 template <int BN, int STAGES, bool X_CONTIGUOUS_OUT, int CTAS = 1>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const GemmParams p) {
-    static_assert(CTAS == 1 || (CTAS == 2 && !X_CONTIGUOUS_OUT && BN % 32 == 0), "pairs serve the row store");
+    static_assert(CTAS == 1 || (CTAS == 2 && !X_CONTIGUOUS_OUT && BN % 16 == 0), "pairs serve the row store");
     using L = SmemLayout<BN, STAGES, X_CONTIGUOUS_OUT, CTAS>;
     uint32_t rank = 0;                       // of this CTA in its pair
     if constexpr (CTAS == 2) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
@@ -643,7 +643,7 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, di
 // and up rows interleaved in blocks of 64 (64 gate rows, the up rows of the same features, ...); the output is
 // silu(gate product) * (up product), half as many features: row store (weights = Y, bn 256, out[x, j]) or
 // transposed store (weights = X, bn <= 128, out[y * stride_y + j]); one split, bf16 out.  pair: two CTAs of a
-// cluster share each 256 x bn tile (row store, bn 128-256 in steps of 32).
+// cluster share each 256 x bn tile (row store, bn 128, 160, 192, 208, 224 or 256).
 PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* Y, int y_rows, long long ldy, int K,
                           void* out, int out_f32, long long stride_x, long long stride_y, long long split_stride,
                           int splits, int bn, int x_is_constant, int gated, int pair, int* err_flag, cudaStream_t stream) {
@@ -658,7 +658,7 @@ PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* 
     if (stride_x != 1 && stride_y != 1) return PYRE_ERR_BAD_ARG;
     const bool xc = (stride_x == 1);
     if (!xc && ((stride_x % 8) || ((uintptr_t)out & 15))) return PYRE_ERR_UNSUPPORTED;  // vector stores of a row
-    if (pair && (xc || bn < 128 || bn % 32)) return PYRE_ERR_BAD_ARG;     // pairs of CTAs serve the row store, widths 128-256 in steps of 32
+    if (pair && (xc || bn < 128)) return PYRE_ERR_BAD_ARG;     // pairs of CTAs serve the row store, widths from 128
     CUtensorMap mx, my;
     int rc = make_map(&mx, X, x_rows, K, ldx, BM);
     if (rc) return rc;
@@ -696,6 +696,7 @@ PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* 
             case 128: return launch<128, 8, false, 2>(mx, my, p, grid2, stream);
             case 160: return launch<160, 7, false, 2>(mx, my, p, grid2, stream);
             case 192: return launch<192, 7, false, 2>(mx, my, p, grid2, stream);
+            case 208: return launch<208, 7, false, 2>(mx, my, p, grid2, stream);
             case 224: return launch<224, 6, false, 2>(mx, my, p, grid2, stream);
             case 256: return launch<256, 6, false, 2>(mx, my, p, grid2, stream);
             default: return PYRE_ERR_BAD_ARG;

@@ -528,7 +528,7 @@ def tc_gemm_plan(M: int, N: int, K: int) -> tuple[bool, int, int]:
     workers = _SM_COUNT // 2 if pair else _SM_COUNT
     rows = -(-M // (256 if pair else 128))
     latency = 1.7 - 0.035 * min(-(-M // 128), 16)
-    widths = ((256, 6), (224, 6), (192, 7), (160, 7), (128, 8)) if pair else \
+    widths = ((256, 6), (224, 6), (208, 7), (192, 7), (160, 7), (128, 8)) if pair else \
         ((256, 4), (224, 5), (208, 5), (192, 5), (160, 5), (128, 6))
     best = [None, None]      # without and with a split K
     for cand, stages in widths:
@@ -579,7 +579,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     splits = max(1, min(splits, -(-K // 64)))
     if pair is None:
         pair = CTA_PAIRS
-    pair = int(bool(pair) and not weights_as_rows and M > 128 and bn >= 128 and bn % 32 == 0)
+    pair = int(bool(pair) and not weights_as_rows and M > 128 and bn in (128, 160, 192, 208, 224, 256))
     err = device_error_flag(x.device)
     if gated:
         if N % (2 * GATED_BLOCK) or out_dtype != torch.bfloat16:

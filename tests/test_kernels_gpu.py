@@ -164,8 +164,8 @@ def test_gemm_tc_matches_fp32_product(ops, M, N, K):
             continue
         other = ops.gemm_tc(a, w, torch.float32, plan=plan, pair=False)
         assert float((other - want).abs().max()) <= 2e-5 * scale * max(1.0, (K / 64) ** 0.5), f"plan {plan}"
-        # two CTAs of a cluster on each 256-row tile (widths in steps of 32): the same sums in the same order
-        if not plan[0] and plan[1] % 32 == 0 and M > 128:
+        # two CTAs of a cluster on each 256-row tile: the same sums in the same order
+        if not plan[0] and M > 128:
             paired = ops.gemm_tc(a, w, torch.float32, plan=plan, pair=True)
             assert torch.equal(paired, other), f"plan {plan} with CTA pairs"
     ops.check_device_errors()
