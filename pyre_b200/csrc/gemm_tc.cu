@@ -8,7 +8,8 @@
 //                          K may be split over CTAs (blockIdx.z) into fp32 partial sums
 //                          that the consumer kernel adds up, so that shapes with few
 //                          128-row tiles still put a CTA on every SM;
-//   many tokens (prefill): X = a (128 tokens per tile), Y = W (up to 256 features per tile).
+//   many tokens (prefill): X = a (128 tokens per tile), Y = W (up to 256 features per tile); by default
+//                          as pairs of CTAs on 256-token tiles (tcgen05 cta_group::2, see the kernel).
 //
 // Structure of a CTA (192 threads), one 128 x BN output tile, K in blocks of 64:
 //   warp 0, one thread : TMA producer.  cp.async.bulk.tensor.2d loads an X box (128 x 64)
@@ -27,7 +28,7 @@
 // already multiplying tile i + 1 into the other one, and the TMA ring never stops.
 // Rows or K beyond the matrices are zero-filled by TMA, so any x_rows, y_rows and K work
 // (K and the leading dimensions must be multiples of 8 elements: TMA strides are 16-byte
-// multiples).  No load uses cluster multicast.
+// multiples).  No load uses cluster multicast (a CTA of a pair fetches its own boxes).
 //
 // Every wait on an mbarrier is bounded.  If one runs out, the kernel raises the error
 // flag, stops waiting everywhere, skips its stores, frees its tensor memory and returns;

@@ -1,0 +1,56 @@
+"""The host-side plans of the kernels (no GPU needed): every plan the matrix-product planner
+and the attention's split rule can return is one the kernels accept, and the choices that
+were measured stay as measured."""
+
+import pytest
+
+from pyre_b200.kernels import ops
+
+WIDTHS_ROW_STORE = {128, 160, 192, 208, 224, 256}
+WIDTHS_WEIGHT_ROWS = {16, 32, 64, 128, 256}
+
+
+@pytest.mark.parametrize("pairs", [True, False])
+def test_every_product_plan_is_one_the_kernel_takes(monkeypatch, pairs):
+    monkeypatch.setattr(ops, "CTA_PAIRS", pairs)
+    for M in [1, 2, 7, 8, 16, 17, 33, 64, 65, 127, 128, 129, 200, 256, 257, 511, 512, 777, 1024, 1040, 2048, 2056, 4096, 8192, 40000]:
+        for N in [8, 64, 130, 136, 512, 1000, 3584, 4608, 5120, 37888, 152064]:
+            for K in [8, 64, 72, 512, 520, 3584, 18944]:
+                weights_as_rows, bn, splits = ops.tc_gemm_plan(M, N, K)[:3]
+                kb = -(-K // 64)
+                assert 1 <= splits <= 16 and splits <= max(kb, 1), (M, N, K, bn, splits)
+                if weights_as_rows:
+                    assert bn in WIDTHS_WEIGHT_ROWS and (M <= 128 or N % 8), (M, N, K, bn)
+                    assert bn >= min(M, 256) or M > 256, (M, N, K, bn)      # the tokens of a tile fit its width
+                else:
+                    assert bn in WIDTHS_ROW_STORE and M > 128 and N % 8 == 0, (M, N, K, bn)
+                if splits > 1:
+                    assert kb // splits >= 4, (M, N, K, splits)             # a split keeps a few K blocks
+
+
+def test_measured_product_choices(monkeypatch):
+    """Shapes of the 7B model whose best plan was measured on a B200 (microseconds in the kernel's profile)."""
+    monkeypatch.setattr(ops, "CTA_PAIRS", True)
+    assert ops.tc_gemm_plan(2048, 4608, 3584)[:3] == (False, 256, 1)          # QKV of a 2,048-token portion
+    assert ops.tc_gemm_plan(2048, 3584, 18944)[:3] == (False, 224, 1)         # down: 128 pair tiles of 224
+    assert ops.tc_gemm_plan(2048, 37888, 3584)[:3] == (False, 256, 1)         # gate/up: whole 256-wide tiles for the fused activation
+    wide, bn, splits = ops.tc_gemm_plan(512, 3584, 18944)[:3]                 # few tiles, long K: wide tiles and a split K
+    assert not wide and bn >= 208 and splits == 2
+    assert ops.tc_gemm_plan(8, 3584, 18944)[:2] == (True, 16)                 # decode: the weights take the MMA's rows
+    assert ops.tc_gemm_plan(64, 37888, 3584)[:3] == (True, 64, 1)
+
+
+def test_attention_splits_stay_in_range():
+    for batch in [1, 2, 3, 8, 16, 32, 64, 128, 256]:
+        for nh, nkv in [(28, 4), (40, 8), (4, 2), (3, 1), (16, 16), (64, 1)]:
+            for ctx in [1, 15, 16, 17, 100, 2048, 8192, 32768, 200000]:
+                for window in [None, 64, 4096]:
+                    s = ops.attention_splits(batch, batch, nh, nkv, ctx, window)
+                    assert s == 32 or 1 <= s <= ops.CLUSTER_MAX_SPLITS, (batch, nh, nkv, ctx, window, s)
+                    span = ctx if not window else min(ctx, window + 16)
+                    assert s <= max(1, -(-span // 16) + 1), (batch, nh, nkv, ctx, window, s)
+    # measured inside whole decode steps of the 7B shape
+    assert ops.attention_splits(8, 8, 28, 4, 2100, None) == 7
+    assert ops.attention_splits(64, 64, 28, 4, 2100, None) == 1
+    assert ops.attention_splits(1, 1, 28, 4, 2100, None) == 16
+    assert ops.attention_splits(1, 1, 28, 4, 32768, None) == 32
