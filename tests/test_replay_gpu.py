@@ -130,3 +130,62 @@ def test_cutting_does_not_change_logits(models, dtype):
     tol = 1e-5 if dtype == "float32" else 2e-2
     for other in runs[1:]:
         assert np.abs(other - runs[0]).max() <= tol * max(1.0, np.abs(runs[0]).max())
+
+
+def random_config(seed: int) -> tuple[dict, int, list[int]]:
+    """A configuration, a page size and request lengths drawn from a seed: head sizes in steps of 16 up to 256, any
+    number of heads and groups, widths and vocabularies that are no power of two."""
+    rng = np.random.default_rng(seed)
+    nkv, grp = int(rng.integers(1, 5)), int(rng.integers(1, 8))
+    raw = dict(architectures=["Qwen2ForCausalLM"], hidden_size=int(rng.choice([8, 4, 2])) * int(rng.integers(9, 40)),
+               intermediate_size=int(rng.choice([8, 2, 16])) * int(rng.integers(11, 50)), num_hidden_layers=int(rng.integers(1, 5)),
+               num_attention_heads=nkv * grp, num_key_value_heads=nkv,
+               head_dim=int(rng.choice([16, 32, 48, 64, 80, 96, 112, 128, 160, 256])), vocab_size=int(rng.integers(100, 3000)),
+               rope_theta=float(rng.choice([1e4, 1e6, 5e5, 12345.0])), rms_norm_eps=float(rng.choice([1e-6, 1e-5, 2e-6])),
+               tie_word_embeddings=bool(rng.integers(0, 2)), max_position_embeddings=2048)
+    page = int(rng.choice([64, 16, 128, 32]))
+    lengths = [int(x) for x in rng.integers(1, 200, 3)] + [int(rng.integers(300, 700))]
+    return raw, page, lengths
+
+
+@pytest.mark.parametrize("seed", [11, 12, 13, 14])
+def test_random_configurations(tmp_path, seed):
+    """Sizes other than the three fixed configurations', whole, in portions and mixed.  bfloat16 is judged as above.
+    float32 is judged against the plain implementation run in 64-bit: the engine's error is no larger (rms) than
+    that of the plain implementation in 32-bit, and no single logit is off by more than twice its largest error."""
+    import torch
+    from plain import qwen2_plain
+    raw, page, lengths = random_config(seed)
+    H.make_model_dir(tmp_path, raw, seed=1000 + seed)
+    reqs = {f"r{i}": H.random_ids(raw["vocab_size"], L, seed=31 * seed + i) for i, L in enumerate(lengths)}
+    portions = []
+    for k, (rid, ids) in enumerate(reqs.items()):
+        portions += H.trace_portions(rid, ids, [[2, 9, 3, 17, 2, 31], [5, 2, 16, 8], [24, 2, 2, 7], [130, 2, 64, 33]][k % 4],
+                                     first_step=len(portions))
+    many = {f"{rid}x{rep}": ids for rep in range(2) for rid, ids in reqs.items()}
+    traces = {"whole": H.trace_whole(reqs), "portions": portions, "mixed": H.trace_mixed(many, seed=seed, max_live=4)}
+    w64 = {k: v.double() for k, v in H.load_plain_weights(tmp_path).items()}
+    with torch.inference_mode():
+        p64 = {rid: qwen2_plain.forward(ids, w64, raw).numpy() for rid, ids in reqs.items()}
+    for dtype in ("float32", "bfloat16"):
+        plain = {rid: H.plain_logits(tmp_path, ids, bf16_weights=(dtype == "bfloat16")) for rid, ids in reqs.items()}
+        if dtype == "float32":
+            e = np.concatenate([(plain[r] - p64[r]).ravel() for r in reqs])
+            plain_rms, plain_max = float(np.sqrt((e ** 2).mean())), float(np.abs(e).max())
+        else:
+            e = np.concatenate([(H.plain_logits_in_bf16(tmp_path, ids) - plain[rid]).ravel() for rid, ids in reqs.items()])
+            bf16_rms = float(np.sqrt((e.astype(np.float64) ** 2).mean()))
+        for what, steps in traces.items():
+            got = H.run_trace_in_process(tmp_path, dtype, steps, H.max_live_tokens(steps, max(64, page)), page)
+            mixed = what == "mixed"
+            if dtype == "bfloat16":
+                want = {f"{rid}x{rep}": plain[rid] for rep in range(2) for rid in reqs} if mixed else plain
+                compare(got, want, dtype, f"{what} of {raw}", bf16_rms)
+                continue
+            want = {f"{rid}x{rep}": p64[rid] for rep in range(2) for rid in reqs} if mixed else p64
+            assert set(got) == set(want)
+            e = np.concatenate([(got[r].astype(np.float64) - want[r]).ravel() for r in want])
+            assert np.isfinite(e).all(), f"{what} of {raw}: non-finite logits"
+            rms, worst = float(np.sqrt((e ** 2).mean())), float(np.abs(e).max())
+            assert rms <= plain_rms and worst <= 2 * plain_max, \
+                f"{what} of {raw} (float32): engine rms {rms:.2e} max {worst:.2e}, plain 32-bit rms {plain_rms:.2e} max {plain_max:.2e}"
