@@ -45,6 +45,8 @@ class EngineConfig:
     ``prefill_chunk``: most prompt tokens of one request in one step.
     ``max_model_len``: longest sequence (prompt + output); defaults to the model's
     ``max_position_embeddings`` capped by the cache capacity.
+    ``admit_whole_prompts``: beside running requests, admit a request only when the pools will hold its
+    whole prompt (see ``engine/scheduler.py``); off: admit as soon as its first portion fits.
     ``lookahead``: start a step before the ids sampled by the step before have reached the
     host (they are fed on the device); the host work of a step then hides behind the GPU's.
     """
@@ -61,6 +63,7 @@ class EngineConfig:
     max_model_len: int | None = None
     cuda_graphs: bool = True
     lookahead: bool = True
+    admit_whole_prompts: bool = True
     debug_poison_freed_pages: bool = False
 
     def __post_init__(self):

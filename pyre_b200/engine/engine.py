@@ -73,7 +73,7 @@ class Engine:
         self.cache.set_poison(ec.debug_poison_freed_pages)
         self.stepper = Stepper(self.model, self.cache, max_positions=max_positions, cuda_graphs=ec.cuda_graphs)
         self.scheduler = Scheduler(self.cache, ec.max_num_seqs, ec.max_num_batched_tokens, ec.prefill_chunk,
-                                   self.max_model_len)
+                                   self.max_model_len, admit_whole_prompts=ec.admit_whole_prompts)
         self.sampler = Sampler(ec.device)
         self._requests: dict[int, Request] = {}
         self._flight = None      # (plan, sampling ticket, error word) of the step whose ids have not been read yet

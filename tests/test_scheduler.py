@@ -246,3 +246,28 @@ def test_lookahead_gives_the_same_tokens(seed):
         else:
             assert got.generated == want, (got.finish_reason, got.generated, want)
     assert cache.stats().pages_free == [cache.num_pages]
+
+
+def test_a_prompt_is_admitted_only_if_it_will_fit_whole():
+    """Beside running requests, a waiting request is admitted when the pools will hold its whole prompt after
+    the running ones have finished theirs (and grown by a page each); admitting its first portion earlier only
+    buys a preemption that throws the portion away.  Outputs are the same either way."""
+    results = {}
+    for whole in (True, False):
+        sched, cache = make(num_pages=12, page_size=4, max_num_seqs=4, budget=16, chunk=8)    # 48 tokens of cache
+        sched.admit_whole_prompts = whole
+        prompts = [[3, 1, 4, 1, 5, 9, 2, 6] * 3, [2, 7, 1, 8, 2, 8, 1, 8] * 3, [1, 6, 1, 8, 0, 3, 3, 9] * 2]   # 24, 24, 16 tokens
+        for p in prompts:
+            sched.add_request(p, SamplingParams(max_new_tokens=2))
+        log = []
+        done = drive(sched, cache, log)
+        for k, p in enumerate(prompts):
+            assert done[k].generated == alone(p, 2)
+        results[whole] = (sched.stats.preempted, sched.stats.scheduled_tokens, log)
+        assert cache.stats().pages_free == [cache.num_pages]
+    # 24 + 24 tokens fill the twelve pages: the second request does not fit whole beside the first, which still
+    # has to grow; with the rule it waits (no preemption), without it its first portion is computed and thrown away
+    assert results[True][0] == 0
+    assert results[False][0] >= 1 and results[False][1] > results[True][1]
+    first_start_of_second = next(n for n, step in enumerate(results[True][2]) if any(s[0] == 1 for s in step))
+    assert first_start_of_second > 3      # not before the first request has made room by finishing
