@@ -21,6 +21,7 @@ import torch
 from ..cache import CacheManager, OutOfPages
 from ..kernels import lib
 from ..models.model import Model
+from ..parts.base import collect_launch_keys
 from .context import KVView, StateView, StepContext
 
 
@@ -355,16 +356,12 @@ class Stepper:
         return result
 
     def _splits_key(self, n_entries: int, max_context: int) -> tuple:
-        """What the attention kernels derive from host-side facts of a decode step; a
-        captured graph is reused only while these stay the same."""
-        from ..kernels import ops
+        """What the parts' kernels derive from host-side facts of a decode step (``Part.launch_key``);
+        a captured graph is reused only while these stay the same."""
         out = set()
-        for blk in self.model.blocks:
-            m = getattr(blk, "mixer", None)
-            if hasattr(m, "n_kv_heads"):
-                out.add(ops.attention_splits(n_entries, n_entries, m.n_heads, m.n_kv_heads, max_context,
-                                             getattr(m, "window", None)))
-        return tuple(sorted(out))
+        for part in [self.model.embed, *self.model.blocks, self.model.final_norm, self.model.head]:
+            out |= collect_launch_keys(part, n_entries, max_context)
+        return tuple(sorted(out, key=repr))
 
     def _copy_flat(self, flat_dev: torch.Tensor, flat: np.ndarray) -> None:
         host = self._staging.stage(flat)

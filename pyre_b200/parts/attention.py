@@ -87,6 +87,10 @@ class Attention(Part):
     def state_spec(self):
         return None
 
+    def launch_key(self, n_rows, max_context):
+        # the tensor-core kernel's split count is chosen on the host from these numbers
+        return (ops.attention_splits(n_rows, n_rows, self.n_heads, self.n_kv_heads, max_context, self.window),)
+
     def forward(self, ctx, h, call):
         kv = ctx.kv_group(call.kv_group)
         layer = kv.pool[call.kv_layer]

@@ -112,6 +112,13 @@ class Part:
         """Sub-parts by the name prefix of their tensors."""
         return {}
 
+    def launch_key(self, n_rows: int, max_context: int) -> tuple:
+        """What this part's launches take from host-side facts of a step of single tokens
+        (``n_rows`` of them, the longest sequence ``max_context`` tokens long) beyond the
+        shapes of the step's arrays: a split count, a choice between kernels.  A captured
+        step is replayed only for steps whose parts give the same keys.  Hashable items."""
+        return ()
+
 
 _REGISTRY: dict[str, dict[str, Callable[..., Part]]] = {c: {} for c in CATEGORIES}
 
@@ -154,6 +161,16 @@ def load_part(part: Part, tensors: Mapping[str, torch.Tensor], prefix: str = "")
 
 def all_graph_safe(part: Part) -> bool:
     return bool(part.graph_safe) and all(all_graph_safe(c) for c in part.children().values())
+
+
+def collect_launch_keys(part: Part, n_rows: int, max_context: int) -> set:
+    """The launch keys of a part and of its sub-parts for a step of single tokens."""
+    key = getattr(part, "launch_key", None)
+    out = {tuple(key(n_rows, max_context))} if key is not None else set()
+    for child in part.children().values():
+        out |= collect_launch_keys(child, n_rows, max_context)
+    out.discard(())
+    return out
 
 
 def collect_libraries(part: Part) -> list[str]:

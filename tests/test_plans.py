@@ -54,3 +54,36 @@ def test_attention_splits_stay_in_range():
     assert ops.attention_splits(64, 64, 28, 4, 2100, None) == 1
     assert ops.attention_splits(1, 1, 28, 4, 2100, None) == 16
     assert ops.attention_splits(1, 1, 28, 4, 32768, None) == 32
+
+
+def test_launch_keys_come_from_the_parts():
+    """The stepper keys its captured decode steps on what the parts say (``Part.launch_key``), not on
+    what it knows of attention: a block's key is its mixer's split count, a part of another kind adds its own."""
+    import torch
+
+    from pyre_b200.config import config_from_dict
+    from pyre_b200.config.registry import architecture_of
+    from pyre_b200.models.model import Model
+    from pyre_b200.parts.base import Part, collect_launch_keys
+
+    cfg = config_from_dict(dict(architectures=["Qwen2ForCausalLM"], hidden_size=64, intermediate_size=176,
+                                num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, vocab_size=512))
+    model = Model(architecture_of(cfg).build(cfg), torch.bfloat16, "cpu")
+    for rows, context in [(1, 40), (8, 2100), (64, 300)]:
+        keys = set()
+        for b in model.blocks:
+            keys |= collect_launch_keys(b, rows, context)
+        assert keys == {(ops.attention_splits(rows, rows, 4, 2, context, None),)}
+    assert collect_launch_keys(model.embed, 8, 100) == set() and collect_launch_keys(model.head, 8, 100) == set()
+
+    class Halves(Part):                     # a part whose launches depend on the longest context in its own way
+        def launch_key(self, n_rows, max_context):
+            return ("halves", max_context > 1000)
+
+    class Holder(Part):
+        def children(self):
+            return {"inner.": Halves(torch.float32, torch.device("cpu"))}
+
+    holder = Holder(torch.float32, torch.device("cpu"))
+    assert collect_launch_keys(holder, 4, 10) == {("halves", False)}
+    assert collect_launch_keys(holder, 4, 5000) == {("halves", True)}
