@@ -4,9 +4,11 @@ Each function checks shapes, dtypes, contiguity and device, then launches the CU
 kernel on torch's current stream.  A size the kernels do not take is refused with a
 clear error; nothing here computes on the CPU or falls back to a library.
 
-The matrix products of the bfloat16 path are the one place where a library stands in
-(cuBLAS through ``torch``), as the reference's engine uses one for every projection
-(``nn.Linear``, pyre/model.py:84-87,133-135,172); see ``linear``.
+The matrix products are the package's own kernels too (``gemm_tc`` on the tcgen05 tensor
+cores for bfloat16, ``sgemm_nt`` for float32).  One case goes to a library (cuBLAS through
+``torch``): a bfloat16 product whose rows are no multiple of 16 bytes, which a TMA copy
+cannot fetch; the reference's engine uses a library for every projection (``nn.Linear``,
+pyre/model.py:84-87,133-135,172).  See ``linear``.
 """
 
 from __future__ import annotations
@@ -131,6 +133,8 @@ def add_rmsnorm(x: torch.Tensor, delta: "torch.Tensor | None", weight: torch.Ten
 
 
 def add_residual(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """x += float32(delta) in place on the fp32 residual stream: for a block arrangement in which no
+    norm follows a branch (the built-in pre-norm block adds its branches inside the next norm's kernel)."""
     _check(x, "x", torch.float32)
     _check(delta, "delta")
     if x.shape != delta.shape:
@@ -655,10 +659,3 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool) ->
     if interleaved and x.dtype == torch.bfloat16 and USE_TC_GEMM and tc_gemm_supported(x, w_gate_up):
         return gemm_tc(x, w_gate_up, torch.bfloat16, gated=True)
     return silu_mul(linear(x, w_gate_up), block=GATED_BLOCK if interleaved else 0)
-
-
-def required_libraries(dtype: torch.dtype) -> list[str]:
-    """Kernel libraries that a decoder step in ``dtype`` calls (built before the first step)."""
-    libs = ["elementwise", "sampling", "attention_generic"]
-    libs.append("gemm_f32" if dtype == torch.float32 else "gemm_tc")
-    return libs

@@ -62,6 +62,18 @@ def test_add_rmsnorm(ops, dtype, H, eps):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 40), (7, 101), (300, 3584)])
+def test_add_residual(ops, dtype, shape):
+    """The plain residual sum for a branch that no norm follows: fp32 stream += delta, summed in fp32."""
+    g = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn(*shape, device="cuda", generator=g)
+    delta = torch.randn(*shape, device="cuda", generator=g).to(dtype)
+    want = x + delta.float()
+    assert ops.add_residual(x, delta) is x
+    assert torch.equal(x, want)                       # one fp32 addition per element: exact
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("I", [176, 99, 1000])
 def test_silu_mul(ops, dtype, I):
     g = torch.Generator(device="cuda").manual_seed(2)
