@@ -151,18 +151,23 @@ def ensure_built(names, verbose: bool = True, extra_flags: "list[str] | None" = 
             for n in todo:
                 tmp = bdir / f".libpyre_{n}.{os.getpid()}.so"
                 cmd = [nvcc, *NVCC_FLAGS, *(extra_flags or []), "-I", str(CSRC), "-o", str(tmp), str(CSRC / LIBRARIES[n])]
-                procs[n] = (subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True), tmp)
+                # the compiler's messages go to a file: a pipe that nobody reads until the exit would block a
+                # compiler that says more than the pipe holds
+                log = tempfile.TemporaryFile(mode="w+", dir=bdir)
+                procs[n] = (subprocess.Popen(cmd, stdout=log, stderr=subprocess.STDOUT), tmp, log)
             pending = dict(procs)
             last = time.time()
             while pending:
                 for n in list(pending):
-                    proc, tmp = pending[n]
+                    proc, tmp, log = pending[n]
                     if proc.poll() is None:
                         continue
-                    out = proc.stdout.read() if proc.stdout else ""
+                    log.seek(0)
+                    out = log.read()
+                    log.close()
                     del pending[n]
                     if proc.returncode != 0:
-                        for p, t in pending.values():
+                        for p, _t, _l in pending.values():
                             p.kill()
                         raise BuildError(f"nvcc failed on {LIBRARIES[n]} (exit {proc.returncode}):\n{out}")
                     os.replace(tmp, library_path(n))
