@@ -17,6 +17,7 @@ already cached (context 2,048 + tokens decoded so far, inside the benchmark cont
   roofline         bytes the decode step must read (every weight once + the cache of the
                    live requests) / its time, against the HBM peak
   points           decode tokens/s at batch 1 and 64
+  env              GPU, compute capability, torch and CUDA versions, commit, time
 
 Peaks come from MEASURED_PEAKS.json beside this file if it is there, else from the
 fallback figures (6.65 TB/s copy bandwidth, 1.59 PFLOP/s bf16).  Every step streams
@@ -429,6 +430,28 @@ def run_sweep(args) -> dict:
     return {"workload": "sweep", "layers": layers, "peaks": peaks, "decode": decode, "prefill": prefill}
 
 
+def environment() -> dict:
+    """Where a number was measured, recorded with it as the reference's harness does (bench/harness.py:49-67):
+    GPU, compute capability, torch and CUDA versions, the checkout's commit, the time."""
+    env = {"gpu": None, "capability": None, "torch": None, "cuda": None, "git": None,
+           "time": time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime())}
+    try:
+        import torch
+        env["torch"], env["cuda"] = torch.__version__, torch.version.cuda
+        if torch.cuda.is_available():
+            env["gpu"] = torch.cuda.get_device_name(0)
+            env["capability"] = ".".join(str(v) for v in torch.cuda.get_device_capability(0))
+    except Exception:       # the record must never cost the measurement
+        pass
+    try:
+        out = subprocess.run(["git", "-C", str(ROOT), "rev-parse", "--short", "HEAD"], capture_output=True, text=True,
+                             timeout=10)
+        env["git"] = out.stdout.strip() or None
+    except (OSError, subprocess.SubprocessError):
+        pass
+    return env
+
+
 def run_reference(args) -> dict:
     from baseline import reference_arm
     return reference_arm.run(args, CONFIG_7B, PROMPT_LEN)
@@ -454,9 +477,13 @@ def main() -> int:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported, run with --gpus 1")
         return 2
     if args.workload:
-        print(json.dumps(run_sweep(args) if args.workload == "sweep" else run_workload(args)))
+        result = run_sweep(args) if args.workload == "sweep" else run_workload(args)
+        result["env"] = environment()
+        print(json.dumps(result))
         return 0
     result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if "unavailable" not in result:
+        result["env"] = environment()
     print(json.dumps(result))
     return 0
 
