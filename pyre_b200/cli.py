@@ -38,7 +38,7 @@ def cmd_generate(args) -> int:
     ec = EngineConfig(dtype=args.dtype, device=args.device, page_size=args.page_size, num_pages=args.num_pages,
                       cache_memory_fraction=args.cache_memory_fraction, lookahead=not args.no_lookahead,
                       max_num_seqs=args.max_num_seqs, max_num_batched_tokens=args.max_batched_tokens,
-                      prefill_chunk=args.prefill_chunk)
+                      prefill_chunk=args.prefill_chunk, record_steps=bool(args.step_log))
     print(f"loading {args.model} on {args.device} ...", file=sys.stderr)
     engine = Engine(args.model, ec)
     params = [SamplingParams(temperature=args.temperature, seed=args.seed + i, max_new_tokens=args.max_new_tokens,
@@ -55,6 +55,10 @@ def cmd_generate(args) -> int:
                            "finish_reason": o.finish_reason} for o in outs]}
     for o in outs:
         print(" ".join(str(t) for t in o.token_ids))
+    if args.step_log:
+        Path(args.step_log).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.step_log).write_text("".join(json.dumps(rec) + "\n" for rec in engine.step_log))
+        print(f"wrote {args.step_log} ({len(engine.step_log)} steps)", file=sys.stderr)
     if args.out:
         Path(args.out).parent.mkdir(parents=True, exist_ok=True)
         Path(args.out).write_text(json.dumps(result, indent=2))
@@ -100,6 +104,8 @@ def main(argv=None) -> int:
     g.add_argument("--max-batched-tokens", type=int, default=2048, help="token budget of one step")
     g.add_argument("--prefill-chunk", type=int, default=2048, help="most prompt tokens of a request per step")
     g.add_argument("--out", default=None, help="write a JSON result file")
+    g.add_argument("--step-log", default=None,
+                   help="write one JSON line per step: tokens, requests, pages free, preemptions, host time")
     g.set_defaults(func=cmd_generate)
 
     r = sub.add_parser("random-model", help="write a model folder with random weights")

@@ -49,6 +49,8 @@ class EngineConfig:
     whole prompt (see ``engine/scheduler.py``); off: admit as soon as its first portion fits.
     ``lookahead``: start a step before the ids sampled by the step before have reached the
     host (they are fed on the device); the host work of a step then hides behind the GPU's.
+    ``record_steps``: keep one record per step in ``Engine.step_log`` (tokens, requests, pages free,
+    preemptions, the host's time in the call); off by default.
     """
 
     dtype: "str | torch.dtype" = "bfloat16"
@@ -65,6 +67,7 @@ class EngineConfig:
     lookahead: bool = True
     admit_whole_prompts: bool = True
     debug_poison_freed_pages: bool = False
+    record_steps: bool = False
 
     def __post_init__(self):
         self.dtype = parse_dtype(self.dtype)

@@ -10,6 +10,7 @@ borrows one from another package in its server only, pyre/server/app.py:54-68).
 
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass
 from pathlib import Path
 from typing import Sequence
@@ -21,7 +22,7 @@ from ..config import EngineConfig, ModelConfig, architecture_of, load_config
 from ..kernels import build, lib
 from ..models.model import Model
 from ..sampling import Sampler, SamplingParams
-from .scheduler import PENDING, Request, Scheduler
+from .scheduler import PENDING, Request, Scheduler, step_record
 from .step import StepEntry, Stepper
 
 
@@ -79,6 +80,7 @@ class Engine:
         self._flight = None      # (plan, sampling ticket, error word) of the step whose ids have not been read yet
         self._err_host = [torch.zeros(1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._err_turn = 0
+        self.step_log: "list[dict] | None" = [] if ec.record_steps else None
 
     def _pages_for_memory(self, ec: EngineConfig, spec) -> int:
         """Pages per group so that all pools together take ``cache_memory_fraction`` of the memory that is free
@@ -121,6 +123,7 @@ class Engine:
         returned one call later, and a request that hits its end-of-sequence token has computed
         one token too many (dropped).  The ids are the same either way."""
         sched = self.scheduler
+        t_call = time.perf_counter()
         plan = sched.schedule()
         flight = None
         if plan:
@@ -150,6 +153,9 @@ class Engine:
         if flight is not None and not self.engine_config.lookahead:
             self._land(flight)
             self._flight = None
+        if self.step_log is not None and plan:
+            self.step_log.append(step_record(sched.stats.steps - 1, plan, self.cache, sched.stats,
+                                             time.perf_counter() - t_call))
         outs = []
         for sid in [sid for sid, r in self._requests.items() if r.done and not r.pending]:
             r = self._requests.pop(sid)

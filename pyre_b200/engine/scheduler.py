@@ -94,6 +94,18 @@ class SchedulerStats:
     scheduled_tokens: int = 0
 
 
+def step_record(index: int, plan: "Sequence[Scheduled]", cache: CacheManager, stats: SchedulerStats,
+                host_seconds: float) -> dict:
+    """What one step did, for a log of a run: its tokens and requests (prompt portions and decoded tokens apart),
+    how many of its entries sample, the pages left in every group afterwards, the preemptions so far, and the
+    host's time in the call.  The reference records only totals per run (bench/harness.py:84-135)."""
+    decoded = sum(1 for s in plan if s.count == 1 and s.samples and s.start >= len(s.request.prompt_ids))
+    return {"step": index, "tokens": sum(s.count for s in plan), "requests": len(plan), "decoded_tokens": decoded,
+            "prompt_tokens": sum(s.count for s in plan) - decoded, "sampling": sum(1 for s in plan if s.samples),
+            "pages_free": list(cache.stats().pages_free), "preempted_so_far": stats.preempted,
+            "host_ms": round(host_seconds * 1e3, 3)}
+
+
 class Scheduler:
     def __init__(self, cache: CacheManager, max_num_seqs: int, max_num_batched_tokens: int,
                  prefill_chunk: int, max_model_len: int, admit_whole_prompts: bool = True):

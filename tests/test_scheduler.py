@@ -271,3 +271,25 @@ def test_a_prompt_is_admitted_only_if_it_will_fit_whole():
     assert results[False][0] >= 1 and results[False][1] > results[True][1]
     first_start_of_second = next(n for n, step in enumerate(results[True][2]) if any(s[0] == 1 for s in step))
     assert first_start_of_second > 3      # not before the first request has made room by finishing
+
+
+def test_step_record_tells_prompt_portions_from_decoded_tokens():
+    from pyre_b200.engine.scheduler import step_record
+
+    sched, cache = make(num_pages=64, budget=10, chunk=6)
+    a = sched.add_request(list(range(1, 9)), SamplingParams(max_new_tokens=3))       # 8 tokens: portions of 6 and 2
+    b = sched.add_request([5, 6, 7], SamplingParams(max_new_tokens=3))
+    records = []
+    for _ in range(4):
+        plan = sched.schedule()
+        for s in plan:
+            cache.commit(s.request.seq_id, s.start + s.count)
+        records.append(step_record(sched.stats.steps - 1, plan, cache, sched.stats, 0.0015))
+        sched.update(plan, [fake_token(s.request.tokens(0, s.start + s.count)) for s in plan if s.samples])
+    first, second, third = records[0], records[1], records[2]
+    assert (first["step"], first["tokens"], first["requests"], first["prompt_tokens"], first["decoded_tokens"]) == (0, 9, 2, 9, 0)
+    assert first["sampling"] == 1 and first["host_ms"] == 1.5 and first["preempted_so_far"] == 0
+    assert first["pages_free"] == [64 - 2 - 1]                                        # 6 and 3 tokens in pages of 4
+    assert (second["tokens"], second["prompt_tokens"], second["decoded_tokens"], second["sampling"]) == (3, 2, 1, 2)
+    assert (third["tokens"], third["prompt_tokens"], third["decoded_tokens"]) == (2, 0, 2)
+    assert a.seq_id != b.seq_id
