@@ -52,6 +52,12 @@ class StepContext:
     state_groups: list[StateView] = field(default_factory=list)
     scratch: dict = field(default_factory=dict)   # per-step values shared between layers (rotary tables)
     error_flag: "torch.Tensor | None" = None
+    # the stepper's own: where tokens sampled by the step before enter this one (``token_ids[feed_dst[b]] =
+    # sampled[feed_src[b]]`` where feed_dst[b] >= 0), the entries of the step and the lengths to commit after it
+    feed_dst: "torch.Tensor | None" = None
+    feed_src: "torch.Tensor | None" = None
+    entries: list = field(default_factory=list)
+    new_lens: list = field(default_factory=list)
 
     def kv_group(self, index: int) -> KVView:
         return self.kv_groups[index]

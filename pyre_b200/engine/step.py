@@ -266,8 +266,8 @@ class Stepper:
         ctx = StepContext(
             dtype=self.model.dtype, device=self.device, num_tokens=T, num_seqs=B, num_logit_rows=R,
             token_ids=view(0), positions=view(1), seq_of_token=view(2), cu_seqlens=view(3), logit_rows=view(4),
-            cu_seqlens_host=cu, start_pos_host=np.asarray(starts, dtype=np.int64), error_flag=self.error_flag)
-        ctx._feed = (view(5), view(6))  # type: ignore[attr-defined]
+            cu_seqlens_host=cu, start_pos_host=np.asarray(starts, dtype=np.int64), error_flag=self.error_flag,
+            feed_dst=view(5), feed_src=view(6), entries=list(entries), new_lens=list(new_lens))
         k = 7
         for g, group in enumerate(cache.groups):
             ctx.kv_groups.append(KVView(group.pool, view(k + 1).view(tables[g]), view(k), group.page_size,
@@ -276,8 +276,6 @@ class Stepper:
         slots_dev = view(k)
         for buf in cache.state.buffers:
             ctx.state_groups.append(StateView(buf, slots_dev, state_slots))
-        ctx._entries = entries  # type: ignore[attr-defined]
-        ctx._new_lens = new_lens  # type: ignore[attr-defined]
         return ctx
 
     def _feed(self, ctx: StepContext, entries: Sequence[StepEntry], fed_from: "torch.Tensor | None") -> None:
@@ -286,13 +284,12 @@ class Stepper:
             if fed_from is None:
                 raise ValueError("an entry asks for a token of the step before, but its sampled ids were not given")
             from ..kernels import ops
-            dst, src = ctx._feed  # type: ignore[attr-defined]
-            ops.feed_tokens(ctx.token_ids, dst, src, fed_from)
+            ops.feed_tokens(ctx.token_ids, ctx.feed_dst, ctx.feed_src, fed_from)
 
     def run_context(self, ctx: StepContext, fed_from: "torch.Tensor | None" = None) -> torch.Tensor:
-        self._feed(ctx, ctx._entries, fed_from)  # type: ignore[attr-defined]
+        self._feed(ctx, ctx.entries, fed_from)
         logits = self.model.forward(ctx)
-        for e, new_len in zip(ctx._entries, ctx._new_lens):  # type: ignore[attr-defined]
+        for e, new_len in zip(ctx.entries, ctx.new_lens):
             self.cache.commit(e.request, new_len)
         self.steps_run += 1
         return logits

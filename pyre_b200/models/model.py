@@ -60,9 +60,6 @@ class Model:
         self.calls, self.kv_groups, self.state_groups = self._bind_schedule()
         self.loaded = False
         self.graph_safe = all(all_graph_safe(p) for p in [self.embed, self.final_norm, self.head, *self.blocks])
-        # the mixer's position encoding is built by the mixer itself
-        self.graph_safe = self.graph_safe and all(getattr(getattr(b, 'mixer', None), 'position', None) is None
-                                                  or b.mixer.position.graph_safe for b in self.blocks)
 
     # ------------------------------------------------------------------ schedule
     def _bind_schedule(self):

@@ -44,7 +44,8 @@ class Attention(Part):
         self.w_qkv = self.b_qkv = self.w_o = None
 
     def children(self):
-        return {}  # the position encodings built so far own no tensors
+        # a position encoding with tensors of its own would find them under the mixer's prefix
+        return {"": self.position}
 
     def tensors(self):
         q, kv = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
@@ -71,7 +72,7 @@ class Attention(Part):
         self.w_o = tensors["o_proj.weight"]
 
     def kernel_libraries(self):
-        libs = ["elementwise"] + self.position.kernel_libraries()
+        libs = ["elementwise"]      # the position encoding, a sub-part, names its own
         if self.dtype == torch.bfloat16 and self.head_dim <= ops.MMA_MAX_HEAD_DIM:
             libs.append("attention_mma")
             if self.head_dim in ops.PREFILL_HEAD_DIMS:

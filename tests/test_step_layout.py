@@ -126,7 +126,7 @@ def test_padded_decode_step_uses_scratch_page_and_slot():
     assert ctx.token_ids.tolist() == [10, 11, 12, 0, 0, 0, 0, 0]
     assert ctx.positions.tolist() == [5, 9, 1, 0, 0, 0, 0, 0]
     assert ctx.cu_seqlens.tolist() == list(range(9)) and ctx.logit_rows.tolist() == list(range(8))
-    dst, src = ctx._feed
+    dst, src = ctx.feed_dst, ctx.feed_src
     assert dst.tolist() == [0, -1, 2, -1, -1, -1, -1, -1] and src.tolist()[:3] == [0, 0, 2]
     for g, group in enumerate(cache.groups):
         kv = ctx.kv_group(g)
@@ -192,3 +192,37 @@ def test_random_steps_write_every_position_once(seed):
     for r in list(live):
         cache.end(r)
     assert all(f == 24 for f in cache.stats().pages_free)
+
+
+def test_step_runs_the_model_on_the_batch_and_commits_lengths(monkeypatch):
+    """``Stepper.step`` end to end with a stand-in model and a host-side token feed: the model sees the
+    context of the batch, fed tokens replace the stand-ins before it runs, lengths are committed after."""
+    from pyre_b200.kernels import ops
+
+    st, cache = make_stepper(page_size=4)
+    seen = {}
+
+    def forward(ctx):
+        seen["tokens"], seen["rows"] = ctx.token_ids.tolist(), ctx.logit_rows.tolist()
+        return torch.arange(ctx.num_logit_rows, dtype=torch.float32)[:, None]
+
+    def feed_tokens(token_ids, dst, src, prev):
+        for d, s in zip(dst.tolist(), src.tolist()):
+            if d >= 0:
+                token_ids[d] = prev[s]
+
+    monkeypatch.setattr(ops, "feed_tokens", feed_tokens)
+    st.model.forward = forward
+    st.cuda_graphs, st.steps_run = False, 0
+    st._staging = types.SimpleNamespace(upload=lambda flat: torch.from_numpy(flat.copy()))
+    for r in "ab":
+        cache.begin(r)
+    st.step([StepEntry("a", [4, 5, 6], [2]), StepEntry("b", [7, 8], [])])
+    assert seen == {"tokens": [4, 5, 6, 7, 8], "rows": [2]} and (cache.length("a"), cache.length("b")) == (3, 2)
+    sampled = torch.tensor([41, 42], dtype=torch.int32)          # ids of the step before, "on the device"
+    logits = st.step([StepEntry("b", [9, 0], [1], feed=1), StepEntry("a", [0], [0], feed=0)], fed_from=sampled)
+    assert seen == {"tokens": [9, 42, 41], "rows": [1, 2]} and logits.shape == (2, 1)
+    assert (cache.length("a"), cache.length("b")) == (4, 4) and st.steps_run == 2
+    with pytest.raises(ValueError, match="sampled ids were not given"):
+        st.step([StepEntry("a", [0], [0], feed=0)])
+    cache.check()
