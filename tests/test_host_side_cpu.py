@@ -1,0 +1,164 @@
+"""The engine's host side on the CPU: the package's parts, model, cache manager, step function and
+replay loop with plain torch stand-ins for the kernels (``tests/standins.py``), in float32, against
+the plain implementation.  The four ways of cutting a trace (whole, the tail token by token, portions
+down to two tokens, mixed with so few pages that they are used again, freed pages filled with NaN)
+must give the plain logits: what differs here is a fault of the batch's layout, the block tables,
+the schedule or the bookkeeping, not of a kernel."""
+
+import json
+import tempfile
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+import standins
+
+LENGTHS = {"A": [5, 17, 33, 70], "B": [1, 7, 40, 63, 81]}
+
+
+def runtime(model_dir, max_tokens, page_size, spec_edit=None):
+    from pyre_b200.config import architecture_of, load_config
+    from pyre_b200.engine.replay import runtime_for_model
+    from pyre_b200.models import Model
+
+    cfg = load_config(model_dir)
+    spec = architecture_of(cfg).build(cfg)
+    if spec_edit is not None:
+        spec_edit(spec)
+    model = Model(spec, torch.float32, "cpu")
+    model.load_weights(model_dir)
+    cache, stepper = runtime_for_model(model, max_tokens, page_size, poison=True, cuda_graphs=False)
+    return model, cache, stepper
+
+
+def run_trace(model_dir, steps, max_tokens, page_size, spec_edit=None):
+    from pyre_b200.engine import replay as rp
+
+    model, cache, stepper = runtime(model_dir, max_tokens, page_size, spec_edit)
+    with tempfile.TemporaryDirectory() as out:
+        rp.replay(stepper, [json.dumps(s) for s in steps], Path(out), done=lambda m: None)
+        got = H.collect_trace_logits(steps, lambda n: np.fromfile(Path(out) / f"{n}.f32", dtype="<f4").reshape(-1, model.vocab_size))
+    cache.check()
+    assert not cache.live() and cache.stats().pages_free == cache.stats().pages_total
+    return got
+
+
+def compare(got, want, what):
+    assert set(got) == set(want)
+    for rid in want:
+        g, w = got[rid], want[rid]
+        assert g.shape == w.shape and np.isfinite(g).all(), f"{what} {rid}"
+        bad = np.abs(g - w) > 2e-5 + 2e-4 * np.abs(w)
+        if bad.any():
+            row = int(np.where(bad.any(axis=1))[0][0])
+            raise AssertionError(f"{what} {rid}: first wrong token at position {row} of {g.shape[0]}, "
+                                 f"max |diff| there {np.abs(g - w)[row].max():.3e}")
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    out = {}
+    for n, name in enumerate(LENGTHS):
+        raw = H.TINY[name]
+        d = tmp_path_factory.mktemp(f"cpu_{name}")
+        H.make_model_dir(d, raw, seed=300 + n)
+        reqs = {f"{name}{i}": H.random_ids(raw["vocab_size"], L, seed=11 * n + i) for i, L in enumerate(LENGTHS[name])}
+        out[name] = (d, reqs, {rid: H.plain_logits(d, ids) for rid, ids in reqs.items()})
+    return out
+
+
+@pytest.mark.parametrize("name", list(LENGTHS))
+def test_every_way_of_cutting_gives_the_plain_logits(models, name, monkeypatch):
+    standins.install(monkeypatch)
+    d, reqs, want = models[name]
+    page = H.PAGE_SIZE[name]
+    steps = H.trace_whole(reqs)
+    compare(run_trace(d, steps, H.max_live_tokens(steps), page), want, "whole")
+    rid = max(reqs, key=lambda r: len(reqs[r]))
+    steps = H.trace_decode_tail(rid, reqs[rid], tail=32)
+    compare(run_trace(d, steps, H.max_live_tokens(steps), page), {rid: want[rid]}, "tail token by token")
+    steps = H.trace_portions(rid, reqs[rid], [7, 2, 19, 3, 2, 30])
+    compare(run_trace(d, steps, H.max_live_tokens(steps), page), {rid: want[rid]}, "portions")
+    for seed in (1, 2):
+        steps = H.trace_mixed(reqs, seed=seed, max_live=3)
+        compare(run_trace(d, steps, H.max_live_tokens(steps), page), want, f"mixed (seed {seed})")
+
+
+def test_a_schedule_with_a_repeated_layer_a_shared_cache_and_a_window(models, monkeypatch):
+    """Layer 0 twice, layer 1 with a window of 9 keys whose second run reads the first run's cache:
+    the plain implementation with the same schedule and window, in portions that straddle pages."""
+    from pyre_b200.models import LayerCall
+    from pyre_b200.parts import PartSpec
+    from plain import qwen2_plain
+
+    standins.install(monkeypatch)
+    d, reqs, _ = models["A"]
+    raw = H.TINY["A"]
+
+    def edit(spec):
+        b = spec.blocks[1]
+        spec.blocks[1] = PartSpec(b.kind, dict(b.params, mixer=PartSpec("attention", dict(b.params["mixer"].params, window=9))))
+        spec.schedule = [LayerCall(0), LayerCall(1, cache="s"), LayerCall(0), LayerCall(1, cache="s", write=False)]
+
+    rid = "A3"
+    ids = reqs[rid]
+    with torch.inference_mode():
+        want = qwen2_plain.forward(ids, H.load_plain_weights(d), raw, schedule=[(0, None), (1, None), (0, None), (1, 1)],
+                                   windows=[None, 9, None, 9]).numpy()
+    for sizes in ([len(ids)], [5, 2, 11, 1, 1, 1, 17], [40] + [1] * 30):
+        steps = H.trace_portions(rid, ids, sizes)
+        got = run_trace(d, steps, 128, 4, edit)
+        compare(got, {rid: want}, f"portions {sizes[:4]}")
+
+
+class HostSampler:
+    """The sampler's two calls without pinned memory or events: greedy ids straight from the stand-in."""
+
+    def sample_async(self, logits, params, token_index):
+        import types
+
+        from pyre_b200.kernels import ops
+        assert all(p.temperature == 0.0 for p in params)
+        return types.SimpleNamespace(ids=ops.sample(logits))
+
+    def read(self, ticket):
+        return ticket.ids.tolist()
+
+
+@pytest.mark.parametrize("lookahead", [True, False])
+def test_greedy_generation_through_the_engine_loop(models, monkeypatch, lookahead):
+    """``Engine.generate`` with the real model, stepper, cache manager and scheduler (kernels and sampler
+    stood in for): few pages, so requests are preempted and recomputed; with ``lookahead`` the token a
+    step needs from the step before never passes through the host.  Ids equal the plain greedy ids."""
+    import contextlib
+
+    from pyre_b200.config import EngineConfig
+    from pyre_b200.engine.engine import Engine
+    from pyre_b200.engine.scheduler import Scheduler
+    from pyre_b200.sampling import SamplingParams
+    from plain import qwen2_plain
+
+    standins.install(monkeypatch)
+    monkeypatch.setattr(torch.cuda, "device", lambda device: contextlib.nullcontext())
+    d, reqs, _ = models["B"]
+    raw = H.TINY["B"]
+    model, cache, stepper = runtime(d, max_tokens=15 * 8, page_size=8)
+    eng = object.__new__(Engine)
+    eng.engine_config = EngineConfig(dtype="float32", lookahead=lookahead, record_steps=True)
+    eng.model, eng.cache, eng.stepper, eng.sampler = model, cache, stepper, HostSampler()
+    eng.max_model_len = 15 * 8
+    eng.scheduler = Scheduler(cache, 4, 48, 20, eng.max_model_len, admit_whole_prompts=False)
+    eng._requests, eng._flight, eng.step_log = {}, None, []
+    eng._err_host, eng._err_turn = [torch.zeros(1, dtype=torch.int32) for _ in range(2)], 0
+    prompts = [ids for ids in reqs.values()]
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=9))
+    w = H.load_plain_weights(d)
+    for p, o in zip(prompts, outs):
+        assert o.finish_reason == "length" and o.token_ids == qwen2_plain.greedy_generate(p, w, raw, 9), len(p)
+    assert eng.stats()["preempted"] > 0, "the cache was meant to be too small for all requests at once"
+    cache.check()
+    assert not cache.live() and cache.stats().pages_free == cache.stats().pages_total
+    assert len(eng.step_log) == eng.scheduler.stats.steps
