@@ -1,4 +1,4 @@
-"""Plain torch stand-ins for the CUDA kernels, float32 only, for tests without a GPU.
+"""Plain torch stand-ins for the CUDA kernels, for tests without a GPU.
 
 They state each kernel's contract (arguments, layouts, what is written where) in the simplest
 terms and share no code with the kernels.  With them in place of ``pyre_b200.kernels.ops`` the
@@ -118,3 +118,129 @@ def install(monkeypatch) -> None:
     monkeypatch.setattr(ops, "check_device_errors", lambda device="cpu": None)
     monkeypatch.setattr(step._Staging, "upload", lambda self, flat: torch.from_numpy(flat.copy()))
     monkeypatch.setattr(torch.cuda, "synchronize", lambda *a, **k: None)
+
+
+# --------------------------------------------------------------------------- the bfloat16 path
+# Stand-ins for the tensor-core kernels: bf16 operands, fp32 arithmetic, results rounded where the
+# kernels round them.  The products honour the package's own plan (orientation, width, split of K), so
+# split-K partial sums travel to their consumers as they do on the device; the attention stand-ins
+# write only the rows of the entries that the kernel they stand for would take.
+
+def _partial_sums_or_tensor(t):
+    from pyre_b200.kernels import ops
+    return t.parts.sum(0) if isinstance(t, ops.PartialSums) else t.float()
+
+
+def add_rmsnorm_any(x, delta, weight, eps, out_dtype, rows=None, update_x=True, out=None):
+    return add_rmsnorm(x, None if delta is None else _partial_sums_or_tensor(delta), weight, eps, out_dtype, rows, update_x)
+
+
+def qkv_rope_write_any(qkv, bias, cos, sin, cache_layer, slot_mapping, n_heads, n_kv_heads, head_dim, rotary_dim,
+                       page_size, q_out=None):
+    act = qkv.dtype          # of the activations, for a tensor and for partial sums alike
+    q = qkv_rope_write(_partial_sums_or_tensor(qkv), bias, cos, sin, cache_layer, slot_mapping, n_heads, n_kv_heads,
+                       head_dim, rotary_dim, page_size)
+    return q.to(act)
+
+
+def materialize(t):
+    from pyre_b200.kernels import ops
+    return t.parts.sum(0).to(t.dtype) if isinstance(t, ops.PartialSums) else t
+
+
+def gemm_tc(x, w, out_dtype=torch.bfloat16, plan=None, reduce=True, gated=False, pair=None):
+    from pyre_b200.kernels import ops
+    assert x.dtype == w.dtype == torch.bfloat16 and x.shape[1] == w.shape[1]
+    M, K = x.shape
+    N = w.shape[0]
+    _rows, _bn, splits = plan or ops.tc_gemm_plan(M, N, K)
+    kb = -(-K // 64)
+    splits = max(1, min(splits, kb))
+    if gated:
+        assert N % (2 * ops.GATED_BLOCK) == 0
+        y = (x.float() @ w.float().t()).view(M, N // (2 * ops.GATED_BLOCK), 2, ops.GATED_BLOCK)
+        return (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(M, N // 2).to(torch.bfloat16)
+    per = -(-kb // splits) * 64
+    parts = torch.stack([x[:, s * per:(s + 1) * per].float() @ w[:, s * per:(s + 1) * per].float().t() for s in range(splits)])
+    if splits == 1 and reduce:
+        return parts[0].to(out_dtype)
+    if not reduce:
+        return ops.PartialSums(parts.contiguous(), out_dtype)
+    return parts.sum(0).to(out_dtype)
+
+
+def silu_mul_any(gate_up, out=None, block=0):
+    if block == 0:
+        return silu_mul(gate_up.float()).to(gate_up.dtype)
+    T, two_i = gate_up.shape
+    y = gate_up.float().view(T, two_i // (2 * block), 2, block)
+    return (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(T, two_i // 2).to(gate_up.dtype)
+
+
+def _attend_entries(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_heads, n_kv_heads, head_dim, scale, window,
+                    out, takes):
+    cu = cu_seqlens.tolist()
+    taken = 0
+    for b in range(n_seqs):
+        n = cu[b + 1] - cu[b]
+        if not takes(n):
+            continue
+        taken += n
+        rows = slice(cu[b], cu[b + 1])
+        out[rows] = paged_attention_generic(q[rows], cache_layer, block_table[b:b + 1], torch.zeros(n, dtype=torch.int32),
+                                            positions[rows], n_heads, n_kv_heads, head_dim, scale, window)
+    return taken
+
+
+def paged_attention_mma(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_heads, n_kv_heads, head_dim, scale,
+                        window=None, n_splits=1, out=None, scratch=None, max_len=0, uniform_len=0):
+    from pyre_b200.kernels import ops
+    assert q.dtype == cache_layer.dtype == torch.bfloat16 and head_dim <= ops.MMA_MAX_HEAD_DIM
+    assert n_splits == 32 or 1 <= n_splits <= ops.CLUSTER_MAX_SPLITS
+    lens = (cu_seqlens[1:] - cu_seqlens[:-1]).tolist()
+    assert not uniform_len or all(n == uniform_len for n in lens), "uniform_len promises entries of one length"
+    if out is None:
+        out = torch.empty_like(q)
+    _attend_entries(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_heads, n_kv_heads, head_dim, scale, window,
+                    out, lambda n: not (max_len > 0 and n > max_len))
+    return out
+
+
+def attention_prefill(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_long_tokens, n_heads, n_kv_heads,
+                      head_dim, scale, window, out, min_len=32):
+    from pyre_b200.kernels import ops
+    assert head_dim in ops.PREFILL_HEAD_DIMS
+    taken = _attend_entries(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_heads, n_kv_heads, head_dim, scale,
+                            window, out, lambda n: n >= min_len)
+    assert taken == n_long_tokens, "n_long_tokens must count the tokens of the entries this kernel takes"
+    return out
+
+
+def attention_prefill_tc(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_long_tokens, n_heads, n_kv_heads,
+                         head_dim, scale, window, out, min_len):
+    page_size = cache_layer.shape[3]
+    assert page_size & (page_size - 1) == 0 and page_size >= 4, "the tcgen05 attention takes power-of-two pages"
+    return attention_prefill(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_long_tokens, n_heads, n_kv_heads,
+                             head_dim, scale, window, out, min_len)
+
+
+def install_bf16(monkeypatch, calls: "dict | None" = None) -> None:
+    """The float32 stand-ins plus those of the bfloat16 path.  ``calls`` (optional) counts how often
+    each attention kernel's stand-in ran."""
+    from pyre_b200.kernels import ops
+
+    install(monkeypatch)
+
+    def counted(name, fn):
+        def wrapper(*a, **k):
+            if calls is not None:
+                calls[name] = calls.get(name, 0) + 1
+            return fn(*a, **k)
+        return wrapper
+
+    for name, fn in dict(add_rmsnorm=add_rmsnorm_any, qkv_rope_write=qkv_rope_write_any, materialize=materialize,
+                         gemm_tc=gemm_tc, silu_mul=silu_mul_any).items():
+        monkeypatch.setattr(ops, name, fn)
+    for name, fn in dict(paged_attention_mma=paged_attention_mma, attention_prefill=attention_prefill,
+                         attention_prefill_tc=attention_prefill_tc).items():
+        monkeypatch.setattr(ops, name, counted(name, fn))

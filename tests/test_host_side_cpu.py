@@ -162,3 +162,73 @@ def test_greedy_generation_through_the_engine_loop(models, monkeypatch, lookahea
     cache.check()
     assert not cache.live() and cache.stats().pages_free == cache.stats().pages_total
     assert len(eng.step_log) == eng.scheduler.stats.steps
+
+
+# --------------------------------------------------------------------------- the bfloat16 path's host side
+TINY_D = dict(architectures=["Qwen2ForCausalLM"], hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=300, rope_theta=10000.0,
+              rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=512)
+
+
+def bf16_runtime(model_dir, max_tokens, page_size):
+    from pyre_b200.config import architecture_of, load_config
+    from pyre_b200.engine.replay import runtime_for_model
+    from pyre_b200.models import Model
+
+    cfg = load_config(model_dir)
+    model = Model(architecture_of(cfg).build(cfg), torch.bfloat16, "cpu")
+    model.load_weights(model_dir)
+    return (model, *runtime_for_model(model, max_tokens, page_size, poison=True, cuda_graphs=False))
+
+
+@pytest.mark.parametrize("page_size", [16, 24])
+def test_bfloat16_dispatch_of_a_mixed_step(tmp_path, monkeypatch, page_size):
+    """Head size 64: entries of 64 tokens or more go to the prompt-portion attention (the tcgen05 kernel with
+    power-of-two pages, else the mma.sync one from 32 tokens on), the rest of the same step to the split-KV
+    kernel; split-K partial sums reach the norm and the rotary kernel; the gated feed-forward's rows are
+    interleaved.  With stand-ins that write only what each kernel takes, logits stay within the error of
+    bfloat16 arithmetic of the plain implementation."""
+    from pyre_b200.engine import replay as rp
+
+    calls = {}
+    standins.install_bf16(monkeypatch, calls)
+    H.make_model_dir(tmp_path, TINY_D, seed=77)
+    reqs = {"a": H.random_ids(300, 150, seed=1), "b": H.random_ids(300, 90, seed=2), "c": H.random_ids(300, 50, seed=3)}
+    a, b, c = reqs["a"], reqs["b"], reqs["c"]
+
+    def entry(rid, toks):
+        return {"id": rid, "tokens": toks, "want": list(range(len(toks)))}
+
+    steps = [
+        {"step": 0, "entries": [entry("a", a[:70])], "end": []},                                   # one long entry
+        {"step": 1, "entries": [entry("a", a[70:71]), entry("b", b[:66]), entry("c", c[:5])], "end": []},   # decode + long + short
+        {"step": 2, "entries": [entry("a", a[71:72]), entry("b", b[66:67]), entry("c", c[5:6])], "end": []},  # decode only
+        {"step": 3, "entries": [entry("c", c[6:46]), entry("a", a[72:150])], "end": ["a"]},        # 40 tokens and 78 tokens
+        {"step": 4, "entries": [entry("b", b[67:90]), entry("c", c[46:50])], "end": ["b", "c"]},
+    ]
+    model, cache, stepper = bf16_runtime(tmp_path, 512, page_size)
+    assert model.blocks[0].ffn.interleaved
+    with tempfile.TemporaryDirectory() as out:
+        rp.replay(stepper, [json.dumps(s) for s in steps], Path(out), done=lambda m: None)
+        got = H.collect_trace_logits(steps, lambda n: np.fromfile(Path(out) / f"{n}.f32", dtype="<f4").reshape(-1, 300))
+    cache.check()
+    assert not cache.live()
+    layers = TINY_D["num_hidden_layers"]
+    if page_size == 16:
+        assert calls.get("attention_prefill_tc") == 3 * layers and "attention_prefill" not in calls    # steps 0, 1, 3
+        assert calls["paged_attention_mma"] == 4 * layers                                          # steps 1-4
+    else:
+        assert calls.get("attention_prefill") == 3 * layers and "attention_prefill_tc" not in calls    # 40 tokens count as long here
+        assert calls["paged_attention_mma"] == 3 * layers                                          # steps 1, 2, 4
+    sq_e = sq_r = cnt = 0.0
+    for rid, ids in reqs.items():
+        truth = H.plain_logits(tmp_path, ids, bf16_weights=True)
+        e, r = got[rid] - truth, H.plain_logits_in_bf16(tmp_path, ids) - truth
+        assert np.isfinite(got[rid]).all()
+        sq_e, sq_r, cnt = sq_e + float((e.astype(np.float64) ** 2).sum()), sq_r + float((r.astype(np.float64) ** 2).sum()), cnt + e.size
+    rms_e, rms_r = (sq_e / cnt) ** 0.5, (sq_r / cnt) ** 0.5
+    assert rms_e <= rms_r, f"rms error {rms_e:.3e} exceeds the {rms_r:.3e} of plain bfloat16 arithmetic"
+    for rid, ids in reqs.items():
+        e = np.abs(got[rid] - H.plain_logits(tmp_path, ids, bf16_weights=True))
+        bad = np.where(e.max(axis=1) > 8 * rms_r)[0]
+        assert not len(bad), f"{rid}: first wrong token at position {int(bad[0])}, error {e[bad[0]].max():.3e} (rms {rms_r:.3e})"
