@@ -165,7 +165,7 @@ def test_greedy_generation_through_the_engine_loop(models, monkeypatch, lookahea
 
 
 # --------------------------------------------------------------------------- the bfloat16 path's host side
-TINY_D = dict(architectures=["Qwen2ForCausalLM"], hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+TINY_D = dict(architectures=["Qwen2ForCausalLM"], hidden_size=512, intermediate_size=640, num_hidden_layers=2,
               num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=300, rope_theta=10000.0,
               rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=512)
 
