@@ -10,6 +10,7 @@ borrows one from another package in its server only, pyre/server/app.py:54-68).
 
 from __future__ import annotations
 
+import dataclasses
 import time
 from dataclasses import dataclass
 from pathlib import Path
@@ -43,12 +44,11 @@ class Engine:
         Keyword ``overrides`` set fields of ``EngineConfig`` (``dtype="float32"``, ...)."""
         if not torch.cuda.is_available():
             raise RuntimeError("pyre_b200 needs a CUDA device (sm_100a); there is no CPU path")
-        ec = engine_config or EngineConfig()
-        for k, v in overrides.items():
-            if not hasattr(ec, k):
-                raise TypeError(f"unknown engine option {k!r}")
-            setattr(ec, k, v)
-        ec.__post_init__()
+        unknown = [k for k in overrides if k not in EngineConfig.__dataclass_fields__]
+        if unknown:
+            raise TypeError(f"unknown engine option {unknown[0]!r}")
+        # a copy: the caller's configuration object is not changed by the overrides
+        ec = dataclasses.replace(engine_config or EngineConfig(), **overrides)
         self.engine_config = ec
         if (model is None) == (config is None):
             raise ValueError("give either a model folder or config= with seed=")

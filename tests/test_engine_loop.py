@@ -153,3 +153,20 @@ def test_a_raised_error_word_is_reported_when_the_step_is_read(monkeypatch):
     eng.step()                                   # reads the first step (clean), starts the second (copies the word)
     with pytest.raises(RuntimeError, match="gave up"):
         eng.step()                               # reads the second step: the word it carries is reported
+
+
+def test_engine_options_are_checked_and_the_caller_s_configuration_is_left_alone(monkeypatch):
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)      # everything below ends before a device is touched
+    ec = EngineConfig(dtype="float32")
+    with pytest.raises(TypeError, match="unknown engine option 'pages'"):
+        Engine("somewhere", ec, pages=3)
+    with pytest.raises(ValueError, match="cache_memory_fraction"):
+        Engine("somewhere", ec, cache_memory_fraction=1.5)
+    with pytest.raises(ValueError, match="either a model folder or config"):
+        Engine(None, ec, page_size=8)
+    with pytest.raises(FileNotFoundError):
+        Engine("/nonexistent/model/folder", ec, page_size=8, dtype="bfloat16")
+    assert ec.page_size == 16 and ec.cache_memory_fraction is None and ec.dtype is torch.float32
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: False)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        Engine("somewhere")
