@@ -5,8 +5,6 @@ the split-K tensor-core products run.  The tiny configurations never reach those
 The oracle is the plain implementation in fp32; it runs on the GPU here (it is plain torch
 either way) because a CPU would need minutes for these widths."""
 
-import json
-
 import numpy as np
 import pytest
 import torch

@@ -3,7 +3,6 @@ orders of requests; windows give pages back; state slots."""
 
 from dataclasses import dataclass
 
-import numpy as np
 import pytest
 import torch
 from hypothesis import given, settings, strategies as st

@@ -13,7 +13,6 @@ import torch
 
 from pyre_b200.cache import CacheManager
 from pyre_b200.config import EngineConfig
-from pyre_b200.engine import engine as engine_module
 from pyre_b200.engine.engine import Engine
 from pyre_b200.engine.scheduler import Scheduler
 from pyre_b200.parts import PagedKVSpec

@@ -1,8 +1,6 @@
 """Each kernel alone against a plain fp32 statement of the same operation, at sizes other
 than the engine's."""
 
-import math
-
 import numpy as np
 import pytest
 import torch

@@ -7,7 +7,6 @@ stepper is built without a device (no error word, no pinned staging); ``build_co
 import random
 import types
 
-import numpy as np
 import pytest
 import torch
 
