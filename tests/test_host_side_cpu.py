@@ -232,3 +232,13 @@ def test_bfloat16_dispatch_of_a_mixed_step(tmp_path, monkeypatch, page_size):
         e = np.abs(got[rid] - H.plain_logits(tmp_path, ids, bf16_weights=True))
         bad = np.where(e.max(axis=1) > 8 * rms_r)[0]
         assert not len(bad), f"{rid}: first wrong token at position {int(bad[0])}, error {e[bad[0]].max():.3e} (rms {rms_r:.3e})"
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps_on_the_cpu(tmp_path, monkeypatch):
+    """The scenario of ``tests/toy_parts.py`` (a recurrent mixer with state in the cache manager's slots and an
+    architecture of its own, registered from the test) with the stand-ins: the package's files need no change
+    for it, and the state slots, their zeroing and the mixed steps work without a GPU too."""
+    import toy_parts
+
+    standins.install(monkeypatch)
+    toy_parts.toy_decay_model_scenario(tmp_path, "cpu")
