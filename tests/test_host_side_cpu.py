@@ -242,3 +242,12 @@ def test_toy_mixer_with_state_registers_builds_and_steps_on_the_cpu(tmp_path, mo
 
     standins.install(monkeypatch)
     toy_parts.toy_decay_model_scenario(tmp_path, "cpu")
+
+
+def test_toy_routed_ffn_and_toy_positions_on_the_cpu(tmp_path, monkeypatch):
+    """The second scenario of ``tests/toy_parts.py``: a routed feed-forward and a position encoding of the
+    test's own beside the package's attention part (which takes the toy positions' tables)."""
+    import toy_parts
+
+    standins.install(monkeypatch)
+    toy_parts.toy_routed_model_scenario(tmp_path, "cpu")

@@ -4,7 +4,6 @@ with a window beside layers without (two cache groups); and a toy mixer with sta
 its own, defined here, registered, built and stepped without any change to the package."""
 
 from dataclasses import dataclass
-from typing import ClassVar
 
 import numpy as np
 import pytest
@@ -238,142 +237,7 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
 
 # --------------------------------------------------------------------------- a toy routed feed-forward and a toy position encoding
 def test_toy_routed_ffn_and_toy_positions_beside_real_attention(tmp_path):
-    """Two more parts that exist only here: a feed-forward that routes every token to the one of
-    three small experts with the largest router logit (fp32 logits), and a position encoding whose
-    angles grow with the square root of the position.  They are registered from this test, put into
-    blocks beside the package's own attention part (which takes the toy positions as its ``position``
-    parameter) and norms, written as a random model, loaded and stepped in portions against a plain
-    evaluation.  No file of the package changes."""
-    from pyre_b200.config import ModelConfig, register_architecture, architecture_of
-    from pyre_b200.engine.replay import runtime_for_model
-    from pyre_b200.engine.step import StepEntry
-    from pyre_b200.kernels import ops
-    from pyre_b200.models import Model, ModelSpec
-    from pyre_b200.parts import Part, PartSpec, register_part
-    from pyre_b200.weights import TensorSpec, write_random_model
-
-    class ToyRoutedFFN(Part):
-        def __init__(self, dtype, device, width, inner, experts):
-            super().__init__(dtype, device)
-            self.width, self.inner, self.experts = width, inner, experts
-
-        def tensors(self):
-            t = {"router.weight": TensorSpec((self.experts, self.width), role="keep", init=("normal", 0.0, 1.0))}
-            for e in range(self.experts):
-                t[f"experts.{e}.up.weight"] = TensorSpec((self.inner, self.width), init=("normal", 0.0, 0.3))
-                t[f"experts.{e}.down.weight"] = TensorSpec((self.width, self.inner), init=("normal", 0.0, 0.3))
-            return t
-
-        def load(self, tensors):
-            self.router = tensors["router.weight"].float()
-            self.up = [tensors[f"experts.{e}.up.weight"].float() for e in range(self.experts)]
-            self.down = [tensors[f"experts.{e}.down.weight"].float() for e in range(self.experts)]
-
-        def forward(self, ctx, h):
-            x = h.float()
-            choice = (x @ self.router.t()).argmax(dim=-1)            # router logits in fp32
-            out = torch.zeros_like(x)
-            for e in range(self.experts):
-                rows = (choice == e).nonzero().flatten()
-                if rows.numel():
-                    out[rows] = torch.relu(x[rows] @ self.up[e].t()) @ self.down[e].t()
-            return out.to(self.dtype)
-
-    class ToySqrtPositions(Part):
-        """cos/sin of sqrt(position) * inv_freq, in the layout the rotary kernels take."""
-        def __init__(self, dtype, device, head_dim, theta):
-            super().__init__(dtype, device)
-            self.rotary_dim = head_dim
-            self.inv_freq = (1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))).to(self.device)
-
-        def kernel_libraries(self):
-            return ["elementwise"]
-
-        def tables(self, ctx):
-            key = ("toy_sqrt", self.rotary_dim)
-            if key not in ctx.scratch:
-                ang = ctx.positions.float().sqrt()[:, None] * self.inv_freq[None, :]
-                ctx.scratch[key] = (ang.cos().contiguous(), ang.sin().contiguous())
-            return ctx.scratch[key]
-
-    register_part("ffn", "toy_routed", ToyRoutedFFN, replace=True)
-    register_part("position", "toy_sqrt", ToySqrtPositions, replace=True)
-
-    @dataclass(frozen=True)
-    class ToyConfig(ModelConfig):
-        architecture: ClassVar[str] = "ToyRoutedForCausalLM"
-        width: int = 40
-        layers: int = 2
-        vocab: int = 61
-        heads: int = 5
-        kv_heads: int = 1
-        head_dim: int = 16
-        experts: int = 3
-
-        @classmethod
-        def from_dict(cls, raw):
-            return cls(*(raw[k] for k in ("width", "layers", "vocab", "heads", "kv_heads", "head_dim", "experts")))
-
-    def build_toy(cfg):
-        norm = PartSpec("rms_norm", {"width": cfg.width, "eps": 1e-5})
-        blocks = [PartSpec("prenorm", {
-            "norm1": norm, "norm2": norm,
-            "mixer": PartSpec("attention", {"width": cfg.width, "n_heads": cfg.heads, "n_kv_heads": cfg.kv_heads,
-                                            "head_dim": cfg.head_dim, "qkv_bias": True, "o_bias": False, "window": None,
-                                            "position": PartSpec("toy_sqrt", {"head_dim": cfg.head_dim, "theta": 100.0})}),
-            "ffn": PartSpec("toy_routed", {"width": cfg.width, "inner": 24, "experts": cfg.experts})})
-            for _ in range(cfg.layers)]
-        return ModelSpec(embed=PartSpec("token_embedding", {"vocab": cfg.vocab, "width": cfg.width}), blocks=blocks,
-                         final_norm=norm, head=PartSpec("linear_head", {"vocab": cfg.vocab, "width": cfg.width}),
-                         vocab_size=cfg.vocab, max_positions=4096)
-
-    register_architecture("ToyRoutedForCausalLM", ToyConfig, build_toy, replace=True)
-    cfg = ToyConfig()
-    write_random_model(tmp_path, cfg, seed=3)
-    from safetensors.torch import load_file
-    w = load_file(str(tmp_path / "model.safetensors"))
-    assert "model.layers.1.mlp.experts.2.down.weight" in w and w["model.layers.0.mlp.router.weight"].dtype == torch.float32
-
-    def plain(ids):
-        T = len(ids)
-        x = w["model.embed_tokens.weight"].float()[ids]
-        inv = 1.0 / (100.0 ** (torch.arange(0, cfg.head_dim, 2, dtype=torch.float32) / cfg.head_dim))
-        ang = torch.arange(T, dtype=torch.float32).sqrt()[:, None] * inv[None, :]
-        cos, sin = torch.cat([ang.cos()] * 2, -1), torch.cat([ang.sin()] * 2, -1)
-        rot = lambda v: torch.cat([-v[..., cfg.head_dim // 2:], v[..., :cfg.head_dim // 2]], -1)
-        used = set()
-        for i in range(cfg.layers):
-            p = f"model.layers.{i}."
-            h = qwen2_plain.rms_norm(x, w[p + "input_layernorm.weight"].float(), 1e-5)
-            q = (h @ w[p + "self_attn.q_proj.weight"].float().t() + w[p + "self_attn.q_proj.bias"].float()).view(T, cfg.heads, cfg.head_dim)
-            k = (h @ w[p + "self_attn.k_proj.weight"].float().t() + w[p + "self_attn.k_proj.bias"].float()).view(T, cfg.kv_heads, cfg.head_dim)
-            v = (h @ w[p + "self_attn.v_proj.weight"].float().t() + w[p + "self_attn.v_proj.bias"].float()).view(T, cfg.kv_heads, cfg.head_dim)
-            q, k = q * cos[:, None] + rot(q) * sin[:, None], k * cos[:, None] + rot(k) * sin[:, None]
-            k, v = k.repeat_interleave(cfg.heads // cfg.kv_heads, 1), v.repeat_interleave(cfg.heads // cfg.kv_heads, 1)
-            s = torch.einsum("qhd,khd->hqk", q, k) * cfg.head_dim ** -0.5
-            s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
-            a = torch.einsum("hqk,khd->qhd", s.softmax(-1), v).reshape(T, -1)
-            x = x + a @ w[p + "self_attn.o_proj.weight"].float().t()
-            h = qwen2_plain.rms_norm(x, w[p + "post_attention_layernorm.weight"].float(), 1e-5)
-            choice = (h @ w[p + "mlp.router.weight"].float().t()).argmax(-1)
-            used |= set(choice.tolist())
-            y = torch.stack([torch.relu(h[t] @ w[p + f"mlp.experts.{int(c)}.up.weight"].float().t())
-                             @ w[p + f"mlp.experts.{int(c)}.down.weight"].float().t() for t, c in enumerate(choice)])
-            x = x + y
-        return qwen2_plain.rms_norm(x, w["model.norm.weight"].float(), 1e-5) @ w["lm_head.weight"].float().t(), used
-
-    model = Model(architecture_of(cfg).build(cfg), torch.float32, "cuda")
-    assert len(model.kv_groups) == 1 and model.state_groups == []
-    model.load_weights(tmp_path)
-    cache, stepper = runtime_for_model(model, 64, 16, max_requests=2)
-    a, b = H.random_ids(cfg.vocab, 37, seed=5), H.random_ids(cfg.vocab, 11, seed=6)
-    cache.begin("a"); cache.begin("b")
-    got_a = [stepper.step([StepEntry("a", a[:18], list(range(18)))])]
-    both = stepper.step([StepEntry("b", b, list(range(11))), StepEntry("a", a[18:20], [0, 1])])
-    got_b, got_a = both[:11], got_a + [both[11:]]
-    got_a.append(stepper.step([StepEntry("a", a[20:], list(range(17)))]))
-    want_a, used = plain(a)
-    want_b, _ = plain(b)
-    assert len(used) >= 2                                              # the router really routes
-    torch.testing.assert_close(torch.cat(got_a).cpu(), want_a, rtol=2e-4, atol=2e-5)
-    torch.testing.assert_close(got_b.cpu(), want_b, rtol=2e-4, atol=2e-5)
+    """A toy routed feed-forward and a toy position encoding (``tests/toy_parts.py``) in blocks beside the
+    package's own attention part, stepped in portions on the device against a plain evaluation."""
+    import toy_parts
+    toy_parts.toy_routed_model_scenario(tmp_path, "cuda")
