@@ -1,0 +1,55 @@
+"""The ctypes signatures against the C prototypes they bind (no GPU, no compiler needed): every function
+of ``kernels/lib.py`` is exported by the source file of the library it names, with the same number of
+arguments and the same kind of each (pointer, int, long long, float).  A drift between the two would not
+fail to load: it would pass garbage to a kernel."""
+
+import re
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+from pyre_b200.kernels import build, lib
+
+KIND = {c_void_p: "pointer", c_int: "int", c_longlong: "long long", c_float: "float"}
+
+
+def prototypes(source: str) -> dict:
+    """name -> list of argument kinds, for every ``PYRE_API <type> name(args)`` of a source file."""
+    text = re.sub(r"//[^\n]*", "", (build.CSRC / source).read_text())
+    out = {}
+    for m in re.finditer(r"PYRE_API\s+[\w ]+?\s+(\w+)\s*\(([^)]*)\)", text):
+        kinds = []
+        for arg in (a.strip() for a in m.group(2).split(",")):
+            if not arg or arg == "void":
+                continue
+            if "*" in arg or re.match(r"(const\s+)?cudaStream_t\b", arg):
+                kinds.append("pointer")
+            elif re.match(r"(const\s+)?long long\b", arg):
+                kinds.append("long long")
+            elif re.match(r"(const\s+)?float\b", arg):
+                kinds.append("float")
+            elif re.match(r"(const\s+)?int\b", arg):
+                kinds.append("int")
+            else:
+                raise AssertionError(f"{source}: {m.group(1)} has an argument this test cannot classify: {arg!r}")
+        out[m.group(1)] = kinds
+    return out
+
+
+def test_every_bound_function_matches_its_prototype():
+    by_library = {name: prototypes(source) for name, source in build.LIBRARIES.items()}
+    for fn, (library, argtypes) in lib.SIGNATURES.items():
+        assert library in by_library, f"{fn} names the unknown library {library!r}"
+        assert fn in by_library[library], f"{fn} is not exported by {build.LIBRARIES[library]}"
+        want = by_library[library][fn]
+        got = [KIND[t] for t in argtypes]
+        assert got == want, f"{fn}: bound as {got}, declared as {want}"
+
+
+def test_every_exported_launcher_is_bound_or_known():
+    """An exported function that nothing binds is dead or forgotten; the few that are called by other means
+    (the allocation-free attention entry and the size queries, through ctypes directly) are named here."""
+    bound = set(lib.SIGNATURES)
+    other = {"pyre_attention_mma_scratch_floats", "pyre_paged_attention_mma_noalloc",
+             "pyre_paged_attention_mma_noalloc_capacity"}
+    for name, source in build.LIBRARIES.items():
+        for fn in prototypes(source):
+            assert fn in bound or fn in other, f"{source} exports {fn}, which kernels/lib.py does not bind"
