@@ -53,3 +53,26 @@ def test_every_exported_launcher_is_bound_or_known():
     for name, source in build.LIBRARIES.items():
         for fn in prototypes(source):
             assert fn in bound or fn in other, f"{source} exports {fn}, which kernels/lib.py does not bind"
+
+
+def test_every_call_site_passes_as_many_arguments_as_the_signature_has():
+    """``lib.call("name", ...)`` in the package: the count of arguments at each call site (none of them starred)
+    equals the signature's, and every name called is a bound one."""
+    import ast
+    from pathlib import Path
+
+    import pyre_b200
+
+    seen = set()
+    for path in Path(pyre_b200.__file__).parent.rglob("*.py"):
+        for node in ast.walk(ast.parse(path.read_text())):
+            if not (isinstance(node, ast.Call) and isinstance(node.func, ast.Attribute) and node.func.attr in ("call", "call_value")
+                    and isinstance(node.func.value, ast.Name) and node.func.value.id == "lib"):
+                continue
+            name = node.args[0]
+            assert isinstance(name, ast.Constant) and name.value in lib.SIGNATURES, f"{path}:{node.lineno}: unknown function"
+            assert not any(isinstance(a, ast.Starred) for a in node.args) and not node.keywords, f"{path}:{node.lineno}"
+            want = len(lib.SIGNATURES[name.value][1])
+            assert len(node.args) - 1 == want, f"{path}:{node.lineno}: {name.value} takes {want} arguments, {len(node.args) - 1} given"
+            seen.add(name.value)
+    assert seen == set(lib.SIGNATURES), f"bound but never called: {sorted(set(lib.SIGNATURES) - seen)}"
