@@ -11,7 +11,7 @@ from .sampling import SamplingParams
 __version__ = "0.1.0"
 
 __all__ = ["Engine", "EngineConfig", "ModelConfig", "Qwen2Config", "RequestOutput", "SamplingParams",
-           "load_config", "register_architecture"]
+           "load_config", "load_model", "register_architecture"]
 
 
 def __getattr__(name):
@@ -19,4 +19,7 @@ def __getattr__(name):
     if name in ("Engine", "RequestOutput"):
         from .engine import engine as _engine
         return getattr(_engine, name)
+    if name == "load_model":
+        from .models.model import load_model
+        return load_model
     raise AttributeError(name)

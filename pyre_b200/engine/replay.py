@@ -26,9 +26,7 @@ from pathlib import Path
 import torch
 
 from ..cache import CacheManager
-from ..config import load_config, architecture_of, parse_dtype
-from ..kernels import build
-from ..models.model import Model
+from ..models.model import Model, load_model
 from .step import StepEntry, Stepper
 
 DEFAULT_PAGE_SIZE = 16
@@ -40,12 +38,7 @@ def build_runtime(model_dir, dtype, max_tokens: int, page_size: int = DEFAULT_PA
     """Model, cache manager and stepper for a model folder: the pieces every entry point shares."""
     if not torch.cuda.is_available():
         raise RuntimeError("pyre_b200 needs a CUDA device (sm_100a); there is no CPU path")
-    dtype = parse_dtype(dtype)
-    config = load_config(model_dir)
-    spec = architecture_of(config).build(config)
-    model = Model(spec, dtype, device)
-    build.ensure_built(model.kernel_libraries())
-    model.load_weights(model_dir)
+    model, _config = load_model(model_dir, device, dtype)
     cache, stepper = runtime_for_model(model, max_tokens, page_size, max_requests, poison)
     return model, cache, stepper
 

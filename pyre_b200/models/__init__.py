@@ -1,4 +1,4 @@
-from .model import KVGroup, Model, StateGroup, tensor_table
+from .model import KVGroup, Model, StateGroup, load_model, tensor_table
 from .spec import LayerCall, ModelSpec
 
-__all__ = ["KVGroup", "LayerCall", "Model", "ModelSpec", "StateGroup", "tensor_table"]
+__all__ = ["KVGroup", "LayerCall", "Model", "ModelSpec", "StateGroup", "load_model", "tensor_table"]

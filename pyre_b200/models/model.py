@@ -154,3 +154,18 @@ class Model:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
         h = self.final_norm.forward(ctx, x, delta=pending, rows=ctx.logit_rows)
         return self.head.forward(ctx, h)
+
+
+def load_model(model_dir: "str | Path", device: str = "cuda:0", dtype="bfloat16"):
+    """A model folder (config.json + safetensors) -> (model with its weights on ``device``, its configuration):
+    the reference's ``load_model(path, device, dtype)`` (pyre/loader.py:33-79).  The model class comes from
+    the registry by the configuration's architecture name, and the kernel libraries this model and dtype
+    need are built if they are not there yet."""
+    from ..config import architecture_of, load_config, parse_dtype
+    from ..kernels import build
+
+    config = load_config(model_dir)
+    model = Model(architecture_of(config).build(config), parse_dtype(dtype), device)
+    build.ensure_built(model.kernel_libraries())
+    model.load_weights(model_dir)
+    return model, config

@@ -251,3 +251,30 @@ def test_toy_routed_ffn_and_toy_positions_on_the_cpu(tmp_path, monkeypatch):
 
     standins.install(monkeypatch)
     toy_parts.toy_routed_model_scenario(tmp_path, "cpu")
+
+
+def test_trace_run_program_and_load_model_on_the_cpu(models, tmp_path, monkeypatch, capsys):
+    """``trace_run``'s own main (arguments, the model through ``load_model`` and the registry, steps from
+    standard input, a ``done`` line per step, the .f32 files) with the stand-ins and ``--device cpu``."""
+    import io
+    import sys
+
+    import pyre_b200
+    from pyre_b200.engine import replay as rp
+
+    standins.install(monkeypatch)
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    d, reqs, want = models["A"]
+    model, cfg = pyre_b200.load_model(d, device="cpu", dtype="float32")
+    assert type(cfg).__name__ == "Qwen2Config" and cfg.hidden_size == 64 and model.loaded and model.dtype is torch.float32
+    ids = reqs["A2"]
+    steps = H.trace_portions("A2", ids, [9, 2, 16]) + [{"step": 99, "entries": [], "end": []}]
+    monkeypatch.setattr(sys, "stdin", io.StringIO("".join(json.dumps(s) + "\n" for s in steps) + "\n"))
+    out = tmp_path / "logits"
+    assert rp.main(["--model", str(d), "--dtype", "float32", "--out", str(out), "--max-tokens", "64", "--device", "cpu"]) == 0
+    assert capsys.readouterr().out.split("\n")[:-1] == [f"done {s['step']}" for s in steps]
+    got = H.collect_trace_logits(steps, lambda n: np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, 512))
+    compare(got, {"A2": want["A2"]}, "trace_run main")
+    assert not (out / "99.f32").exists()                       # nothing wanted, nothing written
+    with pytest.raises(SystemExit):
+        rp.main(["--model", str(d), "--dtype", "float32", "--out", str(out), "--max-tokens", "64", "--page-size", "24"])
