@@ -54,27 +54,55 @@ def runtime_for_model(model: Model, max_tokens: int, page_size: int = DEFAULT_PA
     return cache, stepper
 
 
+class TraceError(ValueError):
+    """A line of the trace that cannot be run: not JSON, a field missing or of the wrong kind, a request
+    ended that is not live, a wanted place outside the entry's tokens, no pages left."""
+
+
+def _parse_step(line: str, number: int):
+    try:
+        rec = json.loads(line)
+    except json.JSONDecodeError as e:
+        raise TraceError(f"line {number}: not JSON ({e.msg} at column {e.colno})") from None
+    if not isinstance(rec, dict) or "step" not in rec:
+        raise TraceError(f"line {number}: a step is an object with a \"step\" field")
+    entries = rec.get("entries", [])
+    end = rec.get("end", [])
+    if not isinstance(entries, list) or not isinstance(end, list):
+        raise TraceError(f"line {number} (step {rec['step']}): \"entries\" and \"end\" are lists")
+    for e in entries:
+        if not isinstance(e, dict) or "id" not in e or not isinstance(e.get("tokens"), list) \
+                or not isinstance(e.get("want", []), list):
+            raise TraceError(f"line {number} (step {rec['step']}): an entry is an object with \"id\", a list "
+                             f"\"tokens\" and an optional list \"want\"")
+        if not all(isinstance(t, int) and not isinstance(t, bool) for t in list(e["tokens"]) + list(e.get("want", []))):
+            raise TraceError(f"line {number} (step {rec['step']}): tokens and wanted places are integers")
+    return rec["step"], entries, end
+
+
 def replay(stepper: Stepper, lines, out_dir: Path, done=print) -> None:
     cache = stepper.cache
     out_dir.mkdir(parents=True, exist_ok=True)
-    for line in lines:
+    for number, line in enumerate(lines, 1):
         line = line.strip()
         if not line:
             continue
-        rec = json.loads(line)
-        step = rec["step"]
-        entries = []
-        for e in rec.get("entries", []):
-            rid = e["id"]
-            if rid not in cache.lengths:
-                cache.begin(rid)
-            entries.append(StepEntry(rid, e["tokens"], e.get("want", [])))
-        if entries:
-            logits = stepper.step(entries)
-            if logits.shape[0]:
-                logits.to("cpu").numpy().astype("<f4", copy=False).tofile(out_dir / f"{step}.f32")
-        for rid in rec.get("end", []):
-            cache.end(rid)
+        step, raw_entries, end = _parse_step(line, number)
+        try:
+            entries = []
+            for e in raw_entries:
+                rid = e["id"]
+                if rid not in cache.lengths:
+                    cache.begin(rid)
+                entries.append(StepEntry(rid, e["tokens"], e.get("want", [])))
+            if entries:
+                logits = stepper.step(entries)
+                if logits.shape[0]:
+                    logits.to("cpu").numpy().astype("<f4", copy=False).tofile(out_dir / f"{step}.f32")
+            for rid in end:
+                cache.end(rid)
+        except (ValueError, MemoryError) as e:     # the stepper's and the cache manager's refusals
+            raise TraceError(f"line {number} (step {step}): {e}") from e
         done(f"done {step}")
     torch.cuda.synchronize()
     stepper.check_device_errors()
@@ -101,5 +129,9 @@ def main(argv=None) -> int:
         sys.stdout.write(msg + "\n")
         sys.stdout.flush()
 
-    replay(stepper, sys.stdin, Path(args.out), done)
+    try:
+        replay(stepper, sys.stdin, Path(args.out), done)
+    except TraceError as e:
+        print(f"trace_run: {e}", file=sys.stderr)
+        return 1
     return 0

@@ -278,3 +278,29 @@ def test_trace_run_program_and_load_model_on_the_cpu(models, tmp_path, monkeypat
     assert not (out / "99.f32").exists()                       # nothing wanted, nothing written
     with pytest.raises(SystemExit):
         rp.main(["--model", str(d), "--dtype", "float32", "--out", str(out), "--max-tokens", "64", "--page-size", "24"])
+
+
+def test_a_trace_that_cannot_be_run_ends_with_one_clear_line(models, tmp_path, monkeypatch, capsys):
+    import io
+    import sys
+
+    from pyre_b200.engine import replay as rp
+
+    standins.install(monkeypatch)
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    d, _, _ = models["A"]
+    good = json.dumps({"step": 0, "entries": [{"id": "a", "tokens": [1, 2, 3], "want": [2]}], "end": []})
+    cases = [('{"step": 1, "entries": [', "line 2: not JSON"),
+             ('[1, 2]', 'line 2: a step is an object with a "step" field'),
+             ('{"step": 1, "entries": [{"id": "a", "tokens": "5"}]}', "line 2 (step 1): an entry is an object"),
+             ('{"step": 1, "entries": [{"id": "a", "tokens": [1.5]}]}', "line 2 (step 1): tokens and wanted places are integers"),
+             ('{"step": 1, "entries": [{"id": "a", "tokens": [4], "want": [1]}]}', "line 2 (step 1): request 'a': wanted place 1"),
+             ('{"step": 1, "entries": [{"id": "a", "tokens": [512]}]}', "line 2 (step 1): request 'a': token id outside"),
+             ('{"step": 1, "entries": [], "end": ["b"]}', "line 2 (step 1): request 'b' is not live"),
+             ('{"step": 1, "entries": [{"id": "b", "tokens": ' + str(list(range(100))) + '}]}', "line 2 (step 1): request 'b': no pages left")]
+    for bad, message in cases:
+        monkeypatch.setattr(sys, "stdin", io.StringIO(good + "\n" + bad + "\n"))
+        rc = rp.main(["--model", str(d), "--dtype", "float32", "--out", str(tmp_path / "o"), "--max-tokens", "64", "--device", "cpu"])
+        captured = capsys.readouterr()
+        assert rc == 1 and captured.out == "done 0\n", bad
+        assert captured.err.strip().startswith("trace_run: " + message), (captured.err, message)
