@@ -78,7 +78,8 @@ class Engine:
         self.sampler = Sampler(ec.device)
         self._requests: dict[int, Request] = {}
         self._flight = None      # (plan, sampling ticket, error word) of the step whose ids have not been read yet
-        self._err_host = [torch.zeros(1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        pinned = self.model.device.type == "cuda"
+        self._err_host = [torch.zeros(1, dtype=torch.int32, pin_memory=pinned) for _ in range(2)]
         self._err_turn = 0
         self.step_log: "list[dict] | None" = [] if ec.record_steps else None
 

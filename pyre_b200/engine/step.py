@@ -127,7 +127,7 @@ class Stepper:
         from ..kernels import ops
         self.error_flag = ops.device_error_flag(self.device)   # one flag per device, raised by any kernel
         self.steps_run = 0
-        self.cuda_graphs = bool(cuda_graphs) and model.graph_safe
+        self.cuda_graphs = bool(cuda_graphs) and model.graph_safe and torch.device(self.device).type == "cuda"
         self._graphs: dict[tuple, _DecodeGraph] = {}
         self._graph_pool = None
         self.graph_replays = 0

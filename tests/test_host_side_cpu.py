@@ -304,3 +304,38 @@ def test_a_trace_that_cannot_be_run_ends_with_one_clear_line(models, tmp_path, m
         captured = capsys.readouterr()
         assert rc == 1 and captured.out == "done 0\n", bad
         assert captured.err.strip().startswith("trace_run: " + message), (captured.err, message)
+
+
+def test_command_line_generates_and_writes_its_result_and_step_log(models, tmp_path, monkeypatch, capsys):
+    """``python -m pyre_b200 generate`` end to end on the CPU: the real ``Engine`` constructor, scheduler and loop
+    (kernels and sampler stood in for, ``--device cpu``), token ids on standard output, ``--out`` and ``--step-log``."""
+    import contextlib
+
+    from pyre_b200 import cli
+    from pyre_b200.sampling import Sampler
+    from plain import qwen2_plain
+
+    standins.install(monkeypatch)
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    monkeypatch.setattr(torch.cuda, "device", lambda device: contextlib.nullcontext())
+    monkeypatch.setattr(Sampler, "sample_async", HostSampler.sample_async)
+    monkeypatch.setattr(Sampler, "read", HostSampler.read)
+    d, reqs, _ = models["A"]
+    prompts = [reqs["A0"], reqs["A1"]]
+    (tmp_path / "prompts.txt").write_text(" ".join(map(str, prompts[1])) + "\n")
+    rc = cli.main(["generate", "--model", str(d), "--device", "cpu", "--dtype", "float32", "--max-new-tokens", "6",
+                   "--prompt-ids", ",".join(map(str, prompts[0])), "--prompt-ids-file", str(tmp_path / "prompts.txt"),
+                   "--num-pages", "12", "--page-size", "8", "--prefill-chunk", "8", "--max-batched-tokens", "16",
+                   "--out", str(tmp_path / "result.json"), "--step-log", str(tmp_path / "steps.jsonl")])
+    assert rc == 0
+    w = H.load_plain_weights(d)
+    want = [qwen2_plain.greedy_generate(p, w, H.TINY["A"], 6) for p in prompts]
+    printed = [[int(t) for t in line.split()] for line in capsys.readouterr().out.strip().split("\n")]
+    assert printed == want
+    result = json.loads((tmp_path / "result.json").read_text())
+    assert [o["token_ids"] for o in result["outputs"]] == want and result["new_tokens"] == 12
+    assert [o["finish_reason"] for o in result["outputs"]] == ["length", "length"] and result["stats"]["finished"] == 2
+    log = [json.loads(line) for line in (tmp_path / "steps.jsonl").read_text().splitlines()]
+    assert len(log) == result["stats"]["steps"] and sum(r["tokens"] for r in log) == result["stats"]["scheduled_tokens"]
+    assert log[0]["prompt_tokens"] == log[0]["tokens"] and log[-1]["decoded_tokens"] >= 1
+    assert cli.main(["generate", "--model", str(d), "--device", "cpu"]) == 2          # no prompts
