@@ -339,3 +339,49 @@ def test_command_line_generates_and_writes_its_result_and_step_log(models, tmp_p
     assert len(log) == result["stats"]["steps"] and sum(r["tokens"] for r in log) == result["stats"]["scheduled_tokens"]
     assert log[0]["prompt_tokens"] == log[0]["tokens"] and log[-1]["decoded_tokens"] >= 1
     assert cli.main(["generate", "--model", str(d), "--device", "cpu"]) == 2          # no prompts
+
+
+def test_temperature_sampling_is_per_request_whatever_the_batch(models, monkeypatch):
+    """The engine hands the sampler each row's own parameters and the index of the token being drawn (tokens
+    still in flight included), so a request's draw depends on its seed and its own history only: together,
+    alone, with or without a step in flight, with preemption, the ids are those of the plain sampler run on
+    the plain logits."""
+    import contextlib
+    import types
+
+    from pyre_b200 import Engine, SamplingParams
+    from pyre_b200.sampling import Sampler
+    from plain import qwen2_plain
+
+    def sample_async(self, logits, params, token_index):
+        ids = [qwen2_plain.sample(row, p.temperature, p.seed, k) for row, p, k in zip(logits, params, token_index)]
+        return types.SimpleNamespace(ids=torch.tensor(ids, dtype=torch.int32))
+
+    standins.install(monkeypatch)
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    monkeypatch.setattr(torch.cuda, "device", lambda device: contextlib.nullcontext())
+    monkeypatch.setattr(Sampler, "sample_async", sample_async)
+    monkeypatch.setattr(Sampler, "read", HostSampler.read)
+    d, reqs, _ = models["B"]
+    raw, w = H.TINY["B"], H.load_plain_weights(d)
+    prompts = [reqs["B1"], reqs["B2"], reqs["B0"]]
+    params = [SamplingParams(temperature=0.8, seed=5, max_new_tokens=7), SamplingParams(temperature=0.0, max_new_tokens=5),
+              SamplingParams(temperature=1.3, seed=6, max_new_tokens=8)]
+
+    def plain_ids(prompt, p):
+        ids = list(prompt)
+        for k in range(p.max_new_tokens):
+            with torch.inference_mode():
+                ids.append(qwen2_plain.sample(qwen2_plain.forward(ids, w, raw)[-1], p.temperature, p.seed, k))
+        return ids[len(prompt):]
+
+    want = [plain_ids(p, sp) for p, sp in zip(prompts, params)]
+    kw = dict(device="cpu", dtype="float32", page_size=8, prefill_chunk=16, max_num_batched_tokens=24)
+    for lookahead, num_pages in ((True, 64), (False, 64), (True, 7)):
+        eng = Engine(d, lookahead=lookahead, num_pages=num_pages, admit_whole_prompts=False, **kw)
+        outs = eng.generate(prompts, params)
+        assert [o.token_ids for o in outs] == want, (lookahead, num_pages)
+        if num_pages == 7:
+            assert eng.stats()["preempted"] > 0
+    alone = Engine(d, num_pages=64, **kw)
+    assert [alone.generate([p], sp)[0].token_ids for p, sp in zip(prompts, params)] == want
