@@ -50,6 +50,7 @@ class PagedGroup:
         self.allocator = PageAllocator(num_pages)
         self.tables: dict[Hashable, list[int]] = {}      # logical page -> physical page, -1 once given back
         self.first_live: dict[Hashable, int] = {}        # first logical page not yet given back
+        self._rows: dict[Hashable, np.ndarray] = {}      # tables as arrays, dropped whenever a table changes
         # one page beyond the allocator's range belongs to no request: the rows that pad a captured step to a
         # common size write their token there and read it back
         self.scratch_page = num_pages
@@ -72,9 +73,20 @@ class PagedGroup:
     def pages_missing(self, req, new_len: int) -> int:
         return max(0, pages_for(new_len, self.page_size) - len(self.tables[req]))
 
+    def take(self, req, n_pages: int) -> None:
+        self.tables[req].extend(self.allocator.allocate_many(n_pages))
+        self._rows.pop(req, None)
+
     def grow(self, req, new_len: int) -> None:
-        table = self.tables[req]
-        table.extend(self.allocator.allocate_many(self.pages_missing(req, new_len)))
+        self.take(req, self.pages_missing(req, new_len))
+
+    def row(self, req) -> np.ndarray:
+        """The request's block table as an int32 array; kept until the table changes (a page taken or
+        given back), which in decoding happens once in ``page_size`` steps."""
+        r = self._rows.get(req)
+        if r is None:
+            r = self._rows[req] = np.asarray(self.tables[req], dtype=np.int32)
+        return r
 
     def release_passed(self, req, length: int) -> list[int]:
         """Give back the pages that no token at position >= length will read."""
@@ -88,6 +100,7 @@ class PagedGroup:
                 if self.allocator.free(table[lp]):
                     freed.append(table[lp])
                 table[lp] = -1
+                self._rows.pop(req, None)
         self.first_live[req] = max(self.first_live[req], keep_from)
         self._poison(freed)
         return freed
@@ -98,6 +111,7 @@ class PagedGroup:
             if page >= 0 and self.allocator.free(page):
                 freed.append(page)
         self.first_live.pop(req)
+        self._rows.pop(req, None)
         self._poison(freed)
         return freed
 
@@ -190,11 +204,16 @@ class CacheManager:
         """Make room for the request to grow to ``new_len`` tokens; all groups or none."""
         if new_len < self.lengths[req]:
             raise ValueError(f"request {req!r} holds {self.lengths[req]} tokens; cannot shrink to {new_len}")
-        if not self.can_reserve(req, new_len):
-            return False
-        for g in self.groups:
-            g.grow(req, new_len)
-        self.reserved[req] = max(self.reserved[req], new_len)
+        groups = self.groups
+        missing = [g.pages_missing(req, new_len) for g in groups]     # mostly zeros: a page lasts page_size tokens
+        for g, m in zip(groups, missing):
+            if m > g.allocator.num_free:
+                return False
+        for g, m in zip(groups, missing):
+            if m:
+                g.take(req, m)
+        if new_len > self.reserved[req]:
+            self.reserved[req] = new_len
         return True
 
     def commit(self, req, new_len: int) -> None:
@@ -228,12 +247,12 @@ class CacheManager:
     # ------------------------------------------------------------------ views for a step
     def block_table_rows(self, group: int, reqs: Sequence, width: int | None = None) -> np.ndarray:
         g = self.groups[group]
+        rows = [g.row(r) for r in reqs]
         if width is None:
-            width = max((len(g.tables[r]) for r in reqs), default=0)
+            width = max((r.shape[0] for r in rows), default=0)
         out = np.full((len(reqs), max(width, 1)), -1, dtype=np.int32)
-        for i, r in enumerate(reqs):
-            t = g.tables[r]
-            out[i, :len(t)] = t
+        for i, r in enumerate(rows):
+            out[i, :r.shape[0]] = r
         return out
 
     def slots_for(self, group: int, req, start: int, count: int) -> np.ndarray:
@@ -262,5 +281,8 @@ class CacheManager:
             for p, n in held.items():
                 if g.allocator.ref_count(p) != n:
                     raise AssertionError(f"page {p}: held by {n} tables, ref count {g.allocator.ref_count(p)}")
+            for r, row in g._rows.items():
+                if row.tolist() != g.tables[r]:
+                    raise AssertionError(f"request {r!r}: the cached row of its block table is stale")
             if len(held) != g.allocator.num_used:
                 raise AssertionError(f"{g.allocator.num_used} pages in use but {len(held)} are in block tables")

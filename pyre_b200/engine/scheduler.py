@@ -70,7 +70,13 @@ class Request:
         return self.prompt_ids[i] if i < n else self.generated[i - n]
 
     def tokens(self, start: int, count: int) -> list[int]:
-        return [self.token_at(i) for i in range(start, start + count)]
+        """A new list of the tokens at positions start .. start + count - 1 (prompt, then generated)."""
+        n, end = len(self.prompt_ids), start + count
+        if end <= n:
+            return self.prompt_ids[start:end]
+        if start >= n:
+            return self.generated[start - n:end - n]
+        return self.prompt_ids[start:] + self.generated[:end - n]
 
 
 @dataclass
@@ -187,12 +193,20 @@ class Scheduler:
             budget -= count
             return True
 
+        decoding, in_prompt = [], []
+        for r in self.running:
+            if not r.closed:
+                left = r.cur_len - r.num_computed
+                if left == 1:
+                    decoding.append(r)
+                elif left > 1:
+                    in_prompt.append(r)
         # 1. requests that are decoding (one token each), oldest first
-        for r in [r for r in self.running if r.cur_len - r.num_computed == 1 and not r.closed]:
+        for r in decoding:
             if r.status == RUNNING and budget > 0:
                 try_schedule(r)
-        # 2. requests in the middle of their prompt (or of a recompute)
-        for r in [r for r in self.running if r.cur_len - r.num_computed > 1 and not r.closed]:
+        # 2. requests in the middle of their prompt (or of a recompute); one that step 1 preempted is no longer running
+        for r in in_prompt:
             if r.status == RUNNING and budget > 0 and r.seq_id not in planned:
                 try_schedule(r)
         for r in aborted:

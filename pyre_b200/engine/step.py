@@ -157,16 +157,21 @@ class Stepper:
                 raise ValueError(f"request {e.request!r} appears twice in one step")
             seen.add(e.request)
             n = len(e.tokens)
-            if n == 0:
+            if n == 1:      # a decoded token: the common case by far
+                if not 0 <= e.tokens[0] < vocab:
+                    raise ValueError(f"request {e.request!r}: token id outside [0, {vocab})")
+                tok_list.append(e.tokens[0])
+            elif n == 0:
                 raise ValueError(f"request {e.request!r}: an entry needs at least one token")
-            if n <= 8:      # a decoded token or a tiny portion: plain integers are cheaper than an array
-                if min(e.tokens) < 0 or max(e.tokens) >= vocab:
-                    raise ValueError(f"request {e.request!r}: token id outside [0, {vocab})")
             else:
-                toks = np.asarray(e.tokens)
-                if toks.min() < 0 or toks.max() >= vocab:
+                if n <= 8:      # a tiny portion: plain integers are cheaper than an array
+                    lo, hi = min(e.tokens), max(e.tokens)
+                else:
+                    toks = np.asarray(e.tokens)
+                    lo, hi = toks.min(), toks.max()
+                if lo < 0 or hi >= vocab:
                     raise ValueError(f"request {e.request!r}: token id outside [0, {vocab})")
-            tok_list.extend(e.tokens)
+                tok_list.extend(e.tokens)
             for w in e.want:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.request!r}: wanted place {w} outside its {n} tokens")
