@@ -172,6 +172,10 @@ def test_random_steps_write_every_position_once(seed):
         if entries:
             ctx, _ = context(st, entries, reserve=False)
             for g, group in enumerate(cache.groups):
+                table = ctx.kv_group(g).block_table.tolist()
+                for b, e in enumerate(entries):                      # the rows are the tables as they stand now
+                    held = group.tables[e.request]
+                    assert table[b][:len(held)] == held and all(p == -1 for p in table[b][len(held):])
                 slots = ctx.kv_group(g).slot_mapping.tolist()
                 pos = ctx.positions.tolist()
                 seq = ctx.seq_of_token.tolist()
