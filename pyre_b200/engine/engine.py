@@ -16,6 +16,7 @@ from dataclasses import dataclass
 from pathlib import Path
 from typing import Sequence
 
+import numpy as np
 import torch
 
 from ..cache import CacheManager
@@ -34,6 +35,7 @@ class RequestOutput:
     token_ids: list[int]
     finish_reason: str
     preemptions: int = 0
+    logits: "np.ndarray | None" = None     # [len(token_ids), vocab] fp32, with SamplingParams.return_logits
 
 
 class Engine:
@@ -144,6 +146,12 @@ class Engine:
                 self._err_turn ^= 1
                 err.copy_(self.stepper.error_flag, non_blocking=True)
                 sampling = [s for s in plan if s.samples]
+                keep = [k for k, s in enumerate(sampling) if s.request.params.return_logits]
+                if keep:
+                    # only requests that ask for their logits pay for this copy (and for the wait it brings)
+                    rows = logits[keep].to("cpu").numpy()
+                    for k, row in zip(keep, rows):
+                        sampling[k].request.logits[len(sampling[k].request.generated)] = row
                 ticket = self.sampler.sample_async(logits, [s.request.params for s in sampling],
                                                    [len(s.request.generated) for s in sampling]) if sampling else None
             sched.launched(plan)
@@ -160,7 +168,11 @@ class Engine:
         outs = []
         for sid in [sid for sid, r in self._requests.items() if r.done and not r.pending]:
             r = self._requests.pop(sid)
-            outs.append(RequestOutput(r.seq_id, r.prompt_ids, list(r.generated), r.finish_reason or "", r.preemptions))
+            kept = None
+            if r.params.return_logits:      # a token computed beyond an end-of-sequence token was dropped, and so are its logits
+                kept = np.stack([r.logits[k] for k in range(len(r.generated))]) if r.generated else \
+                    np.empty((0, self.model.vocab_size), dtype=np.float32)
+            outs.append(RequestOutput(r.seq_id, r.prompt_ids, list(r.generated), r.finish_reason or "", r.preemptions, kept))
         return outs
 
     def _land(self, flight) -> None:

@@ -56,6 +56,7 @@ class Request:
     pending: int = 0               # steps in flight that will deliver a token of this request
     closed: bool = False           # the tokens in flight complete it by length: nothing more is asked for
     feed_row: int = -1             # row of its newest pending token among the ids of the step in flight
+    logits: dict = field(default_factory=dict)   # index of a generated token -> the logits it was chosen from (if asked for)
 
     @property
     def cur_len(self) -> int:

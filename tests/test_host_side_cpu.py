@@ -385,3 +385,41 @@ def test_temperature_sampling_is_per_request_whatever_the_batch(models, monkeypa
             assert eng.stats()["preempted"] > 0
     alone = Engine(d, num_pages=64, **kw)
     assert [alone.generate([p], sp)[0].token_ids for p, sp in zip(prompts, params)] == want
+
+
+@pytest.mark.parametrize("lookahead", [True, False])
+def test_logits_come_back_with_the_tokens_when_asked_for(models, monkeypatch, lookahead):
+    """``SamplingParams.return_logits``: one row per generated token, the logits it was chosen from (the plain
+    logits at that position), also for a request that stops at its end-of-sequence token (whose overshoot is
+    dropped) and for one that was preempted and recomputed; a request that does not ask gets none."""
+    import contextlib
+
+    from pyre_b200 import Engine, SamplingParams
+    from pyre_b200.sampling import Sampler
+    from plain import qwen2_plain
+
+    standins.install(monkeypatch)
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    monkeypatch.setattr(torch.cuda, "device", lambda device: contextlib.nullcontext())
+    monkeypatch.setattr(Sampler, "sample_async", HostSampler.sample_async)
+    monkeypatch.setattr(Sampler, "read", HostSampler.read)
+    d, reqs, _ = models["B"]
+    raw, w = H.TINY["B"], H.load_plain_weights(d)
+    prompts = [reqs["B1"], reqs["B2"], reqs["B0"]]
+    greedy = [qwen2_plain.greedy_generate(p, w, raw, 8) for p in prompts]
+    params = [SamplingParams(max_new_tokens=8, return_logits=True),
+              SamplingParams(max_new_tokens=8, return_logits=True, eos_id=greedy[1][3]),      # stops at its fourth token at the latest
+              SamplingParams(max_new_tokens=8)]
+    eng = Engine(d, device="cpu", dtype="float32", page_size=8, num_pages=8, prefill_chunk=16, max_num_batched_tokens=24,
+                 lookahead=lookahead, admit_whole_prompts=False)
+    outs = eng.generate(prompts, params)
+    assert eng.stats()["preempted"] > 0
+    assert outs[2].logits is None and outs[2].token_ids == greedy[2]
+    stop = greedy[1].index(greedy[1][3]) + 1
+    assert outs[1].token_ids == greedy[1][:stop] and outs[1].finish_reason == "eos" and outs[0].token_ids == greedy[0]
+    for p, o in zip(prompts[:2], outs[:2]):
+        with torch.inference_mode():
+            want = qwen2_plain.forward(list(p) + o.token_ids[:-1], w, raw)[len(p) - 1:].numpy()
+        assert o.logits.shape == (len(o.token_ids), raw["vocab_size"]) and o.logits.dtype == np.float32
+        np.testing.assert_allclose(o.logits, want, rtol=2e-4, atol=2e-5)
+        assert o.logits.argmax(axis=1).tolist() == o.token_ids
