@@ -154,8 +154,11 @@ def test_random_orders_keep_every_page_accounted(data):
         elif op == "end" and live:
             r = data.draw(st.sampled_from(sorted(live)))
             m.end(r); del live[r]
+        rows = m.block_table_rows(0, sorted(live))                   # rows are kept as arrays between changes: check() compares
         m.check()
         g = m.groups[0]
+        for i, r in enumerate(sorted(live)):
+            assert rows[i, :len(g.tables[r])].tolist() == g.tables[r]
         for r, n in live.items():
             if window is None:
                 assert g.pages_held(r) == max(pages_for(n, m.page_size), len([p for p in g.tables[r] if p >= 0]))
