@@ -423,3 +423,42 @@ def test_logits_come_back_with_the_tokens_when_asked_for(models, monkeypatch, lo
         assert o.logits.shape == (len(o.token_ids), raw["vocab_size"]) and o.logits.dtype == np.float32
         np.testing.assert_allclose(o.logits, want, rtol=2e-4, atol=2e-5)
         assert o.logits.argmax(axis=1).tolist() == o.token_ids
+
+
+def test_replay_answers_each_line_before_the_next_one_is_written(models, monkeypatch):
+    """The next step of a trace may come only after ``done <step>``: the loop must answer a line as soon as it
+    has it, without waiting for more input.  Lines go through a pipe one at a time; each answer is awaited."""
+    import os
+    import queue
+    import threading
+
+    from pyre_b200.engine import replay as rp
+
+    standins.install(monkeypatch)
+    d, reqs, want = models["A"]
+    _, cache, stepper = runtime(d, 128, 16)
+    steps = H.trace_portions("A1", reqs["A1"], [4, 2, 5])
+    r_fd, w_fd = os.pipe()
+    answers: "queue.Queue[str]" = queue.Queue()
+    failure = []
+
+    def loop(out):
+        try:
+            with os.fdopen(r_fd, "r") as lines:
+                rp.replay(stepper, lines, Path(out), done=answers.put)
+        except Exception as e:          # handed to the main thread
+            failure.append(e)
+            answers.put("failed")
+
+    with tempfile.TemporaryDirectory() as out:
+        t = threading.Thread(target=loop, args=(out,), daemon=True)
+        t.start()
+        with os.fdopen(w_fd, "w") as pipe:
+            for s in steps:
+                pipe.write(json.dumps(s) + "\n")
+                pipe.flush()
+                assert answers.get(timeout=60) == f"done {s['step']}", failure
+        t.join(timeout=60)
+        assert not t.is_alive() and not failure
+        got = H.collect_trace_logits(steps, lambda n: np.fromfile(Path(out) / f"{n}.f32", dtype="<f4").reshape(-1, 512))
+    compare(got, {"A1": want["A1"]}, "line by line through a pipe")
