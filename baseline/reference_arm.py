@@ -59,7 +59,7 @@ def _write_model_folder(folder: Path, cfg_raw: dict, seed: int) -> None:
         save_file(shard, str(folder / f"model-{n:05d}.safetensors"))
 
 
-def run(args, cfg_raw: dict, prompt_len: int) -> dict:
+def run(args, cfg_raw: dict, prompt_len: int, config_block: "dict | None" = None) -> dict:
     if not (REF / "pyre" / "scheduler.py").is_file():
         return unavailable("baseline/_ref is empty: the reference is not installed on this machine")
     try:
@@ -114,9 +114,10 @@ def run(args, cfg_raw: dict, prompt_len: int) -> dict:
         "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(decode_s / K * 1e3, 3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"model": "Qwen2.5-7B-shaped, random weights", "layers": cfg_raw["num_hidden_layers"],
-                   "layers_full": layers_full, "global_batch": B, "prompt_len": prompt_len, "page_size": 16,
-                   "timing": "wall clock around Scheduler.run(), (t_total - t_ttft) as in the reference's harness"},
+        # the same keys and values as the other arm prints; how this arm is timed stands beside it
+        "config": config_block or {"model": "Qwen2.5-7B-shaped, random weights", "layers": cfg_raw["num_hidden_layers"],
+                                   "layers_full": layers_full, "global_batch": B, "prompt_len": prompt_len, "page_size": 16},
+        "timing": "wall clock around Scheduler.run(), (t_total - t_ttft) as in the reference's harness",
         "e2e": {"value": round(value, 2), "unit": "tokens/s", "note": "the reference's run() is host tokens in, host tokens out"},
         "prefill": {"value": round(prompt_len / t_one, 1), "tokens": prompt_len, "ms": round(t_one * 1e3, 1)},
     }

@@ -37,7 +37,7 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# BASELINE.json configs[2]: the Qwen2.5-7B shape
+# the headline configuration: the Qwen2.5-7B shape
 CONFIG_7B = dict(architectures=["Qwen2ForCausalLM"], hidden_size=3584, intermediate_size=18944,
                  num_hidden_layers=28, num_attention_heads=28, num_key_value_heads=4, head_dim=128,
                  vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
@@ -105,6 +105,17 @@ class ClockSampler:
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None,
                 "sm_max_mhz": int(rows[0][1]) if rows[0][1].isdigit() else None, "reasons": reasons,
                 "samples": len(rows)}
+
+
+def bench_config(cfg_raw: dict, layers: int, layers_full: int, batch: int) -> dict:
+    """The ``config`` block of the bench line: every size of the measured model and workload, flat.
+    Both arms (this engine and the reference) print the same keys with the same values."""
+    return {"model": "Qwen2.5-7B-shaped, random weights", "layers": layers, "layers_full": layers_full,
+            "hidden": cfg_raw["hidden_size"], "heads": cfg_raw["num_attention_heads"],
+            "kv_heads": cfg_raw["num_key_value_heads"], "head_dim": cfg_raw["head_dim"],
+            "intermediate": cfg_raw["intermediate_size"], "vocab": cfg_raw["vocab_size"],
+            "global_batch": batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": PAGE_SIZE,
+            "parallelism": "single GPU", "l2": "inputs larger than L2 (15 GB of weights per step)"}
 
 
 def model_numbers(cfg: dict, layers: int):
@@ -254,18 +265,14 @@ def run_ours(args) -> dict:
         "metric": "decode tok/s (Qwen2.5-7B shape, batch 8, 2,048-token prompts)", "value": round(value, 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"model": "Qwen2.5-7B-shaped, random weights", "layers": layers, "layers_full": layers_full,
-                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
-                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-                   "global_batch": B, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": PAGE_SIZE,
-                   "parallelism": "single GPU", "l2": "inputs larger than L2 (15 GB of weights per step)"},
+        "config": bench_config(cfg_raw, layers, layers_full, B),
         "clocks": clock_summary, "e2e": e2e, "gpu_launches": info["launches"], "prefill": prefill,
         "roofline": roofline, "points": points, "impl": "ours",
     }
 
 
 SHAPES = {
-    # BASELINE.json configs[3] and configs[4]
+    # the two further workloads: continuous batching at the 14B shape, mixed steps at the 32B shape
     "14b": dict(architectures=["Qwen2ForCausalLM"], hidden_size=5120, intermediate_size=13824, num_hidden_layers=48,
                 num_attention_heads=40, num_key_value_heads=8, head_dim=128, vocab_size=152064, rope_theta=1e6,
                 rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=32768),
@@ -454,7 +461,9 @@ def environment() -> dict:
 
 def run_reference(args) -> dict:
     from baseline import reference_arm
-    return reference_arm.run(args, CONFIG_7B, PROMPT_LEN)
+    layers = args.layers or CONFIG_7B["num_hidden_layers"]
+    return reference_arm.run(args, CONFIG_7B, PROMPT_LEN,
+                             bench_config(CONFIG_7B, layers, CONFIG_7B["num_hidden_layers"], args.batch))
 
 
 def main() -> int:

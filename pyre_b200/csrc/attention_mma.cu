@@ -687,7 +687,8 @@ template <int HD>
 int launch(const CUtensorMap& map, const AttnParams& p, int n_groups_bound, bool use_cluster, cudaStream_t stream) {
     dim3 grid(n_groups_bound, p.nkv * p.head_blocks, p.n_splits);
     constexpr int SMEM = WARPS * STAGES * 2 * TILE * HD * 2 + 1024;   // per warp: the stages of a K and a V tile; alignment slack
-    static bool configured = false;
+    static bool configured_on[PYRE_MAX_DEVICES] = {};      // the attributes are per device
+    bool& configured = configured_on[pyre_current_device()];
     if (!configured) {   // more than 48 KB of dynamic shared memory and clusters of more than 8 CTAs are opt-ins
         cudaError_t e = cudaFuncSetAttribute(paged_attention_mma_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(paged_attention_mma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);

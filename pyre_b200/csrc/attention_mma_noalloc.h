@@ -34,8 +34,18 @@
  * different streams without an ordering between them) race on the array and corrupt
  * each other's results; order them on one stream or with events.
  *
+ * Threads.  The table of resolved addresses is filled without a lock.  Two host threads
+ * that make their first call on one device at the same time both look the address up and
+ * store the same value, which is harmless; no other host state is shared.
+ *
  * The entry point calls no cudaMalloc, cudaFree or other allocating routine.
- * Arguments and result are those of pyre_paged_attention_mma() without `scratch`:
+ * Arguments: those of pyre_paged_attention_mma() without `scratch` (built in), and without
+ * `max_len`, `n_pages`, `uniform_len` and `err_flag`, which are passed as 0 / null: every
+ * entry of the batch is served whatever its length, and, because no page count is given, no
+ * tensor map over the pages is built, so keys and values always travel by cp.async copies
+ * (the other entry point moves them by TMA when the page size is a power of two and the head
+ * size a multiple of 64).  The result is the same bit for bit; long contexts are somewhat
+ * slower than through pyre_paged_attention_mma().
  * bfloat16 q [T, nh, hd], one layer of the paged cache [page][2][nkv][page_size][hd],
  * bfloat16 out [T, nh * hd], int32 block_table [n_seqs, bt_stride], cu_seqlens
  * [n_seqs + 1], positions [T].  Returns 0, a cudaError_t value, or a PYRE_ERR_* code.

@@ -283,7 +283,8 @@ __global__ void __launch_bounds__(WARPS * 32, 3) attention_prefill_kernel(const 
 template <int HD>
 int launch(const PrefillParams& p, int tiles_bound, cudaStream_t stream) {
     constexpr int SMEM = 2 * 2 * BN * HD * 2;
-    static bool configured = false;
+    static bool configured_on[PYRE_MAX_DEVICES] = {};      // the attributes are per device
+    bool& configured = configured_on[pyre_current_device()];
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;

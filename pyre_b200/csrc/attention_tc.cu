@@ -535,7 +535,8 @@ bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols,
 template <int HD>
 int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const TcParams& p, int tiles_bound, cudaStream_t stream) {
     using L = Smem<HD>;
-    static bool configured = false;
+    static bool configured_on[PYRE_MAX_DEVICES] = {};      // the attributes are per device
+    bool& configured = configured_on[pyre_current_device()];
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) return (int)e;

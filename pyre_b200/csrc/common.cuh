@@ -139,5 +139,25 @@ static inline cudaError_t pyre_launch(void (*kernel)(KArgs...), dim3 grid, dim3 
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// Per-device host state.  Function attributes (dynamic shared memory, cluster size) and the multiprocessor
+// count belong to a device, not to the process: they are kept by the index of the device that is current at
+// the call.  Written without a lock: two host threads that race here write the same values.
+constexpr int PYRE_MAX_DEVICES = 64;
+static inline int pyre_current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= PYRE_MAX_DEVICES) dev = 0;
+    return dev;
+}
+static inline int pyre_sm_count() {
+    static int count[PYRE_MAX_DEVICES] = {};
+    const int dev = pyre_current_device();
+    if (!count[dev]) {
+        int n = 0;
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        count[dev] = n > 0 ? n : 148;
+    }
+    return count[dev];
+}
+
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 static inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }

@@ -156,7 +156,7 @@ __global__ void add_residual_kernel(float* __restrict__ x, const T* __restrict__
 PYRE_API int pyre_add_residual(float* x, const void* delta, long long n, int dtype, cudaStream_t stream) {
     if (n <= 0) return 0;
     const int threads = 256;
-    const int blocks = (int)min((long long)148 * 8, ceil_div_ll(n, threads));
+    const int blocks = (int)min((long long)pyre_sm_count() * 8, ceil_div_ll(n, threads));
     if (dtype == PYRE_F32) pyre_launch(add_residual_kernel<float>, dim3(blocks), dim3(threads), 0, stream, x, (const float*)delta, (size_t)n);
     else if (dtype == PYRE_BF16) pyre_launch(add_residual_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, x, (const __nv_bfloat16*)delta, (size_t)n);
     else return PYRE_ERR_BAD_ARG;
@@ -441,7 +441,7 @@ PYRE_API int pyre_silu_mul(const void* gu, void* out, int n_tokens, int I, int b
 #define LAUNCH(TT, V)                                                                                      \
     do {                                                                                                   \
         long long total = (long long)n_tokens * (I / V);                                                   \
-        int blocks = (int)min((long long)148 * 16, ceil_div_ll(total, threads));                           \
+        int blocks = (int)min((long long)pyre_sm_count() * 16, ceil_div_ll(total, threads));                           \
         pyre_launch(silu_mul_kernel<TT, V>, dim3(blocks), dim3(threads), 0, stream, (const TT*)gu, (TT*)out, n_tokens, I, block);      \
     } while (0)
     if (dtype == PYRE_F32) { if (I % 4 == 0) LAUNCH(float, 4); else LAUNCH(float, 1); }
@@ -473,7 +473,7 @@ PYRE_API int pyre_sum_partials(const float* partials, int n_splits, long long sp
     if (n <= 0) return 0;
     if (n_splits < 1) return PYRE_ERR_BAD_ARG;
     const int threads = 256;
-    const int blocks = (int)min((long long)148 * 8, ceil_div_ll(n, threads));
+    const int blocks = (int)min((long long)pyre_sm_count() * 8, ceil_div_ll(n, threads));
     if (dtype == PYRE_F32) pyre_launch(sum_partials_kernel<float>, dim3(blocks), dim3(threads), 0, stream, partials, n_splits, split_stride, (float*)out, n);
     else if (dtype == PYRE_BF16) pyre_launch(sum_partials_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, partials, n_splits, split_stride, (__nv_bfloat16*)out, n);
     else return PYRE_ERR_BAD_ARG;

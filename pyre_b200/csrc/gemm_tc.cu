@@ -601,7 +601,8 @@ template <int BN, int STAGES, bool XC, int CTAS = 1>
 int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES, XC, CTAS>;
     static_assert(L::TOTAL <= 232448, "the ring does not fit into shared memory");
-    static bool configured = false;
+    static bool configured_on[PYRE_MAX_DEVICES] = {};      // the attributes are per device
+    bool& configured = configured_on[pyre_current_device()];
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, XC, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) return (int)e;
@@ -675,8 +676,7 @@ PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* 
     p.tiles_x = ceil_div(x_rows, pair ? 2 * BM : BM); p.tiles_y = ceil_div(y_rows, bn);
     const long long n_tiles = (long long)p.tiles_x * p.tiles_y;
     // one CTA per SM stays resident and walks the tiles (a split K keeps one CTA per tile and split)
-    static int sm_count = 0;
-    if (!sm_count) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev); if (sm_count <= 0) sm_count = 148; }
+    const int sm_count = pyre_sm_count();
     long long ctas = splits > 1 ? n_tiles : (n_tiles < sm_count ? n_tiles : sm_count);
     if (xc && splits == 1 && n_tiles > sm_count) {
         // A weight stream (few tokens) is bound by memory: what counts is that no round of the persistent CTAs

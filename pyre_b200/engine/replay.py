@@ -31,6 +31,19 @@ from .step import StepEntry, Stepper
 
 DEFAULT_PAGE_SIZE = 16
 MAX_LIVE_REQUESTS = 64
+TOKEN_QUANTUM = 64      # --max-tokens counts each live request rounded up to a multiple of this (or of the page size)
+
+
+def pages_for_max_tokens(max_tokens: int, page_size: int, max_requests: int = MAX_LIVE_REQUESTS) -> int:
+    """Pages that hold live requests of ``max_tokens`` tokens in all, each request's count rounded up to a
+    multiple of 64 (or of the page size, if that is larger).  When the page size divides that quantum the
+    answer is exact.  Otherwise (pages of 24 or 48 tokens, say) every request but one may need one page more
+    than its share of the sum, so that many pages are added."""
+    quantum = max(TOKEN_QUANTUM, page_size)
+    pages = max(1, -(-int(max_tokens) // page_size))
+    if quantum % page_size:
+        pages += max(0, min(max_requests, int(max_tokens) // quantum) - 1)
+    return pages
 
 
 def build_runtime(model_dir, dtype, max_tokens: int, page_size: int = DEFAULT_PAGE_SIZE,
@@ -46,7 +59,7 @@ def build_runtime(model_dir, dtype, max_tokens: int, page_size: int = DEFAULT_PA
 def runtime_for_model(model: Model, max_tokens: int, page_size: int = DEFAULT_PAGE_SIZE,
                       max_requests: int = MAX_LIVE_REQUESTS, poison: bool = False, cuda_graphs: bool = True):
     """Cache manager and stepper for a model that already has its weights."""
-    num_pages = max(1, -(-int(max_tokens) // page_size))
+    num_pages = pages_for_max_tokens(max_tokens, page_size, max_requests)
     cache = CacheManager(model.kv_groups, model.state_groups, page_size, num_pages, max_requests, model.dtype,
                          model.device)
     cache.set_poison(poison)
@@ -104,7 +117,8 @@ def replay(stepper: Stepper, lines, out_dir: Path, done=print) -> None:
         except (ValueError, MemoryError) as e:     # the stepper's and the cache manager's refusals
             raise TraceError(f"line {number} (step {step}): {e}") from e
         done(f"done {step}")
-    torch.cuda.synchronize()
+    if torch.device(stepper.device).type == "cuda":
+        torch.cuda.synchronize(stepper.device)
     stepper.check_device_errors()
 
 
@@ -115,13 +129,13 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder for the <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
-    ap.add_argument("--page-size", type=int, default=DEFAULT_PAGE_SIZE, help="tokens per cache page (divides 64)")
+    ap.add_argument("--page-size", type=int, default=DEFAULT_PAGE_SIZE, help="tokens per cache page (any size the engine takes)")
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--poison-freed-pages", action="store_true",
                     help="debug: fill pages with NaN when they go back to the pool")
     args = ap.parse_args(argv)
-    if 64 % args.page_size:
-        ap.error("--page-size must divide 64")
+    if args.page_size <= 0:
+        ap.error("--page-size must be positive")
     _, _, stepper = build_runtime(args.model, args.dtype, args.max_tokens, args.page_size, args.device,
                                   poison=args.poison_freed_pages)
 

@@ -10,6 +10,7 @@ two disjoint functions instead: one sequence with any number of tokens
 
 from __future__ import annotations
 
+import contextlib
 import time
 
 from dataclasses import dataclass, field
@@ -28,6 +29,14 @@ from .context import KVView, StateView, StepContext
 # The model's ``max_position_embeddings`` is not enforced here: the reference parses it and never
 # uses it (pyre/config.py:60), and rotary angles are computed from the position itself.
 MAX_EXACT_POSITION = 1 << 24
+
+
+def device_guard(device):
+    """Makes ``device`` the current CUDA device for a block of code.  Kernels are launched on the
+    current device's stream and tensor maps are encoded in its context, so everything that launches
+    for a model runs under this guard, whichever device was current when the caller came in."""
+    device = torch.device(device)
+    return torch.cuda.device(device) if device.type == "cuda" else contextlib.nullcontext()
 
 
 @dataclass
@@ -292,8 +301,9 @@ class Stepper:
             ops.feed_tokens(ctx.token_ids, ctx.feed_dst, ctx.feed_src, fed_from)
 
     def run_context(self, ctx: StepContext, fed_from: "torch.Tensor | None" = None) -> torch.Tensor:
-        self._feed(ctx, ctx.entries, fed_from)
-        logits = self.model.forward(ctx)
+        with device_guard(self.device):
+            self._feed(ctx, ctx.entries, fed_from)
+            logits = self.model.forward(ctx)
         for e, new_len in zip(ctx.entries, ctx.new_lens):
             self.cache.commit(e.request, new_len)
         self.steps_run += 1
@@ -304,9 +314,10 @@ class Stepper:
         order of the entries and of each entry's ``want``.  The tensor is valid until the
         next step (a replayed graph writes its logits to the same memory every time).
         ``fed_from``: the int32 ids that the step before sampled, for entries with ``feed``."""
-        if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            return self._graph_step(entries, reserve, fed_from)
-        return self.run_context(self.build_context(entries, reserve), fed_from)
+        with device_guard(self.device):
+            if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+                return self._graph_step(entries, reserve, fed_from)
+            return self.run_context(self.build_context(entries, reserve), fed_from)
 
     # ------------------------------------------------------------------ captured decode steps
     def _graph_step(self, entries: Sequence[StepEntry], reserve: bool, fed_from: "torch.Tensor | None" = None) -> torch.Tensor:
@@ -373,4 +384,5 @@ class Stepper:
     def check_device_errors(self) -> None:
         """Raise if a kernel of an earlier step raised the device's error flag (synchronises)."""
         from ..kernels import ops
-        ops.check_device_errors(self.device)
+        with device_guard(self.device):
+            ops.check_device_errors(self.device)

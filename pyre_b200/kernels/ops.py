@@ -54,7 +54,19 @@ def materialize(t: "torch.Tensor | PartialSums") -> torch.Tensor:
 
 
 def _stream() -> int:
+    """The current stream of the current device.  Kernels are launched in the current device's
+    context, so the tensors of a call must live there (``_check`` refuses others)."""
     return torch.cuda.current_stream().cuda_stream
+
+
+def require_current_device(device, what: str = "a tensor") -> None:
+    """Raise on the host if ``device`` (a CUDA device) is not the current one.  A kernel launched
+    on another device's stream with this device's pointers would fault on the GPU instead."""
+    current = torch.cuda.current_device()
+    index = device.index if device.index is not None else current
+    if index != current:
+        raise ValueError(f"{what} is on cuda:{index} but the current device is cuda:{current}; "
+                         f"enter torch.cuda.device({index}) around the call")
 
 
 def _ptr(t: "torch.Tensor | None") -> "int | None":
@@ -64,6 +76,7 @@ def _ptr(t: "torch.Tensor | None") -> "int | None":
 def _check(t: torch.Tensor, name: str, dtype=None, dim: "int | None" = None) -> None:
     if not t.is_cuda:
         raise ValueError(f"{name} must be a CUDA tensor (pyre_b200 has no CPU path)")
+    require_current_device(t.device, name)
     if not t.is_contiguous():
         raise ValueError(f"{name} must be contiguous, got strides {t.stride()} for shape {tuple(t.shape)}")
     if dtype is not None and t.dtype != dtype:
@@ -285,7 +298,20 @@ def paged_attention_generic(q: torch.Tensor, cache_layer: torch.Tensor, block_ta
 
 MMA_MAX_HEAD_DIM = 128
 CLUSTER_MAX_SPLITS = 16      # splits of one group merge through a thread-block cluster up to this many
-_SM_COUNT = 148
+_DEFAULT_SM_COUNT = 148     # a B200; used only where no device can be asked (planning on a host without a GPU)
+_sm_counts: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Multiprocessors of ``device`` (default: the current one), as the launch code asks the device
+    too; the planners below size splits and rounds of tiles by it."""
+    if not torch.cuda.is_available():
+        return _DEFAULT_SM_COUNT
+    index = torch.cuda.current_device() if device is None or torch.device(device).index is None else torch.device(device).index
+    n = _sm_counts.get(index)
+    if n is None:
+        n = _sm_counts[index] = int(torch.cuda.get_device_properties(index).multi_processor_count) or _DEFAULT_SM_COUNT
+    return n
 
 
 def attention_splits(n_tokens: int, n_seqs: int, n_heads: int, n_kv_heads: int, max_context: int,
@@ -294,6 +320,7 @@ def attention_splits(n_tokens: int, n_seqs: int, n_heads: int, n_kv_heads: int, 
     about one and a half per SM, at least two 16-key tiles per split, at most 16 (the
     splits of a group form one thread-block cluster), or 32 through scratch memory for a
     single very long sequence."""
+    _SM_COUNT = sm_count()
     n_rep = n_heads // n_kv_heads
     hpg = min(n_rep, 16)
     tpg = 16 // hpg
@@ -513,6 +540,7 @@ def tc_gemm_plan(M: int, N: int, K: int) -> tuple[bool, int, int]:
     CTA lands on every SM, each split keeping at least four 64-wide K blocks.  Beyond
     that the tokens take the rows and 128 to 256 output features form a tile, whichever
     width fills the rounds of the persistent CTAs best."""
+    _SM_COUNT = sm_count()
     kb = -(-K // 64)
     if M <= 128 or N % 8:
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256

@@ -108,11 +108,12 @@ def trace_portions(rid: str, ids: list[int], sizes: list[int], first_step: int =
     return steps
 
 
-def trace_mixed(reqs: dict[str, list[int]], seed: int, max_live: int = 4, prefill_head: float = 0.6) -> list[dict]:
+def trace_mixed(reqs: dict[str, list[int]], seed: int, max_live: int = 4, prefill_head: float = 0.6,
+                portion: tuple[int, int] = (2, 24)) -> list[dict]:
     """Up to ``max_live`` requests at a time: a request first gets portions of random size
-    (2..24 tokens) for the first part of its tokens, then single tokens, beside whatever
-    the other live requests get in the same step; a finished request is ended and the
-    next one begins, so its pages are used again."""
+    (``portion``: smallest and largest, 2..24 tokens by default) for the first part of its
+    tokens, then single tokens, beside whatever the other live requests get in the same step;
+    a finished request is ended and the next one begins, so its pages are used again."""
     rng = np.random.default_rng(seed)
     waiting = list(reqs.items())
     live: dict[str, dict] = {}
@@ -126,7 +127,7 @@ def trace_mixed(reqs: dict[str, list[int]], seed: int, max_live: int = 4, prefil
             if rng.random() < 0.2 and len(live) > 1:
                 continue  # left out of this step, goes on later
             if st["pos"] < st["head"]:
-                n = int(min(rng.integers(2, 25), st["head"] - st["pos"]))
+                n = int(min(rng.integers(portion[0], portion[1] + 1), st["head"] - st["pos"]))
             else:
                 n = 1
             n = min(n, len(st["ids"]) - st["pos"])

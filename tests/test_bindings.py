@@ -6,6 +6,8 @@ fail to load: it would pass garbage to a kernel."""
 import re
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
+import pytest
+
 from pyre_b200.kernels import build, lib
 
 KIND = {c_void_p: "pointer", c_int: "int", c_longlong: "long long", c_float: "float"}
@@ -76,3 +78,49 @@ def test_every_call_site_passes_as_many_arguments_as_the_signature_has():
             assert len(node.args) - 1 == want, f"{path}:{node.lineno}: {name.value} takes {want} arguments, {len(node.args) - 1} given"
             seen.add(name.value)
     assert seen == set(lib.SIGNATURES), f"bound but never called: {sorted(set(lib.SIGNATURES) - seen)}"
+
+
+def test_a_tensor_on_another_device_is_refused_on_the_host(monkeypatch):
+    """Kernels launch on the current device's stream: a tensor of another device is refused before any launch
+    (it would fault on the GPU), and the stepper makes its model's device current around everything it launches.
+    Stand-ins play the devices here; nothing runs on a GPU."""
+    import torch
+    from pyre_b200.engine import step
+    from pyre_b200.kernels import ops
+
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
+    ops.require_current_device(torch.device("cuda:0"))
+    ops.require_current_device(torch.device("cuda"))          # no index: the current device
+    with pytest.raises(ValueError, match=r"cuda:1 but the current device is cuda:0"):
+        ops.require_current_device(torch.device("cuda:1"), "q")
+
+    class FakeTensor:
+        is_cuda, device, dtype = True, torch.device("cuda:1"), torch.float32
+
+        def is_contiguous(self):
+            return True
+
+        def dim(self):
+            return 2
+
+    with pytest.raises(ValueError, match="x is on cuda:1"):
+        ops._check(FakeTensor(), "x", torch.float32, 2)
+
+    entered = []
+
+    class FakeGuard:
+        def __init__(self, device):
+            self.device = device
+
+        def __enter__(self):
+            entered.append(self.device)
+
+        def __exit__(self, *exc):
+            return False
+
+    monkeypatch.setattr(torch.cuda, "device", FakeGuard)
+    with step.device_guard("cuda:1"):
+        pass
+    with step.device_guard("cpu"):          # the stand-ins' device: nothing to enter
+        pass
+    assert entered == [torch.device("cuda:1")]

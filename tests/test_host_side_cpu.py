@@ -276,8 +276,17 @@ def test_trace_run_program_and_load_model_on_the_cpu(models, tmp_path, monkeypat
     got = H.collect_trace_logits(steps, lambda n: np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, 512))
     compare(got, {"A2": want["A2"]}, "trace_run main")
     assert not (out / "99.f32").exists()                       # nothing wanted, nothing written
+    # any page size the engine takes, also one that does not divide 64
+    monkeypatch.setattr(sys, "stdin", io.StringIO("".join(json.dumps(s) + "\n" for s in steps)))
+    out24 = tmp_path / "logits24"
+    assert rp.main(["--model", str(d), "--dtype", "float32", "--out", str(out24), "--max-tokens", "64", "--device", "cpu",
+                    "--page-size", "24"]) == 0
+    got = H.collect_trace_logits(steps, lambda n: np.fromfile(out24 / f"{n}.f32", dtype="<f4").reshape(-1, 512))
+    compare(got, {"A2": want["A2"]}, "trace_run main, pages of 24 tokens")
     with pytest.raises(SystemExit):
-        rp.main(["--model", str(d), "--dtype", "float32", "--out", str(out), "--max-tokens", "64", "--page-size", "24"])
+        rp.main(["--model", str(d), "--dtype", "float32", "--out", str(out), "--max-tokens", "64", "--page-size", "0"])
+    assert rp.pages_for_max_tokens(256, 16) == 16 and rp.pages_for_max_tokens(256, 128) == 2
+    assert rp.pages_for_max_tokens(256, 24) == 11 + 3          # four requests of 64: three pages each, not 11 in all
 
 
 def test_a_trace_that_cannot_be_run_ends_with_one_clear_line(models, tmp_path, monkeypatch, capsys):

@@ -187,6 +187,54 @@ def test_gemm_tc_matches_fp32_product(ops, M, N, K):
         assert float((got - part.float() @ w.float().t()).abs().max()) <= 2e-5 * scale * max(1.0, (K / 64) ** 0.5) * 2
 
 
+@pytest.mark.parametrize("M", [1, 8, 64, 300])
+def test_output_head_at_the_full_vocabulary(ops, M):
+    """The product that gives the logits at the benchmark model's sizes (152,064 x 3,584): fp32 logits
+    from the accumulator, for decode batches (weights on the MMA's rows, many CTAs in several rounds)
+    and for a prompt portion (tokens on the rows, CTA pairs)."""
+    V, K = 152064, 3584
+    g = torch.Generator(device="cuda").manual_seed(M)
+    a = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = torch.empty(V, K, device="cuda", dtype=torch.bfloat16)
+    for lo in range(0, V, 16384):      # drawn in pieces: an fp32 copy of the whole matrix is 2 GB
+        w[lo:lo + 16384] = (torch.randn(min(16384, V - lo), K, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    got = ops.linear(a, w, out_dtype=torch.float32)
+    ops.check_device_errors()
+    assert got.dtype == torch.float32 and got.shape == (M, V)
+    worst, scale = 0.0, 0.0
+    for lo in range(0, V, 16384):
+        want = a.float() @ w[lo:lo + 16384].float().t()
+        worst = max(worst, float((got[:, lo:lo + 16384] - want).abs().max()))
+        scale = max(scale, float(want.abs().max()))
+    assert worst <= 2e-5 * scale * (K / 64) ** 0.5, f"max error {worst:.3e} at scale {scale:.3f}"
+    # the first and the last vocabulary entries come from the first and the last tile
+    assert torch.isfinite(got[:, 0]).all() and torch.isfinite(got[:, -1]).all()
+
+
+def test_sampling_at_the_full_vocabulary(ops):
+    """Greedy and temperature sampling over 152,064 entries (the two-stage kernel, a last slice that is
+    not full) against the plain sampler; ties across slices go to the lowest index."""
+    from plain import qwen2_plain
+    V = 152064
+    g = torch.Generator(device="cuda").manual_seed(21)
+    logits = torch.randn(8, V, device="cuda", generator=g) * 2
+    logits[3, 152063] = 40.0                          # the very last entry
+    logits[4, 70000] = logits[4, 151000] = 41.0       # a tie far apart
+    want = [int(logits[r].argmax()) for r in range(8)]
+    want[3], want[4] = 152063, 70000
+    assert ops.sample(logits).tolist() == want
+    temps = torch.tensor([0.7, 0.0, 1.0, 0.0, 1.9, 0.3, 1.0, 0.7], device="cuda")
+    seeds = torch.tensor([1, 2, 3, 4, 5, 6, 3, 1], dtype=torch.int64, device="cuda")
+    tix = torch.tensor([0, 1, 2, 3, 4, 5, 3, 0], dtype=torch.int32, device="cuda")
+    got = ops.sample(logits, temps, seeds, tix).tolist()
+    cpu = logits.cpu()
+    assert got == [qwen2_plain.sample(cpu[r], float(temps[r]), int(seeds[r]), int(tix[r])) for r in range(8)]
+    # a padded row stride (logits as a slice of a wider buffer), as a captured step hands them over
+    wide = torch.zeros(8, V + 64, device="cuda")
+    wide[:, :V] = logits
+    assert ops.sample(wide[:, :V], temps, seeds, tix).tolist() == got
+
+
 def plain_rope(x, pos, inv, rot):
     # x [T, n, hd]; half-split pairs over the first rot dims (pyre/model.py:41-63);
     # inv = theta^(-2j/rot) is computed once on the CPU and shared with the kernel under
