@@ -17,6 +17,11 @@ already cached (context 2,048 + tokens decoded so far, inside the benchmark cont
   roofline         bytes the decode step must read (every weight once + the cache of the
                    live requests) / its time, against the HBM peak
   points           decode tokens/s at batch 1 and 64
+  kernels          per workload (decode at batch 1, 8 and 64, the 2,048-token prefill) and kernel class
+                   (norm, qkv, rotary+write, attention, o, gate_up, down, head, sampler): device
+                   microseconds with every kernel alone (CUDA events between the launches of an
+                   eager step), the bytes or flops the class has to do, and the fraction of the
+                   measured peak; ``sum_over_step`` compares the classes' sum with that step's time
   env              GPU, compute capability, torch and CUDA versions, commit, time
 
 Peaks come from MEASURED_PEAKS.json beside this file if it is there, else from the
@@ -136,6 +141,56 @@ def model_numbers(cfg: dict, layers: int):
     return weight_bytes, kv_bytes_per_token, flops
 
 
+def class_work(cfg: dict, layers: int, T: int, B: int, context_before: int, logit_rows: int) -> dict:
+    """Per kernel class of one step (T tokens in B entries, each with ``context_before`` tokens cached): the
+    bytes it has to move and the flops it has to do, summed over the layers.  Bytes: every weight once, the
+    cache of the live requests once, activations in and out once (bf16; the residual stream and logits fp32)."""
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    q, kv = nh * hd, nkv * hd
+    keys = B * ((T // B) * context_before + (T // B) * (T // B + 1) / 2)      # query-key pairs under the causal mask
+    cached = B * (context_before + T // B)                                    # tokens whose keys and values are read
+    return {
+        "embed": {"bytes": T * H * (2 + 4), "flops": 0},
+        "norm": {"bytes": (2 * layers + 1) * T * H * (4 + 2 + 4 + 2) + (2 * layers + 1) * H * 4, "flops": 0},
+        "qkv": {"bytes": layers * ((q + 2 * kv) * H * 2 + T * (H + q + 2 * kv) * 2), "flops": 2.0 * layers * T * H * (q + 2 * kv)},
+        "rotary+write": {"bytes": layers * T * (q + 2 * kv) * 2 * 2, "flops": 0},
+        "attention": {"bytes": layers * (cached * 2 * kv * 2 + 2 * T * q * 2), "flops": 4.0 * layers * nh * hd * keys},
+        "o": {"bytes": layers * (H * q * 2 + T * (q + H) * 2), "flops": 2.0 * layers * T * q * H},
+        "gate_up": {"bytes": layers * (2 * I * H * 2 + T * (H + I) * 2), "flops": 4.0 * layers * T * H * I},
+        "down": {"bytes": layers * (H * I * 2 + T * (I + H) * 2), "flops": 2.0 * layers * T * H * I},
+        "head": {"bytes": V * H * 2 + logit_rows * (H * 2 + V * 4), "flops": 2.0 * logit_rows * H * V},
+        "sampler": {"bytes": logit_rows * V * 4, "flops": 0},
+    }
+
+
+def kernel_table(totals: dict, work: dict, step_us: float, peaks: dict) -> dict:
+    """The ``kernels`` block of one workload: per class its device microseconds (every kernel alone, one event
+    between two launches), the bytes and flops it has to do, what it achieved, and the fraction of the measured
+    peak that binds it: the copy bandwidth, or the cuBLAS burst figure (the right one for a kernel timed alone)
+    where the flops are the larger share."""
+    classes = {}
+    for name, t in sorted(totals.items(), key=lambda kv: -kv[1]["us"]):
+        w = work.get(name)
+        row = {"us": round(t["us"], 1), "launches": t["launches"]}
+        if w is not None and t["us"] > 0:
+            # both yardsticks; the class is judged by the one that binds it (the larger fraction)
+            gbs = w["bytes"] / (t["us"] * 1e-6) / 1e9
+            tf = w["flops"] / (t["us"] * 1e-6) / 1e12
+            f_mem, f_flop = gbs / peaks["hbm_gbs"], tf / peaks["bf16_tflops"]
+            row.update(bytes=int(w["bytes"]), gbs=round(gbs, 1))
+            if w["flops"]:
+                row.update(flops=w["flops"], tflops=round(tf, 1))
+            if f_flop > f_mem:
+                row.update(frac=round(f_flop, 3), of="bf16_tflops")
+            else:
+                row.update(frac=round(f_mem, 3), of="hbm_gbs")
+        classes[name] = row
+    total = sum(t["us"] for t in totals.values())
+    return {"step_us": round(step_us, 1), "sum_us": round(total, 1), "sum_over_step": round(total / step_us, 3) if step_us else None,
+            "classes": classes}
+
+
 def run_ours(args) -> dict:
     import numpy as np
     import torch
@@ -237,6 +292,43 @@ def run_ours(args) -> dict:
             v, _ = decode_run(b_, 3, max(8, steps // 2), f"p{b_}")
             points[f"decode_b{b_}"] = round(v, 1)
 
+    # ---------------------------------------------------------------- per kernel class, every kernel alone
+    kernels = {}
+    if not args.no_per_kernel:
+        def timed(run_step, work):
+            run_step()                                     # warm: the eager path's buffers and plans
+            samples = []
+            for _ in range(3):
+                torch.cuda.synchronize()
+                a, b = ev(), ev()
+                with stepper.kernel_timing() as timer:
+                    a.record()
+                    run_step()
+                    b.record()
+                    totals = timer.totals()
+                samples.append((a.elapsed_time(b) * 1e3, totals))
+            samples.sort(key=lambda s_: s_[0])
+            step_us, totals = samples[1]
+            return kernel_table(totals, work, step_us, peaks)
+
+        for b_ in ([1, 8, 64] if not args.skip_points else [B]):
+            reqs = [("k", b_, i) for i in range(b_)]
+            for r in reqs:
+                cache.begin(r)
+                stepper.step([StepEntry(r, rng.integers(0, vocab, PROMPT_LEN).tolist(), [])])
+            kernels[f"decode_b{b_}"] = timed(
+                lambda: ops.sample(stepper.step([StepEntry(r, [int(rng.integers(0, vocab))], [0]) for r in reqs])),
+                class_work(cfg_raw, layers, b_, b_, PROMPT_LEN + 2, b_))
+            for r in reqs:
+                cache.end(r)
+        serial = [0]
+
+        def one_prefill():
+            serial[0] += 1
+            prefill_once(("kp", serial[0]))
+            cache.end(("kp", serial[0]))
+        kernels[f"prefill_{PROMPT_LEN}"] = timed(one_prefill, class_work(cfg_raw, layers, PROMPT_LEN, 1, 0, 1))
+
     # ---------------------------------------------------------------- end to end through Engine.step
     sp = SamplingParams(max_new_tokens=warmup + steps + B + 8, ignore_eos=True)
     sids = [engine.add_request(rng.integers(0, vocab, PROMPT_LEN).tolist(), params=sp) for _ in range(B)]
@@ -267,7 +359,7 @@ def run_ours(args) -> dict:
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": bench_config(cfg_raw, layers, layers_full, B),
         "clocks": clock_summary, "e2e": e2e, "gpu_launches": info["launches"], "prefill": prefill,
-        "roofline": roofline, "points": points, "impl": "ours",
+        "roofline": roofline, "points": points, "kernels": kernels, "impl": "ours",
     }
 
 
@@ -476,6 +568,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")
     ap.add_argument("--prefill-reps", type=int, default=5)
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
+    ap.add_argument("--no-per-kernel", action="store_true",
+                    help="leave out the `kernels` block (device time, bytes or flops and fraction of the peak per kernel class)")
     ap.add_argument("--workload", choices=["serve14b", "mixed32b", "sweep"], default=None,
                     help="run one of the two other baseline workloads, or a sweep over batch sizes, context lengths and "
                          "portion lengths on the 7B shape, instead (prints its own JSON line)")

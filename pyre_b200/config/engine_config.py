@@ -51,6 +51,10 @@ class EngineConfig:
     host (they are fed on the device); the host work of a step then hides behind the GPU's.
     ``record_steps``: keep one record per step in ``Engine.step_log`` (tokens, requests, pages free,
     preemptions, the host's time in the call); off by default.
+    ``time_kernels``: a measuring mode: every step runs kernel by kernel (no captured graphs, no lookahead)
+    with CUDA events around each launch; ``Engine.kernel_times`` sums device microseconds per kernel class
+    (norm, qkv, rotary+write, attention, o, gate_up, down, head, sampler) and each step-log record carries
+    its own.  The reference keeps every measurement with its run (bench/harness.py:84-135).
     """
 
     dtype: "str | torch.dtype" = "bfloat16"
@@ -68,6 +72,7 @@ class EngineConfig:
     admit_whole_prompts: bool = True
     debug_poison_freed_pages: bool = False
     record_steps: bool = False
+    time_kernels: bool = False
 
     def __post_init__(self):
         self.dtype = parse_dtype(self.dtype)

@@ -29,7 +29,7 @@ __global__ void paged_attention_generic_kernel(
     int bt_stride,
     const int* __restrict__ seq_of_token,  // [n_tokens]
     const int* __restrict__ positions,     // [n_tokens]
-    int n_tokens, int nh, int nkv, int hd, int page_size, int window, float scale) {
+    int n_tokens, int nh, int nkv, int hd, int page_size, int window, float scale, long long n_pages, int* err_flag) {
     extern __shared__ float q_smem[];  // [warps][hd]
     pdl_trigger();
     pdl_wait();
@@ -61,7 +61,7 @@ __global__ void paged_attention_generic_kernel(
         float score = -INFINITY;
         int vrow = -1;  // row index of this key's value vector, in units of hd elements
         if (valid) {
-            const int page = table[j / page_size];
+            const int page = pyre_checked_page(table[j / page_size], n_pages, err_flag);
             const int off = j % page_size;
             const size_t krow = ((size_t)(page * 2) * nkv + kvh) * page_size + off;
             vrow = (int)(((size_t)(page * 2 + 1) * nkv + kvh) * page_size + off);
@@ -110,7 +110,8 @@ __global__ void paged_attention_generic_kernel(
 PYRE_API int pyre_paged_attention_generic(const void* q, const void* cache, void* out, const int* block_table,
                                           int bt_stride, const int* seq_of_token, const int* positions,
                                           int n_tokens, int nh, int nkv, int hd, int page_size, int window,
-                                          float scale, int dtype, cudaStream_t stream) {
+                                          float scale, int dtype, long long n_pages, int* err_flag,
+                                          cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd % 8 || hd > 256 || hd <= 0 || nkv <= 0 || nh % nkv || page_size <= 0) return PYRE_ERR_BAD_ARG;
     const int warps = 4;
@@ -120,11 +121,11 @@ PYRE_API int pyre_paged_attention_generic(const void* q, const void* cache, void
     if (dtype == PYRE_F32)
         pyre_launch(paged_attention_generic_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream, 
             (const float*)q, (const float*)cache, (float*)out, block_table, bt_stride, seq_of_token, positions,
-            n_tokens, nh, nkv, hd, page_size, window, scale);
+            n_tokens, nh, nkv, hd, page_size, window, scale, n_pages, err_flag);
     else if (dtype == PYRE_BF16)
         pyre_launch(paged_attention_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, stream, 
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, block_table, bt_stride,
-            seq_of_token, positions, n_tokens, nh, nkv, hd, page_size, window, scale);
+            seq_of_token, positions, n_tokens, nh, nkv, hd, page_size, window, scale, n_pages, err_flag);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;

@@ -120,6 +120,7 @@ struct AttnParams {
                                  // 128-byte column box, page piece and K/V (pages under 16 tokens), 2 = one 5-d copy per tile
     int box_rows;                // rows per TMA box: min(16, page_size)
     int* err_flag;
+    long long n_pages;           // pages of the pool (0 = not known); read by the debug checks only
     int uniform_len;             // > 0: every entry has exactly this many tokens (a decode step): no scan for the group
     int max_len;                 // > 0: only entries with at most this many tokens (longer ones go to the prefill kernel)
     float scale;
@@ -232,7 +233,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
             const bool live = key >= lo_g && key <= pos_last;
             const int lp = p.page_shift >= 0 ? key >> p.page_shift : key / p.page_size;
             const int slot = p.page_shift >= 0 ? key & (p.page_size - 1) : key % p.page_size;
-            const int page = live ? table[lp] : 0;
+            const int page = live ? pyre_checked_page(table[lp], p.n_pages, p.err_flag) : 0;
             const size_t krow = ((size_t)(page * 2) * p.nkv + kvh) * p.page_size + (live ? slot : 0);
             const __nv_bfloat16* ksrc = p.cache + krow * HD + c * 8;
             const uint32_t off = row * (HD * 2) + ((c ^ (row & SWZ)) * 16);
@@ -262,7 +263,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
         const int kt2 = tile_begin + warp + WARPS * (jb + lane);
         const int key = kt2 * TILE;
         const bool live = kt2 < tile_end && key + TILE - 1 >= lo_g && key <= pos_last;
-        pg = live ? table[key >> p.page_shift] : 0;   // a tile wholly outside [lo_g, pos_last] reads page 0 (masked)
+        pg = live ? pyre_checked_page(table[key >> p.page_shift], p.n_pages, p.err_flag) : 0;   // a tile wholly outside [lo_g, pos_last] reads page 0 (masked)
     };
     if (p.use_tma == 2) read_pages(0);
     // bring tile number j of this warp into `stage` (the whole warp calls; lane 0 issues)
@@ -293,7 +294,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
             // a piece wholly outside [lo_g, pos_last] still has to be filled: read page 0 (its scores are masked)
             const int lp = key >> p.page_shift;
             const bool live = key + p.box_rows - 1 >= lo_g && key <= pos_last;
-            const int page = live ? table[lp] : 0;
+            const int page = live ? pyre_checked_page(table[lp], p.n_pages, p.err_flag) : 0;
             const int krow = ((page * 2) * p.nkv + kvh) * p.page_size + (key & (p.page_size - 1));
             const int vrow = krow + p.nkv * p.page_size;
 #pragma unroll
@@ -755,6 +756,7 @@ PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* ou
     CUtensorMap map;
     memset(&map, 0, sizeof(map));
     p.err_flag = err_flag;
+    p.n_pages = n_pages;
     p.uniform_len = (uniform_len > 0 && (long long)uniform_len * n_seqs == n_tokens) ? uniform_len : 0;
     p.box_rows = page_size < TILE ? page_size : TILE;
     p.use_tma = 0;

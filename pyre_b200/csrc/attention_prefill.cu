@@ -58,6 +58,8 @@ struct PrefillParams {
     const int* positions;        // [T]
     int bt_stride, n_seqs, nh, nkv, page_size, window, min_len;
     float scale;
+    long long n_pages;           // pages of the pool (0 = not known) and the device's error word: for the debug checks
+    int* err_flag;
 };
 
 template <int HD>
@@ -131,7 +133,7 @@ __global__ void __launch_bounds__(WARPS * 32, 3) attention_prefill_kernel(const 
             const int row = rr + j * ROWS_PER_PASS;
             const int key = kt * BN + row;
             const bool live = key >= lo_cta && key <= pos_last;
-            const int page = live ? table[key / p.page_size] : 0;
+            const int page = live ? pyre_checked_page(table[key / p.page_size], p.n_pages, p.err_flag) : 0;
             const size_t krow = ((size_t)(page * 2) * p.nkv + kvh) * p.page_size + (live ? key % p.page_size : 0);
             const __nv_bfloat16* ksrc = p.cache + krow * HD + c * 8;
             const __nv_bfloat16* vsrc = ksrc + (size_t)p.nkv * p.page_size * HD;
@@ -302,14 +304,14 @@ int launch(const PrefillParams& p, int tiles_bound, cudaStream_t stream) {
 PYRE_API int pyre_attention_prefill(const void* q, const void* cache, void* out, const int* block_table, int bt_stride,
                                     const int* cu_seqlens, const int* positions, int n_long_tokens, int n_seqs, int nh,
                                     int nkv, int hd, int page_size, int window, float scale, int min_len,
-                                    cudaStream_t stream) {
+                                    long long n_pages, int* err_flag, cudaStream_t stream) {
     if (n_long_tokens <= 0) return 0;
     if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || min_len < 1) return PYRE_ERR_UNSUPPORTED;
     PrefillParams p;
     p.q = (const __nv_bfloat16*)q; p.cache = (const __nv_bfloat16*)cache; p.out = (__nv_bfloat16*)out;
     p.block_table = block_table; p.cu_seqlens = cu_seqlens; p.positions = positions;
     p.bt_stride = bt_stride; p.n_seqs = n_seqs; p.nh = nh; p.nkv = nkv; p.page_size = page_size;
-    p.window = window; p.min_len = min_len; p.scale = scale;
+    p.window = window; p.min_len = min_len; p.scale = scale; p.n_pages = n_pages; p.err_flag = err_flag;
     const int tiles_bound = n_long_tokens / BM + n_seqs;
     return hd == 128 ? launch<128>(p, tiles_bound, stream) : launch<64>(p, tiles_bound, stream);
 }

@@ -169,6 +169,7 @@ struct TcParams {
     int bt_stride, n_seqs, nh, nkv, page_size, page_shift, box_rows, window, min_len;
     float scale;
     int* err_flag;
+    long long n_pages;           // pages of the pool; read by the debug checks only
 };
 
 template <int HD>
@@ -275,7 +276,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         auto read_pages = [&](int i) -> int {
             const int key = (tile_lo + i) * BN + lane * p.box_rows;
             const bool live = lane < pieces && i < n_tiles && key + p.box_rows - 1 >= lo_cta && key <= pos_last;
-            return live ? table[key >> p.page_shift] : 0;   // pieces outside the range read page 0 (masked)
+            return live ? pyre_checked_page(table[key >> p.page_shift], p.n_pages, p.err_flag) : 0;   // pieces outside the range read page 0 (masked)
         };
         const uint32_t bar_empty = which ? bar_o : bar_s, bar_full = which ? bar_v_full : bar_k_full;
         const uint32_t ring = base + (which ? L::OFF_V : L::OFF_K);
@@ -570,7 +571,7 @@ PYRE_API int pyre_attention_prefill_tc(const void* q, const void* cache, void* o
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.box_rows = page_size < BN ? page_size : BN;
-    p.window = window; p.min_len = min_len; p.scale = scale; p.err_flag = err_flag;
+    p.window = window; p.min_len = min_len; p.scale = scale; p.err_flag = err_flag; p.n_pages = n_pages;
     CUtensorMap mq, mkv;
     memset(&mq, 0, sizeof(mq));
     memset(&mkv, 0, sizeof(mkv));

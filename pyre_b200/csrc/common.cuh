@@ -159,5 +159,38 @@ static inline int pyre_sm_count() {
     return count[dev];
 }
 
+// ---------------------------------------------------------------------------
+// Debug checks (-DPYRE_DEBUG_CHECKS; PYRE_DEBUG_CHECKS=1 in the environment builds and loads such libraries).
+// Every page number that an attention kernel takes from a block table for a key it reads, and every cache slot
+// that the K/V write takes from the slot mapping, is checked against the pool: 0 <= page < n_pages (the pages
+// that requests own and the scratch page after them; n_pages <= 0 means "not known": only the sign is checked).
+// A page number outside (a -1 inside the live range of a sequence, a number beyond the pool) raises the
+// device's error word with PYRE_ERRWORD_BAD_PAGE and the access is not made: a read goes to page 0 instead, a
+// write is dropped.  The host side refuses such tables before a step starts (the allocator's hard errors,
+// pyre/paged_cache.py:62-77 of the reference); this is the device-side net under it.  Off, the helpers are
+// the identity and cost nothing.
+// ---------------------------------------------------------------------------
+constexpr int PYRE_ERRWORD_BAD_PAGE = 6;
+#ifdef PYRE_DEBUG_CHECKS
+__device__ __forceinline__ int pyre_checked_page(int page, long long n_pages, int* err) {
+    if (page < 0 || (n_pages > 0 && page >= n_pages)) {
+        if (err) atomicExch(err, PYRE_ERRWORD_BAD_PAGE);
+        return 0;
+    }
+    return page;
+}
+// slot = page * page_size + offset of a token's keys and values, or < 0 for "store nothing"
+__device__ __forceinline__ int pyre_checked_slot(int slot, long long n_pages, int page_size, int* err) {
+    if (slot >= 0 && n_pages > 0 && slot >= n_pages * page_size) {
+        if (err) atomicExch(err, PYRE_ERRWORD_BAD_PAGE);
+        return -1;
+    }
+    return slot;
+}
+#else
+__device__ __forceinline__ int pyre_checked_page(int page, long long, int*) { return page; }
+__device__ __forceinline__ int pyre_checked_slot(int slot, long long, int, int*) { return slot; }
+#endif
+
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 static inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }

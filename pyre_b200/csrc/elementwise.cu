@@ -199,6 +199,7 @@ PYRE_API int pyre_rope_table(const int* positions, const float* inv_freq, float*
 //   q_out[T, nh * hd]             rotated queries
 //   cache: one layer of a paged pool, [page][2 (K,V)][nkv][page_size][hd]
 //   slot_mapping[t] = page * page_size + offset of token t, or < 0: do not store
+//   n_pages, err_flag: the pool's page count and the device's error word, for the debug checks (common.cuh)
 // Rotation (half-split pairs over the first `rot` dims of a head, pyre/model.py:54-63):
 //   out[j]        = x[j] * cos[j]        - x[j + rot/2] * sin[j]
 //   out[j + rot/2] = x[j + rot/2] * cos[j] + x[j]        * sin[j]
@@ -230,7 +231,7 @@ __global__ void qkv_rope_write_kernel(const T* __restrict__ qkv, const float* __
                                       const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                       T* __restrict__ q_out, T* __restrict__ cache,
                                       const int* __restrict__ slot_mapping, int nh, int nkv, int hd, int rot,
-                                      int page_size) {
+                                      int page_size, long long n_pages, int* err_flag) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;   // one token per blockIdx.x; blockIdx.y strides over its items
@@ -241,7 +242,7 @@ __global__ void qkv_rope_write_kernel(const T* __restrict__ qkv, const float* __
     const float* pin = partials ? partials + (size_t)t * n_heads_all * hd : nullptr;
     const float* ct = cos_t + (size_t)t * half;
     const float* st = sin_t + (size_t)t * half;
-    const int slot = (cache && slot_mapping) ? slot_mapping[t] : -1;
+    const int slot = (cache && slot_mapping) ? pyre_checked_slot(slot_mapping[t], n_pages, page_size, err_flag) : -1;
     const int page = slot >= 0 ? slot / page_size : 0;
     const int off = slot >= 0 ? slot - page * page_size : 0;
 
@@ -320,7 +321,8 @@ __global__ void qkv_rope_write_full_kernel(const T* __restrict__ qkv, const floa
                                            long long partial_stride, const float* __restrict__ bias,
                                            const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                            T* __restrict__ q_out, T* __restrict__ cache,
-                                           const int* __restrict__ slot_mapping, int nh, int nkv, int hd, int page_size) {
+                                           const int* __restrict__ slot_mapping, int nh, int nkv, int hd, int page_size,
+                                           long long n_pages, int* err_flag) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -331,7 +333,7 @@ __global__ void qkv_rope_write_full_kernel(const T* __restrict__ qkv, const floa
     const float* pin = partials ? partials + (size_t)t * n_heads_all * hd : nullptr;
     const float* ct = cos_t + (size_t)t * half;
     const float* st = sin_t + (size_t)t * half;
-    const int slot = (cache && slot_mapping) ? slot_mapping[t] : -1;
+    const int slot = (cache && slot_mapping) ? pyre_checked_slot(slot_mapping[t], n_pages, page_size, err_flag) : -1;
     const int page = slot >= 0 ? slot / page_size : 0;
     const int off = slot >= 0 ? slot - page * page_size : 0;
     for (int item = blockIdx.y * blockDim.x + threadIdx.x; item < n_heads_all * per_head; item += gridDim.y * blockDim.x) {
@@ -376,7 +378,8 @@ __global__ void qkv_rope_write_full_kernel(const T* __restrict__ qkv, const floa
 PYRE_API int pyre_qkv_rope_write(const void* qkv, const float* partials, int n_partials, long long partial_stride,
                                  const float* bias, const float* cos_t, const float* sin_t,
                                  void* q_out, void* cache, const int* slot_mapping, int n_tokens, int nh, int nkv,
-                                 int hd, int rot, int page_size, int dtype, cudaStream_t stream) {
+                                 int hd, int rot, int page_size, int dtype, long long n_pages, int* err_flag,
+                                 cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd % 8 || rot % 8 || rot > hd || rot < 0 || page_size <= 0) return PYRE_ERR_BAD_ARG;
     if ((qkv == nullptr) == (partials == nullptr)) return PYRE_ERR_BAD_ARG;
@@ -391,13 +394,13 @@ PYRE_API int pyre_qkv_rope_write(const void* qkv, const float* partials, int n_p
     // one block per token is plenty of parallelism
     const int by = n_tokens >= 256 ? 1 : min(ceil_div(items, threads), 64);
     if (full && dtype == PYRE_F32)
-        pyre_launch(qkv_rope_write_full_kernel<float, 4>, dim3(n_tokens, by), dim3(threads), 0, stream, (const float*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (float*)q_out, (float*)cache, slot_mapping, nh, nkv, hd, page_size);
+        pyre_launch(qkv_rope_write_full_kernel<float, 4>, dim3(n_tokens, by), dim3(threads), 0, stream, (const float*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (float*)q_out, (float*)cache, slot_mapping, nh, nkv, hd, page_size, n_pages, err_flag);
     else if (full && dtype == PYRE_BF16)
-        pyre_launch(qkv_rope_write_full_kernel<__nv_bfloat16, 8>, dim3(n_tokens, by), dim3(threads), 0, stream, (const __nv_bfloat16*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, slot_mapping, nh, nkv, hd, page_size);
+        pyre_launch(qkv_rope_write_full_kernel<__nv_bfloat16, 8>, dim3(n_tokens, by), dim3(threads), 0, stream, (const __nv_bfloat16*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, slot_mapping, nh, nkv, hd, page_size, n_pages, err_flag);
     else if (dtype == PYRE_F32)
-        pyre_launch(qkv_rope_write_kernel<float>, dim3(n_tokens, by), dim3(threads), 0, stream, (const float*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (float*)q_out, (float*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
+        pyre_launch(qkv_rope_write_kernel<float>, dim3(n_tokens, by), dim3(threads), 0, stream, (const float*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (float*)q_out, (float*)cache, slot_mapping, nh, nkv, hd, rot, page_size, n_pages, err_flag);
     else if (dtype == PYRE_BF16)
-        pyre_launch(qkv_rope_write_kernel<__nv_bfloat16>, dim3(n_tokens, by), dim3(threads), 0, stream, (const __nv_bfloat16*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, slot_mapping, nh, nkv, hd, rot, page_size);
+        pyre_launch(qkv_rope_write_kernel<__nv_bfloat16>, dim3(n_tokens, by), dim3(threads), 0, stream, (const __nv_bfloat16*)qkv, partials, n_partials, partial_stride, bias, cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, slot_mapping, nh, nkv, hd, rot, page_size, n_pages, err_flag);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;
@@ -498,6 +501,24 @@ __global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict_
 PYRE_API int pyre_feed_tokens(int* ids, const int* dst, const int* src, const int* prev, int n, cudaStream_t stream) {
     if (n <= 0) return 0;
     pyre_launch(feed_tokens_kernel, dim3(ceil_div(n, 128)), dim3(128), 0, stream, ids, dst, src, prev, n);
+    PYRE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// A kernel that does nothing for `ns` nanoseconds (at most one second): queued before a measured
+// region, it keeps the GPU behind the host, so that every launch of the region is in the stream
+// before the GPU reaches it and event timestamps show device time, not the host's launch rate.
+// ---------------------------------------------------------------------------
+__global__ void delay_kernel(unsigned long long ns) {
+    const unsigned long long t0 = pyre_now_ns();
+    while (pyre_now_ns() - t0 < ns) __nanosleep(2000);
+}
+
+PYRE_API int pyre_delay(long long ns, cudaStream_t stream) {
+    if (ns <= 0) return 0;
+    if (ns > 1000000000ll) return PYRE_ERR_BAD_ARG;
+    delay_kernel<<<1, 1, 0, stream>>>((unsigned long long)ns);
     PYRE_LAUNCH_CHECK();
     return 0;
 }

@@ -10,6 +10,7 @@ borrows one from another package in its server only, pyre/server/app.py:54-68).
 
 from __future__ import annotations
 
+import contextlib
 import dataclasses
 import time
 from dataclasses import dataclass
@@ -84,6 +85,7 @@ class Engine:
         self._err_host = [torch.zeros(1, dtype=torch.int32, pin_memory=pinned) for _ in range(2)]
         self._err_turn = 0
         self.step_log: "list[dict] | None" = [] if ec.record_steps else None
+        self.kernel_times: dict = {}      # with time_kernels: class -> {"us": device time so far, "launches": n}
 
     def _pages_for_memory(self, ec: EngineConfig, spec) -> int:
         """Pages per group so that all pools together take ``cache_memory_fraction`` of the memory that is free
@@ -138,7 +140,8 @@ class Engine:
                 if toks[-1] == PENDING:
                     toks[-1], feed = 0, s.request.feed_row
                 entries.append(StepEntry(s.request.seq_id, toks, [s.count - 1] if s.samples else [], feed))
-            with torch.cuda.device(self.model.device):
+            timing = self.stepper.kernel_timing() if self.engine_config.time_kernels else contextlib.nullcontext()
+            with torch.cuda.device(self.model.device), timing as timer:
                 logits = self.stepper.step(entries, reserve=False, fed_from=prev[1].ids if prev and prev[1] is not None else None)
                 # the device's error flag travels with the ids: a kernel that gave up (bounded wait, bad index) is
                 # reported when this step is read, without a synchronisation of its own
@@ -159,12 +162,21 @@ class Engine:
         if self._flight is not None:
             self._land(self._flight)
         self._flight = flight
-        if flight is not None and not self.engine_config.lookahead:
+        if flight is not None and not (self.engine_config.lookahead and not self.engine_config.time_kernels):
             self._land(flight)
             self._flight = None
+        step_kernels = None
+        if plan and self.engine_config.time_kernels:
+            step_kernels = timer.totals()
+            for cls, t in step_kernels.items():
+                acc = self.kernel_times.setdefault(cls, {"us": 0.0, "launches": 0})
+                acc["us"] += t["us"]
+                acc["launches"] += t["launches"]
         if self.step_log is not None and plan:
             self.step_log.append(step_record(sched.stats.steps - 1, plan, self.cache, sched.stats,
                                              time.perf_counter() - t_call))
+            if step_kernels is not None:
+                self.step_log[-1]["kernel_us"] = {cls: round(t["us"], 1) for cls, t in step_kernels.items()}
         outs = []
         for sid in [sid for sid, r in self._requests.items() if r.done and not r.pending]:
             r = self._requests.pop(sid)

@@ -319,6 +319,24 @@ class Stepper:
                 return self._graph_step(entries, reserve, fed_from)
             return self.run_context(self.build_context(entries, reserve), fed_from)
 
+    @contextlib.contextmanager
+    def kernel_timing(self, lead_ms: float = 25.0):
+        """``with stepper.kernel_timing() as timer:`` steps taken inside run kernel by kernel (no captured
+        graphs) with CUDA events around every launch; ``timer.totals()`` gives device microseconds per kernel
+        class (norm, qkv, rotary+write, attention, o, gate_up, down, head, sampler, ...).  A delay of ``lead_ms``
+        is queued first so that the host's launches are ahead of the GPU (a step of 28 layers is a few hundred
+        launches, a few milliseconds of host time)."""
+        from ..kernels import ops
+        graphs, self.cuda_graphs = self.cuda_graphs, False
+        try:
+            with device_guard(self.device), lib.timing() as timer:
+                if lead_ms > 0:
+                    ops.delay(lead_ms)
+                    timer.records.clear()      # the delay itself is no kernel of the step; its end event starts the first one
+                yield timer
+        finally:
+            self.cuda_graphs = graphs
+
     # ------------------------------------------------------------------ captured decode steps
     def _graph_step(self, entries: Sequence[StepEntry], reserve: bool, fed_from: "torch.Tensor | None" = None) -> torch.Tensor:
         cache = self.cache

@@ -47,6 +47,21 @@ NVCC_FLAGS = [
 ]
 
 
+# PYRE_DEBUG_CHECKS=1 in the environment selects the debug build of every library: compiled with
+# -DPYRE_DEBUG_CHECKS (device-side range checks of cache pages and slots, see csrc/common.cuh) into files of
+# their own (libpyre_<name>_dbg.so), so both builds can lie side by side.
+DEBUG_CHECKS = os.environ.get("PYRE_DEBUG_CHECKS", "") not in ("", "0")
+DEBUG_FLAGS = ["-DPYRE_DEBUG_CHECKS"]
+
+
+def _flags() -> list[str]:
+    return NVCC_FLAGS + (DEBUG_FLAGS if DEBUG_CHECKS else [])
+
+
+def _suffix() -> str:
+    return "_dbg" if DEBUG_CHECKS else ""
+
+
 class BuildError(RuntimeError):
     pass
 
@@ -102,7 +117,7 @@ def build_dir() -> Path:
 
 def _fingerprint(name: str) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(_flags()).encode())
     for rel in [LIBRARIES[name]] + INCLUDED_SOURCES.get(name, []) + sorted(HEADERS):
         p = CSRC / rel
         h.update(rel.encode())
@@ -111,11 +126,11 @@ def _fingerprint(name: str) -> str:
 
 
 def library_path(name: str) -> Path:
-    return build_dir() / f"libpyre_{name}.so"
+    return build_dir() / f"libpyre_{name}{_suffix()}.so"
 
 
 def is_current(name: str) -> bool:
-    so, stamp = library_path(name), build_dir() / f"{name}.stamp"
+    so, stamp = library_path(name), build_dir() / f"{name}{_suffix()}.stamp"
     try:
         return so.is_file() and stamp.read_text() == _fingerprint(name)
     except OSError:
@@ -145,12 +160,12 @@ def ensure_built(names, verbose: bool = True, extra_flags: "list[str] | None" = 
             nvcc = find_nvcc()
             t0 = time.time()
             if verbose:
-                _say(f"compiling {len(todo)} CUDA librar{'y' if len(todo) == 1 else 'ies'} for sm_100a "
-                     f"({', '.join(todo)}) into {bdir}")
+                _say(f"compiling {len(todo)} CUDA librar{'y' if len(todo) == 1 else 'ies'} for sm_100a"
+                     f"{' with debug checks' if DEBUG_CHECKS else ''} ({', '.join(todo)}) into {bdir}")
             procs = {}
             for n in todo:
-                tmp = bdir / f".libpyre_{n}.{os.getpid()}.so"
-                cmd = [nvcc, *NVCC_FLAGS, *(extra_flags or []), "-I", str(CSRC), "-o", str(tmp), str(CSRC / LIBRARIES[n])]
+                tmp = bdir / f".libpyre_{n}{_suffix()}.{os.getpid()}.so"
+                cmd = [nvcc, *_flags(), *(extra_flags or []), "-I", str(CSRC), "-o", str(tmp), str(CSRC / LIBRARIES[n])]
                 # the compiler's messages go to a file: a pipe that nobody reads until the exit would block a
                 # compiler that says more than the pipe holds
                 log = tempfile.TemporaryFile(mode="w+", dir=bdir)
@@ -171,7 +186,7 @@ def ensure_built(names, verbose: bool = True, extra_flags: "list[str] | None" = 
                             p.kill()
                         raise BuildError(f"nvcc failed on {LIBRARIES[n]} (exit {proc.returncode}):\n{out}")
                     os.replace(tmp, library_path(n))
-                    (bdir / f"{n}.stamp").write_text(_fingerprint(n))
+                    (bdir / f"{n}{_suffix()}.stamp").write_text(_fingerprint(n))
                     if verbose:
                         _say(f"  built {n} ({time.time() - t0:.0f} s)")
                 if pending:

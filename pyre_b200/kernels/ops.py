@@ -215,7 +215,8 @@ def qkv_rope_write(qkv: torch.Tensor, bias: "torch.Tensor | None", cos: torch.Te
              _ptr(bias), _ptr(cos) if rotary_dim else None,
              _ptr(sin) if rotary_dim else None, q_out.data_ptr(), _ptr(cache_layer),
              _ptr(slot_mapping) if cache_layer is not None else None, T, n_heads, n_kv_heads, head_dim,
-             rotary_dim, page_size, _dt(act_dtype), _stream())
+             rotary_dim, page_size, _dt(act_dtype), cache_layer.shape[0] if cache_layer is not None else 0,
+             device_error_flag(device).data_ptr(), _stream())
     return q_out
 
 
@@ -243,6 +244,12 @@ def feed_tokens(token_ids: torch.Tensor, dst: torch.Tensor, src: torch.Tensor, p
     if dst.shape[0] != src.shape[0]:
         raise ValueError("dst and src must have one entry each per fed token")
     lib.call("pyre_feed_tokens", token_ids.data_ptr(), dst.data_ptr(), src.data_ptr(), prev.data_ptr(), dst.shape[0], _stream())
+
+
+def delay(milliseconds: float) -> None:
+    """Queue a kernel that idles for ``milliseconds`` (at most 1,000) on the current stream: a measured region
+    queued behind it is in the stream in full before the GPU starts on it."""
+    lib.call("pyre_delay", int(milliseconds * 1e6), _stream())
 
 
 def sample(logits: torch.Tensor, temperature: "torch.Tensor | None" = None, seeds: "torch.Tensor | None" = None,
@@ -292,7 +299,8 @@ def paged_attention_generic(q: torch.Tensor, cache_layer: torch.Tensor, block_ta
         out = torch.empty_like(q)
     lib.call("pyre_paged_attention_generic", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(),
              block_table.data_ptr(), block_table.stride(0), seq_of_token.data_ptr(), positions.data_ptr(), T,
-             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), _dt(q.dtype), _stream())
+             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), _dt(q.dtype), cache_layer.shape[0],
+             device_error_flag(q.device).data_ptr(), _stream())
     return out
 
 
@@ -413,7 +421,8 @@ def attention_prefill(q: torch.Tensor, cache_layer: torch.Tensor, block_table: t
         raise ValueError("out, cu_seqlens and positions do not match the batch")
     lib.call("pyre_attention_prefill", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(), block_table.data_ptr(),
              block_table.stride(0), cu_seqlens.data_ptr(), positions.data_ptr(), int(n_long_tokens), n_seqs, n_heads,
-             n_kv_heads, head_dim, page_size, int(window or 0), float(scale), int(min_len), _stream())
+             n_kv_heads, head_dim, page_size, int(window or 0), float(scale), int(min_len), cache_layer.shape[0],
+             device_error_flag(q.device).data_ptr(), _stream())
     return out
 
 
@@ -509,17 +518,28 @@ def device_error_flag(device) -> torch.Tensor:
     return flag
 
 
+DEVICE_ERROR_MESSAGES = {
+    1: "a kernel met an index outside its range (token id outside the vocabulary)",
+    2: "a tensor-core GEMM gave up waiting on its pipeline (bounded wait ran out)",
+    3: "the attention kernel gave up waiting for a tile copy (bounded wait ran out)",
+    4: "the tcgen05 attention kernel gave up waiting on its pipeline (bounded wait ran out)",
+    5: "the tcgen05 attention kernel found its shared memory misaligned",
+    6: "a kernel met a cache page or slot outside the pool (debug checks): a block table or slot mapping names "
+       "a page that was given back or never existed",
+}
+
+
+def device_error_message(code: int) -> str:
+    """What a value of the device's error word means."""
+    return DEVICE_ERROR_MESSAGES.get(int(code), f"a kernel raised error code {int(code)}")
+
+
 def check_device_errors(device="cuda") -> None:
     flag = device_error_flag(device)
     code = int(flag.item())
     if code:
         flag.zero_()
-        raise lib.KernelError({1: "a kernel met an index outside its range (token id outside the vocabulary)",
-                               2: "a tensor-core GEMM gave up waiting on its pipeline (bounded wait ran out)",
-                               3: "the attention kernel gave up waiting for a tile copy (bounded wait ran out)",
-                               4: "the tcgen05 attention kernel gave up waiting on its pipeline (bounded wait ran out)",
-                               5: "the tcgen05 attention kernel found its shared memory misaligned"}.get(
-            code, f"a kernel raised error code {code}"))
+        raise lib.KernelError(device_error_message(code))
 
 
 def tc_gemm_supported(x: torch.Tensor, w: torch.Tensor) -> bool:

@@ -5,7 +5,7 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels import ops
+from ..kernels import lib, ops
 from ..weights.specs import TensorSpec
 from .base import PagedKVSpec, Part, PartSpec, make_part, register_part
 
@@ -95,7 +95,8 @@ class Attention(Part):
     def forward(self, ctx, h, call):
         kv = ctx.kv_group(call.kv_group)
         layer = kv.pool[call.kv_layer]
-        qkv = ops.linear(h, self.w_qkv, partials_ok=True)
+        with lib.section("qkv"):
+            qkv = ops.linear(h, self.w_qkv, partials_ok=True)
         cos, sin = self.position.tables(ctx)
         q = ops.qkv_rope_write(qkv, self.b_qkv, cos, sin, layer if call.kv_write else None, kv.slot_mapping,
                                self.n_heads, self.n_kv_heads, self.head_dim, self.position.rotary_dim, kv.page_size)
@@ -106,7 +107,8 @@ class Attention(Part):
             # float32 and head sizes above 128: the exact fp32-arithmetic kernel
             a = ops.paged_attention_generic(q, layer, kv.block_table, ctx.seq_of_token, ctx.positions, self.n_heads,
                                             self.n_kv_heads, self.head_dim, self.scale, self.window)
-        return ops.linear(a, self.w_o, partials_ok=True)
+        with lib.section("o"):
+            return ops.linear(a, self.w_o, partials_ok=True)
 
 
 register_part("mixer", "attention", Attention)

@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels import ops
+from ..kernels import lib, ops
 from ..weights.specs import TensorSpec
 from .base import Part, register_part
 
@@ -55,7 +55,8 @@ class LinearHead(Part):
         return ["gemm_f32"] if self.dtype == torch.float32 else ["gemm_tc"]
 
     def forward(self, ctx, h_rows):
-        return ops.linear(h_rows, self.weight, out_dtype=torch.float32)
+        with lib.section("head"):
+            return ops.linear(h_rows, self.weight, out_dtype=torch.float32)
 
 
 register_part("embed", "token_embedding", TokenEmbedding)

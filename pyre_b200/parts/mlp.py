@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels import ops
+from ..kernels import lib, ops
 from ..weights.specs import TensorSpec
 from .base import Part, register_part
 
@@ -43,8 +43,10 @@ class GatedMLP(Part):
         return ["elementwise"] + (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_tc"])
 
     def forward(self, ctx, h):
-        act = ops.gated_linear(h, self.w_gate_up, self.interleaved)
-        return ops.linear(act, self.w_down, partials_ok=True)
+        with lib.section("gate_up"):
+            act = ops.gated_linear(h, self.w_gate_up, self.interleaved)
+        with lib.section("down"):
+            return ops.linear(act, self.w_down, partials_ok=True)
 
 
 register_part("ffn", "gated_mlp", GatedMLP)

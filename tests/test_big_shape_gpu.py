@@ -144,7 +144,7 @@ def test_generation_returns_the_plain_logits(big, dtype, lookahead):
     prompts = [H.random_ids(raw["vocab_size"], n, seed=500 + n) for n in lens]
     params = [SamplingParams(max_new_tokens=40, return_logits=True, temperature=0.0 if k % 2 else 0.8, seed=k)
               for k in range(len(lens))]
-    eng = Engine(d, dtype=dtype, page_size=16, num_pages=80, max_num_seqs=8, max_num_batched_tokens=512,
+    eng = Engine(d, dtype=dtype, page_size=16, num_pages=64, max_num_seqs=8, max_num_batched_tokens=512,
                  prefill_chunk=256, debug_poison_freed_pages=True, lookahead=lookahead)
     outs = eng.generate(prompts, params)
     assert eng.stats()["preempted"] >= 1

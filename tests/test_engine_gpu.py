@@ -303,3 +303,24 @@ def test_padded_captured_steps_give_the_same_logits(model_dirs, dtype):
             assert np.array_equal(a, b)
         else:
             assert np.abs(a - b).max() <= 2e-2 * max(1.0, np.abs(b).max())
+
+
+def test_kernel_times_per_class(model_dirs):
+    """``time_kernels``: every step runs kernel by kernel with events around each launch; the engine sums device
+    time per kernel class and the step log carries each step's own.  The tokens are those of a normal run."""
+    from pyre_b200 import Engine, SamplingParams
+    d, raw = model_dirs["B"], H.TINY["B"]
+    prompts = [H.random_ids(raw["vocab_size"], L, seed=60 + L) for L in (9, 30)]
+    sp = SamplingParams(max_new_tokens=6)
+    kw = dict(dtype="bfloat16", page_size=8, max_cache_tokens=512)
+    plain = Engine(d, **kw).generate(prompts, sp)
+    eng = Engine(d, time_kernels=True, record_steps=True, **kw)
+    timed = eng.generate(prompts, sp)
+    assert [o.token_ids for o in timed] == [o.token_ids for o in plain]
+    assert {"embed", "norm", "qkv", "rotary+write", "attention", "o", "gate_up", "down", "head", "sampler"} <= set(eng.kernel_times)
+    layers = raw["num_hidden_layers"]
+    steps = len(eng.step_log)
+    assert eng.kernel_times["qkv"]["launches"] == layers * steps and eng.kernel_times["head"]["launches"] == steps
+    assert all(t["us"] > 0 for t in eng.kernel_times.values())
+    assert all("kernel_us" in rec and rec["kernel_us"]["attention"] > 0 for rec in eng.step_log)
+    assert eng.stepper.graph_replays == 0          # the measuring mode captures nothing
