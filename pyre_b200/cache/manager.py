@@ -41,6 +41,21 @@ def pages_for(n_tokens: int, page_size: int) -> int:
     return -(-n_tokens // page_size)
 
 
+def pages_per_group(kv_groups: Sequence, page_size: int, full_pages: int, max_requests: int, step_tokens: int) -> list[int]:
+    """How many pages each paged group gets when a group that keeps every token gets ``full_pages``.  A group
+    whose spec bounds what a request holds (``spec.tokens_held(step_tokens)``: a window) never needs more than
+    ``max_requests`` times the pages of that many tokens (one more per request, because a window rarely starts
+    on a page's edge), so its pool is that small; its memory goes to the groups that keep everything."""
+    out = []
+    for g in kv_groups:
+        held = g.spec.tokens_held(step_tokens) if hasattr(g.spec, "tokens_held") else None
+        if held is None:
+            out.append(int(full_pages))
+        else:
+            out.append(max(1, min(int(full_pages), max_requests * (pages_for(held, page_size) + 1))))
+    return out
+
+
 class PagedGroup:
     """Pages and block tables of one group of layers."""
 
@@ -169,14 +184,18 @@ class CacheStats:
 
 
 class CacheManager:
-    def __init__(self, kv_groups: Sequence, state_groups: Sequence, page_size: int, num_pages: int,
+    def __init__(self, kv_groups: Sequence, state_groups: Sequence, page_size: int, num_pages: "int | Sequence[int]",
                  max_requests: int, dtype: torch.dtype, device, allocate: bool = True):
         """``kv_groups`` / ``state_groups``: objects with ``.spec`` and ``.n_layers`` (the model's
-        ``KVGroup`` / ``StateGroup``).  Every paged group gets ``num_pages`` pages."""
+        ``KVGroup`` / ``StateGroup``).  ``num_pages``: one number for every paged group, or one per group
+        (``pages_per_group`` gives a windowed group the small pool it needs)."""
         self.page_size = int(page_size)
-        self.num_pages = int(num_pages)
-        self.groups = [PagedGroup(g.spec, g.n_layers, self.page_size, self.num_pages, dtype, device, allocate)
-                       for g in kv_groups]
+        counts = [int(num_pages)] * len(kv_groups) if isinstance(num_pages, int) else [int(n) for n in num_pages]
+        if len(counts) != len(kv_groups):
+            raise ValueError(f"{len(counts)} page counts for {len(kv_groups)} paged groups")
+        self.num_pages = max(counts, default=int(num_pages) if isinstance(num_pages, int) else 0)
+        self.groups = [PagedGroup(g.spec, g.n_layers, self.page_size, n, dtype, device, allocate)
+                       for g, n in zip(kv_groups, counts)]
         self.state = StateSlots([(g.spec, g.n_layers) for g in state_groups], max_requests, device, allocate)
         self.lengths: dict[Hashable, int] = {}
         self.reserved: dict[Hashable, int] = {}

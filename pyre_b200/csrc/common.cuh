@@ -103,9 +103,10 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 
 // Spin-waits in the kernels (mbarriers of the TMA / tcgen05 pipelines) are bounded by time, not by a
 // count of polls: a wait may legitimately last as long as the kernels before it in the stream run (a CTA
-// can be resident and polling while its predecessor drains), but never seconds.  After PYRE_WAIT_NS the
-// waiter gives up, raises the error word and the kernel winds down.
-constexpr unsigned long long PYRE_WAIT_NS = 4000000000ull;
+// can be resident and polling while its predecessor drains), but never long: a quarter of a second is some
+// seventy decode steps of a 7B model.  After PYRE_WAIT_NS the waiter gives up, raises the error word and the
+// kernel winds down.
+constexpr unsigned long long PYRE_WAIT_NS = 250000000ull;
 __device__ __forceinline__ unsigned long long pyre_now_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

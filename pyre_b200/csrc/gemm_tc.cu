@@ -141,6 +141,20 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr) : "memory");
 }
 
+// The four epilogue warps agree on a predicate (barrier 1 with an AND reduction).  The gated epilogue of the
+// transposed store synchronises those warps inside its loops; whether a tile is processed at all must
+// therefore be one decision for the four of them, also when a bounded wait ran out for some and not for others.
+__device__ __forceinline__ bool epilogue_warps_all(bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %1, 0;\n\t"
+        "bar.red.and.pred q, 1, 128, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(r) : "r"((uint32_t)pred) : "memory");
+    return r != 0;
+}
+
 struct GemmParams {
     int x_rows, y_rows, K;
     int k_blocks_per_split;       // K blocks (of 64) per blockIdx.z
@@ -422,6 +436,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
             if constexpr (X_CONTIGUOUS_OUT && BN <= 128) {
                 if (p.gated) {
+                    alive = epilogue_warps_all(alive);     // the warps meet at barriers below: all of them or none
                     // weights on the rows: this tile's 128 rows are 64 gate features (warps of rows 0..63) and the
                     // up features of the same indices (rows 64..127), its columns are tokens.  The up warps hand
                     // their values over through shared memory; the gate warps compute silu(gate) * up as above and

@@ -20,7 +20,7 @@ from typing import Sequence
 import numpy as np
 import torch
 
-from ..cache import CacheManager
+from ..cache import CacheManager, pages_per_group
 from ..config import EngineConfig, ModelConfig, architecture_of, load_config
 from ..kernels import build, lib
 from ..models.model import Model
@@ -70,9 +70,12 @@ class Engine:
         default_tokens = min(max_positions, 8192) * min(ec.max_num_seqs, 8)
         num_pages = ec.resolve_num_pages(default_tokens)
         if ec.num_pages is None and ec.max_cache_tokens is None and ec.cache_memory_fraction:
-            num_pages = self._pages_for_memory(ec, spec)
+            num_pages = self._pages_for_memory(ec)
         self.max_model_len = min(ec.max_model_len or max_positions, num_pages * ec.page_size)
-        self.cache = CacheManager(self.model.kv_groups, self.model.state_groups, ec.page_size, num_pages,
+        # a group that keeps every token gets num_pages; a windowed group only what its window can hold
+        counts = pages_per_group(self.model.kv_groups, ec.page_size, num_pages, ec.max_num_seqs,
+                                 min(ec.prefill_chunk, ec.max_num_batched_tokens))
+        self.cache = CacheManager(self.model.kv_groups, self.model.state_groups, ec.page_size, counts,
                                   ec.max_num_seqs, ec.dtype, ec.device)
         self.cache.set_poison(ec.debug_poison_freed_pages)
         self.stepper = Stepper(self.model, self.cache, max_positions=max_positions, cuda_graphs=ec.cuda_graphs)
@@ -87,24 +90,43 @@ class Engine:
         self.step_log: "list[dict] | None" = [] if ec.record_steps else None
         self.kernel_times: dict = {}      # with time_kernels: class -> {"us": device time so far, "launches": n}
 
-    def _pages_for_memory(self, ec: EngineConfig, spec) -> int:
-        """Pages per group so that all pools together take ``cache_memory_fraction`` of the memory that is free
-        now (the weights are on the device), less a reserve for the activations of the largest step."""
+    def _pages_for_memory(self, ec: EngineConfig) -> int:
+        """Pages of a group that keeps every token, so that all pools and state buffers together take
+        ``cache_memory_fraction`` of the memory that is free now (the weights are on the device), less a reserve
+        for the activations of the largest step.  Every group's spec says what it costs (``bytes_per_token``,
+        ``tokens_held``; ``bytes_per_request`` for state), so a windowed group or a mixer with state is counted
+        for what it takes."""
         free, _total = torch.cuda.mem_get_info(self.model.device)
         elem = torch.empty((), dtype=ec.dtype).element_size()
-        per_page = sum(g.n_layers * 2 * g.spec.n_kv_heads * g.spec.head_dim * ec.page_size * elem for g in self.model.kv_groups)
-        if per_page == 0:
+        groups = self.model.kv_groups
+        page_bytes = [g.n_layers * g.spec.bytes_per_token(elem) * ec.page_size for g in groups]
+        state_bytes = sum(g.n_layers * (ec.max_num_seqs + 1) * g.spec.bytes_per_request() for g in self.model.state_groups)
+        if not any(page_bytes):
             return 1
         # activations of a step: a few buffers as wide as the widest matrix output per token (the vocabulary aside),
         # fp32 logits of the wanted rows (one per request in generation), and a gigabyte for everything small
         widest = max([t.shape[0] for t in self.model.tensor_table().values()
                       if len(t.shape) == 2 and t.shape[0] != self.model.vocab_size] or [4096])
         reserve = ec.max_num_batched_tokens * widest * 8 + ec.max_num_seqs * self.model.vocab_size * 8 + (1 << 30)
-        budget = int(free * ec.cache_memory_fraction) - reserve
-        if budget < per_page:
+        budget = int(free * ec.cache_memory_fraction) - reserve - state_bytes
+        step_tokens = min(ec.prefill_chunk, ec.max_num_batched_tokens)
+
+        def cost(full_pages: int) -> int:      # every pool has one page more than it hands out
+            counts = pages_per_group(groups, ec.page_size, full_pages, ec.max_num_seqs, step_tokens)
+            return sum(b * (n + 1) for b, n in zip(page_bytes, counts))
+
+        if budget < cost(1):
             raise RuntimeError(f"cache_memory_fraction {ec.cache_memory_fraction} of {free / 2**30:.1f} GiB free leaves no room "
-                               f"for a page of {per_page / 2**20:.1f} MiB after a reserve of {reserve / 2**30:.1f} GiB")
-        return budget // per_page
+                               f"for a page per group ({cost(1) / 2**20:.1f} MiB) after a reserve of {reserve / 2**30:.1f} GiB "
+                               f"and {state_bytes / 2**20:.1f} MiB of per-request state")
+        lo, hi = 1, max(2, budget // max(1, min(b for b in page_bytes if b)))
+        while lo < hi:                          # the largest page count whose pools fit
+            mid = (lo + hi + 1) // 2
+            if cost(mid) <= budget:
+                lo = mid
+            else:
+                hi = mid - 1
+        return lo
 
     # ------------------------------------------------------------------ the reference's two calls
     def add_request(self, prompt_ids: Sequence[int], max_new_tokens: int = 16, eos_id: "int | None" = None,

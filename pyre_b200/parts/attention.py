@@ -7,13 +7,13 @@ import torch
 
 from ..kernels import lib, ops
 from ..weights.specs import TensorSpec
-from .base import PagedKVSpec, Part, PartSpec, make_part, register_part
+from .base import HeadGeometry, PagedKVSpec, Part, PartSpec, make_part, register_part
 
 
 class Attention(Part):
-    """q, k, v projections (stacked into one product), position encoding on q and k,
-    keys and values written to the pages of this call's cache layer, attention of every
-    token of the step over its sequence's cached keys, output projection.
+    """q, k, v projections (stacked into one product); the position encoding (a sub-part, which adds the
+    bias, encodes positions into q and k in its own way and writes keys and values to the pages of this
+    call's cache layer); attention of every token of the step over its sequence's cached keys; output projection.
 
     Parameters: ``width`` (model width), ``n_heads``, ``n_kv_heads``, ``head_dim``
     (``n_heads * head_dim`` need not equal ``width``), ``qkv_bias`` / ``o_bias``,
@@ -40,6 +40,7 @@ class Attention(Part):
         self.qkv_bias = bool(qkv_bias)
         self.scale = float(scale) if scale is not None else self.head_dim ** -0.5
         self.window = window
+        self.heads = HeadGeometry(self.n_heads, self.n_kv_heads, self.head_dim)
         self.position = make_part("position", position or PartSpec("none"), dtype, device)
         self.w_qkv = self.b_qkv = self.w_o = None
 
@@ -97,9 +98,9 @@ class Attention(Part):
         layer = kv.pool[call.kv_layer]
         with lib.section("qkv"):
             qkv = ops.linear(h, self.w_qkv, partials_ok=True)
-        cos, sin = self.position.tables(ctx)
-        q = ops.qkv_rope_write(qkv, self.b_qkv, cos, sin, layer if call.kv_write else None, kv.slot_mapping,
-                               self.n_heads, self.n_kv_heads, self.head_dim, self.position.rotary_dim, kv.page_size)
+        # the position encoding owns the step from projections to cache: bias, its transformation of q and k,
+        # the paged write of k and v; the queries come back
+        q = self.position.apply(ctx, qkv, self.b_qkv, self.heads, kv, layer if call.kv_write else None)
         if self.dtype == torch.bfloat16 and self.head_dim <= ops.MMA_MAX_HEAD_DIM:
             a = ops.paged_attention_bf16(ctx, q, layer, kv.block_table, self.n_heads, self.n_kv_heads, self.head_dim,
                                          self.scale, self.window)

@@ -16,7 +16,13 @@ Interfaces by category (``ctx`` is the StepContext, T its number of tokens):
     norm      forward(ctx, x, delta=None, rows=None, update_x=True) -> h
               h = norm(x + delta) in the activation dtype; writes the sum back to x
               when update_x; with rows, only those rows (gathered), x untouched
-    position  tables(ctx) -> per-step tensors the mixer hands to its kernels
+    position  apply(ctx, qkv, bias, heads, kv, cache_layer) -> q
+              ``qkv``: the stacked projections of the step's tokens [T, (nh + 2 nkv) hd] (a tensor or
+              ``kernels.ops.PartialSums``), ``bias`` fp32 or None, ``heads`` a HeadGeometry, ``kv`` the KVView
+              of the mixer's cache group.  The part adds the bias, encodes the tokens' positions into the
+              queries and keys in whatever way is its own, stores every token's key and value at
+              ``kv.slot_mapping`` in ``cache_layer`` (None: store nothing) and returns the queries
+              [T, nh hd].  ``PositionEncoding.store`` does the storing for encodings that bring no fused kernel
     mixer     forward(ctx, h, call) -> [T, width]    ``call`` (BoundCall) names the cache
               layer or state layer of this use of the mixer; cache_spec()/state_spec()
               say what it needs from the cache manager
@@ -64,6 +70,16 @@ class PagedKVSpec:
     head_dim: int
     window: int | None = None
 
+    def bytes_per_token(self, element_size: int) -> int:
+        """Bytes of one token's keys and values in one layer of the group."""
+        return 2 * self.n_kv_heads * self.head_dim * element_size
+
+    def tokens_held(self, step_tokens: int) -> "int | None":
+        """The most tokens of one request whose pages are held at a time, when a step brings it at most
+        ``step_tokens`` new ones: None = all of them (no window); with a window, the window of the step's first
+        token and the step's own tokens."""
+        return None if self.window is None else self.window - 1 + step_tokens
+
 
 @dataclass(frozen=True)
 class StateSpec:
@@ -72,6 +88,27 @@ class StateSpec:
 
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+    def bytes_per_request(self) -> int:
+        """Bytes of one request's state in one layer of the group."""
+        n = 1
+        for d in self.shape:
+            n *= int(d)
+        return n * torch.empty((), dtype=self.dtype).element_size()
+
+
+@dataclass(frozen=True)
+class HeadGeometry:
+    """How the columns of stacked q, k, v projections divide into heads: ``n_heads`` query heads, then
+    ``n_kv_heads`` key heads, then as many value heads, ``head_dim`` columns each."""
+
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+
+    @property
+    def width(self) -> int:
+        return (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
 
 
 @dataclass(frozen=True)
@@ -118,6 +155,27 @@ class Part:
         shapes of the step's arrays: a split count, a choice between kernels.  A captured
         step is replayed only for steps whose parts give the same keys.  Hashable items."""
         return ()
+
+
+class PositionEncoding(Part):
+    """Base of the ``position`` parts.  The encoding owns what happens between the q/k/v projections and the
+    cache: a mixer hands it the stacked projections and gets the queries back, with keys and values stored.
+    The mixer assumes nothing about the encoding (no tables, no rotary width)."""
+
+    category = "position"
+
+    def apply(self, ctx, qkv, bias, heads: HeadGeometry, kv, cache_layer):
+        """No encoding at all: bias added, keys and values stored as projected."""
+        return self.store(qkv, bias, heads, kv, cache_layer)
+
+    @staticmethod
+    def store(qkv, bias, heads: HeadGeometry, kv, cache_layer):
+        """For an encoding without a fused kernel of its own: it transforms the projections first (any way it
+        likes) and calls this to add ``bias`` (or None), write every token's key and value to the pages and
+        split off the queries."""
+        from ..kernels import ops
+        return ops.qkv_rope_write(qkv, bias, None, None, cache_layer, kv.slot_mapping, heads.n_heads, heads.n_kv_heads,
+                                  heads.head_dim, 0, kv.page_size)
 
 
 _REGISTRY: dict[str, dict[str, Callable[..., Part]]] = {c: {} for c in CATEGORIES}

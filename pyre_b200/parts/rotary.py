@@ -6,14 +6,15 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import Part, register_part
+from .base import HeadGeometry, PositionEncoding, register_part
 
 
-class Rotary(Part):
+class Rotary(PositionEncoding):
     """inv_freq[j] = theta^(-2j / rotary_dim) for j < rotary_dim / 2, computed with the
     reference's fp32 expression (pyre/model.py:45-47); per step, cos and sin of
     float(position) * inv_freq for the step's tokens, shared by all layers that have
-    the same settings.  ``rotary_dim`` < head_dim rotates only the first dims of a head."""
+    the same settings.  ``rotary_dim`` < head_dim rotates only the first dims of a head.  Bias, rotation of
+    q and k and the paged write of k and v are one kernel (``ops.qkv_rope_write``)."""
 
     graph_safe = True
 
@@ -42,18 +43,24 @@ class Rotary(Part):
         return tab
 
 
-class NoPosition(Part):
+    def apply(self, ctx, qkv, bias, heads: HeadGeometry, kv, cache_layer):
+        if heads.head_dim != self.head_dim:
+            raise ValueError(f"rotary part built for head_dim {self.head_dim}, used with {heads.head_dim}")
+        cos, sin = self.tables(ctx)
+        return ops.qkv_rope_write(qkv, bias, cos, sin, cache_layer, kv.slot_mapping, heads.n_heads, heads.n_kv_heads,
+                                  heads.head_dim, self.rotary_dim, kv.page_size)
+
+
+class NoPosition(PositionEncoding):
     """No position encoding: queries and keys are used as projected."""
 
     graph_safe = True
 
-    rotary_dim = 0
-
     def __init__(self, dtype, device):
         super().__init__(dtype, device)
 
-    def tables(self, ctx):
-        return None, None
+    def kernel_libraries(self):
+        return ["elementwise"]
 
 
 register_part("position", "rotary", Rotary)

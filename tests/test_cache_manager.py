@@ -167,3 +167,36 @@ def test_random_orders_keep_every_page_accounted(data):
     for r in list(live):
         m.end(r)
     assert m.stats().pages_free == [m.num_pages] and m.stats().slots_free == 4
+
+
+def test_a_windowed_group_gets_a_pool_of_its_own_size():
+    """Pages per group: the group that keeps every token gets the full count, the group with a window
+    only what its window (plus a step's tokens) can hold per request.  Requests then grow far beyond
+    the small pool's capacity in tokens without the windowed group ever running out."""
+    from pyre_b200.cache import pages_per_group
+    kv = [G(PagedKVSpec(2, 16, None), 2), G(PagedKVSpec(1, 32, 11), 1)]
+    counts = pages_per_group(kv, page_size=4, full_pages=120, max_requests=3, step_tokens=8)
+    assert counts == [120, 3 * (pages_for(11 - 1 + 8, 4) + 1)] == [120, 18]
+    assert pages_per_group(kv, 4, 5, 3, 8) == [5, 5]                    # never more than the full group has
+    m = CacheManager(kv, [], 4, counts, 3, torch.float32, "cpu", allocate=False)
+    assert [g.num_pages for g in m.groups] == [120, 18] and m.stats().pages_total == [120, 18]
+    for r in "abc":
+        m.begin(r)
+    length = {r: 0 for r in "abc"}
+    while length["a"] < 150:
+        for r in "abc":
+            step = 8 if length[r] < 64 else 1                            # portions of a prompt, then decoding
+            assert m.reserve(r, length[r] + step), f"request {r} at {length[r]}: a pool ran out"
+            length[r] += step
+            m.commit(r, length[r])
+        m.check()
+        assert m.groups[1].allocator.num_used <= 18
+    assert m.groups[0].allocator.num_used == 3 * pages_for(length["a"], 4)
+    with pytest.raises(ValueError, match="page counts"):
+        CacheManager(kv, [], 4, [8], 3, torch.float32, "cpu", allocate=False)
+
+
+def test_specs_say_what_they_cost():
+    assert PagedKVSpec(4, 128, None).bytes_per_token(2) == 2 * 4 * 128 * 2
+    assert PagedKVSpec(4, 128, None).tokens_held(2048) is None and PagedKVSpec(4, 128, 512).tokens_held(64) == 575
+    assert StateSpec((3, 5), torch.float32).bytes_per_request() == 60 and StateSpec((8,), torch.bfloat16).bytes_per_request() == 16

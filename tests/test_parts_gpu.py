@@ -241,3 +241,50 @@ def test_toy_routed_ffn_and_toy_positions_beside_real_attention(tmp_path):
     package's own attention part, stepped in portions on the device against a plain evaluation."""
     import toy_parts
     toy_parts.toy_routed_model_scenario(tmp_path, "cuda")
+
+
+# --------------------------------------------------------------------------- a windowed group with a small pool, through the engine
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_engine_gives_a_windowed_group_a_smaller_pool(tmp_path, dtype):
+    """An architecture of this test's own (the decoder with a window of 20 keys on its middle layer) generates through
+    ``Engine``: the windowed layer's cache group gets a pool a fraction the size of the other group's, several
+    requests decode far beyond what that pool could hold without a window, and the tokens are the plain
+    implementation's with the same window."""
+    from pyre_b200 import Engine, SamplingParams
+    from pyre_b200.config import architecture, register_architecture
+    from pyre_b200.config.model_config import Qwen2Config
+    from pyre_b200.parts import PartSpec
+
+    def build(cfg):
+        spec = architecture("Qwen2ForCausalLM").build(cfg)
+        b = spec.blocks[1]
+        spec.blocks[1] = PartSpec(b.kind, dict(b.params, mixer=PartSpec("attention", dict(b.params["mixer"].params, window=20))))
+        return spec
+
+    @dataclass(frozen=True)
+    class WindowedConfig(Qwen2Config):
+        architecture = "ToyWindowedForCausalLM"
+
+    register_architecture("ToyWindowedForCausalLM", WindowedConfig, build, replace=True)
+    raw = dict(H.TINY_B, architectures=["ToyWindowedForCausalLM"])
+    H.make_model_dir(tmp_path, raw, seed=31)
+    prompts = [H.random_ids(raw["vocab_size"], n, seed=90 + n) for n in (50, 9, 33)]
+    eng = Engine(tmp_path, dtype=dtype, page_size=4, num_pages=120, max_num_seqs=3, max_num_batched_tokens=32, prefill_chunk=16,
+                 debug_poison_freed_pages=True)
+    full, windowed = eng.cache.groups
+    assert windowed.spec.window == 20 and full.num_pages == 120
+    assert windowed.num_pages == 3 * (-(-(19 + 16) // 4) + 1) == 30          # 120 tokens for three requests of up to 110
+    outs = eng.generate(prompts, SamplingParams(max_new_tokens=60))
+    assert eng.stats()["preempted"] == 0
+    eng.cache.check()
+    w = H.load_plain_weights(tmp_path, round_matrices_to_bf16=(dtype == "bfloat16"))
+    for p, o in zip(prompts, outs):
+        assert len(o.token_ids) == 60
+        with torch.inference_mode():
+            logits = qwen2_plain.forward(list(p) + o.token_ids[:-1], w, raw, windows=[None, 20, None]).numpy()
+        for k, tok in enumerate(o.token_ids):
+            row = logits[len(p) - 1 + k]
+            if dtype == "float32":
+                assert tok == int(row.argmax()), f"token {k}"
+            else:
+                assert row[tok] >= row.max() - 0.08, f"token {k}: {row[tok]:.4f} against the best {row.max():.4f}"

@@ -126,17 +126,20 @@ def toy_decay_model_scenario(tmp_path, device):
 
 
 def toy_routed_model_scenario(tmp_path, device):
-    """Two more parts that exist only here: a feed-forward that routes every token to the one of
-    three small experts with the largest router logit (fp32 logits), and a position encoding whose
-    angles grow with the square root of the position.  They are registered from this test, put into
-    blocks beside the package's own attention part (which takes the toy positions as its ``position``
-    parameter) and norms, written as a random model, loaded and stepped in portions against a plain
-    evaluation.  No file of the package changes."""
+    """Three more parts that exist only here: a feed-forward that routes every token to the one of
+    three small experts with the largest router logit (fp32 logits); a position encoding whose
+    angles grow with the square root of the position (a rotation, through the package's fused kernel
+    with tables of its own); and one that is no rotation at all (layer 1: queries and keys are
+    multiplied, dimension by dimension, by a gain that depends on the position).  They are registered
+    from this test, put into blocks beside the package's own attention part (which takes a position
+    encoding as its ``position`` parameter and knows nothing about it) and norms, written as a random
+    model, loaded and stepped in portions against a plain evaluation.  No file of the package changes."""
     from pyre_b200.config import ModelConfig, register_architecture, architecture_of
     from pyre_b200.engine.replay import runtime_for_model
     from pyre_b200.engine.step import StepEntry
     from pyre_b200.models import Model, ModelSpec
-    from pyre_b200.parts import Part, PartSpec, register_part
+    from pyre_b200.kernels import ops
+    from pyre_b200.parts import Part, PartSpec, PositionEncoding, register_part
     from pyre_b200.weights import TensorSpec, write_random_model
 
     class ToyRoutedFFN(Part):
@@ -166,8 +169,8 @@ def toy_routed_model_scenario(tmp_path, device):
                     out[rows] = torch.relu(x[rows] @ self.up[e].t()) @ self.down[e].t()
             return out.to(self.dtype)
 
-    class ToySqrtPositions(Part):
-        """cos/sin of sqrt(position) * inv_freq, in the layout the rotary kernels take."""
+    class ToySqrtPositions(PositionEncoding):
+        """A rotation by sqrt(position) * inv_freq: tables of its own into the package's fused kernel."""
         def __init__(self, dtype, device, head_dim, theta):
             super().__init__(dtype, device)
             self.rotary_dim = head_dim
@@ -176,15 +179,41 @@ def toy_routed_model_scenario(tmp_path, device):
         def kernel_libraries(self):
             return ["elementwise"]
 
-        def tables(self, ctx):
+        def apply(self, ctx, qkv, bias, heads, kv, cache_layer):
             key = ("toy_sqrt", self.rotary_dim)
             if key not in ctx.scratch:
                 ang = ctx.positions.float().sqrt()[:, None] * self.inv_freq[None, :]
                 ctx.scratch[key] = (ang.cos().contiguous(), ang.sin().contiguous())
-            return ctx.scratch[key]
+            cos, sin = ctx.scratch[key]
+            return ops.qkv_rope_write(qkv, bias, cos, sin, cache_layer, kv.slot_mapping, heads.n_heads, heads.n_kv_heads,
+                                      heads.head_dim, self.rotary_dim, kv.page_size)
+
+    def toy_gain(positions, head_dim):
+        """gain[t, d] = 1 + 0.4 sin(0.37 position + d): no rotation, nothing a cos/sin table could express."""
+        d = torch.arange(head_dim, dtype=torch.float32, device=positions.device)
+        return 1.0 + 0.4 * torch.sin(0.37 * positions.float()[:, None] + d[None, :])
+
+    class ToyGainPositions(PositionEncoding):
+        """Not a rotation: q and k are scaled per dimension by a gain that depends on the position.  It transforms
+        the projections itself (plain torch: this is a test's part) and uses the base class's ``store``."""
+        def __init__(self, dtype, device, head_dim):
+            super().__init__(dtype, device)
+            self.head_dim = head_dim
+
+        def kernel_libraries(self):
+            return ["elementwise"]
+
+        def apply(self, ctx, qkv, bias, heads, kv, cache_layer):
+            x = ops.materialize(qkv).float() + bias
+            T = x.shape[0]
+            x = x.view(T, heads.n_heads + 2 * heads.n_kv_heads, heads.head_dim)
+            gain = toy_gain(ctx.positions, heads.head_dim)[:, None, :]
+            x[:, :heads.n_heads + heads.n_kv_heads] *= gain                       # queries and keys; values pass
+            return self.store(x.reshape(T, -1).to(self.dtype).contiguous(), None, heads, kv, cache_layer)
 
     register_part("ffn", "toy_routed", ToyRoutedFFN, replace=True)
     register_part("position", "toy_sqrt", ToySqrtPositions, replace=True)
+    register_part("position", "toy_gain", ToyGainPositions, replace=True)
 
     @dataclass(frozen=True)
     class ToyConfig(ModelConfig):
@@ -207,9 +236,10 @@ def toy_routed_model_scenario(tmp_path, device):
             "norm1": norm, "norm2": norm,
             "mixer": PartSpec("attention", {"width": cfg.width, "n_heads": cfg.heads, "n_kv_heads": cfg.kv_heads,
                                             "head_dim": cfg.head_dim, "qkv_bias": True, "o_bias": False, "window": None,
-                                            "position": PartSpec("toy_sqrt", {"head_dim": cfg.head_dim, "theta": 100.0})}),
+                                            "position": PartSpec("toy_sqrt", {"head_dim": cfg.head_dim, "theta": 100.0}) if i == 0
+                                            else PartSpec("toy_gain", {"head_dim": cfg.head_dim})}),
             "ffn": PartSpec("toy_routed", {"width": cfg.width, "inner": 24, "experts": cfg.experts})})
-            for _ in range(cfg.layers)]
+            for i in range(cfg.layers)]
         return ModelSpec(embed=PartSpec("token_embedding", {"vocab": cfg.vocab, "width": cfg.width}), blocks=blocks,
                          final_norm=norm, head=PartSpec("linear_head", {"vocab": cfg.vocab, "width": cfg.width}),
                          vocab_size=cfg.vocab, max_positions=4096)
@@ -235,7 +265,11 @@ def toy_routed_model_scenario(tmp_path, device):
             q = (h @ w[p + "self_attn.q_proj.weight"].float().t() + w[p + "self_attn.q_proj.bias"].float()).view(T, cfg.heads, cfg.head_dim)
             k = (h @ w[p + "self_attn.k_proj.weight"].float().t() + w[p + "self_attn.k_proj.bias"].float()).view(T, cfg.kv_heads, cfg.head_dim)
             v = (h @ w[p + "self_attn.v_proj.weight"].float().t() + w[p + "self_attn.v_proj.bias"].float()).view(T, cfg.kv_heads, cfg.head_dim)
-            q, k = q * cos[:, None] + rot(q) * sin[:, None], k * cos[:, None] + rot(k) * sin[:, None]
+            if i == 0:
+                q, k = q * cos[:, None] + rot(q) * sin[:, None], k * cos[:, None] + rot(k) * sin[:, None]
+            else:
+                gain = toy_gain(torch.arange(T), cfg.head_dim)[:, None, :]
+                q, k = q * gain, k * gain
             k, v = k.repeat_interleave(cfg.heads // cfg.kv_heads, 1), v.repeat_interleave(cfg.heads // cfg.kv_heads, 1)
             s = torch.einsum("qhd,khd->hqk", q, k) * cfg.head_dim ** -0.5
             s = s.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
