@@ -522,3 +522,30 @@ PYRE_API int pyre_delay(long long ns, cudaStream_t stream) {
     PYRE_LAUNCH_CHECK();
     return 0;
 }
+
+// ---------------------------------------------------------------------------
+// out[t, i] = bf16(float(rows[t, i]) * rstd[t]),  rstd[t] = 1 / sqrt(sum_j ssq[j][t] / H + eps):
+// activations that carry a norm's weight but not yet its 1/rms (left so by a product's fix-up, whose
+// consumer normally applies the factor in its own epilogue), made plain for any other consumer.
+// ---------------------------------------------------------------------------
+__global__ void scale_rows_kernel(const __nv_bfloat16* __restrict__ rows, const float* __restrict__ ssq, int n_tiles,
+                                  __nv_bfloat16* __restrict__ out, int n_tokens, int H, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    float s = 0.f;
+    for (int j = 0; j < n_tiles; ++j) s += ssq[(size_t)j * n_tokens + t];
+    const float rstd = 1.0f / sqrtf(s / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        out[(size_t)t * H + i] = __float2bfloat16_rn(__bfloat162float(rows[(size_t)t * H + i]) * rstd);
+}
+
+PYRE_API int pyre_scale_rows(const void* rows, const float* ssq, int n_tiles, void* out, int n_tokens, int H, float eps,
+                             cudaStream_t stream) {
+    if (n_tokens <= 0 || H <= 0) return 0;
+    if (n_tiles < 1) return PYRE_ERR_BAD_ARG;
+    pyre_launch(scale_rows_kernel, dim3(n_tokens), dim3(256), 0, stream, (const __nv_bfloat16*)rows, ssq, n_tiles,
+                (__nv_bfloat16*)out, n_tokens, H, eps);
+    PYRE_LAUNCH_CHECK();
+    return 0;
+}

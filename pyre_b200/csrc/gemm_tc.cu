@@ -166,6 +166,32 @@ struct GemmParams {
     int gated;                    // 1: the weight rows are gate/up rows interleaved in blocks of 64 (gate rows, then the up
                                   // rows of the same features); the epilogue writes silu(gate) * up, half as many features
     int* err_flag;
+    // ---- transposed store only (few tokens): work folded into the product so that no small kernel runs around it
+    // (a) rows scaled: out[token] *= 1 / sqrt(sum_i scale_ssq[i][token] / scale_n + scale_eps), the 1/rms of an
+    //     RMSNorm whose weight the producer of the activations has already applied (see fix == 1)
+    const float* scale_ssq;       // [scale_tiles][y_rows] partial sums of squares per token, or null
+    int scale_tiles;
+    float scale_n, scale_eps;
+    // (b) fix-up: the CTA that finishes a tile last (an arrival counter per tile) turns the tile's fp32 partial
+    //     sums, which every split has stored to `out`, into their final form:
+    //     fix == 1  residual add + norm preparation:  v = resid + sum of partials;  resid = v;
+    //               h_out = bf16(v * norm_w);  ssq_out[tile][token] = sum over the tile's features of v^2
+    //     fix == 2  bias + rotary (half-split pairs over the whole head) + paged K/V write:  the tile's features are
+    //               whole heads of the stacked q/k/v projection; q heads go to q_out, k and v heads to the cache
+    int fix;
+    int* tile_counters;           // [tiles] zero before the launch and after it
+    float* resid;                 // fp32 [y_rows, x_rows]
+    const float* norm_w;          // fp32 [x_rows]
+    __nv_bfloat16* h_out;         // [y_rows, x_rows]
+    float* ssq_out;               // [tiles_x][y_rows]
+    const float* bias;            // fp32 [x_rows] or null
+    const float* cos_t;           // fp32 [y_rows, rot / 2]
+    const float* sin_t;
+    __nv_bfloat16* q_out;         // [y_rows, nh * hd]
+    __nv_bfloat16* kv_cache;      // one layer: [page][2][nkv][page_size][hd], or null (store nothing)
+    const int* slot_mapping;      // [y_rows]
+    int nh, nkv, hd, rot, page_size;
+    long long n_pages;
 };
 
 template <int BN, int STAGES, bool XC, int CTAS = 1>
@@ -183,7 +209,10 @@ struct SmemLayout {
     static constexpr int GW = XC ? 0 : (ROOM >= 4 * 32 * 144 ? 64 : ROOM >= 4 * 32 * 80 ? 32 : 0);
     static constexpr int OUT_PITCH = 2 * GW + 16;
     static constexpr int EPI_BYTES = XC ? (BN <= 128 ? 64 * BN * 4 : 0) : 4 * 32 * OUT_PITCH * (GW > 0 ? 1 : 0);
-    static constexpr int TOTAL = EPI_OFF + EPI_BYTES + 1024;  // bars, tmem slot and abort flag, epilogue buffer, alignment slack
+    // transposed store: 1/rms of the tile's tokens (128 floats) and the "this CTA finished the tile last" flag
+    static constexpr int SCALE_OFF = EPI_OFF + EPI_BYTES;
+    static constexpr int SCALE_BYTES = XC ? 512 + 16 : 0;
+    static constexpr int TOTAL = SCALE_OFF + SCALE_BYTES + 1024;  // bars, tmem slot and abort flag, epilogue buffers, alignment slack
 };
 
 // A CTA is persistent: it walks output tiles c, c + gridDim.x, ...  Two TMEM accumulators
@@ -357,15 +386,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             if constexpr (CTAS == 2) asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(acc_empty_to + 8 * buf) : "memory");
             else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty_to + 8 * buf) : "memory");
         };
+        [[maybe_unused]] float* rstd_s = reinterpret_cast<float*>(gen + L::SCALE_OFF);
+        [[maybe_unused]] volatile int* last_s = reinterpret_cast<volatile int*>(gen + L::SCALE_OFF + 512);
+        [[maybe_unused]] const int epi_tid = quarter * 32 + lane;
+        [[maybe_unused]] int scaled_y0 = -1;
+        [[maybe_unused]] bool in_step = false;     // the epilogue warps synchronise among themselves in this launch
+        if constexpr (X_CONTIGUOUS_OUT) {
+            in_step = p.gated || p.scale_ssq != nullptr || p.fix != 0;
+            if (p.scale_ssq != nullptr || p.fix != 0) pdl_wait();     // these warps read what earlier kernels wrote
+        }
         for (int tile = worker; tile < n_tiles && alive; tile += n_workers, ++j) {
             const int buf = j & 1;
             const int x0 = (tile % p.tiles_x) * (BM * CTAS) + rank * BM, y0 = (tile / p.tiles_x) * BN;
             const int xr = x0 + quarter * 32 + lane;
+            if constexpr (X_CONTIGUOUS_OUT) {
+                if (p.scale_ssq != nullptr && y0 != scaled_y0) {
+                    // 1/rms of this tile's tokens, from the per-tile sums of squares that the producer of the
+                    // activations left (added in tile order: the same sum whatever else the launch holds);
+                    // computed while the main loop of the tile still runs
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    const int y = y0 + epi_tid;
+                    float rs = 0.f;
+                    if (epi_tid < BN && y < p.y_rows) {
+                        float ssq = 0.f;
+                        for (int i = 0; i < p.scale_tiles; ++i) ssq += p.scale_ssq[(size_t)i * p.y_rows + y];
+                        rs = 1.0f / sqrtf(ssq / p.scale_n + p.scale_eps);
+                    }
+                    rstd_s[epi_tid] = rs;
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    scaled_y0 = y0;
+                }
+            }
             bool ok = true;
             if (n_kb > 0) ok = mbar_wait(bar_acc_full + 8 * buf, (j >> 1) & 1, abort_flag, p.err_flag);
             ok = ok && !*abort_flag;   // the issuer signals the accumulator even when it gave up
             if constexpr (CTAS == 2) ok = ok && (p.err_flag == nullptr || *(volatile int*)p.err_flag == 0);   // ... and it may sit in the peer CTA
             alive = __all_sync(0xffffffffu, ok);
+            if constexpr (X_CONTIGUOUS_OUT) {
+                if (in_step) alive = epilogue_warps_all(alive);     // the warps meet at barriers below: all of them or none
+            }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const long long out_base = (long long)blockIdx.z * p.split_stride + (long long)xr * p.stride_x;
             const uint32_t acc = tmem_base + buf * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
@@ -436,7 +495,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
             if constexpr (X_CONTIGUOUS_OUT && BN <= 128) {
                 if (p.gated) {
-                    alive = epilogue_warps_all(alive);     // the warps meet at barriers below: all of them or none
                     // weights on the rows: this tile's 128 rows are 64 gate features (warps of rows 0..63) and the
                     // up features of the same indices (rows 64..127), its columns are tokens.  The up warps hand
                     // their values over through shared memory; the gate warps compute silu(gate) * up as above and
@@ -469,8 +527,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                                 for (int e = 0; e < 4; ++e) {
                                     const int y = y0 + c + 4 * q4 + e;
                                     if (y < p.y_rows && x0 + (quarter & 1) * 32 + lane < p.x_rows) {
-                                        const float z = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[4 * q4 + e])));
-                                        const float v = __bfloat162float(__float2bfloat16_rn(uu[e]));
+                                        const float rs = p.scale_ssq ? rstd_s[c + 4 * q4 + e] : 1.f;
+                                        const float z = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[4 * q4 + e]) * rs));
+                                        const float v = __bfloat162float(__float2bfloat16_rn(uu[e] * rs));
                                         ((__nv_bfloat16*)p.out)[(long long)y * p.stride_y + feature] =
                                             __float2bfloat16_rn(__fmul_rn(z / (1.0f + expf(-z)), v));
                                     }
@@ -556,7 +615,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     for (int q = 0; q < 16; ++q) {
                         const int y = y0 + c + q;
                         if (y < p.y_rows) {
-                            const float v = __uint_as_float(r[q]);
+                            float v = __uint_as_float(r[q]);
+                            if constexpr (X_CONTIGUOUS_OUT) { if (p.scale_ssq) v *= rstd_s[c + q]; }
                             if (p.out_f32) ((float*)p.out)[out_base + (long long)y * p.stride_y] = v;
                             else ((__nv_bfloat16*)p.out)[out_base + (long long)y * p.stride_y] = __float2bfloat16_rn(v);
                         }
@@ -567,6 +627,114 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) hand_back(buf);
+            if constexpr (X_CONTIGUOUS_OUT && BN <= 128) {
+                if (p.fix != 0) {
+                    // ---- fix-up: every split of this tile has stored its partial sums; the CTA that arrives last
+                    // adds them up (in split order, whichever CTA does it) and finishes the tile
+                    __threadfence();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (epi_tid == 0) {
+                        int last = 1;
+                        if (gridDim.z > 1) {
+                            last = atomicAdd(p.tile_counters + tile, 1) == (int)gridDim.z - 1;
+                            if (last) p.tile_counters[tile] = 0;      // ready for the next launch
+                        }
+                        *last_s = last;
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (*last_s && alive) {
+                        __threadfence();
+                        const int n0 = x0 + 4 * lane;                       // this lane's four features of the tile
+                        const bool in = n0 < p.x_rows;                      // x_rows % 4 == 0: all four or none
+                        const int t_end = min(y0 + BN, p.y_rows);
+                        const float* parts = (const float*)p.out;
+                        const int n_parts = (int)gridDim.z;
+                        if (p.fix == 1) {
+                            float4 w4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (in) w4 = *reinterpret_cast<const float4*>(p.norm_w + n0);
+#pragma unroll 2
+                            for (int t = y0 + quarter; t < t_end; t += 4) {           // a warp per token
+                                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (in) {
+                                    const size_t at = (size_t)t * p.stride_y + n0;
+                                    float4 acc = __ldcg(reinterpret_cast<const float4*>(parts + at));
+                                    for (int z = 1; z < n_parts; ++z) {
+                                        const float4 q = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)z * p.split_stride + at));
+                                        acc.x += q.x; acc.y += q.y; acc.z += q.z; acc.w += q.w;
+                                    }
+                                    float* xr4 = p.resid + (size_t)t * p.x_rows + n0;
+                                    v = *reinterpret_cast<const float4*>(xr4);
+                                    v.x += acc.x; v.y += acc.y; v.z += acc.z; v.w += acc.w;
+                                    *reinterpret_cast<float4*>(xr4) = v;
+                                    __nv_bfloat162 lo = __floats2bfloat162_rn(__fmul_rn(v.x, w4.x), __fmul_rn(v.y, w4.y));
+                                    __nv_bfloat162 hi = __floats2bfloat162_rn(__fmul_rn(v.z, w4.z), __fmul_rn(v.w, w4.w));
+                                    *reinterpret_cast<uint2*>(p.h_out + (size_t)t * p.x_rows + n0) =
+                                        make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                                }
+                                float ss = fmaf(v.w, v.w, fmaf(v.z, v.z, fmaf(v.y, v.y, v.x * v.x)));
+                                ss = warp_sum(ss);
+                                if (lane == 0) p.ssq_out[(size_t)(tile % p.tiles_x) * p.y_rows + t] = ss;
+                            }
+                        } else {
+                            const int hd = p.hd, half = p.rot >> 1;
+                            const int head = n0 / hd, d = n0 - head * hd;
+                            const bool is_q = head < p.nh, is_k = !is_q && head < p.nh + p.nkv;
+                            const bool rotate = p.rot > 0 && (is_q || is_k);
+                            const int jj = d < half ? d : d - half;
+                            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (in && p.bias) b4 = *reinterpret_cast<const float4*>(p.bias + n0);
+#pragma unroll 2
+                            for (int t = y0 + quarter; t < t_end; t += 4) {
+                                float4 x4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (in) {
+                                    const size_t at = (size_t)t * p.stride_y + n0;
+                                    x4 = __ldcg(reinterpret_cast<const float4*>(parts + at));
+                                    for (int z = 1; z < n_parts; ++z) {
+                                        const float4 q = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)z * p.split_stride + at));
+                                        x4.x += q.x; x4.y += q.y; x4.z += q.z; x4.w += q.w;
+                                    }
+                                    x4.x += b4.x; x4.y += b4.y; x4.z += b4.z; x4.w += b4.w;
+                                }
+                                // the other half of the rotation's pairs sits hd / 8 lanes away (every lane takes part)
+                                float4 o4;
+                                o4.x = __shfl_xor_sync(0xffffffffu, x4.x, hd >> 3);
+                                o4.y = __shfl_xor_sync(0xffffffffu, x4.y, hd >> 3);
+                                o4.z = __shfl_xor_sync(0xffffffffu, x4.z, hd >> 3);
+                                o4.w = __shfl_xor_sync(0xffffffffu, x4.w, hd >> 3);
+                                if (!in) continue;
+                                if (rotate) {
+                                    const float4 c4 = *reinterpret_cast<const float4*>(p.cos_t + (size_t)t * half + jj);
+                                    const float4 s4 = *reinterpret_cast<const float4*>(p.sin_t + (size_t)t * half + jj);
+                                    if (d < half) {      // out[j] = x[j] cos - x[j + half] sin, products rounded apart
+                                        x4.x = __fadd_rn(__fmul_rn(x4.x, c4.x), __fmul_rn(-o4.x, s4.x));
+                                        x4.y = __fadd_rn(__fmul_rn(x4.y, c4.y), __fmul_rn(-o4.y, s4.y));
+                                        x4.z = __fadd_rn(__fmul_rn(x4.z, c4.z), __fmul_rn(-o4.z, s4.z));
+                                        x4.w = __fadd_rn(__fmul_rn(x4.w, c4.w), __fmul_rn(-o4.w, s4.w));
+                                    } else {             // out[j + half] = x[j + half] cos + x[j] sin
+                                        x4.x = __fadd_rn(__fmul_rn(x4.x, c4.x), __fmul_rn(o4.x, s4.x));
+                                        x4.y = __fadd_rn(__fmul_rn(x4.y, c4.y), __fmul_rn(o4.y, s4.y));
+                                        x4.z = __fadd_rn(__fmul_rn(x4.z, c4.z), __fmul_rn(o4.z, s4.z));
+                                        x4.w = __fadd_rn(__fmul_rn(x4.w, c4.w), __fmul_rn(o4.w, s4.w));
+                                    }
+                                }
+                                __nv_bfloat162 lo = __floats2bfloat162_rn(x4.x, x4.y), hi = __floats2bfloat162_rn(x4.z, x4.w);
+                                const uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                                if (is_q) {
+                                    *reinterpret_cast<uint2*>(p.q_out + ((size_t)t * p.nh + head) * hd + d) = packed;
+                                } else if (p.kv_cache != nullptr) {
+                                    const int slot = pyre_checked_slot(p.slot_mapping[t], p.n_pages, p.page_size, p.err_flag);
+                                    if (slot >= 0) {
+                                        const int page = slot / p.page_size, off = slot - page * p.page_size;
+                                        const int kvh = is_k ? head - p.nh : head - p.nh - p.nkv;
+                                        const size_t row = ((size_t)(page * 2 + (is_k ? 0 : 1)) * p.nkv + kvh) * p.page_size + off;
+                                        *reinterpret_cast<uint2*>(p.kv_cache + row * hd + d) = packed;
+                                    }
+                                }
+                            }
+                        }
+                    }
+                }
+            }
         }
     }
 
@@ -661,10 +829,51 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, di
 // silu(gate product) * (up product), half as many features: row store (weights = Y, bn 256, out[x, j]) or
 // transposed store (weights = X, bn <= 128, out[y * stride_y + j]); one split, bf16 out.  pair: two CTAs of a
 // cluster share each 256 x bn tile (row store, bn 128, 160, 192, 208, 224 or 256).
-PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* Y, int y_rows, long long ldy, int K,
-                          void* out, int out_f32, long long stride_x, long long stride_y, long long split_stride,
-                          int splits, int bn, int x_is_constant, int gated, int pair, int* err_flag, cudaStream_t stream) {
+//
+// fx (may be null): work folded into a product with the transposed store (weights = X, at most 128 tokens = Y in one
+// tile): `scale_ssq` scales the rows of the result by the 1/rms of a norm whose weight the activations already carry;
+// `fix` = 1 / 2 has the CTA that finishes a tile last add up the splits' partial sums (out must be fp32 partials
+// [splits][y_rows][x_rows]) and turn them into the residual update with the next norm's preparation, or into the
+// rotated queries and the cache's keys and values.  See GemmParams.
+struct PyreGemmFix {
+    int fix;
+    int scale_tiles;
+    float scale_n, scale_eps;
+    const float* scale_ssq;
+    int* tile_counters;
+    float* resid;
+    const float* norm_w;
+    void* h_out;
+    float* ssq_out;
+    const float* bias;
+    const float* cos_t;
+    const float* sin_t;
+    void* q_out;
+    void* kv_cache;
+    const int* slot_mapping;
+    int nh, nkv, hd, rot, page_size;
+    long long n_pages;
+};
+
+static int gemm_tc_impl(const void* X, int x_rows, long long ldx, const void* Y, int y_rows, long long ldy, int K,
+                        void* out, int out_f32, long long stride_x, long long stride_y, long long split_stride,
+                        int splits, int bn, int x_is_constant, int gated, int pair, int* err_flag, const PyreGemmFix* fx,
+                        cudaStream_t stream) {
     if (x_rows <= 0 || y_rows <= 0) return 0;
+    if (fx && (fx->fix != 0 || fx->scale_ssq != nullptr)) {
+        if (stride_x != 1 || bn > 128 || y_rows > bn || pair) return PYRE_ERR_BAD_ARG;      // transposed store, one tile of tokens
+        if (fx->scale_ssq && fx->scale_tiles < 1) return PYRE_ERR_BAD_ARG;
+        if (fx->fix != 0) {
+            if (gated || !out_f32 || x_rows % 4 || stride_y != x_rows || !fx->tile_counters) return PYRE_ERR_BAD_ARG;
+            if (fx->fix == 1 && (!fx->resid || !fx->norm_w || !fx->h_out || !fx->ssq_out)) return PYRE_ERR_BAD_ARG;
+            if (fx->fix == 2) {
+                if (fx->hd <= 0 || 128 % fx->hd || fx->hd % 8 || (fx->rot != 0 && fx->rot != fx->hd) || !fx->q_out ||
+                    x_rows != (fx->nh + 2 * fx->nkv) * fx->hd || fx->page_size <= 0 || (fx->kv_cache && !fx->slot_mapping) ||
+                    (fx->rot && (!fx->cos_t || !fx->sin_t)))
+                    return PYRE_ERR_UNSUPPORTED;
+            } else if (fx->fix != 1) return PYRE_ERR_BAD_ARG;
+        }
+    }
     // the gated epilogue: whole tiles of gate/up rows interleaved in blocks of 64, one split, bf16 out; with the
     // tokens on the row side 256-wide tiles, with the weights on the row side at most 128 tokens per tile
     if (gated && (splits != 1 || out_f32)) return PYRE_ERR_BAD_ARG;
@@ -688,6 +897,16 @@ PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* 
     p.k_blocks_per_split = (total_kb + splits - 1) / splits;
     p.stride_x = stride_x; p.stride_y = stride_y; p.split_stride = split_stride;
     p.out = out; p.out_f32 = out_f32; p.x_is_constant = x_is_constant; p.err_flag = err_flag; p.gated = gated ? 1 : 0;
+    p.scale_ssq = nullptr; p.scale_tiles = 0; p.scale_n = 0.f; p.scale_eps = 0.f; p.fix = 0; p.tile_counters = nullptr;
+    p.resid = nullptr; p.norm_w = nullptr; p.h_out = nullptr; p.ssq_out = nullptr; p.bias = nullptr; p.cos_t = p.sin_t = nullptr;
+    p.q_out = nullptr; p.kv_cache = nullptr; p.slot_mapping = nullptr; p.nh = p.nkv = p.hd = p.rot = p.page_size = 0; p.n_pages = 0;
+    if (fx) {
+        p.scale_ssq = fx->scale_ssq; p.scale_tiles = fx->scale_tiles; p.scale_n = fx->scale_n; p.scale_eps = fx->scale_eps;
+        p.fix = fx->fix; p.tile_counters = fx->tile_counters; p.resid = fx->resid; p.norm_w = fx->norm_w;
+        p.h_out = (__nv_bfloat16*)fx->h_out; p.ssq_out = fx->ssq_out; p.bias = fx->bias; p.cos_t = fx->cos_t; p.sin_t = fx->sin_t;
+        p.q_out = (__nv_bfloat16*)fx->q_out; p.kv_cache = (__nv_bfloat16*)fx->kv_cache; p.slot_mapping = fx->slot_mapping;
+        p.nh = fx->nh; p.nkv = fx->nkv; p.hd = fx->hd; p.rot = fx->rot; p.page_size = fx->page_size; p.n_pages = fx->n_pages;
+    }
     p.tiles_x = ceil_div(x_rows, pair ? 2 * BM : BM); p.tiles_y = ceil_div(y_rows, bn);
     const long long n_tiles = (long long)p.tiles_x * p.tiles_y;
     // one CTA per SM stays resident and walks the tiles (a split K keeps one CTA per tile and split)
@@ -737,4 +956,12 @@ PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* 
     }
 #undef GO
     return rc;
+}
+
+PYRE_API int pyre_gemm_tc(const void* X, int x_rows, long long ldx, const void* Y, int y_rows, long long ldy, int K,
+                          void* out, int out_f32, long long stride_x, long long stride_y, long long split_stride,
+                          int splits, int bn, int x_is_constant, int gated, int pair, int* err_flag,
+                          const PyreGemmFix* fx, cudaStream_t stream) {
+    return gemm_tc_impl(X, x_rows, ldx, Y, y_rows, ldy, K, out, out_f32, stride_x, stride_y, split_stride, splits, bn,
+                        x_is_constant, gated, pair, err_flag, fx, stream);
 }

@@ -14,6 +14,15 @@ from . import build
 
 P, I, LL, F = c_void_p, c_int, c_longlong, c_float
 
+
+class GemmFix(ctypes.Structure):
+    """``PyreGemmFix`` of csrc/gemm_tc.cu: work folded into a product of few tokens (field for field)."""
+
+    _fields_ = [("fix", I), ("scale_tiles", I), ("scale_n", F), ("scale_eps", F), ("scale_ssq", P),
+                ("tile_counters", P), ("resid", P), ("norm_w", P), ("h_out", P), ("ssq_out", P), ("bias", P),
+                ("cos_t", P), ("sin_t", P), ("q_out", P), ("kv_cache", P), ("slot_mapping", P),
+                ("nh", I), ("nkv", I), ("hd", I), ("rot", I), ("page_size", I), ("n_pages", LL)]
+
 # function name -> (library, argument types).  Every function returns int: 0 or an error code.
 SIGNATURES: dict[str, tuple[str, list]] = {
     "pyre_embedding": ("elementwise", [P, I, P, P, I, I, I, P, P]),
@@ -25,7 +34,8 @@ SIGNATURES: dict[str, tuple[str, list]] = {
     "pyre_sum_partials": ("elementwise", [P, I, LL, P, LL, I, P]),
     "pyre_feed_tokens": ("elementwise", [P, P, P, P, I, P]),
     "pyre_delay": ("elementwise", [LL, P]),
-    "pyre_gemm_tc": ("gemm_tc", [P, I, LL, P, I, LL, I, P, I, LL, LL, LL, I, I, I, I, I, P, P]),
+    "pyre_gemm_tc": ("gemm_tc", [P, I, LL, P, I, LL, I, P, I, LL, LL, LL, I, I, I, I, I, P, P, P]),
+    "pyre_scale_rows": ("elementwise", [P, P, I, P, I, I, F, P]),
     "pyre_sample": ("sampling", [P, LL, P, P, P, P, I, I, P, P]),
     "pyre_sample_slices": ("sampling", [I]),
     "pyre_paged_attention_generic": ("attention_generic", [P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, LL, P, P]),
@@ -49,7 +59,7 @@ class KernelError(RuntimeError):
 DEFAULT_CLASS = {
     "pyre_embedding": "embed", "pyre_add_rmsnorm": "norm", "pyre_add_residual": "norm", "pyre_rope_table": "rotary+write",
     "pyre_qkv_rope_write": "rotary+write", "pyre_silu_mul": "activation", "pyre_sum_partials": "sum_partials",
-    "pyre_feed_tokens": "feed", "pyre_delay": "delay", "pyre_gemm_tc": "product", "pyre_sgemm_nt": "product", "pyre_sample": "sampler",
+    "pyre_feed_tokens": "feed", "pyre_delay": "delay", "pyre_gemm_tc": "product", "pyre_sgemm_nt": "product", "pyre_scale_rows": "norm", "pyre_sample": "sampler",
     "pyre_paged_attention_generic": "attention", "pyre_paged_attention_mma": "attention",
     "pyre_attention_prefill_tc": "attention", "pyre_attention_prefill": "attention",
 }
@@ -109,10 +119,14 @@ class _NoSection:
 _NO_SECTION = _NoSection()
 
 
-def section(name: str):
+def section(name: "str | None"):
     """``with lib.section("qkv"):`` names the class of the launches inside for the per-kernel timer.
-    Costs nothing while no timer is installed."""
-    return _Section(name) if _timer is not None else _NO_SECTION
+    Costs nothing while no timer is installed (or the name is None)."""
+    return _Section(name) if _timer is not None and name is not None else _NO_SECTION
+
+
+def current_section() -> "str | None":
+    return _sections[-1] if _sections else None
 
 
 class timing:

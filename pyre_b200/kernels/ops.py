@@ -13,6 +13,8 @@ pyre/model.py:84-87,133-135,172).  See ``linear``.
 
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import lib
@@ -43,8 +45,63 @@ class PartialSums:
         return self.parts.shape[0]
 
 
-def materialize(t: "torch.Tensor | PartialSums") -> torch.Tensor:
-    """A plain tensor in the activation dtype from either a tensor or partial sums."""
+class ScaledRows:
+    """Activations that carry a norm's weight but not yet its 1/rms: ``rows`` [T, H] bf16 and, per token, the
+    sums of squares of the normalised vector's elements in tiles of 128 features (``ssq`` [tiles, T] fp32).  The
+    normalised activations are ``rows[t] / sqrt(sum(ssq[:, t]) / H + eps)``.  A product that takes them applies the
+    factor to its result rows in its epilogue (the factor is a scalar per row, so it commutes with the product);
+    anything else calls ``materialize``."""
+
+    def __init__(self, rows: torch.Tensor, ssq: torch.Tensor, eps: float):
+        self.rows, self.ssq, self.eps = rows, ssq, float(eps)
+
+    @property
+    def shape(self):
+        return self.rows.shape
+
+    @property
+    def dtype(self):
+        return self.rows.dtype
+
+    @property
+    def device(self):
+        return self.rows.device
+
+
+class DeferredProduct:
+    """y = x w^T of a linear layer over few tokens, not launched yet.  The kernel that consumes it decides how it
+    runs: the built-in norm launches it with a fix-up that adds the result to the residual stream and prepares the
+    normalised activations (no norm kernel), the rotary position encoding with one that adds the bias, rotates and
+    writes keys and values to the pages (no rotary kernel); anything else calls ``partials`` or ``materialize``."""
+
+    def __init__(self, x: "torch.Tensor | ScaledRows", w: torch.Tensor, dtype: torch.dtype):
+        self.x, self.w, self.dtype = x, w, dtype
+        self.section = lib.current_section()      # the kernel class its launch counts for, whoever launches it
+
+    @property
+    def shape(self):
+        return (self.x.shape[0], self.w.shape[0])
+
+    @property
+    def device(self):
+        return self.w.device
+
+    def partials(self) -> "torch.Tensor | PartialSums":
+        """Launch the plain product: a tensor, or partial sums where K is split."""
+        with lib.section(self.section):
+            return gemm_tc(self.x, self.w, self.dtype, reduce=False)
+
+
+def materialize(t: "torch.Tensor | PartialSums | DeferredProduct | ScaledRows") -> torch.Tensor:
+    """A plain tensor in the activation dtype from a tensor or any of the lazy forms a branch output or a
+    norm's output may take."""
+    if isinstance(t, DeferredProduct):
+        t = t.partials()
+    if isinstance(t, ScaledRows):
+        out = torch.empty_like(t.rows)
+        T, H = t.rows.shape
+        lib.call("pyre_scale_rows", t.rows.data_ptr(), t.ssq.data_ptr(), t.ssq.shape[0], out.data_ptr(), T, H, t.eps, _stream())
+        return out
     if not isinstance(t, PartialSums):
         return t
     out = torch.empty(tuple(t.shape), dtype=t.dtype, device=t.parts.device)
@@ -110,17 +167,27 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: "torch.Tensor | None"
 
 def add_rmsnorm(x: torch.Tensor, delta: "torch.Tensor | None", weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: "torch.Tensor | None" = None, update_x: bool = True,
-                out: "torch.Tensor | None" = None) -> torch.Tensor:
+                out: "torch.Tensor | None" = None, scaled_ok: bool = False) -> "torch.Tensor | ScaledRows":
     """out[r] = rmsnorm(x[src] + delta[src]) * weight with src = rows[r] (or r).
 
     ``x`` is the fp32 residual stream [T, H]; with ``update_x`` (and no ``rows``) the sum is
     written back to it.  ``delta`` has the activation dtype, or is a ``PartialSums`` whose
-    parts the kernel adds.  ``weight`` is fp32 [H]."""
+    parts the kernel adds, or a ``DeferredProduct``.  ``weight`` is fp32 [H].
+
+    ``scaled_ok``: the caller's consumer takes ``ScaledRows``.  Then a deferred product is launched with the
+    residual add and the norm's preparation as its fix-up, and no norm kernel runs at all."""
     _check(x, "x", torch.float32, 2)
     _check(weight, "weight", torch.float32, 1)
     T, H = x.shape
     if weight.shape[0] != H:
         raise ValueError(f"norm weight has {weight.shape[0]} entries, rows have {H}")
+    if isinstance(delta, DeferredProduct):
+        if tuple(delta.shape) != (T, H):
+            raise ValueError(f"delta shape {tuple(delta.shape)} != x shape {(T, H)}")
+        if scaled_ok and rows is None and update_x and out is None and out_dtype == torch.bfloat16 and H % 8 == 0 \
+                and H <= 128 * _MAX_FIX_TILES:
+            return gemm_residual_norm(delta, x, weight, eps)
+        delta = delta.partials()
     parts, n_parts, part_stride = None, 0, 0
     if isinstance(delta, PartialSums):
         if tuple(delta.shape) != (T, H):
@@ -176,6 +243,13 @@ def qkv_rope_write(qkv: torch.Tensor, bias: "torch.Tensor | None", cos: torch.Te
 
     ``cache_layer``: [pages, 2, nkv, page_size, hd] of the activation dtype, or None to
     store nothing (a layer that reads another layer's cache)."""
+    if isinstance(qkv, DeferredProduct):
+        width = (n_heads + 2 * n_kv_heads) * head_dim
+        if q_out is None and qkv.shape[1] == width and 128 % head_dim == 0 and head_dim % 8 == 0 and rotary_dim in (0, head_dim) \
+                and width <= 128 * _MAX_FIX_TILES:
+            return gemm_rope_write(qkv, bias, cos, sin, cache_layer, slot_mapping, n_heads, n_kv_heads, head_dim,
+                                   rotary_dim, page_size)
+        qkv = qkv.partials()
     parts, n_parts = None, 0
     if isinstance(qkv, PartialSums):
         parts, n_parts, act_dtype, device = qkv.parts, qkv.n, qkv.dtype, qkv.parts.device
@@ -539,6 +613,9 @@ def check_device_errors(device="cuda") -> None:
     code = int(flag.item())
     if code:
         flag.zero_()
+        counters = _fix_counters.get(torch.device(device).index or 0)
+        if counters is not None:
+            counters.zero_()      # a product that gave up may have left arrivals uncounted
         raise lib.KernelError(device_error_message(code))
 
 
@@ -609,7 +686,25 @@ def tc_gemm_plan(M: int, N: int, K: int) -> tuple[bool, int, int]:
 GATED_BLOCK = 64     # gate and up rows of a fused feed-forward weight alternate in blocks of this many features
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+_MAX_FIX_TILES = 4096       # arrival counters per device: tiles of 128 features of one folded product
+_fix_counters: dict = {}
+
+
+def _tile_counters(device) -> torch.Tensor:
+    """Arrival counters of the products with a fix-up (zero between launches: the kernel resets what it counts)."""
+    key = torch.device(device).index or 0
+    c = _fix_counters.get(key)
+    if c is None:
+        c = _fix_counters[key] = torch.zeros(_MAX_FIX_TILES, dtype=torch.int32, device=device)
+    return c
+
+
+def _scale_fields(fx: "lib.GemmFix", x: "ScaledRows") -> None:
+    fx.scale_ssq, fx.scale_tiles = x.ssq.data_ptr(), x.ssq.shape[0]
+    fx.scale_n, fx.scale_eps = float(x.rows.shape[1]), x.eps
+
+
+def gemm_tc(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
             plan: "tuple[bool, int, int] | None" = None, reduce: bool = True, gated: bool = False,
             pair: "bool | None" = None) -> torch.Tensor:
     """y = x w^T on the tensor cores (tcgen05, TMEM accumulators, TMA-fed), bf16 in, fp32 accumulate.
@@ -620,7 +715,15 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
 
     ``gated``: w holds gate and up rows alternating in blocks of ``GATED_BLOCK`` features; the
     result is silu(x gate^T) * (x up^T), [M, N / 2] bf16.  The activation runs in the product's
-    epilogue (whole tiles, one split: the usual case in both orientations), otherwise after it."""
+    epilogue (whole tiles, one split: the usual case in both orientations), otherwise after it.
+
+    ``x`` may be ``ScaledRows`` (at most 128 tokens): the result rows are scaled by the tokens' 1/rms in the
+    epilogue, before the activation of a gated product."""
+    scaled = x if isinstance(x, ScaledRows) else None
+    if scaled is not None:
+        x = scaled.rows
+        if x.shape[0] > 128:
+            x, scaled = materialize(scaled), None
     if not tc_gemm_supported(x, w):
         raise UnsupportedSize("gemm_tc needs bf16 operands with K and leading dimensions that are multiples of 8")
     M, K = x.shape
@@ -628,11 +731,19 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     if K != K2:
         raise ValueError(f"inner sizes differ: x is [{M}, {K}], w is [{N}, {K2}]")
     weights_as_rows, bn, splits = plan or tc_gemm_plan(M, N, K)
+    if scaled is not None and (not weights_as_rows or M > bn):
+        x, scaled = materialize(scaled), None
     splits = max(1, min(splits, -(-K // 64)))
     if pair is None:
         pair = CTA_PAIRS
     pair = int(bool(pair) and not weights_as_rows and M > 128 and bn in (128, 160, 192, 208, 224, 256))
     err = device_error_flag(x.device)
+    fx = None
+    if scaled is not None:
+        fold = lib.GemmFix()
+        _scale_fields(fold, scaled)
+        fx = ctypes.byref(fold)
+
     if gated:
         if N % (2 * GATED_BLOCK) or out_dtype != torch.bfloat16:
             raise UnsupportedSize("a gated product needs whole blocks of gate and up rows and a bfloat16 result")
@@ -641,14 +752,15 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
         if not weights_as_rows and bn == 256 and splits == 1 and N % 256 == 0:
             out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
             lib.call("pyre_gemm_tc", x.data_ptr(), M, x.stride(0), w.data_ptr(), N, w.stride(0), K, out.data_ptr(), 0,
-                     N // 2, 1, 0, 1, bn, 0, 1, pair, err.data_ptr(), _stream())
+                     N // 2, 1, 0, 1, bn, 0, 1, pair, err.data_ptr(), fx, _stream())
             return out
         if weights_as_rows and bn <= 128 and splits == 1 and N % 128 == 0:
             out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
             lib.call("pyre_gemm_tc", w.data_ptr(), N, w.stride(0), x.data_ptr(), M, x.stride(0), K, out.data_ptr(), 0,
-                     1, N // 2, 0, 1, bn, 1, 1, 0, err.data_ptr(), _stream())
+                     1, N // 2, 0, 1, bn, 1, 1, 0, err.data_ptr(), fx, _stream())
             return out
-        return silu_mul(gemm_tc(x, w, torch.bfloat16, (weights_as_rows, bn, splits), pair=bool(pair)), block=GATED_BLOCK)
+        return silu_mul(gemm_tc(scaled if scaled is not None else x, w, torch.bfloat16, (weights_as_rows, bn, splits), pair=bool(pair)),
+                        block=GATED_BLOCK)
     if splits == 1 and reduce:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         target, split_stride = out, 0
@@ -658,10 +770,10 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     f32 = int(target.dtype == torch.float32)
     if weights_as_rows:
         lib.call("pyre_gemm_tc", w.data_ptr(), N, w.stride(0), x.data_ptr(), M, x.stride(0), K, target.data_ptr(), f32,
-                 1, N, split_stride, splits, bn, 1, 0, 0, err.data_ptr(), _stream())
+                 1, N, split_stride, splits, bn, 1, 0, 0, err.data_ptr(), fx, _stream())
     else:
         lib.call("pyre_gemm_tc", x.data_ptr(), M, x.stride(0), w.data_ptr(), N, w.stride(0), K, target.data_ptr(), f32,
-                 N, 1, split_stride, splits, bn, 0, 0, pair, err.data_ptr(), _stream())
+                 N, 1, split_stride, splits, bn, 0, 0, pair, err.data_ptr(), fx, _stream())
     if target.dim() == 2:
         return target
     if not reduce:
@@ -669,10 +781,85 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bfl
     return materialize(PartialSums(target, out_dtype))
 
 
+def _launch_with_fixup(prod: DeferredProduct, fx: "lib.GemmFix") -> None:
+    """The product of a ``DeferredProduct`` (weights on the MMA's rows, all tokens in one tile, K split as the
+    plan says) into fp32 partial sums that only its own fix-up reads."""
+    x = prod.x
+    if isinstance(x, ScaledRows):
+        _scale_fields(fx, x)
+        x = x.rows
+    w = prod.w
+    M, K = x.shape
+    N = w.shape[0]
+    _rows, bn, splits = tc_gemm_plan(M, N, K)
+    splits = max(1, min(splits, -(-K // 64)))
+    parts = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+    fx.tile_counters = _tile_counters(x.device).data_ptr()
+    with lib.section(prod.section):
+        lib.call("pyre_gemm_tc", w.data_ptr(), N, w.stride(0), x.data_ptr(), M, x.stride(0), K, parts.data_ptr(), 1,
+                 1, N, M * N, splits, bn, 1, 0, 0, device_error_flag(x.device).data_ptr(), ctypes.byref(fx), _stream())
+
+
+def gemm_residual_norm(prod: DeferredProduct, x: torch.Tensor, weight: torch.Tensor, eps: float) -> ScaledRows:
+    """x += prod (the fp32 residual stream, in place), and the activations of the RMSNorm that follows as
+    ``ScaledRows``: one kernel, the product; the CTA that finishes a tile of 128 features last adds the splits'
+    partial sums and the residual, stores bf16(x * weight) and the tile's sums of squares per token."""
+    T, H = x.shape
+    rows = torch.empty((T, H), dtype=torch.bfloat16, device=x.device)
+    ssq = torch.empty((-(-H // 128), T), dtype=torch.float32, device=x.device)
+    fx = lib.GemmFix()
+    fx.fix = 1
+    fx.resid, fx.norm_w, fx.h_out, fx.ssq_out = x.data_ptr(), weight.data_ptr(), rows.data_ptr(), ssq.data_ptr()
+    _launch_with_fixup(prod, fx)
+    return ScaledRows(rows, ssq, eps)
+
+
+def gemm_rope_write(prod: DeferredProduct, bias, cos, sin, cache_layer, slot_mapping, n_heads: int, n_kv_heads: int,
+                    head_dim: int, rotary_dim: int, page_size: int) -> torch.Tensor:
+    """The stacked q/k/v projection with bias, rotary and the paged K/V write as its fix-up (what
+    ``qkv_rope_write`` does in a kernel of its own); returns the queries [T, nh * hd]."""
+    T = prod.shape[0]
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+    if rotary_dim:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if tuple(cos.shape) != (T, rotary_dim // 2) or tuple(sin.shape) != (T, rotary_dim // 2):
+            raise ValueError(f"cos/sin must be [{T}, {rotary_dim // 2}], got {tuple(cos.shape)}")
+    q_out = torch.empty((T, n_heads * head_dim), dtype=torch.bfloat16, device=prod.device)
+    fx = lib.GemmFix()
+    fx.fix = 2
+    fx.bias = _ptr(bias)
+    fx.cos_t, fx.sin_t = (_ptr(cos), _ptr(sin)) if rotary_dim else (None, None)
+    fx.q_out = q_out.data_ptr()
+    fx.nh, fx.nkv, fx.hd, fx.rot, fx.page_size = n_heads, n_kv_heads, head_dim, rotary_dim, page_size
+    if cache_layer is not None:
+        _check(cache_layer, "cache_layer", torch.bfloat16, 5)
+        if tuple(cache_layer.shape[1:]) != (2, n_kv_heads, page_size, head_dim):
+            raise ValueError(f"cache layer shape {tuple(cache_layer.shape)} does not match "
+                             f"[pages, 2, {n_kv_heads}, {page_size}, {head_dim}]")
+        _check(slot_mapping, "slot_mapping", torch.int32, 1)
+        if slot_mapping.shape[0] != T:
+            raise ValueError("slot_mapping must have one entry per token")
+        fx.kv_cache, fx.slot_mapping, fx.n_pages = cache_layer.data_ptr(), slot_mapping.data_ptr(), cache_layer.shape[0]
+    _launch_with_fixup(prod, fx)
+    return q_out
+
+
 USE_TC_GEMM = True
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: "torch.dtype | None" = None, partials_ok: bool = False):
+# Very few tokens (a decode step of one to four requests): residual add + norm and bias + rotary + K/V write run as
+# fix-ups of the products before them instead of kernels of their own.  Measured inside whole decode steps of the 7B
+# shape: 4 % faster at one request; at eight requests the fix-up's chain of global round trips (store, fence, arrival
+# counter, reload) is longer than the small kernel it replaces, and at 64 its loop over the tokens in the one CTA per
+# tile that arrives last costs several times what the norm kernel's one CTA per token does.
+FOLD_SMALL_KERNELS = True
+FOLD_MAX_TOKENS = 4
+
+
+def linear(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: "torch.dtype | None" = None, partials_ok: bool = False,
+           deferred_ok: bool = False):
     """y = x W^T for a weight in the linear-layer layout [out, in].
 
     float32: the package's own fp32 kernel (no reduced-precision matrix mode).
@@ -680,13 +867,20 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: "torch.dtype | None" = N
     (K not a multiple of 8) go to a library product instead, as the reference uses a library
     for every projection.  ``out_dtype=torch.float32`` keeps the accumulator's precision
     (used for the logits).  ``partials_ok``: the caller's consumer adds split-K partial
-    sums itself, so a ``PartialSums`` may come back instead of a tensor."""
+    sums itself, so a ``PartialSums`` may come back instead of a tensor.  ``deferred_ok``: the caller's
+    consumer is one of the kernels that take a ``DeferredProduct`` (the built-in norm, ``qkv_rope_write``) or
+    calls ``materialize``; for very few tokens (``FOLD_MAX_TOKENS``) the product is then not launched here."""
     if x.dtype == torch.float32:
         return sgemm_nt(x, w)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise ValueError(f"linear: unsupported dtypes {x.dtype} x {w.dtype}")
-    if USE_TC_GEMM and tc_gemm_supported(x, w):
+    rows = x.rows if isinstance(x, ScaledRows) else x
+    if USE_TC_GEMM and tc_gemm_supported(rows, w):
+        if deferred_ok and FOLD_SMALL_KERNELS and rows.shape[0] <= FOLD_MAX_TOKENS and w.shape[0] % 4 == 0 \
+                and out_dtype in (None, torch.bfloat16):
+            return DeferredProduct(x, w, torch.bfloat16)
         return gemm_tc(x, w, out_dtype or torch.bfloat16, reduce=not partials_ok)
+    x = materialize(x)
     if out_dtype is None or out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)
@@ -704,6 +898,7 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool) ->
     """silu(x gate^T) * (x up^T) for the stacked weight of a gated feed-forward: [gates | ups] rows, or
     (``interleaved``) blocks of ``GATED_BLOCK`` gate rows and up rows in turn, which lets the bfloat16
     tensor-core product apply the activation in its epilogue."""
-    if interleaved and x.dtype == torch.bfloat16 and USE_TC_GEMM and tc_gemm_supported(x, w_gate_up):
+    rows = x.rows if isinstance(x, ScaledRows) else x
+    if interleaved and x.dtype == torch.bfloat16 and USE_TC_GEMM and tc_gemm_supported(rows, w_gate_up):
         return gemm_tc(x, w_gate_up, torch.bfloat16, gated=True)
     return silu_mul(linear(x, w_gate_up), block=GATED_BLOCK if interleaved else 0)

@@ -23,6 +23,7 @@ class Attention(Part):
     """
 
     graph_safe = True
+    takes_scaled_rows = True      # ``h`` may be ``ops.ScaledRows``: the q/k/v product applies the norm's 1/rms itself
 
     def __init__(self, dtype, device, width: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: "PartSpec | None" = None, qkv_bias: bool = True, o_bias: bool = False,
@@ -97,7 +98,7 @@ class Attention(Part):
         kv = ctx.kv_group(call.kv_group)
         layer = kv.pool[call.kv_layer]
         with lib.section("qkv"):
-            qkv = ops.linear(h, self.w_qkv, partials_ok=True)
+            qkv = ops.linear(h, self.w_qkv, partials_ok=True, deferred_ok=True)
         # the position encoding owns the step from projections to cache: bias, its transformation of q and k,
         # the paged write of k and v; the queries come back
         q = self.position.apply(ctx, qkv, self.b_qkv, self.heads, kv, layer if call.kv_write else None)
@@ -109,7 +110,7 @@ class Attention(Part):
             a = ops.paged_attention_generic(q, layer, kv.block_table, ctx.seq_of_token, ctx.positions, self.n_heads,
                                             self.n_kv_heads, self.head_dim, self.scale, self.window)
         with lib.section("o"):
-            return ops.linear(a, self.w_o, partials_ok=True)
+            return ops.linear(a, self.w_o, partials_ok=True, deferred_ok=True)
 
 
 register_part("mixer", "attention", Attention)

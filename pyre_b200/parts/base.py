@@ -30,9 +30,12 @@ Interfaces by category (``ctx`` is the StepContext, T its number of tokens):
     block     forward(ctx, x, pending, call) -> (x, pending)   ``pending`` is a branch
               output not yet added to x; the next norm adds it (fused).  A branch output
               (what a mixer or a feed-forward returns, hence ``delta`` and ``pending``) is a
-              tensor [T, width] in the activation dtype or ``kernels.ops.PartialSums``,
-              fp32 partial sums that the built-in norm adds up; a part that needs a plain
-              tensor calls ``kernels.ops.materialize`` on it
+              tensor [T, width] in the activation dtype, or ``kernels.ops.PartialSums`` (fp32
+              partial sums that the built-in norm adds up), or ``kernels.ops.DeferredProduct`` (a
+              product of few tokens that the built-in norm launches with the residual add folded
+              in); a part that needs a plain tensor calls ``kernels.ops.materialize`` on it.
+              Likewise a norm may hand a consumer that declares ``takes_scaled_rows``
+              ``kernels.ops.ScaledRows`` instead of a tensor (see ``PreNormBlock``)
     head      forward(ctx, h_rows) -> fp32 logits [R, vocab]
 
 A new part is a class with these methods and one ``register_part`` call; nothing else

@@ -28,15 +28,23 @@ class PreNormBlock(Part):
         self.mixer = make_part("mixer", mixer, dtype, device)
         self.norm2 = make_part("norm", norm2, dtype, device)
         self.ffn = make_part("ffn", ffn, dtype, device)
+        # A norm that can run as the fix-up of the product before it hands its consumer activations that still lack
+        # the 1/rms factor (``ops.ScaledRows``); it may do so only for a consumer that says it takes them.  Both are
+        # opt-in attributes of the parts; parts without them see plain tensors.
+
+        def lazy(norm, consumer):
+            ok = getattr(norm, "fuses_into_product", False) and getattr(consumer, "takes_scaled_rows", False)
+            return {"scaled_ok": True} if ok else {}
+        self._kw1, self._kw2 = lazy(self.norm1, self.mixer), lazy(self.norm2, self.ffn)
 
     def children(self):
         return {self.names["norm1"]: self.norm1, self.names["mixer"]: self.mixer,
                 self.names["norm2"]: self.norm2, self.names["ffn"]: self.ffn}
 
     def forward(self, ctx, x, pending, call):
-        h = self.norm1.forward(ctx, x, delta=pending)
+        h = self.norm1.forward(ctx, x, delta=pending, **self._kw1)
         a = self.mixer.forward(ctx, h, call)
-        h = self.norm2.forward(ctx, x, delta=a)
+        h = self.norm2.forward(ctx, x, delta=a, **self._kw2)
         return x, self.ffn.forward(ctx, h)
 
 

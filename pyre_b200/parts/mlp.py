@@ -16,6 +16,7 @@ class GatedMLP(Part):
     output tile of the product holds both halves and the activation runs in its epilogue."""
 
     graph_safe = True
+    takes_scaled_rows = True      # ``h`` may be ``ops.ScaledRows``: the gate/up product applies the norm's 1/rms itself
 
     def __init__(self, dtype, device, width: int, intermediate: int, activation: str = "silu"):
         super().__init__(dtype, device)
@@ -46,7 +47,7 @@ class GatedMLP(Part):
         with lib.section("gate_up"):
             act = ops.gated_linear(h, self.w_gate_up, self.interleaved)
         with lib.section("down"):
-            return ops.linear(act, self.w_down, partials_ok=True)
+            return ops.linear(act, self.w_down, partials_ok=True, deferred_ok=True)
 
 
 register_part("ffn", "gated_mlp", GatedMLP)

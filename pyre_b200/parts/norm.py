@@ -12,6 +12,8 @@ class RMSNorm(Part):
     the fp32 residual stream and receives the sum."""
 
     graph_safe = True
+    fuses_into_product = True     # forward takes ``scaled_ok``: with it, the norm may run as the fix-up of the product
+                                  # that ``delta`` stands for and hand its consumer ``ops.ScaledRows``
 
     def __init__(self, dtype, device, width: int, eps: float):
         super().__init__(dtype, device)
@@ -27,8 +29,8 @@ class RMSNorm(Part):
     def kernel_libraries(self):
         return ["elementwise"]
 
-    def forward(self, ctx, x, delta=None, rows=None, update_x=True):
-        return ops.add_rmsnorm(x, delta, self.weight, self.eps, self.dtype, rows=rows, update_x=update_x)
+    def forward(self, ctx, x, delta=None, rows=None, update_x=True, scaled_ok=False):
+        return ops.add_rmsnorm(x, delta, self.weight, self.eps, self.dtype, rows=rows, update_x=update_x, scaled_ok=scaled_ok)
 
 
 register_part("norm", "rms_norm", RMSNorm)

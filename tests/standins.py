@@ -15,7 +15,7 @@ def embedding(table, ids, out=None, err_flag=None):
     return table[ids.long()].float()
 
 
-def add_rmsnorm(x, delta, weight, eps, out_dtype, rows=None, update_x=True, out=None):
+def add_rmsnorm(x, delta, weight, eps, out_dtype, rows=None, update_x=True, out=None, scaled_ok=False):
     v = x if delta is None else x + delta.float()
     if rows is None and update_x and delta is not None:
         x.copy_(v)
@@ -129,10 +129,12 @@ def install(monkeypatch) -> None:
 
 def _partial_sums_or_tensor(t):
     from pyre_b200.kernels import ops
+    if isinstance(t, ops.DeferredProduct):      # a product not launched yet: the stand-ins never fold, they run it plainly
+        t = t.partials()
     return t.parts.sum(0) if isinstance(t, ops.PartialSums) else t.float()
 
 
-def add_rmsnorm_any(x, delta, weight, eps, out_dtype, rows=None, update_x=True, out=None):
+def add_rmsnorm_any(x, delta, weight, eps, out_dtype, rows=None, update_x=True, out=None, scaled_ok=False):
     return add_rmsnorm(x, None if delta is None else _partial_sums_or_tensor(delta), weight, eps, out_dtype, rows, update_x)
 
 
@@ -146,6 +148,8 @@ def qkv_rope_write_any(qkv, bias, cos, sin, cache_layer, slot_mapping, n_heads, 
 
 def materialize(t):
     from pyre_b200.kernels import ops
+    if isinstance(t, ops.DeferredProduct):
+        t = t.partials()
     return t.parts.sum(0).to(t.dtype) if isinstance(t, ops.PartialSums) else t
 
 

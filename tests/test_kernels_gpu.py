@@ -652,3 +652,80 @@ def test_attention_long_context(ops, nh, nkv, hd, page, window):
     ops.attention_prefill(q, cache, table, cu, positions, 2, 700, nh, nkv, hd, scale, window, other)
     ops.check_device_errors()
     check(other, slice(0, 700), "mma.sync prompt kernel")
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 3584, 3584), (8, 3584, 18944), (64, 896, 4864), (100, 200, 136), (128, 3584, 512), (5, 1160, 72)])
+def test_product_with_residual_and_norm_folded_in(ops, M, N, K):
+    """A product of few tokens launched by the norm that consumes it: the CTA that finishes a tile last adds the
+    splits' partial sums to the residual stream and leaves the next norm's activations without their 1/rms
+    (``ScaledRows``); the product that takes those applies the factor in its epilogue.  Against the same steps
+    in fp32, for several launches in a row (the arrival counters return to zero)."""
+    g = torch.Generator(device="cuda").manual_seed(3 * M + N)
+    a = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.03).to(torch.bfloat16)
+    gain = 1 + 0.1 * torch.randn(N, device="cuda", generator=g)
+    w_next = (torch.randn(256, N, device="cuda", generator=g) * 0.05).to(torch.bfloat16)
+    x0 = torch.randn(M, N, device="cuda", generator=g)
+    eps = 1e-5
+    for rep in range(3):
+        x = x0.clone()
+        prod = ops.linear(a, w, partials_ok=True, deferred_ok=True)
+        assert isinstance(prod, ops.DeferredProduct) == (M <= ops.FOLD_MAX_TOKENS)     # offered only where it pays
+        prod = ops.DeferredProduct(a, w, torch.bfloat16)
+        assert tuple(prod.shape) == (M, N)
+        h = ops.add_rmsnorm(x, prod, gain, eps, torch.bfloat16, scaled_ok=True)
+        ops.check_device_errors()
+        assert isinstance(h, ops.ScaledRows)
+        v = x0 + a.float() @ w.float().t()
+        scale = float(v.abs().max())
+        assert float((x - v).abs().max()) <= 2e-5 * scale * max(1.0, (K / 64) ** 0.5), f"launch {rep}: residual stream"
+        want = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * gain
+        torch.testing.assert_close(ops.materialize(h).float(), want, rtol=1.6e-2, atol=2e-3)
+        # the consumer applies the factor itself: plain product, split product, gated product
+        y = ops.linear(h, w_next)
+        torch.testing.assert_close(y.float(), want @ w_next.float().t(), rtol=2e-2, atol=2e-2 * float(want.abs().max()))
+        y_parts = ops.materialize(ops.linear(h, w_next, partials_ok=True))
+        torch.testing.assert_close(y_parts.float(), y.float(), rtol=1.6e-2, atol=1e-2)
+        if N % 8 == 0:
+            gu = ops.interleave_gate_up(w_next[:128], w_next[128:])
+            act = ops.gated_linear(h, gu, interleaved=True)
+            yy = want.to(torch.bfloat16).float() @ w_next.float().t()
+            ref = torch.nn.functional.silu(yy[:, :128]) * yy[:, 128:]
+            torch.testing.assert_close(act.float(), ref, rtol=3e-2, atol=3e-2 * float(ref.abs().max()))
+    # the same norm without the permission to fold gives plain tensors
+    x = x0.clone()
+    plain = ops.add_rmsnorm(x, ops.DeferredProduct(a, w, torch.bfloat16), gain, eps, torch.bfloat16)
+    assert isinstance(plain, torch.Tensor)
+    torch.testing.assert_close(plain.float(), want, rtol=1.6e-2, atol=2e-3)
+    ops.check_device_errors()
+
+
+@pytest.mark.parametrize("nh,nkv,hd,rot,page", [(28, 4, 128, 128, 16), (14, 2, 64, 64, 16), (3, 1, 32, 32, 8), (5, 2, 16, 16, 4),
+                                                (6, 3, 64, 0, 32), (7, 1, 128, 128, 64)])
+@pytest.mark.parametrize("T", [1, 8, 77])
+def test_product_with_rotary_and_cache_write_folded_in(ops, nh, nkv, hd, rot, page, T):
+    """The stacked q/k/v projection launched by ``qkv_rope_write``: bias, rotation and the paged write of keys and
+    values as the product's fix-up give bit for bit what the separate kernel gives on the same partial sums."""
+    g = torch.Generator(device="cuda").manual_seed(nh * 13 + T)
+    K = 264
+    width = (nh + 2 * nkv) * hd
+    a = torch.randn(T, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(width, K, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    bias = torch.randn(width, device="cuda", generator=g)
+    pos = torch.randint(0, 5000, (T,), device="cuda", generator=g, dtype=torch.int32)
+    inv = 1.0 / (1e4 ** (torch.arange(0, max(rot, 2), 2, device="cuda", dtype=torch.float32) / max(rot, 2)))
+    cos, sin = ops.rope_table(pos, inv) if rot else (None, None)
+    n_pages = -(-T // page) + 3
+    slots = torch.randperm(n_pages * page, device="cuda", generator=g)[:T].to(torch.int32).contiguous()
+    caches, qs = [], []
+    for fold in (True, False):
+        cache = torch.zeros(n_pages, 2, nkv, page, hd, device="cuda", dtype=torch.bfloat16)
+        prod = ops.DeferredProduct(a, w, torch.bfloat16)
+        qs.append(ops.qkv_rope_write(prod if fold else prod.partials(), bias, cos, sin, cache, slots, nh, nkv, hd, rot, page))
+        caches.append(cache)
+    ops.check_device_errors()
+    assert torch.equal(qs[0], qs[1]) and torch.equal(caches[0], caches[1])
+    assert float(caches[0].float().abs().sum()) > 0
+    # a layer that reads another layer's cache stores nothing
+    q_only = ops.qkv_rope_write(ops.DeferredProduct(a, w, torch.bfloat16), bias, cos, sin, None, None, nh, nkv, hd, rot, page)
+    assert torch.equal(q_only, qs[0])
