@@ -84,7 +84,10 @@ __device__ __forceinline__ void load_delta(Vec<float, VEC>& a, const T* dr, cons
     }
 }
 
-template <typename T, int VEC>
+// KEEP: vectors of the row that a thread keeps in registers between the sum of squares and the scaling (the row is
+// then read once; every global round trip counts in a kernel that handles a few rows of a decode step); 0: the row
+// is read again for the scaling (any width).
+template <typename T, int VEC, int KEEP>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ partials,
                                    int n_partials, long long partial_stride, const float* __restrict__ w,
                                    T* __restrict__ out, const int* __restrict__ rows, int H, float eps, int update_x) {
@@ -99,27 +102,59 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
     const bool has_delta = dr || pr;
     T* orow = out + (size_t)r * H;
 
+    [[maybe_unused]] Vec<float, VEC> kept[KEEP > 0 ? KEEP : 1];
     float ss = 0.f;
-    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
-        Vec<float, VEC> a = load_vec<float, VEC>(xr + i);
-        if (has_delta) {
-            load_delta<T, VEC>(a, dr, pr, n_partials, partial_stride, i);
-            if (update_x) store_vec<float, VEC>(xr + i, a);
-        }
+    if constexpr (KEEP > 0) {
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) ss = fmaf(a.v[k], a.v[k], ss);
+        for (int j = 0; j < KEEP; ++j) {
+            const int i = (threadIdx.x + j * blockDim.x) * VEC;
+            if (i < H) {
+                Vec<float, VEC> a = load_vec<float, VEC>(xr + i);
+                if (has_delta) {
+                    load_delta<T, VEC>(a, dr, pr, n_partials, partial_stride, i);
+                    if (update_x) store_vec<float, VEC>(xr + i, a);
+                }
+                kept[j] = a;
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) ss = fmaf(a.v[k], a.v[k], ss);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+            Vec<float, VEC> a = load_vec<float, VEC>(xr + i);
+            if (has_delta) {
+                load_delta<T, VEC>(a, dr, pr, n_partials, partial_stride, i);
+                if (update_x) store_vec<float, VEC>(xr + i, a);
+            }
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) ss = fmaf(a.v[k], a.v[k], ss);
+        }
     }
     const float total = block_sum(ss, scratch);
     const float rstd = 1.0f / sqrtf(total / (float)H + eps);
 
-    for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
-        Vec<float, VEC> a = load_vec<float, VEC>(xr + i);
-        if (has_delta && !update_x) load_delta<T, VEC>(a, dr, pr, n_partials, partial_stride, i);
-        Vec<float, VEC> g = load_vec<float, VEC>(w + i);
-        Vec<T, VEC> o;
+    if constexpr (KEEP > 0) {
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) o.v[k] = from_f32<T>(__fmul_rn(__fmul_rn(a.v[k], rstd), g.v[k]));
-        store_vec<T, VEC>(orow + i, o);
+        for (int j = 0; j < KEEP; ++j) {
+            const int i = (threadIdx.x + j * blockDim.x) * VEC;
+            if (i < H) {
+                Vec<float, VEC> g = load_vec<float, VEC>(w + i);
+                Vec<T, VEC> o;
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) o.v[k] = from_f32<T>(__fmul_rn(__fmul_rn(kept[j].v[k], rstd), g.v[k]));
+                store_vec<T, VEC>(orow + i, o);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x * VEC; i < H; i += blockDim.x * VEC) {
+            Vec<float, VEC> a = load_vec<float, VEC>(xr + i);
+            if (has_delta && !update_x) load_delta<T, VEC>(a, dr, pr, n_partials, partial_stride, i);
+            Vec<float, VEC> g = load_vec<float, VEC>(w + i);
+            Vec<T, VEC> o;
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) o.v[k] = from_f32<T>(__fmul_rn(__fmul_rn(a.v[k], rstd), g.v[k]));
+            store_vec<T, VEC>(orow + i, o);
+        }
     }
 }
 
@@ -135,11 +170,15 @@ PYRE_API int pyre_add_rmsnorm(float* x, const void* delta, const float* partials
     const bool vec = (H % 4 == 0);
     const int per = vec ? H / 4 : H;
     const int threads = min(512, max(32, ((per + 31) / 32) * 32));
-#define LAUNCH(TT, V) pyre_launch(add_rmsnorm_kernel<TT, V>, dim3(n_rows), dim3(threads), 0, stream, x, (const TT*)delta, partials, n_partials, partial_stride, weight, (TT*)out, rows, H, eps, update_x)
+    // a row of up to 4 vectors per thread stays in registers between the two passes (the same sums in the same order)
+    const int per_thread = ceil_div(per, threads);
+#define LAUNCH_K(TT, V, KP) pyre_launch(add_rmsnorm_kernel<TT, V, KP>, dim3(n_rows), dim3(threads), 0, stream, x, (const TT*)delta, partials, n_partials, partial_stride, weight, (TT*)out, rows, H, eps, update_x)
+#define LAUNCH(TT, V) do { if (per_thread <= 2) LAUNCH_K(TT, V, 2); else if (per_thread <= 4) LAUNCH_K(TT, V, 4); else LAUNCH_K(TT, V, 0); } while (0)
     if (dtype == PYRE_F32) { if (vec) LAUNCH(float, 4); else LAUNCH(float, 1); }
     else if (dtype == PYRE_BF16) { if (vec) LAUNCH(__nv_bfloat16, 4); else LAUNCH(__nv_bfloat16, 1); }
     else return PYRE_ERR_BAD_ARG;
 #undef LAUNCH
+#undef LAUNCH_K
     PYRE_LAUNCH_CHECK();
     return 0;
 }
