@@ -17,18 +17,23 @@ class Attention(Part):
 
     Parameters: ``width`` (model width), ``n_heads``, ``n_kv_heads``, ``head_dim``
     (``n_heads * head_dim`` need not equal ``width``), ``qkv_bias`` / ``o_bias``,
-    ``scale`` (default head_dim^-0.5, pyre/model.py:82), ``window`` (None = all keys)
-    and ``position``, the PartSpec of the position encoding applied to q and k.
+    ``scale`` (default head_dim^-0.5, pyre/model.py:82), ``window`` (None = all keys),
+    ``position``, the PartSpec of the position encoding applied to q and k, and ``names``, the checkpoint's
+    names of the four projections (default q_proj, k_proj, v_proj, o_proj: an architecture whose checkpoint
+    calls them otherwise says so in its builder, no new part needed).
     A query at position p sees keys max(0, p - window + 1)..p.
     """
+
+    DEFAULT_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"}
 
     graph_safe = True
     takes_scaled_rows = True      # ``h`` may be ``ops.ScaledRows``: the q/k/v product applies the norm's 1/rms itself
 
     def __init__(self, dtype, device, width: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: "PartSpec | None" = None, qkv_bias: bool = True, o_bias: bool = False,
-                 scale: "float | None" = None, window: "int | None" = None):
+                 scale: "float | None" = None, window: "int | None" = None, names: "dict[str, str] | None" = None):
         super().__init__(dtype, device)
+        self.names = dict(self.DEFAULT_NAMES, **(names or {}))
         self.width, self.n_heads, self.n_kv_heads, self.head_dim = int(width), int(n_heads), int(n_kv_heads), int(head_dim)
         if self.n_heads % self.n_kv_heads:
             raise ops.UnsupportedSize(f"{n_heads} query heads cannot be shared among {n_kv_heads} key/value heads")
@@ -51,27 +56,22 @@ class Attention(Part):
 
     def tensors(self):
         q, kv = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
-        t = {
-            "q_proj.weight": TensorSpec((q, self.width)),
-            "k_proj.weight": TensorSpec((kv, self.width)),
-            "v_proj.weight": TensorSpec((kv, self.width)),
-            "o_proj.weight": TensorSpec((self.width, q)),
-        }
-        if self.qkv_bias:
-            t["q_proj.bias"] = TensorSpec((q,), role="vector")
-            t["k_proj.bias"] = TensorSpec((kv,), role="vector")
-            t["v_proj.bias"] = TensorSpec((kv,), role="vector")
-        # checkpoint order: weight then bias per projection, o last
-        order = ["q_proj.weight", "q_proj.bias", "k_proj.weight", "k_proj.bias", "v_proj.weight", "v_proj.bias",
-                 "o_proj.weight"]
-        return {k: t[k] for k in order if k in t}
+        n = self.names
+        t = {}
+        # checkpoint order: weight then bias per projection, the output projection last
+        for key, rows in (("q", q), ("k", kv), ("v", kv)):
+            t[f"{n[key]}.weight"] = TensorSpec((rows, self.width))
+            if self.qkv_bias:
+                t[f"{n[key]}.bias"] = TensorSpec((rows,), role="vector")
+        t[f"{n['o']}.weight"] = TensorSpec((self.width, q))
+        return t
 
     def load(self, tensors):
-        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]],
-                               dim=0).contiguous()
+        n = self.names
+        self.w_qkv = torch.cat([tensors[f"{n[k]}.weight"] for k in "qkv"], dim=0).contiguous()
         if self.qkv_bias:
-            self.b_qkv = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]]).contiguous()
-        self.w_o = tensors["o_proj.weight"]
+            self.b_qkv = torch.cat([tensors[f"{n[k]}.bias"] for k in "qkv"]).contiguous()
+        self.w_o = tensors[f"{n['o']}.weight"]
 
     def kernel_libraries(self):
         libs = ["elementwise"]      # the position encoding, a sub-part, names its own

@@ -729,3 +729,72 @@ def test_product_with_rotary_and_cache_write_folded_in(ops, nh, nkv, hd, rot, pa
     # a layer that reads another layer's cache stores nothing
     q_only = ops.qkv_rope_write(ops.DeferredProduct(a, w, torch.bfloat16), bias, cos, sin, None, None, nh, nkv, hd, rot, page)
     assert torch.equal(q_only, qs[0])
+
+
+@pytest.mark.parametrize("kernel,dtype,nh,nkv,hd,page,window", [
+    ("generic", torch.float32, 6, 3, 48, 4, 37), ("generic", torch.bfloat16, 3, 1, 32, 8, 19), ("generic", torch.float32, 4, 2, 16, 16, 64),
+    ("mma", torch.bfloat16, 6, 3, 48, 4, 37), ("mma", torch.bfloat16, 7, 1, 128, 8, 50), ("mma", torch.bfloat16, 28, 4, 128, 16, 64),
+    ("prefill", torch.bfloat16, 6, 3, 128, 8, 50), ("prefill", torch.bfloat16, 4, 2, 64, 12, 37),
+    ("tc", torch.bfloat16, 6, 3, 128, 8, 50), ("tc", torch.bfloat16, 4, 1, 64, 4, 37), ("tc", torch.bfloat16, 28, 4, 128, 16, 64)])
+def test_window_edges_are_exact(ops, kernel, dtype, nh, nkv, hd, page, window):
+    """Both edges of a window, for a decode row and for a row in the middle of a prompt portion.  The first key inside
+    the window (position p - window + 1) carries a large score and a distinctive value: the output is that value.  The
+    key just outside (p - window) carries a larger score still, and so does a key one page further out: the output
+    must not move by a bit when those keys' values are exchanged (+40 against -40), which an off-by-one at the edge,
+    in the mask or in the tiles' range, could not survive."""
+    g = torch.Generator(device="cuda").manual_seed(nh * 7 + page)
+    ctx_lens, new = [301, 200], [1, 70]
+    n_pages = sum(-(-c // page) for c in ctx_lens) + 2
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(9)).tolist()
+    table = torch.full((2, max(-(-c // page) for c in ctx_lens)), -1, dtype=torch.int32)
+    for s_, c in enumerate(ctx_lens):
+        for lp in range(-(-c // page)):
+            table[s_, lp] = perm.pop()
+    table = table.cuda()
+    seq_of_token = torch.tensor([0] + [1] * 70, dtype=torch.int32, device="cuda")
+    positions = torch.tensor([300] + list(range(130, 200)), dtype=torch.int32, device="cuda")
+    cu = torch.tensor([0, 1, 71], dtype=torch.int32, device="cuda")
+    T = 71
+    q = torch.randn(T, nh * hd, device="cuda", generator=g)
+    master = torch.randn(n_pages, 2, nkv, page, hd, device="cuda", generator=g)
+    rows = [0, 1 + 35]                                   # the decode row; row 35 of the portion
+    inside_value = torch.linspace(-3, 3, hd, device="cuda")
+
+    def slot(s_, pos):
+        return int(table[s_, pos // page]), pos % page
+
+    def build(sign):
+        cache = master.clone()
+        for r in rows:
+            s_, p = int(seq_of_token[r]), int(positions[r])
+            qh = q[r, :hd] / q[r, :hd].norm() * hd ** 0.5      # head 0 of the row, which reads key/value head 0
+            pg, off = slot(s_, p - window + 1)
+            cache[pg, 0, 0, off], cache[pg, 1, 0, off] = qh * 6.0, inside_value
+            for outside in (p - window, p - window - page):      # just outside, and a page further out
+                pg, off = slot(s_, outside)
+                cache[pg, 0, 0, off], cache[pg, 1, 0, off] = qh * 9.0, sign * 40.0
+        return cache.to(dtype)
+
+    qd = q.clone()
+    for r in rows:
+        qd[r, :hd] = q[r, :hd] / q[r, :hd].norm() * hd ** 0.5
+    qd = qd.to(dtype)
+    scale = hd ** -0.5
+
+    def run(cache):
+        if kernel == "generic":
+            return ops.paged_attention_generic(qd, cache, table, seq_of_token, positions, nh, nkv, hd, scale, window)
+        out = torch.zeros_like(qd)
+        if kernel == "mma":
+            return ops.paged_attention_mma(qd, cache, table, cu, positions, 2, nh, nkv, hd, scale, window, 3, out=out)
+        if kernel == "prefill":
+            return ops.attention_prefill(qd, cache, table, cu, positions, 2, 70, nh, nkv, hd, scale, window, out, min_len=32)
+        return ops.attention_prefill_tc(qd, cache, table, cu, positions, 2, 70, nh, nkv, hd, scale, window, out, min_len=64)
+
+    a, b = run(build(+1.0)), run(build(-1.0))
+    ops.check_device_errors()
+    for r in rows if kernel in ("generic", "mma") else rows[1:]:      # the prompt-portion kernels take the long entry only
+        head0 = a[r, :hd].float()
+        assert torch.equal(a[r], b[r]), f"row {r}: a key outside the window reaches the output"
+        assert (head0 - inside_value).abs().max() < 0.05 * 3 + (0.02 if dtype == torch.float32 else 0.06), \
+            f"row {r}: the first key inside the window does not decide (max diff {(head0 - inside_value).abs().max():.3f})"

@@ -61,3 +61,27 @@ def test_schedules_that_cannot_work_are_refused():
     with pytest.raises(ValueError, match="names block 3"):
         spec = architecture("Qwen2ForCausalLM").build(config_from_dict(RAW))
         type(spec)(spec.embed, spec.blocks, spec.final_norm, spec.head, schedule=[LayerCall(3)])
+
+
+def test_checkpoint_names_of_the_projections_are_parameters():
+    """An architecture whose checkpoint calls the projections otherwise sets ``names`` in its builder; the parts stay
+    the same classes.  Here layer 0 of the decoder gets other names, layer 1 keeps the defaults."""
+    from pyre_b200.config import architecture, config_from_dict
+    from pyre_b200.models.model import tensor_table
+    from pyre_b200.parts import PartSpec
+    import helpers as H
+    spec = architecture("Qwen2ForCausalLM").build(config_from_dict(H.TINY_A))
+    b = spec.blocks[0]
+    mixer = PartSpec("attention", dict(b.params["mixer"].params, names={"q": "wq", "k": "wk", "v": "wv", "o": "wo"}))
+    ffn = PartSpec("gated_mlp", dict(b.params["ffn"].params, names={"gate": "w1", "up": "w3", "down": "w2"}))
+    spec.blocks[0] = PartSpec(b.kind, dict(b.params, mixer=mixer, ffn=ffn))
+    table = tensor_table(spec)
+    for name in ("self_attn.wq.weight", "self_attn.wq.bias", "self_attn.wk.weight", "self_attn.wv.bias", "self_attn.wo.weight",
+                 "mlp.w1.weight", "mlp.w3.weight", "mlp.w2.weight"):
+        assert "model.layers.0." + name in table
+    assert "model.layers.0.self_attn.q_proj.weight" not in table and "model.layers.0.self_attn.wo.bias" not in table
+    assert "model.layers.1.self_attn.q_proj.weight" in table and "model.layers.1.mlp.down_proj.weight" in table
+    assert table["model.layers.0.mlp.w2.weight"].shape == (H.TINY_A["hidden_size"], H.TINY_A["intermediate_size"])
+    # the order of a layer's tensors is the checkpoint's: weight then bias per projection, the output projection last
+    layer0 = [n for n in table if n.startswith("model.layers.0.self_attn.")]
+    assert layer0 == ["model.layers.0.self_attn." + n for n in ("wq.weight", "wq.bias", "wk.weight", "wk.bias", "wv.weight", "wv.bias", "wo.weight")]
