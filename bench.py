@@ -399,10 +399,11 @@ def run_workload(args) -> dict:
         outs_len = [int(rng.integers(64, 513)) for _ in range(n_req)]
         need = sum(len(p) + o for p, o in zip(prompts, outs_len))
         eng = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=int(need * args.cache_fraction),
-                     max_num_seqs=64, max_num_batched_tokens=4096, prefill_chunk=2048, max_model_len=8192)
+                     max_num_seqs=64, max_num_batched_tokens=4096, prefill_chunk=2048, max_model_len=8192, record_steps=True)
         params = [SamplingParams(max_new_tokens=o, ignore_eos=True) for o in outs_len]
         eng.generate(prompts[:2], params[:2])       # warm-up: builds, graphs of small shapes
         torch.cuda.synchronize()
+        eng.step_log.clear()
         t0 = time.perf_counter()
         res = eng.generate(prompts, params)
         torch.cuda.synchronize()
@@ -411,12 +412,21 @@ def run_workload(args) -> dict:
         eng.cache.check()
         n_out = sum(len(r.token_ids) for r in res)
         n_in = sum(len(p) for p in prompts)
+        # the host's share: its own work per step against the time it spent waiting for the GPU.  Steps with prompt
+        # tokens run kernel by kernel (hundreds of launches), decode-only steps replay a captured graph.
+        log = eng.step_log
+        mixed = [r for r in log if r["prompt_tokens"]]
+        host = {"steps": len(log), "steps_with_prompt_tokens": len(mixed),
+                "host_ms_total": round(sum(r["host_ms"] for r in log), 1), "wait_ms_total": round(sum(r["wait_ms"] for r in log), 1),
+                "host_ms_per_prompt_step": round(sum(r["host_ms"] for r in mixed) / max(1, len(mixed)), 3),
+                "host_ms_per_decode_step": round(sum(r["host_ms"] for r in log if not r["prompt_tokens"]) / max(1, len(log) - len(mixed)), 3),
+                "steps_the_host_did_not_wait_in": sum(1 for r in log if r["wait_ms"] < 0.05)}
         return {"workload": "serve14b", "layers": cfg.num_hidden_layers, "requests": n_req, "prompt_tokens": n_in,
                 "output_tokens": n_out, "seconds": round(dt, 3), "output_tok_s": round(n_out / dt, 1),
                 "total_tok_s": round((n_in + n_out) / dt, 1), "steps": st["steps"], "preempted": st["preempted"],
                 "cache_tokens": int(need * args.cache_fraction), "finished": sum(r.finish_reason == "length" for r in res),
                 "graph_captures": eng.stepper.graph_captures, "graph_replays": eng.stepper.graph_replays,
-                "capture_seconds": round(eng.stepper.capture_seconds, 3)}
+                "capture_seconds": round(eng.stepper.capture_seconds, 3), "host": host}
     raw = dict(SHAPES["32b"])
     if args.layers:
         raw["num_hidden_layers"] = args.layers

@@ -391,10 +391,15 @@ __global__ void qkv_rope_write_full_kernel(const T* __restrict__ qkv, const floa
         float a1[VEC], a2[VEC];
         load_qkv_vec<T, VEC>(a1, in, pin, n_partials, partial_stride, h * hd + d0);
         load_qkv_vec<T, VEC>(a2, in, pin, n_partials, partial_stride, h * hd + d0 + half);
+        // bias, cos and sin come four floats at a time (VEC is 4 or 8 and d0 a multiple of it)
         if (bias) {
             const float* b = bias + (size_t)h * hd;
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) { a1[k] = a1[k] + b[d0 + k]; a2[k] = a2[k] + b[d0 + half + k]; }
+            for (int k4 = 0; k4 < VEC; k4 += 4) {
+                const Vec<float, 4> b1 = load_vec<float, 4>(b + d0 + k4), b2 = load_vec<float, 4>(b + d0 + half + k4);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { a1[k4 + k] = a1[k4 + k] + b1.v[k]; a2[k4 + k] = a2[k4 + k] + b2.v[k]; }
+            }
         }
         Vec<T, VEC> o1, o2;
         if (is_v) {
@@ -402,10 +407,14 @@ __global__ void qkv_rope_write_full_kernel(const T* __restrict__ qkv, const floa
             for (int k = 0; k < VEC; ++k) { o1.v[k] = from_f32<T>(a1[k]); o2.v[k] = from_f32<T>(a2[k]); }
         } else {
 #pragma unroll
-            for (int k = 0; k < VEC; ++k) {
-                const float c = ct[d0 + k], s_ = st[d0 + k];
-                o1.v[k] = from_f32<T>(__fadd_rn(__fmul_rn(a1[k], c), __fmul_rn(-a2[k], s_)));
-                o2.v[k] = from_f32<T>(__fadd_rn(__fmul_rn(a2[k], c), __fmul_rn(a1[k], s_)));
+            for (int k4 = 0; k4 < VEC; k4 += 4) {
+                const Vec<float, 4> c4 = load_vec<float, 4>(ct + d0 + k4), s4 = load_vec<float, 4>(st + d0 + k4);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float c = c4.v[k], s_ = s4.v[k];
+                    o1.v[k4 + k] = from_f32<T>(__fadd_rn(__fmul_rn(a1[k4 + k], c), __fmul_rn(-a2[k4 + k], s_)));
+                    o2.v[k4 + k] = from_f32<T>(__fadd_rn(__fmul_rn(a2[k4 + k], c), __fmul_rn(a1[k4 + k], s_)));
+                }
             }
         }
         store_vec<T, VEC>(dst + d0, o1);

@@ -89,6 +89,7 @@ class Engine:
         self._err_turn = 0
         self.step_log: "list[dict] | None" = [] if ec.record_steps else None
         self.kernel_times: dict = {}      # with time_kernels: class -> {"us": device time so far, "launches": n}
+        self._waited = 0.0                # seconds of the current call spent waiting for a step's ids
 
     def _pages_for_memory(self, ec: EngineConfig) -> int:
         """Pages of a group that keeps every token, so that all pools and state buffers together take
@@ -151,6 +152,7 @@ class Engine:
         one token too many (dropped).  The ids are the same either way."""
         sched = self.scheduler
         t_call = time.perf_counter()
+        self._waited = 0.0
         plan = sched.schedule()
         flight = None
         if plan:
@@ -195,8 +197,11 @@ class Engine:
                 acc["us"] += t["us"]
                 acc["launches"] += t["launches"]
         if self.step_log is not None and plan:
+            # host_ms: the call's own work (planning, laying out, launching); wait_ms: the part of the call spent
+            # waiting for an earlier step's ids.  While wait_ms is well above zero the GPU is the slower side.
             self.step_log.append(step_record(sched.stats.steps - 1, plan, self.cache, sched.stats,
-                                             time.perf_counter() - t_call))
+                                             time.perf_counter() - t_call - self._waited))
+            self.step_log[-1]["wait_ms"] = round(self._waited * 1e3, 3)
             if step_kernels is not None:
                 self.step_log[-1]["kernel_us"] = {cls: round(t["us"], 1) for cls, t in step_kernels.items()}
         outs = []
@@ -212,7 +217,9 @@ class Engine:
     def _land(self, flight) -> None:
         """Read the ids of a started step and let the scheduler record them."""
         plan, ticket, err = flight
+        t_wait = time.perf_counter()
         ids = self.sampler.read(ticket) if ticket is not None else []
+        self._waited += time.perf_counter() - t_wait      # the host had nothing left to do but wait for the GPU
         if ticket is not None and int(err[0]) != 0:
             self.stepper.check_device_errors()      # raises with the kernel's reason
         self.scheduler.resolve(plan, ids)

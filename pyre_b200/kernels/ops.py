@@ -110,16 +110,29 @@ def materialize(t: "torch.Tensor | PartialSums | DeferredProduct | ScaledRows") 
     return out
 
 
+# A step of prompt portions is a few hundred launches from Python, so the two questions every launch asks (which
+# stream, which device) go to torch's C layer directly where it offers that (a fraction of a microsecond instead of
+# several); the public calls stand in where it does not.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
+def _current_device() -> int:
+    return _raw_device() if _raw_device is not None else torch.cuda.current_device()
+
+
 def _stream() -> int:
     """The current stream of the current device.  Kernels are launched in the current device's
     context, so the tensors of a call must live there (``_check`` refuses others)."""
+    if _raw_stream is not None:
+        return _raw_stream(_current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
 def require_current_device(device, what: str = "a tensor") -> None:
     """Raise on the host if ``device`` (a CUDA device) is not the current one.  A kernel launched
     on another device's stream with this device's pointers would fault on the GPU instead."""
-    current = torch.cuda.current_device()
+    current = _current_device()
     index = device.index if device.index is not None else current
     if index != current:
         raise ValueError(f"{what} is on cuda:{index} but the current device is cuda:{current}; "
@@ -382,14 +395,18 @@ MMA_MAX_HEAD_DIM = 128
 CLUSTER_MAX_SPLITS = 16      # splits of one group merge through a thread-block cluster up to this many
 _DEFAULT_SM_COUNT = 148     # a B200; used only where no device can be asked (planning on a host without a GPU)
 _sm_counts: dict = {}
+_have_cuda: "bool | None" = None
 
 
 def sm_count(device=None) -> int:
     """Multiprocessors of ``device`` (default: the current one), as the launch code asks the device
     too; the planners below size splits and rounds of tiles by it."""
-    if not torch.cuda.is_available():
+    global _have_cuda
+    if _have_cuda is None:
+        _have_cuda = torch.cuda.is_available()
+    if not _have_cuda:
         return _DEFAULT_SM_COUNT
-    index = torch.cuda.current_device() if device is None or torch.device(device).index is None else torch.device(device).index
+    index = _current_device() if device is None or torch.device(device).index is None else torch.device(device).index
     n = _sm_counts.get(index)
     if n is None:
         n = _sm_counts[index] = int(torch.cuda.get_device_properties(index).multi_processor_count) or _DEFAULT_SM_COUNT
@@ -584,7 +601,7 @@ _error_flags: dict = {}
 
 def device_error_flag(device) -> torch.Tensor:
     """One int32 per device that kernels raise when a bounded wait runs out or an index is out of range."""
-    key = torch.device(device).index or 0
+    key = (device.index if isinstance(device, torch.device) else torch.device(device).index) or 0
     flag = _error_flags.get(key)
     if flag is None:
         flag = torch.zeros(1, dtype=torch.int32, device=device)
@@ -706,7 +723,7 @@ def _scale_fields(fx: "lib.GemmFix", x: "ScaledRows") -> None:
 
 def gemm_tc(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
             plan: "tuple[bool, int, int] | None" = None, reduce: bool = True, gated: bool = False,
-            pair: "bool | None" = None) -> torch.Tensor:
+            pair: "bool | None" = None, checked: bool = False) -> torch.Tensor:
     """y = x w^T on the tensor cores (tcgen05, TMEM accumulators, TMA-fed), bf16 in, fp32 accumulate.
 
     With a split K the kernel leaves fp32 partial sums [splits, M, N]; ``reduce`` adds
@@ -724,7 +741,7 @@ def gemm_tc(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: torch.dt
         x = scaled.rows
         if x.shape[0] > 128:
             x, scaled = materialize(scaled), None
-    if not tc_gemm_supported(x, w):
+    if not checked and not tc_gemm_supported(x, w):      # ``checked``: the caller has asked already
         raise UnsupportedSize("gemm_tc needs bf16 operands with K and leading dimensions that are multiples of 8")
     M, K = x.shape
     N, K2 = w.shape
@@ -879,7 +896,7 @@ def linear(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: "torch.dt
         if deferred_ok and FOLD_SMALL_KERNELS and rows.shape[0] <= FOLD_MAX_TOKENS and w.shape[0] % 4 == 0 \
                 and out_dtype in (None, torch.bfloat16):
             return DeferredProduct(x, w, torch.bfloat16)
-        return gemm_tc(x, w, out_dtype or torch.bfloat16, reduce=not partials_ok)
+        return gemm_tc(x, w, out_dtype or torch.bfloat16, reduce=not partials_ok, checked=True)
     x = materialize(x)
     if out_dtype is None or out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
@@ -900,5 +917,5 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, interleaved: bool) ->
     tensor-core product apply the activation in its epilogue."""
     rows = x.rows if isinstance(x, ScaledRows) else x
     if interleaved and x.dtype == torch.bfloat16 and USE_TC_GEMM and tc_gemm_supported(rows, w_gate_up):
-        return gemm_tc(x, w_gate_up, torch.bfloat16, gated=True)
+        return gemm_tc(x, w_gate_up, torch.bfloat16, gated=True, checked=True)
     return silu_mul(linear(x, w_gate_up), block=GATED_BLOCK if interleaved else 0)

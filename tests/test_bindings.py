@@ -88,7 +88,7 @@ def test_a_tensor_on_another_device_is_refused_on_the_host(monkeypatch):
     from pyre_b200.engine import step
     from pyre_b200.kernels import ops
 
-    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
+    monkeypatch.setattr(ops, "_current_device", lambda: 0)
     ops.require_current_device(torch.device("cuda:0"))
     ops.require_current_device(torch.device("cuda"))          # no index: the current device
     with pytest.raises(ValueError, match=r"cuda:1 but the current device is cuda:0"):
