@@ -153,7 +153,7 @@ def materialize(t):
     return t.parts.sum(0).to(t.dtype) if isinstance(t, ops.PartialSums) else t
 
 
-def gemm_tc(x, w, out_dtype=torch.bfloat16, plan=None, reduce=True, gated=False, pair=None):
+def gemm_tc(x, w, out_dtype=torch.bfloat16, plan=None, reduce=True, gated=False, pair=None, checked=False):
     from pyre_b200.kernels import ops
     assert x.dtype == w.dtype == torch.bfloat16 and x.shape[1] == w.shape[1]
     M, K = x.shape
