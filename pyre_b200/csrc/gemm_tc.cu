@@ -391,10 +391,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         [[maybe_unused]] const int epi_tid = quarter * 32 + lane;
         [[maybe_unused]] int scaled_y0 = -1;
         [[maybe_unused]] bool in_step = false;     // the epilogue warps synchronise among themselves in this launch
-        if constexpr (X_CONTIGUOUS_OUT) {
-            in_step = p.gated || p.scale_ssq != nullptr || p.fix != 0;
-            if (p.scale_ssq != nullptr || p.fix != 0) pdl_wait();     // these warps read what earlier kernels wrote
-        }
+        if constexpr (X_CONTIGUOUS_OUT) in_step = p.gated || p.scale_ssq != nullptr || p.fix != 0;
+        if (p.scale_ssq != nullptr || p.fix != 0) pdl_wait();     // these warps read what earlier kernels wrote
         for (int tile = worker; tile < n_tiles && alive; tile += n_workers, ++j) {
             const int buf = j & 1;
             const int x0 = (tile % p.tiles_x) * (BM * CTAS) + rank * BM, y0 = (tile / p.tiles_x) * BN;
@@ -415,6 +413,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     rstd_s[epi_tid] = rs;
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     scaled_y0 = y0;
+                }
+            }
+            // row store: a thread owns a token row, so the row's 1/rms is the thread's own (sums of squares added in
+            // tile order), looked up while the tile's main loop still runs
+            [[maybe_unused]] float row_scale = 1.f;
+            [[maybe_unused]] float row_ssq = 0.f;        // fix == 1: this row's sum of squares over the tile's columns
+            if constexpr (!X_CONTIGUOUS_OUT) {
+                if (p.scale_ssq != nullptr && xr < p.x_rows) {
+                    float ssq = 0.f;
+                    for (int i = 0; i < p.scale_tiles; ++i) ssq += p.scale_ssq[(size_t)i * p.x_rows + xr];
+                    row_scale = 1.0f / sqrtf(ssq / p.scale_n + p.scale_eps);
                 }
             }
             bool ok = true;
@@ -456,6 +465,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     }
                 }
             };
+            // Row store with the residual add folded in (fix == 1, one split): the 16 accumulator values of columns
+            // yc .. yc + 15 of this thread's row become v = resid + product (written back to the fp32 stream), the
+            // value that goes on to the store is v * norm_w (the next norm's activations without their 1/rms), and
+            // the row's sum of squares grows by v^2
+            // (`pre`: the row's residual values of these columns, fetched ahead by the caller, or null)
+            [[maybe_unused]] auto fold16 = [&](uint32_t (&r)[16], int yc, const float4* pre) {
+                if constexpr (!X_CONTIGUOUS_OUT) {
+                    if (!alive || xr >= p.x_rows) return;
+                    float* xp = p.resid + (size_t)xr * p.y_rows + yc;
+                    const float* wp = p.norm_w + yc;
+                    if (yc + 16 <= p.y_rows) {
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            float4 v = pre ? pre[q4] : *reinterpret_cast<const float4*>(xp + 4 * q4);
+                            const float4 w4 = *reinterpret_cast<const float4*>(wp + 4 * q4);
+                            v.x += __uint_as_float(r[4 * q4]); v.y += __uint_as_float(r[4 * q4 + 1]);
+                            v.z += __uint_as_float(r[4 * q4 + 2]); v.w += __uint_as_float(r[4 * q4 + 3]);
+                            *reinterpret_cast<float4*>(xp + 4 * q4) = v;
+                            row_ssq = fmaf(v.w, v.w, fmaf(v.z, v.z, fmaf(v.y, v.y, fmaf(v.x, v.x, row_ssq))));
+                            r[4 * q4] = __float_as_uint(__fmul_rn(v.x, w4.x)); r[4 * q4 + 1] = __float_as_uint(__fmul_rn(v.y, w4.y));
+                            r[4 * q4 + 2] = __float_as_uint(__fmul_rn(v.z, w4.z)); r[4 * q4 + 3] = __float_as_uint(__fmul_rn(v.w, w4.w));
+                        }
+                    } else {
+                        for (int q = 0; q < 16 && yc + q < p.y_rows; ++q) {
+                            const float v = xp[q] + __uint_as_float(r[q]);
+                            xp[q] = v;
+                            row_ssq = fmaf(v, v, row_ssq);
+                            r[q] = __float_as_uint(__fmul_rn(v, wp[q]));
+                        }
+                    }
+                }
+            };
             if constexpr (!X_CONTIGUOUS_OUT && BN == 256) {
                 if (p.gated) {
                     // the tile's columns are two blocks of 64 gate features followed by the 64 up features of the
@@ -477,8 +518,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                                 float o[2];
 #pragma unroll
                                 for (int e = 0; e < 2; ++e) {
-                                    const float z = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[2 * q + e])));
-                                    const float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[2 * q + e])));
+                                    const float z = __bfloat162float(__float2bfloat16_rn(__uint_as_float(g[2 * q + e]) * row_scale));
+                                    const float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[2 * q + e]) * row_scale));
                                     o[e] = __fmul_rn(z / (1.0f + expf(-z)), v);
                                 }
                                 __nv_bfloat162 pr = __floats2bfloat162_rn(o[0], o[1]);
@@ -551,15 +592,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll 1
                     for (int gq = 0; gq < whole; ++gq) {
                         uint32_t w[GW / 2];
+                        // the fold's residual values of the whole group go out at once: one round trip to memory per
+                        // group of GW columns, not one per 16
+                        float4 xg[GW / 4];
+                        const bool prefetched = p.fix == 1 && alive && xr < p.x_rows;
+                        if (prefetched) {
+                            const float4* src = reinterpret_cast<const float4*>(p.resid + (size_t)xr * p.y_rows + y0 + gq * GW);
+#pragma unroll
+                            for (int i = 0; i < GW / 4; ++i) xg[i] = src[i];
+                        }
 #pragma unroll
                         for (int cc = 0; cc < GW; cc += 16) {
                             uint32_t r[16];
                             __syncwarp();
                             tmem_ld16(acc + gq * GW + cc, r);
                             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                            if (p.fix == 1) fold16(r, y0 + gq * GW + cc, prefetched ? &xg[cc / 4] : nullptr);
 #pragma unroll
                             for (int q = 0; q < 8; ++q) {
-                                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * q]), __uint_as_float(r[2 * q + 1]));
+                                __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * q]) * row_scale, __uint_as_float(r[2 * q + 1]) * row_scale);
                                 w[cc / 2 + q] = *reinterpret_cast<uint32_t*>(&v);
                             }
                         }
@@ -578,6 +629,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 } else {
 #pragma unroll
                     for (int q = 0; q < 16; ++q) r[q] = 0u;
+                }
+                if constexpr (!X_CONTIGUOUS_OUT) {
+                    if (p.fix == 1) fold16(r, y0 + c, nullptr);
+                    if (p.scale_ssq != nullptr) {
+#pragma unroll
+                        for (int q = 0; q < 16; ++q) r[q] = __float_as_uint(__uint_as_float(r[q]) * row_scale);
+                    }
                 }
                 if (!alive || xr >= p.x_rows) {
                     // nothing to store for this thread
@@ -627,6 +685,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) hand_back(buf);
+            if constexpr (!X_CONTIGUOUS_OUT) {
+                if (p.fix == 1 && alive && xr < p.x_rows) p.ssq_out[(size_t)(tile / p.tiles_x) * p.x_rows + xr] = row_ssq;
+            }
             if constexpr (X_CONTIGUOUS_OUT && BN <= 128) {
                 if (p.fix != 0) {
                     // ---- fix-up: every split of this tile has stored its partial sums; the CTA that arrives last
@@ -860,7 +921,12 @@ static int gemm_tc_impl(const void* X, int x_rows, long long ldx, const void* Y,
                         int splits, int bn, int x_is_constant, int gated, int pair, int* err_flag, const PyreGemmFix* fx,
                         cudaStream_t stream) {
     if (x_rows <= 0 || y_rows <= 0) return 0;
-    if (fx && (fx->fix != 0 || fx->scale_ssq != nullptr)) {
+    if (fx && (fx->fix != 0 || fx->scale_ssq != nullptr) && stride_x != 1) {
+        // row store (tokens on the rows): every thread of the epilogue owns a token row, so the row scale and the
+        // residual fold (fix == 1) need no exchange between CTAs; one split, no gate with the fold, bf16 out
+        if (fx->scale_ssq && fx->scale_tiles < 1) return PYRE_ERR_BAD_ARG;
+        if (fx->fix != 0 && (fx->fix != 1 || splits != 1 || gated || out_f32 || !fx->resid || !fx->norm_w || !fx->ssq_out)) return PYRE_ERR_BAD_ARG;
+    } else if (fx && (fx->fix != 0 || fx->scale_ssq != nullptr)) {
         if (stride_x != 1 || bn > 128 || y_rows > bn || pair) return PYRE_ERR_BAD_ARG;      // transposed store, one tile of tokens
         if (fx->scale_ssq && fx->scale_tiles < 1) return PYRE_ERR_BAD_ARG;
         if (fx->fix != 0) {

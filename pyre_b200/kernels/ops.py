@@ -198,7 +198,7 @@ def add_rmsnorm(x: torch.Tensor, delta: "torch.Tensor | None", weight: torch.Ten
         if tuple(delta.shape) != (T, H):
             raise ValueError(f"delta shape {tuple(delta.shape)} != x shape {(T, H)}")
         if scaled_ok and rows is None and update_x and out is None and out_dtype == torch.bfloat16 and H % 8 == 0 \
-                and H <= 128 * _MAX_FIX_TILES:
+                and H <= 128 * _MAX_FIX_TILES and folds_residual(T, H, delta.x.shape[1]):
             return gemm_residual_norm(delta, x, weight, eps)
         delta = delta.partials()
     parts, n_parts, part_stride = None, 0, 0
@@ -258,8 +258,8 @@ def qkv_rope_write(qkv: torch.Tensor, bias: "torch.Tensor | None", cos: torch.Te
     store nothing (a layer that reads another layer's cache)."""
     if isinstance(qkv, DeferredProduct):
         width = (n_heads + 2 * n_kv_heads) * head_dim
-        if q_out is None and qkv.shape[1] == width and 128 % head_dim == 0 and head_dim % 8 == 0 and rotary_dim in (0, head_dim) \
-                and width <= 128 * _MAX_FIX_TILES:
+        if q_out is None and qkv.shape[0] <= 128 and qkv.shape[1] == width and 128 % head_dim == 0 and head_dim % 8 == 0 \
+                and rotary_dim in (0, head_dim) and width <= 128 * _MAX_FIX_TILES:
             return gemm_rope_write(qkv, bias, cos, sin, cache_layer, slot_mapping, n_heads, n_kv_heads, head_dim,
                                    rotary_dim, page_size)
         qkv = qkv.partials()
@@ -734,13 +734,11 @@ def gemm_tc(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: torch.dt
     result is silu(x gate^T) * (x up^T), [M, N / 2] bf16.  The activation runs in the product's
     epilogue (whole tiles, one split: the usual case in both orientations), otherwise after it.
 
-    ``x`` may be ``ScaledRows`` (at most 128 tokens): the result rows are scaled by the tokens' 1/rms in the
-    epilogue, before the activation of a gated product."""
+    ``x`` may be ``ScaledRows``: the result rows are scaled by the tokens' 1/rms in the epilogue, before the
+    activation of a gated product."""
     scaled = x if isinstance(x, ScaledRows) else None
     if scaled is not None:
         x = scaled.rows
-        if x.shape[0] > 128:
-            x, scaled = materialize(scaled), None
     if not checked and not tc_gemm_supported(x, w):      # ``checked``: the caller has asked already
         raise UnsupportedSize("gemm_tc needs bf16 operands with K and leading dimensions that are multiples of 8")
     M, K = x.shape
@@ -748,7 +746,7 @@ def gemm_tc(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: torch.dt
     if K != K2:
         raise ValueError(f"inner sizes differ: x is [{M}, {K}], w is [{N}, {K2}]")
     weights_as_rows, bn, splits = plan or tc_gemm_plan(M, N, K)
-    if scaled is not None and (not weights_as_rows or M > bn):
+    if scaled is not None and weights_as_rows and M > bn:      # several tiles of tokens on the narrow side: not served
         x, scaled = materialize(scaled), None
     splits = max(1, min(splits, -(-K // 64)))
     if pair is None:
@@ -798,9 +796,10 @@ def gemm_tc(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: torch.dt
     return materialize(PartialSums(target, out_dtype))
 
 
-def _launch_with_fixup(prod: DeferredProduct, fx: "lib.GemmFix") -> None:
-    """The product of a ``DeferredProduct`` (weights on the MMA's rows, all tokens in one tile, K split as the
-    plan says) into fp32 partial sums that only its own fix-up reads."""
+def _launch_with_fixup(prod: DeferredProduct, fx: "lib.GemmFix", rows_out: "torch.Tensor | None" = None) -> None:
+    """The product of a ``DeferredProduct`` with work folded in.  Few tokens (weights on the MMA's rows, all tokens
+    in one tile, K split as the plan says): fp32 partial sums that only the kernel's own fix-up reads.  Many tokens
+    (tokens on the rows, one split): the epilogue itself folds, and what it stores is ``rows_out``."""
     x = prod.x
     if isinstance(x, ScaledRows):
         _scale_fields(fx, x)
@@ -808,13 +807,34 @@ def _launch_with_fixup(prod: DeferredProduct, fx: "lib.GemmFix") -> None:
     w = prod.w
     M, K = x.shape
     N = w.shape[0]
-    _rows, bn, splits = tc_gemm_plan(M, N, K)
-    splits = max(1, min(splits, -(-K // 64)))
-    parts = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
-    fx.tile_counters = _tile_counters(x.device).data_ptr()
+    weights_as_rows, bn, splits = tc_gemm_plan(M, N, K)
+    err = device_error_flag(x.device).data_ptr()
     with lib.section(prod.section):
-        lib.call("pyre_gemm_tc", w.data_ptr(), N, w.stride(0), x.data_ptr(), M, x.stride(0), K, parts.data_ptr(), 1,
-                 1, N, M * N, splits, bn, 1, 0, 0, device_error_flag(x.device).data_ptr(), ctypes.byref(fx), _stream())
+        if weights_as_rows:
+            splits = max(1, min(splits, -(-K // 64)))
+            parts = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+            fx.tile_counters = _tile_counters(x.device).data_ptr()
+            lib.call("pyre_gemm_tc", w.data_ptr(), N, w.stride(0), x.data_ptr(), M, x.stride(0), K, parts.data_ptr(), 1,
+                     1, N, M * N, splits, bn, 1, 0, 0, err, ctypes.byref(fx), _stream())
+        else:
+            if splits != 1 or rows_out is None:
+                raise UnsupportedSize("a product of many tokens folds only with one split and the residual fix-up")
+            pair = int(CTA_PAIRS and bn in (128, 160, 192, 208, 224, 256))
+            lib.call("pyre_gemm_tc", x.data_ptr(), M, x.stride(0), w.data_ptr(), N, w.stride(0), K, rows_out.data_ptr(), 0,
+                     N, 1, 0, 1, bn, 0, 0, pair, err, ctypes.byref(fx), _stream())
+
+
+def folds_residual(M: int, N: int, K: int) -> bool:
+    """Does a product of this shape take the residual add and the next norm's preparation as folded work?  Very few
+    tokens (the fix-up of the last CTA per tile), or many tokens in one split (the epilogue's threads own token rows)."""
+    if not FOLD_SMALL_KERNELS or N % 8:
+        return False
+    if M <= FOLD_MAX_TOKENS:
+        return True
+    if M <= 128:
+        return False
+    weights_as_rows, _bn, splits = tc_gemm_plan(M, N, K)
+    return not weights_as_rows and splits == 1
 
 
 def gemm_residual_norm(prod: DeferredProduct, x: torch.Tensor, weight: torch.Tensor, eps: float) -> ScaledRows:
@@ -827,7 +847,12 @@ def gemm_residual_norm(prod: DeferredProduct, x: torch.Tensor, weight: torch.Ten
     fx = lib.GemmFix()
     fx.fix = 1
     fx.resid, fx.norm_w, fx.h_out, fx.ssq_out = x.data_ptr(), weight.data_ptr(), rows.data_ptr(), ssq.data_ptr()
-    _launch_with_fixup(prod, fx)
+    if T > 128:
+        # tokens on the rows: a tile is up to 256 features wide, so the sums of squares come per such tile
+        _rows, bn, _splits = tc_gemm_plan(T, H, prod.x.shape[1])
+        ssq = torch.empty((-(-H // bn), T), dtype=torch.float32, device=x.device)
+        fx.ssq_out = ssq.data_ptr()
+    _launch_with_fixup(prod, fx, rows)
     return ScaledRows(rows, ssq, eps)
 
 
@@ -876,7 +901,7 @@ FOLD_MAX_TOKENS = 4
 
 
 def linear(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: "torch.dtype | None" = None, partials_ok: bool = False,
-           deferred_ok: bool = False):
+           deferred_ok: "bool | str" = False):
     """y = x W^T for a weight in the linear-layer layout [out, in].
 
     float32: the package's own fp32 kernel (no reduced-precision matrix mode).
@@ -886,16 +911,19 @@ def linear(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: "torch.dt
     (used for the logits).  ``partials_ok``: the caller's consumer adds split-K partial
     sums itself, so a ``PartialSums`` may come back instead of a tensor.  ``deferred_ok``: the caller's
     consumer is one of the kernels that take a ``DeferredProduct`` (the built-in norm, ``qkv_rope_write``) or
-    calls ``materialize``; for very few tokens (``FOLD_MAX_TOKENS``) the product is then not launched here."""
+    calls ``materialize``; for very few tokens (``FOLD_MAX_TOKENS``) the product is then not launched here.
+    ``deferred_ok="residual"`` says that the consumer is the norm (the product is a branch output): then a product
+    of many tokens in one split is deferred too, since its epilogue can fold the residual add (``folds_residual``)."""
     if x.dtype == torch.float32:
         return sgemm_nt(x, w)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise ValueError(f"linear: unsupported dtypes {x.dtype} x {w.dtype}")
     rows = x.rows if isinstance(x, ScaledRows) else x
     if USE_TC_GEMM and tc_gemm_supported(rows, w):
-        if deferred_ok and FOLD_SMALL_KERNELS and rows.shape[0] <= FOLD_MAX_TOKENS and w.shape[0] % 4 == 0 \
-                and out_dtype in (None, torch.bfloat16):
-            return DeferredProduct(x, w, torch.bfloat16)
+        if deferred_ok and FOLD_SMALL_KERNELS and out_dtype in (None, torch.bfloat16) and w.shape[0] % 4 == 0:
+            M = rows.shape[0]
+            if M <= FOLD_MAX_TOKENS or (deferred_ok == "residual" and folds_residual(M, w.shape[0], w.shape[1])):
+                return DeferredProduct(x, w, torch.bfloat16)
         return gemm_tc(x, w, out_dtype or torch.bfloat16, reduce=not partials_ok, checked=True)
     x = materialize(x)
     if out_dtype is None or out_dtype == torch.bfloat16:

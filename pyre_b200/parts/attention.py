@@ -110,7 +110,7 @@ class Attention(Part):
             a = ops.paged_attention_generic(q, layer, kv.block_table, ctx.seq_of_token, ctx.positions, self.n_heads,
                                             self.n_kv_heads, self.head_dim, self.scale, self.window)
         with lib.section("o"):
-            return ops.linear(a, self.w_o, partials_ok=True, deferred_ok=True)
+            return ops.linear(a, self.w_o, partials_ok=True, deferred_ok="residual")
 
 
 register_part("mixer", "attention", Attention)

@@ -55,7 +55,7 @@ class GatedMLP(Part):
         with lib.section("gate_up"):
             act = ops.gated_linear(h, self.w_gate_up, self.interleaved)
         with lib.section("down"):
-            return ops.linear(act, self.w_down, partials_ok=True, deferred_ok=True)
+            return ops.linear(act, self.w_down, partials_ok=True, deferred_ok="residual")
 
 
 register_part("ffn", "gated_mlp", GatedMLP)

@@ -654,7 +654,8 @@ def test_attention_long_context(ops, nh, nkv, hd, page, window):
     check(other, slice(0, 700), "mma.sync prompt kernel")
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 3584, 3584), (8, 3584, 18944), (64, 896, 4864), (100, 200, 136), (128, 3584, 512), (5, 1160, 72)])
+@pytest.mark.parametrize("M,N,K", [(1, 3584, 3584), (8, 3584, 18944), (64, 896, 4864), (100, 200, 136), (128, 3584, 512), (5, 1160, 72),
+                                   (2048, 3584, 3584), (300, 3584, 3584), (1000, 896, 4864), (2048, 3584, 18944), (700, 1160, 136)])
 def test_product_with_residual_and_norm_folded_in(ops, M, N, K):
     """A product of few tokens launched by the norm that consumes it: the CTA that finishes a tile last adds the
     splits' partial sums to the residual stream and leaves the next norm's activations without their 1/rms
@@ -669,11 +670,13 @@ def test_product_with_residual_and_norm_folded_in(ops, M, N, K):
     eps = 1e-5
     for rep in range(3):
         x = x0.clone()
-        prod = ops.linear(a, w, partials_ok=True, deferred_ok=True)
-        assert isinstance(prod, ops.DeferredProduct) == (M <= ops.FOLD_MAX_TOKENS)     # offered only where it pays
+        prod = ops.linear(a, w, partials_ok=True, deferred_ok="residual")
+        assert isinstance(prod, ops.DeferredProduct) == ops.folds_residual(M, N, K)     # offered only where it pays
         prod = ops.DeferredProduct(a, w, torch.bfloat16)
         assert tuple(prod.shape) == (M, N)
-        h = ops.add_rmsnorm(x, prod, gain, eps, torch.bfloat16, scaled_ok=True)
+        if M > 128 and not ops.folds_residual(M, N, K):
+            pytest.skip(f"the plan for {M} x {N} x {K} splits K: nothing to fold")
+        h = ops.gemm_residual_norm(prod, x, gain, eps) if M <= 128 else ops.add_rmsnorm(x, prod, gain, eps, torch.bfloat16, scaled_ok=True)
         ops.check_device_errors()
         assert isinstance(h, ops.ScaledRows)
         v = x0 + a.float() @ w.float().t()
