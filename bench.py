@@ -152,7 +152,8 @@ def class_work(cfg: dict, layers: int, T: int, B: int, context_before: int, logi
     cached = B * (context_before + T // B)                                    # tokens whose keys and values are read
     return {
         "embed": {"bytes": T * H * (2 + 4), "flops": 0},
-        "norm": {"bytes": (2 * layers + 1) * T * H * (4 + 2 + 4 + 2) + (2 * layers + 1) * H * 4, "flops": 0},
+        # per launch: how many norm kernels run depends on the step (products of very few or of many tokens fold them in)
+        "norm": {"bytes": T * H * (4 + 2 + 4 + 2) + H * 4, "flops": 0, "per_launch": True},
         "qkv": {"bytes": layers * ((q + 2 * kv) * H * 2 + T * (H + q + 2 * kv) * 2), "flops": 2.0 * layers * T * H * (q + 2 * kv)},
         "rotary+write": {"bytes": layers * T * (q + 2 * kv) * 2 * 2, "flops": 0},
         "attention": {"bytes": layers * (cached * 2 * kv * 2 + 2 * T * q * 2), "flops": 4.0 * layers * nh * hd * keys},
@@ -174,6 +175,8 @@ def kernel_table(totals: dict, work: dict, step_us: float, peaks: dict) -> dict:
         w = work.get(name)
         row = {"us": round(t["us"], 1), "launches": t["launches"]}
         if w is not None and t["us"] > 0:
+            if w.get("per_launch"):
+                w = {"bytes": w["bytes"] * t["launches"], "flops": w["flops"] * t["launches"]}
             # both yardsticks; the class is judged by the one that binds it (the larger fraction)
             gbs = w["bytes"] / (t["us"] * 1e-6) / 1e9
             tf = w["flops"] / (t["us"] * 1e-6) / 1e12
