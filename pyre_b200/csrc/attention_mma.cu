@@ -585,9 +585,15 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
 }
 
 // out[t, h, :] = sum_s acc_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)   (maxima are kept in base 2)
-__global__ void combine_splits_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                      __nv_bfloat16* __restrict__ out, int n_splits, int hd, int nh,
-                                      const int* __restrict__ cu_seqlens, int n_seqs, int max_len) {
+// One block of COMBINE_WARPS warps per (token, head).  Warp w takes splits w, w + COMBINE_WARPS, ...; a lane holds
+// four output dims, so a split's partial row is one 16-byte load per lane, and the loads of a warp's splits are
+// independent (four splits in flight).  Each warp keeps a running (max, sum, accumulator) of its own; the warps
+// merge through shared memory in warp order.
+constexpr int COMBINE_WARPS = 8;
+__global__ void __launch_bounds__(COMBINE_WARPS * 32)
+combine_splits_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                      __nv_bfloat16* __restrict__ out, int n_splits, int hd, int nh,
+                      const int* __restrict__ cu_seqlens, int n_seqs, int max_len) {
     pdl_trigger();
     pdl_wait();
     const size_t th = blockIdx.x;
@@ -600,43 +606,56 @@ __global__ void combine_splits_kernel(const float* __restrict__ part_acc, const 
                 break;
             }
     }
-    // blockDim.x (32 or 64) splits at a time: one split's (max, sum) per thread, the factors 2^(m_s - M) shared,
-    // then every thread adds up its output dims with independent loads
-    __shared__ float sm_f[64];
-    __shared__ float sm_red[2];
-    __shared__ float sm_out[128];
+    __shared__ float sm_m[COMBINE_WARPS], sm_l[COMBINE_WARPS];
+    __shared__ __align__(16) float sm_o[COMBINE_WARPS][128];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float* ml = part_ml + th * n_splits * 2;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, chunk = blockDim.x;
+    const float* acc = part_acc + th * n_splits * hd;
+    const bool has_dims = 4 * lane < hd;       // hd is a multiple of 16, at most 128
     float M = -INFINITY, L = 0.f;
-    for (int s0 = 0; s0 < n_splits; s0 += chunk) {
-        const int s = s0 + tid;
-        const float m_s = s < n_splits ? ml[2 * s] : -INFINITY;
-        const float l_s = s < n_splits ? ml[2 * s + 1] : 0.f;
-        float cm = warp_max(m_s);
-        if (lane == 0) sm_red[warp] = cm;
-        __syncthreads();
-        cm = chunk > 32 ? fmaxf(sm_red[0], sm_red[1]) : sm_red[0];
-        const float M_new = fmaxf(M, cm);
-        const float m_use = (M_new == -INFINITY) ? 0.f : M_new;
-        const float f = exp2f(m_s - m_use);                // 0 for the padding
-        float cl = warp_sum(l_s * f);
-        __syncthreads();
-        if (lane == 0) sm_red[warp] = cl;
-        sm_f[tid] = f;
-        __syncthreads();
-        cl = chunk > 32 ? sm_red[0] + sm_red[1] : sm_red[0];
-        const float rescale = exp2f(M - m_use);            // 0 the first time (M = -inf)
-        L = L * rescale + cl;
-        const int n = min(chunk, n_splits - s0);
-        for (int d = tid; d < hd; d += chunk) {
-            float O = s0 == 0 ? 0.f : sm_out[d] * rescale;
-            for (int k = 0; k < n; ++k) O += part_acc[(th * n_splits + s0 + k) * hd + d] * sm_f[k];
-            sm_out[d] = O;
+    float4 O = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s0 = warp; s0 < n_splits; s0 += 4 * COMBINE_WARPS) {
+        float m_s[4], l_s[4];
+        float4 a[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int sp = s0 + k * COMBINE_WARPS;
+            const bool live = sp < n_splits;
+            m_s[k] = live ? ml[2 * sp] : -INFINITY;
+            l_s[k] = live ? ml[2 * sp + 1] : 0.f;
+            a[k] = (live && has_dims) ? *reinterpret_cast<const float4*>(acc + (size_t)sp * hd + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        M = M_new;
-        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float M_new = fmaxf(M, m_s[k]);
+            const float m_use = (M_new == -INFINITY) ? 0.f : M_new;
+            const float f_old = exp2f(M - m_use), f = exp2f(m_s[k] - m_use);      // 0 for an empty side
+            L = L * f_old + l_s[k] * f;
+            O.x = O.x * f_old + a[k].x * f; O.y = O.y * f_old + a[k].y * f;
+            O.z = O.z * f_old + a[k].z * f; O.w = O.w * f_old + a[k].w * f;
+            M = M_new;
+        }
     }
-    for (int d = tid; d < hd; d += chunk) out[th * hd + d] = __float2bfloat16_rn(sm_out[d] / L);
+    if (lane == 0) { sm_m[warp] = M; sm_l[warp] = L; }
+    if (has_dims) *reinterpret_cast<float4*>(&sm_o[warp][4 * lane]) = O;
+    __syncthreads();
+    if (warp == 0 && has_dims) {
+        float Mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < COMBINE_WARPS; ++w) Mx = fmaxf(Mx, sm_m[w]);
+        const float m_use = (Mx == -INFINITY) ? 0.f : Mx;
+        float Ls = 0.f;
+        float4 Os = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < COMBINE_WARPS; ++w) {
+            const float f = exp2f(sm_m[w] - m_use);
+            const float4 o = *reinterpret_cast<const float4*>(&sm_o[w][4 * lane]);
+            Ls += sm_l[w] * f;
+            Os.x += o.x * f; Os.y += o.y * f; Os.z += o.z * f; Os.w += o.w * f;
+        }
+        const float inv = 1.0f / Ls;
+        *reinterpret_cast<uint2*>(out + th * hd + 4 * lane) = make_uint2(pack_bf16(Os.x * inv, Os.y * inv), pack_bf16(Os.z * inv, Os.w * inv));
+    }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -786,7 +805,7 @@ PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* ou
     }
     if (rc) return rc;
     if (n_splits > 1 && !use_cluster) {
-        pyre_launch(combine_splits_kernel, dim3(n_tokens * nh), dim3(hd >= 64 ? 64 : 32), 0, stream, p.part_acc, p.part_ml, p.out, n_splits, hd, nh, cu_seqlens, n_seqs, max_len);
+        pyre_launch(combine_splits_kernel, dim3(n_tokens * nh), dim3(COMBINE_WARPS * 32), 0, stream, p.part_acc, p.part_ml, p.out, n_splits, hd, nh, cu_seqlens, n_seqs, max_len);
         PYRE_LAUNCH_CHECK();
     }
     return 0;

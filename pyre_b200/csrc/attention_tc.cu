@@ -288,14 +288,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             if (!__all_sync(0xffffffffu, ok)) break;
             const uint32_t full = bar_full + 8 * s, dst = ring + s * L::KV_TILE;
             if (lane == 0) mbar_expect_tx(full, L::KV_TILE);
-            for (int pc = 0; pc < pieces; ++pc) {
-                const int page = __shfl_sync(0xffffffffu, pg0, pc);
-                const int key = (tile_lo + i) * BN + pc * p.box_rows;
-                const int row = page * page_rows + row_base + (key & (p.page_size - 1));
-                if (lane == 0) {
-#pragma unroll
-                    for (int h = 0; h < HALVES; ++h)
-                        tma_load_2d(dst + h * (BN * 128) + pc * p.box_rows * 128, &map_kv, full, h * 64, row);
+            __syncwarp();
+            // one box (a page's rows x one 128-byte column box) per lane: the copies of a tile go out as one
+            // instruction of up to 32 lanes instead of a loop in one thread (about a hundred cycles per copy there,
+            // which set the pace of the ring with pages of 16 tokens: eight boxes per tile)
+            for (int b0 = 0; b0 < pieces * HALVES; b0 += 32) {
+                const int box = b0 + lane, pc = box / HALVES, h = box - pc * HALVES;
+                const int page = __shfl_sync(0xffffffffu, pg0, pc & 31);
+                if (box < pieces * HALVES) {
+                    const int key = (tile_lo + i) * BN + pc * p.box_rows;
+                    const int row = page * page_rows + row_base + (key & (p.page_size - 1));
+                    tma_load_2d(dst + h * (BN * 128) + pc * p.box_rows * 128, &map_kv, full, h * 64, row);
                 }
             }
             __syncwarp();

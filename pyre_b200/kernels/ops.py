@@ -393,6 +393,7 @@ def paged_attention_generic(q: torch.Tensor, cache_layer: torch.Tensor, block_ta
 
 MMA_MAX_HEAD_DIM = 128
 CLUSTER_MAX_SPLITS = 16      # splits of one group merge through a thread-block cluster up to this many
+MAX_SCRATCH_SPLITS = 64      # beyond a cluster: partial results through scratch memory and the combining kernel
 _DEFAULT_SM_COUNT = 148     # a B200; used only where no device can be asked (planning on a host without a GPU)
 _sm_counts: dict = {}
 _have_cuda: "bool | None" = None
@@ -417,8 +418,8 @@ def attention_splits(n_tokens: int, n_seqs: int, n_heads: int, n_kv_heads: int, 
                      window: "int | None", n_groups: "int | None" = None) -> int:
     """How many ways the tensor-core kernel splits each sequence's keys: enough CTAs for
     about one and a half per SM, at least two 16-key tiles per split, at most 16 (the
-    splits of a group form one thread-block cluster), or 32 through scratch memory for a
-    single very long sequence."""
+    splits of a group form one thread-block cluster), or 24 to 64 through scratch memory for
+    one or two sequences with long contexts."""
     _SM_COUNT = sm_count()
     n_rep = n_heads // n_kv_heads
     hpg = min(n_rep, 16)
@@ -431,6 +432,14 @@ def attention_splits(n_tokens: int, n_seqs: int, n_heads: int, n_kv_heads: int, 
     # Measured inside whole decode steps (7B shape, contexts of 2-3 thousand tokens): about one and a half CTAs per
     # SM in all is best (batch 8: 7 splits, 16: 4, 32: 2, 64: 1); with two per SM the product that follows
     # finds no SM on which to prefetch its weights while the attention runs.
+    # One or two sequences with long contexts: a cluster's 16 CTAs per group leave most SMs idle and give every warp
+    # dozens of tiles (0.6 us of dependent work each).  Many small CTAs (about 256 in all, at least 16 tiles each)
+    # through scratch memory and the combining kernel win there: alone, 8,192 keys 10.9 -> 8.9 us, 16,384 keys
+    # 16.9 -> 12.3, 32,768 keys 25.7 -> 17.0 (one sequence); 34.0 -> 25.9 for two sequences of 32,768.
+    # Four sequences of 32,768 keys: 16 splits through scratch 47.4 us, 32: 49.3, clusters of 8 or 16: 62-68.
+    many = min(256 // max(ctas, 1), tiles // 16, MAX_SCRATCH_SPLITS)
+    if many >= 24 or (many >= 16 and tiles >= 512):
+        return max(24, many // 8 * 8)
     want = max(1, min(int(1.57 * _SM_COUNT / max(ctas, 1) + 0.5), -(-tiles // 2), CLUSTER_MAX_SPLITS))
     if want > 8:
         # a cluster of 16 CTAs must sit in one GPC: it pays only while all of them fit on the chip at once

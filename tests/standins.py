@@ -201,7 +201,7 @@ def paged_attention_mma(q, cache_layer, block_table, cu_seqlens, positions, n_se
                         window=None, n_splits=1, out=None, scratch=None, max_len=0, uniform_len=0):
     from pyre_b200.kernels import ops
     assert q.dtype == cache_layer.dtype == torch.bfloat16 and head_dim <= ops.MMA_MAX_HEAD_DIM
-    assert n_splits == 32 or 1 <= n_splits <= ops.CLUSTER_MAX_SPLITS
+    assert 1 <= n_splits <= ops.MAX_SCRATCH_SPLITS
     lens = (cu_seqlens[1:] - cu_seqlens[:-1]).tolist()
     assert not uniform_len or all(n == uniform_len for n in lens), "uniform_len promises entries of one length"
     if out is None:

@@ -641,7 +641,7 @@ def test_attention_long_context(ops, nh, nkv, hd, page, window):
     # the decode token alone through the split-KV kernel: one split (long walks per warp), clusters of 4 and 16,
     # and 32 splits, which go through scratch memory and the combining kernel
     dec_cu = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
-    for n_splits in (1, 4, 16, 32):
+    for n_splits in (1, 4, 16, 32, 64):
         alone = ops.paged_attention_mma(q[700:].contiguous(), cache, table[1:2].contiguous(), dec_cu, positions[700:].contiguous(),
                                         1, nh, nkv, hd, scale, window, n_splits, uniform_len=1)
         ops.check_device_errors()
