@@ -16,7 +16,9 @@ already cached (context 2,048 + tokens decoded so far, inside the benchmark cont
                    bf16 peak that its flops reach
   roofline         bytes the decode step must read (every weight once + the cache of the
                    live requests) / its time, against the HBM peak
-  points           decode tokens/s at batch 1 and 64
+  points           decode tokens/s at batch 1 and 64; at contexts of 8,192 and 32,768 tokens (batch 1 and 8); and at
+                   the 14B and 32B shapes of the same architecture (batch 8, 2,048-token prompts), each with its
+                   fraction of the copy roofline (`hbm_frac_*`)
   kernels          per workload (decode at batch 1, 8 and 64, the 2,048-token prefill) and kernel class
                    (norm, qkv, rotary+write, attention, o, gate_up, down, head, sampler): device
                    microseconds with every kernel alone (CUDA events between the launches of an
@@ -356,6 +358,53 @@ def run_ours(args) -> dict:
     clocks.stop()
     stepper.check_device_errors()      # a kernel that gave up waiting would have raised the device's error word
 
+    # ---------------------------------------------------------------- further sizes of the same architecture
+    # decode tokens/s at longer contexts (this model) and at the 14B and 32B shapes (full layer counts, batch 8,
+    # 2,048-token prompts): device-timed like `value`, each with its fraction of the copy roofline beside it
+    if not args.skip_points and not args.skip_sizes:
+        def decode_point(eng, cfg_raw_, n_layers, batch, context, n_warm=8, n_steps=24):
+            st_, cache_ = eng.stepper, eng.cache
+            wb, kvb, _ = model_numbers(cfg_raw_, n_layers)
+            reqs = [("x", batch, context, i) for i in range(batch)]
+            for r in reqs:
+                cache_.begin(r)
+                for lo in range(0, context, 8192):
+                    st_.step([StepEntry(r, rng.integers(0, cfg_raw_["vocab_size"], min(8192, context - lo)).tolist(), [])])
+            toks = rng.integers(0, cfg_raw_["vocab_size"], (n_warm + n_steps, batch))
+            for k in range(n_warm):      # the clocks recover from the prefill's power cap meanwhile
+                ops.sample(st_.step([StepEntry(r, [int(toks[k, i])], [0]) for i, r in enumerate(reqs)]))
+            torch.cuda.synchronize()
+            a, b = ev(), ev()
+            a.record()
+            for k in range(n_warm, n_warm + n_steps):
+                ops.sample(st_.step([StepEntry(r, [int(toks[k, i])], [0]) for i, r in enumerate(reqs)]))
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / n_steps
+            for r in reqs:
+                cache_.end(r)
+            frac = (wb + kvb * (context + n_warm + n_steps / 2) * batch) / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]
+            return round(batch / ms * 1e3, 1), round(frac, 3)
+
+        del stepper, cache, engine
+        torch.cuda.empty_cache()
+        long_cfg = dict(cfg_raw, max_position_embeddings=40960)
+        eng = Engine(config=config_from_dict(long_cfg), seed=0, dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=8 * 33000,
+                     max_num_seqs=8, max_num_batched_tokens=8192, prefill_chunk=8192, max_model_len=40960)
+        for batch, context in ((1, 8192), (1, 32768), (8, 8192), (8, 32768)):
+            points[f"decode_b{batch}_ctx{context // 1024}k"], points[f"hbm_frac_b{batch}_ctx{context // 1024}k"] = \
+                decode_point(eng, long_cfg, layers, batch, context)
+        del eng
+        torch.cuda.empty_cache()
+        if layers == layers_full:      # the other shapes only beside the full model
+            for name in ("14b", "32b"):
+                raw = dict(SHAPES[name])
+                eng = Engine(config=config_from_dict(raw), seed=0, dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=8 * 2200 + 4096,
+                             max_num_seqs=8, max_num_batched_tokens=2048, prefill_chunk=2048, max_model_len=4096)
+                points[f"decode_b8_{name}"], points[f"hbm_frac_b8_{name}"] = decode_point(eng, raw, raw["num_hidden_layers"], 8, PROMPT_LEN)
+                del eng
+                torch.cuda.empty_cache()
+
     return {
         "metric": "decode tok/s (Qwen2.5-7B shape, batch 8, 2,048-token prompts)", "value": round(value, 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 4),
@@ -581,6 +630,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")
     ap.add_argument("--prefill-reps", type=int, default=5)
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
+    ap.add_argument("--skip-sizes", action="store_true",
+                    help="leave out the points at longer contexts and at the 14B and 32B shapes")
     ap.add_argument("--no-per-kernel", action="store_true",
                     help="leave out the `kernels` block (device time, bytes or flops and fraction of the peak per kernel class)")
     ap.add_argument("--workload", choices=["serve14b", "mixed32b", "sweep"], default=None,
