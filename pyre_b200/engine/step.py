@@ -390,7 +390,7 @@ class Stepper:
         """What the parts' kernels derive from host-side facts of a decode step (``Part.launch_key``);
         a captured graph is reused only while these stay the same."""
         out = set()
-        for part in [self.model.embed, *self.model.blocks, self.model.final_norm, self.model.head]:
+        for part in self.model.parts():
             out |= collect_launch_keys(part, n_entries, max_context)
         return tuple(sorted(out, key=repr))
 

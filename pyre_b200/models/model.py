@@ -33,20 +33,18 @@ class StateGroup:
 def _instantiate(spec: ModelSpec, dtype, device):
     embed = make_part("embed", spec.embed, dtype, device)
     blocks = [make_part("block", b, dtype, device) for b in spec.blocks]
-    final_norm = make_part("norm", spec.final_norm, dtype, device)
-    head = make_part("head", spec.head, dtype, device)
-    return embed, blocks, final_norm, head
+    tail = make_part("tail", spec.tail, dtype, device)
+    return embed, blocks, tail
 
 
 def tensor_table(spec: ModelSpec) -> dict[str, TensorSpec]:
     """Checkpoint name -> TensorSpec for every tensor of the model, in a fixed order
     (embedding, layers in order, final norm, head)."""
-    embed, blocks, final_norm, head = _instantiate(spec, torch.float32, "meta")
+    embed, blocks, tail = _instantiate(spec, torch.float32, "meta")
     table = collect_tensors(embed, spec.embed_prefix)
     for i, b in enumerate(blocks):
         table.update(collect_tensors(b, spec.block_prefix.format(i=i)))
-    table.update(collect_tensors(final_norm, spec.final_norm_prefix))
-    table.update(collect_tensors(head, spec.head_prefix))
+    table.update(collect_tensors(tail, spec.tail_prefix))
     return table
 
 
@@ -55,11 +53,15 @@ class Model:
         self.spec = spec
         self.dtype = dtype
         self.device = torch.device(device)
-        self.embed, self.blocks, self.final_norm, self.head = _instantiate(spec, dtype, self.device)
+        self.embed, self.blocks, self.tail = _instantiate(spec, dtype, self.device)
         self.vocab_size = spec.vocab_size
         self.calls, self.kv_groups, self.state_groups = self._bind_schedule()
         self.loaded = False
-        self.graph_safe = all(all_graph_safe(p) for p in [self.embed, self.final_norm, self.head, *self.blocks])
+        self.graph_safe = all(all_graph_safe(p) for p in self.parts())
+
+    def parts(self) -> list:
+        """The top-level parts: embedding, blocks, tail."""
+        return [self.embed, *self.blocks, self.tail]
 
     # ------------------------------------------------------------------ schedule
     def _bind_schedule(self):
@@ -122,8 +124,7 @@ class Model:
             # the block has packed what it needs; drop the originals of this layer
             for name in [n for n in tensors if n.startswith(prefix)]:
                 del tensors[name]
-        load_part(self.final_norm, tensors, self.spec.final_norm_prefix)
-        load_part(self.head, tensors, self.spec.head_prefix)
+        load_part(self.tail, tensors, self.spec.tail_prefix)
         self.loaded = True
 
     def load_weights(self, model_dir: "str | Path") -> None:
@@ -136,9 +137,9 @@ class Model:
         self._bind(tensors)
 
     def kernel_libraries(self) -> list[str]:
-        libs = collect_libraries(self.embed) + collect_libraries(self.final_norm) + collect_libraries(self.head)
-        for b in self.blocks:
-            libs += collect_libraries(b)
+        libs = []
+        for part in self.parts():
+            libs += collect_libraries(part)
         return list(dict.fromkeys(libs + ["sampling"]))
 
     # ------------------------------------------------------------------ compute
@@ -152,8 +153,7 @@ class Model:
             x, pending = self.blocks[call.block].forward(ctx, x, pending, call)
         if ctx.num_logit_rows == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)
-        h = self.final_norm.forward(ctx, x, delta=pending, rows=ctx.logit_rows)
-        return self.head.forward(ctx, h)
+        return self.tail.forward(ctx, x, pending)
 
 
 def load_model(model_dir: "str | Path", device: str = "cuda:0", dtype="bfloat16"):

@@ -24,10 +24,14 @@ class LayerCall:
 
 @dataclass
 class ModelSpec:
+    """The skeleton of a model is data too: an embedding, blocks run in the order of ``schedule``, and a tail
+    (everything after the last block).  ``final_norm`` and ``head`` are a shorthand for the usual tail (a norm over
+    the wanted rows, then a head); an architecture that ends otherwise gives ``tail`` itself."""
+
     embed: PartSpec
     blocks: list[PartSpec]
-    final_norm: PartSpec
-    head: PartSpec
+    final_norm: "PartSpec | None" = None
+    head: "PartSpec | None" = None
     schedule: list[LayerCall] = field(default_factory=list)
     # prefixes of the checkpoint names
     embed_prefix: str = "model.embed_tokens."
@@ -36,6 +40,8 @@ class ModelSpec:
     head_prefix: str = "lm_head."
     vocab_size: int = 0
     max_positions: int = 0
+    tail: "PartSpec | None" = None
+    tail_prefix: str = ""
 
     def __post_init__(self):
         if not self.schedule:
@@ -43,3 +49,8 @@ class ModelSpec:
         for call in self.schedule:
             if not 0 <= call.block < len(self.blocks):
                 raise ValueError(f"schedule names block {call.block}, the model has {len(self.blocks)}")
+        if self.tail is None:
+            if self.final_norm is None or self.head is None:
+                raise ValueError("a model needs a tail: give final_norm and head, or tail")
+            self.tail = PartSpec("norm_head", {"norm": self.final_norm, "head": self.head,
+                                               "names": {"norm": self.final_norm_prefix, "head": self.head_prefix}})

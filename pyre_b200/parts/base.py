@@ -1,7 +1,7 @@
 """The vocabulary of model parts.
 
-A model is put together from parts of seven categories: ``embed``, ``norm``,
-``position``, ``mixer``, ``ffn``, ``block`` and ``head``.  A part
+A model is put together from parts of eight categories: ``embed``, ``norm``,
+``position``, ``mixer``, ``ffn``, ``block``, ``head`` and ``tail``.  A part
 
 * is described by data: ``PartSpec(kind, params)``; ``kind`` is looked up in the
   registry of its category, ``params`` are the sizes and constants it is built with
@@ -37,6 +37,8 @@ Interfaces by category (``ctx`` is the StepContext, T its number of tokens):
               Likewise a norm may hand a consumer that declares ``takes_scaled_rows``
               ``kernels.ops.ScaledRows`` instead of a tensor (see ``PreNormBlock``)
     head      forward(ctx, h_rows) -> fp32 logits [R, vocab]
+    tail      forward(ctx, x, pending) -> fp32 logits [R, vocab] at ``ctx.logit_rows``: everything after the last
+              block (the built-in one: a norm over the wanted rows, then a head)
 
 A new part is a class with these methods and one ``register_part`` call; nothing else
 in the package has to change.
@@ -51,7 +53,7 @@ import torch
 
 from ..weights.specs import TensorSpec
 
-CATEGORIES = ("embed", "norm", "position", "mixer", "ffn", "block", "head")
+CATEGORIES = ("embed", "norm", "position", "mixer", "ffn", "block", "head", "tail")
 
 
 @dataclass(frozen=True)

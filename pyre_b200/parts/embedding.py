@@ -6,7 +6,7 @@ import torch
 
 from ..kernels import lib, ops
 from ..weights.specs import TensorSpec
-from .base import Part, register_part
+from .base import Part, PartSpec, make_part, register_part
 
 
 class TokenEmbedding(Part):
@@ -59,5 +59,30 @@ class LinearHead(Part):
             return ops.linear(h_rows, self.weight, out_dtype=torch.float32)
 
 
+class NormHeadTail(Part):
+    """What follows the last block in this architecture (pyre/model.py:199-201): the final norm, applied to the rows
+    whose logits are wanted only (the last block's branch output still pending is added on the way), then the head.
+    ``names``: the checkpoint prefixes of the two sub-parts' tensors.  An architecture that ends otherwise (no norm,
+    a scaled head, several heads) brings a tail of its own; the model's skeleton is embed, the scheduled blocks, tail."""
+
+    graph_safe = True
+
+    DEFAULT_NAMES = {"norm": "model.norm.", "head": "lm_head."}
+
+    def __init__(self, dtype, device, norm: PartSpec, head: PartSpec, names: "dict[str, str] | None" = None):
+        super().__init__(dtype, device)
+        self.names = dict(self.DEFAULT_NAMES, **(names or {}))
+        self.norm = make_part("norm", norm, dtype, device)
+        self.head = make_part("head", head, dtype, device)
+
+    def children(self):
+        return {self.names["norm"]: self.norm, self.names["head"]: self.head}
+
+    def forward(self, ctx, x, pending):
+        h = self.norm.forward(ctx, x, delta=pending, rows=ctx.logit_rows)
+        return self.head.forward(ctx, h)
+
+
 register_part("embed", "token_embedding", TokenEmbedding)
+register_part("tail", "norm_head", NormHeadTail)
 register_part("head", "linear_head", LinearHead)

@@ -471,3 +471,71 @@ def test_replay_answers_each_line_before_the_next_one_is_written(models, monkeyp
         assert not t.is_alive() and not failure
         got = H.collect_trace_logits(steps, lambda n: np.fromfile(Path(out) / f"{n}.f32", dtype="<f4").reshape(-1, 512))
     compare(got, {"A1": want["A1"]}, "line by line through a pipe")
+
+
+def test_a_tail_of_the_tests_own_ends_the_model(models, monkeypatch):
+    """The model's skeleton is data: embed, the scheduled blocks, a tail.  A tail registered from this test (no final
+    norm; two heads whose logits are averaged and scaled) replaces the usual norm + head without a change to the
+    package; the step function, the replay loop and the loader serve it as they serve the built-in one."""
+    from pyre_b200.config import architecture_of, load_config
+    from pyre_b200.engine.replay import runtime_for_model
+    from pyre_b200.engine.step import StepEntry
+    from pyre_b200.kernels import ops
+    from pyre_b200.models import Model
+    from pyre_b200.parts import Part, PartSpec, register_part
+    from pyre_b200.weights import TensorSpec
+
+    standins.install(monkeypatch)
+
+    class ToyTwoHeadTail(Part):
+        def __init__(self, dtype, device, vocab, width, scale):
+            super().__init__(dtype, device)
+            self.vocab, self.width, self.scale = vocab, width, scale
+
+        def tensors(self):
+            return {"head_a.weight": TensorSpec((self.vocab, self.width)), "head_b.weight": TensorSpec((self.vocab, self.width))}
+
+        def load(self, tensors):
+            self.a, self.b = tensors["head_a.weight"], tensors["head_b.weight"]
+
+        def forward(self, ctx, x, pending):
+            v = x + ops.materialize(pending).float()            # the last block's branch output is still pending
+            rows = v[ctx.logit_rows.long()]
+            return (rows @ self.a.float().t() + rows @ self.b.float().t()) * (0.5 * self.scale)
+
+    register_part("tail", "toy_two_heads", ToyTwoHeadTail, replace=True)
+    d, reqs, _ = models["A"]
+    cfg = load_config(d)
+    spec = architecture_of(cfg).build(cfg)
+    spec.tail = PartSpec("toy_two_heads", {"vocab": cfg.vocab_size, "width": cfg.hidden_size, "scale": 3.0})
+    spec.tail_prefix = "out."
+    model = Model(spec, torch.float32, "cpu")
+    table = model.tensor_table()
+    assert "out.head_a.weight" in table and "model.norm.weight" not in table and "lm_head.weight" not in table
+    w = H.load_plain_weights(d)
+    g = torch.Generator().manual_seed(4)
+    extra = {"out.head_a.weight": torch.randn(cfg.vocab_size, cfg.hidden_size, generator=g) * 0.1,
+             "out.head_b.weight": torch.randn(cfg.vocab_size, cfg.hidden_size, generator=g) * 0.1}
+    from safetensors.torch import save_file
+    import tempfile
+    with tempfile.TemporaryDirectory() as tmp:
+        tensors = {k: v for k, v in w.items() if k in table}
+        tensors.update(extra)
+        save_file(tensors, str(Path(tmp) / "model.safetensors"))
+        (Path(tmp) / "config.json").write_text((Path(d) / "config.json").read_text())
+        model.load_weights(tmp)
+    cache, stepper = runtime_for_model(model, 128, 16, cuda_graphs=False)
+    ids = reqs["A3"]
+    cache.begin("r")
+    got = torch.cat([stepper.step([StepEntry("r", ids[:30], list(range(30)))]),
+                     stepper.step([StepEntry("r", ids[30:], list(range(len(ids) - 30)))])])
+    with torch.inference_mode():
+        _, hidden = qwen2_plain_forward_hidden(ids, w, H.TINY["A"])
+    want = (hidden @ extra["out.head_a.weight"].t() + hidden @ extra["out.head_b.weight"].t()) * 1.5
+    assert np.abs(got.numpy() - want.numpy()).max() <= 2e-5 + 2e-4 * float(want.abs().max())
+
+
+def qwen2_plain_forward_hidden(ids, w, raw):
+    from plain import qwen2_plain
+    logits, hidden = qwen2_plain.forward(ids, w, raw, return_hidden=True)
+    return logits, hidden[-1]

@@ -76,7 +76,7 @@ def test_launch_keys_come_from_the_parts():
         for b in model.blocks:
             keys |= collect_launch_keys(b, rows, context)
         assert keys == {(ops.attention_splits(rows, rows, 4, 2, context, None),)}
-    assert collect_launch_keys(model.embed, 8, 100) == set() and collect_launch_keys(model.head, 8, 100) == set()
+    assert collect_launch_keys(model.embed, 8, 100) == set() and collect_launch_keys(model.tail, 8, 100) == set()
 
     class Halves(Part):                     # a part whose launches depend on the longest context in its own way
         def launch_key(self, n_rows, max_context):
