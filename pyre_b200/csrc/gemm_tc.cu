@@ -225,7 +225,7 @@ struct SmemLayout {
 // drains its own 128 accumulator rows.  Barriers: the first CTA's "full" barriers count the bytes of both CTAs'
 // loads; the MMA commits arrive on the "empty" and "accumulator full" barriers of both; the epilogue warps of
 // both arrive on the first CTA's "accumulator empty" barriers.
-template <int BN, int STAGES, bool X_CONTIGUOUS_OUT, int CTAS = 1>
+template <int BN, int STAGES, bool X_CONTIGUOUS_OUT, int CTAS = 1, bool FOLD = true>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const GemmParams p) {
     static_assert(CTAS == 1 || (CTAS == 2 && !X_CONTIGUOUS_OUT && BN % 16 == 0), "pairs serve the row store");
@@ -243,6 +243,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::TILES + L::N_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::TILES + L::N_BARS * 8 + 8);
 
+    // the folded work (row scales, fix-ups, the residual fold) is compiled into the FOLD variants only: the plain
+    // weight stream keeps its small register count, so that the next kernel's CTAs find room beside it
+    const int fix = FOLD ? p.fix : 0;
+    const float* const scale_ssq = FOLD ? p.scale_ssq : nullptr;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_kb = (p.K + BK - 1) / BK;
     const int kb_begin = blockIdx.z * p.k_blocks_per_split;
@@ -391,14 +395,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         [[maybe_unused]] const int epi_tid = quarter * 32 + lane;
         [[maybe_unused]] int scaled_y0 = -1;
         [[maybe_unused]] bool in_step = false;     // the epilogue warps synchronise among themselves in this launch
-        if constexpr (X_CONTIGUOUS_OUT) in_step = p.gated || p.scale_ssq != nullptr || p.fix != 0;
-        if (p.scale_ssq != nullptr || p.fix != 0) pdl_wait();     // these warps read what earlier kernels wrote
+        if constexpr (X_CONTIGUOUS_OUT) in_step = p.gated || scale_ssq != nullptr || fix != 0;
+        if (scale_ssq != nullptr || fix != 0) pdl_wait();     // these warps read what earlier kernels wrote
         for (int tile = worker; tile < n_tiles && alive; tile += n_workers, ++j) {
             const int buf = j & 1;
             const int x0 = (tile % p.tiles_x) * (BM * CTAS) + rank * BM, y0 = (tile / p.tiles_x) * BN;
             const int xr = x0 + quarter * 32 + lane;
             if constexpr (X_CONTIGUOUS_OUT) {
-                if (p.scale_ssq != nullptr && y0 != scaled_y0) {
+                if (scale_ssq != nullptr && y0 != scaled_y0) {
                     // 1/rms of this tile's tokens, from the per-tile sums of squares that the producer of the
                     // activations left (added in tile order: the same sum whatever else the launch holds);
                     // computed while the main loop of the tile still runs
@@ -407,7 +411,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     float rs = 0.f;
                     if (epi_tid < BN && y < p.y_rows) {
                         float ssq = 0.f;
-                        for (int i = 0; i < p.scale_tiles; ++i) ssq += p.scale_ssq[(size_t)i * p.y_rows + y];
+                        for (int i = 0; i < p.scale_tiles; ++i) ssq += scale_ssq[(size_t)i * p.y_rows + y];
                         rs = 1.0f / sqrtf(ssq / p.scale_n + p.scale_eps);
                     }
                     rstd_s[epi_tid] = rs;
@@ -420,9 +424,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             [[maybe_unused]] float row_scale = 1.f;
             [[maybe_unused]] float row_ssq = 0.f;        // fix == 1: this row's sum of squares over the tile's columns
             if constexpr (!X_CONTIGUOUS_OUT) {
-                if (p.scale_ssq != nullptr && xr < p.x_rows) {
+                if (scale_ssq != nullptr && xr < p.x_rows) {
                     float ssq = 0.f;
-                    for (int i = 0; i < p.scale_tiles; ++i) ssq += p.scale_ssq[(size_t)i * p.x_rows + xr];
+                    for (int i = 0; i < p.scale_tiles; ++i) ssq += scale_ssq[(size_t)i * p.x_rows + xr];
                     row_scale = 1.0f / sqrtf(ssq / p.scale_n + p.scale_eps);
                 }
             }
@@ -568,7 +572,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                                 for (int e = 0; e < 4; ++e) {
                                     const int y = y0 + c + 4 * q4 + e;
                                     if (y < p.y_rows && x0 + (quarter & 1) * 32 + lane < p.x_rows) {
-                                        const float rs = p.scale_ssq ? rstd_s[c + 4 * q4 + e] : 1.f;
+                                        const float rs = scale_ssq ? rstd_s[c + 4 * q4 + e] : 1.f;
                                         const float z = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[4 * q4 + e]) * rs));
                                         const float v = __bfloat162float(__float2bfloat16_rn(uu[e] * rs));
                                         ((__nv_bfloat16*)p.out)[(long long)y * p.stride_y + feature] =
@@ -595,7 +599,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         // the fold's residual values of the whole group go out at once: one round trip to memory per
                         // group of GW columns, not one per 16
                         float4 xg[GW / 4];
-                        const bool prefetched = p.fix == 1 && alive && xr < p.x_rows;
+                        const bool prefetched = fix == 1 && alive && xr < p.x_rows;
                         if (prefetched) {
                             const float4* src = reinterpret_cast<const float4*>(p.resid + (size_t)xr * p.y_rows + y0 + gq * GW);
 #pragma unroll
@@ -607,7 +611,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                             __syncwarp();
                             tmem_ld16(acc + gq * GW + cc, r);
                             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                            if (p.fix == 1) fold16(r, y0 + gq * GW + cc, prefetched ? &xg[cc / 4] : nullptr);
+                            if (fix == 1) fold16(r, y0 + gq * GW + cc, prefetched ? &xg[cc / 4] : nullptr);
 #pragma unroll
                             for (int q = 0; q < 8; ++q) {
                                 __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * q]) * row_scale, __uint_as_float(r[2 * q + 1]) * row_scale);
@@ -631,8 +635,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     for (int q = 0; q < 16; ++q) r[q] = 0u;
                 }
                 if constexpr (!X_CONTIGUOUS_OUT) {
-                    if (p.fix == 1) fold16(r, y0 + c, nullptr);
-                    if (p.scale_ssq != nullptr) {
+                    if (fix == 1) fold16(r, y0 + c, nullptr);
+                    if (scale_ssq != nullptr) {
 #pragma unroll
                         for (int q = 0; q < 16; ++q) r[q] = __float_as_uint(__uint_as_float(r[q]) * row_scale);
                     }
@@ -674,7 +678,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         const int y = y0 + c + q;
                         if (y < p.y_rows) {
                             float v = __uint_as_float(r[q]);
-                            if constexpr (X_CONTIGUOUS_OUT) { if (p.scale_ssq) v *= rstd_s[c + q]; }
+                            if constexpr (X_CONTIGUOUS_OUT) { if (scale_ssq) v *= rstd_s[c + q]; }
                             if (p.out_f32) ((float*)p.out)[out_base + (long long)y * p.stride_y] = v;
                             else ((__nv_bfloat16*)p.out)[out_base + (long long)y * p.stride_y] = __float2bfloat16_rn(v);
                         }
@@ -686,10 +690,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             __syncwarp();
             if (lane == 0) hand_back(buf);
             if constexpr (!X_CONTIGUOUS_OUT) {
-                if (p.fix == 1 && alive && xr < p.x_rows) p.ssq_out[(size_t)(tile / p.tiles_x) * p.x_rows + xr] = row_ssq;
+                if (fix == 1 && alive && xr < p.x_rows) p.ssq_out[(size_t)(tile / p.tiles_x) * p.x_rows + xr] = row_ssq;
             }
             if constexpr (X_CONTIGUOUS_OUT && BN <= 128) {
-                if (p.fix != 0) {
+                if (fix != 0) {
                     // ---- fix-up: every split of this tile has stored its partial sums; the CTA that arrives last
                     // adds them up (in split order, whichever CTA does it) and finishes the tile
                     __threadfence();
@@ -710,7 +714,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         const int t_end = min(y0 + BN, p.y_rows);
                         const float* parts = (const float*)p.out;
                         const int n_parts = (int)gridDim.z;
-                        if (p.fix == 1) {
+                        if (fix == 1) {
                             float4 w4 = make_float4(0.f, 0.f, 0.f, 0.f);
                             if (in) w4 = *reinterpret_cast<const float4*>(p.norm_w + n0);
 #pragma unroll 2
@@ -841,14 +845,14 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, long long ld, i
     return r == CUDA_SUCCESS ? 0 : PYRE_ERR_BAD_ARG;
 }
 
-template <int BN, int STAGES, bool XC, int CTAS = 1>
+template <int BN, int STAGES, bool XC, int CTAS = 1, bool FOLD = true>
 int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES, XC, CTAS>;
     static_assert(L::TOTAL <= 232448, "the ring does not fit into shared memory");
     static bool configured_on[PYRE_MAX_DEVICES] = {};      // the attributes are per device
     bool& configured = configured_on[pyre_current_device()];
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, XC, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES, XC, CTAS, FOLD>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -869,9 +873,9 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, di
         attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = pyre_pdl_enabled() ? 2 : 1;
-        e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, XC, CTAS>, mx, my, p);
+        e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES, XC, CTAS, FOLD>, mx, my, p);
     } else {
-        e = pyre_launch(gemm_tc_kernel<BN, STAGES, XC, CTAS>, grid, dim3(THREADS), (size_t)L::TOTAL, stream, mx, my, p);
+        e = pyre_launch(gemm_tc_kernel<BN, STAGES, XC, CTAS, FOLD>, grid, dim3(THREADS), (size_t)L::TOTAL, stream, mx, my, p);
     }
     if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();
@@ -1004,8 +1008,11 @@ static int gemm_tc_impl(const void* X, int x_rows, long long ldx, const void* Y,
         }
     }
     dim3 grid((unsigned)ctas, 1, splits);
+    const bool fold = p.fix != 0 || p.scale_ssq != nullptr;      // the plain products run the variant without that code
 #define GO(BN_, ST_)                                                              \
-    rc = xc ? launch<BN_, ST_, true>(mx, my, p, grid, stream) : launch<BN_, ST_, false>(mx, my, p, grid, stream)
+    rc = !xc ? launch<BN_, ST_, false>(mx, my, p, grid, stream)                                   \
+        : fold ? launch<BN_, ST_, true, 1, true>(mx, my, p, grid, stream)                           \
+               : launch<BN_, ST_, true, 1, false>(mx, my, p, grid, stream)
     switch (bn) {
         case 16: GO(16, 10); break;
         case 32: GO(32, 10); break;

@@ -826,6 +826,9 @@ def _launch_with_fixup(prod: DeferredProduct, fx: "lib.GemmFix", rows_out: "torc
     M, K = x.shape
     N = w.shape[0]
     weights_as_rows, bn, splits = tc_gemm_plan(M, N, K)
+    if M <= 128 and not weights_as_rows:
+        # the fix-up lives in the orientation with the weights on the rows; the same tiles and splits serve it
+        weights_as_rows, bn = True, 128
     err = device_error_flag(x.device).data_ptr()
     with lib.section(prod.section):
         if weights_as_rows:
