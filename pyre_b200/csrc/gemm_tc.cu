@@ -226,7 +226,7 @@ struct SmemLayout {
 // loads; the MMA commits arrive on the "empty" and "accumulator full" barriers of both; the epilogue warps of
 // both arrive on the first CTA's "accumulator empty" barriers.
 template <int BN, int STAGES, bool X_CONTIGUOUS_OUT, int CTAS = 1, bool FOLD = true>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, (X_CONTIGUOUS_OUT && FOLD) ? 5 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const GemmParams p) {
     static_assert(CTAS == 1 || (CTAS == 2 && !X_CONTIGUOUS_OUT && BN % 16 == 0), "pairs serve the row store");
     using L = SmemLayout<BN, STAGES, X_CONTIGUOUS_OUT, CTAS>;
