@@ -512,6 +512,76 @@ def test_attention_prefill_and_mixed_dispatch(ops, nh, nkv, hd, page, window):
     assert (out[:314].float() - want[:314]).abs().max() < 0.05
 
 
+def plain_attention_portions(q, cache, table, cu, starts, nh, nkv, hd, scale, window):
+    """Causal (windowed) attention of whole portions over the paged cache, in float64: pyre/model.py:104-124."""
+    page = cache.shape[3]
+    out = torch.zeros(q.shape[0], nh, hd, dtype=torch.float64, device=q.device)
+    for s in range(len(starts)):
+        b, e = int(cu[s]), int(cu[s + 1])
+        n, ctx = e - b, int(starts[s]) + e - b
+        idx = torch.arange(ctx, device=q.device)
+        pages = table[s, idx // page].long()
+        k = cache[pages, 0, :, idx % page].double().repeat_interleave(nh // nkv, dim=1)     # [ctx, nh, hd]
+        v = cache[pages, 1, :, idx % page].double().repeat_interleave(nh // nkv, dim=1)
+        pos = int(starts[s]) + torch.arange(n, device=q.device)
+        mask = idx[None, :] <= pos[:, None]
+        if window:
+            mask &= idx[None, :] >= pos[:, None] - window + 1
+        sc = torch.einsum("qhd,khd->hqk", q[b:e].double().view(n, nh, hd), k) * scale
+        pr = torch.softmax(sc.masked_fill(~mask[None], float("-inf")), dim=-1)
+        out[b:e] = torch.einsum("hqk,khd->qhd", pr, v)
+    return out.view(q.shape[0], nh * hd).float()
+
+
+@pytest.mark.parametrize("nh,nkv,hd,page,window", [(4, 2, 128, 16, None), (3, 1, 64, 4, None), (2, 2, 128, 64, 100),
+                                                   (4, 1, 64, 256, 300), (2, 1, 128, 8, 129), (7, 1, 128, 16, 1000)])
+def test_attention_prefill_tc_long_portions(ops, nh, nkv, hd, page, window):
+    """Portions of several 256-token pieces that start anywhere in their contexts (two query tiles per CTA share the
+    key tiles; the last piece has one tile, or a second one of a single row), windows shorter and longer than a
+    tile, pages from 4 tokens to more than a key tile; unwritten cache positions hold NaN, and one far key decides
+    a row deep in the first portion."""
+    g = torch.Generator(device="cuda").manual_seed(41)
+    ctx_lens = [1000, 300, 2000, 500, 70]
+    new = [700, 300, 257, 129, 64]
+    starts = [c - n for c, n in zip(ctx_lens, new)]
+    B = len(new)
+    n_pages = sum(-(-c // page) for c in ctx_lens) + 3
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(42)).tolist()
+    W = max(-(-c // page) for c in ctx_lens)
+    table = torch.full((B, W), -1, dtype=torch.int32)
+    for s_, c in enumerate(ctx_lens):
+        for lp in range(-(-c // page)):
+            table[s_, lp] = perm.pop()
+    table = table.cuda()
+    cache = torch.randn(n_pages, 2, nkv, page, hd, device="cuda", generator=g)
+    for s_, c in enumerate(ctx_lens):
+        if c % page:
+            cache[int(table[s_, (c - 1) // page]), :, :, c % page:] = float("nan")
+    for pg in perm:
+        cache[pg] = float("nan")
+    cu = torch.tensor([0] + [sum(new[:k + 1]) for k in range(B)], dtype=torch.int32, device="cuda")
+    positions = torch.tensor(sum((list(range(c - n, c)) for c, n in zip(ctx_lens, new)), []), dtype=torch.int32, device="cuda")
+    T = int(positions.shape[0])
+    q = torch.randn(T, nh * hd, device="cuda", generator=g) * 1.5
+    row = 600                                           # of the first portion: position 900
+    far = 5 if not window else max(int(positions[row]) - window + 1, 3)
+    pg, off = int(table[0, far // page]), far % page
+    cache[pg, 0, 0, off] = q[row, :hd] * 2.0
+    cache, q = cache.to(torch.bfloat16), q.to(torch.bfloat16)
+    scale = hd ** -0.5
+    want = plain_attention_portions(q.float(), cache.float(), table, cu, starts, nh, nkv, hd, scale, window)
+    for rep in range(2):
+        got = torch.full_like(q, 7.0)
+        ops.attention_prefill_tc(q, cache, table, cu, positions, B, T, nh, nkv, hd, scale, window, got, 64)
+        ops.check_device_errors()
+        assert torch.isfinite(got).all()
+        err = (got.float() - want).abs()
+        bad = (err > 1.2e-2 + 1.6e-2 * want.abs()).any(dim=1)
+        assert not bad.any(), f"first wrong token row {int(torch.where(bad)[0][0])} of {T}, max error {float(err.max()):.3e}"
+        v_far = cache[pg, 1, 0, off].float()
+        assert (got[row, :hd].float() - v_far).abs().max() < 0.25 * v_far.abs().max() + 0.1
+
+
 def test_sampling_large_vocabulary_two_stages(ops):
     from plain import qwen2_plain
     g = torch.Generator(device="cuda").manual_seed(8)
