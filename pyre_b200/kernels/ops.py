@@ -764,7 +764,7 @@ def gemm_tc(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: torch.dt
     weights_as_rows, bn, splits = plan or tc_gemm_plan(M, N, K)
     if gated and plan is None and 64 < M <= 128 and N % 256 == 0:
         weights_as_rows, bn, splits = False, 256, 1      # 128 tokens: 59.9 us with the weights on the rows, 53.1 so
-    if scaled is not None and weights_as_rows and M > bn:      # several tiles of tokens on the narrow side: not served
+    if scaled is not None and weights_as_rows and (M > bn or bn > 128):      # more than one tile of at most 128 tokens on the narrow side: not served
         x, scaled = materialize(scaled), None
     splits = max(1, min(splits, -(-K // 64)))
     if pair is None:

@@ -724,6 +724,28 @@ def test_attention_long_context(ops, nh, nkv, hd, page, window):
     check(other, slice(0, 700), "mma.sync prompt kernel")
 
 
+@pytest.mark.parametrize("M", [3, 100, 165, 256, 358])
+@pytest.mark.parametrize("N", [148, 256, 20])
+def test_rows_without_their_rms_into_any_product(ops, M, N):
+    """Activations that still lack their 1/rms (``ScaledRows``) go into products of every plan: widths that are no
+    multiple of 8 put the weights on the MMA's rows whatever the token count, and more than 128 tokens there are
+    served by materialising the rows first."""
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    H, eps = 112, 1e-5
+    v = torch.randn(M, H, device="cuda", generator=g) * 3.0
+    gain = 1 + 0.1 * torch.randn(H, device="cuda", generator=g)
+    w = (torch.randn(N, H, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    rows = (v * gain).to(torch.bfloat16)
+    ssq = v.pow(2).sum(-1)[None].contiguous()                     # one tile of up to 128 features
+    h = ops.ScaledRows(rows, ssq, eps)
+    want = (rows.float() * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)) @ w.float().t()
+    got = ops.linear(h, w)
+    ops.check_device_errors()
+    torch.testing.assert_close(got.float(), want, rtol=2e-2, atol=2e-2 * float(want.abs().max()))
+    torch.testing.assert_close(ops.materialize(h).float(), rows.float() * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps),
+                               rtol=1e-2, atol=1e-2)
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 3584, 3584), (8, 3584, 18944), (64, 896, 4864), (100, 200, 136), (128, 3584, 512), (5, 1160, 72),
                                    (2048, 3584, 3584), (300, 3584, 3584), (1000, 896, 4864), (2048, 3584, 18944), (700, 1160, 136)])
 def test_product_with_residual_and_norm_folded_in(ops, M, N, K):
