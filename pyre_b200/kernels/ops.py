@@ -948,6 +948,8 @@ def linear(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: "torch.dt
         return gemm_tc(x, w, out_dtype or torch.bfloat16, reduce=not partials_ok, checked=True)
     x = materialize(x)
     if out_dtype is None or out_dtype == torch.bfloat16:
+        if partials_ok:     # the consumer adds fp32 partial sums: hand it the accumulator unrounded, as one part
+            return PartialSums(torch.mm(x, w.t(), out_dtype=torch.float32).unsqueeze(0), torch.bfloat16)
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)
 
