@@ -23,8 +23,14 @@ TINY_B = dict(architectures=["Qwen2ForCausalLM"], hidden_size=96, intermediate_s
 TINY_C = dict(architectures=["Qwen2ForCausalLM"], hidden_size=120, intermediate_size=200, num_hidden_layers=2,
               num_attention_heads=6, num_key_value_heads=3, head_dim=48, vocab_size=777, rope_theta=50000.0,
               rms_norm_eps=3e-6, tie_word_embeddings=False, max_position_embeddings=384)
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-PAGE_SIZE = {"A": 16, "B": 8, "C": 32}
+# A fourth one whose width and feed-forward size are no multiples of 8: rows that a TMA copy cannot fetch, so the
+# bfloat16 products with those inner sizes take the library fallback, and the vector paths of the small kernels
+# their scalar form.
+TINY_D = dict(architectures=["Qwen2ForCausalLM"], hidden_size=92, intermediate_size=66, num_hidden_layers=2,
+              num_attention_heads=10, num_key_value_heads=2, head_dim=80, vocab_size=333, rope_theta=12345.0,
+              rms_norm_eps=2e-6, tie_word_embeddings=True, max_position_embeddings=512)
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+PAGE_SIZE = {"A": 16, "B": 8, "C": 32, "D": 64}
 
 
 def make_model_dir(path: Path, raw_cfg: dict, seed: int, sharpen: float = 6.0, matrix_scale: float = 2.5) -> dict[str, torch.Tensor]:

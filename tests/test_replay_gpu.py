@@ -2,7 +2,7 @@
 alone and whole; most of it in one step and the last 32 tokens one by one; in portions
 of changing size down to two tokens; and mixed, up to four live requests with so few
 pages that they are used again (pages that go back to the pool are filled with NaN
-first, so a stale read shows).  In 32-bit and in bfloat16, for three tiny
+first, so a stale read shows).  In 32-bit and in bfloat16, for four tiny
 configurations that differ in every size."""
 
 import numpy as np
@@ -23,7 +23,7 @@ pytestmark = pytest.mark.gpu
 TOL = {"float32": dict(rtol=2e-4, atol=2e-5)}
 BF16_MAX_OVER_RMS = 8.0
 
-LENGTHS = {"A": [5, 17, 33, 70, 100], "B": [1, 7, 40, 63, 100, 131], "C": [3, 64, 97]}
+LENGTHS = {"A": [5, 17, 33, 70, 100], "B": [1, 7, 40, 63, 100, 131], "C": [3, 64, 97], "D": [2, 130, 165, 300]}
 
 
 @pytest.fixture(scope="module")
@@ -71,7 +71,7 @@ def compare(got: dict, want: dict, dtype: str, what: str, bf16_rms: float = 0.0)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_whole(models, name, dtype):
     d, reqs, plain = models[name]
     steps = H.trace_whole(reqs)
@@ -80,7 +80,7 @@ def test_whole(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_last_32_one_by_one(models, name, dtype):
     d, reqs, plain = models[name]
     steps = []
@@ -91,7 +91,7 @@ def test_last_32_one_by_one(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_portions(models, name, dtype):
     d, reqs, plain = models[name]
     steps = []
@@ -103,7 +103,7 @@ def test_portions(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_with_page_reuse(models, name, dtype):
     d, reqs, plain = models[name]
     # every request twice under different ids, so that later ones land on pages the earlier ones gave back
