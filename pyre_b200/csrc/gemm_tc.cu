@@ -881,6 +881,15 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, di
     return (int)cudaGetLastError();
 }
 
+// The row store of one CTA per tile: the variant without the folded work exists at 128 columns only.
+template <int BN, int STAGES>
+int launch_rows(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, dim3 grid, cudaStream_t stream, bool fold) {
+    if constexpr (BN == 128) {
+        if (!fold) return launch<BN, STAGES, false, 1, false>(mx, my, p, grid, stream);
+    }
+    return launch<BN, STAGES, false>(mx, my, p, grid, stream);
+}
+
 }  // namespace
 
 // D[x, y] = sum_k X[x, k] Y[y, k] for bf16 X [x_rows, K] (leading dimension ldx) and Y [y_rows, K] (ldy).
@@ -1008,9 +1017,11 @@ static int gemm_tc_impl(const void* X, int x_rows, long long ldx, const void* Y,
         }
     }
     dim3 grid((unsigned)ctas, 1, splits);
-    const bool fold = p.fix != 0 || p.scale_ssq != nullptr;      // the plain products run the variant without that code
+    // the plain products run the variant without that code: the weight stream always, the row store at the one width
+    // that decode steps of 65-128 tokens use (106 registers instead of 183: the attention's CTAs fit beside it)
+    const bool fold = p.fix != 0 || p.scale_ssq != nullptr;
 #define GO(BN_, ST_)                                                              \
-    rc = !xc ? launch<BN_, ST_, false>(mx, my, p, grid, stream)                                   \
+    rc = !xc ? launch_rows<BN_, ST_>(mx, my, p, grid, stream, fold)                               \
         : fold ? launch<BN_, ST_, true, 1, true>(mx, my, p, grid, stream)                           \
                : launch<BN_, ST_, true, 1, false>(mx, my, p, grid, stream)
     switch (bn) {
