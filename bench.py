@@ -252,7 +252,10 @@ def run_ours(args) -> dict:
     pf_ms = sorted(times)[len(times) // 2]
     pf_flops = flops(PROMPT_LEN, 0, 1)
     prefill = {"value": round(PROMPT_LEN / pf_ms * 1e3, 1), "tokens": PROMPT_LEN, "ms": round(pf_ms, 3),
-               "frac": round(pf_flops / (pf_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+               "frac": round(pf_flops / (pf_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4),
+               # the same against the figure of a seconds-long loop under the power cap (this step repeats back to back)
+               "frac_of_sustained": round(pf_flops / (pf_ms * 1e-3) / (peaks["bf16_tflops_sustained"] * 1e12), 4),
+               "first_ms": round(times[0], 3)}
 
     # ---------------------------------------------------------------- decode, device-timed
     def decode_run(batch: int, n_warm: int, n_steps: int, tag: str):
