@@ -16,6 +16,14 @@ import time
 from pathlib import Path
 
 
+SIZES = ("Sizes: a head size must be a multiple of 16 up to 256 (others are refused when the model is built).  "
+         "In bfloat16, head sizes up to 128 run on the tensor-core attention kernels, larger ones on the exact "
+         "fp32-arithmetic kernel, as every float32 run does (slower).  A bfloat16 product whose inner size is no "
+         "multiple of 8 (a hidden or feed-forward size like 92) goes to a library product; every other product and "
+         "every size of the supported checkpoints runs on the package's own kernels.  Pages of the tcgen05 prompt "
+         "attention are powers of two from 4 tokens; other page sizes use the mma.sync kernels.")
+
+
 def _parse_ids(text: str) -> list[int]:
     return [int(t) for t in text.replace(",", " ").split()]
 
@@ -81,10 +89,10 @@ def cmd_random_model(args) -> int:
 
 
 def main(argv=None) -> int:
-    ap = argparse.ArgumentParser(prog="pyre_b200", description=__doc__.split("\n\n")[0])
+    ap = argparse.ArgumentParser(prog="pyre_b200", description=__doc__.split("\n\n")[0], epilog=SIZES)
     sub = ap.add_subparsers(dest="command", required=True)
 
-    g = sub.add_parser("generate", help="generate tokens for prompts given as token ids")
+    g = sub.add_parser("generate", help="generate tokens for prompts given as token ids", epilog=SIZES)
     g.add_argument("--model", required=True, help="folder with config.json and *.safetensors")
     g.add_argument("--device", default="cuda:0")
     g.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
