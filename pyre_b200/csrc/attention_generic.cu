@@ -31,8 +31,8 @@ __global__ void paged_attention_generic_kernel(
     const int* __restrict__ positions,     // [n_tokens]
     int n_tokens, int nh, int nkv, int hd, int page_size, int window, float scale, long long n_pages, int* err_flag) {
     extern __shared__ float q_smem[];  // [warps][hd]
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int warps = blockDim.x >> 5;
     const long long item = (long long)blockIdx.x * warps + warp;

@@ -16,8 +16,8 @@
 template <typename T, int VEC>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
                                  int H, int V, int* __restrict__ err) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* dst = x + (size_t)t * H;
@@ -91,8 +91,8 @@ template <typename T, int VEC, int KEEP>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ partials,
                                    int n_partials, long long partial_stride, const float* __restrict__ w,
                                    T* __restrict__ out, const int* __restrict__ rows, int H, float eps, int update_x) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -186,8 +186,8 @@ PYRE_API int pyre_add_rmsnorm(float* x, const void* delta, const float* partials
 // x[t, :] += delta[t, :] (fp32 sum), for a residual that no norm follows.
 template <typename T>
 __global__ void add_residual_kernel(float* __restrict__ x, const T* __restrict__ delta, size_t n) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         x[i] = x[i] + to_f32<T>(delta[i]);
 }
@@ -210,8 +210,8 @@ PYRE_API int pyre_add_residual(float* x, const void* delta, long long n, int dty
 // ---------------------------------------------------------------------------
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                   float* __restrict__ cos_out, float* __restrict__ sin_out, int n_tokens, int half) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_tokens * half) return;
     const int t = i / half, j = i - t * half;
@@ -271,8 +271,8 @@ __global__ void qkv_rope_write_kernel(const T* __restrict__ qkv, const float* __
                                       T* __restrict__ q_out, T* __restrict__ cache,
                                       const int* __restrict__ slot_mapping, int nh, int nkv, int hd, int rot,
                                       int page_size, long long n_pages, int* err_flag) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;   // one token per blockIdx.x; blockIdx.y strides over its items
     const int half = rot / 2;
     const int chunks = hd / 4;
@@ -362,8 +362,8 @@ __global__ void qkv_rope_write_full_kernel(const T* __restrict__ qkv, const floa
                                            T* __restrict__ q_out, T* __restrict__ cache,
                                            const int* __restrict__ slot_mapping, int nh, int nkv, int hd, int page_size,
                                            long long n_pages, int* err_flag) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     const int half = hd / 2;
     const int per_head = half / VEC;
@@ -459,8 +459,8 @@ PYRE_API int pyre_qkv_rope_write(const void* qkv, const float* partials, int n_p
 // ---------------------------------------------------------------------------
 template <typename T, int VEC>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tokens, int I, int block) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const size_t per_row = (size_t)(I / VEC);
     const size_t total = per_row * n_tokens;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -510,8 +510,8 @@ PYRE_API int pyre_silu_mul(const void* gu, void* out, int n_tokens, int I, int b
 template <typename T>
 __global__ void sum_partials_kernel(const float* __restrict__ partials, int n_splits, long long split_stride,
                                     T* __restrict__ out, long long n) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         float acc = partials[i];
         for (int s = 1; s < n_splits; ++s) acc += partials[(long long)s * split_stride + i];
@@ -538,8 +538,8 @@ PYRE_API int pyre_sum_partials(const float* partials, int n_splits, long long sp
 // ---------------------------------------------------------------------------
 __global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ dst, const int* __restrict__ src,
                                    const int* __restrict__ prev, int n) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int d = dst[i];
@@ -578,8 +578,8 @@ PYRE_API int pyre_delay(long long ns, cudaStream_t stream) {
 // ---------------------------------------------------------------------------
 __global__ void scale_rows_kernel(const __nv_bfloat16* __restrict__ rows, const float* __restrict__ ssq, int n_tiles,
                                   __nv_bfloat16* __restrict__ out, int n_tokens, int H, float eps) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const int t = blockIdx.x;
     float s = 0.f;
     for (int j = 0; j < n_tiles; ++j) s += ssq[(size_t)j * n_tokens + t];

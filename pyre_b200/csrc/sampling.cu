@@ -39,8 +39,8 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long ld, co
                               const unsigned long long* __restrict__ seeds, const int* __restrict__ token_index,
                               int* __restrict__ out, int V) {
     __shared__ Best warp_best[32];
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * ld;
     const float temp = temperature ? temperature[r] : 0.f;
@@ -82,8 +82,8 @@ __global__ void sample_slices_kernel(const float* __restrict__ logits, long long
                                      const unsigned long long* __restrict__ seeds, const int* __restrict__ token_index,
                                      float* __restrict__ slice_score, int* __restrict__ slice_index, int V, int slice) {
     __shared__ Best warp_best[32];
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const int r = blockIdx.y, sl = blockIdx.x;
     const float* row = logits + (size_t)r * ld;
     const float temp = temperature ? temperature[r] : 0.f;
@@ -123,8 +123,8 @@ __global__ void sample_slices_kernel(const float* __restrict__ logits, long long
 
 __global__ void sample_pick_kernel(const float* __restrict__ slice_score, const int* __restrict__ slice_index,
                                    int* __restrict__ out, int n_slices) {
-    pdl_trigger();
     pdl_wait();
+    pdl_trigger();
     const int r = blockIdx.x;
     Best best{-INFINITY, 0x7fffffff};
     for (int i = threadIdx.x; i < n_slices; i += 32)
