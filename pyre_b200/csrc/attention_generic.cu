@@ -22,17 +22,17 @@
 
 template <typename T>
 __global__ void paged_attention_generic_kernel(
-    const T* __restrict__ q,             // [n_tokens, nh, hd]
-    const T* __restrict__ cache,         // one layer: [page][2][nkv][page_size][hd]
-    T* __restrict__ out,                 // [n_tokens, nh * hd]
-    const int* __restrict__ block_table, // [n_seqs, bt_stride] logical page -> physical page (or -1)
+    const T* q,             // [n_tokens, nh, hd]
+    const T* cache,         // one layer: [page][2][nkv][page_size][hd]
+    T* out,                 // [n_tokens, nh * hd]
+    const int* block_table, // [n_seqs, bt_stride] logical page -> physical page (or -1)
     int bt_stride,
-    const int* __restrict__ seq_of_token,  // [n_tokens]
-    const int* __restrict__ positions,     // [n_tokens]
+    const int* seq_of_token,  // [n_tokens]
+    const int* positions,     // [n_tokens]
     int n_tokens, int nh, int nkv, int hd, int page_size, int window, float scale, long long n_pages, int* err_flag) {
     extern __shared__ float q_smem[];  // [warps][hd]
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int warps = blockDim.x >> 5;
     const long long item = (long long)blockIdx.x * warps + warp;

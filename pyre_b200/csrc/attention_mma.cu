@@ -156,6 +156,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     if constexpr (CLUSTER) (void)cg::this_cluster().barrier_arrive();   // phase 1 ("this CTA runs"), awaited before the merge
+    pdl_trigger();
     // What follows until pdl_wait() reads only what no kernel of this step writes: the step's index arrays
     // (copied from the host before the step's first kernel) and keys and values of EARLIER steps.  The
     // queries, and the keys and values of this step's own tokens, are touched after the wait.
@@ -326,7 +327,6 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
         }
     }
     pdl_wait();
-    pdl_trigger();
 #pragma unroll
     for (int j = 0; j < STAGES - 1; ++j) {
         if (j < n_mine && !is_old(j)) {
@@ -591,11 +591,11 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
 // merge through shared memory in warp order.
 constexpr int COMBINE_WARPS = 8;
 __global__ void __launch_bounds__(COMBINE_WARPS * 32)
-combine_splits_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                      __nv_bfloat16* __restrict__ out, int n_splits, int hd, int nh,
-                      const int* __restrict__ cu_seqlens, int n_seqs, int max_len) {
-    pdl_wait();
+combine_splits_kernel(const float* part_acc, const float* part_ml,
+                      __nv_bfloat16* out, int n_splits, int hd, int nh,
+                      const int* cu_seqlens, int n_seqs, int max_len) {
     pdl_trigger();
+    pdl_wait();
     const size_t th = blockIdx.x;
     if (max_len > 0) {
         // rows of entries longer than max_len belong to the prefill kernel: no partials, nothing to do

@@ -71,8 +71,8 @@ __global__ void __launch_bounds__(WARPS * 32, 3) attention_prefill_kernel(const 
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    pdl_wait();   // queries, pages and index arrays come from earlier kernels of the step
     pdl_trigger();
+    pdl_wait();   // queries, pages and index arrays come from earlier kernels of the step
 
     // ---- which 64-token tile of which entry is this CTA's?  (entries shorter than min_len are skipped)
     // CTAs start in the order of blockIdx.x; the last tile of a portion sees the most keys, so

@@ -208,6 +208,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::OFF_BAR + L::N_BARS * 8 + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_trigger();
 
     // ---- which 128-token tile of which entry?  tiles are numbered from the end of each portion
     // (the last tile sees the most keys and starts first)
@@ -262,7 +263,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_kv)) : "memory");
         }
         pdl_wait();   // queries and pages of this step come from earlier kernels
-        pdl_trigger();
         if (which == 0 && lane == 0) {
             mbar_expect_tx(bar_q, L::Q_BYTES);
 #pragma unroll

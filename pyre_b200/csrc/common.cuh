@@ -96,15 +96,17 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 // earlier kernel of the step writes or still reads (only its own set-up and constant
 // weights); pdl_wait() returns when the kernel before it has completed and its writes
 // are visible, which, by induction along the stream, holds for all earlier kernels too.
-// A kernel calls pdl_trigger() AFTER its own pdl_wait(), never before.  With the trigger first, a
-// kernel's successor could be resident while the kernel's predecessor was still running; an SM's L1 is
-// made clean when a kernel starts on it, so lines that the old kernel then read there (a buffer that is
-// recycled and rewritten in between) were stale for the successor's loads after its wait.  This was seen,
-// not guessed: the fp32 tile product read stale activations in tiny models where three kernels of a chain
-// fit on one SM at once.  With the trigger after the wait, everything before a kernel's predecessor has
-// completed when the kernel's CTAs start.
 // Without the attribute both calls do nothing.  PYRE_PDL=0 in the environment turns the
 // attribute off.
+//
+// NO READ-ONLY LOADS of anything an earlier kernel writes.  "Visible" holds for ordinary loads.  A load
+// through the read-only path (ld.global.nc: what the compiler makes of a `const T* __restrict__`
+// parameter, and what __ldg() is) promises that the data does not change while the kernel lives, and under
+// this attribute a kernel lives while its predecessors still write: such a load returned stale activations
+// (seen in the fp32 tile product of tiny models, where three kernels of a chain sit on one SM at once;
+// gone with an ordinary load).  So no kernel parameter in this directory is `__restrict__`, nothing uses
+// __ldg(), and tests/test_bindings.py compiles every source to PTX and fails if an ld.global.nc appears
+// (the one in sincosf's table of 2/pi apart).
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

@@ -14,10 +14,10 @@
 // and raises the error flag (the host checks ids first; this only guards memory).
 // ---------------------------------------------------------------------------
 template <typename T, int VEC>
-__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
-                                 int H, int V, int* __restrict__ err) {
-    pdl_wait();
+__global__ void embedding_kernel(const T* table, const int* ids, float* x,
+                                 int H, int V, int* err) {
     pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* dst = x + (size_t)t * H;
@@ -88,11 +88,11 @@ __device__ __forceinline__ void load_delta(Vec<float, VEC>& a, const T* dr, cons
 // then read once; every global round trip counts in a kernel that handles a few rows of a decode step); 0: the row
 // is read again for the scaling (any width).
 template <typename T, int VEC, int KEEP>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ partials,
-                                   int n_partials, long long partial_stride, const float* __restrict__ w,
-                                   T* __restrict__ out, const int* __restrict__ rows, int H, float eps, int update_x) {
-    pdl_wait();
+__global__ void add_rmsnorm_kernel(float* x, const T* delta, const float* partials,
+                                   int n_partials, long long partial_stride, const float* w,
+                                   T* out, const int* rows, int H, float eps, int update_x) {
     pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
@@ -185,9 +185,9 @@ PYRE_API int pyre_add_rmsnorm(float* x, const void* delta, const float* partials
 
 // x[t, :] += delta[t, :] (fp32 sum), for a residual that no norm follows.
 template <typename T>
-__global__ void add_residual_kernel(float* __restrict__ x, const T* __restrict__ delta, size_t n) {
-    pdl_wait();
+__global__ void add_residual_kernel(float* x, const T* delta, size_t n) {
     pdl_trigger();
+    pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         x[i] = x[i] + to_f32<T>(delta[i]);
 }
@@ -208,14 +208,14 @@ PYRE_API int pyre_add_residual(float* x, const void* delta, long long n, int dty
 // all in fp32 (accurate sincosf; this file is never built with fast-math).  Computed
 // once per step and shared by every layer with the same rotary settings.
 // ---------------------------------------------------------------------------
-__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
-                                  float* __restrict__ cos_out, float* __restrict__ sin_out, int n_tokens, int half) {
-    pdl_wait();
+__global__ void rope_table_kernel(const int* positions, const float* inv_freq,
+                                  float* cos_out, float* sin_out, int n_tokens, int half) {
     pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_tokens * half) return;
     const int t = i / half, j = i - t * half;
-    const float ang = __fmul_rn((float)positions[t], inv_freq[j]);
+    const float ang = __fmul_rn((float)__ldcg(positions + t), inv_freq[j]);   // positions may come from an earlier kernel: no read-only load
     float s, c;
     sincosf(ang, &s, &c);
     cos_out[i] = c;
@@ -265,14 +265,14 @@ __device__ __forceinline__ void load_qkv4(float (&v)[4], const T* in, const floa
 }
 
 template <typename T>
-__global__ void qkv_rope_write_kernel(const T* __restrict__ qkv, const float* __restrict__ partials, int n_partials,
-                                      long long partial_stride, const float* __restrict__ bias,
-                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                      T* __restrict__ q_out, T* __restrict__ cache,
-                                      const int* __restrict__ slot_mapping, int nh, int nkv, int hd, int rot,
+__global__ void qkv_rope_write_kernel(const T* qkv, const float* partials, int n_partials,
+                                      long long partial_stride, const float* bias,
+                                      const float* cos_t, const float* sin_t,
+                                      T* q_out, T* cache,
+                                      const int* slot_mapping, int nh, int nkv, int hd, int rot,
                                       int page_size, long long n_pages, int* err_flag) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;   // one token per blockIdx.x; blockIdx.y strides over its items
     const int half = rot / 2;
     const int chunks = hd / 4;
@@ -356,14 +356,14 @@ __device__ __forceinline__ void load_qkv_vec(float (&v)[VEC], const T* in, const
 }
 
 template <typename T, int VEC>
-__global__ void qkv_rope_write_full_kernel(const T* __restrict__ qkv, const float* __restrict__ partials, int n_partials,
-                                           long long partial_stride, const float* __restrict__ bias,
-                                           const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                                           T* __restrict__ q_out, T* __restrict__ cache,
-                                           const int* __restrict__ slot_mapping, int nh, int nkv, int hd, int page_size,
+__global__ void qkv_rope_write_full_kernel(const T* qkv, const float* partials, int n_partials,
+                                           long long partial_stride, const float* bias,
+                                           const float* cos_t, const float* sin_t,
+                                           T* q_out, T* cache,
+                                           const int* slot_mapping, int nh, int nkv, int hd, int page_size,
                                            long long n_pages, int* err_flag) {
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     const int half = hd / 2;
     const int per_head = half / VEC;
@@ -458,9 +458,9 @@ PYRE_API int pyre_qkv_rope_write(const void* qkv, const float* partials, int n_p
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i],  silu(z) = z / (1 + exp(-z))  in fp32.
 // ---------------------------------------------------------------------------
 template <typename T, int VEC>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int n_tokens, int I, int block) {
-    pdl_wait();
+__global__ void silu_mul_kernel(const T* gu, T* out, int n_tokens, int I, int block) {
     pdl_trigger();
+    pdl_wait();
     const size_t per_row = (size_t)(I / VEC);
     const size_t total = per_row * n_tokens;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -508,10 +508,10 @@ PYRE_API int pyre_silu_mul(const void* gu, void* out, int n_tokens, int I, int b
 // product whose K was split over CTAs, in a fixed order, and converts.
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void sum_partials_kernel(const float* __restrict__ partials, int n_splits, long long split_stride,
-                                    T* __restrict__ out, long long n) {
-    pdl_wait();
+__global__ void sum_partials_kernel(const float* partials, int n_splits, long long split_stride,
+                                    T* out, long long n) {
     pdl_trigger();
+    pdl_wait();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
         float acc = partials[i];
         for (int s = 1; s < n_splits; ++s) acc += partials[(long long)s * split_stride + i];
@@ -536,10 +536,10 @@ PYRE_API int pyre_sum_partials(const float* partials, int n_splits, long long sp
 // ids[dst[i]] = prev[src[i]] for every i with dst[i] >= 0: the tokens that the last step
 // sampled become inputs of the next step without a trip through the host.
 // ---------------------------------------------------------------------------
-__global__ void feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ dst, const int* __restrict__ src,
-                                   const int* __restrict__ prev, int n) {
-    pdl_wait();
+__global__ void feed_tokens_kernel(int* ids, const int* dst, const int* src,
+                                   const int* prev, int n) {
     pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int d = dst[i];
@@ -576,10 +576,10 @@ PYRE_API int pyre_delay(long long ns, cudaStream_t stream) {
 // activations that carry a norm's weight but not yet its 1/rms (left so by a product's fix-up, whose
 // consumer normally applies the factor in its own epilogue), made plain for any other consumer.
 // ---------------------------------------------------------------------------
-__global__ void scale_rows_kernel(const __nv_bfloat16* __restrict__ rows, const float* __restrict__ ssq, int n_tiles,
-                                  __nv_bfloat16* __restrict__ out, int n_tokens, int H, float eps) {
-    pdl_wait();
+__global__ void scale_rows_kernel(const __nv_bfloat16* rows, const float* ssq, int n_tiles,
+                                  __nv_bfloat16* out, int n_tokens, int H, float eps) {
     pdl_trigger();
+    pdl_wait();
     const int t = blockIdx.x;
     float s = 0.f;
     for (int j = 0; j < n_tiles; ++j) s += ssq[(size_t)j * n_tokens + t];

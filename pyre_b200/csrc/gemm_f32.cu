@@ -20,13 +20,13 @@
 
 template <int BM, int BN, int BK, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
-sgemm_nt_kernel(const float* __restrict__ A, long long lda, const float* __restrict__ W, long long ldw,
-                float* __restrict__ C, long long ldc, const float* __restrict__ bias, int M, int N, int K) {
+sgemm_nt_kernel(const float* A, long long lda, const float* W, long long ldw,
+                float* C, long long ldc, const float* bias, int M, int N, int K) {
     constexpr int THREADS = (BM / TM) * (BN / TN);
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int tid = threadIdx.x;
     const int tx = tid % (BN / TN);  // column group
     const int ty = tid / (BN / TN);  // row group
@@ -94,13 +94,13 @@ sgemm_nt_kernel(const float* __restrict__ A, long long lda, const float* __restr
 // cover 128 consecutive bytes of shared memory.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-sgemm_nt_tiles_kernel(const float* __restrict__ A, long long lda, const float* __restrict__ W, long long ldw,
-                      float* __restrict__ C, long long ldc, const float* __restrict__ bias, int M, int N, int K) {
+sgemm_nt_tiles_kernel(const float* A, long long lda, const float* W, long long ldw,
+                      float* C, long long ldc, const float* bias, int M, int N, int K) {
     constexpr int BM = 128, BN = 128, BK = 16, RUN = 32;
     __shared__ __align__(16) float As[2][BK][BM + 4];
     __shared__ __align__(16) float Ws[2][BK][BN + 4];
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     // loads: 128 rows x 4 float4 per operand and step; a thread fetches rows lr and lr + 64, k quad lq
@@ -179,11 +179,12 @@ sgemm_nt_tiles_kernel(const float* __restrict__ A, long long lda, const float* _
 // ---------------------------------------------------------------------------
 template <int MT>
 __global__ void __launch_bounds__(128)
-sgemm_nt_stream_kernel(const float* __restrict__ A, long long lda, const float* __restrict__ W, long long ldw,
-                       float* __restrict__ C, long long ldc, const float* __restrict__ bias, int M, int N, int K) {
+sgemm_nt_stream_kernel(const float* A, long long lda, const float* W, long long ldw,
+                       float* C, long long ldc, const float* bias, int M, int N, int K) {
     constexpr int FN = 16, RUN = 32, STAGES = 4, PITCH = RUN + 4, PER = MT / 8;
     __shared__ __align__(16) float Ws[STAGES][FN][PITCH];
     __shared__ __align__(16) float As[STAGES][MT][PITCH];
+    pdl_trigger();
     const int tid = threadIdx.x, tn = tid & 15, tg = tid >> 4;
     const int n0 = blockIdx.x * FN, m0 = blockIdx.y * MT;
     const int n_runs = (K + RUN - 1) / RUN;
@@ -208,7 +209,6 @@ sgemm_nt_stream_kernel(const float* __restrict__ A, long long lda, const float* 
     // the weights depend on no earlier kernel: their first stages are on their way before the wait
     for (int s = 0; s < STAGES - 1; ++s) load_w(s, s);
     pdl_wait();
-    pdl_trigger();
     for (int s = 0; s < STAGES - 1; ++s) {
         load_a(s, s);
         asm volatile("cp.async.commit_group;" ::: "memory");

@@ -256,6 +256,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     constexpr uint32_t ACC_COLS = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;   // columns of one accumulator (a power of two)
     constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;        // power of two >= 32, at most 512
 
+    pdl_trigger();
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
@@ -312,7 +313,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         else load(ys, &map_y, full_to + 8 * j, k, y0);
                     }
                     pdl_wait();
-                    pdl_trigger();      // only now: see common.cuh on why a kernel lets its successor in after its own wait
                     waited = true;
                     for (int j = 0; j < pre; ++j) {
                         const uint32_t xs = base + j * L::STAGE_BYTES, ys = xs + L::X_BYTES;
@@ -337,7 +337,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 }
                 if (!ok) break;
             }
-            if (!waited) { pdl_wait(); pdl_trigger(); }
+            if (!waited) pdl_wait();
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {

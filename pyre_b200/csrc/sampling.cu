@@ -35,12 +35,12 @@ __device__ __forceinline__ Best better(Best a, Best b) {
     return a;
 }
 
-__global__ void sample_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ temperature,
-                              const unsigned long long* __restrict__ seeds, const int* __restrict__ token_index,
-                              int* __restrict__ out, int V) {
+__global__ void sample_kernel(const float* logits, long long ld, const float* temperature,
+                              const unsigned long long* seeds, const int* token_index,
+                              int* out, int V) {
     __shared__ Best warp_best[32];
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * ld;
     const float temp = temperature ? temperature[r] : 0.f;
@@ -78,12 +78,12 @@ __global__ void sample_kernel(const float* __restrict__ logits, long long ld, co
 // Large vocabularies: stage 1 scans a slice of the row per block and leaves its best
 // (score, index) in scratch; stage 2 picks the best slice.  The winner is the same as
 // in the one-block kernel: largest score, lowest index on a tie.
-__global__ void sample_slices_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ temperature,
-                                     const unsigned long long* __restrict__ seeds, const int* __restrict__ token_index,
-                                     float* __restrict__ slice_score, int* __restrict__ slice_index, int V, int slice) {
+__global__ void sample_slices_kernel(const float* logits, long long ld, const float* temperature,
+                                     const unsigned long long* seeds, const int* token_index,
+                                     float* slice_score, int* slice_index, int V, int slice) {
     __shared__ Best warp_best[32];
-    pdl_wait();
     pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.y, sl = blockIdx.x;
     const float* row = logits + (size_t)r * ld;
     const float temp = temperature ? temperature[r] : 0.f;
@@ -121,10 +121,10 @@ __global__ void sample_slices_kernel(const float* __restrict__ logits, long long
     }
 }
 
-__global__ void sample_pick_kernel(const float* __restrict__ slice_score, const int* __restrict__ slice_index,
-                                   int* __restrict__ out, int n_slices) {
-    pdl_wait();
+__global__ void sample_pick_kernel(const float* slice_score, const int* slice_index,
+                                   int* out, int n_slices) {
     pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     Best best{-INFINITY, 0x7fffffff};
     for (int i = threadIdx.x; i < n_slices; i += 32)

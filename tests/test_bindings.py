@@ -124,3 +124,35 @@ def test_a_tensor_on_another_device_is_refused_on_the_host(monkeypatch):
     with step.device_guard("cpu"):          # the stand-ins' device: nothing to enter
         pass
     assert entered == [torch.device("cuda:1")]
+
+
+def test_no_kernel_reads_through_the_read_only_path():
+    """Kernels run under programmatic dependent launch: a CTA may live while earlier kernels still write what
+    it will read, so no load may take the read-only path (``ld.global.nc``), which promises unchanging data for
+    the kernel's whole life (csrc/common.cuh).  Every source is compiled to PTX here and searched; the only such
+    load allowed reads the constant table inside ``sincosf``."""
+    import shutil
+    import subprocess
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not shutil.which(nvcc):
+        pytest.skip("no nvcc on this machine")
+    sources = sorted(set(build.LIBRARIES.values()))
+    assert sources
+    for name in sources:
+        text = (build.CSRC / name).read_text()
+        assert "__restrict__" not in text and "__ldg(" not in text, f"{name}: a read-only qualifier or load"
+    procs = {name: subprocess.Popen([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-I", str(build.CSRC),
+                                     "-ptx", str(build.CSRC / name), "-o", "/dev/stdout"],
+                                    stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for name in sources}
+    for name, proc in procs.items():
+        ptx, err = proc.communicate(timeout=600)
+        assert proc.returncode == 0, f"{name}: {err[-500:]}"
+        lines = ptx.splitlines()
+        bad = []
+        for n, line in enumerate(lines):
+            if "ld.global.nc" in line:
+                address = line.split("[")[-1].split("]")[0].split("+")[0].strip()
+                origin = [prev for prev in lines[max(0, n - 40):n] if address + "," in prev and "mov." in prev]
+                if not (origin and "__cudart_i2opi_f" in origin[-1]):
+                    bad.append(line.strip())
+        assert not bad, f"{name}: read-only loads in the PTX: {bad[:3]}"
