@@ -214,7 +214,7 @@ def run_ours(args) -> dict:
     B = args.batch
     steps, warmup = args.steps, max(args.warmup, 3)
     biggest = max(B, 64 if not args.skip_points else B)
-    tokens_needed = biggest * (PROMPT_LEN + 64 + warmup + steps + PAGE_SIZE) + 2 * CONTEXT
+    tokens_needed = biggest * (PROMPT_LEN + 64 + warmup + steps + PAGE_SIZE) + B * (2 * B + 64) + 2 * CONTEXT
     torch.cuda.set_device(0)
     engine = Engine(config=cfg, seed=0, dtype="bfloat16", device="cuda:0", page_size=PAGE_SIZE,
                     max_cache_tokens=tokens_needed, max_num_seqs=biggest, max_num_batched_tokens=PROMPT_LEN,
@@ -338,7 +338,9 @@ def run_ours(args) -> dict:
         kernels[f"prefill_{PROMPT_LEN}"] = timed(one_prefill, class_work(cfg_raw, layers, PROMPT_LEN, 1, 0, 1))
 
     # ---------------------------------------------------------------- end to end through Engine.step
-    sp = SamplingParams(max_new_tokens=warmup + steps + B + 8, ignore_eos=True)
+    # every request must outlive the timed steps: the first one decodes while the others' prompts (cut to what the
+    # token budget leaves beside the decoded tokens) are still being read, about B * PROMPT_LEN / (budget - B) steps
+    sp = SamplingParams(max_new_tokens=warmup + steps + 2 * B + 64, ignore_eos=True)
     sids = [engine.add_request(rng.integers(0, vocab, PROMPT_LEN).tolist(), params=sp) for _ in range(B)]
     live = [engine._requests[sid] for sid in sids]
     while any(not r.generated for r in live):
@@ -397,6 +399,13 @@ def run_ours(args) -> dict:
         for batch, context in ((1, 8192), (1, 32768), (8, 8192), (8, 32768)):
             points[f"decode_b{batch}_ctx{context // 1024}k"], points[f"hbm_frac_b{batch}_ctx{context // 1024}k"] = \
                 decode_point(eng, long_cfg, layers, batch, context)
+        del eng
+        torch.cuda.empty_cache()
+        # many requests at the benchmark's context
+        eng = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=256 * (PROMPT_LEN + 64),
+                     max_num_seqs=256, max_num_batched_tokens=PROMPT_LEN, prefill_chunk=PROMPT_LEN, max_model_len=CONTEXT)
+        for batch in (128, 256):
+            points[f"decode_b{batch}"], points[f"hbm_frac_b{batch}"] = decode_point(eng, cfg_raw, layers, batch, PROMPT_LEN, n_steps=16)
         del eng
         torch.cuda.empty_cache()
         if layers == layers_full:      # the other shapes only beside the full model
