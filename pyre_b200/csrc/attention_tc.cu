@@ -29,6 +29,11 @@
 // The softmax arithmetic uses the packed fp32 pairs of sm_100 (fma.rn.f32x2, add.rn.f32x2), the
 // three-input max and ex2.approx: about four instructions per score.
 //
+// Few query tiles after a long context (a short portion of a long prompt) would leave most SMs idle: then
+// grid.z CTAs share the key tiles of every (query tile, head), each leaves its unnormalised O with the rows'
+// maxima and sums in scratch memory, and combine_shares_kernel puts them together (the host decides how many:
+// only while there are fewer items than SMs, see ops.prefill_key_splits).
+//
 // Whole page rows arrive, so rows of a V tile outside [first row's window start, last row's
 // position] may hold anything; the row threads zero them in shared memory before the P V
 // product (their probabilities are exactly 0, but 0 x NaN is not).
@@ -170,6 +175,12 @@ struct TcParams {
     float scale;
     int* err_flag;
     long long n_pages;           // pages of the pool; read by the debug checks only
+    // key_splits > 1: grid.z CTAs share the key tiles of one (query tile, head); each leaves its unnormalised O
+    // (fp32 [T, nh, key_splits, HD]) and the row's (maximum in log2 units, sum) ([T, nh, key_splits, 2]) for the
+    // combining kernel
+    int key_splits;
+    float* part_o;
+    float* part_ml;
 };
 
 template <int HD>
@@ -232,7 +243,22 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int* table = p.block_table + (size_t)seq * p.bt_stride;
     const int pos_first = p.positions[tok0], pos_last = pos_first + n_tok - 1;   // consecutive positions
     const int lo_cta = (p.window > 0 && pos_first - p.window + 1 > 0) ? pos_first - p.window + 1 : 0;
-    const int tile_lo = lo_cta / BN, tile_hi = pos_last / BN;
+    int tile_lo = lo_cta / BN, tile_hi = pos_last / BN;
+    if (p.key_splits > 1) {
+        // this CTA's share of the key tiles; a share may be empty (few tiles): it says so and leaves
+        const int per = (tile_hi - tile_lo + p.key_splits) / p.key_splits;
+        tile_lo += (int)blockIdx.z * per;
+        tile_hi = min(tile_hi, tile_lo + per - 1);
+        if (tile_lo > tile_hi) {
+            pdl_wait();      // the scratch may still be read by the combining kernel of the layer before
+            if ((int)threadIdx.x < n_tok) {
+                float* ml = p.part_ml + (((size_t)(tok0 + threadIdx.x) * p.nh + blockIdx.x) * p.key_splits + blockIdx.z) * 2;
+                ml[0] = -INFINITY;
+                ml[1] = 0.f;
+            }
+            return;
+        }
+    }
     const int n_tiles = tile_hi - tile_lo + 1;
 
     if (threadIdx.x == 0) {
@@ -480,13 +506,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = (row_ok && l_sum > 0.f) ? 1.0f / l_sum : 0.f;
             __nv_bfloat16* orow = p.out + ((size_t)(tok0 + (row_ok ? row : 0)) * p.nh + head) * HD;
+            const size_t piece_at = ((size_t)(tok0 + (row_ok ? row : 0)) * p.nh + head) * p.key_splits + blockIdx.z;
+            if (p.key_splits > 1 && row_ok) {
+                p.part_ml[piece_at * 2] = m_ref;
+                p.part_ml[piece_at * 2 + 1] = l_sum;
+            }
 #pragma unroll 1
             for (int c = 0; c < HD; c += 16) {
                 uint32_t r[16];
                 __syncwarp();
                 tmem_ld16(lane_addr + O_COL + c, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row_ok) {
+                if (p.key_splits > 1) {
+                    if (row_ok) {
+                        float4* dst = reinterpret_cast<float4*>(p.part_o + piece_at * HD + c);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                    }
+                } else if (row_ok) {
                     uint32_t w[8];
 #pragma unroll
                     for (int q = 0; q < 8; ++q) w[q] = pack_bf16(__uint_as_float(r[2 * q]) * inv, __uint_as_float(r[2 * q + 1]) * inv);
@@ -504,6 +542,63 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (warp == 1) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// The shares of a (query tile, head) put together: out = sum_i O_i 2^(m_i - M) / sum_i l_i 2^(m_i - M) over the
+// shares that saw a key (l_i > 0).  One CTA per query tile and head as in the main kernel, a warp per row, a lane per
+// four head dimensions.
+template <int HD>
+__global__ void __launch_bounds__(128)
+combine_shares_kernel(const TcParams p) {
+    pdl_trigger();
+    pdl_wait();
+    int tile = blockIdx.y, seq = -1, tok0 = 0, n_tok = 0;
+    for (int b = 0; b < p.n_seqs; ++b) {
+        const int begin = p.cu_seqlens[b], len = p.cu_seqlens[b + 1] - begin;
+        if (len < p.min_len) continue;
+        const int nt = (len + BM - 1) / BM;
+        if (tile < nt) {
+            const int qt = nt - 1 - tile;
+            seq = b;
+            tok0 = begin + qt * BM;
+            n_tok = min(BM, len - qt * BM);
+            break;
+        }
+        tile -= nt;
+    }
+    if (seq < 0) return;
+    const int head = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, S = p.key_splits;
+    for (int row = warp; row < n_tok; row += 4) {
+        const size_t at = ((size_t)(tok0 + row) * p.nh + head) * S;
+        float m = -INFINITY, l = 0.f;
+        if (lane < S) {
+            m = p.part_ml[(at + lane) * 2];
+            l = p.part_ml[(at + lane) * 2 + 1];
+            if (!(l > 0.f)) { m = -INFINITY; l = 0.f; }
+        }
+        float top = m;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+        const float w = l > 0.f ? ex2(m - top) : 0.f;
+        float denom = l * w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = 0; i < S; ++i) {
+            const float wi = __shfl_sync(0xffffffffu, w, i);
+            if (wi > 0.f && lane < HD / 4) {
+                const float4 o = *reinterpret_cast<const float4*>(p.part_o + (at + i) * HD + 4 * lane);
+                acc.x = fmaf(wi, o.x, acc.x); acc.y = fmaf(wi, o.y, acc.y); acc.z = fmaf(wi, o.z, acc.z); acc.w = fmaf(wi, o.w, acc.w);
+            }
+        }
+        if (lane < HD / 4) {
+            const float inv = denom > 0.f ? 1.0f / denom : 0.f;
+            uint2 packed;
+            packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+            packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+            *reinterpret_cast<uint2*>(p.out + ((size_t)(tok0 + row) * p.nh + head) * HD + 4 * lane) = packed;
+        }
     }
 }
 
@@ -546,8 +641,12 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const TcParams& p, int
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    cudaError_t e = pyre_launch(attention_tc_kernel<HD>, dim3(p.nh, tiles_bound), dim3(THREADS), (size_t)L::TOTAL, stream, mq, mkv, p);
+    cudaError_t e = pyre_launch(attention_tc_kernel<HD>, dim3(p.nh, tiles_bound, p.key_splits), dim3(THREADS), (size_t)L::TOTAL, stream, mq, mkv, p);
     if (e != cudaSuccess) return (int)e;
+    if (p.key_splits > 1) {
+        e = pyre_launch(combine_shares_kernel<HD>, dim3(p.nh, tiles_bound), dim3(128), 0, stream, p);
+        if (e != cudaSuccess) return (int)e;
+    }
     return (int)cudaGetLastError();
 }
 
@@ -556,11 +655,13 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const TcParams& p, int
 // Attention of every entry with at least min_len tokens (other entries' rows are left untouched).
 // bfloat16, head sizes 64 and 128, pages of a power-of-two number of tokens (4 or more).  n_long_tokens: total
 // tokens of those entries (bounds the grid); n_tokens: rows of q; n_pages: pages of the cache layer.
+// key_splits > 1: that many CTAs share the key tiles of every (query tile, head) and a second kernel puts their
+// results together; part_o: fp32 [n_tokens, nh, key_splits, hd], part_ml: fp32 [n_tokens, nh, key_splits, 2].
 PYRE_API int pyre_attention_prefill_tc(const void* q, const void* cache, void* out, const int* block_table,
                                        int bt_stride, const int* cu_seqlens, const int* positions, int n_tokens,
                                        int n_long_tokens, int n_seqs, int nh, int nkv, int hd, int page_size,
-                                       long long n_pages, int window, float scale, int min_len, int* err_flag,
-                                       cudaStream_t stream) {
+                                       long long n_pages, int window, float scale, int min_len, int key_splits,
+                                       float* part_o, float* part_ml, int* err_flag, cudaStream_t stream) {
     if (n_long_tokens <= 0) return 0;
     if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || page_size < 4 || (page_size & (page_size - 1)) || min_len < 1)
         return PYRE_ERR_UNSUPPORTED;
@@ -575,6 +676,8 @@ PYRE_API int pyre_attention_prefill_tc(const void* q, const void* cache, void* o
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.box_rows = page_size < BN ? page_size : BN;
     p.window = window; p.min_len = min_len; p.scale = scale; p.err_flag = err_flag; p.n_pages = n_pages;
+    if (key_splits < 1 || key_splits > 32 || (key_splits > 1 && (!part_o || !part_ml || ((uintptr_t)part_o & 15)))) return PYRE_ERR_BAD_ARG;
+    p.key_splits = key_splits; p.part_o = part_o; p.part_ml = part_ml;
     CUtensorMap mq, mkv;
     memset(&mq, 0, sizeof(mq));
     memset(&mkv, 0, sizeof(mkv));

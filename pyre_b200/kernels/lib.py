@@ -41,7 +41,7 @@ SIGNATURES: dict[str, tuple[str, list]] = {
     "pyre_paged_attention_generic": ("attention_generic", [P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, LL, P, P]),
     "pyre_sgemm_nt": ("gemm_f32", [P, LL, P, LL, P, LL, P, I, I, I, P]),
     "pyre_paged_attention_mma": ("attention_mma", [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, I, LL, I, P, P]),
-    "pyre_attention_prefill_tc": ("attention_tc", [P, P, P, P, I, P, P, I, I, I, I, I, I, I, LL, I, F, I, P, P]),
+    "pyre_attention_prefill_tc": ("attention_tc", [P, P, P, P, I, P, P, I, I, I, I, I, I, I, LL, I, F, I, I, P, P, P, P]),
     "pyre_attention_prefill": ("attention_prefill", [P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, LL, P, P]),
 }
 

@@ -530,11 +530,33 @@ USE_TC_ATTENTION = True
 TC_ATTENTION_MIN_LEN = 64    # entries with at least this many tokens go to the tcgen05 kernel (128-query tiles)
 
 
+MAX_KEY_SPLITS = 8
+KEY_SPLIT_SCRATCH_BYTES = 256 << 20
+
+
+def prefill_key_splits(n_items: int, mean_tiles: float, n_tokens: int, n_heads: int, head_dim: int) -> int:
+    """Into how many shares of the keys the prompt attention cuts every (128-query tile, head).  Shares pay only
+    while SMs would stand idle: an SM runs the tiles of one CTA alone as fast as those of two together, so what
+    counts is that every SM has a CTA, and a share costs its partial output's trip through memory and a second
+    kernel (measured: 2,048 tokens after 8,192, 448 items, 292 us whole, 350 in two shares; 512 tokens after 30,720,
+    112 items, 492 us whole, 298 in two shares, 275 in five).  So: only with fewer items than SMs, as many shares as
+    fill two CTAs per SM, each of at least 16 key tiles (1,024 keys)."""
+    sms = sm_count()
+    if n_items >= sms:
+        return 1
+    s = min(MAX_KEY_SPLITS, 2 * sms // max(n_items, 1), int(mean_tiles // 16))
+    while s > 1 and n_tokens * n_heads * s * head_dim * 4 > KEY_SPLIT_SCRATCH_BYTES:
+        s -= 1
+    return max(1, s)
+
+
 def attention_prefill_tc(q: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor, cu_seqlens: torch.Tensor,
                          positions: torch.Tensor, n_seqs: int, n_long_tokens: int, n_heads: int, n_kv_heads: int,
-                         head_dim: int, scale: float, window: "int | None", out: torch.Tensor, min_len: int) -> torch.Tensor:
+                         head_dim: int, scale: float, window: "int | None", out: torch.Tensor, min_len: int,
+                         key_splits: int = 1) -> torch.Tensor:
     """bfloat16 attention of the entries with at least ``min_len`` tokens on the tcgen05 tensor
-    cores (scores and output in tensor memory, Q/K/V tiles by TMA); writes only those entries' rows."""
+    cores (scores and output in tensor memory, Q/K/V tiles by TMA); writes only those entries' rows.
+    ``key_splits`` > 1: that many CTAs share the keys of every (query tile, head); a second kernel combines them."""
     _check(q, "q", torch.bfloat16, 2)
     _check(cache_layer, "cache_layer", torch.bfloat16, 5)
     _check(block_table, "block_table", torch.int32, 2)
@@ -548,10 +570,17 @@ def attention_prefill_tc(q: torch.Tensor, cache_layer: torch.Tensor, block_table
         raise ValueError("q or the cache layer do not match the head sizes")
     if out.shape != q.shape or cu_seqlens.shape[0] != n_seqs + 1 or positions.shape[0] != q.shape[0]:
         raise ValueError("out, cu_seqlens and positions do not match the batch")
+    key_splits = int(key_splits)
+    if not 1 <= key_splits <= 32:
+        raise ValueError(f"key_splits must be 1 to 32, got {key_splits}")
+    part_o = part_ml = None
+    if key_splits > 1:
+        part_o = torch.empty((q.shape[0], n_heads, key_splits, head_dim), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((q.shape[0], n_heads, key_splits, 2), dtype=torch.float32, device=q.device)
     lib.call("pyre_attention_prefill_tc", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(), block_table.data_ptr(),
              block_table.stride(0), cu_seqlens.data_ptr(), positions.data_ptr(), q.shape[0], int(n_long_tokens), n_seqs,
              n_heads, n_kv_heads, head_dim, page_size, cache_layer.shape[0], int(window or 0), float(scale), int(min_len),
-             device_error_flag(q.device).data_ptr(), _stream())
+             key_splits, _ptr(part_o), _ptr(part_ml), device_error_flag(q.device).data_ptr(), _stream())
     return out
 
 
@@ -568,8 +597,17 @@ def paged_attention_bf16(ctx, q: torch.Tensor, cache_layer: torch.Tensor, block_
     n_short_seqs = int((~long_mask).sum())
     out = torch.empty_like(q)
     if n_long and use_tc:
+        long_lens, long_starts = lens[long_mask], ctx.start_pos_host[long_mask]
+        q_tiles = -(-long_lens // 128)
+        # key tiles of 64 that a query tile walks, averaged over the tiles: from position 0 (or the window's start)
+        # to the tile's last row
+        keys = long_starts + long_lens / 2.0 + 64.0
+        if window:
+            keys = keys.clip(max=window + 192.0)
+        mean_tiles = float((keys / 64.0 * q_tiles).sum() / q_tiles.sum())
+        key_splits = prefill_key_splits(int(q_tiles.sum()) * n_heads, mean_tiles, q.shape[0], n_heads, head_dim)
         attention_prefill_tc(q, cache_layer, block_table, ctx.cu_seqlens, ctx.positions, ctx.num_seqs, n_long, n_heads,
-                             n_kv_heads, head_dim, scale, window, out, min_len)
+                             n_kv_heads, head_dim, scale, window, out, min_len, key_splits)
     elif n_long:
         attention_prefill(q, cache_layer, block_table, ctx.cu_seqlens, ctx.positions, ctx.num_seqs, n_long, n_heads,
                           n_kv_heads, head_dim, scale, window, out)

@@ -222,8 +222,9 @@ def attention_prefill(q, cache_layer, block_table, cu_seqlens, positions, n_seqs
 
 
 def attention_prefill_tc(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_long_tokens, n_heads, n_kv_heads,
-                         head_dim, scale, window, out, min_len):
+                         head_dim, scale, window, out, min_len, key_splits=1):
     page_size = cache_layer.shape[3]
+    assert 1 <= key_splits <= 32
     assert page_size & (page_size - 1) == 0 and page_size >= 4, "the tcgen05 attention takes power-of-two pages"
     return attention_prefill(q, cache_layer, block_table, cu_seqlens, positions, n_seqs, n_long_tokens, n_heads, n_kv_heads,
                              head_dim, scale, window, out, min_len)

@@ -132,6 +132,22 @@ def test_long_portions_beside_decoded_tokens(big, dtype):
     check(got, want, dtype, plain["bf16_rms"], f"{raw['head_dim']} long mixed")
 
 
+def test_long_portions_with_their_keys_in_shares(big, monkeypatch):
+    """The same steps with the prompt attention forced to cut every (query tile, head) into three shares of its
+    keys (the planner asks for shares only after contexts of thousands of tokens, which these requests do not
+    reach): partial outputs, the combining kernel and empty shares inside whole model steps, beside the decode
+    kernel that writes the other rows of the same tensor."""
+    from pyre_b200.kernels import ops
+    d, raw, reqs, plain = big
+    calls = []
+    monkeypatch.setattr(ops, "prefill_key_splits", lambda *a: calls.append(a) or 3)
+    steps, many = long_mixed_trace(reqs)
+    got = H.run_trace_in_process(d, "bfloat16", steps, H.max_live_tokens(steps), 16)
+    assert calls, "no step reached the tcgen05 prompt attention"
+    want = {rid: plain["bfloat16"][rid.rstrip("2")] for rid in many}
+    check(got, want, "bfloat16", plain["bf16_rms"], f"{raw['head_dim']} long mixed in shares")
+
+
 @pytest.mark.parametrize("lookahead", [True, False])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_generation_returns_the_plain_logits(big, dtype, lookahead):

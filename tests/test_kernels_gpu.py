@@ -570,14 +570,16 @@ def test_attention_prefill_tc_long_portions(ops, nh, nkv, hd, page, window):
     cache, q = cache.to(torch.bfloat16), q.to(torch.bfloat16)
     scale = hd ** -0.5
     want = plain_attention_portions(q.float(), cache.float(), table, cu, starts, nh, nkv, hd, scale, window)
-    for rep in range(2):
+    # whole, and with the keys of every (query tile, head) shared by 2, 3 and 8 CTAs (some shares are empty, some hold
+    # only masked keys for their first rows): the second launch of each also shows that nothing is left behind
+    for key_splits in (1, 1, 2, 3, 8, 8):
         got = torch.full_like(q, 7.0)
-        ops.attention_prefill_tc(q, cache, table, cu, positions, B, T, nh, nkv, hd, scale, window, got, 64)
+        ops.attention_prefill_tc(q, cache, table, cu, positions, B, T, nh, nkv, hd, scale, window, got, 64, key_splits)
         ops.check_device_errors()
-        assert torch.isfinite(got).all()
+        assert torch.isfinite(got).all(), f"{key_splits} shares"
         err = (got.float() - want).abs()
         bad = (err > 1.2e-2 + 1.6e-2 * want.abs()).any(dim=1)
-        assert not bad.any(), f"first wrong token row {int(torch.where(bad)[0][0])} of {T}, max error {float(err.max()):.3e}"
+        assert not bad.any(), f"{key_splits} shares: first wrong token row {int(torch.where(bad)[0][0])} of {T}, max error {float(err.max()):.3e}"
         v_far = cache[pg, 1, 0, off].float()
         assert (got[row, :hd].float() - v_far).abs().max() < 0.25 * v_far.abs().max() + 0.1
 

@@ -93,3 +93,18 @@ def test_launch_keys_come_from_the_parts():
     holder = Holder(torch.float32, torch.device("cpu"))
     assert collect_launch_keys(holder, 4, 10) == {("halves", False)}
     assert collect_launch_keys(holder, 4, 5000) == {("halves", True)}
+
+
+def test_shares_of_the_keys_in_the_prompt_attention(monkeypatch):
+    """Shares of the keys only where SMs would stand idle: fewer (query tile, head) items than SMs, and then as many
+    as fill two CTAs per SM, each with at least 16 key tiles."""
+    from pyre_b200.kernels import ops
+    monkeypatch.setattr(ops, "sm_count", lambda: 148)
+    assert ops.prefill_key_splits(16 * 28, 17.0, 2048, 28, 128) == 1            # 2,048 fresh tokens
+    assert ops.prefill_key_splits(16 * 28, 144.0, 2048, 28, 128) == 1           # 2,048 after 8,192: every SM is busy
+    assert ops.prefill_key_splits(8 * 28, 136.0, 1024, 28, 128) == 1            # 224 items
+    assert ops.prefill_key_splits(4 * 28, 484.0, 512, 28, 128) == 2             # 512 after 30,720: 112 items
+    assert ops.prefill_key_splits(4 * 28, 5.0, 512, 28, 128) == 1               # 512 fresh tokens: nothing to share
+    assert ops.prefill_key_splits(1 * 28, 481.0, 128, 28, 128) == 8             # one query tile per head
+    assert ops.prefill_key_splits(1 * 28, 40.0, 128, 28, 128) == 2              # shares of at least 16 tiles
+    assert ops.prefill_key_splits(2 * 28, 484.0, 1 << 19, 28, 128) == 1         # the scratch would not fit
