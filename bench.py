@@ -579,7 +579,7 @@ def run_sweep(args) -> dict:
         for r in reqs:
             cache.end(r)
     prefill = []
-    for T, start in ((512, 0), (2048, 0), (4096, 0), (8192, 0), (2048, 8192), (2048, 30720)):
+    for T, start in ((512, 0), (2048, 0), (4096, 0), (8192, 0), (2048, 8192), (2048, 30720), (512, 30720), (128, 30720)):
         times = []
         for rep in range(4):
             r = ("p", T, start, rep)
