@@ -589,6 +589,81 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     continue;
                 }
             }
+            if constexpr (!X_CONTIGUOUS_OUT && FOLD) {
+                if (fix == 2) {
+                    // Row store with bias, rotary and the paged K/V write folded in (one split; the tile's columns are
+                    // whole heads): this thread's token row holds, per head, the pairs (d, d + hd / 2) that the half-split
+                    // rotation mixes.  q heads go to q_out, k and v heads to the token's slot of the cache; the
+                    // arithmetic is that of the rotary kernel (separate products and sum, one rounding to bf16).
+                    const bool live = alive && xr < p.x_rows;
+                    const int hd = p.hd, half = hd >> 1;
+                    int page = 0, off = 0;
+                    bool kv_ok = false;
+                    if (live && p.kv_cache && p.slot_mapping) {
+                        const int slot = pyre_checked_slot(p.slot_mapping[xr], p.n_pages, p.page_size, p.err_flag);
+                        if (slot >= 0) { page = slot / p.page_size; off = slot - page * p.page_size; kv_ok = true; }
+                    }
+                    const float* ct = p.cos_t + (size_t)(live ? xr : 0) * half;
+                    const float* st = p.sin_t + (size_t)(live ? xr : 0) * half;
+#pragma unroll 1
+                    for (int hc = 0; hc < BN && y0 + hc < p.y_rows; hc += hd) {
+                        const int gh = (y0 + hc) / hd;
+                        const bool is_v = gh >= p.nh + p.nkv, is_k = !is_v && gh >= p.nh;
+                        __nv_bfloat16* dst = nullptr;
+                        if (live) {
+                            if (!is_k && !is_v) dst = (__nv_bfloat16*)p.q_out + ((size_t)xr * p.nh + gh) * hd;
+                            else if (kv_ok) dst = (__nv_bfloat16*)p.kv_cache +
+                                (((size_t)(page * 2 + (is_v ? 1 : 0)) * p.nkv + (is_k ? gh - p.nh : gh - p.nh - p.nkv)) * p.page_size + off) * hd;
+                        }
+                        const bool rotate = !is_v && p.rot != 0;
+#pragma unroll 1
+                        for (int c = 0; c < half; c += 16) {
+                            uint32_t lo[16], hi[16];
+                            __syncwarp();
+                            tmem_ld16(acc + hc + c, lo);
+                            tmem_ld16(acc + hc + half + c, hi);
+                            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                            if (dst == nullptr) continue;
+                            uint32_t w1[8], w2[8];
+#pragma unroll
+                            for (int q4 = 0; q4 < 4; ++q4) {
+                                float4 b1 = make_float4(0.f, 0.f, 0.f, 0.f), b2 = b1, c4 = b1, s4 = b1;
+                                if (p.bias) {
+                                    b1 = *reinterpret_cast<const float4*>(p.bias + y0 + hc + c + 4 * q4);
+                                    b2 = *reinterpret_cast<const float4*>(p.bias + y0 + hc + half + c + 4 * q4);
+                                }
+                                if (rotate) {
+                                    c4 = *reinterpret_cast<const float4*>(ct + c + 4 * q4);
+                                    s4 = *reinterpret_cast<const float4*>(st + c + 4 * q4);
+                                }
+                                const float bb1[4] = {b1.x, b1.y, b1.z, b1.w}, bb2[4] = {b2.x, b2.y, b2.z, b2.w};
+                                const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+                                float o1[4], o2[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const float a1 = __fadd_rn(__fmul_rn(__uint_as_float(lo[4 * q4 + e]), row_scale), bb1[e]);
+                                    const float a2 = __fadd_rn(__fmul_rn(__uint_as_float(hi[4 * q4 + e]), row_scale), bb2[e]);
+                                    o1[e] = rotate ? __fadd_rn(__fmul_rn(a1, cc[e]), __fmul_rn(-a2, ss[e])) : a1;
+                                    o2[e] = rotate ? __fadd_rn(__fmul_rn(a2, cc[e]), __fmul_rn(a1, ss[e])) : a2;
+                                }
+                                __nv_bfloat162 v;
+                                v = __floats2bfloat162_rn(o1[0], o1[1]); w1[2 * q4] = *reinterpret_cast<uint32_t*>(&v);
+                                v = __floats2bfloat162_rn(o1[2], o1[3]); w1[2 * q4 + 1] = *reinterpret_cast<uint32_t*>(&v);
+                                v = __floats2bfloat162_rn(o2[0], o2[1]); w2[2 * q4] = *reinterpret_cast<uint32_t*>(&v);
+                                v = __floats2bfloat162_rn(o2[2], o2[3]); w2[2 * q4 + 1] = *reinterpret_cast<uint32_t*>(&v);
+                            }
+                            uint4* d1 = reinterpret_cast<uint4*>(dst + c);
+                            uint4* d2 = reinterpret_cast<uint4*>(dst + half + c);
+                            d1[0] = make_uint4(w1[0], w1[1], w1[2], w1[3]); d1[1] = make_uint4(w1[4], w1[5], w1[6], w1[7]);
+                            d2[0] = make_uint4(w2[0], w2[1], w2[2], w2[3]); d2[1] = make_uint4(w2[4], w2[5], w2[6], w2[7]);
+                        }
+                    }
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) hand_back(buf);
+                    continue;
+                }
+            }
             int c_begin = 0;
             if constexpr (!X_CONTIGUOUS_OUT && GW > 0) {
                 if (!p.out_f32 && n_kb > 0) {
@@ -938,7 +1013,16 @@ static int gemm_tc_impl(const void* X, int x_rows, long long ldx, const void* Y,
         // row store (tokens on the rows): every thread of the epilogue owns a token row, so the row scale and the
         // residual fold (fix == 1) need no exchange between CTAs; one split, no gate with the fold, bf16 out
         if (fx->scale_ssq && fx->scale_tiles < 1) return PYRE_ERR_BAD_ARG;
-        if (fx->fix != 0 && (fx->fix != 1 || splits != 1 || gated || out_f32 || !fx->resid || !fx->norm_w || !fx->ssq_out)) return PYRE_ERR_BAD_ARG;
+        if (fx->fix == 1 && (splits != 1 || gated || out_f32 || !fx->resid || !fx->norm_w || !fx->ssq_out)) return PYRE_ERR_BAD_ARG;
+        if (fx->fix == 2) {
+            // bias + rotary + cache write in the epilogue: whole heads per tile, pairs in chunks of 16
+            if (splits != 1 || gated || out_f32) return PYRE_ERR_BAD_ARG;
+            if (fx->hd <= 0 || fx->hd % 32 || bn % fx->hd || (fx->rot != 0 && fx->rot != fx->hd) || !fx->q_out ||
+                y_rows != (fx->nh + 2 * fx->nkv) * fx->hd || fx->page_size <= 0 || (fx->kv_cache && !fx->slot_mapping) ||
+                (fx->rot && (!fx->cos_t || !fx->sin_t)))
+                return PYRE_ERR_UNSUPPORTED;
+        }
+        if (fx->fix != 0 && fx->fix != 1 && fx->fix != 2) return PYRE_ERR_BAD_ARG;
     } else if (fx && (fx->fix != 0 || fx->scale_ssq != nullptr)) {
         if (stride_x != 1 || bn > 128 || y_rows > bn || pair) return PYRE_ERR_BAD_ARG;      // transposed store, one tile of tokens
         if (fx->scale_ssq && fx->scale_tiles < 1) return PYRE_ERR_BAD_ARG;

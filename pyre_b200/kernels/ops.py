@@ -258,8 +258,9 @@ def qkv_rope_write(qkv: torch.Tensor, bias: "torch.Tensor | None", cos: torch.Te
     store nothing (a layer that reads another layer's cache)."""
     if isinstance(qkv, DeferredProduct):
         width = (n_heads + 2 * n_kv_heads) * head_dim
-        if q_out is None and qkv.shape[0] <= 128 and qkv.shape[1] == width and 128 % head_dim == 0 and head_dim % 8 == 0 \
-                and rotary_dim in (0, head_dim) and width <= 128 * _MAX_FIX_TILES:
+        few = qkv.shape[0] <= 128 and 128 % head_dim == 0 and head_dim % 8 == 0 and width <= 128 * _MAX_FIX_TILES
+        many = qkv.shape[0] > 128 and folds_rope(qkv.shape[0], width, qkv.x.shape[1], head_dim)
+        if q_out is None and qkv.shape[1] == width and rotary_dim in (0, head_dim) and (few or many):
             return gemm_rope_write(qkv, bias, cos, sin, cache_layer, slot_mapping, n_heads, n_kv_heads, head_dim,
                                    rotary_dim, page_size)
         qkv = qkv.partials()
@@ -852,7 +853,8 @@ def gemm_tc(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: torch.dt
     return materialize(PartialSums(target, out_dtype))
 
 
-def _launch_with_fixup(prod: DeferredProduct, fx: "lib.GemmFix", rows_out: "torch.Tensor | None" = None) -> None:
+def _launch_with_fixup(prod: DeferredProduct, fx: "lib.GemmFix", rows_out: "torch.Tensor | None" = None,
+                       row_plan: "tuple[bool, int, int] | None" = None) -> None:
     """The product of a ``DeferredProduct`` with work folded in.  Few tokens (weights on the MMA's rows, all tokens
     in one tile, K split as the plan says): fp32 partial sums that only the kernel's own fix-up reads.  Many tokens
     (tokens on the rows, one split): the epilogue itself folds, and what it stores is ``rows_out``."""
@@ -863,7 +865,7 @@ def _launch_with_fixup(prod: DeferredProduct, fx: "lib.GemmFix", rows_out: "torc
     w = prod.w
     M, K = x.shape
     N = w.shape[0]
-    weights_as_rows, bn, splits = tc_gemm_plan(M, N, K)
+    weights_as_rows, bn, splits = row_plan or tc_gemm_plan(M, N, K)
     if M <= 128 and not weights_as_rows:
         # the fix-up lives in the orientation with the weights on the rows; the same tiles and splits serve it
         weights_as_rows, bn = True, 128
@@ -891,6 +893,28 @@ def folds_residual(M: int, N: int, K: int) -> bool:
     if M <= FOLD_MAX_TOKENS:
         return True
     if M <= 128:
+        return False
+    weights_as_rows, _bn, splits = tc_gemm_plan(M, N, K)
+    return not weights_as_rows and splits == 1
+
+
+def rope_fold_width(N: int, head_dim: int) -> int:
+    """The tile width with which a q/k/v product of many tokens carries bias, rotary and the cache write in its
+    epilogue (tiles of whole heads), or 0."""
+    for bn in (256, 128):
+        if N % bn == 0 and bn % head_dim == 0 and head_dim % 32 == 0:
+            return bn
+    return 0
+
+
+def folds_rope(M: int, N: int, K: int, head_dim: int) -> bool:
+    """Does the stacked q/k/v product of this shape take bias, rotary and the paged write as folded work?  Very few
+    tokens (the fix-up of the last CTA per tile), or a prompt portion whose plan is one split of the row store."""
+    if not FOLD_SMALL_KERNELS or N % 8:
+        return False
+    if M <= FOLD_MAX_TOKENS:
+        return True
+    if M <= 128 or not rope_fold_width(N, head_dim):
         return False
     weights_as_rows, _bn, splits = tc_gemm_plan(M, N, K)
     return not weights_as_rows and splits == 1
@@ -943,7 +967,11 @@ def gemm_rope_write(prod: DeferredProduct, bias, cos, sin, cache_layer, slot_map
         if slot_mapping.shape[0] != T:
             raise ValueError("slot_mapping must have one entry per token")
         fx.kv_cache, fx.slot_mapping, fx.n_pages = cache_layer.data_ptr(), slot_mapping.data_ptr(), cache_layer.shape[0]
-    _launch_with_fixup(prod, fx)
+    if T > 128:
+        # tokens on the rows: the epilogue thread that owns a token row rotates and stores whole heads
+        _launch_with_fixup(prod, fx, q_out, (False, rope_fold_width(prod.shape[1], head_dim), 1))
+    else:
+        _launch_with_fixup(prod, fx)
     return q_out
 
 
@@ -960,7 +988,7 @@ FOLD_MAX_TOKENS = 4
 
 
 def linear(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: "torch.dtype | None" = None, partials_ok: bool = False,
-           deferred_ok: "bool | str" = False):
+           deferred_ok: "bool | str | tuple" = False):
     """y = x W^T for a weight in the linear-layer layout [out, in].
 
     float32: the package's own fp32 kernel (no reduced-precision matrix mode).
@@ -972,7 +1000,9 @@ def linear(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: "torch.dt
     consumer is one of the kernels that take a ``DeferredProduct`` (the built-in norm, ``qkv_rope_write``) or
     calls ``materialize``; for very few tokens (``FOLD_MAX_TOKENS``) the product is then not launched here.
     ``deferred_ok="residual"`` says that the consumer is the norm (the product is a branch output): then a product
-    of many tokens in one split is deferred too, since its epilogue can fold the residual add (``folds_residual``)."""
+    of many tokens in one split is deferred too, since its epilogue can fold the residual add (``folds_residual``).
+    ``deferred_ok=("rope", head_dim)``: the consumer is a position encoding that may fold bias, rotation and the cache
+    write into the stacked q/k/v product (``folds_rope``)."""
     if x.dtype == torch.float32:
         return sgemm_nt(x, w)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
@@ -981,7 +1011,8 @@ def linear(x: "torch.Tensor | ScaledRows", w: torch.Tensor, out_dtype: "torch.dt
     if USE_TC_GEMM and tc_gemm_supported(rows, w):
         if deferred_ok and FOLD_SMALL_KERNELS and out_dtype in (None, torch.bfloat16) and w.shape[0] % 4 == 0:
             M = rows.shape[0]
-            if M <= FOLD_MAX_TOKENS or (deferred_ok == "residual" and folds_residual(M, w.shape[0], w.shape[1])):
+            if M <= FOLD_MAX_TOKENS or (deferred_ok == "residual" and folds_residual(M, w.shape[0], w.shape[1])) or \
+                    (isinstance(deferred_ok, tuple) and deferred_ok[0] == "rope" and folds_rope(M, w.shape[0], w.shape[1], deferred_ok[1])):
                 return DeferredProduct(x, w, torch.bfloat16)
         return gemm_tc(x, w, out_dtype or torch.bfloat16, reduce=not partials_ok, checked=True)
     x = materialize(x)

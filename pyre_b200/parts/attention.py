@@ -98,7 +98,7 @@ class Attention(Part):
         kv = ctx.kv_group(call.kv_group)
         layer = kv.pool[call.kv_layer]
         with lib.section("qkv"):
-            qkv = ops.linear(h, self.w_qkv, partials_ok=True, deferred_ok=True)
+            qkv = ops.linear(h, self.w_qkv, partials_ok=True, deferred_ok=("rope", self.head_dim))
         # the position encoding owns the step from projections to cache: bias, its transformation of q and k,
         # the paged write of k and v; the queries come back
         q = self.position.apply(ctx, qkv, self.b_qkv, self.heads, kv, layer if call.kv_write else None)

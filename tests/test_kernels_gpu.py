@@ -828,6 +828,51 @@ def test_product_with_rotary_and_cache_write_folded_in(ops, nh, nkv, hd, rot, pa
     assert torch.equal(q_only, qs[0])
 
 
+@pytest.mark.parametrize("nh,nkv,hd,rot,page", [(28, 4, 128, 128, 16), (14, 2, 64, 64, 16), (6, 3, 64, 0, 32), (3, 1, 32, 32, 8),
+                                                (7, 1, 128, 128, 64), (5, 2, 48, 48, 16)])
+@pytest.mark.parametrize("T", [129, 300, 2048])
+def test_rotary_and_cache_write_in_the_epilogue_of_a_prompt_portion(ops, nh, nkv, hd, rot, page, T):
+    """More than 128 tokens: the stacked q/k/v product has the tokens on the MMA's rows, and where its tiles hold whole
+    heads the epilogue thread that owns a token row adds the bias, rotates and stores queries, keys and values itself
+    (no rotary kernel, no q/k/v matrix in memory).  Against the formula in fp64; the folded result rounds once and is
+    at least as close as the separate kernel's; shapes whose heads do not fill tiles take the separate kernel."""
+    g = torch.Generator(device="cuda").manual_seed(nh * 17 + T)
+    K = 264
+    width = (nh + 2 * nkv) * hd
+    a = torch.randn(T, K, device="cuda", generator=g).to(torch.bfloat16)
+    w = (torch.randn(width, K, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+    bias = torch.randn(width, device="cuda", generator=g)
+    pos = torch.randint(0, 5000, (T,), device="cuda", generator=g, dtype=torch.int32)
+    inv = 1.0 / (1e4 ** (torch.arange(0, max(rot, 2), 2, device="cuda", dtype=torch.float32) / max(rot, 2)))
+    cos, sin = ops.rope_table(pos, inv) if rot else (None, None)
+    n_pages = -(-T // page) + 3
+    slots = torch.randperm(n_pages * page, device="cuda", generator=g)[:T].to(torch.int32).contiguous()
+    y = (a.double() @ w.double().t() + bias.double()).view(T, nh + 2 * nkv, hd)
+    if rot:
+        c, s_ = cos.double()[:, None, :], sin.double()[:, None, :]
+        y1, y2 = y[:, :nh + nkv, :hd // 2], y[:, :nh + nkv, hd // 2:]
+        y = torch.cat([torch.cat([y1 * c - y2 * s_, y2 * c + y1 * s_], dim=-1), y[:, nh + nkv:]], dim=1)
+    want_q = y[:, :nh].reshape(T, nh * hd)
+    want_k, want_v = y[:, nh:nh + nkv], y[:, nh + nkv:]
+    assert ops.folds_rope(T, width, K, hd) == (ops.rope_fold_width(width, hd) > 0)
+    errs = []
+    for fold in (True, False):
+        cache = torch.full((n_pages, 2, nkv, page, hd), 9.0, device="cuda", dtype=torch.bfloat16)
+        prod = ops.DeferredProduct(a, w, torch.bfloat16)
+        q = ops.qkv_rope_write(prod if fold else prod.partials(), bias, cos, sin, cache, slots, nh, nkv, hd, rot, page)
+        ops.check_device_errors()
+        pg, off = (slots // page).long(), (slots % page).long()
+        got_k, got_v = cache[pg, 0, :, off], cache[pg, 1, :, off]             # [T, nkv, hd]
+        scale = float(y.abs().max())
+        for got, want in ((q, want_q), (got_k, want_k), (got_v, want_v)):
+            assert float((got.double() - want).abs().max()) <= 1.2e-2 * scale
+        errs.append(float((q.double() - want_q).abs().mean() + (got_k.double() - want_k).abs().mean()))
+        untouched = torch.ones(n_pages * page, dtype=torch.bool, device="cuda")
+        untouched[slots.long()] = False
+        assert bool((cache.permute(0, 3, 1, 2, 4).reshape(n_pages * page, -1)[untouched] == 9.0).all()), "a slot of no token was written"
+    assert errs[0] <= errs[1] * 1.02, f"folded {errs[0]:.3e} against separate {errs[1]:.3e}"
+
+
 @pytest.mark.parametrize("kernel,dtype,nh,nkv,hd,page,window", [
     ("generic", torch.float32, 6, 3, 48, 4, 37), ("generic", torch.bfloat16, 3, 1, 32, 8, 19), ("generic", torch.float32, 4, 2, 16, 16, 64),
     ("mma", torch.bfloat16, 6, 3, 48, 4, 37), ("mma", torch.bfloat16, 7, 1, 128, 8, 50), ("mma", torch.bfloat16, 28, 4, 128, 16, 64),
