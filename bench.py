@@ -157,7 +157,9 @@ def class_work(cfg: dict, layers: int, T: int, B: int, context_before: int, logi
         # per launch: how many norm kernels run depends on the step (products of very few or of many tokens fold them in)
         "norm": {"bytes": T * H * (4 + 2 + 4 + 2) + H * 4, "flops": 0, "per_launch": True},
         "qkv": {"bytes": layers * ((q + 2 * kv) * H * 2 + T * (H + q + 2 * kv) * 2), "flops": 2.0 * layers * T * H * (q + 2 * kv)},
-        "rotary+write": {"bytes": layers * T * (q + 2 * kv) * 2 * 2, "flops": 0},
+        # per launch too: the step's one table of angles, then a kernel per layer unless the q/k/v product carries the
+        # rotation in its epilogue (very few tokens, or a prompt portion)
+        "rotary+write": {"bytes": T * (q + 2 * kv) * 2 * 2, "flops": 0, "per_launch": True, "first_launch_bytes": T * (hd * 4 + 4)},
         "attention": {"bytes": layers * (cached * 2 * kv * 2 + 2 * T * q * 2), "flops": 4.0 * layers * nh * hd * keys},
         "o": {"bytes": layers * (H * q * 2 + T * (q + H) * 2), "flops": 2.0 * layers * T * q * H},
         "gate_up": {"bytes": layers * (2 * I * H * 2 + T * (H + I) * 2), "flops": 4.0 * layers * T * H * I},
@@ -178,7 +180,9 @@ def kernel_table(totals: dict, work: dict, step_us: float, peaks: dict) -> dict:
         row = {"us": round(t["us"], 1), "launches": t["launches"]}
         if w is not None and t["us"] > 0:
             if w.get("per_launch"):
-                w = {"bytes": w["bytes"] * t["launches"], "flops": w["flops"] * t["launches"]}
+                first = w.get("first_launch_bytes")
+                n = t["launches"] if first is None else t["launches"] - 1
+                w = {"bytes": w["bytes"] * n + (first or 0), "flops": w["flops"] * t["launches"]}
             # both yardsticks; the class is judged by the one that binds it (the larger fraction)
             gbs = w["bytes"] / (t["us"] * 1e-6) / 1e9
             tf = w["flops"] / (t["us"] * 1e-6) / 1e12
