@@ -166,7 +166,10 @@ struct GemmParams {
     int gated;                    // 1: the weight rows are gate/up rows interleaved in blocks of 64 (gate rows, then the up
                                   // rows of the same features); the epilogue writes silu(gate) * up, half as many features
     int* err_flag;
-    // ---- transposed store only (few tokens): work folded into the product so that no small kernel runs around it
+    // ---- work folded into the product so that no small kernel runs around it.  With the transposed store (few
+    // tokens, the weights on the MMA's rows) as described below; with the row store (many tokens in one split, an
+    // epilogue thread owns a token row) the same three without a fix-up: (a) the thread scales its own row, fix == 1
+    // and fix == 2 happen in the epilogue itself (resid, bias, tables and outputs are then indexed [x_rows, y_rows]).
     // (a) rows scaled: out[token] *= 1 / sqrt(sum_i scale_ssq[i][token] / scale_n + scale_eps), the 1/rms of an
     //     RMSNorm whose weight the producer of the activations has already applied (see fix == 1)
     const float* scale_ssq;       // [scale_tiles][y_rows] partial sums of squares per token, or null
