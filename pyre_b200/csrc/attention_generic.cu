@@ -83,15 +83,50 @@ __global__ void paged_attention_generic_kernel(
 #pragma unroll
         for (int i = 0; i < 8; ++i) part[i] = 0.f;
         const int n_keys = min(32, pos - c + 1);
-        for (int jj = 0; jj < n_keys; ++jj) {
-            const float pj = __shfl_sync(0xffffffffu, p, jj);
-            const int vr = __shfl_sync(0xffffffffu, vrow, jj);
-            if (vr < 0) continue;  // before the window: same for the whole warp
-            const T* vp = cache + (size_t)vr * hd;
+        if constexpr (sizeof(T) == 4) {
+            // float32 storage: four keys at a time.  Their value rows are fetched together (one key after the other,
+            // the loads were a chain of memory latencies: 2.5 times the time of a decode step's launch), then added
+            // in the order of the keys, as below: the same sums, bit for bit.  (With 2-byte values the wider loop is
+            // slower; they keep the plain one.)
+            for (int j0 = 0; j0 < n_keys; j0 += 4) {
+                float pj[4];
+                int vr[4];
+                float val[4][8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int d = lane + 32 * i;
-                if (i < n_own && d < hd) part[i] = fmaf(pj, to_f32<T>(vp[d]), part[i]);
+                for (int u = 0; u < 4; ++u) {
+                    pj[u] = __shfl_sync(0xffffffffu, p, (j0 + u) & 31);
+                    vr[u] = (j0 + u < n_keys) ? __shfl_sync(0xffffffffu, vrow, (j0 + u) & 31) : -1;   // -1: before the window, or past the chunk's keys
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const T* vp = cache + (size_t)(vr[u] < 0 ? 0 : vr[u]) * hd;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int d = lane + 32 * i;
+                        val[u][i] = (vr[u] >= 0 && i < n_own && d < hd) ? to_f32<T>(vp[d]) : 0.f;
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (vr[u] < 0) continue;  // the same for the whole warp
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int d = lane + 32 * i;
+                        if (i < n_own && d < hd) part[i] = fmaf(pj[u], val[u][i], part[i]);
+                    }
+                }
+            }
+        } else {
+            for (int jj = 0; jj < n_keys; ++jj) {
+                const float pj = __shfl_sync(0xffffffffu, p, jj);
+                const int vr = __shfl_sync(0xffffffffu, vrow, jj);
+                if (vr < 0) continue;  // before the window: same for the whole warp
+                const T* vp = cache + (size_t)vr * hd;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int d = lane + 32 * i;
+                    if (i < n_own && d < hd) part[i] = fmaf(pj, to_f32<T>(vp[d]), part[i]);
+                }
             }
         }
 #pragma unroll
