@@ -532,7 +532,7 @@ TC_ATTENTION_MIN_LEN = 64    # entries with at least this many tokens go to the 
 
 
 MAX_KEY_SPLITS = 8
-KEY_SPLIT_SCRATCH_BYTES = 256 << 20
+KEY_SPLIT_SCRATCH_BYTES = 128 << 20      # of partial outputs per launch (fewer items than SMs keep it below this anyway)
 
 
 def prefill_key_splits(n_items: int, mean_tiles: float, n_tokens: int, n_heads: int, head_dim: int) -> int:

@@ -107,4 +107,4 @@ def test_shares_of_the_keys_in_the_prompt_attention(monkeypatch):
     assert ops.prefill_key_splits(4 * 28, 5.0, 512, 28, 128) == 1               # 512 fresh tokens: nothing to share
     assert ops.prefill_key_splits(1 * 28, 481.0, 128, 28, 128) == 8             # one query tile per head
     assert ops.prefill_key_splits(1 * 28, 40.0, 128, 28, 128) == 2              # shares of at least 16 tiles
-    assert ops.prefill_key_splits(2 * 28, 484.0, 1 << 19, 28, 128) == 1         # the scratch would not fit
+    assert ops.prefill_key_splits(2 * 28, 484.0, 1 << 18, 28, 128) == 1         # the scratch would not fit
