@@ -668,8 +668,88 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 }
             }
             int c_begin = 0;
+            [[maybe_unused]] bool folded_in_lines = false;
+            if constexpr (!X_CONTIGUOUS_OUT && FOLD && GW == 64) {
+                if (fix == 1 && scale_ssq == nullptr && n_kb > 0) {
+                    // The residual fold in whole lines.  A thread that owns a token row would touch 32 different
+                    // 128-byte lines of the fp32 stream per instruction with its warp (rows lie kilobytes apart), so
+                    // the accumulator values of 32 columns go through shared memory (the bf16 staging area: 32 rows of
+                    // 128 bytes per warp) and the warp works on four rows per instruction, eight lanes per row of
+                    // 128 bytes: residual read, sum written back, sum of squares, activations (sum x norm weight) as
+                    // bf16.  The residual values of the next 32 columns are fetched while these are worked on.
+                    constexpr int UW = 32;
+                    const int units = min(BN, p.y_rows - y0) / UW;
+                    const int rsub = lane >> 3, piece = lane & 7;
+                    const int row0 = x0 + quarter * 32;
+                    float part[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) part[i] = 0.f;
+                    float4 cur[8], nxt[8];
+                    auto fetch = [&](int u, float4 (&dst)[8]) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int grow = row0 + i * 4 + rsub;
+                            dst[i] = (alive && grow < p.x_rows)
+                                ? *reinterpret_cast<const float4*>(p.resid + (size_t)grow * p.y_rows + y0 + u * UW + piece * 4)
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+                        }
+                    };
+                    if (units > 0) fetch(0, cur);
+#pragma unroll 1
+                    for (int u = 0; u < units; ++u) {
+                        if (u + 1 < units) fetch(u + 1, nxt);
+                        uint32_t r0[16], r1[16];
+                        __syncwarp();     // every lane has read the staging area of the unit before
+                        tmem_ld16(acc + u * UW, r0);
+                        tmem_ld16(acc + u * UW + 16, r1);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(out_stage + lane * L::OUT_PITCH + q * 16),
+                                         "r"(r0[4 * q]), "r"(r0[4 * q + 1]), "r"(r0[4 * q + 2]), "r"(r0[4 * q + 3]) : "memory");
+                            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(out_stage + lane * L::OUT_PITCH + 64 + q * 16),
+                                         "r"(r1[4 * q]), "r"(r1[4 * q + 1]), "r"(r1[4 * q + 2]), "r"(r1[4 * q + 3]) : "memory");
+                        }
+                        __syncwarp();
+                        const int col = y0 + u * UW + piece * 4;
+                        const float4 w4 = *reinterpret_cast<const float4*>(p.norm_w + col);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int rr = i * 4 + rsub, grow = row0 + rr;
+                            uint32_t a0, a1, a2, a3;
+                            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3)
+                                         : "r"(out_stage + rr * L::OUT_PITCH + piece * 16) : "memory");
+                            if (alive && grow < p.x_rows) {
+                                float4 v = cur[i];
+                                v.x += __uint_as_float(a0); v.y += __uint_as_float(a1);
+                                v.z += __uint_as_float(a2); v.w += __uint_as_float(a3);
+                                *reinterpret_cast<float4*>(p.resid + (size_t)grow * p.y_rows + col) = v;
+                                part[i] = fmaf(v.w, v.w, fmaf(v.z, v.z, fmaf(v.y, v.y, fmaf(v.x, v.x, part[i]))));
+                                __nv_bfloat162 lo = __floats2bfloat162_rn(__fmul_rn(v.x, w4.x), __fmul_rn(v.y, w4.y));
+                                __nv_bfloat162 hi = __floats2bfloat162_rn(__fmul_rn(v.z, w4.z), __fmul_rn(v.w, w4.w));
+                                *reinterpret_cast<uint2*>((__nv_bfloat16*)p.out + (long long)grow * p.stride_x + col) =
+                                    make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
+                    }
+                    // a row's sum of squares: over its eight lanes, then to the thread that owns the row
+                    // (row i * 4 + rsub sits in lanes 8 rsub .. 8 rsub + 7; the owner of row r is lane r)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        part[i] += __shfl_xor_sync(0xffffffffu, part[i], 1);
+                        part[i] += __shfl_xor_sync(0xffffffffu, part[i], 2);
+                        part[i] += __shfl_xor_sync(0xffffffffu, part[i], 4);
+                        const float mine = __shfl_sync(0xffffffffu, part[i], 8 * (lane & 3));
+                        if ((lane >> 2) == i) row_ssq = mine;
+                    }
+                    c_begin = units * UW;
+                    folded_in_lines = true;
+                }
+            }
             if constexpr (!X_CONTIGUOUS_OUT && GW > 0) {
-                if (!p.out_f32 && n_kb > 0) {
+                if (!folded_in_lines && !p.out_f32 && n_kb > 0) {
                     const int whole = min(BN, p.y_rows - y0) / GW;      // groups of GW columns inside the matrix
 #pragma unroll 1
                     for (int gq = 0; gq < whole; ++gq) {
