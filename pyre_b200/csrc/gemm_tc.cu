@@ -229,7 +229,7 @@ struct SmemLayout {
 // loads; the MMA commits arrive on the "empty" and "accumulator full" barriers of both; the epilogue warps of
 // both arrive on the first CTA's "accumulator empty" barriers.
 template <int BN, int STAGES, bool X_CONTIGUOUS_OUT, int CTAS = 1, bool FOLD = true>
-__global__ void __launch_bounds__(THREADS, (X_CONTIGUOUS_OUT && FOLD) ? 5 : 1)
+__global__ void __launch_bounds__(THREADS, (X_CONTIGUOUS_OUT && FOLD) ? 5 : (!X_CONTIGUOUS_OUT && !FOLD) ? 3 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const GemmParams p) {
     static_assert(CTAS == 1 || (CTAS == 2 && !X_CONTIGUOUS_OUT && BN % 16 == 0), "pairs serve the row store");
     using L = SmemLayout<BN, STAGES, X_CONTIGUOUS_OUT, CTAS>;
@@ -748,6 +748,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     folded_in_lines = true;
                 }
             }
+            if constexpr (!X_CONTIGUOUS_OUT && GW == 64) {
+                if (p.out_f32 && n_kb > 0 && fix == 0) {
+                    // fp32 partial sums of a split K, in whole lines as well: 32 columns of the warp's 32 rows go
+                    // through the staging area and leave as 128 bytes per row, four rows per instruction (a thread
+                    // storing 16 bytes of its own row makes its warp touch 32 lines per instruction, and with one
+                    // tile per CTA nothing hides this epilogue)
+                    const int units = min(BN, p.y_rows - y0) / 32;
+                    const int rsub = lane >> 3, piece = lane & 7;
+                    const int row0 = x0 + quarter * 32;
+#pragma unroll 1
+                    for (int u = 0; u < units; ++u) {
+                        uint32_t r0[16], r1[16];
+                        __syncwarp();     // every lane has read the staging area of the unit before
+                        tmem_ld16(acc + u * 32, r0);
+                        tmem_ld16(acc + u * 32 + 16, r1);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (scale_ssq != nullptr) {
+#pragma unroll
+                            for (int q = 0; q < 16; ++q) {
+                                r0[q] = __float_as_uint(__uint_as_float(r0[q]) * row_scale);
+                                r1[q] = __float_as_uint(__uint_as_float(r1[q]) * row_scale);
+                            }
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(out_stage + lane * L::OUT_PITCH + q * 16),
+                                         "r"(r0[4 * q]), "r"(r0[4 * q + 1]), "r"(r0[4 * q + 2]), "r"(r0[4 * q + 3]) : "memory");
+                            asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(out_stage + lane * L::OUT_PITCH + 64 + q * 16),
+                                         "r"(r1[4 * q]), "r"(r1[4 * q + 1]), "r"(r1[4 * q + 2]), "r"(r1[4 * q + 3]) : "memory");
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int rr = i * 4 + rsub, grow = row0 + rr;
+                            uint32_t a0, a1, a2, a3;
+                            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3)
+                                         : "r"(out_stage + rr * L::OUT_PITCH + piece * 16) : "memory");
+                            if (alive && grow < p.x_rows)
+                                *reinterpret_cast<uint4*>((float*)p.out + (long long)blockIdx.z * p.split_stride +
+                                                          (long long)grow * p.stride_x + y0 + u * 32 + piece * 4) = make_uint4(a0, a1, a2, a3);
+                        }
+                    }
+                    c_begin = units * 32;
+                }
+            }
             if constexpr (!X_CONTIGUOUS_OUT && GW > 0) {
                 if (!folded_in_lines && !p.out_f32 && n_kb > 0) {
                     const int whole = min(BN, p.y_rows - y0) / GW;      // groups of GW columns inside the matrix
@@ -1185,7 +1230,7 @@ static int gemm_tc_impl(const void* X, int x_rows, long long ldx, const void* Y,
     }
     dim3 grid((unsigned)ctas, 1, splits);
     // the plain products run the variant without that code: the weight stream always, the row store at the one width
-    // that decode steps of 65-128 tokens use (106 registers instead of 183: the attention's CTAs fit beside it)
+    // that decode steps of 33-128 tokens use (96 registers, held there by its launch bounds, instead of 183: two of the attention's CTAs fit beside it)
     const bool fold = p.fix != 0 || p.scale_ssq != nullptr;
 #define GO(BN_, ST_)                                                              \
     rc = !xc ? launch_rows<BN_, ST_>(mx, my, p, grid, stream, fold)                               \

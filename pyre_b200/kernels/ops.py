@@ -708,12 +708,13 @@ def tc_gemm_plan(M: int, N: int, K: int) -> tuple[bool, int, int]:
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
         tiles = -(-N // 128) * -(-M // bn)
         splits = max(1, min(_SM_COUNT // tiles if tiles < _SM_COUNT else 1, kb // 4, 16))
-        # 65 to 128 tokens and few tiles (a split K): one 128-row tile of tokens against 128 weight rows per CTA, the
+        # 33 to 128 tokens and few tiles (a split K): one 128-row tile of tokens against 128 weight rows per CTA, the
         # same tiles and splits with the operands' roles exchanged, is faster: the narrow operand then costs 16 KB per K
         # block whatever the token count.  Timed alone at 128 tokens (28 weight matrices in turn): down 34.4 -> 30.4 us,
-        # q/k/v 16.6 -> 12.2, output 15.3 -> 11.3; the decode step of 128 requests 7.03 -> 6.66 ms.  At 64 tokens the
-        # same exchange wins alone (12.1 -> 10.8, 11.3 -> 9.7) and loses inside the step (4.97 -> 5.03 ms): not taken.
-        if 64 < M <= 128 and N % 8 == 0 and splits > 1:
+        # q/k/v 16.6 -> 12.2, output 15.3 -> 11.3; the decode step of 128 requests 7.03 -> 6.66 ms.  From 33 tokens it
+        # pays inside the step too since the fp32 partial sums leave the epilogue in whole lines (64 requests 4.71 ->
+        # 4.67 ms, 40 requests 4.22 -> 4.19); up to 32 tokens the weights stay on the rows (16 requests: 3.51 against 3.61).
+        if 32 < M <= 128 and N % 8 == 0 and splits > 1:
             return False, 128, splits
         return True, bn, splits
     # The tile width and the split of K with the least estimated time on the persistent CTAs (microseconds).

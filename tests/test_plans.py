@@ -23,8 +23,8 @@ def test_every_product_plan_is_one_the_kernel_takes(monkeypatch, pairs):
                     assert bn in WIDTHS_WEIGHT_ROWS and (M <= 128 or N % 8), (M, N, K, bn)
                     assert bn >= min(M, 256) or M > 256, (M, N, K, bn)      # the tokens of a tile fit its width
                 else:
-                    # tokens on the rows: many tokens, or 65 to 128 of them with a split K (tiles of 128 x 128)
-                    assert bn in WIDTHS_ROW_STORE and N % 8 == 0 and (M > 128 or (M > 64 and bn == 128 and splits > 1)), (M, N, K, bn)
+                    # tokens on the rows: many tokens, or 33 to 128 of them with a split K (tiles of 128 x 128)
+                    assert bn in WIDTHS_ROW_STORE and N % 8 == 0 and (M > 128 or (M > 32 and bn == 128 and splits > 1)), (M, N, K, bn)
                 if splits > 1:
                     assert kb // splits >= 4, (M, N, K, splits)             # a split keeps a few K blocks
 
@@ -39,8 +39,9 @@ def test_measured_product_choices(monkeypatch):
     assert not wide and bn >= 208 and splits == 2
     assert ops.tc_gemm_plan(8, 3584, 18944)[:2] == (True, 16)                 # decode: the weights take the MMA's rows
     assert ops.tc_gemm_plan(64, 37888, 3584)[:3] == (True, 64, 1)
-    assert ops.tc_gemm_plan(64, 3584, 18944)[:3] == (True, 64, 5)
-    assert ops.tc_gemm_plan(128, 4608, 3584)[:3] == (False, 128, 4)           # 65-128 tokens, split K: tokens on the rows
+    assert ops.tc_gemm_plan(32, 3584, 18944)[:3] == (True, 32, 5)
+    assert ops.tc_gemm_plan(64, 3584, 18944)[:3] == (False, 128, 5)           # 33-128 tokens, split K: tokens on the rows
+    assert ops.tc_gemm_plan(128, 4608, 3584)[:3] == (False, 128, 4)
     assert ops.tc_gemm_plan(100, 3584, 18944)[:3] == (False, 128, 5)
 
 
