@@ -133,6 +133,17 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                  ::"r"(bar), "h"(both) : "memory");
 }
+// 32 bytes per thread in one request (sm_100: 256-bit global accesses; the address is 32-byte aligned).  A plain load,
+// not the read-only path (see common.cuh on programmatic dependent launch).
+__device__ __forceinline__ void ld_global_32B(const float* ptr, float* v) {
+    asm volatile("ld.global.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]) : "l"(ptr) : "memory");
+}
+__device__ __forceinline__ void st_global_32B(void* ptr, const uint32_t* w) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 :: "l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -228,8 +239,8 @@ struct SmemLayout {
 // drains its own 128 accumulator rows.  Barriers: the first CTA's "full" barriers count the bytes of both CTAs'
 // loads; the MMA commits arrive on the "empty" and "accumulator full" barriers of both; the epilogue warps of
 // both arrive on the first CTA's "accumulator empty" barriers.
-template <int BN, int STAGES, bool X_CONTIGUOUS_OUT, int CTAS = 1, bool FOLD = true>
-__global__ void __launch_bounds__(THREADS, (X_CONTIGUOUS_OUT && FOLD) ? 5 : (!X_CONTIGUOUS_OUT && !FOLD) ? 3 : 1)
+template <int BN, int STAGES, bool X_CONTIGUOUS_OUT, int CTAS = 1, int FOLD = 1>
+__global__ void __launch_bounds__(THREADS, (X_CONTIGUOUS_OUT && FOLD != 0) ? 5 : (!X_CONTIGUOUS_OUT && FOLD == 0) ? 3 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y, const GemmParams p) {
     static_assert(CTAS == 1 || (CTAS == 2 && !X_CONTIGUOUS_OUT && BN % 16 == 0), "pairs serve the row store");
     using L = SmemLayout<BN, STAGES, X_CONTIGUOUS_OUT, CTAS>;
@@ -246,10 +257,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + L::TILES + L::N_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + L::TILES + L::N_BARS * 8 + 8);
 
-    // the folded work (row scales, fix-ups, the residual fold) is compiled into the FOLD variants only: the plain
+    // the folded work (row scales, fix-ups, the residual fold) is compiled into the FOLD != 0 variants only: the plain
     // weight stream keeps its small register count, so that the next kernel's CTAs find room beside it
-    const int fix = FOLD ? p.fix : 0;
-    const float* const scale_ssq = FOLD ? p.scale_ssq : nullptr;
+    const int fix = FOLD != 0 ? p.fix : 0;
+    const float* const scale_ssq = FOLD != 0 ? p.scale_ssq : nullptr;
+    // the row store's residual fold, and its rotary epilogue (FOLD == 2), live in variants of their own: each keeps
+    // its registers (compiled into one kernel, the 32-byte accesses of the one cost the other 8 % of its time)
+    [[maybe_unused]] const bool fix1_rows = !X_CONTIGUOUS_OUT && FOLD == 1 && fix == 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_kb = (p.K + BK - 1) / BK;
     const int kb_begin = blockIdx.z * p.k_blocks_per_split;
@@ -592,7 +606,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     continue;
                 }
             }
-            if constexpr (!X_CONTIGUOUS_OUT && FOLD) {
+            if constexpr (!X_CONTIGUOUS_OUT && FOLD == 2) {
                 if (fix == 2) {
                     // Row store with bias, rotary and the paged K/V write folded in (one split; the tile's columns are
                     // whole heads): this thread's token row holds, per head, the pairs (d, d + hd / 2) that the half-split
@@ -621,6 +635,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         const bool rotate = !is_v && p.rot != 0;
 #pragma unroll 1
                         for (int c = 0; c < half; c += 16) {
+                            // the tables' 16 values of this token (32 bytes per request, asked for before the
+                            // accumulator is read), then 32 bytes per store: whole sectors
+                            float cs[16], sn[16];
+                            if (rotate && dst != nullptr) {
+                                ld_global_32B(ct + c, cs); ld_global_32B(ct + c + 8, cs + 8);
+                                ld_global_32B(st + c, sn); ld_global_32B(st + c + 8, sn + 8);
+                            }
                             uint32_t lo[16], hi[16];
                             __syncwarp();
                             tmem_ld16(acc + hc + c, lo);
@@ -630,17 +651,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                             uint32_t w1[8], w2[8];
 #pragma unroll
                             for (int q4 = 0; q4 < 4; ++q4) {
-                                float4 b1 = make_float4(0.f, 0.f, 0.f, 0.f), b2 = b1, c4 = b1, s4 = b1;
+                                float4 b1 = make_float4(0.f, 0.f, 0.f, 0.f), b2 = b1;
                                 if (p.bias) {
                                     b1 = *reinterpret_cast<const float4*>(p.bias + y0 + hc + c + 4 * q4);
                                     b2 = *reinterpret_cast<const float4*>(p.bias + y0 + hc + half + c + 4 * q4);
                                 }
-                                if (rotate) {
-                                    c4 = *reinterpret_cast<const float4*>(ct + c + 4 * q4);
-                                    s4 = *reinterpret_cast<const float4*>(st + c + 4 * q4);
-                                }
                                 const float bb1[4] = {b1.x, b1.y, b1.z, b1.w}, bb2[4] = {b2.x, b2.y, b2.z, b2.w};
-                                const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+                                const float* cc = cs + 4 * q4;
+                                const float* ss = sn + 4 * q4;
                                 float o1[4], o2[4];
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
@@ -655,10 +673,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                                 v = __floats2bfloat162_rn(o2[0], o2[1]); w2[2 * q4] = *reinterpret_cast<uint32_t*>(&v);
                                 v = __floats2bfloat162_rn(o2[2], o2[3]); w2[2 * q4 + 1] = *reinterpret_cast<uint32_t*>(&v);
                             }
-                            uint4* d1 = reinterpret_cast<uint4*>(dst + c);
-                            uint4* d2 = reinterpret_cast<uint4*>(dst + half + c);
-                            d1[0] = make_uint4(w1[0], w1[1], w1[2], w1[3]); d1[1] = make_uint4(w1[4], w1[5], w1[6], w1[7]);
-                            d2[0] = make_uint4(w2[0], w2[1], w2[2], w2[3]); d2[1] = make_uint4(w2[4], w2[5], w2[6], w2[7]);
+                            st_global_32B(dst + c, w1);
+                            st_global_32B(dst + half + c, w2);
                         }
                     }
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -669,7 +685,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
             int c_begin = 0;
             [[maybe_unused]] bool folded_in_lines = false;
-            if constexpr (!X_CONTIGUOUS_OUT && FOLD && GW == 64) {
+            if constexpr (!X_CONTIGUOUS_OUT && FOLD == 1 && GW == 64) {
                 if (fix == 1 && scale_ssq == nullptr && n_kb > 0) {
                     // The residual fold in whole lines.  A thread that owns a token row would touch 32 different
                     // 128-byte lines of the fp32 stream per instruction with its warp (rows lie kilobytes apart), so
@@ -802,7 +818,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                         // the fold's residual values of the whole group go out at once: one round trip to memory per
                         // group of GW columns, not one per 16
                         float4 xg[GW / 4];
-                        const bool prefetched = fix == 1 && alive && xr < p.x_rows;
+                        const bool prefetched = fix1_rows && alive && xr < p.x_rows;
                         if (prefetched) {
                             const float4* src = reinterpret_cast<const float4*>(p.resid + (size_t)xr * p.y_rows + y0 + gq * GW);
 #pragma unroll
@@ -814,7 +830,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                             __syncwarp();
                             tmem_ld16(acc + gq * GW + cc, r);
                             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                            if (fix == 1) fold16(r, y0 + gq * GW + cc, prefetched ? &xg[cc / 4] : nullptr);
+                            if (fix1_rows) fold16(r, y0 + gq * GW + cc, prefetched ? &xg[cc / 4] : nullptr);
 #pragma unroll
                             for (int q = 0; q < 8; ++q) {
                                 __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * q]) * row_scale, __uint_as_float(r[2 * q + 1]) * row_scale);
@@ -838,7 +854,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                     for (int q = 0; q < 16; ++q) r[q] = 0u;
                 }
                 if constexpr (!X_CONTIGUOUS_OUT) {
-                    if (fix == 1) fold16(r, y0 + c, nullptr);
+                    if (fix1_rows) fold16(r, y0 + c, nullptr);
                     if (scale_ssq != nullptr) {
 #pragma unroll
                         for (int q = 0; q < 16; ++q) r[q] = __float_as_uint(__uint_as_float(r[q]) * row_scale);
@@ -893,7 +909,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             __syncwarp();
             if (lane == 0) hand_back(buf);
             if constexpr (!X_CONTIGUOUS_OUT) {
-                if (fix == 1 && alive && xr < p.x_rows) p.ssq_out[(size_t)(tile / p.tiles_x) * p.x_rows + xr] = row_ssq;
+                if (fix1_rows && alive && xr < p.x_rows) p.ssq_out[(size_t)(tile / p.tiles_x) * p.x_rows + xr] = row_ssq;
             }
             if constexpr (X_CONTIGUOUS_OUT && BN <= 128) {
                 if (fix != 0) {
@@ -1048,7 +1064,7 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, long long ld, i
     return r == CUDA_SUCCESS ? 0 : PYRE_ERR_BAD_ARG;
 }
 
-template <int BN, int STAGES, bool XC, int CTAS = 1, bool FOLD = true>
+template <int BN, int STAGES, bool XC, int CTAS = 1, int FOLD = 1>
 int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, dim3 grid, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES, XC, CTAS>;
     static_assert(L::TOTAL <= 232448, "the ring does not fit into shared memory");
@@ -1084,11 +1100,16 @@ int launch(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, di
     return (int)cudaGetLastError();
 }
 
-// The row store of one CTA per tile: the variant without the folded work exists at 128 columns only.
+// The row store of one CTA per tile: the variant without the folded work exists at 128 columns only, the one with the
+// rotary epilogue at 128 and 256.
 template <int BN, int STAGES>
 int launch_rows(const CUtensorMap& mx, const CUtensorMap& my, const GemmParams& p, dim3 grid, cudaStream_t stream, bool fold) {
     if constexpr (BN == 128) {
-        if (!fold) return launch<BN, STAGES, false, 1, false>(mx, my, p, grid, stream);
+        if (!fold) return launch<BN, STAGES, false, 1, 0>(mx, my, p, grid, stream);
+    }
+    if (p.fix == 2) {          // the rotary epilogue: tiles of whole heads, 128 or 256 columns
+        if constexpr (BN == 128 || BN == 256) return launch<BN, STAGES, false, 1, 2>(mx, my, p, grid, stream);
+        else return PYRE_ERR_BAD_ARG;
     }
     return launch<BN, STAGES, false>(mx, my, p, grid, stream);
 }
@@ -1149,6 +1170,8 @@ static int gemm_tc_impl(const void* X, int x_rows, long long ldx, const void* Y,
                 y_rows != (fx->nh + 2 * fx->nkv) * fx->hd || fx->page_size <= 0 || (fx->kv_cache && !fx->slot_mapping) ||
                 (fx->rot && (!fx->cos_t || !fx->sin_t)))
                 return PYRE_ERR_UNSUPPORTED;
+            // the epilogue moves 32 bytes per request: tables, queries and cache rows start on such boundaries
+            if ((((uintptr_t)fx->q_out | (uintptr_t)fx->kv_cache | (uintptr_t)fx->cos_t | (uintptr_t)fx->sin_t) & 31) != 0) return PYRE_ERR_UNSUPPORTED;
         }
         if (fx->fix != 0 && fx->fix != 1 && fx->fix != 2) return PYRE_ERR_BAD_ARG;
     } else if (fx && (fx->fix != 0 || fx->scale_ssq != nullptr)) {
@@ -1218,6 +1241,13 @@ static int gemm_tc_impl(const void* X, int x_rows, long long ldx, const void* Y,
         // one pair per TPC stays resident (a split K keeps one pair per tile and split)
         const long long pairs = splits > 1 ? n_tiles : (n_tiles < sm_count / 2 ? n_tiles : sm_count / 2);
         dim3 grid2((unsigned)(2 * pairs), 1, splits);
+        if (p.fix == 2) {      // the rotary epilogue: tiles of whole heads
+            switch (bn) {
+                case 128: return launch<128, 8, false, 2, 2>(mx, my, p, grid2, stream);
+                case 256: return launch<256, 6, false, 2, 2>(mx, my, p, grid2, stream);
+                default: return PYRE_ERR_BAD_ARG;
+            }
+        }
         switch (bn) {
             case 128: return launch<128, 8, false, 2>(mx, my, p, grid2, stream);
             case 160: return launch<160, 7, false, 2>(mx, my, p, grid2, stream);
@@ -1234,8 +1264,8 @@ static int gemm_tc_impl(const void* X, int x_rows, long long ldx, const void* Y,
     const bool fold = p.fix != 0 || p.scale_ssq != nullptr;
 #define GO(BN_, ST_)                                                              \
     rc = !xc ? launch_rows<BN_, ST_>(mx, my, p, grid, stream, fold)                               \
-        : fold ? launch<BN_, ST_, true, 1, true>(mx, my, p, grid, stream)                           \
-               : launch<BN_, ST_, true, 1, false>(mx, my, p, grid, stream)
+        : fold ? launch<BN_, ST_, true, 1, 1>(mx, my, p, grid, stream)                              \
+               : launch<BN_, ST_, true, 1, 0>(mx, my, p, grid, stream)
     switch (bn) {
         case 16: GO(16, 10); break;
         case 32: GO(32, 10); break;
@@ -1244,10 +1274,10 @@ static int gemm_tc_impl(const void* X, int x_rows, long long ldx, const void* Y,
         case 256: GO(256, 4); break;
         // widths between 128 and 256 exist for the row-store orientation only: they let the planner pick the
         // tile count that fills the rounds of the persistent CTAs best
-        case 160: if (xc) return PYRE_ERR_BAD_ARG; rc = launch<160, 5, false>(mx, my, p, grid, stream); break;
-        case 192: if (xc) return PYRE_ERR_BAD_ARG; rc = launch<192, 5, false>(mx, my, p, grid, stream); break;
-        case 208: if (xc) return PYRE_ERR_BAD_ARG; rc = launch<208, 5, false>(mx, my, p, grid, stream); break;
-        case 224: if (xc) return PYRE_ERR_BAD_ARG; rc = launch<224, 5, false>(mx, my, p, grid, stream); break;
+        case 160: if (xc || p.fix == 2) return PYRE_ERR_BAD_ARG; rc = launch<160, 5, false>(mx, my, p, grid, stream); break;
+        case 192: if (xc || p.fix == 2) return PYRE_ERR_BAD_ARG; rc = launch<192, 5, false>(mx, my, p, grid, stream); break;
+        case 208: if (xc || p.fix == 2) return PYRE_ERR_BAD_ARG; rc = launch<208, 5, false>(mx, my, p, grid, stream); break;
+        case 224: if (xc || p.fix == 2) return PYRE_ERR_BAD_ARG; rc = launch<224, 5, false>(mx, my, p, grid, stream); break;
         default: return PYRE_ERR_BAD_ARG;
     }
 #undef GO
