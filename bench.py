@@ -55,6 +55,12 @@ PAGE_SIZE = 16
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
+# Decode steps run untimed before the W warm-up steps of a decode measurement: the prompts before them are a burst of
+# dense products that leaves the SM clock low under the power cap for a while, and a decode step measured right after
+# it reads 2-3 % slower than the same step a tenth of a second later.
+SETTLE_STEPS = 32
+
+
 def load_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.is_file():
@@ -218,11 +224,11 @@ def run_ours(args) -> dict:
     B = args.batch
     steps, warmup = args.steps, max(args.warmup, 3)
     biggest = max(B, 64 if not args.skip_points else B)
-    tokens_needed = biggest * (PROMPT_LEN + 64 + warmup + steps + PAGE_SIZE) + B * (2 * B + 64) + 2 * CONTEXT
+    tokens_needed = biggest * (PROMPT_LEN + 64 + SETTLE_STEPS + warmup + steps + PAGE_SIZE) + B * (2 * B + 64) + 2 * CONTEXT
     torch.cuda.set_device(0)
     engine = Engine(config=cfg, seed=0, dtype="bfloat16", device="cuda:0", page_size=PAGE_SIZE,
                     max_cache_tokens=tokens_needed, max_num_seqs=biggest, max_num_batched_tokens=PROMPT_LEN,
-                    prefill_chunk=PROMPT_LEN, max_model_len=CONTEXT)
+                    prefill_chunk=PROMPT_LEN, max_model_len=max(CONTEXT, PROMPT_LEN + SETTLE_STEPS + warmup + steps + 2 * B + 128))
     stepper, cache = engine.stepper, engine.cache
     vocab = cfg.vocab_size
     rng = np.random.default_rng(0)
@@ -267,6 +273,7 @@ def run_ours(args) -> dict:
         for r in reqs:
             cache.begin(r)
             stepper.step([StepEntry(r, rng.integers(0, vocab, PROMPT_LEN).tolist(), [])])
+        n_warm += SETTLE_STEPS
         toks = rng.integers(0, vocab, (n_warm + n_steps, batch))
 
         def one(k):
@@ -344,12 +351,12 @@ def run_ours(args) -> dict:
     # ---------------------------------------------------------------- end to end through Engine.step
     # every request must outlive the timed steps: the first one decodes while the others' prompts (cut to what the
     # token budget leaves beside the decoded tokens) are still being read, about B * PROMPT_LEN / (budget - B) steps
-    sp = SamplingParams(max_new_tokens=warmup + steps + 2 * B + 64, ignore_eos=True)
+    sp = SamplingParams(max_new_tokens=SETTLE_STEPS + warmup + steps + 2 * B + 64, ignore_eos=True)
     sids = [engine.add_request(rng.integers(0, vocab, PROMPT_LEN).tolist(), params=sp) for _ in range(B)]
     live = [engine._requests[sid] for sid in sids]
     while any(not r.generated for r in live):
         engine.step()                      # the prompts, one per step under the token budget
-    for _ in range(warmup):
+    for _ in range(SETTLE_STEPS + warmup):
         engine.step()
     torch.cuda.synchronize()
     up0 = stepper._staging.bytes_uploaded + engine.sampler.bytes_uploaded
@@ -371,7 +378,7 @@ def run_ours(args) -> dict:
     # decode tokens/s at longer contexts (this model) and at the 14B and 32B shapes (full layer counts, batch 8,
     # 2,048-token prompts): device-timed like `value`, each with its fraction of the copy roofline beside it
     if not args.skip_points and not args.skip_sizes:
-        def decode_point(eng, cfg_raw_, n_layers, batch, context, n_warm=8, n_steps=24):
+        def decode_point(eng, cfg_raw_, n_layers, batch, context, n_warm=SETTLE_STEPS + 8, n_steps=24):
             st_, cache_ = eng.stepper, eng.cache
             wb, kvb, _ = model_numbers(cfg_raw_, n_layers)
             reqs = [("x", batch, context, i) for i in range(batch)]
@@ -398,7 +405,7 @@ def run_ours(args) -> dict:
         del stepper, cache, engine
         torch.cuda.empty_cache()
         long_cfg = dict(cfg_raw, max_position_embeddings=40960)
-        eng = Engine(config=config_from_dict(long_cfg), seed=0, dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=8 * 33000,
+        eng = Engine(config=config_from_dict(long_cfg), seed=0, dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=8 * (32768 + SETTLE_STEPS + 256),
                      max_num_seqs=8, max_num_batched_tokens=8192, prefill_chunk=8192, max_model_len=40960)
         for batch, context in ((1, 8192), (1, 32768), (8, 8192), (8, 32768)):
             points[f"decode_b{batch}_ctx{context // 1024}k"], points[f"hbm_frac_b{batch}_ctx{context // 1024}k"] = \
@@ -406,7 +413,7 @@ def run_ours(args) -> dict:
         del eng
         torch.cuda.empty_cache()
         # many requests at the benchmark's context
-        eng = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=256 * (PROMPT_LEN + 64),
+        eng = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=256 * (PROMPT_LEN + SETTLE_STEPS + 64),
                      max_num_seqs=256, max_num_batched_tokens=PROMPT_LEN, prefill_chunk=PROMPT_LEN, max_model_len=CONTEXT)
         for batch in (128, 256):
             points[f"decode_b{batch}"], points[f"hbm_frac_b{batch}"] = decode_point(eng, cfg_raw, layers, batch, PROMPT_LEN, n_steps=16)
@@ -423,7 +430,8 @@ def run_ours(args) -> dict:
 
     return {
         "metric": "decode tok/s (Qwen2.5-7B shape, batch 8, 2,048-token prompts)", "value": round(value, 1),
-        "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 4),
+        "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "untimed_steps": SETTLE_STEPS + warmup,
+        "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": bench_config(cfg_raw, layers, layers_full, B),
         "clocks": clock_summary, "e2e": e2e, "gpu_launches": info["launches"], "prefill": prefill,
@@ -548,7 +556,7 @@ def run_sweep(args) -> dict:
     weight_bytes, kv_per_token, flops = model_numbers(cfg_raw, layers)
     grid = [(1, 512), (1, 8192), (1, 32768), (8, 512), (8, 2048), (8, 8192), (8, 32768), (32, 2048), (64, 512), (64, 2048),
             (64, 8192), (128, 2048)]
-    biggest = max(b * (c + 64) for b, c in grid)
+    biggest = max(b * (c + SETTLE_STEPS + 64) for b, c in grid)
     eng = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=PAGE_SIZE, max_cache_tokens=biggest + 8192,
                  max_num_seqs=128, max_num_batched_tokens=8192, prefill_chunk=8192, max_model_len=40960)
     st, cache = eng.stepper, eng.cache
@@ -565,7 +573,7 @@ def run_sweep(args) -> dict:
             cache.begin(r)
             for lo in range(0, ctx, 8192):
                 st.step([StepEntry(r, rng.integers(0, vocab, min(8192, ctx - lo)).tolist(), [])])
-        n_warm, n_steps = 8, 32
+        n_warm, n_steps = SETTLE_STEPS + 8, 32
         toks = rng.integers(0, vocab, (n_warm + n_steps, batch))
         for k in range(n_warm):
             ops.sample(st.step([StepEntry(r, [int(toks[k, i])], [0]) for i, r in enumerate(reqs)]))
