@@ -116,6 +116,11 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// 32 bytes per thread in one request (sm_100: 256-bit global stores; the address is 32-byte aligned): whole sectors
+__device__ __forceinline__ void st_global_32B(void* ptr, const uint32_t* w) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 :: "l"(ptr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]) : "memory");
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -519,18 +524,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 if (p.key_splits > 1) {
                     if (row_ok) {
-                        float4* dst = reinterpret_cast<float4*>(p.part_o + piece_at * HD + c);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q)
-                            dst[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                        st_global_32B(p.part_o + piece_at * HD + c, r);
+                        st_global_32B(p.part_o + piece_at * HD + c + 8, r + 8);
                     }
                 } else if (row_ok) {
                     uint32_t w[8];
 #pragma unroll
                     for (int q = 0; q < 8; ++q) w[q] = pack_bf16(__uint_as_float(r[2 * q]) * inv, __uint_as_float(r[2 * q + 1]) * inv);
-                    uint4* dst = reinterpret_cast<uint4*>(orow + c);
-                    dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                    dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                    st_global_32B(orow + c, w);
                 }
             }
         }
@@ -666,7 +667,7 @@ PYRE_API int pyre_attention_prefill_tc(const void* q, const void* cache, void* o
     if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || page_size < 4 || (page_size & (page_size - 1)) || min_len < 1)
         return PYRE_ERR_UNSUPPORTED;
     const long long kv_rows = n_pages * 2 * nkv * page_size;
-    if (((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)out & 15) || kv_rows >= (1ll << 31) || n_pages <= 0)
+    if (((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || ((uintptr_t)out & 31) || kv_rows >= (1ll << 31) || n_pages <= 0)
         return PYRE_ERR_UNSUPPORTED;
     TcParams p;
     p.out = (__nv_bfloat16*)out;
@@ -676,7 +677,7 @@ PYRE_API int pyre_attention_prefill_tc(const void* q, const void* cache, void* o
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.box_rows = page_size < BN ? page_size : BN;
     p.window = window; p.min_len = min_len; p.scale = scale; p.err_flag = err_flag; p.n_pages = n_pages;
-    if (key_splits < 1 || key_splits > 32 || (key_splits > 1 && (!part_o || !part_ml || ((uintptr_t)part_o & 15)))) return PYRE_ERR_BAD_ARG;
+    if (key_splits < 1 || key_splits > 32 || (key_splits > 1 && (!part_o || !part_ml || ((uintptr_t)part_o & 31)))) return PYRE_ERR_BAD_ARG;
     p.key_splits = key_splits; p.part_o = part_o; p.part_ml = part_ml;
     CUtensorMap mq, mkv;
     memset(&mq, 0, sizeof(mq));
