@@ -540,12 +540,17 @@ def prefill_key_splits(n_items: int, mean_tiles: float, n_tokens: int, n_heads: 
     while SMs would stand idle: an SM runs the tiles of one CTA alone as fast as those of two together, so what
     counts is that every SM has a CTA, and a share costs its partial output's trip through memory and a second
     kernel (measured: 2,048 tokens after 8,192, 448 items, 292 us whole, 350 in two shares; 512 tokens after 30,720,
-    112 items, 492 us whole, 298 in two shares, 275 in five).  So: only with fewer items than SMs, as many shares as
-    fill two CTAs per SM, each of at least 16 key tiles (1,024 keys)."""
+    112 items, 492 us whole, 294 in two shares, 269 in five).  So: only with fewer items than SMs, as many shares as
+    fill two CTAs per SM, each of at least 16 key tiles (1,024 keys); or as many as fill them twice over, if every
+    share then still has 80 key tiles (two rounds of 97 tiles beat one round of 242; two rounds of 65 lose to one of
+    131: 640 tokens after 16,384, 191 us in four shares against 186 in two)."""
     sms = sm_count()
     if n_items >= sms:
         return 1
     s = min(MAX_KEY_SPLITS, 2 * sms // max(n_items, 1), int(mean_tiles // 16))
+    twice = min(MAX_KEY_SPLITS, 4 * sms // max(n_items, 1))
+    if twice > s and mean_tiles / twice >= 80:
+        s = twice
     while s > 1 and n_tokens * n_heads * s * head_dim * 4 > KEY_SPLIT_SCRATCH_BYTES:
         s -= 1
     return max(1, s)

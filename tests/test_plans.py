@@ -104,7 +104,9 @@ def test_shares_of_the_keys_in_the_prompt_attention(monkeypatch):
     assert ops.prefill_key_splits(16 * 28, 17.0, 2048, 28, 128) == 1            # 2,048 fresh tokens
     assert ops.prefill_key_splits(16 * 28, 144.0, 2048, 28, 128) == 1           # 2,048 after 8,192: every SM is busy
     assert ops.prefill_key_splits(8 * 28, 136.0, 1024, 28, 128) == 1            # 224 items
-    assert ops.prefill_key_splits(4 * 28, 484.0, 512, 28, 128) == 2             # 512 after 30,720: 112 items
+    assert ops.prefill_key_splits(4 * 28, 484.0, 512, 28, 128) == 5             # 512 after 30,720: 112 items, two rounds of 97 tiles
+    assert ops.prefill_key_splits(4 * 28, 133.0, 512, 28, 128) == 2             # 512 after 8,192: one round
+    assert ops.prefill_key_splits(5 * 28, 262.0, 640, 28, 128) == 2             # 640 after 16,384: two rounds would leave 65 tiles each
     assert ops.prefill_key_splits(4 * 28, 5.0, 512, 28, 128) == 1               # 512 fresh tokens: nothing to share
     assert ops.prefill_key_splits(1 * 28, 481.0, 128, 28, 128) == 8             # one query tile per head
     assert ops.prefill_key_splits(1 * 28, 40.0, 128, 28, 128) == 2              # shares of at least 16 tiles
