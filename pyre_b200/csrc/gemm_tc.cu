@@ -1248,15 +1248,20 @@ static int gemm_tc_impl(const void* X, int x_rows, long long ldx, const void* Y,
                 default: return PYRE_ERR_BAD_ARG;
             }
         }
+        // plain products (decode steps of 129-256 requests) run the variant without the folded work: few registers,
+        // so that the next kernels' CTAs find room beside the draining pairs
+        const bool plain = p.fix == 0 && p.scale_ssq == nullptr;
+#define GO2(BN_, ST_) return plain ? launch<BN_, ST_, false, 2, 0>(mx, my, p, grid2, stream) : launch<BN_, ST_, false, 2, 1>(mx, my, p, grid2, stream)
         switch (bn) {
-            case 128: return launch<128, 8, false, 2>(mx, my, p, grid2, stream);
-            case 160: return launch<160, 7, false, 2>(mx, my, p, grid2, stream);
-            case 192: return launch<192, 7, false, 2>(mx, my, p, grid2, stream);
-            case 208: return launch<208, 7, false, 2>(mx, my, p, grid2, stream);
-            case 224: return launch<224, 6, false, 2>(mx, my, p, grid2, stream);
-            case 256: return launch<256, 6, false, 2>(mx, my, p, grid2, stream);
+            case 128: GO2(128, 8);
+            case 160: GO2(160, 7);
+            case 192: GO2(192, 7);
+            case 208: GO2(208, 7);
+            case 224: GO2(224, 6);
+            case 256: GO2(256, 6);
             default: return PYRE_ERR_BAD_ARG;
         }
+#undef GO2
     }
     dim3 grid((unsigned)ctas, 1, splits);
     // the plain products run the variant without that code: the weight stream always, the row store at the one width
